@@ -1,0 +1,547 @@
+/*
+ * mnemo_oracle.c -- CPU restatement of the reference's Q4_K / Q6_K hot path.
+ *
+ * TEST INFRASTRUCTURE ONLY: the checker for the CUDA library and the timed CPU
+ * baseline. The product path never calls into this file.
+ *
+ * Build with -ffp-contract=off: the dequant expressions must round exactly as
+ * the numpy float32 statements of tools/validate_dequant.py do (product first,
+ * then subtraction), which is also what gguf.quants.dequantize produces.
+ *
+ * Parity pin: no golden vectors exist in the reference for this path; see the
+ * header of mnemo_oracle.h for how the restatement is pinned.
+ */
+#include "mnemo_oracle.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* ------------------------------------------------------------------------ */
+/* helpers                                                                   */
+/* ------------------------------------------------------------------------ */
+
+/* kernels.cu:41-43 (__half2float): exact, subnormals included
+ * (forward.c:1197-1202 spells the subnormal branch out on the host). */
+float mo_f16_to_f32(uint16_t h)
+{
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1Fu;
+    uint32_t man = h & 0x3FFu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else { /* subnormal: normalise */
+            int e = -1;
+            do {
+                man <<= 1;
+                e++;
+            } while (!(man & 0x400u));
+            man &= 0x3FFu;
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | (man << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7F800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 127 - 15) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+uint16_t mo_f32_to_f16(float f)
+{
+    uint32_t x;
+    memcpy(&x, &f, 4);
+    uint32_t sign = (x >> 16) & 0x8000u;
+    uint32_t ex = (x >> 23) & 0xFFu;
+    uint32_t man = x & 0x7FFFFFu;
+    if (ex == 255) return (uint16_t)(sign | 0x7C00u | (man ? 0x200u : 0));
+    int e = (int)ex - 127 + 15;
+    if (e >= 31) return (uint16_t)(sign | 0x7C00u);
+    if (e <= 0) {
+        if (e < -10) return (uint16_t)sign;
+        man |= 0x800000u;
+        int shift = 14 - e; /* 14..24 */
+        uint32_t half = man >> shift;
+        uint32_t rem = man & ((1u << shift) - 1);
+        uint32_t mid = 1u << (shift - 1);
+        if (rem > mid || (rem == mid && (half & 1))) half++;
+        return (uint16_t)(sign | half);
+    }
+    uint32_t half = ((uint32_t)e << 10) | (man >> 13);
+    uint32_t rem = man & 0x1FFFu;
+    if (rem > 0x1000u || (rem == 0x1000u && (half & 1))) half++;
+    return (uint16_t)(sign | half);
+}
+
+/* kernels.cu:45-53 == validate_dequant.py:53-61 */
+void mo_get_scale_min_k4(int j, const uint8_t *q, uint8_t *sc, uint8_t *m)
+{
+    if (j < 4) {
+        *sc = q[j] & 63;
+        *m = q[j + 4] & 63;
+    } else {
+        *sc = (uint8_t)((q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4));
+        *m = (uint8_t)((q[j + 4] >> 4) | ((q[j] >> 6) << 4));
+    }
+}
+
+static uint16_t rd16(const uint8_t *p) { return (uint16_t)(p[0] | (p[1] << 8)); }
+
+/* ------------------------------------------------------------------------ */
+/* integer unpack                                                            */
+/* ------------------------------------------------------------------------ */
+
+/* kernels.cu:20-25 layout; validate_dequant.py:92-113 weight order:
+ * qs chunk c (32 bytes): low nibbles -> weights 64c..64c+31 with (sc,m)[2c],
+ * high nibbles -> 64c+32..64c+63 with (sc,m)[2c+1]. */
+void mo_unpack_q4k_block(const uint8_t *blk, uint16_t *d_bits, uint16_t *dmin_bits,
+                         uint8_t sc[8], uint8_t m[8], uint8_t q[256])
+{
+    *d_bits = rd16(blk);
+    *dmin_bits = rd16(blk + 2);
+    for (int j = 0; j < 8; j++) mo_get_scale_min_k4(j, blk + 4, &sc[j], &m[j]);
+    const uint8_t *qs = blk + 16;
+    for (int c = 0; c < 4; c++)
+        for (int l = 0; l < 32; l++) {
+            q[64 * c + l] = qs[32 * c + l] & 0xF;
+            q[64 * c + 32 + l] = qs[32 * c + l] >> 4;
+        }
+}
+
+/* kernels.cu:27-32 layout; validate_dequant.py:286-317 order. */
+void mo_unpack_q6k_block(const uint8_t *blk, uint16_t *d_bits, int8_t scales[16], int8_t q[256])
+{
+    const uint8_t *ql = blk, *qh = blk + 128;
+    for (int i = 0; i < 16; i++) scales[i] = (int8_t)blk[192 + i];
+    *d_bits = rd16(blk + 208);
+    for (int h = 0; h < 2; h++)
+        for (int g = 0; g < 4; g++)
+            for (int l = 0; l < 32; l++) {
+                uint8_t lo4 = (uint8_t)((ql[64 * h + 32 * (g & 1) + l] >> (4 * (g >> 1))) & 0xF);
+                uint8_t hi2 = (uint8_t)((qh[32 * h + l] >> (2 * g)) & 3);
+                q[128 * h + 32 * g + l] = (int8_t)((int)((hi2 << 4) | lo4) - 32);
+            }
+}
+
+/* ------------------------------------------------------------------------ */
+/* dequant                                                                   */
+/* ------------------------------------------------------------------------ */
+
+static void dequant_q4k_block(const uint8_t *blk, float out[256])
+{
+    uint16_t db, mb;
+    uint8_t sc[8], m[8], q[256];
+    mo_unpack_q4k_block(blk, &db, &mb, sc, m, q);
+    float d = mo_f16_to_f32(db), dmin = mo_f16_to_f32(mb);
+    for (int s = 0; s < 8; s++) {
+        float ds = d * (float)sc[s];    /* validate_dequant.py:94,97 */
+        float ms = dmin * (float)m[s];  /* validate_dequant.py:95,98 */
+        for (int l = 0; l < 32; l++) out[32 * s + l] = ds * (float)q[32 * s + l] - ms;
+    }
+}
+
+static void dequant_q6k_block(const uint8_t *blk, float out[256])
+{
+    uint16_t db;
+    int8_t sc[16], q[256];
+    mo_unpack_q6k_block(blk, &db, sc, q);
+    float d = mo_f16_to_f32(db);
+    for (int g = 0; g < 16; g++) {
+        float s = d * (float)sc[g]; /* validate_dequant.py:309 */
+        for (int l = 0; l < 16; l++) out[16 * g + l] = s * (float)q[16 * g + l];
+    }
+}
+
+static inline int bpr_of(int n_cols) { return (n_cols + 255) / 256; }
+
+void mo_dequant_q4k(const uint8_t *w, int n_rows, int n_cols, float *out)
+{
+    int bpr = bpr_of(n_cols);
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < n_rows; r++) {
+        float tmp[256];
+        for (int b = 0; b < bpr; b++) {
+            dequant_q4k_block(w + ((size_t)r * bpr + b) * MO_Q4K_BLOCK_BYTES, tmp);
+            int n = n_cols - b * 256 < 256 ? n_cols - b * 256 : 256;
+            memcpy(out + (size_t)r * n_cols + b * 256, tmp, (size_t)n * sizeof(float));
+        }
+    }
+}
+
+void mo_dequant_q6k(const uint8_t *w, int n_rows, int n_cols, float *out)
+{
+    int bpr = bpr_of(n_cols);
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < n_rows; r++) {
+        float tmp[256];
+        for (int b = 0; b < bpr; b++) {
+            dequant_q6k_block(w + ((size_t)r * bpr + b) * MO_Q6K_BLOCK_BYTES, tmp);
+            int n = n_cols - b * 256 < 256 ? n_cols - b * 256 : 256;
+            memcpy(out + (size_t)r * n_cols + b * 256, tmp, (size_t)n * sizeof(float));
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------ */
+/* matvecs                                                                   */
+/* ------------------------------------------------------------------------ */
+
+/* One Q4_K row dot. Tail rule of the kernels (kernels.cu:124,131): a group of
+ * four consecutive columns contributes only if all four are < n_cols. */
+static void row_dot_q4k(const uint8_t *row, const float *x, int n_cols, float *s32, double *s64,
+                        double *sabs)
+{
+    int bpr = bpr_of(n_cols);
+    float acc = 0.0f;
+    double acc64 = 0.0, a = 0.0;
+    float tmp[256];
+    for (int b = 0; b < bpr; b++) {
+        dequant_q4k_block(row + (size_t)b * MO_Q4K_BLOCK_BYTES, tmp);
+        int base = b * 256;
+        for (int c = 0; c < 256; c += 4) {
+            if (base + c + 3 >= n_cols) continue;
+            for (int i = 0; i < 4; i++) {
+                float w = tmp[c + i], xv = x[base + c + i];
+                acc += w * xv;
+                acc64 += (double)w * (double)xv;
+                a += fabs((double)w * (double)xv);
+            }
+        }
+    }
+    *s32 = acc;
+    *s64 = acc64;
+    *sabs = a;
+}
+
+/* Q6_K row dot. Tail rule: per element (kernels.cu:474). */
+static void row_dot_q6k(const uint8_t *row, const float *x, int n_cols, float *s32, double *s64,
+                        double *sabs)
+{
+    int bpr = bpr_of(n_cols);
+    float acc = 0.0f;
+    double acc64 = 0.0, a = 0.0;
+    float tmp[256];
+    for (int b = 0; b < bpr; b++) {
+        dequant_q6k_block(row + (size_t)b * MO_Q6K_BLOCK_BYTES, tmp);
+        int base = b * 256;
+        for (int c = 0; c < 256 && base + c < n_cols; c++) {
+            float w = tmp[c], xv = x[base + c];
+            acc += w * xv;
+            acc64 += (double)w * (double)xv;
+            a += fabs((double)w * (double)xv);
+        }
+    }
+    *s32 = acc;
+    *s64 = acc64;
+    *sabs = a;
+}
+
+void mo_matvec_q4k(const uint8_t *w, const float *x, float *y, double *y64, double *abs_dot,
+                   int n_rows, int n_cols)
+{
+    size_t rb = (size_t)bpr_of(n_cols) * MO_Q4K_BLOCK_BYTES;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < n_rows; r++) {
+        float s;
+        double s64, a;
+        row_dot_q4k(w + (size_t)r * rb, x, n_cols, &s, &s64, &a);
+        y[r] = s;
+        if (y64) y64[r] = s64;
+        if (abs_dot) abs_dot[r] = a;
+    }
+}
+
+void mo_matvec_q4k_add(const uint8_t *w, const float *x, const float *residual, float *y,
+                       double *y64, int n_rows, int n_cols)
+{
+    size_t rb = (size_t)bpr_of(n_cols) * MO_Q4K_BLOCK_BYTES;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < n_rows; r++) {
+        float s;
+        double s64, a;
+        row_dot_q4k(w + (size_t)r * rb, x, n_cols, &s, &s64, &a);
+        y[r] = s + residual[r]; /* kernels.cu:197 */
+        if (y64) y64[r] = s64 + (double)residual[r];
+    }
+}
+
+void mo_matvec_q4k_qkv(const uint8_t *wq, const uint8_t *wk, const uint8_t *wv, const float *x,
+                       float *q, float *k, float *v, int q_rows, int kv_rows, int n_cols)
+{
+    mo_matvec_q4k(wq, x, q, NULL, NULL, q_rows, n_cols);
+    mo_matvec_q4k(wk, x, k, NULL, NULL, kv_rows, n_cols);
+    mo_matvec_q4k(wv, x, v, NULL, NULL, kv_rows, n_cols);
+}
+
+void mo_matvec_q4k_dual(const uint8_t *wa, const uint8_t *wb, const float *x, float *ya, float *yb,
+                        int n_rows, int n_cols)
+{
+    mo_matvec_q4k(wa, x, ya, NULL, NULL, n_rows, n_cols);
+    mo_matvec_q4k(wb, x, yb, NULL, NULL, n_rows, n_cols);
+}
+
+void mo_matvec_q4k_scaled_add(const uint8_t *w, const float *x, float *y, int n_rows, int n_cols,
+                              float scale)
+{
+    size_t rb = (size_t)bpr_of(n_cols) * MO_Q4K_BLOCK_BYTES;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < n_rows; r++) {
+        float s;
+        double s64, a;
+        row_dot_q4k(w + (size_t)r * rb, x, n_cols, &s, &s64, &a);
+        y[r] += scale * s; /* kernels.cu:413 */
+    }
+}
+
+void mo_matvec_q6k(const uint8_t *w, const float *x, float *y, double *y64, double *abs_dot,
+                   int n_rows, int n_cols)
+{
+    size_t rb = (size_t)bpr_of(n_cols) * MO_Q6K_BLOCK_BYTES;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < n_rows; r++) {
+        float s;
+        double s64, a;
+        row_dot_q6k(w + (size_t)r * rb, x, n_cols, &s, &s64, &a);
+        y[r] = s;
+        if (y64) y64[r] = s64;
+        if (abs_dot) abs_dot[r] = a;
+    }
+}
+
+/* kernels.cu:859-880: lane l accumulates columns l, l+32, ... with a fused
+ * multiply-add (nvcc's default contraction), then the shfl_down tree
+ * (offsets 16,8,4,2,1; an out-of-range source returns the lane's own value). */
+void mo_matvec_f32(const float *w, const float *x, float *y, int n_rows, int n_cols)
+{
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < n_rows; r++) {
+        const float *row = w + (size_t)r * n_cols;
+        float p[32], t[32];
+        for (int l = 0; l < 32; l++) {
+            float s = 0.0f;
+            for (int c = l; c < n_cols; c += 32) s = fmaf(row[c], x[c], s);
+            p[l] = s;
+        }
+        for (int off = 16; off > 0; off >>= 1) {
+            for (int l = 0; l < 32; l++) t[l] = p[l] + (l + off < 32 ? p[l + off] : p[l]);
+            memcpy(p, t, sizeof p);
+        }
+        y[r] = p[0];
+    }
+}
+
+void mo_matvec_f32_f64(const float *w, const float *x, double *y, int n_rows, int n_cols)
+{
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < n_rows; r++) {
+        const float *row = w + (size_t)r * n_cols;
+        double s = 0.0;
+        for (int c = 0; c < n_cols; c++) s += (double)row[c] * (double)x[c];
+        y[r] = s;
+    }
+}
+
+/* ------------------------------------------------------------------------ */
+/* elementwise                                                               */
+/* ------------------------------------------------------------------------ */
+
+/* kernels.cu:677-688 */
+void mo_swiglu(const float *gate, const float *up, float *out, int n)
+{
+    for (int i = 0; i < n; i++) {
+        float g = gate[i];
+        float silu = g / (1.0f + expf(-g));
+        out[i] = silu * up[i];
+    }
+}
+
+/* kernels.cu:980-988 */
+void mo_scaled_add(float *out, const float *x, float scale, int n)
+{
+    for (int i = 0; i < n; i++) out[i] += scale * x[i];
+}
+
+/* ------------------------------------------------------------------------ */
+/* router select                                                             */
+/* ------------------------------------------------------------------------ */
+
+/* kernels.cu:993-1057. 32 lanes each keep a local top-k of their strided
+ * slice with "replace the first minimum if strictly greater"; the 32x16
+ * candidate table is then scanned in (lane, slot) order by the same rule;
+ * weights = softmax over the k kept logits, emitted in slot order. */
+void mo_topk_softmax(const float *scores, int *indices, float *weights, int n_experts, int k)
+{
+    float s_vals[32 * 16];
+    int s_ids[32 * 16];
+    for (int tid = 0; tid < 32; tid++) {
+        float v[16];
+        int id[16];
+        for (int i = 0; i < k; i++) {
+            v[i] = -1e30f;
+            id[i] = -1;
+        }
+        for (int j = tid; j < n_experts; j += 32) {
+            float val = scores[j];
+            int mi = 0;
+            for (int i = 1; i < k; i++)
+                if (v[i] < v[mi]) mi = i;
+            if (val > v[mi]) {
+                v[mi] = val;
+                id[mi] = j;
+            }
+        }
+        for (int i = 0; i < 16; i++) {
+            s_vals[tid * 16 + i] = i < k ? v[i] : -1e30f;
+            s_ids[tid * 16 + i] = i < k ? id[i] : -1;
+        }
+    }
+    float tv[16];
+    int ti[16];
+    for (int i = 0; i < k; i++) {
+        tv[i] = -1e30f;
+        ti[i] = -1;
+    }
+    for (int j = 0; j < 32 * 16; j++) {
+        float val = s_vals[j];
+        if (val <= -1e30f) continue;
+        int mi = 0;
+        for (int i = 1; i < k; i++)
+            if (tv[i] < tv[mi]) mi = i;
+        if (val > tv[mi]) {
+            tv[mi] = val;
+            ti[mi] = s_ids[j];
+        }
+    }
+    float mx = tv[0];
+    for (int i = 1; i < k; i++)
+        if (tv[i] > mx) mx = tv[i];
+    float sum = 0.0f;
+    for (int i = 0; i < k; i++) {
+        tv[i] = expf(tv[i] - mx);
+        sum += tv[i];
+    }
+    for (int i = 0; i < k; i++) {
+        weights[i] = tv[i] / sum;
+        indices[i] = ti[i];
+    }
+}
+
+/* ------------------------------------------------------------------------ */
+/* expert / MoE block                                                        */
+/* ------------------------------------------------------------------------ */
+
+/* forward.c:1122-1142 */
+void mo_expert_fwd(const uint8_t *expert, size_t gate_sz, size_t up_sz, int H, int EFF,
+                   int down_type, float weight, const float *x, float *moe_out)
+{
+    float *g = (float *)malloc(sizeof(float) * (size_t)EFF * 3);
+    float *u = g + EFF, *act = u + EFF;
+    mo_matvec_q4k_dual(expert, expert + gate_sz, x, g, u, EFF, H);
+    mo_swiglu(g, u, act, EFF);
+    const uint8_t *down = expert + gate_sz + up_sz;
+    if (down_type == 12) {
+        mo_matvec_q4k_scaled_add(down, act, moe_out, H, EFF, weight);
+    } else {
+        float *o = (float *)malloc(sizeof(float) * (size_t)H);
+        mo_matvec_q6k(down, act, o, NULL, NULL, H, EFF);
+        mo_scaled_add(moe_out, o, weight, H);
+        free(o);
+    }
+    free(g);
+}
+
+/* forward.c:818-823 (router + select), :875 (zero), expert loop, :1114 (residual add) */
+void mo_moe_block(const float *router_w, const uint8_t *experts, size_t expert_stride,
+                  size_t gate_sz, size_t up_sz, int down_type, int NE, int K, int H, int EFF,
+                  const float *x, const float *residual, float *out, int *indices, float *weights)
+{
+    float *logits = (float *)malloc(sizeof(float) * (size_t)NE);
+    float *moe = (float *)calloc((size_t)H, sizeof(float));
+    mo_matvec_f32(router_w, x, logits, NE, H);
+    mo_topk_softmax(logits, indices, weights, NE, K);
+    for (int i = 0; i < K; i++) {
+        if (indices[i] < 0) continue;
+        mo_expert_fwd(experts + (size_t)indices[i] * expert_stride, gate_sz, up_sz, H, EFF,
+                      down_type, weights[i], x, moe);
+    }
+    for (int i = 0; i < H; i++) out[i] = moe[i] + residual[i];
+    free(logits);
+    free(moe);
+}
+
+/* ------------------------------------------------------------------------ */
+/* GEMM oracle                                                               */
+/* ------------------------------------------------------------------------ */
+
+static void gemm_f16(const uint8_t *w, int q6, const uint16_t *x_f16, float *out, int M, int N,
+                     int K)
+{
+    int bpr = bpr_of(K);
+    size_t rb = (size_t)bpr * (q6 ? MO_Q6K_BLOCK_BYTES : MO_Q4K_BLOCK_BYTES);
+    float *xf = (float *)malloc(sizeof(float) * (size_t)M * K);
+    for (size_t i = 0; i < (size_t)M * K; i++) xf[i] = mo_f16_to_f32(x_f16[i]);
+#pragma omp parallel
+    {
+        float *wrow = (float *)malloc(sizeof(float) * (size_t)bpr * 256);
+#pragma omp for schedule(static)
+        for (int n = 0; n < N; n++) {
+            for (int b = 0; b < bpr; b++) {
+                const uint8_t *blk = w + (size_t)n * rb + (size_t)b * (q6 ? 210 : 144);
+                if (q6)
+                    dequant_q6k_block(blk, wrow + b * 256);
+                else
+                    dequant_q4k_block(blk, wrow + b * 256);
+            }
+            for (int t = 0; t < M; t++) {
+                const float *xr = xf + (size_t)t * K;
+                double s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+                int c = 0;
+                for (; c + 3 < K; c += 4) {
+                    s0 += (double)wrow[c] * xr[c];
+                    s1 += (double)wrow[c + 1] * xr[c + 1];
+                    s2 += (double)wrow[c + 2] * xr[c + 2];
+                    s3 += (double)wrow[c + 3] * xr[c + 3];
+                }
+                for (; c < K; c++) s0 += (double)wrow[c] * xr[c];
+                out[(size_t)t * N + n] = (float)((s0 + s1) + (s2 + s3));
+            }
+        }
+        free(wrow);
+    }
+    free(xf);
+}
+
+void mo_gemm_q4k_f16(const uint8_t *w, const uint16_t *x_f16, float *out, int M, int N, int K)
+{
+    gemm_f16(w, 0, x_f16, out, M, N, K);
+}
+
+void mo_gemm_q6k_f16(const uint8_t *w, const uint16_t *x_f16, float *out, int M, int N, int K)
+{
+    gemm_f16(w, 1, x_f16, out, M, N, K);
+}
+
+int mo_num_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+void mo_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
