@@ -1,0 +1,122 @@
+/*
+ * mnemo_b200.h -- C ABI of libmnemo_b200.so: sm_100a kernels for the quantized
+ * weight hot path of MnemoCUDA (GGUF Q4_K / Q6_K dequant-matvec for decode, the
+ * Q4_K tensor-core GEMM for prefill, and its grouped per-expert form).
+ *
+ * Part 1 exports the reference's own kernel entry points under their own
+ * names and signatures, so the reference's forward.c / engine.c link against
+ * this library unchanged. The reference has no header for them: forward.c
+ * re-declares each one by hand (src/forward.c:24-152); the definitions being
+ * replaced are cited per function (paths relative to the reference project).
+ *
+ * Conventions (same as the reference): every pointer is a device pointer owned
+ * by the caller; the library allocates nothing in these calls and keeps no
+ * pointer beyond the call; the caller selects the device; any stream may be
+ * passed, including one that is being captured into a CUDA graph; Part-1
+ * functions return void and report launch errors on stderr. Weights are raw
+ * GGUF blocks, row-major, ceil(n_cols/256) blocks per row, rows contiguous.
+ * Q4_K tensors must start on a 16-byte boundary (the reference aligns resident
+ * tensors to 256 B, src/engine.c:874, and expert parts to multiples of 144 B);
+ * Q6_K tensors need 2-byte alignment only.
+ *
+ * Part 2 (mb200_*) are additions that return a status code.
+ */
+#ifndef MNEMO_B200_H
+#define MNEMO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifndef __CUDA_RUNTIME_API_H__
+#ifndef __DRIVER_TYPES_H__
+typedef struct CUstream_st *cudaStream_t;
+#endif
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ===================== Part 1: the reference's kernel ABI ===================== */
+
+/* One-time setup (shared-memory opt-in, status word). Replaces src/kernels.cu:2217-2240;
+ * called by the engine at load (src/engine.c:1203-1207). Safe to call more than once. */
+void cuda_kernels_init(void);
+
+/* y = W x, W Q4_K [n_rows x n_cols]. Replaces src/kernels.cu:1071-1079 (kernel :66-145). */
+void cuda_matvec_q4k(const void *weights, const float *x, float *y, int n_rows, int n_cols,
+                     cudaStream_t stream);
+
+/* y = W x + residual. Replaces src/kernels.cu:1094-1102 (kernel :149-199). */
+void cuda_matvec_q4k_add(const void *weights, const float *x, const float *residual, float *y,
+                         int n_rows, int n_cols, cudaStream_t stream);
+
+/* q,k,v = Wq x, Wk x, Wv x in one launch. Replaces src/kernels.cu:1081-1092 (kernel :205-274). */
+void cuda_matvec_q4k_qkv(const void *w_q, const void *w_k, const void *w_v, const float *x,
+                         float *out_q, float *out_k, float *out_v, int q_rows, int kv_rows,
+                         int n_cols, cudaStream_t stream);
+
+/* ya = A x, yb = B x (same shape, shared x). Replaces src/kernels.cu:1104-1113 (kernel :278-354). */
+void cuda_matvec_q4k_dual(const void *wa, const void *wb, const float *x, float *ya, float *yb,
+                          int n_rows, int n_cols, cudaStream_t stream);
+
+/* y += scale * (W x). Replaces src/kernels.cu:1115-1124 (kernel :358-415). */
+void cuda_matvec_q4k_scaled_add(const void *weights, const float *x, float *y, int n_rows,
+                                int n_cols, float scale, cudaStream_t stream);
+
+/* y = W x, W Q6_K. Replaces src/kernels.cu:1126-1135 (kernel :427-491). */
+void cuda_matvec_q6k(const void *weights, const float *x, float *y, int n_rows, int n_cols,
+                     cudaStream_t stream);
+
+/* y = W x, W fp32 row-major (the router). Replaces src/kernels.cu:1275-1281 (kernel :859-880). */
+void cuda_matvec_f32(const float *weights, const float *x, float *y, int n_rows, int n_cols,
+                     cudaStream_t stream);
+
+/* top-k of n_experts scores + softmax over the k kept scores; k <= 16. Output
+ * slot order is the reference's. Replaces src/kernels.cu:1301-1305 (kernel :993-1057). */
+void cuda_topk_softmax(const float *scores, int *indices, float *weights, int n_experts, int k,
+                       cudaStream_t stream);
+
+/* out = silu(gate) * up. Replaces src/kernels.cu:1170-1176 (kernel :677-688). */
+void cuda_swiglu(const float *gate, const float *up, float *out, int n, cudaStream_t stream);
+
+/* out += scale * x. Replaces src/kernels.cu:1293-1299 (kernel :980-988). */
+void cuda_scaled_add(float *out, const float *x, float scale, int n, cudaStream_t stream);
+
+/* ===================== Part 2: additions (status-returning) ===================== */
+
+enum {
+    MB200_OK = 0,
+    MB200_ERR_ARG = 1,       /* bad size / alignment / null pointer: nothing was launched */
+    MB200_ERR_LAUNCH = 2,    /* the CUDA runtime refused a launch */
+    MB200_ERR_TIMEOUT = 3,   /* a kernel gave up on a bounded wait (see mb200_device_error) */
+    MB200_ERR_UNSUPPORTED = 4
+};
+
+int mb200_init(void);
+/* First failure recorded since the last call to mb200_clear_status (0 = none). */
+int mb200_last_status(void);
+const char *mb200_last_status_where(void);
+void mb200_clear_status(void);
+/* Synchronises the device and returns the device-side error word (0 = no kernel gave up on a wait). */
+int mb200_device_error(void);
+
+/* act = silu(Wg x) * (Wu x): the expert gate+up pair with SwiGLU in the epilogue
+ * (reference sequence src/forward.c:1128-1131: matvec_q4k_dual then swiglu). */
+int mb200_matvec_q4k_dual_swiglu(const void *w_gate, const void *w_up, const float *x, float *act,
+                                 int n_rows, int n_cols, cudaStream_t stream);
+
+/* y += scale * (W x), W Q6_K (reference sequence src/forward.c:1137-1140: matvec_q6k then scaled_add). */
+int mb200_matvec_q6k_scaled_add(const void *weights, const float *x, float *y, int n_rows,
+                                int n_cols, float scale, cudaStream_t stream);
+
+/* Seeded synthetic tensors written on the device (benchmark workloads). */
+int mb200_fill_q4k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream);
+int mb200_fill_q6k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream);
+int mb200_fill_normal_f32(float *dst, size_t n, uint64_t seed, float scale, cudaStream_t stream);
+int mb200_fill_normal_f16(void *dst, size_t n, uint64_t seed, float scale, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MNEMO_B200_H */

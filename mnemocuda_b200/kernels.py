@@ -1,0 +1,151 @@
+"""Host-side mirror of the reference's kernel ABI (src/forward.c:24-152) over torch tensors.
+
+Same names, argument order and meaning as the `extern "C"` functions; tensors
+stand in for the raw device pointers, and `stream` defaults to torch's current
+stream. torch only supplies device memory and streams here: every function
+goes straight into libmnemo_b200.so.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+MB200_OK = 0
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("device tensor expected (the kernels take device pointers)")
+    if not t.is_contiguous():
+        raise ValueError("contiguous tensor expected")
+    return t.data_ptr()
+
+
+def _f32(t: torch.Tensor) -> int:
+    if t.dtype != torch.float32:
+        raise TypeError(f"float32 expected, got {t.dtype}")
+    return _ptr(t)
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, torch.cuda.Stream):
+        return stream.cuda_stream
+    return int(stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code != MB200_OK:
+        where = _lib.lib().mb200_last_status_where()
+        raise RuntimeError(f"{what} failed with status {code} ({where.decode() if where else ''})")
+
+
+def _raise_if_failed(what: str) -> None:
+    code = _lib.lib().mb200_last_status()
+    if code != MB200_OK:
+        where = _lib.lib().mb200_last_status_where()
+        _lib.lib().mb200_clear_status()
+        raise RuntimeError(f"{what} failed with status {code} ({where.decode() if where else ''})")
+
+
+def cuda_kernels_init() -> None:
+    _lib.lib().cuda_kernels_init()
+    _raise_if_failed("cuda_kernels_init")
+
+
+def cuda_matvec_q4k(weights, x, y, n_rows, n_cols, stream=None):
+    _lib.lib().cuda_matvec_q4k(_ptr(weights), _f32(x), _f32(y), n_rows, n_cols, _stream(stream))
+    _raise_if_failed("cuda_matvec_q4k")
+
+
+def cuda_matvec_q4k_add(weights, x, residual, y, n_rows, n_cols, stream=None):
+    _lib.lib().cuda_matvec_q4k_add(_ptr(weights), _f32(x), _f32(residual), _f32(y), n_rows, n_cols,
+                                   _stream(stream))
+    _raise_if_failed("cuda_matvec_q4k_add")
+
+
+def cuda_matvec_q4k_qkv(w_q, w_k, w_v, x, out_q, out_k, out_v, q_rows, kv_rows, n_cols, stream=None):
+    _lib.lib().cuda_matvec_q4k_qkv(_ptr(w_q), _ptr(w_k), _ptr(w_v), _f32(x), _f32(out_q), _f32(out_k),
+                                   _f32(out_v), q_rows, kv_rows, n_cols, _stream(stream))
+    _raise_if_failed("cuda_matvec_q4k_qkv")
+
+
+def cuda_matvec_q4k_dual(wa, wb, x, ya, yb, n_rows, n_cols, stream=None):
+    _lib.lib().cuda_matvec_q4k_dual(_ptr(wa), _ptr(wb), _f32(x), _f32(ya), _f32(yb), n_rows, n_cols,
+                                    _stream(stream))
+    _raise_if_failed("cuda_matvec_q4k_dual")
+
+
+def cuda_matvec_q4k_scaled_add(weights, x, y, n_rows, n_cols, scale, stream=None):
+    _lib.lib().cuda_matvec_q4k_scaled_add(_ptr(weights), _f32(x), _f32(y), n_rows, n_cols, float(scale),
+                                          _stream(stream))
+    _raise_if_failed("cuda_matvec_q4k_scaled_add")
+
+
+def cuda_matvec_q6k(weights, x, y, n_rows, n_cols, stream=None):
+    _lib.lib().cuda_matvec_q6k(_ptr(weights), _f32(x), _f32(y), n_rows, n_cols, _stream(stream))
+    _raise_if_failed("cuda_matvec_q6k")
+
+
+def cuda_matvec_f32(weights, x, y, n_rows, n_cols, stream=None):
+    _lib.lib().cuda_matvec_f32(_f32(weights), _f32(x), _f32(y), n_rows, n_cols, _stream(stream))
+    _raise_if_failed("cuda_matvec_f32")
+
+
+def cuda_topk_softmax(scores, indices, weights, n_experts, k, stream=None):
+    if indices.dtype != torch.int32:
+        raise TypeError("indices must be int32")
+    _lib.lib().cuda_topk_softmax(_f32(scores), _ptr(indices), _f32(weights), n_experts, k, _stream(stream))
+    _raise_if_failed("cuda_topk_softmax")
+
+
+def cuda_swiglu(gate, up, out, n, stream=None):
+    _lib.lib().cuda_swiglu(_f32(gate), _f32(up), _f32(out), n, _stream(stream))
+    _raise_if_failed("cuda_swiglu")
+
+
+def cuda_scaled_add(out, x, scale, n, stream=None):
+    _lib.lib().cuda_scaled_add(_f32(out), _f32(x), float(scale), n, _stream(stream))
+    _raise_if_failed("cuda_scaled_add")
+
+
+# ---- additions --------------------------------------------------------------
+
+def mb200_init() -> None:
+    _check(_lib.lib().mb200_init(), "mb200_init")
+
+
+def mb200_device_error() -> int:
+    return _lib.lib().mb200_device_error()
+
+
+def mb200_matvec_q4k_dual_swiglu(w_gate, w_up, x, act, n_rows, n_cols, stream=None):
+    _check(_lib.lib().mb200_matvec_q4k_dual_swiglu(_ptr(w_gate), _ptr(w_up), _f32(x), _f32(act), n_rows,
+                                                   n_cols, _stream(stream)), "mb200_matvec_q4k_dual_swiglu")
+
+
+def mb200_matvec_q6k_scaled_add(weights, x, y, n_rows, n_cols, scale, stream=None):
+    _check(_lib.lib().mb200_matvec_q6k_scaled_add(_ptr(weights), _f32(x), _f32(y), n_rows, n_cols,
+                                                  float(scale), _stream(stream)), "mb200_matvec_q6k_scaled_add")
+
+
+def mb200_fill_q4k(dst, n_blocks, seed, stream=None):
+    _check(_lib.lib().mb200_fill_q4k(_ptr(dst), n_blocks, seed, _stream(stream)), "mb200_fill_q4k")
+
+
+def mb200_fill_q6k(dst, n_blocks, seed, stream=None):
+    _check(_lib.lib().mb200_fill_q6k(_ptr(dst), n_blocks, seed, _stream(stream)), "mb200_fill_q6k")
+
+
+def mb200_fill_normal_f32(dst, n, seed, scale=1.0, stream=None):
+    _check(_lib.lib().mb200_fill_normal_f32(_f32(dst), n, seed, float(scale), _stream(stream)),
+           "mb200_fill_normal_f32")
+
+
+def mb200_fill_normal_f16(dst, n, seed, scale=1.0, stream=None):
+    _check(_lib.lib().mb200_fill_normal_f16(_ptr(dst), n, seed, float(scale), _stream(stream)),
+           "mb200_fill_normal_f16")

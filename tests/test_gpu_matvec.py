@@ -1,0 +1,208 @@
+"""GPU parity: every matvec entry point of the C ABI against the CPU oracle on
+seeded synthetic blocks (tolerance: 1e-3 relative L2, fp64-accumulated oracle)."""
+import numpy as np
+import pytest
+import torch
+
+from mnemocuda_b200 import synth
+from oracle import oracle
+from tests.gpu_util import assert_close_matvec, dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from mnemocuda_b200 import kernels
+    kernels.mb200_init()
+    yield kernels
+    torch.cuda.synchronize()
+    assert kernels.mb200_device_error() == 0
+
+
+Q4_SHAPES = [
+    (8192, 4096),   # Q projection, 235B shape (benchmark config 1)
+    (4096, 8192),   # O projection
+    (1536, 4096),   # expert gate / up
+    (4096, 1536),   # expert down when stored as Q4_K (6 blocks per row)
+    (4096, 2048),   # 30B-shape Q projection
+    (1, 256), (3, 256), (64, 256), (5, 300), (33, 1000), (7, 2048), (130, 768), (3, 16384),
+    (149, 1280), (1000, 512),
+]
+
+
+@pytest.mark.parametrize("rows,cols", Q4_SHAPES)
+def test_matvec_q4k(K, rows, cols):
+    w = synth.q4k_matrix(1000 + rows + cols, rows, cols)
+    x = synth.normal_f32(2000 + cols, cols)
+    y_ref, y64, ad = oracle.matvec_q4k(w, x, rows, cols, full=True)
+    y = torch.full((rows,), float("nan"), device="cuda")
+    K.cuda_matvec_q4k(dev(w), dev(x), y, rows, cols)
+    assert_close_matvec(host(y), y64, ad, f"q4k {rows}x{cols}")
+
+
+def test_matvec_q4k_outlier_activations(K):
+    """Groups with one huge activation: the two-level split must still hold the tolerance."""
+    rows, cols = 256, 4096
+    w = synth.q4k_matrix(31, rows, cols)
+    x = synth.normal_f32(32, cols)
+    x[::97] *= 1000.0
+    x[5] = 0.0
+    x[1024:1056] = 0.0  # an all-zero group
+    _, y64, ad = oracle.matvec_q4k(w, x, rows, cols, full=True)
+    y = torch.empty(rows, device="cuda")
+    K.cuda_matvec_q4k(dev(w), dev(x), y, rows, cols)
+    assert_close_matvec(host(y), y64, ad, "q4k outliers")
+
+
+def test_matvec_q4k_known_blocks(K, golden):
+    """Hand-built blocks (subnormal / negative d, extreme scales) as a 1-block-per-row matrix."""
+    w = golden["q4k_known_w"][[0, 2, 3, 4, 5, 6]]  # block 1 holds NaN-free but 0xFF data too; keep finite ones
+    rows = w.shape[0]
+    x = synth.normal_f32(33, 256)
+    _, y64, ad = oracle.matvec_q4k(w.reshape(-1), x, rows, 256, full=True)
+    y = torch.empty(rows, device="cuda")
+    K.cuda_matvec_q4k(dev(w.reshape(-1)), dev(x), y, rows, 256)
+    assert_close_matvec(host(y), y64, ad, "q4k known blocks")
+
+
+def test_matvec_q4k_add(K):
+    rows, cols = 4096, 8192
+    w = synth.q4k_matrix(41, rows, cols)
+    x = synth.normal_f32(42, cols)
+    res = synth.normal_f32(43, rows, 50.0)
+    _, y64, ad = oracle.matvec_q4k(w, x, rows, cols, full=True)
+    y = torch.empty(rows, device="cuda")
+    K.cuda_matvec_q4k_add(dev(w), dev(x), dev(res), y, rows, cols)
+    assert_close_matvec(host(y), y64 + res, ad + np.abs(res), "q4k_add")
+    np.testing.assert_allclose(host(y), oracle.matvec_q4k_add(w, x, res, rows, cols), rtol=0, atol=1e-3 * np.abs(y64).max())
+
+
+@pytest.mark.parametrize("q_rows,kv_rows,cols", [(8192, 512, 4096), (64, 8, 512), (10, 3, 300), (4096, 512, 2048)])
+def test_matvec_q4k_qkv(K, q_rows, kv_rows, cols):
+    wq = synth.q4k_matrix(51, q_rows, cols)
+    wk = synth.q4k_matrix(52, kv_rows, cols)
+    wv = synth.q4k_matrix(53, kv_rows, cols)
+    x = synth.normal_f32(54, cols)
+    q, k, v = (torch.empty(n, device="cuda") for n in (q_rows, kv_rows, kv_rows))
+    K.cuda_matvec_q4k_qkv(dev(wq), dev(wk), dev(wv), dev(x), q, k, v, q_rows, kv_rows, cols)
+    for got, w, n, name in ((q, wq, q_rows, "q"), (k, wk, kv_rows, "k"), (v, wv, kv_rows, "v")):
+        _, y64, ad = oracle.matvec_q4k(w, x, n, cols, full=True)
+        assert_close_matvec(host(got), y64, ad, f"qkv.{name}")
+
+
+@pytest.mark.parametrize("rows,cols", [(1536, 4096), (768, 2048), (9, 300)])
+def test_matvec_q4k_dual(K, rows, cols):
+    wa = synth.q4k_matrix(61, rows, cols)
+    wb = synth.q4k_matrix(62, rows, cols)
+    x = synth.normal_f32(63, cols)
+    ya, yb = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    K.cuda_matvec_q4k_dual(dev(wa), dev(wb), dev(x), ya, yb, rows, cols)
+    for got, w in ((ya, wa), (yb, wb)):
+        _, y64, ad = oracle.matvec_q4k(w, x, rows, cols, full=True)
+        assert_close_matvec(host(got), y64, ad, "dual")
+
+
+def test_matvec_q4k_scaled_add_accumulates(K):
+    rows, cols = 4096, 1536
+    w = synth.q4k_matrix(71, rows, cols)
+    x = synth.normal_f32(72, cols)
+    y0 = synth.normal_f32(73, rows, 10.0)
+    _, y64, ad = oracle.matvec_q4k(w, x, rows, cols, full=True)
+    y = dev(y0.copy())
+    K.cuda_matvec_q4k_scaled_add(dev(w), dev(x), y, rows, cols, 0.37)
+    K.cuda_matvec_q4k_scaled_add(dev(w), dev(x), y, rows, cols, -1.5)
+    want = y0.astype(np.float64) + (0.37 - 1.5) * y64
+    assert_close_matvec(host(y), want, 1.87 * ad + np.abs(y0), "q4k_scaled_add x2")
+
+
+@pytest.mark.parametrize("rows,cols", [(1536, 4096), (768, 2048), (9, 300), (1, 256)])
+def test_dual_swiglu(K, rows, cols):
+    wg = synth.q4k_matrix(81, rows, cols)
+    wu = synth.q4k_matrix(82, rows, cols)
+    x = synth.normal_f32(83, cols)
+    g, u = oracle.matvec_q4k_dual(wg, wu, x, rows, cols)
+    _, g64, gad = oracle.matvec_q4k(wg, x, rows, cols, full=True)
+    _, u64, uad = oracle.matvec_q4k(wu, x, rows, cols, full=True)
+    want = g64 / (1.0 + np.exp(-g64)) * u64
+    act = torch.empty(rows, device="cuda")
+    K.mb200_matvec_q4k_dual_swiglu(dev(wg), dev(wu), dev(x), act, rows, cols)
+    # error scale of a product: |silu(g)| * err(u) + |u| * err(g)
+    scale = np.abs(g64 / (1 + np.exp(-g64))) * uad + np.abs(u64) * 1.1 * gad
+    assert_close_matvec(host(act), want, scale, "dual_swiglu")
+    np.testing.assert_allclose(host(act), oracle.swiglu(g, u), rtol=2e-3, atol=1e-3 * np.abs(want).max())
+
+
+Q6_SHAPES = [
+    (4096, 1536),   # expert down (benchmark config 2)
+    (512, 4096),    # V projection
+    (2048, 768),    # 30B expert down: 3 blocks per row, rows only 2-byte aligned
+    (1000, 2048),
+    (1, 256), (5, 256), (17, 300), (33, 1000), (7, 1280), (3, 16384), (149, 512),
+]
+
+
+@pytest.mark.parametrize("rows,cols", Q6_SHAPES)
+def test_matvec_q6k(K, rows, cols):
+    w = synth.q6k_matrix(3000 + rows + cols, rows, cols)
+    x = synth.normal_f32(4000 + cols, cols)
+    _, y64, ad = oracle.matvec_q6k(w, x, rows, cols, full=True)
+    y = torch.full((rows,), float("nan"), device="cuda")
+    K.cuda_matvec_q6k(dev(w), dev(x), y, rows, cols)
+    assert_close_matvec(host(y), y64, ad, f"q6k {rows}x{cols}")
+
+
+@pytest.mark.parametrize("offset", [2, 6, 14, 210])
+def test_matvec_q6k_unaligned_base(K, offset):
+    """Q6_K tensors only promise 2-byte alignment (expert blobs place them after two Q4_K parts)."""
+    rows, cols = 96, 1536
+    w = synth.q6k_matrix(91, rows, cols)
+    x = synth.normal_f32(92, cols)
+    _, y64, ad = oracle.matvec_q6k(w, x, rows, cols, full=True)
+    buf = torch.zeros(w.size + 512, dtype=torch.uint8, device="cuda")
+    buf[offset:offset + w.size] = dev(w)
+    y = torch.empty(rows, device="cuda")
+    K.cuda_matvec_q6k(buf[offset:], dev(x), y, rows, cols)
+    assert_close_matvec(host(y), y64, ad, f"q6k base+{offset}")
+
+
+def test_matvec_q6k_known_blocks(K, golden):
+    w = golden["q6k_known_w"]
+    rows = w.shape[0]
+    x = synth.normal_f32(93, 256)
+    _, y64, ad = oracle.matvec_q6k(w.reshape(-1), x, rows, 256, full=True)
+    y = torch.empty(rows, device="cuda")
+    K.cuda_matvec_q6k(dev(w.reshape(-1)), dev(x), y, rows, 256)
+    assert_close_matvec(host(y), y64, ad, "q6k known blocks")
+
+
+def test_matvec_q6k_scaled_add(K):
+    rows, cols = 4096, 1536
+    w = synth.q6k_matrix(94, rows, cols)
+    x = synth.normal_f32(95, cols)
+    y0 = synth.normal_f32(96, rows)
+    _, y64, ad = oracle.matvec_q6k(w, x, rows, cols, full=True)
+    y = dev(y0.copy())
+    K.mb200_matvec_q6k_scaled_add(dev(w), dev(x), y, rows, cols, 0.25)
+    K.mb200_matvec_q6k_scaled_add(dev(w), dev(x), y, rows, cols, 0.5)
+    assert_close_matvec(host(y), y0 + 0.75 * y64, 0.75 * ad + np.abs(y0), "q6k_scaled_add x2")
+
+
+def test_repeat_calls_are_bitwise_stable(K):
+    """Fixed tile schedule and ordered partial sums: the same call gives the same bits."""
+    rows, cols = 8192, 4096
+    w, x = dev(synth.q4k_matrix(97, rows, cols)), dev(synth.normal_f32(98, cols))
+    a, b = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    K.cuda_matvec_q4k(w, x, a, rows, cols)
+    K.cuda_matvec_q4k(w, x, b, rows, cols)
+    assert torch.equal(a, b)
+
+
+def test_bad_alignment_is_reported_not_run(K):
+    rows, cols = 4, 256
+    buf = torch.zeros(rows * 144 + 64, dtype=torch.uint8, device="cuda")
+    y = torch.zeros(rows, device="cuda")
+    with pytest.raises(RuntimeError):
+        K.cuda_matvec_q4k(buf[4:], torch.zeros(cols, device="cuda"), y, rows, cols)
+    with pytest.raises(RuntimeError):
+        K.cuda_matvec_q4k(buf, torch.zeros(20000, device="cuda"), y, rows, 20000)
