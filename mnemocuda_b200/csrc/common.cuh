@@ -100,7 +100,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 }
 // Returns false if the phase did not complete within the iteration budget
 // (each try_wait already blocks for a hardware time slice).
-constexpr uint32_t kWaitBudget = 1u << 22;
+constexpr uint32_t kWaitBudget = 1u << 20;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
 {
     for (uint32_t i = 0; i < kWaitBudget; i++)

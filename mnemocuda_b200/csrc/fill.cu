@@ -26,12 +26,6 @@ __device__ inline float normal_from(uint64_t w)
     return sqrtf(-2.0f * logf(fminf(u1, 1.0f))) * cospif(2.0f * u2);
 }
 
-__device__ inline void put_u16(uint8_t *p, uint16_t v)
-{
-    p[0] = static_cast<uint8_t>(v);
-    p[1] = static_cast<uint8_t>(v >> 8);
-}
-
 // one thread per 64-bit word; blocks are 18 (Q4_K) or 27 (Q6_K, last 6 bytes dropped) words
 __global__ void fill_q4k_kernel(uint8_t *dst, size_t n_blocks, uint64_t base, uint64_t nbase)
 {
@@ -59,17 +53,21 @@ __global__ void fill_q6k_kernel(uint8_t *dst, size_t n_blocks, uint64_t base, ui
         const uint64_t w = mix(base + i);
         const size_t blk = i / 27, j = i % 27;
         uint8_t *b = dst + blk * kQ6KBlock;
+        uint32_t d_bits = 0;
+        if (j == 26) {
+            const float d = fabsf(normal_from(mix(nbase + blk))) * 1e-3f;
+            d_bits = __half_as_ushort(__float2half_rn(d));
+        }
 #pragma unroll
         for (int k = 0; k < 8; k++) {
             const int off = static_cast<int>(j) * 8 + k;
+            if (off >= kQ6KBlock) continue;  // bytes 210..215 of the last word do not exist
             uint8_t v = static_cast<uint8_t>(w >> (8 * k));
-            if (off >= 208) continue;  // d is written below; bytes 210..215 do not exist
-            if (off >= 192) v = static_cast<uint8_t>(static_cast<int8_t>((v & 63) - 32));
+            if (off >= 208)
+                v = static_cast<uint8_t>(d_bits >> (8 * (off - 208)));
+            else if (off >= 192)
+                v = static_cast<uint8_t>(static_cast<int8_t>((v & 63) - 32));
             b[off] = v;
-        }
-        if (j == 26) {
-            const float d = fabsf(normal_from(mix(nbase + blk))) * 1e-3f;
-            put_u16(b + 208, __half_as_ushort(__float2half_rn(d)));
         }
     }
 }

@@ -1,0 +1,421 @@
+// Streaming dequant-matvec skeleton shared by the Q4_K and Q6_K kernels (batch 1).
+//
+// A weight matrix is a contiguous stream of super-blocks. It is cut into tiles
+// of whole rows; CTA c owns tiles c, c+grid, ... One producer warp moves each
+// tile into a ring of shared-memory stages with a 1-D bulk async copy (TMA
+// engine, completion on an mbarrier); kConsumers consumer warps wait on the
+// "full" barrier of a stage, compute their rows, publish partial sums in shared
+// memory and arrive on the stage's "empty" barrier; the producer warp then adds
+// the partials of each row in fixed order, applies the epilogue (store,
+// + residual, scaled accumulate, SwiGLU pairing) and refills the stage. There is
+// no block-wide barrier inside the loop, and every wait is bounded.
+//
+// Work split inside a tile: a warp pass covers G = 32 / lanes-per-block
+// super-blocks. The block-columns of a row are split into column groups of G;
+// each consumer warp is bound to one column group for the whole kernel, so its
+// share of the activation vector is loaded into registers once. A trailing
+// group with v < G columns (v dividing G) covers G / v rows per pass instead of
+// idling lanes. A unit is RU passes issued back to back (independent rows:
+// instruction-level parallelism), reduced together with one packed butterfly.
+#pragma once
+
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace mb200 {
+namespace stream {
+
+constexpr int kConsumers = 12;
+constexpr int kThreads = (kConsumers + 1) * 32;
+constexpr int kMaxStages = 6;
+
+enum : int { kStore = 0, kAddResidual = 1, kScaledAdd = 2, kSwiGLU = 3 };
+
+struct Seg {
+    const uint8_t *w;
+    float *y;
+    int rows;
+    int tile0;
+};
+
+struct Params {
+    Seg seg[3];
+    int nseg, n_tiles, tile_rows;  // SwiGLU: a tile holds tile_rows/2 gate rows then tile_rows/2 up rows
+    const float *x;
+    const float *residual;
+    float scale;
+    int n_cols, bpr, mode, stages;
+    int *err;
+};
+
+struct Layout {
+    int bars, xq1, xq2, xs1, xsum, part, stages, stage_bytes, total;
+};
+
+template <class F>
+__host__ __device__ inline Layout layout(int bpr, int tile_rows, int n_stages)
+{
+    Layout s;
+    const int kpad = bpr * 256;
+    const int ng = (bpr + F::kG - 1) / F::kG;
+    int o = 0;
+    s.bars = o;  o += 128;
+    s.xq1 = o;   o += kpad;
+    s.xq2 = o;   o += kpad;
+    s.xs1 = o;   o += (kpad / 32) * 4;
+    s.xsum = o;  o += (kpad / F::kSumCols) * 4;
+    s.part = o;  o += n_stages * tile_rows * ng * 4;
+    o = (o + 127) & ~127;
+    s.stages = o;
+    s.stage_bytes = (tile_rows * bpr * F::kBlockBytes + 32 + 127) & ~127;  // +32: alignment skew, word over-read
+    s.total = o + n_stages * s.stage_bytes;
+    return s;
+}
+
+// Static selects instead of P.seg[i]: dynamic indexing would push the parameter block to local memory.
+__device__ __forceinline__ const uint8_t *seg_w(const Params &P, int i)
+{
+    return i == 0 ? P.seg[0].w : (i == 1 ? P.seg[1].w : P.seg[2].w);
+}
+__device__ __forceinline__ float *seg_y(const Params &P, int i)
+{
+    return i == 0 ? P.seg[0].y : (i == 1 ? P.seg[1].y : P.seg[2].y);
+}
+__device__ __forceinline__ int seg_rows(const Params &P, int i)
+{
+    return i == 0 ? P.seg[0].rows : (i == 1 ? P.seg[1].rows : P.seg[2].rows);
+}
+__device__ __forceinline__ int seg_tile0(const Params &P, int i)
+{
+    return i == 0 ? P.seg[0].tile0 : (i == 1 ? P.seg[1].tile0 : P.seg[2].tile0);
+}
+
+struct Tile {
+    int seg, row0, rows;  // rows: per segment (SwiGLU tiles hold 2*rows rows)
+};
+
+__device__ __forceinline__ Tile tile_of(const Params &P, int tile)
+{
+    Tile t;
+    t.seg = 0;
+    if (P.nseg > 1 && tile >= P.seg[1].tile0) t.seg = 1;
+    if (P.nseg > 2 && tile >= P.seg[2].tile0) t.seg = 2;
+    const int per = (P.mode == kSwiGLU) ? (P.tile_rows >> 1) : P.tile_rows;
+    t.row0 = (tile - seg_tile0(P, t.seg)) * per;
+    t.rows = min(per, seg_rows(P, t.seg) - t.row0);
+    return t;
+}
+
+// The 16-byte-aligned span enclosing rows [row0, row0+rows) of a tensor and the
+// offset of the first row inside it. Reading the few bytes before/after the rows
+// stays inside the 16-byte granule of a valid byte, hence inside a mapped page.
+__device__ __forceinline__ void span_of(const uint8_t *w, size_t row_bytes, int row0, int rows,
+                                        const uint8_t *&src, uint32_t &bytes, uint32_t &skew)
+{
+    const uintptr_t begin = reinterpret_cast<uintptr_t>(w) + (size_t)row0 * row_bytes;
+    const uintptr_t end = begin + (size_t)rows * row_bytes;
+    const uintptr_t a0 = begin & ~static_cast<uintptr_t>(15);
+    const uintptr_t a1 = (end + 15) & ~static_cast<uintptr_t>(15);
+    src = reinterpret_cast<const uint8_t *>(a0);
+    bytes = static_cast<uint32_t>(a1 - a0);
+    skew = static_cast<uint32_t>(begin - a0);
+}
+
+template <class F>
+__device__ __forceinline__ void issue_tile(const Params &P, int tile, uint8_t *stage, uint64_t *bar)
+{
+    const Tile t = tile_of(P, tile);
+    const size_t row_bytes = (size_t)P.bpr * F::kBlockBytes;
+    const uint8_t *src;
+    uint32_t bytes, skew;
+    if (P.mode == kSwiGLU) {  // Q4_K only: spans are exact (rows are multiples of 16 bytes)
+        const uint32_t half = t.rows * (uint32_t)row_bytes;
+        mbar_expect_tx(bar, 2 * half);
+        bulk_g2s(stage, P.seg[0].w + (size_t)t.row0 * row_bytes, half, bar);
+        bulk_g2s(stage + half, P.seg[1].w + (size_t)t.row0 * row_bytes, half, bar);
+    } else {
+        span_of(seg_w(P, t.seg), row_bytes, t.row0, t.rows, src, bytes, skew);
+        mbar_expect_tx(bar, bytes);
+        bulk_g2s(stage, src, bytes, bar);
+    }
+}
+
+// Sum RU per-lane values over groups of W lanes (W = 32, 16 or 8), RU in {1,2,4}.
+// On return, lane l with (l & (W/RU - 1)) == 0 holds the sum for value index
+// `which` (= (l & (W-1)) / (W/RU)) of its W-lane group.
+template <int RU>
+__device__ __forceinline__ float packed_sum(float (&a)[RU], int W, int lane, int &which)
+{
+    int off = W >> 1;
+    float v;
+    if (RU == 4) {
+        const bool hi = (lane & off) != 0;
+        float k0 = hi ? a[2] : a[0], k1 = hi ? a[3] : a[1];
+        const float s0 = hi ? a[0] : a[2], s1 = hi ? a[1] : a[3];
+        k0 += __shfl_xor_sync(0xffffffffu, s0, off);
+        k1 += __shfl_xor_sync(0xffffffffu, s1, off);
+        which = hi ? 2 : 0;
+        off >>= 1;
+        const bool hi2 = (lane & off) != 0;
+        v = hi2 ? k1 : k0;
+        v += __shfl_xor_sync(0xffffffffu, hi2 ? k0 : k1, off);
+        which += hi2 ? 1 : 0;
+        off >>= 1;
+    } else if (RU == 2) {
+        const bool hi = (lane & off) != 0;
+        v = hi ? a[1] : a[0];
+        v += __shfl_xor_sync(0xffffffffu, hi ? a[0] : a[1], off);
+        which = hi ? 1 : 0;
+        off >>= 1;
+    } else {
+        v = a[0];
+        which = 0;
+    }
+    for (; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+template <class F, int RU>
+__global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int S = P.stages;
+    const Layout L = layout<F>(P.bpr, P.tile_rows, S);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.bars);
+    uint64_t *empty = full + kMaxStages;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.bars + 120);
+    float *part = reinterpret_cast<float *>(smem + L.part);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int my_tiles = (P.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    if (my_tiles <= 0) return;
+    const int NG = (P.bpr + F::kG - 1) / F::kG;
+    const uint32_t row_bytes = P.bpr * F::kBlockBytes;
+
+    if (tid == kConsumers * 32) {
+        *abort_flag = 0;
+        for (int s = 0; s < S; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kConsumers);
+        }
+        mbar_fence_init();
+        for (int k = 0; k < S && k < my_tiles; k++)
+            issue_tile<F>(P, blockIdx.x + k * gridDim.x, smem + L.stages + k * L.stage_bytes, &full[k]);
+    }
+    quantize_x<kThreads, F::kSumCols, F::kGroup4Tail>(
+        P.x, P.n_cols, P.bpr * 256, reinterpret_cast<int8_t *>(smem + L.xq1),
+        reinterpret_cast<int8_t *>(smem + L.xq2), reinterpret_cast<float *>(smem + L.xs1),
+        reinterpret_cast<float *>(smem + L.xsum));
+    __syncthreads();  // the only block-wide barrier: x is staged, barriers are initialised
+
+    if (warp == kConsumers) {
+        // ---------------- producer + epilogue warp ----------------
+        for (int k = 0; k < my_tiles + S; k++) {
+            const int s = k % S;
+            if (k >= S) {
+                const int kd = k - S;  // tile whose partials are complete once `empty` flips
+                if (!mbar_wait(&empty[s], (kd / S) & 1)) *abort_flag = 1;
+                if (*abort_flag) break;
+                const Tile t = tile_of(P, blockIdx.x + kd * gridDim.x);
+                const float *pt = part + s * P.tile_rows * NG;
+                for (int r = lane; r < t.rows; r += 32) {
+                    float v = 0.0f;
+                    for (int c = 0; c < NG; c++) v += pt[r * NG + c];
+                    const int row = t.row0 + r;
+                    if (P.mode == kStore) {
+                        seg_y(P, t.seg)[row] = v;
+                    } else if (P.mode == kAddResidual) {
+                        seg_y(P, t.seg)[row] = v + P.residual[row];
+                    } else if (P.mode == kScaledAdd) {
+                        seg_y(P, t.seg)[row] += P.scale * v;
+                    } else {
+                        float u = 0.0f;
+                        for (int c = 0; c < NG; c++) u += pt[(r + t.rows) * NG + c];
+                        P.seg[0].y[row] = v / (1.0f + expf(-v)) * u;
+                    }
+                }
+                __syncwarp();
+            }
+            if (k >= S && k < my_tiles && lane == 0)
+                issue_tile<F>(P, blockIdx.x + k * gridDim.x, smem + L.stages + s * L.stage_bytes, &full[s]);
+        }
+        if (*abort_flag && lane == 0) atomicExch(P.err, MB200_ERR_TIMEOUT);
+        return;
+    }
+
+    // ---------------- consumer warps ----------------
+    // Bind the warp to a column group: groups get warps in proportion to their
+    // work per row (a trailing group of v columns packs G/v rows into a pass).
+    const int v_last = P.bpr - (NG - 1) * F::kG;
+    const int rpp_last = (F::kG % v_last == 0) ? F::kG / v_last : 1;
+    // work units per row in 1/rpp_last: full groups weigh rpp_last, the last group 1
+    const int weight_total = (NG - 1) * rpp_last + 1;
+    int ng, idx, cnt;
+    {
+        // warps [0, n_last) serve the last group, the rest are dealt round-robin to full groups
+        int n_last = (kConsumers + weight_total / 2) / weight_total;
+        if (n_last < 1) n_last = 1;
+        if (NG == 1) n_last = kConsumers;
+        if (NG > 1 && kConsumers - n_last < NG - 1) n_last = kConsumers - (NG - 1);
+        if (warp < n_last) {
+            ng = NG - 1;
+            idx = warp;
+            cnt = n_last;
+        } else {
+            const int w2 = warp - n_last, rest = kConsumers - n_last;
+            ng = w2 % (NG - 1);
+            idx = w2 / (NG - 1);
+            cnt = (rest - ng + (NG - 2)) / (NG - 1);
+        }
+    }
+    const int v = (ng == NG - 1) ? v_last : F::kG;
+    const int rpp = (ng == NG - 1) ? rpp_last : 1;
+    const int q = lane / F::kLanesPerBlock, sub = lane % F::kLanesPerBlock;
+    const bool lane_ok = q < v * rpp;
+    const int col = ng * F::kG + (lane_ok ? q % v : 0);
+    const int roff = lane_ok ? q / v : 0;
+    const int W = (rpp > 1) ? v * F::kLanesPerBlock : 32;
+    const uint32_t col_off = col * F::kBlockBytes;
+    typename F::XRegs xr;
+    F::load_xregs(xr, smem, L, col, sub, lane_ok);
+    const int unit_rows = RU * rpp;
+
+    for (int k = 0; k < my_tiles; k++) {
+        const int s = k % S;
+        const Tile t = tile_of(P, blockIdx.x + k * gridDim.x);
+        const int R = (P.mode == kSwiGLU) ? 2 * t.rows : t.rows;
+        uint32_t skew = 0;
+        if (F::kBlockBytes % 16 != 0) {
+            const uintptr_t begin = reinterpret_cast<uintptr_t>(seg_w(P, t.seg)) + (size_t)t.row0 * row_bytes;
+            skew = static_cast<uint32_t>(begin & 15);
+        }
+        const uint8_t *base = smem + L.stages + s * L.stage_bytes + skew;
+        float *pt = part + s * P.tile_rows * NG;
+
+        if (!mbar_wait(&full[s], (k / S) & 1)) *abort_flag = 1;
+
+        for (int r0 = idx * unit_rows; r0 < R; r0 += cnt * unit_rows) {
+            float acc[RU];
+#pragma unroll
+            for (int u = 0; u < RU; u++) {
+                const int row = r0 + u * rpp + roff;
+                const bool ok = lane_ok && row < R;
+                const uint8_t *blk = base + (size_t)min(row, R - 1) * row_bytes + col_off;
+                const float d = F::block_dot(blk, sub, xr);
+                acc[u] = ok ? d : 0.0f;
+            }
+            int which;
+            const float sum = packed_sum<RU>(acc, W, lane, which);
+            const int wr = W / RU;  // lanes per result
+            const int row = r0 + which * rpp + roff;
+            if ((lane & (wr - 1)) == 0 && row < R) pt[row * NG + ng] = sum;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+        if (*abort_flag) break;
+    }
+}
+
+template <class F, int RU>
+inline void launch_one(Params &P, const Layout &L, int grid, cudaStream_t stream)
+{
+    static bool optin = false;
+    if (!optin) {
+        cudaFuncSetAttribute(stream_kernel<F, RU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        optin = true;
+    }
+    stream_kernel<F, RU><<<grid, kThreads, L.total, stream>>>(P);
+}
+
+template <class F>
+inline void init_attrs()
+{
+    cudaFuncSetAttribute(stream_kernel<F, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(stream_kernel<F, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaFuncSetAttribute(stream_kernel<F, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+}
+
+// Host-side geometry + launch. Segment pointers/rows, x, mode etc. are set by the caller.
+template <class F>
+inline void launch(Params &P, cudaStream_t stream, const char *where)
+{
+    if (P.n_cols <= 0) return;
+    if (P.n_cols > F::kMaxCols) {
+        fprintf(stderr, "[mnemo_b200] %s: n_cols=%d exceeds the supported %d\n", where, P.n_cols, F::kMaxCols);
+        set_status(MB200_ERR_UNSUPPORTED, where);
+        return;
+    }
+    for (int i = 0; i < P.nseg; i++)
+        if (reinterpret_cast<uintptr_t>(P.seg[i].w) & (F::kBaseAlign - 1)) {
+            fprintf(stderr, "[mnemo_b200] %s: tensor %d is not %d-byte aligned\n", where, i, F::kBaseAlign);
+            set_status(MB200_ERR_ARG, where);
+            return;
+        }
+    P.bpr = (P.n_cols + 255) / 256;
+    const int row_bytes = P.bpr * F::kBlockBytes;
+    const int NG = (P.bpr + F::kG - 1) / F::kG;
+    const int v_last = P.bpr - (NG - 1) * F::kG;
+    const int rpp_last = (F::kG % v_last == 0) ? F::kG / v_last : 1;
+
+    // rows per tile: a multiple of the rows one sweep of all consumer warps covers
+    // (so every warp gets whole units), close to F::kTileTargetBytes
+    int max_rows = 0;
+    for (int i = 0; i < P.nseg; i++) max_rows = P.seg[i].rows > max_rows ? P.seg[i].rows : max_rows;
+    if (max_rows <= 0) return;
+    const int weight_total = (NG - 1) * rpp_last + 1;
+    int n_last = (kConsumers + weight_total / 2) / weight_total;
+    if (n_last < 1) n_last = 1;
+    if (NG == 1) n_last = kConsumers;
+    if (NG > 1 && kConsumers - n_last < NG - 1) n_last = kConsumers - (NG - 1);
+    const int n_full = NG > 1 ? (kConsumers - n_last) / (NG - 1) : 0;  // warps per full group (min)
+    int target = F::kTileTargetBytes / row_bytes;
+    if (target < 1) target = 1;
+    int ru = 4;
+    int sweep;
+    for (;; ru >>= 1) {
+        const int a = n_last * rpp_last * ru;
+        const int b = NG > 1 ? (n_full > 0 ? n_full : 1) * ru : a;
+        sweep = a > b ? a : b;
+        if (ru == 1 || sweep <= target) break;
+    }
+    int tr = sweep * (target / sweep > 0 ? target / sweep : 1);
+    // do not make tiles so large that the grid cannot cover all SMs
+    while (tr > sweep && (max_rows + tr - 1) / tr < kSMs) tr -= sweep;
+    if (P.mode == kSwiGLU && (tr & 1)) tr *= 2;
+    P.tile_rows = tr;
+
+    const int per = (P.mode == kSwiGLU) ? tr / 2 : tr;
+    int tiles = 0;
+    const int counted = (P.mode == kSwiGLU) ? 1 : P.nseg;
+    for (int i = 0; i < P.nseg; i++) {
+        P.seg[i].tile0 = tiles;
+        if (i < counted) tiles += (P.seg[i].rows + per - 1) / per;
+    }
+    P.n_tiles = tiles;
+    if (tiles == 0) return;
+    P.err = device_error_word();
+
+    int S = kMaxStages;
+    Layout L = layout<F>(P.bpr, P.tile_rows, S);
+    while (S > 2 && L.total > 200 * 1024) {
+        S--;
+        L = layout<F>(P.bpr, P.tile_rows, S);
+    }
+    if (L.total > 227 * 1024) {
+        fprintf(stderr, "[mnemo_b200] %s: shape does not fit shared memory\n", where);
+        set_status(MB200_ERR_UNSUPPORTED, where);
+        return;
+    }
+    P.stages = S;
+    const int grid = tiles < kSMs ? tiles : kSMs;
+    if (ru == 4)
+        launch_one<F, 4>(P, L, grid, stream);
+    else if (ru == 2)
+        launch_one<F, 2>(P, L, grid, stream);
+    else
+        launch_one<F, 1>(P, L, grid, stream);
+    MB200_CHECK_LAUNCH(where);
+}
+
+}  // namespace stream
+}  // namespace mb200
