@@ -101,11 +101,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 // Returns false if the phase did not complete within the iteration budget
 // (each try_wait already blocks for a hardware time slice).
 constexpr uint32_t kWaitBudget = 1u << 20;
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
 {
+#ifdef MB200_V_TESTWAIT
+    for (uint32_t i = 0; i < kWaitBudget * 16; i++) {
+        if (mbar_test_wait(bar, parity)) return true;
+        __nanosleep(20);
+    }
+    return false;
+#else
     for (uint32_t i = 0; i < kWaitBudget; i++)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
+#endif
 }
 
 // 1-D bulk copy; src and dst 16-byte aligned, bytes a multiple of 16.
@@ -133,58 +153,6 @@ __device__ __forceinline__ void q4k_scale_pair(uint32_t a, uint32_t b, uint32_t 
     } else {
         sc2 = (cs & 0x0F0Fu) | ((as >> 2) & 0x3030u);
         m2 = ((cs >> 4) & 0x0F0Fu) | ((bs >> 2) & 0x3030u);
-    }
-}
-
-// ---- activation split shared by the Q4_K and Q6_K streaming kernels ----------
-// x[c] ~= s1[c/32] * (q1[c] + q2[c]/254) with q1, q2 int8: two exact dp4a dot
-// products then recover sum(q*x) to ~1e-5 relative (|error| <= max|x|/64516 per
-// 32-column group). xsum holds exact fp32 sums of x over SUM_COLS columns (for
-// the terms that multiply sum(x): Q4_K's -dmin*m, Q6_K's -32 offset).
-// Columns outside the matrix are stored as zero. GROUP4: a group of 4 columns
-// counts only if all four are < n_cols (the Q4_K kernels' tail rule,
-// reference src/kernels.cu:124,131); otherwise per column (Q6_K, :474).
-// kpad is a multiple of 256; all threads of the CTA call this.
-template <int THREADS, int SUM_COLS, bool GROUP4>
-__device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_cols, int kpad,
-                                           int8_t *q1, int8_t *q2, float *s1, float *xsum)
-{
-    static_assert(SUM_COLS == 16 || SUM_COLS == 8, "sum granularity");
-    const int lane = threadIdx.x & 31;
-    for (int c0 = threadIdx.x * 4; c0 < kpad; c0 += THREADS * 4) {
-        float v[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const bool in = GROUP4 ? (c0 + 3) < n_cols : (c0 + i) < n_cols;
-            v[i] = in ? __ldg(x + c0 + i) : 0.0f;
-        }
-        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-        float sum = (v[0] + v[1]) + (v[2] + v[3]);
-        // 8 lanes = 32 columns share a scale
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        if (SUM_COLS == 16) sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        const float sc = amax * (1.0f / 127.0f);
-        const float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
-        uint32_t p1 = 0, p2 = 0;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float a = fminf(fmaxf(rintf(v[i] * inv), -127.0f), 127.0f);
-            const float r = fmaf(-a, sc, v[i]);
-            const float b = fminf(fmaxf(rintf(r * inv * 254.0f), -127.0f), 127.0f);
-            p1 |= (static_cast<uint32_t>(static_cast<int>(a)) & 0xFFu) << (8 * i);
-            p2 |= (static_cast<uint32_t>(static_cast<int>(b)) & 0xFFu) << (8 * i);
-        }
-        reinterpret_cast<uint32_t *>(q1)[c0 >> 2] = p1;
-        reinterpret_cast<uint32_t *>(q2)[c0 >> 2] = p2;
-        if ((lane & 7) == 0) s1[c0 >> 5] = sc;
-        if (SUM_COLS == 16) {
-            if ((lane & 3) == 0) xsum[c0 >> 4] = sum;
-        } else {
-            if ((lane & 1) == 0) xsum[c0 >> 3] = sum;
-        }
     }
 }
 

@@ -27,6 +27,11 @@ struct Q4 {
     static constexpr int kBaseAlign = 16;
     static constexpr int kTileTargetBytes = 27648;
     static constexpr int kMaxCols = 16384;
+    // x staging: 16 words per lane slot, slot = 4 * block-column + g
+    static constexpr int kXWords = 16;
+    static constexpr int kSlotsPerBlock = 4;
+    __device__ static __forceinline__ int xslot(int c0) { return c0 >> 6; }
+    __device__ static __forceinline__ int xword(int c0) { return ((c0 & 31) >> 2) + ((c0 & 32) ? 8 : 0); }
 
     struct XRegs {
         uint32_t q1[16], q2[16];  // [0..7]: columns of the low-nibble sub-block, [8..15]: high
@@ -35,16 +40,17 @@ struct Q4 {
     };
 
     __device__ static __forceinline__ void load_xregs(XRegs &xr, const uint8_t *smem, const stream::Layout &L,
-                                                      int col, int g, bool valid)
+                                                      int bpr, int col, int g, bool valid)
     {
-        const uint32_t *q1 = reinterpret_cast<const uint32_t *>(smem + L.xq1) + col * 64 + g * 16;
-        const uint32_t *q2 = reinterpret_cast<const uint32_t *>(smem + L.xq2) + col * 64 + g * 16;
+        const int pitch = kSlotsPerBlock * bpr + 1;
+        const uint32_t *q1 = reinterpret_cast<const uint32_t *>(smem + L.xq1) + col * 4 + g;
+        const uint32_t *q2 = reinterpret_cast<const uint32_t *>(smem + L.xq2) + col * 4 + g;
         const float *s1 = reinterpret_cast<const float *>(smem + L.xs1) + col * 8 + g * 2;
         const float *xs = reinterpret_cast<const float *>(smem + L.xsum) + col * 16 + g * 4;
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-            xr.q1[i] = valid ? q1[i] : 0u;
-            xr.q2[i] = valid ? q2[i] : 0u;
+            xr.q1[i] = valid ? q1[i * pitch] : 0u;
+            xr.q2[i] = valid ? q2[i * pitch] : 0u;
         }
         xr.kl = valid ? s1[0] * (1.0f / 254.0f) : 0.0f;
         xr.kh = valid ? s1[1] * (1.0f / (254.0f * 16.0f)) : 0.0f;
@@ -177,3 +183,11 @@ int mb200_matvec_q4k_dual_swiglu(const void *w_gate, const void *w_up, const flo
 }
 
 }  // extern "C"
+
+#ifdef MB200_TRACE
+extern "C" void mb200_trace_read(void *dst)
+{
+    cudaMemcpyFromSymbol(dst, mb200::stream::g_trace, sizeof(long long) * mb200::kSMs * 2 * 16, 0,
+                         cudaMemcpyDeviceToDevice);
+}
+#endif

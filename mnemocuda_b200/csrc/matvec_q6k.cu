@@ -40,6 +40,11 @@ struct Q6 {
     static constexpr int kBaseAlign = 2;
     static constexpr int kTileTargetBytes = 20480;
     static constexpr int kMaxCols = 12288;  // one consumer warp per group of 4 block-columns
+    // x staging: 8 words per lane slot, slot = 8 * block-column + 4 * half + jj; word = 2g + i
+    static constexpr int kXWords = 8;
+    static constexpr int kSlotsPerBlock = 8;
+    __device__ static __forceinline__ int xslot(int c0) { return ((c0 >> 8) << 3) + (((c0 >> 7) & 1) << 2) + ((c0 >> 3) & 3); }
+    __device__ static __forceinline__ int xword(int c0) { return (((c0 >> 5) & 3) << 1) + ((c0 >> 2) & 1); }
 
     struct XRegs {
         uint32_t q1[8], q2[8];  // [2g + i]: columns 32g + 8jj + 4i .. +3 of the lane's half
@@ -48,12 +53,13 @@ struct Q6 {
     };
 
     __device__ static __forceinline__ void load_xregs(XRegs &xr, const uint8_t *smem, const stream::Layout &L,
-                                                      int col, int sub, bool valid)
+                                                      int bpr, int col, int sub, bool valid)
     {
         const int hh = sub >> 2, jj = sub & 3;
         const int c0 = col * 256 + hh * 128 + jj * 8;  // first column of the lane in group 0
-        const uint32_t *q1 = reinterpret_cast<const uint32_t *>(smem + L.xq1);
-        const uint32_t *q2 = reinterpret_cast<const uint32_t *>(smem + L.xq2);
+        const int pitch = kSlotsPerBlock * bpr + 1;
+        const uint32_t *q1 = reinterpret_cast<const uint32_t *>(smem + L.xq1) + col * 8 + sub;
+        const uint32_t *q2 = reinterpret_cast<const uint32_t *>(smem + L.xq2) + col * 8 + sub;
         const float *s1 = reinterpret_cast<const float *>(smem + L.xs1);
         const float *xs = reinterpret_cast<const float *>(smem + L.xsum);
 #pragma unroll
@@ -61,8 +67,8 @@ struct Q6 {
             const int c = c0 + 32 * g;
 #pragma unroll
             for (int i = 0; i < 2; i++) {
-                xr.q1[2 * g + i] = valid ? q1[(c >> 2) + i] : 0u;
-                xr.q2[2 * g + i] = valid ? q2[(c >> 2) + i] : 0u;
+                xr.q1[2 * g + i] = valid ? q1[(2 * g + i) * pitch] : 0u;
+                xr.q2[2 * g + i] = valid ? q2[(2 * g + i) * pitch] : 0u;
             }
             xr.k[g] = valid ? s1[c >> 5] * (1.0f / 254.0f) : 0.0f;
             xr.sx32[g] = valid ? 32.0f * xs[c >> 3] : 0.0f;
@@ -154,3 +160,11 @@ int mb200_matvec_q6k_scaled_add(const void *weights, const float *x, float *y, i
 }
 
 }  // extern "C"
+
+#ifdef MB200_TRACE
+extern "C" void mb200_trace_read_q6k(void *dst)
+{
+    cudaMemcpyFromSymbol(dst, mb200::stream::g_trace, sizeof(long long) * mb200::kSMs * 2 * 16, 0,
+                         cudaMemcpyDeviceToDevice);
+}
+#endif

@@ -1,14 +1,17 @@
 // Streaming dequant-matvec skeleton shared by the Q4_K and Q6_K kernels (batch 1).
 //
 // A weight matrix is a contiguous stream of super-blocks. It is cut into tiles
-// of whole rows; CTA c owns tiles c, c+grid, ... One producer warp moves each
-// tile into a ring of shared-memory stages with a 1-D bulk async copy (TMA
-// engine, completion on an mbarrier); kConsumers consumer warps wait on the
-// "full" barrier of a stage, compute their rows, publish partial sums in shared
-// memory and arrive on the stage's "empty" barrier; the producer warp then adds
-// the partials of each row in fixed order, applies the epilogue (store,
-// + residual, scaled accumulate, SwiGLU pairing) and refills the stage. There is
-// no block-wide barrier inside the loop, and every wait is bounded.
+// of whole rows; CTA c owns tiles c, c+grid, ... Three roles per CTA:
+//   * issuer (one lane of warp kConsumers): moves each tile into a ring of
+//     shared-memory stages with a 1-D bulk async copy (TMA engine, completion
+//     on the stage's "full" mbarrier) as soon as the stage's "empty" barrier flips;
+//   * kConsumers consumer warps: wait on "full", compute their rows, publish
+//     partial sums in shared memory, arrive on "empty";
+//   * epilogue warp (kConsumers+1): after "empty" flips, adds the partials of
+//     each row in fixed order, applies the epilogue (store, + residual, scaled
+//     accumulate, SwiGLU pairing) and arrives on the stage's next "full" phase,
+//     which is what lets consumers overwrite the partial-sum slot again.
+// There is no block-wide barrier inside the loop, and every wait is bounded.
 //
 // Work split inside a tile: a warp pass covers G = 32 / lanes-per-block
 // super-blocks. The block-columns of a row are split into column groups of G;
@@ -27,7 +30,7 @@ namespace mb200 {
 namespace stream {
 
 constexpr int kConsumers = 12;
-constexpr int kThreads = (kConsumers + 1) * 32;
+constexpr int kThreads = (kConsumers + 2) * 32;
 constexpr int kMaxStages = 6;
 
 enum : int { kStore = 0, kAddResidual = 1, kScaledAdd = 2, kSwiGLU = 3 };
@@ -61,8 +64,8 @@ __host__ __device__ inline Layout layout(int bpr, int tile_rows, int n_stages)
     const int ng = (bpr + F::kG - 1) / F::kG;
     int o = 0;
     s.bars = o;  o += 128;
-    s.xq1 = o;   o += kpad;
-    s.xq2 = o;   o += kpad;
+    s.xq1 = o;   o += F::kXWords * (F::kSlotsPerBlock * bpr + 1) * 4;  // [word][slot], +1 pad: conflict-free both ways
+    s.xq2 = o;   o += F::kXWords * (F::kSlotsPerBlock * bpr + 1) * 4;
     s.xs1 = o;   o += (kpad / 32) * 4;
     s.xsum = o;  o += (kpad / F::kSumCols) * 4;
     s.part = o;  o += n_stages * tile_rows * ng * 4;
@@ -137,7 +140,14 @@ __device__ __forceinline__ void issue_tile(const Params &P, int tile, uint8_t *s
     } else {
         span_of(seg_w(P, t.seg), row_bytes, t.row0, t.rows, src, bytes, skew);
         mbar_expect_tx(bar, bytes);
+#ifdef MB200_V_CHUNK
+        for (uint32_t o = 0; o < bytes; o += MB200_V_CHUNK) {
+            const uint32_t n = bytes - o < MB200_V_CHUNK ? bytes - o : MB200_V_CHUNK;
+            bulk_g2s(stage + o, src + o, n, bar);
+        }
+#else
         bulk_g2s(stage, src, bytes, bar);
+#endif
     }
 }
 
@@ -176,6 +186,92 @@ __device__ __forceinline__ float packed_sum(float (&a)[RU], int W, int lane, int
     return v;
 }
 
+#ifdef MB200_TRACE
+// Developer aid (off in product builds): per-CTA clock stamps at phase boundaries.
+static __device__ long long g_trace[kSMs * 2][16];  // one copy per translation unit
+#define MB200_STAMP(slot)                                                     \
+    do {                                                                      \
+        if ((threadIdx.x & 31) == 0 && blockIdx.x < kSMs * 2) {               \
+            long long t__;                                                    \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));           \
+            g_trace[blockIdx.x][slot] = t__;                                  \
+        }                                                                     \
+    } while (0)
+#else
+#define MB200_STAMP(slot) do {} while (0)
+#endif
+
+// Activation split: x[c] ~= s1[c/32] * (q1[c] + q2[c]/254) with q1, q2 int8, so
+// two exact dp4a dot products recover sum(q*x) to ~1e-5 relative
+// (|error| <= max|x|/64516 per 32-column group). xsum holds exact fp32 sums of
+// x over F::kSumCols columns (for the terms that multiply sum(x): Q4_K's
+// -dmin*m, Q6_K's -32 offset). Columns outside the matrix are stored as zero;
+// F::kGroup4Tail: a group of 4 columns counts only if all four are < n_cols
+// (the Q4_K kernels' tail rule, reference src/kernels.cu:124,131), else per
+// column (Q6_K, :474). The int8 words are stored transposed, [word][lane slot]
+// with an odd row pitch, so that the consumer lanes' register loads and these
+// stores are both free of bank conflicts. All loads of a thread are issued
+// before the first use: one memory round trip for K <= 3 * 4 * kThreads.
+template <class F>
+__device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_cols, int bpr,
+                                           uint32_t *q1, uint32_t *q2, float *s1, float *xsum)
+{
+    constexpr int UN = 3;
+    const int kpad = bpr * 256;
+    const int pitch = F::kSlotsPerBlock * bpr + 1;
+    const int lane = threadIdx.x & 31;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    for (int base = threadIdx.x * 4; base < kpad; base += kThreads * 4 * UN) {
+        float v[UN][4];
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const int c0 = base + u * kThreads * 4;
+            if (vec_ok && c0 + 3 < n_cols) {
+                const float4 t = __ldg(reinterpret_cast<const float4 *>(x + c0));
+                v[u][0] = t.x; v[u][1] = t.y; v[u][2] = t.z; v[u][3] = t.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const bool in = F::kGroup4Tail ? (c0 + 3) < n_cols : (c0 + i) < n_cols;
+                    v[u][i] = in ? __ldg(x + c0 + i) : 0.0f;
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const int c0 = base + u * kThreads * 4;
+            if (c0 >= kpad) break;  // warp-uniform: a warp covers 128 columns, kpad is a multiple of 256
+            float amax = fmaxf(fmaxf(fabsf(v[u][0]), fabsf(v[u][1])), fmaxf(fabsf(v[u][2]), fabsf(v[u][3])));
+            float sum = (v[u][0] + v[u][1]) + (v[u][2] + v[u][3]);
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));  // 8 lanes = 32 columns share a scale
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            if (F::kSumCols == 16) sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            const float sc = amax * (1.0f / 127.0f);
+            const float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+            uint32_t p1 = 0, p2 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float a = fminf(fmaxf(rintf(v[u][i] * inv), -127.0f), 127.0f);
+                const float r = fmaf(-a, sc, v[u][i]);
+                const float b = fminf(fmaxf(rintf(r * inv * 254.0f), -127.0f), 127.0f);
+                p1 |= (static_cast<uint32_t>(static_cast<int>(a)) & 0xFFu) << (8 * i);
+                p2 |= (static_cast<uint32_t>(static_cast<int>(b)) & 0xFFu) << (8 * i);
+            }
+            const int idx = F::xword(c0) * pitch + F::xslot(c0);
+            q1[idx] = p1;
+            q2[idx] = p2;
+            if ((lane & 7) == 0) s1[c0 >> 5] = sc;
+            if (F::kSumCols == 16) {
+                if ((lane & 3) == 0) xsum[c0 >> 4] = sum;
+            } else {
+                if ((lane & 1) == 0) xsum[c0 >> 3] = sum;
+            }
+        }
+    }
+}
+
 template <class F, int RU>
 __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
 {
@@ -189,57 +285,81 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int my_tiles = (P.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     if (my_tiles <= 0) return;
+    if (warp == 0) MB200_STAMP(0);
     const int NG = (P.bpr + F::kG - 1) / F::kG;
     const uint32_t row_bytes = P.bpr * F::kBlockBytes;
 
     if (tid == kConsumers * 32) {
         *abort_flag = 0;
         for (int s = 0; s < S; s++) {
-            mbar_init(&full[s], 1);
+            mbar_init(&full[s], 2);  // the issuer's expect_tx arrival + the epilogue warp's "partials are free"
             mbar_init(&empty[s], kConsumers);
         }
         mbar_fence_init();
-        for (int k = 0; k < S && k < my_tiles; k++)
-            issue_tile<F>(P, blockIdx.x + k * gridDim.x, smem + L.stages + k * L.stage_bytes, &full[k]);
+        for (int k = 0; k < S; k++) {
+            mbar_arrive(&full[k]);  // first phase: nothing to drain yet
+            if (k < my_tiles)
+                issue_tile<F>(P, blockIdx.x + k * gridDim.x, smem + L.stages + k * L.stage_bytes, &full[k]);
+        }
     }
-    quantize_x<kThreads, F::kSumCols, F::kGroup4Tail>(
-        P.x, P.n_cols, P.bpr * 256, reinterpret_cast<int8_t *>(smem + L.xq1),
-        reinterpret_cast<int8_t *>(smem + L.xq2), reinterpret_cast<float *>(smem + L.xs1),
-        reinterpret_cast<float *>(smem + L.xsum));
+    quantize_x<F>(P.x, P.n_cols, P.bpr, reinterpret_cast<uint32_t *>(smem + L.xq1),
+                  reinterpret_cast<uint32_t *>(smem + L.xq2), reinterpret_cast<float *>(smem + L.xs1),
+                  reinterpret_cast<float *>(smem + L.xsum));
+    if (warp == 0) MB200_STAMP(1);
     __syncthreads();  // the only block-wide barrier: x is staged, barriers are initialised
+    if (warp == 0) MB200_STAMP(2);
 
     if (warp == kConsumers) {
-        // ---------------- producer + epilogue warp ----------------
-        for (int k = 0; k < my_tiles + S; k++) {
-            const int s = k % S;
-            if (k >= S) {
-                const int kd = k - S;  // tile whose partials are complete once `empty` flips
-                if (!mbar_wait(&empty[s], (kd / S) & 1)) *abort_flag = 1;
-                if (*abort_flag) break;
-                const Tile t = tile_of(P, blockIdx.x + kd * gridDim.x);
-                const float *pt = part + s * P.tile_rows * NG;
-                for (int r = lane; r < t.rows; r += 32) {
-                    float v = 0.0f;
-                    for (int c = 0; c < NG; c++) v += pt[r * NG + c];
-                    const int row = t.row0 + r;
-                    if (P.mode == kStore) {
-                        seg_y(P, t.seg)[row] = v;
-                    } else if (P.mode == kAddResidual) {
-                        seg_y(P, t.seg)[row] = v + P.residual[row];
-                    } else if (P.mode == kScaledAdd) {
-                        seg_y(P, t.seg)[row] += P.scale * v;
-                    } else {
-                        float u = 0.0f;
-                        for (int c = 0; c < NG; c++) u += pt[(r + t.rows) * NG + c];
-                        P.seg[0].y[row] = v / (1.0f + expf(-v)) * u;
-                    }
+        // ---------------- issuer: refill a stage as soon as its consumers are done ----------------
+        if (lane == 0) {
+            int s = 0, ph = 0;
+            for (int k = S; k < my_tiles; k++) {
+                if (!mbar_wait(&empty[s], ph)) {
+                    *abort_flag = 1;
+                    break;
                 }
-                __syncwarp();
-            }
-            if (k >= S && k < my_tiles && lane == 0)
                 issue_tile<F>(P, blockIdx.x + k * gridDim.x, smem + L.stages + s * L.stage_bytes, &full[s]);
+                if (++s == S) {
+                    s = 0;
+                    ph ^= 1;
+                }
+            }
+        }
+        return;
+    }
+    if (warp == kConsumers + 1) {
+        // ---------------- epilogue warp ----------------
+        int s = 0, ph = 0;
+        for (int kd = 0; kd < my_tiles; kd++) {
+            if (!mbar_wait(&empty[s], ph)) *abort_flag = 1;
+            if (*abort_flag) break;
+            const Tile t = tile_of(P, blockIdx.x + kd * gridDim.x);
+            const float *pt = part + s * P.tile_rows * NG;
+            for (int r = lane; r < t.rows; r += 32) {
+                float v = 0.0f;
+                for (int c = 0; c < NG; c++) v += pt[r * NG + c];
+                const int row = t.row0 + r;
+                if (P.mode == kStore) {
+                    seg_y(P, t.seg)[row] = v;
+                } else if (P.mode == kAddResidual) {
+                    seg_y(P, t.seg)[row] = v + P.residual[row];
+                } else if (P.mode == kScaledAdd) {
+                    seg_y(P, t.seg)[row] += P.scale * v;
+                } else {
+                    float u = 0.0f;
+                    for (int c = 0; c < NG; c++) u += pt[(r + t.rows) * NG + c];
+                    P.seg[0].y[row] = v / (1.0f + expf(-v)) * u;
+                }
+            }
+            __syncwarp();
+            if (lane == 0 && kd + S < my_tiles) mbar_arrive(&full[s]);  // partial-sum slot s may be rewritten
+            if (++s == S) {
+                s = 0;
+                ph ^= 1;
+            }
         }
         if (*abort_flag && lane == 0) atomicExch(P.err, MB200_ERR_TIMEOUT);
+        MB200_STAMP(6);
         return;
     }
 
@@ -248,11 +368,10 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
     // work per row (a trailing group of v columns packs G/v rows into a pass).
     const int v_last = P.bpr - (NG - 1) * F::kG;
     const int rpp_last = (F::kG % v_last == 0) ? F::kG / v_last : 1;
-    // work units per row in 1/rpp_last: full groups weigh rpp_last, the last group 1
-    const int weight_total = (NG - 1) * rpp_last + 1;
+    const int weight_total = (NG - 1) * rpp_last + 1;  // full groups weigh rpp_last, the last group 1
     int ng, idx, cnt;
     {
-        // warps [0, n_last) serve the last group, the rest are dealt round-robin to full groups
+        // warps [0, n_last) serve the last group, the rest are dealt round-robin to the full groups
         int n_last = (kConsumers + weight_total / 2) / weight_total;
         if (n_last < 1) n_last = 1;
         if (NG == 1) n_last = kConsumers;
@@ -277,11 +396,11 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
     const int W = (rpp > 1) ? v * F::kLanesPerBlock : 32;
     const uint32_t col_off = col * F::kBlockBytes;
     typename F::XRegs xr;
-    F::load_xregs(xr, smem, L, col, sub, lane_ok);
+    F::load_xregs(xr, smem, L, P.bpr, col, sub, lane_ok);
     const int unit_rows = RU * rpp;
 
+    int s = 0, ph = 0;
     for (int k = 0; k < my_tiles; k++) {
-        const int s = k % S;
         const Tile t = tile_of(P, blockIdx.x + k * gridDim.x);
         const int R = (P.mode == kSwiGLU) ? 2 * t.rows : t.rows;
         uint32_t skew = 0;
@@ -292,8 +411,18 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
         const uint8_t *base = smem + L.stages + s * L.stage_bytes + skew;
         float *pt = part + s * P.tile_rows * NG;
 
-        if (!mbar_wait(&full[s], (k / S) & 1)) *abort_flag = 1;
+        if (!mbar_wait(&full[s], ph)) *abort_flag = 1;
+        if (warp == 0 && k == 0) MB200_STAMP(3);
+        if (warp == 0 && k == my_tiles - 1) MB200_STAMP(4);
 
+#ifdef MB200_V_NOCOMPUTE
+        if (k >= 0) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+            if (++s == S) { s = 0; ph ^= 1; }
+            continue;
+        }
+#endif
         for (int r0 = idx * unit_rows; r0 < R; r0 += cnt * unit_rows) {
             float acc[RU];
 #pragma unroll
@@ -313,7 +442,12 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
         if (*abort_flag) break;
+        if (++s == S) {
+            s = 0;
+            ph ^= 1;
+        }
     }
+    if (warp == 0) MB200_STAMP(5);
 }
 
 template <class F, int RU>
