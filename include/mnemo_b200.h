@@ -101,6 +101,14 @@ void mb200_clear_status(void);
 /* Synchronises the device and returns the device-side error word (0 = no kernel gave up on a wait). */
 int mb200_device_error(void);
 
+/* Programmatic dependent launch for the streaming matvec kernels. 0 (default): plain
+ * launches. 1: each kernel may start while the previous kernel of the stream is still
+ * draining; it requests its first weight tiles at once and waits for that kernel only
+ * before it reads x or writes y. Use 1 only when no weight tensor is written by the
+ * kernel immediately upstream in the same stream (weights loaded once, as the engine
+ * does at load time, satisfy this). Returns the previous setting. */
+int mb200_set_pdl(int enabled);
+
 /* act = silu(Wg x) * (Wu x): the expert gate+up pair with SwiGLU in the epilogue
  * (reference sequence src/forward.c:1128-1131: matvec_q4k_dual then swiglu). */
 int mb200_matvec_q4k_dual_swiglu(const void *w_gate, const void *w_up, const float *x, float *act,

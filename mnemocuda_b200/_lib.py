@@ -33,6 +33,7 @@ SIGNATURES = {
     "mb200_last_status_where": (C.c_char_p, []),
     "mb200_clear_status": (None, []),
     "mb200_device_error": (_i, []),
+    "mb200_set_pdl": (_i, [_i]),
     "mb200_matvec_q4k_dual_swiglu": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "mb200_matvec_q6k_scaled_add": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp]),
     "mb200_fill_q4k": (_i, [_vp, _sz, _u64, _vp]),

@@ -166,6 +166,13 @@ void cuda_matvec_q4k_scaled_add(const void *weights, const float *x, float *y, i
     stream::launch<Q4>(P, stream, "cuda_matvec_q4k_scaled_add");
 }
 
+int mb200_set_pdl(int enabled)
+{
+    const int prev = stream::pdl_mode();
+    stream::pdl_mode() = enabled ? 1 : 0;
+    return prev;
+}
+
 int mb200_matvec_q4k_dual_swiglu(const void *w_gate, const void *w_up, const float *x, float *act,
                                  int n_rows, int n_cols, cudaStream_t stream)
 {

@@ -1,7 +1,9 @@
 // Streaming dequant-matvec skeleton shared by the Q4_K and Q6_K kernels (batch 1).
 //
-// A weight matrix is a contiguous stream of super-blocks. It is cut into tiles
-// of whole rows; CTA c owns tiles c, c+grid, ... Three roles per CTA:
+// A weight matrix is a contiguous stream of super-blocks. The rows of all
+// segments of a call (one tensor; Q,K,V; gate,up) are split into one contiguous
+// range per CTA (balanced to a row), and each range is cut into tiles of whole
+// rows. Three roles per CTA:
 //   * issuer (one lane of warp kConsumers): moves each tile into a ring of
 //     shared-memory stages with a 1-D bulk async copy (TMA engine, completion
 //     on the stage's "full" mbarrier) as soon as the stage's "empty" barrier flips;
@@ -31,6 +33,7 @@ namespace stream {
 
 constexpr int kConsumers = 12;
 constexpr int kThreads = (kConsumers + 2) * 32;
+constexpr int kQuantThreads = kConsumers * 32;  // the consumer warps stage x; issuer/epilogue warps do not
 constexpr int kMaxStages = 6;
 
 enum : int { kStore = 0, kAddResidual = 1, kScaledAdd = 2, kSwiGLU = 3 };
@@ -39,16 +42,19 @@ struct Seg {
     const uint8_t *w;
     float *y;
     int rows;
-    int tile0;
+    int start;  // first virtual row of this segment (rows of all segments are numbered consecutively)
 };
 
 struct Params {
     Seg seg[3];
-    int nseg, n_tiles, tile_rows;  // SwiGLU: a tile holds tile_rows/2 gate rows then tile_rows/2 up rows
+    int nseg;
+    int vrows;      // virtual rows to split over CTAs (SwiGLU: gate rows; each brings its up row along)
+    int tile_rows;  // rows per tile and segment (SwiGLU tiles hold this many gate rows + as many up rows)
     const float *x;
     const float *residual;
     float scale;
     int n_cols, bpr, mode, stages;
+    int pdl;        // launched with programmatic stream serialization: wait for the upstream grid before touching x / y
     int *err;
 };
 
@@ -57,7 +63,7 @@ struct Layout {
 };
 
 template <class F>
-__host__ __device__ inline Layout layout(int bpr, int tile_rows, int n_stages)
+__host__ __device__ inline Layout layout(int bpr, int tile_rows_in_stage, int n_stages)
 {
     Layout s;
     const int kpad = bpr * 256;
@@ -68,10 +74,10 @@ __host__ __device__ inline Layout layout(int bpr, int tile_rows, int n_stages)
     s.xq2 = o;   o += F::kXWords * (F::kSlotsPerBlock * bpr + 1) * 4;
     s.xs1 = o;   o += (kpad / 32) * 4;
     s.xsum = o;  o += (kpad / F::kSumCols) * 4;
-    s.part = o;  o += n_stages * tile_rows * ng * 4;
+    s.part = o;  o += n_stages * tile_rows_in_stage * ng * 4;
     o = (o + 127) & ~127;
     s.stages = o;
-    s.stage_bytes = (tile_rows * bpr * F::kBlockBytes + 32 + 127) & ~127;  // +32: alignment skew, word over-read
+    s.stage_bytes = (tile_rows_in_stage * bpr * F::kBlockBytes + 32 + 127) & ~127;  // +32: alignment skew, word over-read
     s.total = o + n_stages * s.stage_bytes;
     return s;
 }
@@ -85,79 +91,72 @@ __device__ __forceinline__ float *seg_y(const Params &P, int i)
 {
     return i == 0 ? P.seg[0].y : (i == 1 ? P.seg[1].y : P.seg[2].y);
 }
-__device__ __forceinline__ int seg_rows(const Params &P, int i)
-{
-    return i == 0 ? P.seg[0].rows : (i == 1 ? P.seg[1].rows : P.seg[2].rows);
-}
-__device__ __forceinline__ int seg_tile0(const Params &P, int i)
-{
-    return i == 0 ? P.seg[0].tile0 : (i == 1 ? P.seg[1].tile0 : P.seg[2].tile0);
-}
 
 struct Tile {
-    int seg, row0, rows;  // rows: per segment (SwiGLU tiles hold 2*rows rows)
+    int seg, row0, rows;  // rows per segment (a SwiGLU tile holds 2*rows rows)
 };
 
-__device__ __forceinline__ Tile tile_of(const Params &P, int tile)
-{
-    Tile t;
-    t.seg = 0;
-    if (P.nseg > 1 && tile >= P.seg[1].tile0) t.seg = 1;
-    if (P.nseg > 2 && tile >= P.seg[2].tile0) t.seg = 2;
-    const int per = (P.mode == kSwiGLU) ? (P.tile_rows >> 1) : P.tile_rows;
-    t.row0 = (tile - seg_tile0(P, t.seg)) * per;
-    t.rows = min(per, seg_rows(P, t.seg) - t.row0);
-    return t;
-}
-
-// The 16-byte-aligned span enclosing rows [row0, row0+rows) of a tensor and the
-// offset of the first row inside it. Reading the few bytes before/after the rows
-// stays inside the 16-byte granule of a valid byte, hence inside a mapped page.
-__device__ __forceinline__ void span_of(const uint8_t *w, size_t row_bytes, int row0, int rows,
-                                        const uint8_t *&src, uint32_t &bytes, uint32_t &skew)
-{
-    const uintptr_t begin = reinterpret_cast<uintptr_t>(w) + (size_t)row0 * row_bytes;
-    const uintptr_t end = begin + (size_t)rows * row_bytes;
-    const uintptr_t a0 = begin & ~static_cast<uintptr_t>(15);
-    const uintptr_t a1 = (end + 15) & ~static_cast<uintptr_t>(15);
-    src = reinterpret_cast<const uint8_t *>(a0);
-    bytes = static_cast<uint32_t>(a1 - a0);
-    skew = static_cast<uint32_t>(begin - a0);
-}
+// Walks the tiles of this CTA's row range [cur, end). Every role runs the same walk.
+struct TileWalk {
+    int cur, end;
+    __device__ __forceinline__ void init(const Params &P)
+    {
+        cur = static_cast<int>((long long)P.vrows * blockIdx.x / gridDim.x);
+        end = static_cast<int>((long long)P.vrows * (blockIdx.x + 1) / gridDim.x);
+    }
+    __device__ __forceinline__ bool next(const Params &P, Tile &t)
+    {
+        if (cur >= end) return false;
+        int seg = 0, s0 = 0, s1 = P.seg[0].rows;
+        if (P.mode != kSwiGLU) {
+            if (P.nseg > 1 && cur >= P.seg[1].start) {
+                seg = 1;
+                s0 = P.seg[1].start;
+                s1 = s0 + P.seg[1].rows;
+            }
+            if (P.nseg > 2 && cur >= P.seg[2].start) {
+                seg = 2;
+                s0 = P.seg[2].start;
+                s1 = s0 + P.seg[2].rows;
+            }
+        }
+        const int stop = min(min(end, s1), cur + P.tile_rows);
+        t.seg = seg;
+        t.row0 = cur - s0;
+        t.rows = stop - cur;
+        cur = stop;
+        return true;
+    }
+};
 
 template <class F>
-__device__ __forceinline__ void issue_tile(const Params &P, int tile, uint8_t *stage, uint64_t *bar)
+__device__ __forceinline__ void issue_tile(const Params &P, const Tile &t, uint8_t *stage, uint64_t *bar)
 {
-    const Tile t = tile_of(P, tile);
     const size_t row_bytes = (size_t)P.bpr * F::kBlockBytes;
-    const uint8_t *src;
-    uint32_t bytes, skew;
-    if (P.mode == kSwiGLU) {  // Q4_K only: spans are exact (rows are multiples of 16 bytes)
+    if (P.mode == kSwiGLU) {  // Q4_K only: rows are multiples of 16 bytes, spans are exact
         const uint32_t half = t.rows * (uint32_t)row_bytes;
         mbar_expect_tx(bar, 2 * half);
         bulk_g2s(stage, P.seg[0].w + (size_t)t.row0 * row_bytes, half, bar);
         bulk_g2s(stage + half, P.seg[1].w + (size_t)t.row0 * row_bytes, half, bar);
     } else {
-        span_of(seg_w(P, t.seg), row_bytes, t.row0, t.rows, src, bytes, skew);
+        // The 16-byte-aligned span enclosing the rows. The few bytes read before/after them share a
+        // 16-byte granule with a valid byte, hence lie inside a mapped page.
+        const uintptr_t begin = reinterpret_cast<uintptr_t>(seg_w(P, t.seg)) + (size_t)t.row0 * row_bytes;
+        const uintptr_t stop = begin + (size_t)t.rows * row_bytes;
+        const uintptr_t a0 = begin & ~static_cast<uintptr_t>(15);
+        const uint32_t bytes = static_cast<uint32_t>(((stop + 15) & ~static_cast<uintptr_t>(15)) - a0);
         mbar_expect_tx(bar, bytes);
-#ifdef MB200_V_CHUNK
-        for (uint32_t o = 0; o < bytes; o += MB200_V_CHUNK) {
-            const uint32_t n = bytes - o < MB200_V_CHUNK ? bytes - o : MB200_V_CHUNK;
-            bulk_g2s(stage + o, src + o, n, bar);
-        }
-#else
-        bulk_g2s(stage, src, bytes, bar);
-#endif
+        bulk_g2s(stage, reinterpret_cast<const void *>(a0), bytes, bar);
     }
 }
 
 // Sum RU per-lane values over groups of W lanes (W = 32, 16 or 8), RU in {1,2,4}.
 // On return, lane l with (l & (W/RU - 1)) == 0 holds the sum for value index
 // `which` (= (l & (W-1)) / (W/RU)) of its W-lane group.
-template <int RU>
+template <int RU, bool W32>
 __device__ __forceinline__ float packed_sum(float (&a)[RU], int W, int lane, int &which)
 {
-    int off = W >> 1;
+    int off = W32 ? 16 : (W >> 1);
     float v;
     if (RU == 4) {
         const bool hi = (lane & off) != 0;
@@ -182,7 +181,12 @@ __device__ __forceinline__ float packed_sum(float (&a)[RU], int W, int lane, int
         v = a[0];
         which = 0;
     }
-    for (; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    if (W32) {
+#pragma unroll
+        for (int o = 16 / RU; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    } else {
+        for (; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    }
     return v;
 }
 
@@ -211,7 +215,8 @@ static __device__ long long g_trace[kSMs * 2][16];  // one copy per translation 
 // column (Q6_K, :474). The int8 words are stored transposed, [word][lane slot]
 // with an odd row pitch, so that the consumer lanes' register loads and these
 // stores are both free of bank conflicts. All loads of a thread are issued
-// before the first use: one memory round trip for K <= 3 * 4 * kThreads.
+// before the first use: one memory round trip for K <= 3 * 4 * kQuantThreads.
+// Called by the consumer warps only (threadIdx.x < kQuantThreads).
 template <class F>
 __device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_cols, int bpr,
                                            uint32_t *q1, uint32_t *q2, float *s1, float *xsum)
@@ -221,11 +226,11 @@ __device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_co
     const int pitch = F::kSlotsPerBlock * bpr + 1;
     const int lane = threadIdx.x & 31;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-    for (int base = threadIdx.x * 4; base < kpad; base += kThreads * 4 * UN) {
+    for (int base = threadIdx.x * 4; base < kpad; base += kQuantThreads * 4 * UN) {
         float v[UN][4];
 #pragma unroll
         for (int u = 0; u < UN; u++) {
-            const int c0 = base + u * kThreads * 4;
+            const int c0 = base + u * kQuantThreads * 4;
             if (vec_ok && c0 + 3 < n_cols) {
                 const float4 t = __ldg(reinterpret_cast<const float4 *>(x + c0));
                 v[u][0] = t.x; v[u][1] = t.y; v[u][2] = t.z; v[u][3] = t.w;
@@ -239,7 +244,7 @@ __device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_co
         }
 #pragma unroll
         for (int u = 0; u < UN; u++) {
-            const int c0 = base + u * kThreads * 4;
+            const int c0 = base + u * kQuantThreads * 4;
             if (c0 >= kpad) break;  // warp-uniform: a warp covers 128 columns, kpad is a multiple of 256
             float amax = fmaxf(fmaxf(fabsf(v[u][0]), fabsf(v[u][1])), fmaxf(fabsf(v[u][2]), fabsf(v[u][3])));
             float sum = (v[u][0] + v[u][1]) + (v[u][2] + v[u][3]);
@@ -272,53 +277,58 @@ __device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_co
     }
 }
 
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 template <class F, int RU>
 __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     const int S = P.stages;
-    const Layout L = layout<F>(P.bpr, P.tile_rows, S);
+    const int stage_rows = (P.mode == kSwiGLU) ? 2 * P.tile_rows : P.tile_rows;
+    const Layout L = layout<F>(P.bpr, stage_rows, S);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.bars);
     uint64_t *empty = full + kMaxStages;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.bars + 120);
     float *part = reinterpret_cast<float *>(smem + L.part);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int my_tiles = (P.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    if (my_tiles <= 0) return;
     if (warp == 0) MB200_STAMP(0);
     const int NG = (P.bpr + F::kG - 1) / F::kG;
     const uint32_t row_bytes = P.bpr * F::kBlockBytes;
+    const int part_pitch = stage_rows * NG;
 
-    if (tid == kConsumers * 32) {
-        *abort_flag = 0;
-        for (int s = 0; s < S; s++) {
-            mbar_init(&full[s], 2);  // the issuer's expect_tx arrival + the epilogue warp's "partials are free"
-            mbar_init(&empty[s], kConsumers);
-        }
-        mbar_fence_init();
-        for (int k = 0; k < S; k++) {
-            mbar_arrive(&full[k]);  // first phase: nothing to drain yet
-            if (k < my_tiles)
-                issue_tile<F>(P, blockIdx.x + k * gridDim.x, smem + L.stages + k * L.stage_bytes, &full[k]);
-        }
-    }
-    quantize_x<F>(P.x, P.n_cols, P.bpr, reinterpret_cast<uint32_t *>(smem + L.xq1),
-                  reinterpret_cast<uint32_t *>(smem + L.xq2), reinterpret_cast<float *>(smem + L.xs1),
-                  reinterpret_cast<float *>(smem + L.xsum));
-    if (warp == 0) MB200_STAMP(1);
-    __syncthreads();  // the only block-wide barrier: x is staged, barriers are initialised
-    if (warp == 0) MB200_STAMP(2);
+    TileWalk walk;
+    walk.init(P);
 
     if (warp == kConsumers) {
-        // ---------------- issuer: refill a stage as soon as its consumers are done ----------------
+        // ---------------- issuer ----------------
+        // The weights never depend on the upstream kernel, so the first stages are
+        // requested before the grid-dependency wait: they stream in while the
+        // upstream kernel drains and while x is staged.
         if (lane == 0) {
+            *abort_flag = 0;
+            for (int s = 0; s < S; s++) {
+                mbar_init(&full[s], 2);  // the issuer's expect_tx arrival + the epilogue warp's "partials are free"
+                mbar_init(&empty[s], kConsumers);
+            }
+            mbar_fence_init();
+            Tile t;
+            for (int s = 0; s < S; s++) {
+                mbar_arrive(&full[s]);  // first phase: nothing to drain yet
+                if (walk.next(P, t)) issue_tile<F>(P, t, smem + L.stages + s * L.stage_bytes, &full[s]);
+            }
+        }
+        __syncthreads();
+        if (lane == 0) {
+            if (P.pdl) grid_dep_launch();
+            Tile t;
             int s = 0, ph = 0;
-            for (int k = S; k < my_tiles; k++) {
+            while (walk.next(P, t)) {
                 if (!mbar_wait(&empty[s], ph)) {
                     *abort_flag = 1;
                     break;
                 }
-                issue_tile<F>(P, blockIdx.x + k * gridDim.x, smem + L.stages + s * L.stage_bytes, &full[s]);
+                issue_tile<F>(P, t, smem + L.stages + s * L.stage_bytes, &full[s]);
                 if (++s == S) {
                     s = 0;
                     ph ^= 1;
@@ -329,12 +339,17 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
     }
     if (warp == kConsumers + 1) {
         // ---------------- epilogue warp ----------------
+        __syncthreads();
+        if (P.pdl) grid_dep_wait();  // y / residual may still be in use by the upstream kernel
+        Tile t, ahead;
+        TileWalk look = walk;
+        for (int i = 0; i < S; i++) look.next(P, ahead);  // `look` runs S tiles ahead: does stage s get reused?
         int s = 0, ph = 0;
-        for (int kd = 0; kd < my_tiles; kd++) {
+        while (walk.next(P, t)) {
+            const bool reused = look.next(P, ahead);
             if (!mbar_wait(&empty[s], ph)) *abort_flag = 1;
             if (*abort_flag) break;
-            const Tile t = tile_of(P, blockIdx.x + kd * gridDim.x);
-            const float *pt = part + s * P.tile_rows * NG;
+            const float *pt = part + s * part_pitch;
             for (int r = lane; r < t.rows; r += 32) {
                 float v = 0.0f;
                 for (int c = 0; c < NG; c++) v += pt[r * NG + c];
@@ -352,7 +367,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
                 }
             }
             __syncwarp();
-            if (lane == 0 && kd + S < my_tiles) mbar_arrive(&full[s]);  // partial-sum slot s may be rewritten
+            if (lane == 0 && reused) mbar_arrive(&full[s]);  // partial-sum slot s may be rewritten
             if (++s == S) {
                 s = 0;
                 ph ^= 1;
@@ -364,6 +379,14 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
     }
 
     // ---------------- consumer warps ----------------
+    if (P.pdl) grid_dep_wait();  // x is produced by the upstream kernel
+    quantize_x<F>(P.x, P.n_cols, P.bpr, reinterpret_cast<uint32_t *>(smem + L.xq1),
+                  reinterpret_cast<uint32_t *>(smem + L.xq2), reinterpret_cast<float *>(smem + L.xs1),
+                  reinterpret_cast<float *>(smem + L.xsum));
+    if (warp == 0) MB200_STAMP(1);
+    __syncthreads();  // the only block-wide barrier: x is staged, barriers are initialised
+    if (warp == 0) MB200_STAMP(2);
+
     // Bind the warp to a column group: groups get warps in proportion to their
     // work per row (a trailing group of v columns packs G/v rows into a pass).
     const int v_last = P.bpr - (NG - 1) * F::kG;
@@ -394,14 +417,18 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
     const int col = ng * F::kG + (lane_ok ? q % v : 0);
     const int roff = lane_ok ? q / v : 0;
     const int W = (rpp > 1) ? v * F::kLanesPerBlock : 32;
-    const uint32_t col_off = col * F::kBlockBytes;
     typename F::XRegs xr;
     F::load_xregs(xr, smem, L, P.bpr, col, sub, lane_ok);
     const int unit_rows = RU * rpp;
+    const uint32_t lane_base = col * F::kBlockBytes + roff * row_bytes + idx * unit_rows * row_bytes;
+    const uint32_t unit_stride = cnt * unit_rows * row_bytes;
+    const uint32_t pass_stride = rpp * row_bytes;
+    const bool all_lanes = (v * rpp == F::kG);  // no idle lane groups
 
+    Tile t;
     int s = 0, ph = 0;
-    for (int k = 0; k < my_tiles; k++) {
-        const Tile t = tile_of(P, blockIdx.x + k * gridDim.x);
+    int k = 0;
+    while (walk.next(P, t)) {
         const int R = (P.mode == kSwiGLU) ? 2 * t.rows : t.rows;
         uint32_t skew = 0;
         if (F::kBlockBytes % 16 != 0) {
@@ -409,39 +436,55 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
             skew = static_cast<uint32_t>(begin & 15);
         }
         const uint8_t *base = smem + L.stages + s * L.stage_bytes + skew;
-        float *pt = part + s * P.tile_rows * NG;
+        float *pt = part + s * part_pitch + ng;
 
+#ifndef MB200_V_NOWAIT
         if (!mbar_wait(&full[s], ph)) *abort_flag = 1;
-        if (warp == 0 && k == 0) MB200_STAMP(3);
-        if (warp == 0 && k == my_tiles - 1) MB200_STAMP(4);
-
-#ifdef MB200_V_NOCOMPUTE
-        if (k >= 0) {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-            if (++s == S) { s = 0; ph ^= 1; }
-            continue;
-        }
 #endif
-        for (int r0 = idx * unit_rows; r0 < R; r0 += cnt * unit_rows) {
+        if (warp == 0 && k == 0) MB200_STAMP(3);
+        if (warp == 0) MB200_STAMP(4);
+        k++;
+
+        int r0 = idx * unit_rows;
+        const uint8_t *up = base + lane_base;
+        // fast path: whole units inside the tile, every lane busy -> no bounds logic
+        if (all_lanes) {
+            for (; r0 + unit_rows <= R; r0 += cnt * unit_rows, up += unit_stride) {
+                float acc[RU];
+#pragma unroll
+                for (int u = 0; u < RU; u++) acc[u] = F::block_dot(up + u * pass_stride, sub, xr);
+                int which;
+                float sum;
+                if (W == 32)
+                    sum = packed_sum<RU, true>(acc, 32, lane, which);
+                else
+                    sum = packed_sum<RU, false>(acc, W, lane, which);
+                const int wr = W / RU;  // lanes per result
+                if ((lane & (wr - 1)) == 0) pt[(r0 + which * rpp + roff) * NG] = sum;
+            }
+        }
+        // general path: ragged units, idle lane groups
+        for (; r0 < R; r0 += cnt * unit_rows) {
             float acc[RU];
 #pragma unroll
             for (int u = 0; u < RU; u++) {
                 const int row = r0 + u * rpp + roff;
                 const bool ok = lane_ok && row < R;
-                const uint8_t *blk = base + (size_t)min(row, R - 1) * row_bytes + col_off;
+                const uint8_t *blk = base + (size_t)min(row, R - 1) * row_bytes + col * F::kBlockBytes;
                 const float d = F::block_dot(blk, sub, xr);
                 acc[u] = ok ? d : 0.0f;
             }
             int which;
-            const float sum = packed_sum<RU>(acc, W, lane, which);
-            const int wr = W / RU;  // lanes per result
+            const float sum = packed_sum<RU, false>(acc, W, lane, which);
+            const int wr = W / RU;
             const int row = r0 + which * rpp + roff;
-            if ((lane & (wr - 1)) == 0 && row < R) pt[row * NG + ng] = sum;
+            if ((lane & (wr - 1)) == 0 && row < R) pt[row * NG] = sum;
         }
         __syncwarp();
+#ifndef MB200_V_NOWAIT
         if (lane == 0) mbar_arrive(&empty[s]);
         if (*abort_flag) break;
+#endif
         if (++s == S) {
             s = 0;
             ph ^= 1;
@@ -450,15 +493,31 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
     if (warp == 0) MB200_STAMP(5);
 }
 
+// 0: plain launches. 1: launches carry the programmatic-stream-serialization
+// attribute, so a kernel may start while the previous kernel of the stream is
+// still draining; it then prefetches weights early and waits for that kernel
+// only before it reads x or writes y. Only safe when the weight tensors are
+// not produced by the kernel immediately upstream in the same stream.
+inline int &pdl_mode()
+{
+    static int mode = 0;
+    return mode;
+}
+
 template <class F, int RU>
 inline void launch_one(Params &P, const Layout &L, int grid, cudaStream_t stream)
 {
-    static bool optin = false;
-    if (!optin) {
-        cudaFuncSetAttribute(stream_kernel<F, RU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        optin = true;
-    }
-    stream_kernel<F, RU><<<grid, kThreads, L.total, stream>>>(P);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = L.total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = P.pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, stream_kernel<F, RU>, P);
 }
 
 template <class F>
@@ -473,6 +532,11 @@ inline void init_attrs()
 template <class F>
 inline void launch(Params &P, cudaStream_t stream, const char *where)
 {
+    static bool attrs_done = false;
+    if (!attrs_done) {
+        init_attrs<F>();
+        attrs_done = true;
+    }
     if (P.n_cols <= 0) return;
     if (P.n_cols > F::kMaxCols) {
         fprintf(stderr, "[mnemo_b200] %s: n_cols=%d exceeds the supported %d\n", where, P.n_cols, F::kMaxCols);
@@ -491,49 +555,65 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
     const int v_last = P.bpr - (NG - 1) * F::kG;
     const int rpp_last = (F::kG % v_last == 0) ? F::kG / v_last : 1;
 
-    // rows per tile: a multiple of the rows one sweep of all consumer warps covers
-    // (so every warp gets whole units), close to F::kTileTargetBytes
-    int max_rows = 0;
-    for (int i = 0; i < P.nseg; i++) max_rows = P.seg[i].rows > max_rows ? P.seg[i].rows : max_rows;
-    if (max_rows <= 0) return;
+    // virtual rows
+    int vrows = 0;
+    if (P.mode == kSwiGLU) {
+        vrows = P.seg[0].rows;
+        P.seg[0].start = 0;
+        P.seg[1].start = 0;
+    } else {
+        for (int i = 0; i < P.nseg; i++) {
+            P.seg[i].start = vrows;
+            vrows += P.seg[i].rows > 0 ? P.seg[i].rows : 0;
+        }
+    }
+    if (vrows <= 0) return;
+    P.vrows = vrows;
+    const int grid = vrows < kSMs ? vrows : kSMs;
+    const int per_cta = (vrows + grid - 1) / grid;  // rows of the longest range
+    const int mult = (P.mode == kSwiGLU) ? 2 : 1;   // stage rows per virtual row
+
+    // rows that one round of all consumer warps covers at RU = 1
     const int weight_total = (NG - 1) * rpp_last + 1;
     int n_last = (kConsumers + weight_total / 2) / weight_total;
     if (n_last < 1) n_last = 1;
     if (NG == 1) n_last = kConsumers;
     if (NG > 1 && kConsumers - n_last < NG - 1) n_last = kConsumers - (NG - 1);
-    const int n_full = NG > 1 ? (kConsumers - n_last) / (NG - 1) : 0;  // warps per full group (min)
-    int target = F::kTileTargetBytes / row_bytes;
-    if (target < 1) target = 1;
-    int ru = 4;
-    int sweep;
-    for (;; ru >>= 1) {
-        const int a = n_last * rpp_last * ru;
-        const int b = NG > 1 ? (n_full > 0 ? n_full : 1) * ru : a;
-        sweep = a > b ? a : b;
-        if (ru == 1 || sweep <= target) break;
-    }
-    int tr = sweep * (target / sweep > 0 ? target / sweep : 1);
-    // do not make tiles so large that the grid cannot cover all SMs
-    while (tr > sweep && (max_rows + tr - 1) / tr < kSMs) tr -= sweep;
-    if (P.mode == kSwiGLU && (tr & 1)) tr *= 2;
-    P.tile_rows = tr;
+    const int n_full = NG > 1 ? (kConsumers - n_last) / (NG - 1) : 0;
+    const int a1 = n_last * rpp_last, b1 = NG > 1 ? (n_full > 0 ? n_full : 1) : a1;
+    const int sweep1 = a1 > b1 ? a1 : b1;
 
-    const int per = (P.mode == kSwiGLU) ? tr / 2 : tr;
-    int tiles = 0;
-    const int counted = (P.mode == kSwiGLU) ? 1 : P.nseg;
-    for (int i = 0; i < P.nseg; i++) {
-        P.seg[i].tile0 = tiles;
-        if (i < counted) tiles += (P.seg[i].rows + per - 1) / per;
+    // RU: the fewest pass-times to cover the longest range; ties go to the larger RU (more independent work per warp)
+    int ru = 1, best = 1 << 30;
+    for (int cand = 1; cand <= 4; cand *= 2) {
+        const int rows = mult * per_cta;
+        const int cost = ((rows + sweep1 * cand - 1) / (sweep1 * cand)) * cand;
+        if (cost <= best) {
+            best = cost;
+            ru = cand;
+        }
     }
-    P.n_tiles = tiles;
-    if (tiles == 0) return;
-    P.err = device_error_word();
+    // tile: a whole number of sweeps near the target size, never more than the range
+    const int sweep = sweep1 * ru;
+    int target = F::kTileTargetBytes / row_bytes;  // stage rows
+    if (target < 1) target = 1;
+    int stage_rows = sweep * (target / sweep > 0 ? target / sweep : 1);
+    if (stage_rows > mult * per_cta) stage_rows = mult * per_cta;
+    if (mult == 2 && (stage_rows & 1)) stage_rows += 1;
+    P.tile_rows = stage_rows / mult;
+    if (P.tile_rows < 1) P.tile_rows = 1;
+    stage_rows = P.tile_rows * mult;
 
     int S = kMaxStages;
-    Layout L = layout<F>(P.bpr, P.tile_rows, S);
+    Layout L = layout<F>(P.bpr, stage_rows, S);
     while (S > 2 && L.total > 200 * 1024) {
         S--;
-        L = layout<F>(P.bpr, P.tile_rows, S);
+        L = layout<F>(P.bpr, stage_rows, S);
+    }
+    while (L.total > 227 * 1024 && P.tile_rows > 1) {  // very wide rows: shrink the tile
+        P.tile_rows = (P.tile_rows + 1) / 2;
+        stage_rows = P.tile_rows * mult;
+        L = layout<F>(P.bpr, stage_rows, S);
     }
     if (L.total > 227 * 1024) {
         fprintf(stderr, "[mnemo_b200] %s: shape does not fit shared memory\n", where);
@@ -541,7 +621,8 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
         return;
     }
     P.stages = S;
-    const int grid = tiles < kSMs ? tiles : kSMs;
+    P.pdl = pdl_mode();
+    P.err = device_error_word();
     if (ru == 4)
         launch_one<F, 4>(P, L, grid, stream);
     else if (ru == 2)

@@ -123,6 +123,11 @@ def mb200_device_error() -> int:
     return _lib.lib().mb200_device_error()
 
 
+def mb200_set_pdl(enabled: bool) -> bool:
+    """Programmatic dependent launch for the streaming matvecs (see include/mnemo_b200.h)."""
+    return bool(_lib.lib().mb200_set_pdl(1 if enabled else 0))
+
+
 def mb200_matvec_q4k_dual_swiglu(w_gate, w_up, x, act, n_rows, n_cols, stream=None):
     _check(_lib.lib().mb200_matvec_q4k_dual_swiglu(_ptr(w_gate), _ptr(w_up), _f32(x), _f32(act), n_rows,
                                                    n_cols, _stream(stream)), "mb200_matvec_q4k_dual_swiglu")
