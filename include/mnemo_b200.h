@@ -118,6 +118,43 @@ int mb200_matvec_q4k_dual_swiglu(const void *w_gate, const void *w_up, const flo
 int mb200_matvec_q6k_scaled_add(const void *weights, const float *x, float *y, int n_rows,
                                 int n_cols, float scale, cudaStream_t stream);
 
+/* ---- decode-time MoE block with the routed expert ids kept on the device ----
+ * The reference copies the k routed ids to the host and synchronises in every layer
+ * (src/forward.c:849-882) before issuing 3-4 launches per expert (src/forward.c:1122-1142).
+ * These three calls do the block in three launches with no host round trip; ids and
+ * weights stay in device memory (they are outputs of the first call and inputs of the others).
+ * An expert blob is [gate Q4_K EFF x H][up Q4_K EFF x H][down H x EFF], expert e at
+ * experts + e * expert_stride (src/forward.c:1127-1136). */
+
+/* Bytes of scratch mb200_router_topk needs: a ticket counter followed by the logits. */
+size_t mb200_router_scratch_bytes(int n_experts);
+
+/* logits = router_w x (fp32 [n_experts x n_cols], src/kernels.cu:859-880), then the
+ * reference's top-k + softmax (src/kernels.cu:993-1057), in one launch. scratch: 16-byte
+ * aligned device memory of mb200_router_scratch_bytes(n_experts) bytes whose first word is zero
+ * before the first call (each call leaves it zero); the logits can be read from it at byte 32. */
+int mb200_router_topk(const float *router_w, const float *x, void *scratch, int *indices,
+                      float *weights, int n_experts, int n_cols, int k, cudaStream_t stream);
+
+/* act[s][r] = silu(gate_e[r].x) * (up_e[r].x), e = ids[s], for the n_slots routed experts;
+ * act is [n_slots][EFF]. Slots with ids[s] < 0 give zeros. (src/forward.c:1128-1131 per expert.) */
+int mb200_moe_gate_up(const void *experts, size_t expert_stride, size_t gate_off, size_t up_off,
+                      const int *ids, int n_slots, const float *x, float *act, int EFF, int H,
+                      cudaStream_t stream);
+
+/* y[r] = (residual ? residual[r] : y[r]) + sum_s wts[s] * (down_e[r] . act[s]), slots added in
+ * order; down_type 14 = Q6_K, 12 = Q4_K (src/forward.c:1133-1141, and the zero + residual add
+ * around the expert loop: src/forward.c:875,1114). */
+int mb200_moe_down(const void *experts, size_t expert_stride, size_t down_off, int down_type,
+                   const int *ids, const float *wts, int n_slots, const float *act,
+                   const float *residual, float *y, int H, int EFF, cudaStream_t stream);
+
+/* The three calls in sequence. ids/wts: [k]; act: [k][EFF]; scratch as for mb200_router_topk. */
+int mb200_moe_block(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz,
+                    size_t up_sz, int down_type, int n_experts, int k, int H, int EFF,
+                    const float *x, const float *residual, float *out, int *ids, float *wts,
+                    float *act, void *scratch, cudaStream_t stream);
+
 /* Seeded synthetic tensors written on the device (benchmark workloads). */
 int mb200_fill_q4k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream);
 int mb200_fill_q6k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream);

@@ -36,6 +36,11 @@ SIGNATURES = {
     "mb200_set_pdl": (_i, [_i]),
     "mb200_matvec_q4k_dual_swiglu": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "mb200_matvec_q6k_scaled_add": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp]),
+    "mb200_router_scratch_bytes": (_sz, [_i]),
+    "mb200_router_topk": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "mb200_moe_gate_up": (_i, [_vp, _sz, _sz, _sz, _vp, _i, _vp, _vp, _i, _i, _vp]),
+    "mb200_moe_down": (_i, [_vp, _sz, _sz, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp]),
+    "mb200_moe_block": (_i, [_vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mb200_fill_q4k": (_i, [_vp, _sz, _u64, _vp]),
     "mb200_fill_q6k": (_i, [_vp, _sz, _u64, _vp]),
     "mb200_fill_normal_f32": (_i, [_vp, _sz, _u64, _f, _vp]),

@@ -100,7 +100,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 }
 // Returns false if the phase did not complete within the iteration budget
 // (each try_wait already blocks for a hardware time slice).
-constexpr uint32_t kWaitBudget = 1u << 20;
+constexpr uint32_t kWaitBudget = 1u << 16;  // x a few microseconds per try_wait: a fraction of a second
 __device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity)
 {
     uint32_t ok;

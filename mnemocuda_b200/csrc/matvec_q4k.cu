@@ -77,7 +77,8 @@ struct Q4 {
         }
         uint32_t sc2, m2;
         q4k_scale_pair(hdr.y, hdr.z, hdr.w, g, sc2, m2);
-        const float d = h2f_lo(hdr.x), dmin = h2f_hi(hdr.x);
+        const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+        const float d = dd.x, dmin = dd.y;
         const float il = static_cast<float>(i1l * 254 + i2l);
         const float ih = static_cast<float>(i1h * 254 + i2h);
         float p = static_cast<float>(sc2 & 0xFFu) * (xr.kl * il);
@@ -93,6 +94,48 @@ using stream::Params;
 }  // namespace
 
 void q4k_init() { stream::init_attrs<Q4>(); }
+int pdl_enabled() { return stream::pdl_mode(); }
+
+void moe_gate_up_q4k(const void *experts, size_t stride, size_t gate_off, size_t up_off, const int *ids, int n_slots,
+                     const float *x, float *act, int EFF, int H, cudaStream_t stream, const char *where)
+{
+    Params P{};
+    P.seg[0].y = act;
+    P.nseg = 1;
+    P.x = x;
+    P.n_cols = H;
+    P.mode = stream::kMoeGateUp;
+    P.ids = ids;
+    P.ebase = static_cast<const uint8_t *>(experts);
+    P.estride = stride;
+    P.off_a = gate_off;
+    P.off_b = up_off;
+    P.n_slots = n_slots;
+    P.erows = EFF;
+    stream::launch<Q4>(P, stream, where);
+}
+
+void moe_down_q4k(const void *experts, size_t stride, size_t down_off, const int *ids, const float *wts, int n_slots,
+                  const float *act, const float *residual, float *y, int H, int EFF, cudaStream_t stream,
+                  const char *where)
+{
+    Params P{};
+    P.seg[0].y = y;
+    P.nseg = 1;
+    P.x = act;
+    P.x_stride = EFF;
+    P.residual = residual;
+    P.n_cols = EFF;
+    P.mode = stream::kMoeDown;
+    P.ids = ids;
+    P.wts = wts;
+    P.ebase = static_cast<const uint8_t *>(experts);
+    P.estride = stride;
+    P.off_a = down_off;
+    P.n_slots = n_slots;
+    P.erows = H;
+    stream::launch<Q4>(P, stream, where);
+}
 
 }  // namespace mb200
 

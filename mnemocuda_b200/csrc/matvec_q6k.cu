@@ -6,10 +6,10 @@
 // span of a tile and lanes read their fields from shared memory as aligned
 // words + funnel shift.
 //
-// Lane mapping: 8 lanes per super-block. Lane (hh = half 0/1, jj = 0..3) owns
-// positions l = 8jj..8jj+7 of half hh: 8 bytes of ql[64hh..], 8 bytes of
-// ql[64hh+32..] and 8 bytes of qh[32hh..] give its 32 weights (4 sixteen-groups
-// x 8 columns): q = lo4 | hi2 << 4 rebuilt as bytes, dp4a against the two int8
+// Lane mapping: 4 lanes per super-block. Lane (hh = half 0/1, jj = 0/1) owns
+// positions l = 16jj..16jj+15 of half hh: 16 bytes of ql[64hh..], 16 bytes of
+// ql[64hh+32..] and 16 bytes of qh[32hh..] give its 64 weights (4 sixteen-groups
+// x 16 columns): q = lo4 | hi2 << 4 rebuilt as bytes, dp4a against the two int8
 // levels of x, weight = d * scale * (q - 32)
 // (reference src/kernels.cu:455-484, tools/validate_dequant.py:286-317).
 #include "stream_matvec.cuh"
@@ -17,7 +17,19 @@
 namespace mb200 {
 namespace {
 
-// 8 bytes starting at any byte address in shared memory -> two words
+// 16 bytes starting at any byte address in shared memory -> four words
+__device__ __forceinline__ void lds16(const uint8_t *p, uint32_t (&w)[4])
+{
+    const uint32_t a = smem_u32(p);
+    const uint32_t base = a & ~3u;
+    const uint32_t sh = (a & 3u) * 8u;
+    uint32_t t[5];
+#pragma unroll
+    for (int i = 0; i < 5; i++) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(t[i]) : "r"(base + 4 * i));
+#pragma unroll
+    for (int i = 0; i < 4; i++) w[i] = __funnelshift_r(t[i], t[i + 1], sh);
+}
+// 8 bytes -> two words
 __device__ __forceinline__ void lds8(const uint8_t *p, uint32_t &w0, uint32_t &w1)
 {
     const uint32_t a = smem_u32(p);
@@ -33,56 +45,57 @@ __device__ __forceinline__ void lds8(const uint8_t *p, uint32_t &w0, uint32_t &w
 
 struct Q6 {
     static constexpr int kBlockBytes = kQ6KBlock;
-    static constexpr int kLanesPerBlock = 8;
-    static constexpr int kG = 4;
-    static constexpr int kSumCols = 8;
+    static constexpr int kLanesPerBlock = 4;
+    static constexpr int kG = 8;
+    static constexpr int kSumCols = 16;
     static constexpr bool kGroup4Tail = false;  // per-element tail, reference src/kernels.cu:474
     static constexpr int kBaseAlign = 2;
-    static constexpr int kTileTargetBytes = 20480;
-    static constexpr int kMaxCols = 12288;  // one consumer warp per group of 4 block-columns
-    // x staging: 8 words per lane slot, slot = 8 * block-column + 4 * half + jj; word = 2g + i
-    static constexpr int kXWords = 8;
-    static constexpr int kSlotsPerBlock = 8;
-    __device__ static __forceinline__ int xslot(int c0) { return ((c0 >> 8) << 3) + (((c0 >> 7) & 1) << 2) + ((c0 >> 3) & 3); }
-    __device__ static __forceinline__ int xword(int c0) { return (((c0 >> 5) & 3) << 1) + ((c0 >> 2) & 1); }
+    static constexpr int kTileTargetBytes = 30720;
+    static constexpr int kMaxCols = 16384;
+    // x staging: 16 words per lane slot; slot = 4 * block-column + 2 * half + jj; word = 4g + i
+    static constexpr int kXWords = 16;
+    static constexpr int kSlotsPerBlock = 4;
+    __device__ static __forceinline__ int xslot(int c0) { return ((c0 >> 8) << 2) + (((c0 >> 7) & 1) << 1) + ((c0 >> 4) & 1); }
+    __device__ static __forceinline__ int xword(int c0) { return (((c0 >> 5) & 3) << 2) + ((c0 >> 2) & 3); }
 
     struct XRegs {
-        uint32_t q1[8], q2[8];  // [2g + i]: columns 32g + 8jj + 4i .. +3 of the lane's half
-        float k[4];             // s1 / 254 per sixteen-group g
-        float sx32[4];          // 32 * sum of x over the lane's 8 columns of group g
+        uint32_t q1[16], q2[16];  // [4g + i]: columns 32g + 16jj + 4i .. +3 of the lane's half
+        float k[4];               // s1 / 254 per sixteen-group g
+        float sx32[4];            // 32 * sum of x over the lane's 16 columns of group g
     };
 
     __device__ static __forceinline__ void load_xregs(XRegs &xr, const uint8_t *smem, const stream::Layout &L,
                                                       int bpr, int col, int sub, bool valid)
     {
-        const int hh = sub >> 2, jj = sub & 3;
-        const int c0 = col * 256 + hh * 128 + jj * 8;  // first column of the lane in group 0
+        const int hh = sub >> 1, jj = sub & 1;
+        const int c0 = col * 256 + hh * 128 + jj * 16;  // first column of the lane in group 0
         const int pitch = kSlotsPerBlock * bpr + 1;
-        const uint32_t *q1 = reinterpret_cast<const uint32_t *>(smem + L.xq1) + col * 8 + sub;
-        const uint32_t *q2 = reinterpret_cast<const uint32_t *>(smem + L.xq2) + col * 8 + sub;
+        const uint32_t *q1 = reinterpret_cast<const uint32_t *>(smem + L.xq1) + col * 4 + sub;
+        const uint32_t *q2 = reinterpret_cast<const uint32_t *>(smem + L.xq2) + col * 4 + sub;
         const float *s1 = reinterpret_cast<const float *>(smem + L.xs1);
         const float *xs = reinterpret_cast<const float *>(smem + L.xsum);
 #pragma unroll
+        for (int w = 0; w < 16; w++) {
+            xr.q1[w] = valid ? q1[w * pitch] : 0u;
+            xr.q2[w] = valid ? q2[w * pitch] : 0u;
+        }
+#pragma unroll
         for (int g = 0; g < 4; g++) {
             const int c = c0 + 32 * g;
-#pragma unroll
-            for (int i = 0; i < 2; i++) {
-                xr.q1[2 * g + i] = valid ? q1[(2 * g + i) * pitch] : 0u;
-                xr.q2[2 * g + i] = valid ? q2[(2 * g + i) * pitch] : 0u;
-            }
             xr.k[g] = valid ? s1[c >> 5] * (1.0f / 254.0f) : 0.0f;
-            xr.sx32[g] = valid ? 32.0f * xs[c >> 3] : 0.0f;
+            xr.sx32[g] = valid ? 32.0f * xs[c >> 4] : 0.0f;
         }
     }
 
-    // One lane's 32 weights of one super-block of one row.
+    // One lane's 64 weights of one super-block of one row: positions l = 16jj..16jj+15 of half hh,
+    // in the four sixteen-groups g (g = 0,1: low nibbles of ql[64hh..], ql[64hh+32..]; g = 2,3: their high nibbles).
     __device__ static __forceinline__ float block_dot(const uint8_t *blk, int sub, const XRegs &xr)
     {
-        const int hh = sub >> 2, jj = sub & 3;
-        uint32_t A[2], B[2], H[2], S[2];
-        lds8(blk + 64 * hh + 8 * jj, A[0], A[1]);
-        lds8(blk + 64 * hh + 32 + 8 * jj, B[0], B[1]);
-        lds8(blk + 128 + 32 * hh + 8 * jj, H[0], H[1]);
+        const int hh = sub >> 1, jj = sub & 1;
+        uint32_t A[4], B[4], H[4], S[2];
+        lds16(blk + 64 * hh + 16 * jj, A);
+        lds16(blk + 64 * hh + 32 + 16 * jj, B);
+        lds16(blk + 128 + 32 * hh + 16 * jj, H);
         lds8(blk + 192 + 8 * hh, S[0], S[1]);
         unsigned short d_bits;
         asm volatile("ld.shared.u16 %0, [%1+208];" : "=h"(d_bits) : "r"(smem_u32(blk)));
@@ -90,22 +103,24 @@ struct Q6 {
 
         int i1[4] = {0, 0, 0, 0}, i2[4] = {0, 0, 0, 0};
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const uint32_t q0 = (A[i] & 0x0F0F0F0Fu) | ((H[i] << 4) & 0x30303030u);
-            const uint32_t q1 = (B[i] & 0x0F0F0F0Fu) | ((H[i] << 2) & 0x30303030u);
-            const uint32_t q2 = ((A[i] >> 4) & 0x0F0F0F0Fu) | (H[i] & 0x30303030u);
-            const uint32_t q3 = ((B[i] >> 4) & 0x0F0F0F0Fu) | ((H[i] >> 2) & 0x30303030u);
+        for (int i = 0; i < 4; i++) {
+            const uint32_t h0 = (H[i] << 4) & 0x30303030u, h1 = (H[i] << 2) & 0x30303030u;
+            const uint32_t h2 = H[i] & 0x30303030u, h3 = (H[i] >> 2) & 0x30303030u;
+            const uint32_t q0 = (A[i] & 0x0F0F0F0Fu) | h0;
+            const uint32_t q1 = (B[i] & 0x0F0F0F0Fu) | h1;
+            const uint32_t q2 = ((A[i] >> 4) & 0x0F0F0F0Fu) | h2;
+            const uint32_t q3 = ((B[i] >> 4) & 0x0F0F0F0Fu) | h3;
             i1[0] = dp4a_us(q0, xr.q1[0 + i], i1[0]);
             i2[0] = dp4a_us(q0, xr.q2[0 + i], i2[0]);
-            i1[1] = dp4a_us(q1, xr.q1[2 + i], i1[1]);
-            i2[1] = dp4a_us(q1, xr.q2[2 + i], i2[1]);
-            i1[2] = dp4a_us(q2, xr.q1[4 + i], i1[2]);
-            i2[2] = dp4a_us(q2, xr.q2[4 + i], i2[2]);
-            i1[3] = dp4a_us(q3, xr.q1[6 + i], i1[3]);
-            i2[3] = dp4a_us(q3, xr.q2[6 + i], i2[3]);
+            i1[1] = dp4a_us(q1, xr.q1[4 + i], i1[1]);
+            i2[1] = dp4a_us(q1, xr.q2[4 + i], i2[1]);
+            i1[2] = dp4a_us(q2, xr.q1[8 + i], i1[2]);
+            i2[2] = dp4a_us(q2, xr.q2[8 + i], i2[2]);
+            i1[3] = dp4a_us(q3, xr.q1[12 + i], i1[3]);
+            i2[3] = dp4a_us(q3, xr.q2[12 + i], i2[3]);
         }
-        // scales[8hh + 2g + (jj >> 1)], g = 0..3: bytes (jj>>1) + {0,2,4,6} of the 8 loaded
-        const uint32_t sh = (jj >> 1) * 8;
+        // scales[8hh + 2g + jj], g = 0..3: bytes jj + {0,2,4,6} of the 8 loaded
+        const uint32_t sh = jj * 8;
         const int sc0 = static_cast<int8_t>((S[0] >> sh) & 0xFF);
         const int sc1 = static_cast<int8_t>((S[0] >> (sh + 16)) & 0xFF);
         const int sc2 = static_cast<int8_t>((S[1] >> sh) & 0xFF);
@@ -124,6 +139,28 @@ using stream::Params;
 }  // namespace
 
 void q6k_init() { stream::init_attrs<Q6>(); }
+
+void moe_down_q6k(const void *experts, size_t stride, size_t down_off, const int *ids, const float *wts, int n_slots,
+                  const float *act, const float *residual, float *y, int H, int EFF, cudaStream_t stream,
+                  const char *where)
+{
+    Params P{};
+    P.seg[0].y = y;
+    P.nseg = 1;
+    P.x = act;
+    P.x_stride = EFF;
+    P.residual = residual;
+    P.n_cols = EFF;
+    P.mode = stream::kMoeDown;
+    P.ids = ids;
+    P.wts = wts;
+    P.ebase = static_cast<const uint8_t *>(experts);
+    P.estride = stride;
+    P.off_a = down_off;
+    P.n_slots = n_slots;
+    P.erows = H;
+    stream::launch<Q6>(P, stream, where);
+}
 
 }  // namespace mb200
 

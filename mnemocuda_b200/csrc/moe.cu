@@ -1,0 +1,186 @@
+// Decode-time MoE block with the routed expert ids kept on the device.
+//
+// The reference selects experts on the GPU, copies the k ids and weights to
+// the host, synchronises, and then issues 3-4 launches per expert
+// (src/forward.c:818-882, 1122-1142). With every expert resident in HBM the
+// ids never need to leave the device: three launches do the whole block --
+//   1. router logits (fp32 matvec) + top-k + softmax in one kernel,
+//   2. gate/up + SwiGLU of all routed experts (stream kernel, mode kMoeGateUp),
+//   3. down projections of all routed experts, weighted sum and residual add
+//      (stream kernel, mode kMoeDown),
+// and the sequence can be captured in a CUDA graph.
+#include <cstdio>
+
+#include "common.cuh"
+#include "topk.cuh"
+
+namespace mb200 {
+
+void moe_gate_up_q4k(const void *experts, size_t stride, size_t gate_off, size_t up_off, const int *ids, int n_slots,
+                     const float *x, float *act, int EFF, int H, cudaStream_t stream, const char *where);
+void moe_down_q4k(const void *experts, size_t stride, size_t down_off, const int *ids, const float *wts, int n_slots,
+                  const float *act, const float *residual, float *y, int H, int EFF, cudaStream_t stream,
+                  const char *where);
+void moe_down_q6k(const void *experts, size_t stride, size_t down_off, const int *ids, const float *wts, int n_slots,
+                  const float *act, const float *residual, float *y, int H, int EFF, cudaStream_t stream,
+                  const char *where);
+int pdl_enabled();
+
+namespace {
+
+constexpr int kRouterThreads = 128;
+
+// One CTA per expert row computes its logit; the CTA that finishes last (device-wide
+// ticket in scratch[0]) runs the reference's top-k + softmax over all logits.
+// scratch: int ticket (zero before the first use; the kernel leaves it zero) followed by
+// n_experts floats of logits starting at scratch + 8 words.
+template <bool PDL>
+__global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const float *__restrict__ w,
+                                                                      const float *__restrict__ x, int *scratch,
+                                                                      int *__restrict__ indices,
+                                                                      float *__restrict__ weights, int n_experts,
+                                                                      int n_cols, int k, int vec_ok)
+{
+    __shared__ float red[kRouterThreads / 32];
+    __shared__ int is_last;
+    __shared__ float s_vals[32 * 16];
+    __shared__ int s_ids[32 * 16];
+    float *logits = reinterpret_cast<float *>(scratch + 8);
+    const int row = blockIdx.x;
+    const float *wr = w + (size_t)row * n_cols;
+    float acc = 0.0f;
+    if (vec_ok) {
+        // the router weights do not depend on the upstream kernel: fetch them before waiting for it
+        const float4 *w4 = reinterpret_cast<const float4 *>(wr);
+        const float4 *x4 = reinterpret_cast<const float4 *>(x);
+        const int n4 = n_cols >> 2;
+        bool waited = false;
+        for (int i0 = threadIdx.x; i0 < n4; i0 += kRouterThreads * 8) {
+            float4 a[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int i = i0 + u * kRouterThreads;
+                a[u] = i < n4 ? __ldcs(w4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            if (PDL && !waited) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                waited = true;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int i = i0 + u * kRouterThreads;
+                if (i < n4) {
+                    const float4 b = x4[i];
+                    acc = fmaf(a[u].x, b.x, acc);
+                    acc = fmaf(a[u].y, b.y, acc);
+                    acc = fmaf(a[u].z, b.z, acc);
+                    acc = fmaf(a[u].w, b.w, acc);
+                }
+            }
+        }
+        if (PDL && !waited) asm volatile("griddepcontrol.wait;" ::: "memory");
+    } else {
+        if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
+        for (int c = threadIdx.x; c < n_cols; c += kRouterThreads) acc = fmaf(wr[c], x[c], acc);
+    }
+    if (PDL) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        logits[row] = (red[0] + red[1]) + (red[2] + red[3]);
+        __threadfence();
+        const int ticket = atomicAdd(scratch, 1);
+        is_last = (ticket == n_experts - 1);
+    }
+    __syncthreads();
+    if (!is_last || threadIdx.x >= 32) return;
+    __threadfence();
+    topk_softmax_warp(const_cast<const float *>(static_cast<volatile float *>(logits)), indices, weights, n_experts, k,
+                      s_vals, s_ids);
+    if (threadIdx.x == 0) scratch[0] = 0;  // ready for the next call
+}
+
+}  // namespace
+
+int launch_router(const float *router_w, const float *x, void *scratch, int *ids, float *wts, int n_experts, int H,
+                  int k, cudaStream_t stream)
+{
+    const int vec_ok = (H % 4 == 0) && ((reinterpret_cast<uintptr_t>(router_w) & 15) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_experts);
+    cfg.blockDim = dim3(kRouterThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    const int pdl = pdl_enabled();
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e;
+    if (pdl)
+        e = cudaLaunchKernelEx(&cfg, router_topk_kernel<true>, router_w, x, static_cast<int *>(scratch), ids, wts,
+                               n_experts, H, k, vec_ok);
+    else
+        e = cudaLaunchKernelEx(&cfg, router_topk_kernel<false>, router_w, x, static_cast<int *>(scratch), ids, wts,
+                               n_experts, H, k, vec_ok);
+    return e == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
+}
+
+}  // namespace mb200
+
+using namespace mb200;
+
+extern "C" {
+
+size_t mb200_router_scratch_bytes(int n_experts) { return sizeof(int) * 8 + sizeof(float) * (size_t)(n_experts > 0 ? n_experts : 0); }
+
+int mb200_router_topk(const float *router_w, const float *x, void *scratch, int *indices, float *weights,
+                      int n_experts, int n_cols, int k, cudaStream_t stream)
+{
+    if (!router_w || !x || !scratch || !indices || !weights || n_experts < 1 || n_cols < 1 || k < 1 || k > 16)
+        return MB200_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(scratch) & 15) return MB200_ERR_ARG;
+    return launch_router(router_w, x, scratch, indices, weights, n_experts, n_cols, k, stream);
+}
+
+int mb200_moe_gate_up(const void *experts, size_t expert_stride, size_t gate_off, size_t up_off, const int *ids,
+                      int n_slots, const float *x, float *act, int EFF, int H, cudaStream_t stream)
+{
+    if (!experts || !ids || !x || !act || n_slots < 1 || n_slots > 16 || EFF < 1 || H < 1) return MB200_ERR_ARG;
+    mb200_clear_status();
+    moe_gate_up_q4k(experts, expert_stride, gate_off, up_off, ids, n_slots, x, act, EFF, H, stream,
+                    "mb200_moe_gate_up");
+    return mb200_last_status();
+}
+
+int mb200_moe_down(const void *experts, size_t expert_stride, size_t down_off, int down_type, const int *ids,
+                   const float *wts, int n_slots, const float *act, const float *residual, float *y, int H, int EFF,
+                   cudaStream_t stream)
+{
+    if (!experts || !ids || !wts || !act || !y || n_slots < 1 || n_slots > 16 || EFF < 1 || H < 1) return MB200_ERR_ARG;
+    if (down_type != 12 && down_type != 14) return MB200_ERR_UNSUPPORTED;
+    mb200_clear_status();
+    if (down_type == 14)
+        moe_down_q6k(experts, expert_stride, down_off, ids, wts, n_slots, act, residual, y, H, EFF, stream,
+                     "mb200_moe_down");
+    else
+        moe_down_q4k(experts, expert_stride, down_off, ids, wts, n_slots, act, residual, y, H, EFF, stream,
+                     "mb200_moe_down");
+    return mb200_last_status();
+}
+
+int mb200_moe_block(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz,
+                    int down_type, int n_experts, int k, int H, int EFF, const float *x, const float *residual,
+                    float *out, int *ids, float *wts, float *act, void *scratch, cudaStream_t stream)
+{
+    int rc = mb200_router_topk(router_w, x, scratch, ids, wts, n_experts, H, k, stream);
+    if (rc != MB200_OK) return rc;
+    rc = mb200_moe_gate_up(experts, expert_stride, 0, gate_sz, ids, k, x, act, EFF, H, stream);
+    if (rc != MB200_OK) return rc;
+    return mb200_moe_down(experts, expert_stride, gate_sz + up_sz, down_type, ids, wts, k, act, residual, out, H, EFF,
+                          stream);
+}
+
+}  // extern "C"

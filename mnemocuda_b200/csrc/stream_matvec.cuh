@@ -16,27 +16,44 @@
 // There is no block-wide barrier inside the loop, and every wait is bounded.
 //
 // Work split inside a tile: a warp pass covers G = 32 / lanes-per-block
-// super-blocks. The block-columns of a row are split into column groups of G;
-// each consumer warp is bound to one column group for the whole kernel, so its
-// share of the activation vector is loaded into registers once. A trailing
-// group with v < G columns (v dividing G) covers G / v rows per pass instead of
-// idling lanes. A unit is RU passes issued back to back (independent rows:
-// instruction-level parallelism), reduced together with one packed butterfly.
+// super-blocks. The block-columns of a row are split into column groups of v
+// columns, v the largest power of two (<= G) dividing the blocks per row, and a
+// pass covers G / v consecutive rows of its group, so no lane idles for any
+// row length (rows whose block count has too small a power-of-two factor fall
+// back to groups of G columns with a ragged, partly idle last group). Each
+// consumer warp is bound to one column group for the whole kernel (host-made
+// table in the launch parameters), so its share of the activation vector is
+// loaded into registers once. A unit is RU passes issued back to back
+// (independent rows: instruction-level parallelism), reduced together with one
+// packed butterfly.
 #pragma once
 
 #include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 
 namespace mb200 {
 namespace stream {
 
-constexpr int kConsumers = 12;
+#ifndef MB200_CONSUMERS
+#define MB200_CONSUMERS 12
+#endif
+constexpr int kConsumers = MB200_CONSUMERS;
 constexpr int kThreads = (kConsumers + 2) * 32;
 constexpr int kQuantThreads = kConsumers * 32;  // the consumer warps stage x; issuer/epilogue warps do not
 constexpr int kMaxStages = 6;
 
-enum : int { kStore = 0, kAddResidual = 1, kScaledAdd = 2, kSwiGLU = 3 };
+enum : int {
+    kStore = 0,
+    kAddResidual = 1,
+    kScaledAdd = 2,
+    kSwiGLU = 3,
+    // routed experts, ids and weights read on the device (reference sequence src/forward.c:1122-1142 per expert):
+    kMoeGateUp = 4,  // act[e][r] = silu(gate_e[r].x) * (up_e[r].x) for the n_slots routed experts, one launch
+    kMoeDown = 5     // y[r] = (residual[r] | y[r]) + sum_e w_e * (down_e[r] . act[e]), experts added in slot order
+};
+constexpr int kMaxSlots = 16;  // top-k limit of the router (cuda_topk_softmax: k <= 16)
 
 struct Seg {
     const uint8_t *w;
@@ -56,24 +73,37 @@ struct Params {
     int n_cols, bpr, mode, stages;
     int pdl;        // launched with programmatic stream serialization: wait for the upstream grid before touching x / y
     int *err;
+    // routed-expert modes
+    const int *ids;          // [n_slots] expert index per slot (device); < 0 = empty slot
+    const float *wts;        // [n_slots] routing weight per slot (device)
+    const uint8_t *ebase;    // expert e's blob starts at ebase + e * estride
+    size_t estride, off_a, off_b;  // byte offsets inside a blob: gate/up (kMoeGateUp) or down (off_a, kMoeDown)
+    int n_slots, erows;      // experts per token; rows per expert tensor
+    int x_stride;            // kMoeDown: floats between the activation vectors of consecutive slots
+    int n_groups;   // column groups (= partial sums per row)
+    // per consumer warp: group | first column << 5 | columns v << 12 | rows per pass << 16 | index in group << 20 | warps of group << 24
+    uint32_t warp_cfg[kConsumers];
 };
 
 struct Layout {
-    int bars, xq1, xq2, xs1, xsum, part, stages, stage_bytes, total;
+    int bars, xq1, xq2, xs1, xsum, x_stride, part, stages, stage_bytes, total;
 };
 
+// bars: 2 * kMaxStages mbarriers, abort flag at +120, routed ids at +128, routing weights at +192
 template <class F>
-__host__ __device__ inline Layout layout(int bpr, int tile_rows_in_stage, int n_stages)
+__host__ __device__ inline Layout layout(int bpr, int tile_rows_in_stage, int n_stages, int ng, int n_x)
 {
     Layout s;
     const int kpad = bpr * 256;
-    const int ng = (bpr + F::kG - 1) / F::kG;
     int o = 0;
-    s.bars = o;  o += 128;
+    s.bars = o;  o += 256;
+    const int x0 = o;
     s.xq1 = o;   o += F::kXWords * (F::kSlotsPerBlock * bpr + 1) * 4;  // [word][slot], +1 pad: conflict-free both ways
     s.xq2 = o;   o += F::kXWords * (F::kSlotsPerBlock * bpr + 1) * 4;
     s.xs1 = o;   o += (kpad / 32) * 4;
     s.xsum = o;  o += (kpad / F::kSumCols) * 4;
+    s.x_stride = o - x0;  // one staged activation vector; kMoeDown stages one per slot
+    o += (n_x - 1) * s.x_stride;
     s.part = o;  o += n_stages * tile_rows_in_stage * ng * 4;
     o = (o + 127) & ~127;
     s.stages = o;
@@ -97,18 +127,34 @@ struct Tile {
 };
 
 // Walks the tiles of this CTA's row range [cur, end). Every role runs the same walk.
+// t.seg is the segment (plain modes) or the expert slot (routed modes).
 struct TileWalk {
-    int cur, end;
+    int cur, end, e;
     __device__ __forceinline__ void init(const Params &P)
     {
         cur = static_cast<int>((long long)P.vrows * blockIdx.x / gridDim.x);
         end = static_cast<int>((long long)P.vrows * (blockIdx.x + 1) / gridDim.x);
+        e = 0;
     }
     __device__ __forceinline__ bool next(const Params &P, Tile &t)
     {
         if (cur >= end) return false;
+        if (P.mode == kMoeDown) {  // the same rows for slot 0, 1, ... then the next rows
+            t.seg = e;
+            t.row0 = cur;
+            t.rows = min(P.tile_rows, end - cur);
+            if (++e == P.n_slots) {
+                e = 0;
+                cur += t.rows;
+            }
+            return true;
+        }
         int seg = 0, s0 = 0, s1 = P.seg[0].rows;
-        if (P.mode != kSwiGLU) {
+        if (P.mode == kMoeGateUp) {
+            seg = cur / P.erows;
+            s0 = seg * P.erows;
+            s1 = s0 + P.erows;
+        } else if (P.mode != kSwiGLU) {
             if (P.nseg > 1 && cur >= P.seg[1].start) {
                 seg = 1;
                 s0 = P.seg[1].start;
@@ -129,19 +175,37 @@ struct TileWalk {
     }
 };
 
+__device__ __forceinline__ bool pair_mode(int mode) { return mode == kSwiGLU || mode == kMoeGateUp; }
+
+// First byte of the tile's rows (for pair modes: of its gate rows; `second` selects the up rows).
+__device__ __forceinline__ const uint8_t *tile_src(const Params &P, const Tile &t, size_t row_bytes, const int *sid,
+                                                   bool second = false)
+{
+    const uint8_t *w;
+    if (P.mode == kMoeGateUp || P.mode == kMoeDown) {
+        const int id = sid[t.seg];
+        w = P.ebase + (size_t)(id < 0 ? 0 : id) * P.estride + (second ? P.off_b : P.off_a);
+    } else if (P.mode == kSwiGLU) {
+        w = second ? P.seg[1].w : P.seg[0].w;
+    } else {
+        w = seg_w(P, t.seg);
+    }
+    return w + (size_t)t.row0 * row_bytes;
+}
+
 template <class F>
-__device__ __forceinline__ void issue_tile(const Params &P, const Tile &t, uint8_t *stage, uint64_t *bar)
+__device__ __forceinline__ void issue_tile(const Params &P, const Tile &t, uint8_t *stage, uint64_t *bar, const int *sid)
 {
     const size_t row_bytes = (size_t)P.bpr * F::kBlockBytes;
-    if (P.mode == kSwiGLU) {  // Q4_K only: rows are multiples of 16 bytes, spans are exact
+    if (pair_mode(P.mode)) {  // Q4_K only: rows are multiples of 16 bytes, spans are exact
         const uint32_t half = t.rows * (uint32_t)row_bytes;
         mbar_expect_tx(bar, 2 * half);
-        bulk_g2s(stage, P.seg[0].w + (size_t)t.row0 * row_bytes, half, bar);
-        bulk_g2s(stage + half, P.seg[1].w + (size_t)t.row0 * row_bytes, half, bar);
+        bulk_g2s(stage, tile_src(P, t, row_bytes, sid, false), half, bar);
+        bulk_g2s(stage + half, tile_src(P, t, row_bytes, sid, true), half, bar);
     } else {
         // The 16-byte-aligned span enclosing the rows. The few bytes read before/after them share a
         // 16-byte granule with a valid byte, hence lie inside a mapped page.
-        const uintptr_t begin = reinterpret_cast<uintptr_t>(seg_w(P, t.seg)) + (size_t)t.row0 * row_bytes;
+        const uintptr_t begin = reinterpret_cast<uintptr_t>(tile_src(P, t, row_bytes, sid));
         const uintptr_t stop = begin + (size_t)t.rows * row_bytes;
         const uintptr_t a0 = begin & ~static_cast<uintptr_t>(15);
         const uint32_t bytes = static_cast<uint32_t>(((stop + 15) & ~static_cast<uintptr_t>(15)) - a0);
@@ -217,11 +281,10 @@ static __device__ long long g_trace[kSMs * 2][16];  // one copy per translation 
 // stores are both free of bank conflicts. All loads of a thread are issued
 // before the first use: one memory round trip for K <= 3 * 4 * kQuantThreads.
 // Called by the consumer warps only (threadIdx.x < kQuantThreads).
-template <class F>
+template <class F, int UN>
 __device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_cols, int bpr,
                                            uint32_t *q1, uint32_t *q2, float *s1, float *xsum)
 {
-    constexpr int UN = 3;
     const int kpad = bpr * 256;
     const int pitch = F::kSlotsPerBlock * bpr + 1;
     const int lane = threadIdx.x & 31;
@@ -258,11 +321,74 @@ __device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_co
             uint32_t p1 = 0, p2 = 0;
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const float a = fminf(fmaxf(rintf(v[u][i] * inv), -127.0f), 127.0f);
+                // |x| <= amax, so |a| <= 127; |r| <= sc/2 (+ rounding), so |b| <= 127: clamp only guards NaN/Inf input
+                const float a = rintf(v[u][i] * inv);
                 const float r = fmaf(-a, sc, v[u][i]);
                 const float b = fminf(fmaxf(rintf(r * inv * 254.0f), -127.0f), 127.0f);
-                p1 |= (static_cast<uint32_t>(static_cast<int>(a)) & 0xFFu) << (8 * i);
-                p2 |= (static_cast<uint32_t>(static_cast<int>(b)) & 0xFFu) << (8 * i);
+                p1 |= (static_cast<uint32_t>(__float2int_rn(a)) & 0xFFu) << (8 * i);
+                p2 |= (static_cast<uint32_t>(__float2int_rn(b)) & 0xFFu) << (8 * i);
+            }
+            const int idx = F::xword(c0) * pitch + F::xslot(c0);
+            q1[idx] = p1;
+            q2[idx] = p2;
+            if ((lane & 7) == 0) s1[c0 >> 5] = sc;
+            if (F::kSumCols == 16) {
+                if ((lane & 3) == 0) xsum[c0 >> 4] = sum;
+            } else {
+                if ((lane & 1) == 0) xsum[c0 >> 3] = sum;
+            }
+        }
+    }
+}
+
+// Same split done by a single warp for one whole vector (routed down-projection:
+// one activation vector per expert slot, each handled by one warp).
+template <class F>
+__device__ __forceinline__ void quantize_x_warp(const float *__restrict__ x, int n_cols, int bpr,
+                                                uint32_t *q1, uint32_t *q2, float *s1, float *xsum)
+{
+    constexpr int UN = 4;
+    const int kpad = bpr * 256;
+    const int pitch = F::kSlotsPerBlock * bpr + 1;
+    const int lane = threadIdx.x & 31;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    for (int base = lane * 4; base < kpad; base += 128 * UN) {
+        float v[UN][4];
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const int c0 = base + u * 128;
+            if (vec_ok && c0 + 3 < n_cols) {
+                const float4 t = __ldg(reinterpret_cast<const float4 *>(x + c0));
+                v[u][0] = t.x; v[u][1] = t.y; v[u][2] = t.z; v[u][3] = t.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const bool in = F::kGroup4Tail ? (c0 + 3) < n_cols : (c0 + i) < n_cols;
+                    v[u][i] = in ? __ldg(x + c0 + i) : 0.0f;
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const int c0 = base + u * 128;
+            if (c0 - lane * 4 >= kpad) break;  // warp-uniform
+            float amax = fmaxf(fmaxf(fabsf(v[u][0]), fabsf(v[u][1])), fmaxf(fabsf(v[u][2]), fabsf(v[u][3])));
+            float sum = (v[u][0] + v[u][1]) + (v[u][2] + v[u][3]);
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            if (F::kSumCols == 16) sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            const float sc = amax * (1.0f / 127.0f);
+            const float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+            uint32_t p1 = 0, p2 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float a = rintf(v[u][i] * inv);
+                const float r = fmaf(-a, sc, v[u][i]);
+                const float b = fminf(fmaxf(rintf(r * inv * 254.0f), -127.0f), 127.0f);
+                p1 |= (static_cast<uint32_t>(__float2int_rn(a)) & 0xFFu) << (8 * i);
+                p2 |= (static_cast<uint32_t>(__float2int_rn(b)) & 0xFFu) << (8 * i);
             }
             const int idx = F::xword(c0) * pitch + F::xslot(c0);
             q1[idx] = p1;
@@ -281,25 +407,36 @@ __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.w
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <class F, int RU>
-__global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
+__global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_constant__ Params P)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     const int S = P.stages;
-    const int stage_rows = (P.mode == kSwiGLU) ? 2 * P.tile_rows : P.tile_rows;
-    const Layout L = layout<F>(P.bpr, stage_rows, S);
+    const bool pairs = pair_mode(P.mode);
+    const bool routed = (P.mode == kMoeGateUp || P.mode == kMoeDown);
+    const int stage_rows = pairs ? 2 * P.tile_rows : P.tile_rows;
+    const int NG = P.n_groups;
+    const int n_x = (P.mode == kMoeDown) ? P.n_slots : 1;
+    const Layout L = layout<F>(P.bpr, stage_rows, S, NG, n_x);
+    int *sid = reinterpret_cast<int *>(smem + L.bars + 128);      // routed expert per slot
+    float *swt = reinterpret_cast<float *>(smem + L.bars + 192);  // routing weight per slot
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.bars);
     uint64_t *empty = full + kMaxStages;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.bars + 120);
     float *part = reinterpret_cast<float *>(smem + L.part);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (warp == 0) MB200_STAMP(0);
-    const int NG = (P.bpr + F::kG - 1) / F::kG;
     const uint32_t row_bytes = P.bpr * F::kBlockBytes;
     const int part_pitch = stage_rows * NG;
 
     TileWalk walk;
     walk.init(P);
 
+#ifdef MB200_V_NOWAIT
+    if (warp >= kConsumers) {
+        __syncthreads();
+        return;
+    }
+#endif
     if (warp == kConsumers) {
         // ---------------- issuer ----------------
         // The weights never depend on the upstream kernel, so the first stages are
@@ -312,10 +449,19 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
                 mbar_init(&empty[s], kConsumers);
             }
             mbar_fence_init();
+            if (routed) {
+                // which experts to stream is decided by the upstream kernel (the router): wait for it first
+                if (P.pdl) grid_dep_wait();
+                for (int e = 0; e < P.n_slots; e++) {
+                    const int id = P.ids[e];
+                    sid[e] = id;
+                    swt[e] = (id < 0 || P.wts == nullptr) ? 0.0f : P.wts[e];  // gate/up has no routing weights
+                }
+            }
             Tile t;
             for (int s = 0; s < S; s++) {
                 mbar_arrive(&full[s]);  // first phase: nothing to drain yet
-                if (walk.next(P, t)) issue_tile<F>(P, t, smem + L.stages + s * L.stage_bytes, &full[s]);
+                if (walk.next(P, t)) issue_tile<F>(P, t, smem + L.stages + s * L.stage_bytes, &full[s], sid);
             }
         }
         __syncthreads();
@@ -328,7 +474,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
                     *abort_flag = 1;
                     break;
                 }
-                issue_tile<F>(P, t, smem + L.stages + s * L.stage_bytes, &full[s]);
+                issue_tile<F>(P, t, smem + L.stages + s * L.stage_bytes, &full[s], sid);
                 if (++s == S) {
                     s = 0;
                     ph ^= 1;
@@ -342,6 +488,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
         __syncthreads();
         if (P.pdl) grid_dep_wait();  // y / residual may still be in use by the upstream kernel
         Tile t, ahead;
+        float eacc0 = 0.0f, eacc1 = 0.0f;  // kMoeDown: per-row running sums (tiles hold at most 64 rows)
         TileWalk look = walk;
         for (int i = 0; i < S; i++) look.next(P, ahead);  // `look` runs S tiles ahead: does stage s get reused?
         int s = 0, ph = 0;
@@ -350,7 +497,8 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
             if (!mbar_wait(&empty[s], ph)) *abort_flag = 1;
             if (*abort_flag) break;
             const float *pt = part + s * part_pitch;
-            for (int r = lane; r < t.rows; r += 32) {
+            int it = 0;
+            for (int r = lane; r < t.rows; r += 32, it++) {
                 float v = 0.0f;
                 for (int c = 0; c < NG; c++) v += pt[r * NG + c];
                 const int row = t.row0 + r;
@@ -360,10 +508,21 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
                     seg_y(P, t.seg)[row] = v + P.residual[row];
                 } else if (P.mode == kScaledAdd) {
                     seg_y(P, t.seg)[row] += P.scale * v;
+                } else if (P.mode == kMoeDown) {
+                    // slots arrive in order 0..n_slots-1 for the same rows: keep the running sum in registers
+                    float a = (t.seg == 0) ? 0.0f : (it == 0 ? eacc0 : eacc1);
+                    a = fmaf(swt[t.seg], v, a);
+                    if (it == 0) eacc0 = a; else eacc1 = a;
+                    if (t.seg == P.n_slots - 1)
+                        P.seg[0].y[row] = (P.residual ? P.residual[row] : P.seg[0].y[row]) + a;
                 } else {
                     float u = 0.0f;
                     for (int c = 0; c < NG; c++) u += pt[(r + t.rows) * NG + c];
-                    P.seg[0].y[row] = v / (1.0f + expf(-v)) * u;
+                    const float act = v / (1.0f + expf(-v)) * u;
+                    if (P.mode == kSwiGLU)
+                        P.seg[0].y[row] = act;
+                    else
+                        P.seg[0].y[t.seg * P.erows + row] = sid[t.seg] < 0 ? 0.0f : act;
                 }
             }
             __syncwarp();
@@ -380,41 +539,30 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
 
     // ---------------- consumer warps ----------------
     if (P.pdl) grid_dep_wait();  // x is produced by the upstream kernel
-    quantize_x<F>(P.x, P.n_cols, P.bpr, reinterpret_cast<uint32_t *>(smem + L.xq1),
-                  reinterpret_cast<uint32_t *>(smem + L.xq2), reinterpret_cast<float *>(smem + L.xs1),
-                  reinterpret_cast<float *>(smem + L.xsum));
+    if (n_x == 1) {
+        quantize_x<F, 3>(P.x, P.n_cols, P.bpr, reinterpret_cast<uint32_t *>(smem + L.xq1),
+                         reinterpret_cast<uint32_t *>(smem + L.xq2), reinterpret_cast<float *>(smem + L.xs1),
+                         reinterpret_cast<float *>(smem + L.xsum));
+    } else {
+        // one activation vector per slot; warps take slots round-robin so the loads of all slots are in flight together
+        for (int e = warp; e < n_x; e += kConsumers) {
+            uint8_t *xb = smem + e * L.x_stride;
+            quantize_x_warp<F>(P.x + (size_t)e * P.x_stride, P.n_cols, P.bpr, reinterpret_cast<uint32_t *>(xb + L.xq1),
+                               reinterpret_cast<uint32_t *>(xb + L.xq2), reinterpret_cast<float *>(xb + L.xs1),
+                               reinterpret_cast<float *>(xb + L.xsum));
+        }
+    }
     if (warp == 0) MB200_STAMP(1);
     __syncthreads();  // the only block-wide barrier: x is staged, barriers are initialised
     if (warp == 0) MB200_STAMP(2);
 
-    // Bind the warp to a column group: groups get warps in proportion to their
-    // work per row (a trailing group of v columns packs G/v rows into a pass).
-    const int v_last = P.bpr - (NG - 1) * F::kG;
-    const int rpp_last = (F::kG % v_last == 0) ? F::kG / v_last : 1;
-    const int weight_total = (NG - 1) * rpp_last + 1;  // full groups weigh rpp_last, the last group 1
-    int ng, idx, cnt;
-    {
-        // warps [0, n_last) serve the last group, the rest are dealt round-robin to the full groups
-        int n_last = (kConsumers + weight_total / 2) / weight_total;
-        if (n_last < 1) n_last = 1;
-        if (NG == 1) n_last = kConsumers;
-        if (NG > 1 && kConsumers - n_last < NG - 1) n_last = kConsumers - (NG - 1);
-        if (warp < n_last) {
-            ng = NG - 1;
-            idx = warp;
-            cnt = n_last;
-        } else {
-            const int w2 = warp - n_last, rest = kConsumers - n_last;
-            ng = w2 % (NG - 1);
-            idx = w2 / (NG - 1);
-            cnt = (rest - ng + (NG - 2)) / (NG - 1);
-        }
-    }
-    const int v = (ng == NG - 1) ? v_last : F::kG;
-    const int rpp = (ng == NG - 1) ? rpp_last : 1;
+    // The warp's column group (host-made table).
+    const uint32_t cfg = P.warp_cfg[warp];
+    const int ng = cfg & 31, col0 = (cfg >> 5) & 127, v = (cfg >> 12) & 15, rpp = (cfg >> 16) & 15;
+    const int idx = (cfg >> 20) & 15, cnt = (cfg >> 24) & 15;
     const int q = lane / F::kLanesPerBlock, sub = lane % F::kLanesPerBlock;
     const bool lane_ok = q < v * rpp;
-    const int col = ng * F::kG + (lane_ok ? q % v : 0);
+    const int col = col0 + (lane_ok ? q % v : 0);
     const int roff = lane_ok ? q / v : 0;
     const int W = (rpp > 1) ? v * F::kLanesPerBlock : 32;
     typename F::XRegs xr;
@@ -428,12 +576,15 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const Params P)
     Tile t;
     int s = 0, ph = 0;
     int k = 0;
+    int cur_slot = 0;
     while (walk.next(P, t)) {
-        const int R = (P.mode == kSwiGLU) ? 2 * t.rows : t.rows;
+        const int R = pairs ? 2 * t.rows : t.rows;
         uint32_t skew = 0;
-        if (F::kBlockBytes % 16 != 0) {
-            const uintptr_t begin = reinterpret_cast<uintptr_t>(seg_w(P, t.seg)) + (size_t)t.row0 * row_bytes;
-            skew = static_cast<uint32_t>(begin & 15);
+        if (F::kBlockBytes % 16 != 0)
+            skew = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(tile_src(P, t, row_bytes, sid)) & 15);
+        if (P.mode == kMoeDown && t.seg != cur_slot) {  // next expert: its own activation vector
+            cur_slot = t.seg;
+            F::load_xregs(xr, smem + cur_slot * L.x_stride, L, P.bpr, col, sub, lane_ok);
         }
         const uint8_t *base = smem + L.stages + s * L.stage_bytes + skew;
         float *pt = part + s * part_pitch + ng;
@@ -543,21 +694,79 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
         set_status(MB200_ERR_UNSUPPORTED, where);
         return;
     }
-    for (int i = 0; i < P.nseg; i++)
-        if (reinterpret_cast<uintptr_t>(P.seg[i].w) & (F::kBaseAlign - 1)) {
-            fprintf(stderr, "[mnemo_b200] %s: tensor %d is not %d-byte aligned\n", where, i, F::kBaseAlign);
-            set_status(MB200_ERR_ARG, where);
-            return;
-        }
+    const bool routed = (P.mode == kMoeGateUp || P.mode == kMoeDown);
+    bool misaligned = false;
+    if (routed) {
+        const uintptr_t b = reinterpret_cast<uintptr_t>(P.ebase);
+        misaligned = ((b + P.off_a) | P.estride) & (F::kBaseAlign - 1);
+        if (P.mode == kMoeGateUp) misaligned = misaligned || ((b + P.off_b) & (F::kBaseAlign - 1));
+        if (P.n_slots < 1 || P.n_slots > kMaxSlots || P.erows < 1) misaligned = true;
+    } else {
+        for (int i = 0; i < P.nseg; i++)
+            if (reinterpret_cast<uintptr_t>(P.seg[i].w) & (F::kBaseAlign - 1)) misaligned = true;
+    }
+    if (misaligned) {
+        fprintf(stderr, "[mnemo_b200] %s: a weight tensor is not %d-byte aligned (or bad slot count)\n", where,
+                F::kBaseAlign);
+        set_status(MB200_ERR_ARG, where);
+        return;
+    }
     P.bpr = (P.n_cols + 255) / 256;
     const int row_bytes = P.bpr * F::kBlockBytes;
-    const int NG = (P.bpr + F::kG - 1) / F::kG;
-    const int v_last = P.bpr - (NG - 1) * F::kG;
-    const int rpp_last = (F::kG % v_last == 0) ? F::kG / v_last : 1;
+
+    // ---- column groups and the warp table ----
+    int gw = 1;
+    while (gw * 2 <= F::kG && P.bpr % (gw * 2) == 0) gw *= 2;
+    int NG = P.bpr / gw;
+    int grp_col0[kConsumers], grp_v[kConsumers], grp_rpp[kConsumers], grp_warps[kConsumers];
+    if (NG <= kConsumers) {
+        for (int g = 0; g < NG; g++) {
+            grp_col0[g] = g * gw;
+            grp_v[g] = gw;
+            grp_rpp[g] = F::kG / gw;
+        }
+    } else {
+        NG = (P.bpr + F::kG - 1) / F::kG;
+        if (NG > kConsumers) {
+            fprintf(stderr, "[mnemo_b200] %s: n_cols=%d needs more column groups than consumer warps\n", where, P.n_cols);
+            set_status(MB200_ERR_UNSUPPORTED, where);
+            return;
+        }
+        for (int g = 0; g < NG; g++) {
+            const int vv = (g == NG - 1) ? P.bpr - g * F::kG : F::kG;
+            grp_col0[g] = g * F::kG;
+            grp_v[g] = vv;
+            grp_rpp[g] = (F::kG % vv == 0) ? F::kG / vv : 1;
+        }
+    }
+    // warps per group in proportion to passes per row (1 / rpp): every group gets one, the rest go where the load is highest
+    for (int g = 0; g < NG; g++) grp_warps[g] = 1;
+    for (int w = NG; w < kConsumers; w++) {
+        int arg = 0;
+        for (int g = 1; g < NG; g++)  // load(g) = 1 / (rpp * warps); compare by cross-multiplying
+            if (grp_rpp[arg] * grp_warps[arg] > grp_rpp[g] * grp_warps[g]) arg = g;
+        grp_warps[arg]++;
+    }
+    int sweep1 = 0;  // rows one round of the slowest-covering group handles at RU = 1 (tiles are multiples of the largest)
+    {
+        int w = 0;
+        for (int g = 0; g < NG; g++) {
+            for (int i = 0; i < grp_warps[g]; i++, w++)
+                P.warp_cfg[w] = (uint32_t)g | ((uint32_t)grp_col0[g] << 5) | ((uint32_t)grp_v[g] << 12) |
+                                ((uint32_t)grp_rpp[g] << 16) | ((uint32_t)i << 20) | ((uint32_t)grp_warps[g] << 24);
+            const int rows = grp_warps[g] * grp_rpp[g];
+            sweep1 = rows > sweep1 ? rows : sweep1;
+        }
+    }
+    P.n_groups = NG;
 
     // virtual rows
     int vrows = 0;
-    if (P.mode == kSwiGLU) {
+    if (P.mode == kMoeGateUp) {
+        vrows = P.n_slots * P.erows;
+    } else if (P.mode == kMoeDown) {
+        vrows = P.erows;
+    } else if (P.mode == kSwiGLU) {
         vrows = P.seg[0].rows;
         P.seg[0].start = 0;
         P.seg[1].start = 0;
@@ -571,17 +780,8 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
     P.vrows = vrows;
     const int grid = vrows < kSMs ? vrows : kSMs;
     const int per_cta = (vrows + grid - 1) / grid;  // rows of the longest range
-    const int mult = (P.mode == kSwiGLU) ? 2 : 1;   // stage rows per virtual row
-
-    // rows that one round of all consumer warps covers at RU = 1
-    const int weight_total = (NG - 1) * rpp_last + 1;
-    int n_last = (kConsumers + weight_total / 2) / weight_total;
-    if (n_last < 1) n_last = 1;
-    if (NG == 1) n_last = kConsumers;
-    if (NG > 1 && kConsumers - n_last < NG - 1) n_last = kConsumers - (NG - 1);
-    const int n_full = NG > 1 ? (kConsumers - n_last) / (NG - 1) : 0;
-    const int a1 = n_last * rpp_last, b1 = NG > 1 ? (n_full > 0 ? n_full : 1) : a1;
-    const int sweep1 = a1 > b1 ? a1 : b1;
+    const int mult = (P.mode == kSwiGLU || P.mode == kMoeGateUp) ? 2 : 1;  // stage rows per virtual row
+    const int n_x = (P.mode == kMoeDown) ? P.n_slots : 1;
 
     // RU: the fewest pass-times to cover the longest range; ties go to the larger RU (more independent work per warp)
     int ru = 1, best = 1 << 30;
@@ -593,6 +793,9 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
             ru = cand;
         }
     }
+#ifdef MB200_TUNING
+    if (const char *e = getenv("MB200_FORCE_RU")) ru = atoi(e);
+#endif
     // tile: a whole number of sweeps near the target size, never more than the range
     const int sweep = sweep1 * ru;
     int target = F::kTileTargetBytes / row_bytes;  // stage rows
@@ -602,18 +805,19 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
     if (mult == 2 && (stage_rows & 1)) stage_rows += 1;
     P.tile_rows = stage_rows / mult;
     if (P.tile_rows < 1) P.tile_rows = 1;
+    if (P.mode == kMoeDown && P.tile_rows > 64) P.tile_rows = 64;  // the epilogue keeps two running sums per lane
     stage_rows = P.tile_rows * mult;
 
     int S = kMaxStages;
-    Layout L = layout<F>(P.bpr, stage_rows, S);
+    Layout L = layout<F>(P.bpr, stage_rows, S, NG, n_x);
     while (S > 2 && L.total > 200 * 1024) {
         S--;
-        L = layout<F>(P.bpr, stage_rows, S);
+        L = layout<F>(P.bpr, stage_rows, S, NG, n_x);
     }
     while (L.total > 227 * 1024 && P.tile_rows > 1) {  // very wide rows: shrink the tile
         P.tile_rows = (P.tile_rows + 1) / 2;
         stage_rows = P.tile_rows * mult;
-        L = layout<F>(P.bpr, stage_rows, S);
+        L = layout<F>(P.bpr, stage_rows, S, NG, n_x);
     }
     if (L.total > 227 * 1024) {
         fprintf(stderr, "[mnemo_b200] %s: shape does not fit shared memory\n", where);

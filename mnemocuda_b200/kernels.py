@@ -138,6 +138,34 @@ def mb200_matvec_q6k_scaled_add(weights, x, y, n_rows, n_cols, scale, stream=Non
                                                   float(scale), _stream(stream)), "mb200_matvec_q6k_scaled_add")
 
 
+def mb200_router_scratch_bytes(n_experts: int) -> int:
+    return int(_lib.lib().mb200_router_scratch_bytes(n_experts))
+
+
+def mb200_router_topk(router_w, x, scratch, indices, weights, n_experts, n_cols, k, stream=None):
+    _check(_lib.lib().mb200_router_topk(_f32(router_w), _f32(x), _ptr(scratch), _ptr(indices), _f32(weights),
+                                        n_experts, n_cols, k, _stream(stream)), "mb200_router_topk")
+
+
+def mb200_moe_gate_up(experts, expert_stride, gate_off, up_off, ids, n_slots, x, act, EFF, H, stream=None):
+    _check(_lib.lib().mb200_moe_gate_up(_ptr(experts), expert_stride, gate_off, up_off, _ptr(ids), n_slots,
+                                        _f32(x), _f32(act), EFF, H, _stream(stream)), "mb200_moe_gate_up")
+
+
+def mb200_moe_down(experts, expert_stride, down_off, down_type, ids, wts, n_slots, act, residual, y, H, EFF,
+                   stream=None):
+    _check(_lib.lib().mb200_moe_down(_ptr(experts), expert_stride, down_off, down_type, _ptr(ids), _f32(wts),
+                                     n_slots, _f32(act), _ptr(residual), _f32(y), H, EFF, _stream(stream)),
+           "mb200_moe_down")
+
+
+def mb200_moe_block(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts, k, H, EFF, x, residual,
+                    out, ids, wts, act, scratch, stream=None):
+    _check(_lib.lib().mb200_moe_block(_f32(router_w), _ptr(experts), expert_stride, gate_sz, up_sz, down_type,
+                                      n_experts, k, H, EFF, _f32(x), _ptr(residual), _f32(out), _ptr(ids),
+                                      _f32(wts), _f32(act), _ptr(scratch), _stream(stream)), "mb200_moe_block")
+
+
 def mb200_fill_q4k(dst, n_blocks, seed, stream=None):
     _check(_lib.lib().mb200_fill_q4k(_ptr(dst), n_blocks, seed, _stream(stream)), "mb200_fill_q4k")
 

@@ -138,7 +138,7 @@ Q6_SHAPES = [
     (512, 4096),    # V projection
     (2048, 768),    # 30B expert down: 3 blocks per row, rows only 2-byte aligned
     (1000, 2048),
-    (1, 256), (5, 256), (17, 300), (33, 1000), (7, 1280), (3, 12288), (149, 512),
+    (1, 256), (5, 256), (17, 300), (33, 1000), (7, 1280), (3, 12288), (3, 16384), (149, 512),
 ]
 
 
