@@ -1,0 +1,330 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized-weight hot path: one MoE expert block, batch 1, Qwen3-235B shape.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE config 2): router fp32 128x4096 -> top-8 of 128 experts; per routed expert a
+fused gate+up Q4_K matvec (2 x 1536x4096) with SwiGLU and a Q6_K down matvec (4096x1536), weighted
+sum + residual. Weights are seeded synthetic GGUF blocks with the benchmark's distributions
+(mnemocuda_b200/synth.py); no dataset or checkpoint is involved. A "step" is one block on one
+layer; steps rotate over `layers` resident layers (>= 18 GB), so every pass is cold in L2.
+
+`value` is algorithmic GB/s (router + the 8 routed expert blobs = 100 007 936 B per step) with all
+inputs resident in HBM, timed with CUDA events around a CUDA graph of the K steps. `e2e` is the
+same metric through the host-buffer call (pinned host x/residual in, result out, every step).
+`roofline` is for the dominant kernel (the routed gate/up stream kernel). `cpu_baseline` and
+`--impl reference` time the C oracle (the CPU restatement of the reference's algorithm -- the
+reference has no CPU implementation of this path) on the box's host cores on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "Q4K/Q6K matvec HBM GB/s"
+UNIT = "GB/s"
+WORKLOAD = ("configs[1]: MoE expert block, batch 1, Qwen3-235B shape -- router fp32 128x4096 + top-8 of 128 "
+            "experts, Q4_K gate/up 2x(1536x4096)+SwiGLU, Q6_K down 4096x1536, weighted sum + residual")
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one routed gate/up launch (8 experts, 56 623 104
+# algorithmic bytes), from the ncu capture summarised in profiles/; None until captured.
+GATE_UP_TRAFFIC_BYTES = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz, self._stop = [], set(), None, threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+        self.t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": "nvmlClocksEventReasonHwSlowdown", "hw_thermal_slowdown": "nvmlClocksEventReasonHwThermalSlowdown",
+                 "sw_thermal_slowdown": "nvmlClocksEventReasonSwThermalSlowdown", "sw_power_cap": "nvmlClocksEventReasonSwPowerCap"}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+                mask = get(self.h)
+                for key, const in names.items():
+                    bit = getattr(nv, const, None) or getattr(nv, const.replace("Event", "Throttle"), 0)
+                    if bit and (mask & bit):
+                        self.reasons.add(key)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self.nv:
+            self.t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self.nv:
+            self.t.join(timeout=1)
+
+    def summary(self):
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def cpu_block_baseline(shape, experts_host, router_host, seconds=12.0, threads=None):
+    """Oracle MoE blocks per second on the host cores -> GB/s of algorithmic bytes."""
+    from oracle import oracle
+    from mnemocuda_b200 import synth
+    if threads:
+        oracle.set_num_threads(threads)
+    cores = oracle.num_threads()
+    s = shape
+    n, t0 = 0, time.perf_counter()
+    while True:
+        x = synth.normal_f32(900 + n, s.H)
+        res = synth.normal_f32(1900 + n, s.H)
+        oracle.moe_block(router_host, experts_host, s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE, s.K, s.H, s.EFF,
+                         x, res)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds or n >= 4000:
+            break
+    return s.algorithmic_bytes * n / dt / 1e9, cores, n, dt
+
+
+def host_layer(shape, seed=1, layer=0):
+    """One layer's router + experts as host arrays (numpy generator: same streams as the device fill)."""
+    from mnemocuda_b200 import synth
+    s = shape
+    blobs = []
+    for e in range(s.NE):
+        tid = (seed * 1000 + layer) * 1000 + e
+        q4 = synth.q4k_blocks(tid * 2, (s.gate_sz + s.up_sz) // synth.Q4K_BLOCK).reshape(-1)
+        dn = synth.q6k_blocks(tid * 2 + 1, s.down_sz // synth.Q6K_BLOCK).reshape(-1)
+        blobs.append(np.concatenate([q4, dn]))
+    router = synth.normal_f32(seed * 100003 + layer, s.NE * s.H, s.H ** -0.5)
+    return np.concatenate(blobs), router
+
+
+def run_reference(args):
+    """The reference arm: the oracle (CPU restatement of the reference's algorithm) on all host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from mnemocuda_b200.moe import MoEShape
+    shape = MoEShape()
+    experts, router = None, None
+    try:
+        import torch
+        if torch.cuda.is_available():
+            from mnemocuda_b200.moe import ResidentMoE
+            moe = ResidentMoE(shape, 1, "cuda:0", seed=1)
+            experts = moe.experts[0].reshape(-1).cpu().numpy()
+            router = moe.router[0].reshape(-1).cpu().numpy()
+            del moe
+    except Exception:
+        experts = None
+    if experts is None:
+        experts, router = host_layer(shape)
+    from oracle import oracle
+    cores = oracle.num_threads()
+    from mnemocuda_b200 import synth
+    s = shape
+    per_step = 4  # blocks per "step": a bounded sample of the workload
+    def step(i):
+        for j in range(per_step):
+            x = synth.normal_f32(900 + i * per_step + j, s.H)
+            res = synth.normal_f32(1900 + i * per_step + j, s.H)
+            oracle.moe_block(router, experts, s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE, s.K, s.H, s.EFF, x, res)
+    for i in range(args.warmup):
+        step(i)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        step(i)
+    dt = time.perf_counter() - t0
+    value = s.algorithmic_bytes * per_step * args.steps / dt / 1e9
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 dot, fp32 accumulate",
+            "data": "synthetic", "config": {"workload": WORKLOAD},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                             "sample": f"{per_step} MoE blocks per step on layer 0 (C oracle, OpenMP over rows)"},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from mnemocuda_b200 import kernels as K
+    from mnemocuda_b200.moe import HostMoEBlock, MoEShape, ResidentMoE
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the kernels have no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    shape = MoEShape()
+    layers = args.layers
+    moe = ResidentMoE(shape, layers, dev, seed=1)
+    K.mb200_set_pdl(not args.no_pdl)
+    H = shape.H
+    xs = torch.empty(layers, H, device=dev)
+    rs = torch.empty(layers, H, device=dev)
+    outs = torch.empty(layers, H, device=dev)
+    K.mb200_fill_normal_f32(xs, layers * H, 4242, 1.0)
+    K.mb200_fill_normal_f32(rs, layers * H, 4243, 1.0)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed_graph(fn, steps, warmup):
+        """fn(i) enqueues step i; returns ms per step for `steps` steps captured in one CUDA graph."""
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(steps):
+                fn(warmup + i)
+        g.replay()  # untimed: instantiate/upload
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1) / steps
+
+    # ---- device-resident: the whole block, K steps in one graph ----
+    block = lambda i: moe.forward(i % layers, xs[i % layers], rs[i % layers], outs[i % layers])
+    with ClockSampler(local) as clk:
+        ms = timed_graph(block, args.steps, args.warmup)
+        # ---- dominant kernel alone (ids already routed by the runs above) ----
+        gu_ms = timed_graph(lambda i: moe.gate_up(i % layers, xs[i % layers]), args.steps, args.warmup)
+        dn_ms = timed_graph(lambda i: moe.down(i % layers, rs[i % layers], outs[i % layers]), args.steps, args.warmup)
+        rt_ms = timed_graph(lambda i: moe.route(i % layers, xs[i % layers]), args.steps, args.warmup)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = shape.algorithmic_bytes * world / (ms * 1e-3) / 1e9
+
+    # ---- end to end through host buffers ----
+    host_block = HostMoEBlock(moe)
+    hx = torch.randn(layers, H).pin_memory()
+    hr = torch.randn(layers, H).pin_memory()
+    ho = torch.empty(layers, H).pin_memory()
+    for i in range(args.warmup):
+        host_block(i % layers, hx[i % layers], hr[i % layers], ho[i % layers])
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        j = (args.warmup + i) % layers
+        host_block(j, hx[j], hr[j], ho[j])
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = shape.algorithmic_bytes * world / (e2e_ms * 1e-3) / 1e9
+
+    err = K.mb200_device_error()
+    if err != 0:
+        raise RuntimeError(f"a kernel reported device error {err}")
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, which = measured_peaks()
+    gu_bytes = shape.K * (shape.gate_sz + shape.up_sz) + shape.H * 4 + shape.K * shape.EFF * 4
+    achieved = gu_bytes / (gu_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 dot (u8 x s8 dp4a), fp32 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers_resident": layers, "resident_GB": round(moe.experts.numel() / 1e9, 2),
+                   "l2": "inputs larger than L2: steps rotate over resident layers, 1.57 GB of experts each",
+                   "timing": "CUDA events around one CUDA graph of the timed steps", "pdl": not args.no_pdl,
+                   "parallelism": "independent replicas per GPU" if world > 1 else "single GPU"},
+        "clocks": clk.summary(),
+        "gpu_launches": 3 * args.steps,
+        "kernels_ms": {"router_topk": rt_ms, "moe_gate_up": gu_ms, "moe_down": dn_ms},
+        "roofline": {"bound": "hbm", "kernel": "stream_kernel<Q4,*> (routed gate/up + SwiGLU, 8 experts per launch)",
+                     "achieved": achieved, "peak": peak, "peak_source": which + " copy bandwidth (MEASURED_PEAKS.json)",
+                     "unit": "GB/s", "frac": achieved / peak, "frac_of_8TBs_nominal": achieved / 8000.0,
+                     "algorithmic_bytes_per_launch": gu_bytes, "traffic": GATE_UP_TRAFFIC_BYTES},
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": host_block.h2d_bytes,
+                "d2h_bytes_per_step": host_block.d2h_bytes},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        experts_host = moe.experts[0].reshape(-1).cpu().numpy()
+        router_host = moe.router[0].reshape(-1).cpu().numpy()
+        v, cores, n, dt = cpu_block_baseline(shape, experts_host, router_host, seconds=args.cpu_seconds)
+        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": f"{n} MoE blocks on layer 0 in {dt:.1f} s (C oracle, OpenMP over rows)"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=12, help="resident MoE layers the steps rotate over")
+    ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launch")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        if args.steps > 20:
+            args.steps = 20  # each step is 4 CPU blocks: keep the run within a few minutes
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

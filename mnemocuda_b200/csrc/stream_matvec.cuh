@@ -347,7 +347,7 @@ template <class F>
 __device__ __forceinline__ void quantize_x_warp(const float *__restrict__ x, int n_cols, int bpr,
                                                 uint32_t *q1, uint32_t *q2, float *s1, float *xsum)
 {
-    constexpr int UN = 4;
+    constexpr int UN = 12;  // 1536 columns (the 235B expert width) in one round of loads
     const int kpad = bpr * 256;
     const int pitch = F::kSlotsPerBlock * bpr + 1;
     const int lane = threadIdx.x & 31;

@@ -1,0 +1,104 @@
+"""Host side of the decode-time MoE block: resident expert weights + the three-launch
+device path (router + top-k, routed gate/up + SwiGLU, routed down + weighted sum + residual).
+
+Mirrors what the reference's forward_layer does between ffn_norm and the residual add
+(src/forward.c:810-823, 875, 1122-1142, 1114) with every expert resident in HBM, so there
+is no cache walk and no host round trip for the routed ids.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import kernels as K
+from . import synth
+
+
+class MoEShape:
+    def __init__(self, n_experts=128, top_k=8, hidden=4096, eff=1536, down_type=14):
+        self.NE, self.K, self.H, self.EFF, self.down_type = n_experts, top_k, hidden, eff, down_type
+        self.gate_sz, self.up_sz, self.down_sz = synth.expert_sizes(hidden, eff, down_type)
+        self.stride = self.gate_sz + self.up_sz + self.down_sz
+
+    @property
+    def router_bytes(self) -> int:
+        return self.NE * self.H * 4
+
+    @property
+    def algorithmic_bytes(self) -> int:
+        """Bytes one block must read: the router matrix and the K routed expert blobs."""
+        return self.router_bytes + self.K * self.stride
+
+
+class ResidentMoE:
+    """`n_layers` MoE layers' routers and experts resident on one device, seeded synthetic values."""
+
+    def __init__(self, shape: MoEShape, n_layers: int, device="cuda", seed: int = 1, expert_range=None):
+        self.shape, self.n_layers, self.device = shape, n_layers, torch.device(device)
+        s = shape
+        lo, hi = expert_range if expert_range is not None else (0, s.NE)
+        self.expert_lo, self.n_local = lo, hi - lo
+        self.router = torch.empty(n_layers, s.NE, s.H, dtype=torch.float32, device=self.device)
+        self.experts = torch.empty(n_layers, self.n_local, s.stride, dtype=torch.uint8, device=self.device)
+        K.mb200_init()
+        q4_blocks = (s.gate_sz + s.up_sz) // synth.Q4K_BLOCK
+        for layer in range(n_layers):
+            K.mb200_fill_normal_f32(self.router[layer], s.NE * s.H, seed * 100003 + layer, s.H ** -0.5)
+            for e in range(self.n_local):
+                tid = (seed * 1000 + layer) * 1000 + lo + e  # one seed per tensor
+                blob = self.experts[layer, e]
+                K.mb200_fill_q4k(blob, q4_blocks, tid * 2 + 0)
+                if s.down_type == 14:
+                    K.mb200_fill_q6k(blob[s.gate_sz + s.up_sz:], s.down_sz // synth.Q6K_BLOCK, tid * 2 + 1)
+                else:
+                    K.mb200_fill_q4k(blob[s.gate_sz + s.up_sz:], s.down_sz // synth.Q4K_BLOCK, tid * 2 + 1)
+        self.ids = torch.zeros(n_layers, s.K, dtype=torch.int32, device=self.device)
+        self.wts = torch.zeros(n_layers, s.K, dtype=torch.float32, device=self.device)
+        self.act = torch.zeros(s.K, s.EFF, dtype=torch.float32, device=self.device)
+        n = K.mb200_router_scratch_bytes(s.NE)
+        self.scratch = torch.zeros((n + 15) // 16 * 16, dtype=torch.uint8, device=self.device)
+        torch.cuda.synchronize(self.device)
+
+    def forward(self, layer: int, x: torch.Tensor, residual: torch.Tensor, out: torch.Tensor, stream=None) -> None:
+        """out = residual + MoE(x) for one layer; all tensors on the device."""
+        s = self.shape
+        K.mb200_moe_block(self.router[layer], self.experts[layer], s.stride, s.gate_sz, s.up_sz, s.down_type,
+                          s.NE, s.K, s.H, s.EFF, x, residual, out, self.ids[layer], self.wts[layer], self.act,
+                          self.scratch, stream)
+
+    def route(self, layer: int, x: torch.Tensor, stream=None) -> None:
+        s = self.shape
+        K.mb200_router_topk(self.router[layer], x, self.scratch, self.ids[layer], self.wts[layer], s.NE, s.H, s.K,
+                            stream)
+
+    def gate_up(self, layer: int, x: torch.Tensor, stream=None) -> None:
+        s = self.shape
+        K.mb200_moe_gate_up(self.experts[layer], s.stride, 0, s.gate_sz, self.ids[layer], s.K, x, self.act, s.EFF,
+                            s.H, stream)
+
+    def down(self, layer: int, residual, out: torch.Tensor, stream=None) -> None:
+        s = self.shape
+        K.mb200_moe_down(self.experts[layer], s.stride, s.gate_sz + s.up_sz, s.down_type, self.ids[layer],
+                         self.wts[layer], s.K, self.act, residual, out, s.H, s.EFF, stream)
+
+
+class HostMoEBlock:
+    """The call a user of host buffers makes: hidden state in, hidden state out.
+
+    Copies x and the residual from pinned host memory, runs the block, copies the result back
+    and waits for it (the reference's engine does the same per token for the logits)."""
+
+    def __init__(self, moe: ResidentMoE):
+        self.moe = moe
+        H = moe.shape.H
+        self.x = torch.empty(H, dtype=torch.float32, device=moe.device)
+        self.res = torch.empty(H, dtype=torch.float32, device=moe.device)
+        self.out = torch.empty(H, dtype=torch.float32, device=moe.device)
+        self.h2d_bytes = 2 * H * 4
+        self.d2h_bytes = H * 4
+
+    def __call__(self, layer: int, x_host: torch.Tensor, res_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        self.x.copy_(x_host, non_blocking=True)
+        self.res.copy_(res_host, non_blocking=True)
+        self.moe.forward(layer, self.x, self.res, self.out)
+        out_host.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
