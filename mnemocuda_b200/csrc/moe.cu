@@ -43,8 +43,7 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const float
 {
     __shared__ float red[kRouterThreads / 32];
     __shared__ int is_last;
-    __shared__ float s_vals[32 * 16];
-    __shared__ int s_ids[32 * 16];
+    __shared__ TopkShared topk_sh;
     float *logits = reinterpret_cast<float *>(scratch + 8);
     const int row = blockIdx.x;
     const float *wr = w + (size_t)row * n_cols;
@@ -97,7 +96,7 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const float
     if (!is_last || threadIdx.x >= 32) return;
     __threadfence();
     topk_softmax_warp(const_cast<const float *>(static_cast<volatile float *>(logits)), indices, weights, n_experts, k,
-                      s_vals, s_ids);
+                      topk_sh);
     if (threadIdx.x == 0) scratch[0] = 0;  // ready for the next call
 }
 

@@ -59,9 +59,8 @@ __global__ void __launch_bounds__(32) topk_softmax_kernel(const float *__restric
                                                           float *__restrict__ weights, int n_experts,
                                                           int k)
 {
-    __shared__ float s_vals[32 * 16];
-    __shared__ int s_ids[32 * 16];
-    topk_softmax_warp(scores, indices, weights, n_experts, k, s_vals, s_ids);
+    __shared__ TopkShared sh;
+    topk_softmax_warp(scores, indices, weights, n_experts, k, sh);
 }
 
 __global__ void swiglu_kernel(const float *__restrict__ gate, const float *__restrict__ up,

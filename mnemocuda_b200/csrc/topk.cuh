@@ -12,111 +12,355 @@ namespace mb200 {
 // greater"; (2) the 32 x 16 candidate table is scanned in (lane, slot) order by
 // the same rule. Stage 2 keeps its k slots in registers and tracks the running
 // minimum, so a rejected candidate costs one compare.
-struct TopK {
-    float v[16];
-    int id[16];
-    float cur_min;
-    int cur_mi;
-    __device__ void reset(int k)
+// The k live slots kept sorted by (value, slot) in registers, so the reference's "first index
+// of the minimum" is always entry 0. Replacing the minimum = evict entry 0 and insert the
+// newcomer, which inherits the evicted slot. The insert is branch-free and shallow: all
+// compares are independent, then an add tree, then independent selects. KW = 8 or 16 wide.
+template <int KW>
+struct SortedSlots {
+    float v[KW];
+    int slot[KW];
+    int id[KW];
+    __device__ __forceinline__ void reset(int k)
     {
 #pragma unroll
-        for (int i = 0; i < 16; i++) {
-            v[i] = -1e30f;
+        for (int i = 0; i < KW; i++) {
+            v[i] = i < k ? -1e30f : 3.0e38f;  // entries >= k: +huge sentinels that never move
+            slot[i] = i;
             id[i] = -1;
         }
-        cur_min = -1e30f;
-        cur_mi = 0;
-        (void)k;
     }
-    __device__ void offer(float val, int ident, int k)
+    __device__ __forceinline__ void replace_min(float val, int ident)
     {
-        if (!(val > cur_min)) return;
+        const int s = slot[0];
+        int before[KW];
 #pragma unroll
-        for (int i = 0; i < 16; i++)
-            if (i == cur_mi) {
-                v[i] = val;
-                id[i] = ident;
-            }
-        // first index of the minimum over the k live slots
-        float m = v[0];
-        int mi = 0;
+        for (int i = 1; i < KW; i++) before[i] = (v[i] < val || (v[i] == val && slot[i] < s)) ? 1 : 0;
+        before[0] = 0;
+        int pos = 0;  // entries 1..KW-1 ordered before the newcomer
 #pragma unroll
-        for (int i = 1; i < 16; i++)
-            if (i < k && v[i] < m) {
-                m = v[i];
-                mi = i;
-            }
-        cur_min = m;
-        cur_mi = mi;
+        for (int i = 1; i < KW; i++) pos += before[i];
+        // entries 1..pos move down one place, the newcomer lands at pos; sorted order makes
+        // "i < pos" the same as before[i+1]
+#pragma unroll
+        for (int i = 0; i < KW - 1; i++) {
+            const bool shift = before[i + 1] != 0;
+            const bool here = (i == pos);
+            v[i] = shift ? v[i + 1] : (here ? val : v[i]);
+            slot[i] = shift ? slot[i + 1] : (here ? s : slot[i]);
+            id[i] = shift ? id[i + 1] : (here ? ident : id[i]);
+        }
+        if (pos == KW - 1) {
+            v[KW - 1] = val;
+            slot[KW - 1] = s;
+            id[KW - 1] = ident;
+        }
     }
 };
 
-// Order-preserving map float -> int (for redux.sync min/max); -0.0 is folded onto +0.0 so that
-// keys compare exactly like the floats do.
-__device__ __forceinline__ int float_key(float f)
+// One warp. Stage 1: each lane keeps the local top-k of scores lane, lane+32, ... and writes it
+// to the 32 x 16 candidate table by slot. Stage 2: every lane runs the same walk over the table
+// in (lane, slot) order (broadcast reads, uniform branches); a source lane whose best candidate
+// cannot enter is skipped with one compare.
+template <int KW>
+__device__ __noinline__ void topk_softmax_warp_seq_kw(const float *scores, int *indices, float *weights,
+                                                     int n_experts, int k, float *s_vals, int *s_ids)
 {
-    int b = __float_as_int(f);
-    if (b == static_cast<int>(0x80000000u)) b = 0;
-    return b ^ ((b >> 31) & 0x7FFFFFFF);
-}
-__device__ __forceinline__ float key_float(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7FFFFFFF)); }
-
-// One warp. Stage 1 runs in parallel (one local top-k per lane, registers). Stage 2 walks the
-// candidates in the reference's (lane, slot) order with the k result slots spread over lanes
-// 0..k-1: a rejected candidate costs a shuffle and a compare, an accepted one a warp-wide
-// integer min (redux.sync) plus a ballot to find the first slot that holds the new minimum.
-// s_vals / s_ids are unused scratch kept for interface stability.
-__device__ __forceinline__ void topk_softmax_warp(const float *scores, int *indices, float *weights, int n_experts,
-                                                  int k, float *s_vals, int *s_ids)
-{
-    (void)s_vals;
-    (void)s_ids;
     const unsigned full = 0xffffffffu;
     const int lane = threadIdx.x & 31;
-    TopK loc;
+#ifdef MB200_TRACE
+    long long t0 = clock64();
+#endif
+    SortedSlots<KW> loc;
     loc.reset(k);
-    int cnt = 0;  // live entries of this lane: stage 1 fills slots 0,1,.. in order before it ever replaces
-    for (int j = lane; j < n_experts; j += 32) {
-        const float val = scores[j];
-        if (val > loc.cur_min) {
-            loc.offer(val, j, k);
-            if (cnt < k) cnt++;
-        }
-    }
-    const int cmax = __reduce_max_sync(full, cnt);
-
-    float sv = -1e30f;  // lane i < k holds result slot i
-    int sid = -1;
-    float cur_min = -1e30f;
-    int cur_mi = 0;
-    for (int l = 0; l < 32; l++) {
-        const int cl = __shfl_sync(full, cnt, l);
+    int cnt = 0;  // live entries of this lane (slots 0..cnt-1: stage 1 fills them in order before it ever replaces)
+    float lmax = -1e30f;
+    for (int j0 = lane; j0 < n_experts; j0 += 32 * 8) {
+        float sv[8];
 #pragma unroll
-        for (int i = 0; i < 16; i++) {
-            if (i >= cmax) break;
-            const float val = __shfl_sync(full, loc.v[i], l);
-            if (i >= cl || !(val > cur_min)) continue;  // warp-uniform
-            const int cid = __shfl_sync(full, loc.id[i], l);
-            if (lane == cur_mi) {
-                sv = val;
-                sid = cid;
+        for (int u = 0; u < 8; u++) sv[u] = (j0 + 32 * u < n_experts) ? scores[j0 + 32 * u] : -1e30f;  // loads in flight together
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+            if (sv[u] > loc.v[0]) {
+                loc.replace_min(sv[u], j0 + 32 * u);
+                lmax = fmaxf(lmax, sv[u]);
+                if (cnt < k) cnt++;
             }
-            const int key = lane < k ? float_key(sv) : 0x7FFFFFFF;
-            const int mkey = __reduce_min_sync(full, key);
-            cur_mi = __ffs(__ballot_sync(full, key == mkey)) - 1;
-            cur_min = key_float(mkey);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i++) s_vals[lane * 16 + i] = -1e30f;
+#pragma unroll
+    for (int i = 0; i < KW; i++)
+        if (i < k && loc.id[i] >= 0) {
+            s_vals[lane * 16 + loc.slot[i]] = loc.v[i];
+            s_ids[lane * 16 + loc.slot[i]] = loc.id[i];
+        }
+    const int cmax = __reduce_max_sync(full, cnt);
+    __syncwarp();
+#ifdef MB200_TRACE
+    long long t1 = clock64();
+#endif
+
+    SortedSlots<KW> top;
+    top.reset(k);
+    for (int l = 0; l < 32; l++) {
+        const float best = __shfl_sync(full, lmax, l);
+        if (!(best > top.v[0])) continue;  // uniform: nothing of this source lane can enter
+        float cv[KW];
+#pragma unroll
+        for (int i = 0; i < KW; i++) cv[i] = i < cmax ? s_vals[l * 16 + i] : -1e30f;
+#pragma unroll
+        for (int i = 0; i < KW; i++) {
+            if (i >= cmax) break;
+            if (__any_sync(full, cv[i] > top.v[0]))  // uniform by construction; sentinels (-1e30) never pass
+                top.replace_min(cv[i], s_ids[l * 16 + i]);
         }
     }
-    // softmax over the k kept logits, summed in slot order like the reference
-    const int xkey = __reduce_max_sync(full, lane < k ? float_key(sv) : static_cast<int>(0x80000000u));
-    const float mx = key_float(xkey);
-    const float ex = lane < k ? expf(sv - mx) : 0.0f;
-    float sum = 0.0f;
-    for (int i = 0; i < k; i++) sum += __shfl_sync(full, ex, i);
-    if (lane < k) {
-        weights[lane] = ex / sum;
-        indices[lane] = sid;
+#ifdef MB200_TRACE
+    long long t2 = clock64();
+    if (lane == 0) printf("topk: stage1 %lld cycles, stage2 %lld cycles\n", t1 - t0, t2 - t1);
+#endif
+    // back to slot order through the (now free) table, then softmax summed in slot order like the reference
+    __syncwarp();
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < KW; i++)
+            if (i < k) {
+                s_vals[top.slot[i]] = top.v[i];
+                s_ids[top.slot[i]] = top.id[i];
+            }
+        float mx = s_vals[0];
+        for (int i = 1; i < k; i++) mx = fmaxf(mx, s_vals[i]);
+        float sum = 0.0f;
+        for (int i = 0; i < k; i++) {
+            const float e = expf(s_vals[i] - mx);
+            s_vals[i] = e;
+            sum += e;
+        }
+        for (int i = 0; i < k; i++) {
+            weights[i] = s_vals[i] / sum;
+            indices[i] = s_ids[i];
+        }
     }
+}
+
+// ---- parallel form -------------------------------------------------------------
+// The replace-the-minimum walk of stage 2 has a closed form when no two ACCEPTED
+// candidates are equal. With candidates p = 0..M-1 in the reference's (lane, slot) order:
+//   accept(p)  <=>  #{q < p : v_q >= v_p} < k            (v_p beats the k-th largest so far)
+//   t(p) = number of accepted candidates before p        (arrival index)
+//   r(p) = number of accepted candidates smaller than p  (the j-th eviction removes rank j,
+//                                                         because evicted values never decrease)
+//   slot(p) = t(p) if t(p) < k, else slot(the accepted candidate of rank t(p) - k)
+// and the survivors are the k accepted candidates of highest rank. All counts are data-parallel;
+// only the slot chain is a short pointer walk. Equal accepted values fall back to the serial form.
+struct __align__(16) TopkShared {
+    float val[512];   // candidates in sequence order
+    int cid[512];
+    float aval[512];  // accepted candidates in arrival order
+    int aid[512];
+    int byrank[512];
+    float outv[16];
+    int outid[16];
+};
+
+template <int KW>
+__device__ __forceinline__ bool topk_softmax_warp_par(const float *scores, int *indices, float *weights,
+                                                      int n_experts, int k, TopkShared &sh)
+{
+    const unsigned full = 0xffffffffu;
+    const int lane = threadIdx.x & 31;
+    // ---- stage 1: the lane's candidates, in slot order ----
+    float lv[KW];
+    int li[KW];
+    int cnt = 0;
+#pragma unroll
+    for (int i = 0; i < KW; i++) {
+        lv[i] = -1e30f;
+        li[i] = -1;
+    }
+    if (n_experts <= 32 * k) {
+        // at most k scores per lane: nothing is ever replaced, slots fill in arrival order
+        float sv[KW];
+#pragma unroll
+        for (int u = 0; u < KW; u++) sv[u] = (u < k && lane + 32 * u < n_experts) ? scores[lane + 32 * u] : -1e30f;
+#pragma unroll
+        for (int u = 0; u < KW; u++)
+            if (sv[u] > -1e30f) {
+#pragma unroll
+                for (int i = 0; i < KW; i++)
+                    if (i == cnt) {
+                        lv[i] = sv[u];
+                        li[i] = lane + 32 * u;
+                    }
+                cnt++;
+            }
+    } else {
+        SortedSlots<KW> loc;
+        loc.reset(k);
+        for (int j0 = lane; j0 < n_experts; j0 += 32 * 8) {
+            float sv[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) sv[u] = (j0 + 32 * u < n_experts) ? scores[j0 + 32 * u] : -1e30f;
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (sv[u] > loc.v[0]) {
+                    loc.replace_min(sv[u], j0 + 32 * u);
+                    if (cnt < k) cnt++;
+                }
+        }
+#pragma unroll
+        for (int i = 0; i < KW; i++)
+            if (i < k && loc.id[i] >= 0) {
+#pragma unroll
+                for (int j = 0; j < KW; j++)
+                    if (loc.slot[i] == j) {
+                        lv[j] = loc.v[i];
+                        li[j] = loc.id[i];
+                    }
+            }
+    }
+    // dense sequence index: exclusive scan of cnt over lanes
+    int base = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(full, base, o);
+        if (lane >= o) base += t;
+    }
+    const int M = __shfl_sync(full, base, 31);
+    base -= cnt;
+#pragma unroll
+    for (int i = 0; i < KW; i++)
+        if (i < cnt) {
+            sh.val[base + i] = lv[i];
+            sh.cid[base + i] = li[i];
+        }
+    const int Mpad = (M + 3) & ~3;
+    if (lane < Mpad - M) sh.val[M + lane] = __int_as_float(0x7FC00000);  // NaN padding: compares false
+    if (lane < 16) {
+        sh.outv[lane] = -1e30f;
+        sh.outid[lane] = -1;
+    }
+    __syncwarp();
+
+    // ---- accept flags and arrival indices, four rows of 32 candidates at a time ----
+    int m = 0;
+    for (int row0 = 0; row0 * 32 < M; row0 += 4) {
+        float v[4];
+        int c[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int p = (row0 + i) * 32 + lane;
+            v[i] = p < M ? sh.val[p] : __int_as_float(0x7FC00000);
+            c[i] = 0;
+        }
+        // rows before row0: every q is earlier than every p of this chunk
+        const int q_full = row0 * 32;
+        for (int q = 0; q < q_full; q += 4) {
+            const float4 w = *reinterpret_cast<const float4 *>(&sh.val[q]);
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                c[i] += (w.x >= v[i]) + (w.y >= v[i]) + (w.z >= v[i]) + (w.w >= v[i]);
+        }
+        // the chunk's own rows: q counts only if q < p
+        const int q_end = min(Mpad, (row0 + 4) * 32);
+        for (int q = q_full; q < q_end; q += 4) {
+            const float4 w = *reinterpret_cast<const float4 *>(&sh.val[q]);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int p = (row0 + i) * 32 + lane;
+                c[i] += (q + 0 < p && w.x >= v[i]) + (q + 1 < p && w.y >= v[i]) + (q + 2 < p && w.z >= v[i]) +
+                        (q + 3 < p && w.w >= v[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int p = (row0 + i) * 32 + lane;
+            const bool acc = p < M && c[i] < k;
+            const unsigned bal = __ballot_sync(full, acc);
+            if (acc) {
+                const int t = m + __popc(bal & ((1u << lane) - 1u));
+                sh.aval[t] = v[i];
+                sh.aid[t] = sh.cid[p];
+            }
+            m += __popc(bal);
+        }
+    }
+    const int mpad = (m + 3) & ~3;
+    __syncwarp();
+    if (lane < mpad - m) sh.aval[m + lane] = __int_as_float(0x7FC00000);
+    __syncwarp();
+
+    // ---- ranks among the accepted, and the tie check ----
+    bool tie = false;
+    for (int t0 = 0; t0 < m; t0 += 32) {
+        const int t = t0 + lane;
+        const float av = t < m ? sh.aval[t] : __int_as_float(0x7FC00000);
+        int r = 0, eq = 0;
+        for (int u = 0; u < mpad; u += 4) {
+            const float4 w = *reinterpret_cast<const float4 *>(&sh.aval[u]);
+            r += (w.x < av) + (w.y < av) + (w.z < av) + (w.w < av);
+            eq += (w.x == av) + (w.y == av) + (w.z == av) + (w.w == av);
+        }
+        if (t < m) {
+            if (eq > 1) tie = true;
+            sh.byrank[r] = t;
+            sh.cid[t] = r;  // cid is free now: rank by arrival index
+        }
+    }
+    if (__any_sync(full, tie)) return false;
+    __syncwarp();
+
+    // ---- survivors walk their slot chain ----
+    for (int t0 = 0; t0 < m; t0 += 32) {
+        const int t = t0 + lane;
+        if (t < m && sh.cid[t] >= m - k) {
+            int cur = t;
+            while (cur >= k) cur = sh.byrank[cur - k];
+            sh.outv[cur] = sh.aval[t];
+            sh.outid[cur] = sh.aid[t];
+        }
+    }
+    __syncwarp();
+    // ---- softmax over the k kept logits, summed in slot order like the reference ----
+    if (lane == 0) {
+        float mx = sh.outv[0];
+        for (int i = 1; i < k; i++) mx = fmaxf(mx, sh.outv[i]);
+        float e[16];
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+            if (i < k) {
+                e[i] = expf(sh.outv[i] - mx);
+                sum += e[i];
+            }
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+            if (i < k) {
+                weights[i] = e[i] / sum;
+                indices[i] = sh.outid[i];
+            }
+    }
+    return true;
+}
+
+// One warp. `sh` is shared memory. Results are identical to the reference's kernel
+// (src/kernels.cu:993-1057): same kept set, same output slot order.
+__device__ __forceinline__ void topk_softmax_warp(const float *scores, int *indices, float *weights, int n_experts,
+                                                  int k, TopkShared &sh)
+{
+    bool done;
+    if (k <= 8)
+        done = topk_softmax_warp_par<8>(scores, indices, weights, n_experts, k, sh);
+    else
+        done = topk_softmax_warp_par<16>(scores, indices, weights, n_experts, k, sh);
+    if (done) return;
+    __syncwarp();
+    // equal accepted values: the serial walk decides
+    if (k <= 8)
+        topk_softmax_warp_seq_kw<8>(scores, indices, weights, n_experts, k, sh.val, sh.cid);
+    else
+        topk_softmax_warp_seq_kw<16>(scores, indices, weights, n_experts, k, sh.val, sh.cid);
 }
 
 }  // namespace mb200
