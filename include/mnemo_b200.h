@@ -136,6 +136,20 @@ size_t mb200_router_scratch_bytes(int n_experts);
 int mb200_router_topk(const float *router_w, const float *x, void *scratch, int *indices,
                       float *weights, int n_experts, int n_cols, int k, cudaStream_t stream);
 
+/* Same operation and results as mb200_router_topk, for callers that have no device memory to
+ * give and cannot get any: an engine that has already handed every free byte to its expert
+ * cache and KV cache at load time, or a serving loop that runs under a no-allocation rule
+ * once warm-up is over. This entry point has no counterpart in the reference. The ticket and
+ * logits live in an array inside the library image instead (about 4 KB, held on each device
+ * that loads the library until the process exits), so n_experts is limited to 1024; larger
+ * values are refused with MB200_ERR_UNSUPPORTED. Nothing is allocated or freed by the call.
+ * The first call on a device looks up the array's device address (the device must be current);
+ * make that first call before starting any stream capture. All calls on a device share the one
+ * array: calls whose kernels can overlap on the GPU (different streams) race on it -- serialise
+ * them or use mb200_router_topk with separate scratch buffers. */
+int mb200_router_topk_static(const float *router_w, const float *x, int *indices, float *weights,
+                             int n_experts, int n_cols, int k, cudaStream_t stream);
+
 /* act[s][r] = silu(gate_e[r].x) * (up_e[r].x), e = ids[s], for the n_slots routed experts;
  * act is [n_slots][EFF]. Slots with ids[s] < 0 give zeros. (src/forward.c:1128-1131 per expert.) */
 int mb200_moe_gate_up(const void *experts, size_t expert_stride, size_t gate_off, size_t up_off,

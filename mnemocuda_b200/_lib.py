@@ -38,6 +38,7 @@ SIGNATURES = {
     "mb200_matvec_q6k_scaled_add": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp]),
     "mb200_router_scratch_bytes": (_sz, [_i]),
     "mb200_router_topk": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "mb200_router_topk_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "mb200_moe_gate_up": (_i, [_vp, _sz, _sz, _sz, _vp, _i, _vp, _vp, _i, _i, _vp]),
     "mb200_moe_down": (_i, [_vp, _sz, _sz, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp]),
     "mb200_moe_block": (_i, [_vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -127,6 +127,27 @@ int launch_router(const float *router_w, const float *x, void *scratch, int *ids
     return e == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
 }
 
+// ---- scratch that lives in the library image (for mb200_router_topk_static) ----
+// Ticket word + logits, same layout as the caller-provided scratch of mb200_router_topk.
+// One copy exists on every device that loads the library, for the life of the process.
+constexpr int kStaticRouterMaxExperts = 1024;
+static __device__ __align__(256) int g_router_scratch[8 + kStaticRouterMaxExperts];
+static int *g_router_scratch_ptr[64] = {nullptr};  // device address of the array, per device ordinal
+
+// The array's name is only a host-side handle; kernels need its device address, which the
+// runtime hands out per device. Looked up once per device, with that device current.
+static int *static_router_scratch()
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!g_router_scratch_ptr[dev]) {
+        int *ptr = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_router_scratch) != cudaSuccess) return nullptr;
+        g_router_scratch_ptr[dev] = ptr;
+    }
+    return g_router_scratch_ptr[dev];
+}
+
 }  // namespace mb200
 
 using namespace mb200;
@@ -141,6 +162,25 @@ int mb200_router_topk(const float *router_w, const float *x, void *scratch, int 
     if (!router_w || !x || !scratch || !indices || !weights || n_experts < 1 || n_cols < 1 || k < 1 || k > 16)
         return MB200_ERR_ARG;
     if (reinterpret_cast<uintptr_t>(scratch) & 15) return MB200_ERR_ARG;
+    return launch_router(router_w, x, scratch, indices, weights, n_experts, n_cols, k, stream);
+}
+
+int mb200_router_topk_static(const float *router_w, const float *x, int *indices, float *weights, int n_experts,
+                             int n_cols, int k, cudaStream_t stream)
+{
+    if (!router_w || !x || !indices || !weights || n_experts < 1 || n_cols < 1 || k < 1 || k > 16) return MB200_ERR_ARG;
+    if (n_experts > kStaticRouterMaxExperts) {
+        fprintf(stderr, "[mnemo_b200] mb200_router_topk_static: n_experts=%d exceeds the built-in scratch (max %d); "
+                        "use mb200_router_topk with caller-provided scratch\n", n_experts, kStaticRouterMaxExperts);
+        return MB200_ERR_UNSUPPORTED;
+    }
+    int *scratch = static_router_scratch();
+    if (!scratch) {
+        fprintf(stderr, "[mnemo_b200] mb200_router_topk_static: could not resolve the built-in scratch on this device\n");
+        return MB200_ERR_LAUNCH;
+    }
+    // The array keeps whatever the previous call left; the ticket must start at zero.
+    if (cudaMemsetAsync(scratch, 0, sizeof(int), stream) != cudaSuccess) return MB200_ERR_LAUNCH;
     return launch_router(router_w, x, scratch, indices, weights, n_experts, n_cols, k, stream);
 }
 

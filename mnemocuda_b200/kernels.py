@@ -147,6 +147,12 @@ def mb200_router_topk(router_w, x, scratch, indices, weights, n_experts, n_cols,
                                         n_experts, n_cols, k, _stream(stream)), "mb200_router_topk")
 
 
+def mb200_router_topk_static(router_w, x, indices, weights, n_experts, n_cols, k, stream=None):
+    """Router + top-k with the library's built-in scratch (no caller scratch, nothing allocated)."""
+    _check(_lib.lib().mb200_router_topk_static(_f32(router_w), _f32(x), _ptr(indices), _f32(weights), n_experts,
+                                               n_cols, k, _stream(stream)), "mb200_router_topk_static")
+
+
 def mb200_moe_gate_up(experts, expert_stride, gate_off, up_off, ids, n_slots, x, act, EFF, H, stream=None):
     _check(_lib.lib().mb200_moe_gate_up(_ptr(experts), expert_stride, gate_off, up_off, _ptr(ids), n_slots,
                                         _f32(x), _f32(act), EFF, H, _stream(stream)), "mb200_moe_gate_up")
