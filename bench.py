@@ -37,7 +37,7 @@ WORKLOAD = ("configs[1]: MoE expert block, batch 1, Qwen3-235B shape -- router f
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one routed gate/up launch (8 experts, 56 623 104
 # algorithmic bytes), from the ncu capture summarised in profiles/; None until captured.
-GATE_UP_TRAFFIC_BYTES = None
+GATE_UP_TRAFFIC_BYTES = 56726784 + 569088  # profiles/moe_block_stream_kernels_ncu.md
 
 
 def measured_peaks():
@@ -195,7 +195,13 @@ def run_ours(args):
 
     shape = MoEShape()
     layers = args.layers
-    moe = ResidentMoE(shape, layers, dev, seed=1)
+    if world > 1:
+        # expert-sharded: this rank holds experts [lo, hi) of every layer; the router is replicated
+        from mnemocuda_b200.sharded import ShardedMoE, expert_range
+        moe = ResidentMoE(shape, layers, dev, seed=1, expert_range=expert_range(shape.NE, world, rank))
+        smoe = ShardedMoE(moe, rank, world)
+    else:
+        moe = ResidentMoE(shape, layers, dev, seed=1)
     K.mb200_set_pdl(not args.no_pdl)
     H = shape.H
     xs = torch.empty(layers, H, device=dev)
@@ -229,21 +235,49 @@ def run_ours(args):
         return e0.elapsed_time(e1) / steps
 
     # ---- device-resident: the whole block, K steps in one graph ----
-    block = lambda i: moe.forward(i % layers, xs[i % layers], rs[i % layers], outs[i % layers])
+    if world > 1:
+        block = lambda i: smoe.forward(i % layers, xs[i % layers], rs[i % layers], outs[i % layers])
+    else:
+        block = lambda i: moe.forward(i % layers, xs[i % layers], rs[i % layers], outs[i % layers])
+
+    def timed_eager(fn, steps, warmup):
+        for i in range(warmup):
+            fn(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1) / steps
+
+    timing_how = "CUDA events around one CUDA graph of the timed steps"
     with ClockSampler(local) as clk:
-        ms = timed_graph(block, args.steps, args.warmup)
+        try:
+            ms = timed_graph(block, args.steps, args.warmup)
+        except Exception as exc:  # a collective that cannot be captured: time the eager loop instead
+            if world == 1:
+                raise
+            torch.cuda.synchronize()
+            timing_how = f"CUDA events around the eager loop (graph capture failed: {type(exc).__name__})"
+            ms = timed_eager(block, args.steps, args.warmup)
         # ---- dominant kernel alone (ids already routed by the runs above) ----
-        gu_ms = timed_graph(lambda i: moe.gate_up(i % layers, xs[i % layers]), args.steps, args.warmup)
-        dn_ms = timed_graph(lambda i: moe.down(i % layers, rs[i % layers], outs[i % layers]), args.steps, args.warmup)
-        rt_ms = timed_graph(lambda i: moe.route(i % layers, xs[i % layers]), args.steps, args.warmup)
+        if world == 1:
+            gu_ms = timed_graph(lambda i: moe.gate_up(i % layers, xs[i % layers]), args.steps, args.warmup)
+            dn_ms = timed_graph(lambda i: moe.down(i % layers, rs[i % layers], outs[i % layers]), args.steps, args.warmup)
+            rt_ms = timed_graph(lambda i: moe.route(i % layers, xs[i % layers]), args.steps, args.warmup)
+        else:
+            gu_ms = dn_ms = rt_ms = None
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    value = shape.algorithmic_bytes * world / (ms * 1e-3) / 1e9
+    # N > 1 shards ONE block over the GPUs (strong scaling): the job's bytes per step stay those of one block
+    value = shape.algorithmic_bytes / (ms * 1e-3) / 1e9
 
     # ---- end to end through host buffers ----
-    host_block = HostMoEBlock(moe)
+    host_block = HostMoEBlock(moe, smoe if world > 1 else None)
     hx = torch.randn(layers, H).pin_memory()
     hr = torch.randn(layers, H).pin_memory()
     ho = torch.empty(layers, H).pin_memory()
@@ -262,7 +296,7 @@ def run_ours(args):
         t = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
-    e2e_value = shape.algorithmic_bytes * world / (e2e_ms * 1e-3) / 1e9
+    e2e_value = shape.algorithmic_bytes / (e2e_ms * 1e-3) / 1e9
 
     err = K.mb200_device_error()
     if err != 0:
@@ -275,25 +309,27 @@ def run_ours(args):
 
     peak, which = measured_peaks()
     gu_bytes = shape.K * (shape.gate_sz + shape.up_sz) + shape.H * 4 + shape.K * shape.EFF * 4
-    achieved = gu_bytes / (gu_ms * 1e-3) / 1e9
+    achieved = gu_bytes / (gu_ms * 1e-3) / 1e9 if gu_ms else None
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
         "dtype": "int8 dot (u8 x s8 dp4a), fp32 accumulate", "data": "synthetic",
         "config": {"workload": WORKLOAD, "layers_resident": layers, "resident_GB": round(moe.experts.numel() / 1e9, 2),
                    "l2": "inputs larger than L2: steps rotate over resident layers, 1.57 GB of experts each",
-                   "timing": "CUDA events around one CUDA graph of the timed steps", "pdl": not args.no_pdl,
-                   "parallelism": "independent replicas per GPU" if world > 1 else "single GPU"},
+                   "timing": timing_how, "pdl": not args.no_pdl,
+                   "parallelism": (f"experts sharded {world}-way (router replicated), NCCL all-reduce of the 16 KB partial hidden vector"
+                                   if world > 1 else "single GPU")},
         "clocks": clk.summary(),
         "gpu_launches": 3 * args.steps,
         "kernels_ms": {"router_topk": rt_ms, "moe_gate_up": gu_ms, "moe_down": dn_ms},
-        "roofline": {"bound": "hbm", "kernel": "stream_kernel<Q4,*> (routed gate/up + SwiGLU, 8 experts per launch)",
+    }
+    if world == 1:
+        line["roofline"] = {"bound": "hbm", "kernel": "stream_kernel<Q4,*> (routed gate/up + SwiGLU, 8 experts per launch)",
                      "achieved": achieved, "peak": peak, "peak_source": which + " copy bandwidth (MEASURED_PEAKS.json)",
                      "unit": "GB/s", "frac": achieved / peak, "frac_of_8TBs_nominal": achieved / 8000.0,
-                     "algorithmic_bytes_per_launch": gu_bytes, "traffic": GATE_UP_TRAFFIC_BYTES},
-        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": host_block.h2d_bytes,
-                "d2h_bytes_per_step": host_block.d2h_bytes},
-    }
+                     "algorithmic_bytes_per_launch": gu_bytes, "traffic": GATE_UP_TRAFFIC_BYTES}
+    line["e2e"] = {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": host_block.h2d_bytes,
+                   "d2h_bytes_per_step": host_block.d2h_bytes}
     if world == 1 and not args.no_cpu_baseline:
         experts_host = moe.experts[0].reshape(-1).cpu().numpy()
         router_host = moe.router[0].reshape(-1).cpu().numpy()

@@ -151,7 +151,7 @@ int mb200_router_topk_static(const float *router_w, const float *x, int *indices
                              int n_experts, int n_cols, int k, cudaStream_t stream);
 
 /* act[s][r] = silu(gate_e[r].x) * (up_e[r].x), e = ids[s], for the n_slots routed experts;
- * act is [n_slots][EFF]. Slots with ids[s] < 0 give zeros. (src/forward.c:1128-1131 per expert.) */
+ * act is [n_slots][EFF]. Slots with ids[s] < 0 are skipped (their rows of act are not written). (src/forward.c:1128-1131 per expert.) */
 int mb200_moe_gate_up(const void *experts, size_t expert_stride, size_t gate_off, size_t up_off,
                       const int *ids, int n_slots, const float *x, float *act, int EFF, int H,
                       cudaStream_t stream);
@@ -162,6 +162,20 @@ int mb200_moe_gate_up(const void *experts, size_t expert_stride, size_t gate_off
 int mb200_moe_down(const void *experts, size_t expert_stride, size_t down_off, int down_type,
                    const int *ids, const float *wts, int n_slots, const float *act,
                    const float *residual, float *y, int H, int EFF, cudaStream_t stream);
+
+/* Expert-sharded forms (this replaces the reference's layer-split hand-off, src/engine.c:761-775,
+ * src/forward.c:1555-1581): the device holds experts [expert_lo, expert_lo + expert_cnt) of the
+ * layer, `experts` points at expert_lo's blob, and routed slots whose id falls outside that range
+ * are skipped without reading anything. ids are the router's global ids (the router is replicated).
+ * mb200_moe_down_local adds only the local experts; the caller sums the partial results of all
+ * devices (NCCL all-reduce) -- pass the residual on one device and NULL with a zeroed y elsewhere. */
+int mb200_moe_gate_up_local(const void *experts, size_t expert_stride, size_t gate_off, size_t up_off,
+                            const int *ids, int n_slots, int expert_lo, int expert_cnt, const float *x,
+                            float *act, int EFF, int H, cudaStream_t stream);
+int mb200_moe_down_local(const void *experts, size_t expert_stride, size_t down_off, int down_type,
+                         const int *ids, const float *wts, int n_slots, int expert_lo, int expert_cnt,
+                         const float *act, const float *residual, float *y, int H, int EFF,
+                         cudaStream_t stream);
 
 /* The three calls in sequence. ids/wts: [k]; act: [k][EFF]; scratch as for mb200_router_topk. */
 int mb200_moe_block(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz,

@@ -41,6 +41,8 @@ SIGNATURES = {
     "mb200_router_topk_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "mb200_moe_gate_up": (_i, [_vp, _sz, _sz, _sz, _vp, _i, _vp, _vp, _i, _i, _vp]),
     "mb200_moe_down": (_i, [_vp, _sz, _sz, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp]),
+    "mb200_moe_gate_up_local": (_i, [_vp, _sz, _sz, _sz, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp]),
+    "mb200_moe_down_local": (_i, [_vp, _sz, _sz, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp]),
     "mb200_moe_block": (_i, [_vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mb200_fill_q4k": (_i, [_vp, _sz, _u64, _vp]),
     "mb200_fill_q6k": (_i, [_vp, _sz, _u64, _vp]),

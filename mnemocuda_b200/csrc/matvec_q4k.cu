@@ -97,7 +97,8 @@ void q4k_init() { stream::init_attrs<Q4>(); }
 int pdl_enabled() { return stream::pdl_mode(); }
 
 void moe_gate_up_q4k(const void *experts, size_t stride, size_t gate_off, size_t up_off, const int *ids, int n_slots,
-                     const float *x, float *act, int EFF, int H, cudaStream_t stream, const char *where)
+                     int expert_lo, int expert_cnt, const float *x, float *act, int EFF, int H, cudaStream_t stream,
+                     const char *where)
 {
     Params P{};
     P.seg[0].y = act;
@@ -111,13 +112,15 @@ void moe_gate_up_q4k(const void *experts, size_t stride, size_t gate_off, size_t
     P.off_a = gate_off;
     P.off_b = up_off;
     P.n_slots = n_slots;
+    P.expert_lo = expert_lo;
+    P.expert_cnt = expert_cnt;
     P.erows = EFF;
     stream::launch<Q4>(P, stream, where);
 }
 
 void moe_down_q4k(const void *experts, size_t stride, size_t down_off, const int *ids, const float *wts, int n_slots,
-                  const float *act, const float *residual, float *y, int H, int EFF, cudaStream_t stream,
-                  const char *where)
+                  int expert_lo, int expert_cnt, const float *act, const float *residual, float *y, int H, int EFF,
+                  cudaStream_t stream, const char *where)
 {
     Params P{};
     P.seg[0].y = y;
@@ -133,6 +136,8 @@ void moe_down_q4k(const void *experts, size_t stride, size_t down_off, const int
     P.estride = stride;
     P.off_a = down_off;
     P.n_slots = n_slots;
+    P.expert_lo = expert_lo;
+    P.expert_cnt = expert_cnt;
     P.erows = H;
     stream::launch<Q4>(P, stream, where);
 }

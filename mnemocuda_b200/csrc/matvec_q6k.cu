@@ -141,8 +141,8 @@ using stream::Params;
 void q6k_init() { stream::init_attrs<Q6>(); }
 
 void moe_down_q6k(const void *experts, size_t stride, size_t down_off, const int *ids, const float *wts, int n_slots,
-                  const float *act, const float *residual, float *y, int H, int EFF, cudaStream_t stream,
-                  const char *where)
+                  int expert_lo, int expert_cnt, const float *act, const float *residual, float *y, int H, int EFF,
+                  cudaStream_t stream, const char *where)
 {
     Params P{};
     P.seg[0].y = y;
@@ -158,6 +158,8 @@ void moe_down_q6k(const void *experts, size_t stride, size_t down_off, const int
     P.estride = stride;
     P.off_a = down_off;
     P.n_slots = n_slots;
+    P.expert_lo = expert_lo;
+    P.expert_cnt = expert_cnt;
     P.erows = H;
     stream::launch<Q6>(P, stream, where);
 }

@@ -17,13 +17,14 @@
 namespace mb200 {
 
 void moe_gate_up_q4k(const void *experts, size_t stride, size_t gate_off, size_t up_off, const int *ids, int n_slots,
-                     const float *x, float *act, int EFF, int H, cudaStream_t stream, const char *where);
+                     int expert_lo, int expert_cnt, const float *x, float *act, int EFF, int H, cudaStream_t stream,
+                     const char *where);
 void moe_down_q4k(const void *experts, size_t stride, size_t down_off, const int *ids, const float *wts, int n_slots,
-                  const float *act, const float *residual, float *y, int H, int EFF, cudaStream_t stream,
-                  const char *where);
+                  int expert_lo, int expert_cnt, const float *act, const float *residual, float *y, int H, int EFF,
+                  cudaStream_t stream, const char *where);
 void moe_down_q6k(const void *experts, size_t stride, size_t down_off, const int *ids, const float *wts, int n_slots,
-                  const float *act, const float *residual, float *y, int H, int EFF, cudaStream_t stream,
-                  const char *where);
+                  int expert_lo, int expert_cnt, const float *act, const float *residual, float *y, int H, int EFF,
+                  cudaStream_t stream, const char *where);
 int pdl_enabled();
 
 namespace {
@@ -184,13 +185,41 @@ int mb200_router_topk_static(const float *router_w, const float *x, int *indices
     return launch_router(router_w, x, scratch, indices, weights, n_experts, n_cols, k, stream);
 }
 
+int mb200_moe_gate_up_local(const void *experts, size_t expert_stride, size_t gate_off, size_t up_off, const int *ids,
+                            int n_slots, int expert_lo, int expert_cnt, const float *x, float *act, int EFF, int H,
+                            cudaStream_t stream)
+{
+    if (!experts || !ids || !x || !act || n_slots < 1 || n_slots > 16 || EFF < 1 || H < 1 || expert_lo < 0 ||
+        expert_cnt < 0)
+        return MB200_ERR_ARG;
+    mb200_clear_status();
+    moe_gate_up_q4k(experts, expert_stride, gate_off, up_off, ids, n_slots, expert_lo, expert_cnt, x, act, EFF, H,
+                    stream, "mb200_moe_gate_up");
+    return mb200_last_status();
+}
+
 int mb200_moe_gate_up(const void *experts, size_t expert_stride, size_t gate_off, size_t up_off, const int *ids,
                       int n_slots, const float *x, float *act, int EFF, int H, cudaStream_t stream)
 {
-    if (!experts || !ids || !x || !act || n_slots < 1 || n_slots > 16 || EFF < 1 || H < 1) return MB200_ERR_ARG;
+    return mb200_moe_gate_up_local(experts, expert_stride, gate_off, up_off, ids, n_slots, 0, 0x7fffffff, x, act, EFF,
+                                   H, stream);
+}
+
+int mb200_moe_down_local(const void *experts, size_t expert_stride, size_t down_off, int down_type, const int *ids,
+                         const float *wts, int n_slots, int expert_lo, int expert_cnt, const float *act,
+                         const float *residual, float *y, int H, int EFF, cudaStream_t stream)
+{
+    if (!experts || !ids || !wts || !act || !y || n_slots < 1 || n_slots > 16 || EFF < 1 || H < 1 || expert_lo < 0 ||
+        expert_cnt < 0)
+        return MB200_ERR_ARG;
+    if (down_type != 12 && down_type != 14) return MB200_ERR_UNSUPPORTED;
     mb200_clear_status();
-    moe_gate_up_q4k(experts, expert_stride, gate_off, up_off, ids, n_slots, x, act, EFF, H, stream,
-                    "mb200_moe_gate_up");
+    if (down_type == 14)
+        moe_down_q6k(experts, expert_stride, down_off, ids, wts, n_slots, expert_lo, expert_cnt, act, residual, y, H,
+                     EFF, stream, "mb200_moe_down");
+    else
+        moe_down_q4k(experts, expert_stride, down_off, ids, wts, n_slots, expert_lo, expert_cnt, act, residual, y, H,
+                     EFF, stream, "mb200_moe_down");
     return mb200_last_status();
 }
 
@@ -198,16 +227,8 @@ int mb200_moe_down(const void *experts, size_t expert_stride, size_t down_off, i
                    const float *wts, int n_slots, const float *act, const float *residual, float *y, int H, int EFF,
                    cudaStream_t stream)
 {
-    if (!experts || !ids || !wts || !act || !y || n_slots < 1 || n_slots > 16 || EFF < 1 || H < 1) return MB200_ERR_ARG;
-    if (down_type != 12 && down_type != 14) return MB200_ERR_UNSUPPORTED;
-    mb200_clear_status();
-    if (down_type == 14)
-        moe_down_q6k(experts, expert_stride, down_off, ids, wts, n_slots, act, residual, y, H, EFF, stream,
-                     "mb200_moe_down");
-    else
-        moe_down_q4k(experts, expert_stride, down_off, ids, wts, n_slots, act, residual, y, H, EFF, stream,
-                     "mb200_moe_down");
-    return mb200_last_status();
+    return mb200_moe_down_local(experts, expert_stride, down_off, down_type, ids, wts, n_slots, 0, 0x7fffffff, act,
+                                residual, y, H, EFF, stream);
 }
 
 int mb200_moe_block(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz,

@@ -79,6 +79,7 @@ struct Params {
     const uint8_t *ebase;    // expert e's blob starts at ebase + e * estride
     size_t estride, off_a, off_b;  // byte offsets inside a blob: gate/up (kMoeGateUp) or down (off_a, kMoeDown)
     int n_slots, erows;      // experts per token; rows per expert tensor
+    int expert_lo, expert_cnt;  // this device holds experts [expert_lo, expert_lo + expert_cnt) at ebase; other ids are skipped
     int x_stride;            // kMoeDown: floats between the activation vectors of consecutive slots
     int n_groups;   // column groups (= partial sums per row)
     // per consumer warp: group | first column << 5 | columns v << 12 | rows per pass << 16 | index in group << 20 | warps of group << 24
@@ -89,14 +90,15 @@ struct Layout {
     int bars, xq1, xq2, xs1, xsum, x_stride, part, stages, stage_bytes, total;
 };
 
-// bars: 2 * kMaxStages mbarriers, abort flag at +120, routed ids at +128, routing weights at +192
+// bars: 2 * kMaxStages mbarriers, abort flag at +120, routed ids at +128, routing weights at +192,
+// active-slot list at +256, its length at +320
 template <class F>
 __host__ __device__ inline Layout layout(int bpr, int tile_rows_in_stage, int n_stages, int ng, int n_x)
 {
     Layout s;
     const int kpad = bpr * 256;
     int o = 0;
-    s.bars = o;  o += 256;
+    s.bars = o;  o += 384;
     const int x0 = o;
     s.xq1 = o;   o += F::kXWords * (F::kSlotsPerBlock * bpr + 1) * 4;  // [word][slot], +1 pad: conflict-free both ways
     s.xq2 = o;   o += F::kXWords * (F::kSlotsPerBlock * bpr + 1) * 4;
@@ -124,26 +126,34 @@ __device__ __forceinline__ float *seg_y(const Params &P, int i)
 
 struct Tile {
     int seg, row0, rows;  // rows per segment (a SwiGLU tile holds 2*rows rows)
+    int j;                // routed modes: position of the slot in the active list
 };
 
 // Walks the tiles of this CTA's row range [cur, end). Every role runs the same walk.
 // t.seg is the segment (plain modes) or the expert slot (routed modes).
 struct TileWalk {
-    int cur, end, e;
-    __device__ __forceinline__ void init(const Params &P)
+    int cur, end, e, n_act;
+    const int *act;  // active slots (routed modes), shared memory
+    __device__ __forceinline__ void init(const Params &P, const int *act_list, int n_active)
     {
-        cur = static_cast<int>((long long)P.vrows * blockIdx.x / gridDim.x);
-        end = static_cast<int>((long long)P.vrows * (blockIdx.x + 1) / gridDim.x);
+        act = act_list;
+        n_act = n_active;
+        const int vrows = (P.mode == kMoeGateUp) ? n_active * P.erows : P.vrows;
+        cur = static_cast<int>((long long)vrows * blockIdx.x / gridDim.x);
+        end = static_cast<int>((long long)vrows * (blockIdx.x + 1) / gridDim.x);
+        if (P.mode == kMoeDown && n_active == 0) end = cur;
         e = 0;
     }
     __device__ __forceinline__ bool next(const Params &P, Tile &t)
     {
         if (cur >= end) return false;
-        if (P.mode == kMoeDown) {  // the same rows for slot 0, 1, ... then the next rows
-            t.seg = e;
+        t.j = 0;
+        if (P.mode == kMoeDown) {  // the same rows for every active slot in turn, then the next rows
+            t.j = e;
+            t.seg = act[e];
             t.row0 = cur;
             t.rows = min(P.tile_rows, end - cur);
-            if (++e == P.n_slots) {
+            if (++e == n_act) {
                 e = 0;
                 cur += t.rows;
             }
@@ -151,8 +161,9 @@ struct TileWalk {
         }
         int seg = 0, s0 = 0, s1 = P.seg[0].rows;
         if (P.mode == kMoeGateUp) {
-            seg = cur / P.erows;
-            s0 = seg * P.erows;
+            t.j = cur / P.erows;
+            seg = act[t.j];
+            s0 = t.j * P.erows;
             s1 = s0 + P.erows;
         } else if (P.mode != kSwiGLU) {
             if (P.nseg > 1 && cur >= P.seg[1].start) {
@@ -419,6 +430,8 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
     const Layout L = layout<F>(P.bpr, stage_rows, S, NG, n_x);
     int *sid = reinterpret_cast<int *>(smem + L.bars + 128);      // routed expert per slot
     float *swt = reinterpret_cast<float *>(smem + L.bars + 192);  // routing weight per slot
+    int *act_list = reinterpret_cast<int *>(smem + L.bars + 256);  // slots this device serves, in slot order
+    int *n_act_p = reinterpret_cast<int *>(smem + L.bars + 320);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.bars);
     uint64_t *empty = full + kMaxStages;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.bars + 120);
@@ -429,7 +442,6 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
     const int part_pitch = stage_rows * NG;
 
     TileWalk walk;
-    walk.init(P);
 
 #ifdef MB200_V_NOWAIT
     if (warp >= kConsumers) {
@@ -452,12 +464,17 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
             if (routed) {
                 // which experts to stream is decided by the upstream kernel (the router): wait for it first
                 if (P.pdl) grid_dep_wait();
+                int n = 0;
                 for (int e = 0; e < P.n_slots; e++) {
                     const int id = P.ids[e];
-                    sid[e] = id;
-                    swt[e] = (id < 0 || P.wts == nullptr) ? 0.0f : P.wts[e];  // gate/up has no routing weights
+                    const bool here = id >= P.expert_lo && id - P.expert_lo < P.expert_cnt;  // empty slots have id < 0
+                    sid[e] = here ? id - P.expert_lo : -1;
+                    swt[e] = (!here || P.wts == nullptr) ? 0.0f : P.wts[e];  // gate/up has no routing weights
+                    if (here) act_list[n++] = e;
                 }
+                *n_act_p = n;
             }
+            walk.init(P, act_list, routed ? *n_act_p : 0);
             Tile t;
             for (int s = 0; s < S; s++) {
                 mbar_arrive(&full[s]);  // first phase: nothing to drain yet
@@ -487,6 +504,13 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
         // ---------------- epilogue warp ----------------
         __syncthreads();
         if (P.pdl) grid_dep_wait();  // y / residual may still be in use by the upstream kernel
+        walk.init(P, act_list, routed ? *n_act_p : 0);
+        if (P.mode == kMoeDown && walk.n_act == 0 && P.residual) {
+            // no routed expert lives on this device: the block reduces to the residual
+            const int r0 = static_cast<int>((long long)P.vrows * blockIdx.x / gridDim.x);
+            const int r1 = static_cast<int>((long long)P.vrows * (blockIdx.x + 1) / gridDim.x);
+            for (int r = r0 + lane; r < r1; r += 32) P.seg[0].y[r] = P.residual[r];
+        }
         Tile t, ahead;
         float eacc0 = 0.0f, eacc1 = 0.0f;  // kMoeDown: per-row running sums (tiles hold at most 64 rows)
         TileWalk look = walk;
@@ -510,10 +534,10 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
                     seg_y(P, t.seg)[row] += P.scale * v;
                 } else if (P.mode == kMoeDown) {
                     // slots arrive in order 0..n_slots-1 for the same rows: keep the running sum in registers
-                    float a = (t.seg == 0) ? 0.0f : (it == 0 ? eacc0 : eacc1);
+                    float a = (t.j == 0) ? 0.0f : (it == 0 ? eacc0 : eacc1);
                     a = fmaf(swt[t.seg], v, a);
                     if (it == 0) eacc0 = a; else eacc1 = a;
-                    if (t.seg == P.n_slots - 1)
+                    if (t.j == walk.n_act - 1)
                         P.seg[0].y[row] = (P.residual ? P.residual[row] : P.seg[0].y[row]) + a;
                 } else {
                     float u = 0.0f;
@@ -522,7 +546,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
                     if (P.mode == kSwiGLU)
                         P.seg[0].y[row] = act;
                     else
-                        P.seg[0].y[t.seg * P.erows + row] = sid[t.seg] < 0 ? 0.0f : act;
+                        P.seg[0].y[t.seg * P.erows + row] = act;
                 }
             }
             __syncwarp();
@@ -546,6 +570,8 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
     } else {
         // one activation vector per slot; warps take slots round-robin so the loads of all slots are in flight together
         for (int e = warp; e < n_x; e += kConsumers) {
+            const int id = P.ids[e];
+            if (id < P.expert_lo || id - P.expert_lo >= P.expert_cnt) continue;  // not served here: its activations do not exist
             uint8_t *xb = smem + e * L.x_stride;
             quantize_x_warp<F>(P.x + (size_t)e * P.x_stride, P.n_cols, P.bpr, reinterpret_cast<uint32_t *>(xb + L.xq1),
                                reinterpret_cast<uint32_t *>(xb + L.xq2), reinterpret_cast<float *>(xb + L.xs1),
@@ -555,6 +581,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
     if (warp == 0) MB200_STAMP(1);
     __syncthreads();  // the only block-wide barrier: x is staged, barriers are initialised
     if (warp == 0) MB200_STAMP(2);
+    walk.init(P, act_list, routed ? *n_act_p : 0);
 
     // The warp's column group (host-made table).
     const uint32_t cfg = P.warp_cfg[warp];
@@ -566,7 +593,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
     const int roff = lane_ok ? q / v : 0;
     const int W = (rpp > 1) ? v * F::kLanesPerBlock : 32;
     typename F::XRegs xr;
-    F::load_xregs(xr, smem, L, P.bpr, col, sub, lane_ok);
+    if (P.mode != kMoeDown) F::load_xregs(xr, smem, L, P.bpr, col, sub, lane_ok);  // kMoeDown loads per slot
     const int unit_rows = RU * rpp;
     const uint32_t lane_base = col * F::kBlockBytes + roff * row_bytes + idx * unit_rows * row_bytes;
     const uint32_t unit_stride = cnt * unit_rows * row_bytes;
@@ -576,7 +603,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
     Tile t;
     int s = 0, ph = 0;
     int k = 0;
-    int cur_slot = 0;
+    int cur_slot = -1;
     while (walk.next(P, t)) {
         const int R = pairs ? 2 * t.rows : t.rows;
         uint32_t skew = 0;

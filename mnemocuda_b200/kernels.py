@@ -165,6 +165,20 @@ def mb200_moe_down(experts, expert_stride, down_off, down_type, ids, wts, n_slot
            "mb200_moe_down")
 
 
+def mb200_moe_gate_up_local(experts, expert_stride, gate_off, up_off, ids, n_slots, expert_lo, expert_cnt, x, act,
+                            EFF, H, stream=None):
+    _check(_lib.lib().mb200_moe_gate_up_local(_ptr(experts), expert_stride, gate_off, up_off, _ptr(ids), n_slots,
+                                              expert_lo, expert_cnt, _f32(x), _f32(act), EFF, H, _stream(stream)),
+           "mb200_moe_gate_up_local")
+
+
+def mb200_moe_down_local(experts, expert_stride, down_off, down_type, ids, wts, n_slots, expert_lo, expert_cnt, act,
+                         residual, y, H, EFF, stream=None):
+    _check(_lib.lib().mb200_moe_down_local(_ptr(experts), expert_stride, down_off, down_type, _ptr(ids), _f32(wts),
+                                           n_slots, expert_lo, expert_cnt, _f32(act), _ptr(residual), _f32(y), H, EFF,
+                                           _stream(stream)), "mb200_moe_down_local")
+
+
 def mb200_moe_block(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts, k, H, EFF, x, residual,
                     out, ids, wts, act, scratch, stream=None):
     _check(_lib.lib().mb200_moe_block(_f32(router_w), _ptr(experts), expert_stride, gate_sz, up_sz, down_type,

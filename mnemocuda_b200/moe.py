@@ -87,8 +87,9 @@ class HostMoEBlock:
     Copies x and the residual from pinned host memory, runs the block, copies the result back
     and waits for it (the reference's engine does the same per token for the logits)."""
 
-    def __init__(self, moe: ResidentMoE):
+    def __init__(self, moe: ResidentMoE, sharded=None):
         self.moe = moe
+        self.sharded = sharded  # a sharded.ShardedMoE when the experts are split over several GPUs
         H = moe.shape.H
         self.x = torch.empty(H, dtype=torch.float32, device=moe.device)
         self.res = torch.empty(H, dtype=torch.float32, device=moe.device)
@@ -99,6 +100,9 @@ class HostMoEBlock:
     def __call__(self, layer: int, x_host: torch.Tensor, res_host: torch.Tensor, out_host: torch.Tensor) -> None:
         self.x.copy_(x_host, non_blocking=True)
         self.res.copy_(res_host, non_blocking=True)
-        self.moe.forward(layer, self.x, self.res, self.out)
+        if self.sharded is not None:
+            self.sharded.forward(layer, self.x, self.res, self.out)
+        else:
+            self.moe.forward(layer, self.x, self.res, self.out)
         out_host.copy_(self.out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
