@@ -183,6 +183,17 @@ int mb200_moe_block(const float *router_w, const void *experts, size_t expert_st
                     const float *x, const float *residual, float *out, int *ids, float *wts,
                     float *act, void *scratch, cudaStream_t stream);
 
+/* ---- prefill GEMM on tcgen05 tensor cores ----
+ * out[t][n] = sum_k f16(X[t][k]) * dequant(W)[n][k]; X fp16 [M x K] row-major (16-byte aligned),
+ * W Q4_K / Q6_K [N x K] as for the matvecs, out fp32 [M x N]; K a multiple of 256. Weights are
+ * dequantised in fp32 and rounded to fp16 for the tensor core, accumulation is fp32.
+ * The reference's counterpart is its int8 mma.sync experiment (src/gemm_q4k.cu:272-324, used at
+ * batch 1 only, src/forward.c:683-698); prefill proper is token-serial there (src/forward.c:1783-1830). */
+int mb200_gemm_q4k_f16(const void *w, const void *x_f16, float *out, int M, int N, int K,
+                       cudaStream_t stream);
+int mb200_gemm_q6k_f16(const void *w, const void *x_f16, float *out, int M, int N, int K,
+                       cudaStream_t stream);
+
 /* Seeded synthetic tensors written on the device (benchmark workloads). */
 int mb200_fill_q4k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream);
 int mb200_fill_q6k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream);

@@ -9,6 +9,7 @@ namespace mb200 {
 
 void q4k_init();
 void q6k_init();
+void gemm_init();
 
 namespace {
 int g_status = MB200_OK;
@@ -54,6 +55,7 @@ void cuda_kernels_init(void)
 {
     q4k_init();
     q6k_init();
+    gemm_init();
     (void)device_error_word();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {

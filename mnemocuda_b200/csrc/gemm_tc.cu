@@ -1,0 +1,403 @@
+// Prefill GEMM on 5th-generation tensor cores (tcgen05 + TMEM), sm_100a:
+//     out[t][n] = sum_k  f16(X[t][k]) * dequant(W)[n][k]        X: fp16 [M x K], W: Q4_K or Q6_K [N x K], out: fp32 [M x N]
+//
+// The reference's "tensor-core GEMM" (src/gemm_q4k.cu:201-266) is an int8 mma.sync experiment that
+// quantises activations to Q8_1 and is only ever run at batch 1; its numerics are not validated.
+// The semantics implemented here are the ones the reference's dequant defines: fp32 dequant(W),
+// fp16 activations, fp32 accumulation (W rounded to fp16 for the tensor core: 2.8e-4 relative L2).
+//
+// Mapping. The weight rows are the UMMA M dimension (128 rows per CTA), the tokens the UMMA N
+// dimension (256 per CTA), K is walked in chunks of 64 (one 128-byte swizzle row of fp16):
+//   D[n (128 TMEM lanes)][t (256 TMEM columns)] += A[n][k] * B[t][k]
+//   * B (activations) arrives by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast);
+//   * A (weights) is produced in the kernel: 8 warps read the raw GGUF blocks from global memory,
+//     rebuild w = d*sc*q - dmin*m (Q4_K) / d*sc*(q-32) (Q6_K) in fp32, round to fp16 and store
+//     the tile in the same K-major 128-byte-swizzled layout TMA would have produced;
+//   * one elected thread issues tcgen05.mma (kind::f16, M128 N256 K16), accumulators live in
+//     TMEM (256 columns), tcgen05.commit signals the stage free / the accumulator complete;
+//   * 4 warps read the accumulator back with tcgen05.ld and store out[t][n] (coalesced over n).
+// 4-stage ring (48 KB per stage); every mbarrier wait is bounded; TMEM is always released.
+#include <cuda.h>
+
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace mb200 {
+namespace {
+
+constexpr int kBN = 128;   // weight rows per CTA (UMMA M)
+constexpr int kBT = 256;   // tokens per CTA (UMMA N)
+constexpr int kBK = 64;    // K per stage: 64 fp16 = one 128-byte swizzle row
+constexpr int kStages = 4;
+constexpr int kDequantWarps = 8;
+constexpr int kThreads = (2 + kDequantWarps) * 32;  // warp 0: TMA, warp 1: MMA + TMEM, warps 2..9: dequant (+ epilogue)
+constexpr int kABytes = kBN * kBK * 2;               // 16 KB
+constexpr int kBBytes = kBT * kBK * 2;               // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kTmemCols = 256;
+
+// ---- tcgen05 / TMA wrappers ---------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void proxy_fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, "
+        "[%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *map, int x, int y, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes, 8-row
+// groups 1024 bytes apart (SBO); the tile base is 1024-byte aligned (base offset 0).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+    d |= static_cast<uint64_t>(1) << 16;                  // leading-dimension offset: unused for swizzled K-major
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;          // stride-dimension offset
+    d |= static_cast<uint64_t>(1) << 46;                  // descriptor version (sm_100)
+    d |= static_cast<uint64_t>(2) << 61;                  // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: fp16 x fp16 -> fp32, both operands K-major, M = kBN, N = kBT.
+constexpr uint32_t kIdesc = (1u << 4) | (static_cast<uint32_t>(kBT >> 3) << 17) | (static_cast<uint32_t>(kBN >> 4) << 24);
+
+struct GemmParams {
+    const uint8_t *w;
+    float *out;
+    int M, N, K, bpr;
+    int q6;  // 0: Q4_K, 1: Q6_K
+    int *err;
+};
+
+// ---- one thread's 32 weights of a 64-wide K chunk, as fp32 ----------------------
+// Q4_K: thread (row, h): chunk c of block b holds qs[32c..32c+31]; low nibbles are k-local 0..31
+// (sub-block 2c), high nibbles 32..63 (sub-block 2c+1)  (reference src/kernels.cu:114-136).
+__device__ __forceinline__ void dequant32_q4k(const uint8_t *blk, int c, int h, float (&wv)[32])
+{
+    const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
+    const uint4 q0 = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 32 * c));
+    const uint4 q1 = __ldg(reinterpret_cast<const uint4 *>(blk + 32 + 32 * c));
+    uint32_t sc2, m2;
+    q4k_scale_pair(hdr.y, hdr.z, hdr.w, c, sc2, m2);
+    const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
+    const float sc = static_cast<float>(h ? (sc2 >> 8) : (sc2 & 0xFFu));
+    const float mn = static_cast<float>(h ? (m2 >> 8) : (m2 & 0xFFu));
+    // nibble n placed at mantissa bits 19..22 of 1.0f gives v = 1 + n/16 without an int->float convert:
+    // w = d*sc*n - dmin*m = (16*d*sc) * v - (16*d*sc + dmin*m)
+    const float a = 16.0f * (dd.x * sc);
+    const float b = -(a + dd.y * mn);
+    const uint32_t qs[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const uint32_t word = h ? (qs[i] >> 4) : qs[i];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const uint32_t bits = (((word >> (8 * k)) & 0xFu) << 19) | 0x3F800000u;
+            wv[4 * i + k] = fmaf(a, __uint_as_float(bits), b);
+        }
+    }
+}
+
+// Q6_K: a 64-wide K chunk c (0..3) of block b covers half hh = c >> 1 and sixteen-groups
+// g = 2*(c&1) + {0,1} of that half... in value order: values 128hh + 32g + l. Thread h takes
+// group g = 2*(c&1) + h, i.e. k-local 32h + l, l = 0..31  (reference src/kernels.cu:455-484).
+__device__ __forceinline__ void dequant32_q6k(const uint8_t *blk, int c, int h, float (&wv)[32])
+{
+    const int hh = c >> 1, g = 2 * (c & 1) + h;
+    const uint8_t *ql = blk + 64 * hh + 32 * (g & 1);  // 2-byte aligned only
+    const uint8_t *qh = blk + 128 + 32 * hh;
+    const int8_t *scs = reinterpret_cast<const int8_t *>(blk + 192 + 8 * hh + 2 * g);
+    const unsigned short dbits = __ldg(reinterpret_cast<const unsigned short *>(blk + 208));
+    const float d = __half2float(__ushort_as_half(dbits));
+    const float s0 = d * static_cast<float>(__ldg(scs)), s1 = d * static_cast<float>(__ldg(scs + 1));
+    const int lo_shift = 4 * (g >> 1), hi_shift = 2 * g;
+#pragma unroll
+    for (int l2 = 0; l2 < 16; l2++) {
+        const unsigned short a = __ldg(reinterpret_cast<const unsigned short *>(ql + 2 * l2));
+        const unsigned short b = __ldg(reinterpret_cast<const unsigned short *>(qh + 2 * l2));
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            const int l = 2 * l2 + e;
+            const int lo4 = ((a >> (8 * e)) >> lo_shift) & 0xF;
+            const int hi2 = ((b >> (8 * e)) >> hi_shift) & 3;
+            const int q = ((hi2 << 4) | lo4) - 32;
+            wv[l] = (l < 16 ? s0 : s1) * static_cast<float>(q);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap,
+                                                               const __grid_constant__ GemmParams P)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t *stage_base = smem;                                    // kStages x (A 16 KB | B 32 KB), 1024-byte aligned
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes);
+    uint64_t *empty = full + kStages;
+    uint64_t *acc_full = empty + kStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n0 = blockIdx.x * kBN;  // first weight row of this CTA
+    const int t0 = blockIdx.y * kBT;  // first token
+    const int n_kb = P.K / kBK;
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&full[s], kDequantWarps + 1);  // 8 dequant warps + the TMA thread's expect_tx arrival
+            mbar_init(&empty[s], 1);                 // tcgen05.commit
+        }
+        mbar_init(acc_full, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer: activations ----------------
+        if (lane == 0) {
+            int s = 0, ph = 0;
+            for (int kb = 0; kb < n_kb; kb++) {
+                if (kb >= kStages && !mbar_wait(&empty[s], ph ^ 1)) {
+                    *abort_flag = 1;
+                    break;
+                }
+                uint8_t *b_tile = stage_base + s * kStageBytes + kABytes;
+                mbar_expect_tx(&full[s], kBBytes);
+                tma_load_2d(b_tile, &xmap, kb * kBK, t0, &full[s]);
+                if (++s == kStages) {
+                    s = 0;
+                    ph ^= 1;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int s = 0, ph = 0;
+            for (int kb = 0; kb < n_kb; kb++) {
+                if (!mbar_wait(&full[s], ph)) {
+                    *abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(stage_base + s * kStageBytes);
+                const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kABytes);
+#pragma unroll
+                for (int kk = 0; kk < kBK / 16; kk++)  // 16 fp16 = 32 bytes = 2 descriptor units per K step
+                    umma_f16(tmem_base, da + 2 * kk, db + 2 * kk, kIdesc, (kb | kk) != 0);
+                umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+                if (++s == kStages) {
+                    s = 0;
+                    ph ^= 1;
+                }
+            }
+            umma_commit(acc_full);  // all MMAs done: the accumulator is complete
+        }
+    } else {
+        // ---------------- dequant producers: weights -> fp16, swizzled K-major ----------------
+        const int dt = tid - 64;        // 0..255
+        const int r = dt >> 1, h = dt & 1;
+        const int n = n0 + r;
+        const bool row_ok = n < P.N;
+        const size_t blk_bytes = P.q6 ? kQ6KBlock : kQ4KBlock;
+        const uint8_t *row = P.w + (size_t)(row_ok ? n : 0) * P.bpr * blk_bytes;
+        int s = 0, ph = 0;
+        for (int kb = 0; kb < n_kb; kb++) {
+            float wv[32];
+            const uint8_t *blk = row + (size_t)(kb >> 2) * blk_bytes;
+            if (P.q6)
+                dequant32_q6k(blk, kb & 3, h, wv);
+            else
+                dequant32_q4k(blk, kb & 3, h, wv);
+            if (kb >= kStages && !mbar_wait(&empty[s], ph ^ 1)) *abort_flag = 1;
+            uint8_t *a_row = stage_base + s * kStageBytes + r * 128;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {  // four 16-byte chunks of 8 fp16: logical chunk 4h + j, XOR-swizzled by the row
+                uint32_t pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const __half2 hv = row_ok ? __floats2half2_rn(wv[8 * j + 2 * e], wv[8 * j + 2 * e + 1])
+                                              : __floats2half2_rn(0.0f, 0.0f);
+                    pk[e] = *reinterpret_cast<const uint32_t *>(&hv);
+                }
+                const int chunk = (4 * h + j) ^ (r & 7);
+                *reinterpret_cast<uint4 *>(a_row + chunk * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+            proxy_fence_async();  // generic-proxy stores above must be visible to the tensor core's async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);
+            if (*abort_flag) break;
+            if (++s == kStages) {
+                s = 0;
+                ph ^= 1;
+            }
+        }
+        // ---------------- epilogue: warps 2..5 own TMEM lane quarters (warp % 4) ----------------
+        if (warp < 6) {
+            const int quarter = warp & 3;  // a warp may only touch TMEM lanes 32*(warp%4) .. +31
+            if (!mbar_wait(acc_full, 0)) *abort_flag = 1;
+            tc_fence_after();
+            if (!*abort_flag) {
+                const int nrow = n0 + quarter * 32 + lane;
+#pragma unroll 1
+                for (int c0 = 0; c0 < kBT; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+                    if (nrow < P.N) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const int t = t0 + c0 + j;
+                            if (t < P.M) P.out[(size_t)t * P.N + nrow] = __uint_as_float(v[j]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+    if (tid == 0 && *abort_flag) atomicExch(P.err, MB200_ERR_TIMEOUT);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+int launch_gemm(const void *w, const void *x_f16, float *out, int M, int N, int K, int q6, cudaStream_t stream,
+                const char *where)
+{
+    if (!w || !x_f16 || !out || M < 1 || N < 1 || K < 1) return MB200_ERR_ARG;
+    if (K % 256 != 0) {
+        fprintf(stderr, "[mnemo_b200] %s: K=%d must be a multiple of 256\n", where, K);
+        return MB200_ERR_UNSUPPORTED;
+    }
+    if ((reinterpret_cast<uintptr_t>(x_f16) & 15) || (!q6 && (reinterpret_cast<uintptr_t>(w) & 15)) ||
+        (q6 && (reinterpret_cast<uintptr_t>(w) & 1)))
+        return MB200_ERR_ARG;
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) {
+        fprintf(stderr, "[mnemo_b200] %s: cuTensorMapEncodeTiled is not available\n", where);
+        return MB200_ERR_LAUNCH;
+    }
+    CUtensorMap xmap;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+    const cuuint32_t box[2] = {kBK, kBT};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x_f16), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+        fprintf(stderr, "[mnemo_b200] %s: tensor map for X could not be encoded\n", where);
+        return MB200_ERR_ARG;
+    }
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        attr_done = true;
+    }
+    GemmParams P{};
+    P.w = static_cast<const uint8_t *>(w);
+    P.out = out;
+    P.M = M;
+    P.N = N;
+    P.K = K;
+    P.bpr = K / 256;
+    P.q6 = q6;
+    P.err = device_error_word();
+    const dim3 grid((N + kBN - 1) / kBN, (M + kBT - 1) / kBT);
+    gemm_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(xmap, P);
+    return cudaGetLastError() == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
+}
+
+}  // namespace
+
+void gemm_init()
+{
+    cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    (void)encode_tiled();
+}
+
+}  // namespace mb200
+
+using namespace mb200;
+
+extern "C" {
+
+int mb200_gemm_q4k_f16(const void *w, const void *x_f16, float *out, int M, int N, int K, cudaStream_t stream)
+{
+    return launch_gemm(w, x_f16, out, M, N, K, 0, stream, "mb200_gemm_q4k_f16");
+}
+
+int mb200_gemm_q6k_f16(const void *w, const void *x_f16, float *out, int M, int N, int K, cudaStream_t stream)
+{
+    return launch_gemm(w, x_f16, out, M, N, K, 1, stream, "mb200_gemm_q6k_f16");
+}
+
+}  // extern "C"

@@ -186,6 +186,20 @@ def mb200_moe_block(router_w, experts, expert_stride, gate_sz, up_sz, down_type,
                                       _f32(wts), _f32(act), _ptr(scratch), _stream(stream)), "mb200_moe_block")
 
 
+def mb200_gemm_q4k_f16(w, x_f16, out, M, N, K_, stream=None):
+    if x_f16.dtype != torch.float16:
+        raise TypeError("x must be float16")
+    _check(_lib.lib().mb200_gemm_q4k_f16(_ptr(w), _ptr(x_f16), _f32(out), M, N, K_, _stream(stream)),
+           "mb200_gemm_q4k_f16")
+
+
+def mb200_gemm_q6k_f16(w, x_f16, out, M, N, K_, stream=None):
+    if x_f16.dtype != torch.float16:
+        raise TypeError("x must be float16")
+    _check(_lib.lib().mb200_gemm_q6k_f16(_ptr(w), _ptr(x_f16), _f32(out), M, N, K_, _stream(stream)),
+           "mb200_gemm_q6k_f16")
+
+
 def mb200_fill_q4k(dst, n_blocks, seed, stream=None):
     _check(_lib.lib().mb200_fill_q4k(_ptr(dst), n_blocks, seed, _stream(stream)), "mb200_fill_q4k")
 
