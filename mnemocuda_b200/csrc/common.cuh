@@ -116,9 +116,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity)
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
 {
 #ifdef MB200_V_TESTWAIT
-    for (uint32_t i = 0; i < kWaitBudget * 16; i++) {
+    for (uint32_t i = 0; i < kWaitBudget * 64; i++) {
         if (mbar_test_wait(bar, parity)) return true;
-        __nanosleep(20);
     }
     return false;
 #else

@@ -10,12 +10,14 @@
 // dimension (256 per CTA), K is walked in chunks of 64 (one 128-byte swizzle row of fp16):
 //   D[n (128 TMEM lanes)][t (256 TMEM columns)] += A[n][k] * B[t][k]
 //   * B (activations) arrives by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast);
-//   * A (weights) is produced in the kernel: 8 warps read the raw GGUF blocks from global memory,
+//   * A (weights) is produced in the kernel: two groups of 8 warps (even / odd K chunks, so one
+//     group's latency hides behind the other's) read the raw GGUF blocks from global memory,
 //     rebuild w = d*sc*q - dmin*m (Q4_K) / d*sc*(q-32) (Q6_K) in fp32, round to fp16 and store
 //     the tile in the same K-major 128-byte-swizzled layout TMA would have produced;
 //   * one elected thread issues tcgen05.mma (kind::f16, M128 N256 K16), accumulators live in
 //     TMEM (256 columns), tcgen05.commit signals the stage free / the accumulator complete;
-//   * 4 warps read the accumulator back with tcgen05.ld and store out[t][n] (coalesced over n).
+//   * the 16 producer warps read the accumulator back with tcgen05.ld and store out[t][n]
+//     (coalesced over n).
 // 4-stage ring (48 KB per stage); every mbarrier wait is bounded; TMEM is always released.
 #include <cuda.h>
 
@@ -30,8 +32,8 @@ constexpr int kBN = 128;   // weight rows per CTA (UMMA M)
 constexpr int kBT = 256;   // tokens per CTA (UMMA N)
 constexpr int kBK = 64;    // K per stage: 64 fp16 = one 128-byte swizzle row
 constexpr int kStages = 4;
-constexpr int kDequantWarps = 8;
-constexpr int kThreads = (2 + kDequantWarps) * 32;  // warp 0: TMA, warp 1: MMA + TMEM, warps 2..9: dequant (+ epilogue)
+constexpr int kDequantWarps = 16;
+constexpr int kThreads = (2 + kDequantWarps) * 32;  // warp 0: TMA, warp 1: MMA + TMEM, warps 2..17: dequant (+ epilogue)
 constexpr int kABytes = kBN * kBK * 2;               // 16 KB
 constexpr int kBBytes = kBT * kBK * 2;               // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
@@ -108,6 +110,10 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr)
 // Instruction descriptor: fp16 x fp16 -> fp32, both operands K-major, M = kBN, N = kBT.
 constexpr uint32_t kIdesc = (1u << 4) | (static_cast<uint32_t>(kBT >> 3) << 17) | (static_cast<uint32_t>(kBN >> 4) << 24);
 
+#ifdef MB200_TRACE
+__device__ long long g_gemm_trace[256];
+#endif
+
 struct GemmParams {
     const uint8_t *w;
     float *out;
@@ -119,56 +125,76 @@ struct GemmParams {
 // ---- one thread's 32 weights of a 64-wide K chunk, as fp32 ----------------------
 // Q4_K: thread (row, h): chunk c of block b holds qs[32c..32c+31]; low nibbles are k-local 0..31
 // (sub-block 2c), high nibbles 32..63 (sub-block 2c+1)  (reference src/kernels.cu:114-136).
-__device__ __forceinline__ void dequant32_q4k(const uint8_t *blk, int c, int h, float (&wv)[32])
+// `raw` is the whole 144-byte block in registers (header + 8 x 16 bytes of qs), fetched one block
+// ahead of its use so the global-memory latency hides behind four K chunks of work.
+struct RawQ4 {
+    uint4 hdr;
+    uint4 q[2][2];  // the two chunks of the block this producer group handles (c = grp, grp + 2), 32 bytes each
+};
+__device__ __forceinline__ void load_raw_q4k(RawQ4 &raw, const uint8_t *blk, int grp)
 {
-    const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
-    const uint4 q0 = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 32 * c));
-    const uint4 q1 = __ldg(reinterpret_cast<const uint4 *>(blk + 32 + 32 * c));
+    raw.hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const uint8_t *q = blk + 16 + 32 * (grp + 2 * i);
+        raw.q[i][0] = __ldg(reinterpret_cast<const uint4 *>(q));
+        raw.q[i][1] = __ldg(reinterpret_cast<const uint4 *>(q + 16));
+    }
+}
+// 32 weights of chunk c = grp + 2*I: low (h = 0) or high (h = 1) nibbles of its 32 bytes
+template <int I>
+__device__ __forceinline__ void dequant32_q4k(const RawQ4 &raw, int grp, int h, float (&wv)[32])
+{
+    const uint4 hdr = raw.hdr;
     uint32_t sc2, m2;
-    q4k_scale_pair(hdr.y, hdr.z, hdr.w, c, sc2, m2);
+    q4k_scale_pair(hdr.y, hdr.z, hdr.w, grp + 2 * I, sc2, m2);
     const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&hdr.x));
     const float sc = static_cast<float>(h ? (sc2 >> 8) : (sc2 & 0xFFu));
     const float mn = static_cast<float>(h ? (m2 >> 8) : (m2 & 0xFFu));
-    // nibble n placed at mantissa bits 19..22 of 1.0f gives v = 1 + n/16 without an int->float convert:
-    // w = d*sc*n - dmin*m = (16*d*sc) * v - (16*d*sc + dmin*m)
-    const float a = 16.0f * (dd.x * sc);
-    const float b = -(a + dd.y * mn);
-    const uint32_t qs[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    // A masked nibble byte dropped into byte 2 of 2.0f (0x40000000) is v = 2 + n/64 -- an int->float
+    // convert for the price of one byte permute:  w = d*sc*n - dmin*m = (64*d*sc) * v - (128*d*sc + dmin*m).
+    // The cancellation costs ~8 of fp32's 24 bits; fp16 needs 11.
+    const float a = 64.0f * (dd.x * sc);
+    const float b = -(2.0f * a + dd.y * mn);
+    const uint32_t qs[8] = {raw.q[I][0].x, raw.q[I][0].y, raw.q[I][0].z, raw.q[I][0].w,
+                            raw.q[I][1].x, raw.q[I][1].y, raw.q[I][1].z, raw.q[I][1].w};
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        const uint32_t word = h ? (qs[i] >> 4) : qs[i];
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const uint32_t bits = (((word >> (8 * k)) & 0xFu) << 19) | 0x3F800000u;
-            wv[4 * i + k] = fmaf(a, __uint_as_float(bits), b);
-        }
+        const uint32_t word = (h ? (qs[i] >> 4) : qs[i]) & 0x0F0F0F0Fu;
+        wv[4 * i + 0] = fmaf(a, __uint_as_float(__byte_perm(word, 0x40000000u, 0x7054)), b);
+        wv[4 * i + 1] = fmaf(a, __uint_as_float(__byte_perm(word, 0x40000000u, 0x7154)), b);
+        wv[4 * i + 2] = fmaf(a, __uint_as_float(__byte_perm(word, 0x40000000u, 0x7254)), b);
+        wv[4 * i + 3] = fmaf(a, __uint_as_float(__byte_perm(word, 0x40000000u, 0x7354)), b);
     }
 }
 
-// Q6_K: a 64-wide K chunk c (0..3) of block b covers half hh = c >> 1 and sixteen-groups
-// g = 2*(c&1) + {0,1} of that half... in value order: values 128hh + 32g + l. Thread h takes
-// group g = 2*(c&1) + h, i.e. k-local 32h + l, l = 0..31  (reference src/kernels.cu:455-484).
+// Q6_K: a 64-wide K chunk c (0..3) of block b covers half hh = c >> 1 and the two thirty-two-groups
+// g = 2*(c&1) + {0,1} of that half (value order 128hh + 32g + l). Thread h takes group
+// g = 2*(c&1) + h, positions l = 0..31, i.e. k-local 32h + l  (reference src/kernels.cu:455-484).
 __device__ __forceinline__ void dequant32_q6k(const uint8_t *blk, int c, int h, float (&wv)[32])
 {
     const int hh = c >> 1, g = 2 * (c & 1) + h;
     const uint8_t *ql = blk + 64 * hh + 32 * (g & 1);  // 2-byte aligned only
     const uint8_t *qh = blk + 128 + 32 * hh;
-    const int8_t *scs = reinterpret_cast<const int8_t *>(blk + 192 + 8 * hh + 2 * g);
+    const unsigned short scb = __ldg(reinterpret_cast<const unsigned short *>(blk + 192 + 8 * hh + 2 * g));
     const unsigned short dbits = __ldg(reinterpret_cast<const unsigned short *>(blk + 208));
     const float d = __half2float(__ushort_as_half(dbits));
-    const float s0 = d * static_cast<float>(__ldg(scs)), s1 = d * static_cast<float>(__ldg(scs + 1));
+    const float s0 = d * static_cast<float>(static_cast<int8_t>(scb & 0xFF));
+    const float s1 = d * static_cast<float>(static_cast<int8_t>(scb >> 8));
     const int lo_shift = 4 * (g >> 1), hi_shift = 2 * g;
+    unsigned short a[16], b[16];
+#pragma unroll
+    for (int l2 = 0; l2 < 16; l2++) {  // all loads first
+        a[l2] = __ldg(reinterpret_cast<const unsigned short *>(ql + 2 * l2));
+        b[l2] = __ldg(reinterpret_cast<const unsigned short *>(qh + 2 * l2));
+    }
 #pragma unroll
     for (int l2 = 0; l2 < 16; l2++) {
-        const unsigned short a = __ldg(reinterpret_cast<const unsigned short *>(ql + 2 * l2));
-        const unsigned short b = __ldg(reinterpret_cast<const unsigned short *>(qh + 2 * l2));
 #pragma unroll
         for (int e = 0; e < 2; e++) {
-            const int l = 2 * l2 + e;
-            const int lo4 = ((a >> (8 * e)) >> lo_shift) & 0xF;
-            const int hi2 = ((b >> (8 * e)) >> hi_shift) & 3;
-            const int q = ((hi2 << 4) | lo4) - 32;
-            wv[l] = (l < 16 ? s0 : s1) * static_cast<float>(q);
+            const int lo4 = ((a[l2] >> (8 * e)) >> lo_shift) & 0xF;
+            const int hi2 = ((b[l2] >> (8 * e)) >> hi_shift) & 3;
+            wv[2 * l2 + e] = (l2 < 8 ? s0 : s1) * static_cast<float>(((hi2 << 4) | lo4) - 32);
         }
     }
 }
@@ -186,6 +212,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#ifdef MB200_TRACE
+    const long long tr0 = clock64();
+#define GSTAMP(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) g_gemm_trace[slot] = clock64() - tr0; } while (0)
+#else
+#define GSTAMP(name) do {} while (0)
+#endif
     const int n0 = blockIdx.x * kBN;  // first weight row of this CTA
     const int t0 = blockIdx.y * kBT;  // first token
     const int n_kb = P.K / kBK;
@@ -193,7 +225,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     if (tid == 0) {
         *abort_flag = 0;
         for (int s = 0; s < kStages; s++) {
-            mbar_init(&full[s], kDequantWarps + 1);  // 8 dequant warps + the TMA thread's expect_tx arrival
+            mbar_init(&full[s], kDequantWarps / 2 + 1);  // the 8 warps of one producer group + the TMA thread's expect_tx arrival
             mbar_init(&empty[s], 1);                 // tcgen05.commit
         }
         mbar_init(acc_full, 1);
@@ -204,6 +236,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (warp <= 2) GSTAMP(warp);
 
     if (warp == 0) {
         // ---------------- TMA producer: activations ----------------
@@ -215,8 +248,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     break;
                 }
                 uint8_t *b_tile = stage_base + s * kStageBytes + kABytes;
+#ifdef MB200_V_NOTMA
+                mbar_arrive(&full[s]);
+#else
                 mbar_expect_tx(&full[s], kBBytes);
                 tma_load_2d(b_tile, &xmap, kb * kBK, t0, &full[s]);
+#endif
                 if (++s == kStages) {
                     s = 0;
                     ph ^= 1;
@@ -233,12 +270,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     break;
                 }
                 tc_fence_after();
+                if (kb >= 16 && kb < 24) GSTAMP(32 + (kb - 16) * 2);
+                if (kb == 0) GSTAMP(4);
+                if (kb == 8) GSTAMP(5);
+                if (kb == n_kb - 1) GSTAMP(6);
                 const uint32_t a_addr = smem_u32(stage_base + s * kStageBytes);
                 const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kABytes);
+#ifndef MB200_V_NOMMA
 #pragma unroll
                 for (int kk = 0; kk < kBK / 16; kk++)  // 16 fp16 = 32 bytes = 2 descriptor units per K step
                     umma_f16(tmem_base, da + 2 * kk, db + 2 * kk, kIdesc, (kb | kk) != 0);
+#endif
                 umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
+                if (kb >= 16 && kb < 24) GSTAMP(33 + (kb - 16) * 2);
                 if (++s == kStages) {
                     s = 0;
                     ph ^= 1;
@@ -248,21 +292,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         }
     } else {
         // ---------------- dequant producers: weights -> fp16, swizzled K-major ----------------
-        const int dt = tid - 64;        // 0..255
-        const int r = dt >> 1, h = dt & 1;
+        const int dt = tid - 64;        // 0..511
+        const int grp = dt >> 8;        // producer group: K chunks kb = grp, grp + 2, ...
+        const int r = (dt & 255) >> 1, h = dt & 1;  // weight row of the tile; low / high nibbles (k-local 32h ..)
         const int n = n0 + r;
         const bool row_ok = n < P.N;
         const size_t blk_bytes = P.q6 ? kQ6KBlock : kQ4KBlock;
         const uint8_t *row = P.w + (size_t)(row_ok ? n : 0) * P.bpr * blk_bytes;
-        int s = 0, ph = 0;
-        for (int kb = 0; kb < n_kb; kb++) {
-            float wv[32];
-            const uint8_t *blk = row + (size_t)(kb >> 2) * blk_bytes;
-            if (P.q6)
-                dequant32_q6k(blk, kb & 3, h, wv);
-            else
-                dequant32_q4k(blk, kb & 3, h, wv);
-            if (kb >= kStages && !mbar_wait(&empty[s], ph ^ 1)) *abort_flag = 1;
+        bool stop = false;
+        // store this thread's 32 weights of K chunk kb into the A tile of its stage and publish it
+        auto publish = [&](const float (&wv)[32], int kb) {
+            const int s = kb % kStages, use = kb / kStages;
+            if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1)) *abort_flag = 1;
             uint8_t *a_row = stage_base + s * kStageBytes + r * 128;
 #pragma unroll
             for (int j = 0; j < 4; j++) {  // four 16-byte chunks of 8 fp16: logical chunk 4h + j, XOR-swizzled by the row
@@ -279,34 +320,54 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             proxy_fence_async();  // generic-proxy stores above must be visible to the tensor core's async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[s]);
-            if (*abort_flag) break;
-            if (++s == kStages) {
-                s = 0;
-                ph ^= 1;
+            if (*abort_flag) stop = true;
+        };
+        if (P.q6) {
+            for (int kb = grp; kb < n_kb && !stop; kb += 2) {
+                float wv[32];
+                dequant32_q6k(row + (size_t)(kb >> 2) * blk_bytes, kb & 3, h, wv);
+                publish(wv, kb);
+            }
+        } else {
+            RawQ4 cur, nxt;
+            load_raw_q4k(cur, row, grp);
+            for (int b = 0; b < P.bpr && !stop; b++) {
+                if (b + 1 < P.bpr) load_raw_q4k(nxt, row + (size_t)(b + 1) * kQ4KBlock, grp);  // one block ahead
+                float wv[32];
+                dequant32_q4k<0>(cur, grp, h, wv);
+                publish(wv, 4 * b + grp);
+                if (!stop) {
+                    dequant32_q4k<1>(cur, grp, h, wv);
+                    publish(wv, 4 * b + grp + 2);
+                }
+                cur = nxt;
             }
         }
-        // ---------------- epilogue: warps 2..5 own TMEM lane quarters (warp % 4) ----------------
-        if (warp < 6) {
-            const int quarter = warp & 3;  // a warp may only touch TMEM lanes 32*(warp%4) .. +31
+        // ---------------- epilogue: every producer warp; a warp may only touch TMEM lanes 32*(warp%4).. ----------------
+        {
+            const int quarter = warp & 3;
+            const int part = (warp - 2) >> 2;  // 4 warps share a lane quarter and split the 8 column chunks
             if (!mbar_wait(acc_full, 0)) *abort_flag = 1;
             tc_fence_after();
+            if (warp == 2) GSTAMP(12);
             if (!*abort_flag) {
                 const int nrow = n0 + quarter * 32 + lane;
 #pragma unroll 1
-                for (int c0 = 0; c0 < kBT; c0 += 32) {
+                for (int c0 = part * 32; c0 < kBT; c0 += 128) {
+                    if (t0 + c0 >= P.M) break;
                     uint32_t v[32];
                     tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
                     if (nrow < P.N) {
+                        float *o = P.out + (size_t)(t0 + c0) * P.N + nrow;
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const int t = t0 + c0 + j;
-                            if (t < P.M) P.out[(size_t)t * P.N + nrow] = __uint_as_float(v[j]);
-                        }
+                        for (int j = 0; j < 32; j++)
+                            if (t0 + c0 + j < P.M) o[(size_t)j * P.N] = __uint_as_float(v[j]);
                     }
                 }
             }
         }
     }
+    if (warp == 2) GSTAMP(13);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
@@ -401,3 +462,10 @@ int mb200_gemm_q6k_f16(const void *w, const void *x_f16, float *out, int M, int 
 }
 
 }  // extern "C"
+
+#ifdef MB200_TRACE
+extern "C" void mb200_gemm_trace_read(void *dst)
+{
+    cudaMemcpyFromSymbol(dst, mb200::g_gemm_trace, sizeof(long long) * 256, 0, cudaMemcpyDeviceToDevice);
+}
+#endif
