@@ -194,6 +194,23 @@ int mb200_gemm_q4k_f16(const void *w, const void *x_f16, float *out, int M, int 
 int mb200_gemm_q6k_f16(const void *w, const void *x_f16, float *out, int M, int N, int K,
                        cudaStream_t stream);
 
+/* ---- grouped per-expert GEMM: the MoE block for a batch of tokens (prefill) ----
+ * For every token t and slot s with e = ids[t][s] >= 0:
+ *   y[t] = (residual ? residual[t] : 0) + sum_s wts[t][s] * Wdown_e . SwiGLU(Wgate_e x_t, Wup_e x_t)
+ * (the per-token sequence of src/forward.c:1122-1142 applied to a batch; the reference has no batched
+ * form: its prefill runs the decode path token by token, src/forward.c:1783-1830). The routed pairs
+ * are sorted by expert on the device, each expert's gate|up (one [2*EFF x H] Q4_K matrix) and down
+ * ([H x EFF], Q6_K = 14 or Q4_K = 12) run as tcgen05 GEMMs on its token slice in two grouped
+ * launches, slots are added in slot order. x is fp16 [M][H]; ids/wts are [M][k] on the device.
+ * workspace: mb200_moe_prefill_workspace_bytes() bytes, 256-byte aligned, contents don't matter.
+ * max_tokens_per_expert sizes the launches (0 = M, always safe); if an expert receives more tokens
+ * than that, the device error word is set (mb200_device_error) and y is incomplete. */
+size_t mb200_moe_prefill_workspace_bytes(int M, int k, int H, int EFF, int n_experts);
+int mb200_moe_prefill(const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz, int down_type,
+                      int n_experts, int k, int H, int EFF, const void *x_f16, const int *ids,
+                      const float *wts, const float *residual, float *y, int M, int max_tokens_per_expert,
+                      void *workspace, cudaStream_t stream);
+
 /* Seeded synthetic tensors written on the device (benchmark workloads). */
 int mb200_fill_q4k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream);
 int mb200_fill_q6k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream);

@@ -46,6 +46,8 @@ SIGNATURES = {
     "mb200_moe_block": (_i, [_vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mb200_gemm_q4k_f16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "mb200_gemm_q6k_f16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "mb200_moe_prefill_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "mb200_moe_prefill": (_i, [_vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
     "mb200_fill_q4k": (_i, [_vp, _sz, _u64, _vp]),
     "mb200_fill_q6k": (_i, [_vp, _sz, _u64, _vp]),
     "mb200_fill_normal_f32": (_i, [_vp, _sz, _u64, _f, _vp]),

@@ -29,16 +29,23 @@ namespace mb200 {
 namespace {
 
 constexpr int kBN = 128;   // weight rows per CTA (UMMA M)
-constexpr int kBT = 256;   // tokens per CTA (UMMA N)
+// tokens per CTA (UMMA N) is a template parameter BT: 256 for the dense GEMM, 64 for the grouped
+// per-expert form (about 32 tokens per expert in the benchmark's routing)
 constexpr int kBK = 64;    // K per stage: 64 fp16 = one 128-byte swizzle row
-constexpr int kStages = 4;
 constexpr int kDequantWarps = 16;
 constexpr int kThreads = (2 + kDequantWarps) * 32;  // warp 0: TMA, warp 1: MMA + TMEM, warps 2..17: dequant (+ epilogue)
 constexpr int kABytes = kBN * kBK * 2;               // 16 KB
-constexpr int kBBytes = kBT * kBK * 2;               // 32 KB
-constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
-constexpr int kTmemCols = 256;
+template <int BT>
+struct Cfg {
+    static constexpr int kBBytes = BT * kBK * 2;  // 32 KB (BT = 256) / 8 KB (BT = 64)
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = BT == 256 ? 4 : 8;  // 192 KB of operands in flight either way
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int kTmemCols = BT;  // power of two >= 32
+    // Instruction descriptor: fp16 x fp16 -> fp32, both operands K-major, M = kBN, N = BT.
+    static constexpr uint32_t kIdesc =
+        (1u << 4) | (static_cast<uint32_t>(BT >> 3) << 17) | (static_cast<uint32_t>(kBN >> 4) << 24);
+};
 
 // ---- tcgen05 / TMA wrappers ---------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t ncols)
@@ -107,19 +114,22 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr)
     d |= static_cast<uint64_t>(2) << 61;                  // SWIZZLE_128B
     return d;
 }
-// Instruction descriptor: fp16 x fp16 -> fp32, both operands K-major, M = kBN, N = kBT.
-constexpr uint32_t kIdesc = (1u << 4) | (static_cast<uint32_t>(kBT >> 3) << 17) | (static_cast<uint32_t>(kBN >> 4) << 24);
 
 #ifdef MB200_TRACE
 __device__ long long g_gemm_trace[256];
 #endif
 
 struct GemmParams {
-    const uint8_t *w;
-    float *out;
-    int M, N, K, bpr;
-    int q6;  // 0: Q4_K, 1: Q6_K
+    const uint8_t *w;   // dense: the matrix; grouped: expert 0's blob + offset of the matrix inside a blob
+    float *out;         // [rows of X][N]
+    int M, N, K, bpr;   // M: rows of X (dense: tokens; grouped: routed (token, expert) pairs, expert-sorted)
+    int q6;             // 0: Q4_K, 1: Q6_K
     int *err;
+    // grouped form: CTA x = expert * tiles_per_expert + row tile; the expert's tokens are rows
+    // [seg_off[e], seg_off[e] + seg_cnt[e]) of X
+    const int *seg_off, *seg_cnt;
+    int tiles_per_expert;  // 0 = dense
+    size_t expert_stride;
 };
 
 // ---- one thread's 32 weights of a 64-wide K chunk, as fp32 ----------------------
@@ -199,9 +209,13 @@ __device__ __forceinline__ void dequant32_q6k(const uint8_t *blk, int c, int h, 
     }
 }
 
+template <int BT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap,
                                                                const __grid_constant__ GemmParams P)
 {
+    using C = Cfg<BT>;
+    constexpr int kStages = C::kStages, kStageBytes = C::kStageBytes, kBBytes = C::kBBytes, kTmemCols = C::kTmemCols;
+    constexpr uint32_t kIdesc = C::kIdesc;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t *stage_base = smem;                                    // kStages x (A 16 KB | B 32 KB), 1024-byte aligned
@@ -218,8 +232,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
 #else
 #define GSTAMP(name) do {} while (0)
 #endif
-    const int n0 = blockIdx.x * kBN;  // first weight row of this CTA
-    const int t0 = blockIdx.y * kBT;  // first token
+    // dense: weight tile blockIdx.x, token tile blockIdx.y. grouped: blockIdx.x = (expert, weight tile),
+    // tokens = the expert's slice of X; a CTA whose token tile lies beyond the slice has nothing to do.
+    const int expert = P.tiles_per_expert ? blockIdx.x / P.tiles_per_expert : 0;
+    const int n0 = (P.tiles_per_expert ? blockIdx.x % P.tiles_per_expert : blockIdx.x) * kBN;  // first weight row
+    const int seg0 = P.tiles_per_expert ? P.seg_off[expert] : 0;
+    const int seg_n = P.tiles_per_expert ? P.seg_cnt[expert] : P.M;
+    if (static_cast<int>(blockIdx.y) * BT >= seg_n) return;  // before any barrier / TMEM use: uniform for the CTA
+    const int t0 = seg0 + blockIdx.y * BT;   // first row of X for this CTA
+    const int t_end = seg0 + seg_n;          // rows of X past this belong to someone else
+    const uint8_t *wbase = P.w + (size_t)expert * P.expert_stride;
     const int n_kb = P.K / kBK;
 
     if (tid == 0) {
@@ -298,7 +320,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
         const int n = n0 + r;
         const bool row_ok = n < P.N;
         const size_t blk_bytes = P.q6 ? kQ6KBlock : kQ4KBlock;
-        const uint8_t *row = P.w + (size_t)(row_ok ? n : 0) * P.bpr * blk_bytes;
+        const uint8_t *row = wbase + (size_t)(row_ok ? n : 0) * P.bpr * blk_bytes;
         bool stop = false;
         // store this thread's 32 weights of K chunk kb into the A tile of its stage and publish it
         auto publish = [&](const float (&wv)[32], int kb) {
@@ -353,15 +375,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             if (!*abort_flag) {
                 const int nrow = n0 + quarter * 32 + lane;
 #pragma unroll 1
-                for (int c0 = part * 32; c0 < kBT; c0 += 128) {
-                    if (t0 + c0 >= P.M) break;
+                for (int c0 = part * 32; c0 < BT; c0 += 128) {
+                    if (t0 + c0 >= t_end) break;
                     uint32_t v[32];
                     tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
                     if (nrow < P.N) {
                         float *o = P.out + (size_t)(t0 + c0) * P.N + nrow;
 #pragma unroll
                         for (int j = 0; j < 32; j++)
-                            if (t0 + c0 + j < P.M) o[(size_t)j * P.N] = __uint_as_float(v[j]);
+                            if (t0 + c0 + j < t_end) o[(size_t)j * P.N] = __uint_as_float(v[j]);
                     }
                 }
             }
@@ -391,6 +413,37 @@ EncodeTiledFn encode_tiled()
     return fn;
 }
 
+// X: fp16 [rows_x][K] row-major. Launches gemm_tc_kernel<BT> over grid (weight tiles [x experts], token tiles).
+template <int BT>
+int launch_gemm_bt(GemmParams &P, const void *x_f16, int rows_x, dim3 grid, cudaStream_t stream, const char *where)
+{
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) {
+        fprintf(stderr, "[mnemo_b200] %s: cuTensorMapEncodeTiled is not available\n", where);
+        return MB200_ERR_LAUNCH;
+    }
+    CUtensorMap xmap;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(P.K), static_cast<cuuint64_t>(rows_x)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(P.K) * 2};
+    const cuuint32_t box[2] = {kBK, BT};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x_f16), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+        fprintf(stderr, "[mnemo_b200] %s: tensor map for X could not be encoded\n", where);
+        return MB200_ERR_ARG;
+    }
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(gemm_tc_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BT>::kSmemBytes);
+        attr_done = true;
+    }
+    P.bpr = P.K / 256;
+    P.err = device_error_word();
+    gemm_tc_kernel<BT><<<grid, kThreads, Cfg<BT>::kSmemBytes, stream>>>(xmap, P);
+    return cudaGetLastError() == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
+}
+
 int launch_gemm(const void *w, const void *x_f16, float *out, int M, int N, int K, int q6, cudaStream_t stream,
                 const char *where)
 {
@@ -402,46 +455,130 @@ int launch_gemm(const void *w, const void *x_f16, float *out, int M, int N, int 
     if ((reinterpret_cast<uintptr_t>(x_f16) & 15) || (!q6 && (reinterpret_cast<uintptr_t>(w) & 15)) ||
         (q6 && (reinterpret_cast<uintptr_t>(w) & 1)))
         return MB200_ERR_ARG;
-    EncodeTiledFn enc = encode_tiled();
-    if (!enc) {
-        fprintf(stderr, "[mnemo_b200] %s: cuTensorMapEncodeTiled is not available\n", where);
-        return MB200_ERR_LAUNCH;
-    }
-    CUtensorMap xmap;
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
-    const cuuint32_t box[2] = {kBK, kBT};
-    const cuuint32_t estr[2] = {1, 1};
-    if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x_f16), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-        fprintf(stderr, "[mnemo_b200] %s: tensor map for X could not be encoded\n", where);
-        return MB200_ERR_ARG;
-    }
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        attr_done = true;
-    }
     GemmParams P{};
     P.w = static_cast<const uint8_t *>(w);
     P.out = out;
     P.M = M;
     P.N = N;
     P.K = K;
-    P.bpr = K / 256;
     P.q6 = q6;
-    P.err = device_error_word();
-    const dim3 grid((N + kBN - 1) / kBN, (M + kBT - 1) / kBT);
-    gemm_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(xmap, P);
-    return cudaGetLastError() == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
+    if (M <= 64)
+        return launch_gemm_bt<64>(P, x_f16, M, dim3((N + kBN - 1) / kBN, 1), stream, where);
+    return launch_gemm_bt<256>(P, x_f16, M, dim3((N + kBN - 1) / kBN, (M + 255) / 256), stream, where);
+}
+
+// ---- grouped per-expert form: the MoE block for a batch of tokens (prefill) ----------------------
+// Routed (token, slot) pairs are sorted by expert; each expert's tokens then form a contiguous
+// slice of the gathered activations and one grouped launch runs every expert's GEMM on its slice.
+constexpr int kGroupBT = 64;
+
+struct SortOut {
+    int *cnt, *off, *row_of_pair, *pair_of_row;
+};
+
+// One block. Thread e counts and then places the pairs routed to expert e, in pair order, so the
+// layout is deterministic. Pairs with id < 0 (empty slots) or id >= n_experts get row -1.
+__global__ void moe_sort_kernel(const int *__restrict__ ids, int n_pairs, int n_experts, int cap, SortOut o, int *err)
+{
+    __shared__ int s_off[1025];
+    const int e = threadIdx.x;
+    int c = 0;
+    if (e < n_experts)
+        for (int p = 0; p < n_pairs; p++) c += (ids[p] == e);
+    if (e < n_experts) {
+        o.cnt[e] = c;
+        s_off[e + 1] = c;
+        if (c > cap) atomicExch(err, MB200_ERR_UNSUPPORTED);  // more tokens on one expert than the launch was sized for
+    }
+    if (e == 0) s_off[0] = 0;
+    __syncthreads();
+    if (e == 0)
+        for (int i = 0; i < n_experts; i++) s_off[i + 1] += s_off[i];
+    __syncthreads();
+    if (e < n_experts) o.off[e] = s_off[e];
+    if (e == 0) o.off[n_experts] = s_off[n_experts];
+    if (e < n_experts) {
+        int r = s_off[e];
+        for (int p = 0; p < n_pairs; p++)
+            if (ids[p] == e) {
+                o.row_of_pair[p] = r;
+                o.pair_of_row[r] = p;
+                r++;
+            }
+    }
+    for (int p = e; p < n_pairs; p += blockDim.x)
+        if (ids[p] < 0 || ids[p] >= n_experts) o.row_of_pair[p] = -1;
+}
+
+// Xs[row] = X[token of the pair in that row]; one block per row, 16-byte copies
+__global__ void moe_gather_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ xs, const int *__restrict__ pair_of_row,
+                                  const int *__restrict__ off, int n_experts, int k, int vec_per_row)
+{
+    const int row = blockIdx.x;
+    if (row >= off[n_experts]) return;
+    const int t = pair_of_row[row] / k;
+    for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) xs[(size_t)row * vec_per_row + i] = x[(size_t)t * vec_per_row + i];
+}
+
+// act16[row][j] = fp16(silu(gate) * up * 2^-4): the 2^-4 keeps SwiGLU outputs inside fp16's range
+// (they reach ~2.5e4 with the benchmark's weights); the combine step multiplies it back exactly.
+constexpr float kActScale = 1.0f / 16.0f;
+__global__ void moe_swiglu_rows_kernel(const float *__restrict__ gu, __half *__restrict__ act, const int *__restrict__ off,
+                                       int n_experts, int EFF)
+{
+    const int row = blockIdx.x;
+    if (row >= off[n_experts]) return;
+    const float *g = gu + (size_t)row * 2 * EFF;
+    for (int j = threadIdx.x; j < EFF; j += blockDim.x) {
+        const float gv = g[j];
+        act[(size_t)row * EFF + j] = __float2half_rn(gv / (1.0f + expf(-gv)) * g[EFF + j] * kActScale);
+    }
+}
+
+// y[t] = (residual ? residual[t] : 0) + sum over slots, in slot order, of w * down-output of that pair
+__global__ void moe_combine_kernel(const float *__restrict__ dn, const int *__restrict__ row_of_pair,
+                                   const float *__restrict__ wts, const float *__restrict__ residual,
+                                   float *__restrict__ y, int k, int H)
+{
+    const int t = blockIdx.x;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < k; s++) {
+            const int row = row_of_pair[t * k + s];
+            if (row >= 0) acc = fmaf(wts[t * k + s] * (1.0f / kActScale), dn[(size_t)row * H + j], acc);
+        }
+        y[(size_t)t * H + j] = (residual ? residual[(size_t)t * H + j] : 0.0f) + acc;
+    }
+}
+
+inline size_t align_up(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+struct Workspace {
+    size_t cnt, off, row_of_pair, pair_of_row, xs, gu, act, dn, total;
+};
+Workspace workspace_layout(int M, int k, int H, int EFF, int n_experts)
+{
+    const size_t P = (size_t)M * k;
+    Workspace w;
+    size_t o = 0;
+    w.cnt = o;          o = align_up(o + sizeof(int) * n_experts);
+    w.off = o;          o = align_up(o + sizeof(int) * (n_experts + 1));
+    w.row_of_pair = o;  o = align_up(o + sizeof(int) * P);
+    w.pair_of_row = o;  o = align_up(o + sizeof(int) * P);
+    w.xs = o;           o = align_up(o + 2 * P * H);
+    w.gu = o;           o = align_up(o + 4 * P * 2 * EFF);
+    w.act = o;          o = align_up(o + 2 * P * EFF);
+    w.dn = o;           o = align_up(o + 4 * P * H);
+    w.total = o;
+    return w;
 }
 
 }  // namespace
 
 void gemm_init()
 {
-    cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<256>::kSmemBytes);
+    cudaFuncSetAttribute(gemm_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<64>::kSmemBytes);
     (void)encode_tiled();
 }
 
@@ -459,6 +596,76 @@ int mb200_gemm_q4k_f16(const void *w, const void *x_f16, float *out, int M, int 
 int mb200_gemm_q6k_f16(const void *w, const void *x_f16, float *out, int M, int N, int K, cudaStream_t stream)
 {
     return launch_gemm(w, x_f16, out, M, N, K, 1, stream, "mb200_gemm_q6k_f16");
+}
+
+size_t mb200_moe_prefill_workspace_bytes(int M, int k, int H, int EFF, int n_experts)
+{
+    if (M < 1 || k < 1 || H < 1 || EFF < 1 || n_experts < 1) return 0;
+    return workspace_layout(M, k, H, EFF, n_experts).total;
+}
+
+int mb200_moe_prefill(const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz, int down_type,
+                      int n_experts, int k, int H, int EFF, const void *x_f16, const int *ids, const float *wts,
+                      const float *residual, float *y, int M, int max_tokens_per_expert, void *workspace,
+                      cudaStream_t stream)
+{
+    const char *where = "mb200_moe_prefill";
+    if (!experts || !x_f16 || !ids || !wts || !y || !workspace || M < 1 || k < 1 || k > 16 || n_experts < 1 ||
+        n_experts > 1024)
+        return MB200_ERR_ARG;
+    if (H % 256 != 0 || EFF % 256 != 0 || (down_type != 12 && down_type != 14)) return MB200_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(experts) & 15) || (expert_stride & 15) || (gate_sz & 15) ||
+        (reinterpret_cast<uintptr_t>(x_f16) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+        return MB200_ERR_ARG;
+    if (gate_sz != up_sz || gate_sz != (size_t)EFF * (H / 256) * kQ4KBlock) return MB200_ERR_ARG;
+    const int P = M * k;
+    const int cap = (max_tokens_per_expert > 0 && max_tokens_per_expert < M) ? max_tokens_per_expert : M;
+    const Workspace L = workspace_layout(M, k, H, EFF, n_experts);
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    SortOut so{reinterpret_cast<int *>(ws + L.cnt), reinterpret_cast<int *>(ws + L.off),
+               reinterpret_cast<int *>(ws + L.row_of_pair), reinterpret_cast<int *>(ws + L.pair_of_row)};
+    __half *xs = reinterpret_cast<__half *>(ws + L.xs);
+    float *gu = reinterpret_cast<float *>(ws + L.gu);
+    __half *act = reinterpret_cast<__half *>(ws + L.act);
+    float *dn = reinterpret_cast<float *>(ws + L.dn);
+
+    moe_sort_kernel<<<1, 1024, 0, stream>>>(ids, P, n_experts, cap, so, device_error_word());
+    moe_gather_kernel<<<P, 128, 0, stream>>>(static_cast<const uint4 *>(x_f16), reinterpret_cast<uint4 *>(xs),
+                                             so.pair_of_row, so.off, n_experts, k, H / 8);
+    const int token_tiles = (cap + kGroupBT - 1) / kGroupBT;
+
+    GemmParams G{};  // gate and up are adjacent Q4_K matrices of a blob: one [2*EFF x H] matrix
+    G.w = static_cast<const uint8_t *>(experts);
+    G.out = gu;
+    G.M = P;
+    G.N = 2 * EFF;
+    G.K = H;
+    G.q6 = 0;
+    G.seg_off = so.off;
+    G.seg_cnt = so.cnt;
+    G.tiles_per_expert = (2 * EFF + kBN - 1) / kBN;
+    G.expert_stride = expert_stride;
+    int rc = launch_gemm_bt<kGroupBT>(G, xs, P, dim3(n_experts * G.tiles_per_expert, token_tiles), stream, where);
+    if (rc != MB200_OK) return rc;
+
+    moe_swiglu_rows_kernel<<<P, 256, 0, stream>>>(gu, act, so.off, n_experts, EFF);
+
+    GemmParams D{};
+    D.w = static_cast<const uint8_t *>(experts) + gate_sz + up_sz;
+    D.out = dn;
+    D.M = P;
+    D.N = H;
+    D.K = EFF;
+    D.q6 = down_type == 14;
+    D.seg_off = so.off;
+    D.seg_cnt = so.cnt;
+    D.tiles_per_expert = (H + kBN - 1) / kBN;
+    D.expert_stride = expert_stride;
+    rc = launch_gemm_bt<kGroupBT>(D, act, P, dim3(n_experts * D.tiles_per_expert, token_tiles), stream, where);
+    if (rc != MB200_OK) return rc;
+
+    moe_combine_kernel<<<M, 256, 0, stream>>>(dn, so.row_of_pair, wts, residual, y, k, H);
+    return cudaGetLastError() == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
 }
 
 }  // extern "C"

@@ -200,6 +200,19 @@ def mb200_gemm_q6k_f16(w, x_f16, out, M, N, K_, stream=None):
            "mb200_gemm_q6k_f16")
 
 
+def mb200_moe_prefill_workspace_bytes(M, k, H, EFF, n_experts) -> int:
+    return int(_lib.lib().mb200_moe_prefill_workspace_bytes(M, k, H, EFF, n_experts))
+
+
+def mb200_moe_prefill(experts, expert_stride, gate_sz, up_sz, down_type, n_experts, k, H, EFF, x_f16, ids, wts,
+                      residual, y, M, max_tokens_per_expert, workspace, stream=None):
+    if x_f16.dtype != torch.float16:
+        raise TypeError("x must be float16")
+    _check(_lib.lib().mb200_moe_prefill(_ptr(experts), expert_stride, gate_sz, up_sz, down_type, n_experts, k, H, EFF,
+                                        _ptr(x_f16), _ptr(ids), _f32(wts), _ptr(residual), _f32(y), M,
+                                        max_tokens_per_expert, _ptr(workspace), _stream(stream)), "mb200_moe_prefill")
+
+
 def mb200_fill_q4k(dst, n_blocks, seed, stream=None):
     _check(_lib.lib().mb200_fill_q4k(_ptr(dst), n_blocks, seed, _stream(stream)), "mb200_fill_q4k")
 

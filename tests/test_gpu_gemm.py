@@ -71,3 +71,71 @@ def test_gemm_rejects_bad_k(K):
         K.mb200_gemm_q4k_f16(torch.zeros(144 * 128, dtype=torch.uint8, device="cuda"),
                              torch.zeros(16, 128, dtype=torch.float16, device="cuda"),
                              torch.zeros(16, 128, device="cuda"), 16, 128, 128)
+
+
+def _moe_prefill_oracle(experts, stride, g, u, down_type, H, EFF, x16, ids, wts, res):
+    M, k = ids.shape
+    out = np.zeros((M, H), np.float64)
+    for t in range(M):
+        xt = x16[t].astype(np.float32)
+        acc = np.zeros(H, np.float32)
+        for s in range(k):
+            e = int(ids[t, s])
+            if e < 0:
+                continue
+            acc = oracle.expert_fwd(experts[e * stride:(e + 1) * stride], g, u, H, EFF, down_type, float(wts[t, s]), xt, acc)
+        out[t] = res[t].astype(np.float64) + acc
+    return out
+
+
+@pytest.mark.parametrize("M,NE,k,H,EFF,down_type", [(48, 8, 2, 512, 256, 14), (96, 16, 4, 1024, 512, 14),
+                                                     (40, 8, 3, 512, 256, 12), (130, 4, 2, 512, 256, 14)])
+def test_moe_prefill_grouped(K, M, NE, k, H, EFF, down_type):
+    g, u, d = synth.expert_sizes(H, EFF, down_type)
+    stride = g + u + d
+    experts = np.concatenate([synth.expert_blob(800 + e, H, EFF, down_type) for e in range(NE)])
+    x = synth.normal_f16(801, M * H).reshape(M, H)
+    res = synth.normal_f32(802, M * H).reshape(M, H)
+    rng = np.random.default_rng(803)
+    ids = np.stack([rng.permutation(NE)[:k] for _ in range(M)]).astype(np.int32)
+    ids[0, 0] = -1  # an empty slot
+    wts = rng.random((M, k)).astype(np.float32)
+    wts /= wts.sum(1, keepdims=True)
+    want = _moe_prefill_oracle(experts, stride, g, u, down_type, H, EFF, x, ids, wts, res)
+    n = K.mb200_moe_prefill_workspace_bytes(M, k, H, EFF, NE)
+    ws = torch.empty(n + 256, dtype=torch.uint8, device="cuda")
+    ws = ws[(256 - ws.data_ptr() % 256) % 256:]
+    y = torch.full((M, H), float("nan"), device="cuda")
+    K.mb200_moe_prefill(dev(experts), stride, g, u, down_type, NE, k, H, EFF, dev(x), dev(ids), dev(wts), dev(res), y,
+                        M, 0, ws)
+    got = host(y).astype(np.float64)
+    assert np.all(np.isfinite(got))
+    moe_ref = want - res
+    num = np.linalg.norm((got - res) - moe_ref, axis=1)
+    den = np.linalg.norm(moe_ref, axis=1)
+    rel = num / den
+    # Two chained GEMMs with fp16 weight tiles: each GEMM is within 1e-3 of fp32 on its own inputs
+    # (tests above, and the stage check below); end to end the two roundings of W compound to a median
+    # of ~4.5e-4 per token row with a tail up to ~2e-3 on rows whose output happens to be small.
+    assert float(np.median(rel)) <= 1e-3, float(np.median(rel))
+    assert float(rel.max()) <= 2.5e-3, float(rel.max())
+
+    # stage check: the grouped launches give what the dense GEMM gives on each expert's gathered tokens
+    d_exp, d_x = dev(experts), dev(x)
+    acc = torch.zeros(M, H, device="cuda")
+    for e in range(NE):
+        rows, slots = np.nonzero(ids == e)
+        if rows.size == 0:
+            continue
+        xe = d_x[torch.from_numpy(rows).cuda()].contiguous()
+        gu = torch.empty(rows.size, 2 * EFF, device="cuda")
+        K.mb200_gemm_q4k_f16(d_exp[e * stride:], xe, gu, rows.size, 2 * EFF, H)
+        act = (torch.nn.functional.silu(gu[:, :EFF]) * gu[:, EFF:] / 16).half().contiguous()
+        dn = torch.empty(rows.size, H, device="cuda")
+        (K.mb200_gemm_q6k_f16 if down_type == 14 else K.mb200_gemm_q4k_f16)(d_exp[e * stride + g + u:], act, dn,
+                                                                             rows.size, H, EFF)
+        wv = torch.from_numpy(wts[rows, slots]).cuda()[:, None] * 16
+        acc.index_add_(0, torch.from_numpy(rows).cuda(), dn * wv)
+    composed = host(acc).astype(np.float64)
+    d2 = np.linalg.norm((got - res) - composed, axis=1) / np.linalg.norm(composed, axis=1)
+    assert float(d2.max()) <= 2e-4, float(d2.max())
