@@ -341,6 +341,101 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_secondary(args):
+    """Other workloads of the same path, one JSON line each (not the headline; used for profiles)."""
+    import torch
+    from mnemocuda_b200 import kernels as K
+    from mnemocuda_b200.moe import MoEShape, ResidentMoE
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the kernels have no CPU fallback")
+    K.mb200_init()
+    dev = torch.device("cuda", 0)
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    tf = float(peaks.get("bf16_tflops", 1590.0))
+
+    def timed(fn, steps, warmup):
+        """ms per step of `steps` steps replayed as one CUDA graph, CUDA events around the replay."""
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(steps):
+                fn(warmup + i)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    steps, warmup = args.steps, args.warmup
+    with ClockSampler(0) as clk:
+        if args.workload == "matvec":
+            # the vocabulary-sized matvec (151936 x 4096): 350 MB (Q4_K) / 510 MB (Q6_K) per pass, larger than L2
+            rows, cols = 151936, 4096
+            out = {}
+            for name, bb, fill, call in (("q4k", 144, K.mb200_fill_q4k, K.cuda_matvec_q4k), ("q6k", 210, K.mb200_fill_q6k, K.cuda_matvec_q6k)):
+                nb = rows * cols // 256
+                w = torch.empty(nb * bb, dtype=torch.uint8, device=dev)
+                fill(w, nb, 3)
+                x = torch.randn(cols, device=dev)
+                y = torch.empty(rows, device=dev)
+                ms = timed(lambda i: call(w, x, y, rows, cols), steps, warmup)
+                by = nb * bb + 4 * (rows + cols)
+                out[name] = {"ms": ms, "GBs": by / ms / 1e6, "frac_of_measured_hbm": by / ms / 1e6 / hbm, "bytes": by}
+                del w
+            line = {"workload": "matvec 151936x4096 (lm_head shape), one CUDA graph of the steps", "results": out}
+        elif args.workload == "gemm":
+            # configs 3a: dense prefill GEMM 512 tokens x (8192 x 4096), weights rotate over 8 copies
+            M, N, Kd, copies = 512, 8192, 4096, 8
+            out = {}
+            for name, bb, fill, call in (("q4k", 144, K.mb200_fill_q4k, K.mb200_gemm_q4k_f16), ("q6k", 210, K.mb200_fill_q6k, K.mb200_gemm_q6k_f16)):
+                nb = N * Kd // 256
+                w = torch.empty(copies * nb * bb, dtype=torch.uint8, device=dev)
+                fill(w, copies * nb, 3)
+                x = torch.randn(M, Kd, device=dev).half()
+                y = torch.empty(M, N, device=dev)
+                ws = [w[i * nb * bb:(i + 1) * nb * bb] for i in range(copies)]
+                ms = timed(lambda i: call(ws[i % copies], x, y, M, N, Kd), steps, warmup)
+                fl = 2.0 * M * N * Kd
+                out[name] = {"ms": ms, "TFLOPs": fl / ms / 1e9, "frac_of_measured_bf16_burst": fl / ms / 1e9 / tf}
+                del w
+            line = {"workload": "configs 3a: prefill GEMM 512 x 8192 x 4096, fp16 tcgen05 with in-kernel dequant", "results": out}
+        else:
+            # configs 3b: grouped per-expert prefill, 512 tokens, top-8 of 128 experts
+            shape = MoEShape()
+            s = shape
+            moe = ResidentMoE(shape, 1, dev, seed=1)
+            M, k = 512, s.K
+            x = torch.randn(M, s.H, device=dev).half()
+            top = torch.topk(x.float() @ moe.router[0].T, k, dim=1)
+            ids = top.indices.int().contiguous()
+            wts = torch.softmax(top.values, dim=1).contiguous()
+            cnt = torch.bincount(ids.flatten().long(), minlength=s.NE)
+            cap = 64 if int(cnt.max()) <= 64 else 0
+            nbytes = K.mb200_moe_prefill_workspace_bytes(M, k, s.H, s.EFF, s.NE) + 256
+            ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+            ws = ws[(256 - ws.data_ptr() % 256) % 256:]
+            y = torch.empty(M, s.H, device=dev)
+            res = torch.randn(M, s.H, device=dev)
+            ms = timed(lambda i: K.mb200_moe_prefill(moe.experts[0], s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE, k, s.H,
+                                                     s.EFF, x, ids, wts, res, y, M, cap, ws), steps, warmup)
+            fl = 2.0 * M * k * 3 * s.EFF * s.H
+            wb = s.NE * s.stride
+            line = {"workload": "configs 3b: grouped per-expert prefill MoE block, 512 tokens, top-8 of 128 experts",
+                    "results": {"ms": ms, "TFLOPs": fl / ms / 1e9, "weights_GBs": wb / ms / 1e6,
+                                "hbm_floor_ms": wb / hbm / 1e6, "tokens_per_expert_max": int(cnt.max()), "cap": cap}}
+    err = K.mb200_device_error()
+    if err != 0:
+        raise RuntimeError(f"a kernel reported device error {err}")
+    line.update({"secondary": True, "steps": steps, "warmup": warmup, "clocks": clk.summary(), "data": "synthetic"})
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -351,6 +446,8 @@ def main():
     ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--workload", default="moe_block", choices=["moe_block", "matvec", "gemm", "prefill"],
+                    help="moe_block is the headline; the others print a secondary line for the same path")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -358,6 +455,8 @@ def main():
         if args.steps > 20:
             args.steps = 20  # each step is 4 CPU blocks: keep the run within a few minutes
         run_reference(args)
+    elif args.workload != "moe_block":
+        run_secondary(args)
     else:
         run_ours(args)
 
