@@ -183,6 +183,25 @@ int mb200_moe_block(const float *router_w, const void *experts, size_t expert_st
                     const float *x, const float *residual, float *out, int *ids, float *wts,
                     float *act, void *scratch, cudaStream_t stream);
 
+/* Gate/up + SwiGLU, down projections, weighted sum and residual add of the routed experts in ONE
+ * cooperative launch (the two phases are separated by a device-wide barrier inside the kernel, and the
+ * down-projection weights stream in while the CTAs meet). Same arguments and results as
+ * mb200_moe_gate_up_local followed by mb200_moe_down_local; the expert range [expert_lo, expert_lo +
+ * expert_cnt) is what this device holds at `experts` (0, INT_MAX for all). `sync`: two 64-bit words,
+ * 8-byte aligned, zero before the first use and owned by this call sequence afterwards (arrival
+ * counters that only grow; after MB200_ERR_TIMEOUT they must be zeroed again).
+ * Covers H a multiple of 2048 with 12 % (H / 2048) == 0, EFF a multiple of 512 whose column groups
+ * divide 12, at most 8 slots, 16-byte aligned tensors; returns MB200_ERR_UNSUPPORTED -- and launches
+ * nothing -- otherwise. mb200_moe_block uses it when it applies (words 2-5 of its scratch are the
+ * barrier state) and falls back to the two separate kernels when not, or after mb200_set_fused(0).
+ * The first call in a process should be made outside stream capture. */
+int mb200_moe_experts_fused(const void *experts, size_t expert_stride, size_t gate_off, size_t up_off,
+                            size_t down_off, int down_type, const int *ids, const float *wts, int n_slots,
+                            int expert_lo, int expert_cnt, const float *x, float *act,
+                            const float *residual, float *y, int H, int EFF, void *sync,
+                            cudaStream_t stream);
+void mb200_set_fused(int on);
+
 /* ---- prefill GEMM on tcgen05 tensor cores ----
  * out[t][n] = sum_k f16(X[t][k]) * dequant(W)[n][k]; X fp16 [M x K] row-major (16-byte aligned),
  * W Q4_K / Q6_K [N x K] as for the matvecs, out fp32 [M x N]; K a multiple of 256. Weights are

@@ -26,6 +26,11 @@ void moe_down_q6k(const void *experts, size_t stride, size_t down_off, const int
                   int expert_lo, int expert_cnt, const float *act, const float *residual, float *y, int H, int EFF,
                   cudaStream_t stream, const char *where);
 int pdl_enabled();
+int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off, size_t down_off, int down_type,
+              const int *ids, const float *wts, int n_slots, int expert_lo, int expert_cnt, const float *x, float *act,
+              const float *residual, float *y, int H, int EFF, unsigned long long *sync, cudaStream_t stream);
+void moe_fused_set_mode(int mode);
+int moe_fused_mode();
 
 namespace {
 
@@ -231,12 +236,33 @@ int mb200_moe_down(const void *experts, size_t expert_stride, size_t down_off, i
                                 residual, y, H, EFF, stream);
 }
 
+void mb200_set_fused(int on) { moe_fused_set_mode(on ? 1 : 0); }
+
+int mb200_moe_experts_fused(const void *experts, size_t expert_stride, size_t gate_off, size_t up_off, size_t down_off,
+                            int down_type, const int *ids, const float *wts, int n_slots, int expert_lo, int expert_cnt,
+                            const float *x, float *act, const float *residual, float *y, int H, int EFF, void *sync,
+                            cudaStream_t stream)
+{
+    if (!experts || !ids || !wts || !x || !act || !y || !sync || n_slots < 1 || EFF < 1 || H < 1 || expert_lo < 0 ||
+        expert_cnt < 0)
+        return MB200_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(sync) & 7) return MB200_ERR_ARG;
+    return moe_fused(experts, expert_stride, gate_off, up_off, down_off, down_type, ids, wts, n_slots, expert_lo,
+                     expert_cnt, x, act, residual, y, H, EFF, static_cast<unsigned long long *>(sync), stream);
+}
+
 int mb200_moe_block(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz,
                     int down_type, int n_experts, int k, int H, int EFF, const float *x, const float *residual,
                     float *out, int *ids, float *wts, float *act, void *scratch, cudaStream_t stream)
 {
     int rc = mb200_router_topk(router_w, x, scratch, ids, wts, n_experts, H, k, stream);
     if (rc != MB200_OK) return rc;
+    if (moe_fused_mode() && act) {
+        // words 2-5 of the router scratch are the fused kernel's barrier state
+        rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, ids, wts, k, 0, 0x7fffffff, x, act,
+                       residual, out, H, EFF, reinterpret_cast<unsigned long long *>(static_cast<unsigned *>(scratch) + 2), stream);
+        if (rc != MB200_ERR_UNSUPPORTED) return rc;
+    }
     rc = mb200_moe_gate_up(experts, expert_stride, 0, gate_sz, ids, k, x, act, EFF, H, stream);
     if (rc != MB200_OK) return rc;
     return mb200_moe_down(experts, expert_stride, gate_sz + up_sz, down_type, ids, wts, k, act, residual, out, H, EFF,

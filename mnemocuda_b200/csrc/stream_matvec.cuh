@@ -267,13 +267,13 @@ __device__ __forceinline__ float packed_sum(float (&a)[RU], int W, int lane, int
 
 #ifdef MB200_TRACE
 // Developer aid (off in product builds): per-CTA clock stamps at phase boundaries.
-static __device__ long long g_trace[kSMs * 2][16];  // one copy per translation unit
+static __device__ long long g_trace[kSMs * 2][48];  // one copy per translation unit
 #define MB200_STAMP(slot)                                                     \
     do {                                                                      \
         if ((threadIdx.x & 31) == 0 && blockIdx.x < kSMs * 2) {               \
             long long t__;                                                    \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));           \
-            g_trace[blockIdx.x][slot] = t__;                                  \
+            ::mb200::stream::g_trace[blockIdx.x][slot] = t__;                                 \
         }                                                                     \
     } while (0)
 #else
@@ -516,10 +516,12 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
         TileWalk look = walk;
         for (int i = 0; i < S; i++) look.next(P, ahead);  // `look` runs S tiles ahead: does stage s get reused?
         int s = 0, ph = 0;
+        int ek = 0;
         while (walk.next(P, t)) {
             const bool reused = look.next(P, ahead);
             if (!mbar_wait(&empty[s], ph)) *abort_flag = 1;
             if (*abort_flag) break;
+            if (ek < 8) MB200_STAMP(32 + ek);
             const float *pt = part + s * part_pitch;
             int it = 0;
             for (int r = lane; r < t.rows; r += 32, it++) {
@@ -551,6 +553,8 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
             }
             __syncwarp();
             if (lane == 0 && reused) mbar_arrive(&full[s]);  // partial-sum slot s may be rewritten
+            if (ek < 8) MB200_STAMP(40 + ek);
+            ek++;
             if (++s == S) {
                 s = 0;
                 ph ^= 1;
@@ -621,6 +625,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
 #endif
         if (warp == 0 && k == 0) MB200_STAMP(3);
         if (warp == 0) MB200_STAMP(4);
+        if (warp == 0 && k < 8) MB200_STAMP(16 + k);
         k++;
 
         int r0 = idx * unit_rows;
@@ -663,6 +668,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
         if (lane == 0) mbar_arrive(&empty[s]);
         if (*abort_flag) break;
 #endif
+        if (warp == 0 && k <= 8) MB200_STAMP(24 + k - 1);
         if (++s == S) {
             s = 0;
             ph ^= 1;

@@ -186,6 +186,19 @@ def mb200_moe_block(router_w, experts, expert_stride, gate_sz, up_sz, down_type,
                                       _f32(wts), _f32(act), _ptr(scratch), _stream(stream)), "mb200_moe_block")
 
 
+def mb200_moe_experts_fused(experts, expert_stride, gate_off, up_off, down_off, down_type, ids, wts, n_slots, expert_lo,
+                            expert_cnt, x, act, residual, y, H, EFF, sync, stream=None):
+    """Gate/up + SwiGLU + down + weighted sum + residual in one cooperative launch (include/mnemo_b200.h)."""
+    _check(_lib.lib().mb200_moe_experts_fused(_ptr(experts), expert_stride, gate_off, up_off, down_off, down_type,
+                                              _ptr(ids), _f32(wts), n_slots, expert_lo, expert_cnt, _f32(x), _f32(act),
+                                              _ptr(residual), _f32(y), H, EFF, _ptr(sync), _stream(stream)),
+           "mb200_moe_experts_fused")
+
+
+def mb200_set_fused(on: bool) -> None:
+    _lib.lib().mb200_set_fused(1 if on else 0)
+
+
 def mb200_gemm_q4k_f16(w, x_f16, out, M, N, K_, stream=None):
     if x_f16.dtype != torch.float16:
         raise TypeError("x must be float16")
