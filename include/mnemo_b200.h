@@ -126,7 +126,8 @@ int mb200_matvec_q6k_scaled_add(const void *weights, const float *x, float *y, i
  * An expert blob is [gate Q4_K EFF x H][up Q4_K EFF x H][down H x EFF], expert e at
  * experts + e * expert_stride (src/forward.c:1127-1136). */
 
-/* Bytes of scratch mb200_router_topk needs: a ticket counter followed by the logits. */
+/* Bytes of scratch mb200_router_topk / mb200_moe_block need: a ticket counter, the logits, and
+ * (16-byte aligned, at the end) 64 bytes of barrier counters for mb200_moe_block. */
 size_t mb200_router_scratch_bytes(int n_experts);
 
 /* logits = router_w x (fp32 [n_experts x n_cols], src/kernels.cu:859-880), then the
@@ -187,12 +188,12 @@ int mb200_moe_block(const float *router_w, const void *experts, size_t expert_st
  * cooperative launch (the two phases are separated by a device-wide barrier inside the kernel, and the
  * down-projection weights stream in while the CTAs meet). Same arguments and results as
  * mb200_moe_gate_up_local followed by mb200_moe_down_local; the expert range [expert_lo, expert_lo +
- * expert_cnt) is what this device holds at `experts` (0, INT_MAX for all). `sync`: two 64-bit words,
- * 8-byte aligned, zero before the first use and owned by this call sequence afterwards (arrival
- * counters that only grow; after MB200_ERR_TIMEOUT they must be zeroed again).
+ * expert_cnt) is what this device holds at `experts` (0, INT_MAX for all). `sync`: 32 bytes (four
+ * 64-bit words), 8-byte aligned, zero before the first use and owned by this call sequence afterwards
+ * (arrival counters that only grow; after MB200_ERR_TIMEOUT they must be zeroed again).
  * Covers H a multiple of 2048 with 12 % (H / 2048) == 0, EFF a multiple of 512 whose column groups
  * divide 12, at most 8 slots, 16-byte aligned tensors; returns MB200_ERR_UNSUPPORTED -- and launches
- * nothing -- otherwise. mb200_moe_block uses it when it applies (words 2-5 of its scratch are the
+ * nothing -- otherwise. mb200_moe_block uses it when it applies (the tail of its scratch is the
  * barrier state) and falls back to the two separate kernels when not, or after mb200_set_fused(0).
  * The first call in a process should be made outside stream capture. */
 int mb200_moe_experts_fused(const void *experts, size_t expert_stride, size_t gate_off, size_t up_off,

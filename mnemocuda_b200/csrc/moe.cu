@@ -160,7 +160,13 @@ using namespace mb200;
 
 extern "C" {
 
-size_t mb200_router_scratch_bytes(int n_experts) { return sizeof(int) * 8 + sizeof(float) * (size_t)(n_experts > 0 ? n_experts : 0); }
+// ticket + padding (8 words), the logits, then (16-byte aligned) the 64 bytes of barrier counters that
+// mb200_moe_block hands to the fused expert kernel
+static size_t router_part_bytes(int n_experts)
+{
+    return (sizeof(int) * 8 + sizeof(float) * (size_t)(n_experts > 0 ? n_experts : 0) + 15) & ~static_cast<size_t>(15);
+}
+size_t mb200_router_scratch_bytes(int n_experts) { return router_part_bytes(n_experts) + 64; }
 
 int mb200_router_topk(const float *router_w, const float *x, void *scratch, int *indices, float *weights,
                       int n_experts, int n_cols, int k, cudaStream_t stream)
@@ -258,9 +264,11 @@ int mb200_moe_block(const float *router_w, const void *experts, size_t expert_st
     int rc = mb200_router_topk(router_w, x, scratch, ids, wts, n_experts, H, k, stream);
     if (rc != MB200_OK) return rc;
     if (moe_fused_mode() && act) {
-        // words 2-5 of the router scratch are the fused kernel's barrier state
+        // the last 64 bytes of the scratch are the fused kernel's barrier counters
         rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, ids, wts, k, 0, 0x7fffffff, x, act,
-                       residual, out, H, EFF, reinterpret_cast<unsigned long long *>(static_cast<unsigned *>(scratch) + 2), stream);
+                       residual, out, H, EFF,
+                       reinterpret_cast<unsigned long long *>(static_cast<char *>(scratch) + router_part_bytes(n_experts)),
+                       stream);
         if (rc != MB200_ERR_UNSUPPORTED) return rc;
     }
     rc = mb200_moe_gate_up(experts, expert_stride, 0, gate_sz, ids, k, x, act, EFF, H, stream);

@@ -11,20 +11,25 @@
 // for the barrier, so the down-projection weights stream in while the last
 // gate/up tiles are consumed and while the CTAs meet.
 //
-// Roles per CTA (416 threads): warps 0-11 consume tiles (int8 dp4a dot
+// Roles per CTA (448 threads): warps 0-11 consume tiles (int8 dp4a dot
 // products, see q4k_policy.cuh / q6k_policy.cuh) and leave per-column-group
 // partial sums in shared memory; the warp that stores the last partial sum of
 // a tile finishes it (SwiGLU and the act store, or the running weighted sum
 // over the expert slots in slot order -- deterministic, no atomics). Warp 12
-// issues the copies. The warp that finishes the CTA's last gate/up tile
-// arrives at the device-wide barrier.
+// issues the weight copies. Warp 13 (the courier) does every slow device-wide
+// step so that no consumer warp waits on global memory: barrier arrivals, the
+// polls, and the bulk copies that bring finished activation vectors into
+// shared memory.
 //
-// The device-wide barrier: an arrival counter and a generation word in global
-// memory (zero before the first use, left ready for the next launch). The last
-// CTA to arrive clears the counter and bumps the generation; consumer warps
-// poll the generation with a bounded loop. The launch is cooperative (all
-// CTAs co-resident) and every wait gives up after a bounded number of polls,
-// setting the library's device error word instead of hanging.
+// The routed slots are handled in batches of two. Gate/up tiles are dealt to
+// the CTAs in batch order, and each batch has its own device-wide barrier: an
+// arrival counter in global memory that only ever grows (a launch knows its
+// target from the value it reads at its start). The activations of a batch
+// are therefore complete, copied into every SM and split into int8 levels
+// (a share per consumer warp, at tile boundaries) while later tiles are still
+// being streamed; only the last batch can make the down phase wait. The launch
+// is cooperative (all CTAs co-resident) and every wait gives up after a bounded
+// number of polls, setting the library's device error word instead of hanging.
 #include <cstdio>
 
 #include "q4k_policy.cuh"
@@ -41,7 +46,11 @@ using stream::Layout;
 
 constexpr int kFusedMaxSlots = 8;
 constexpr int kFusedMaxStages = 6;
-constexpr int kFusedThreads = (kConsumers + 1) * 32;  // 12 consumer warps + the issuer warp
+constexpr int kFusedThreads = (kConsumers + 2) * 32;  // 12 consumer warps + tile issuer + courier
+constexpr int kBatchSlots = 2;                         // served slots per batch
+constexpr int kFusedMaxBatches = kFusedMaxSlots / kBatchSlots;
+constexpr int kFusedMaxTiles = 16;  // gate/up tiles per CTA (one lane of the issuer warp lists each)
+constexpr int kCtrlBytes = 592;     // mbarriers, routing tables, running sums, tile list
 constexpr int kXBase = 384;  // stream::layout<> puts the first staged vector at this offset of its base pointer
 
 struct FusedParams {
@@ -53,7 +62,7 @@ struct FusedParams {
     const float *residual;
     float *y;
     float *act;      // [n_slots][EFF] fp32, written in phase 1 and read back (through L2) in phase 2
-    unsigned long long *sync;  // arrival counters of the two batch barriers (monotonic)
+    unsigned long long *sync;  // arrival counters of the batch barriers (kFusedMaxBatches, monotonic)
     int *err;
     int n_slots, expert_lo, expert_cnt;
     int H, EFF, bprB, bprC;
@@ -61,6 +70,7 @@ struct FusedParams {
     int ngC, wpgC, vC, rppC, TC;   // down: column groups, warps per group, blocks per row group, rows per pass, rows per tile
     int stages, stage_bytes;
     int off_xb, off_xc, xc_stride, off_part, part_pitch, off_stages;  // shared-memory offsets (bytes; part_pitch in floats)
+    int off_raw, raw_bytes;        // two buffers for the fp32 activation vectors of one batch
     int pdl;
 };
 
@@ -73,60 +83,65 @@ struct FTile {
     int row0, rows;
 };
 
+// Device-wide barrier state: one 64-bit arrival counter per batch that only ever grows. Every
+// launch adds exactly gridDim.x arrivals to a counter it uses, so between launches its value is a
+// multiple of gridDim.x; a CTA that reads c at its start (when at most gridDim.x - 1 arrivals of its
+// own launch can be in) knows the launch is complete at c - c % gridDim.x + gridDim.x.
+__device__ __forceinline__ unsigned long long barrier_target(const unsigned long long *ctr)
+{
+    unsigned long long c;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(ctr) : "memory");
+    return c - c % gridDim.x + gridDim.x;
+}
+// Release-arrive: every store this thread has made or observed (through the block-scope handshakes
+// between the warps that finished the CTA's tiles) is visible to whoever acquires the counter.
+__device__ __forceinline__ void barrier_arrive(unsigned long long *ctr)
+{
+    asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(ctr) : "memory");
+}
 // The CTA's tiles in issue order. Every role runs the same walk.
 //
-// Gate/up work is split in whole tiles (TB pair rows of one expert). The served slots form two
-// batches (first half, second half); every CTA does its share of batch 0 first, then its share of
-// batch 1, so that the activations of batch 0 are complete device-wide half way through the phase
-// and the barrier that guards them costs nothing. With T0 tiles in batch 0 and T in total, CTA b
-// takes batch-0 tiles [T0*b/G, T0*(b+1)/G) and batch-1 tiles [F(b), F(b+1)), F(b) = T*b/G - T0*b/G,
-// which gives every CTA T/G tiles (rounded) in total.
+// Gate/up work is split in whole tiles (TB pair rows of one expert), numbered through the served
+// slots in order and dealt to the CTAs round robin. The served slots form batches of kBatchSlots,
+// so every CTA does its share of batch 0 first, then of batch 1, ...: the activations of the early
+// batches are complete device-wide long before the down phase needs them, and the barrier that
+// guards a batch (plus the copy of its activations into every SM) hides behind the remaining work.
+// The issuer warp lists the CTA's gate/up tiles once (build_tiles) and leaves the list in shared
+// memory; the down tiles follow by simple arithmetic.
 struct FWalk {
-    int g0, g0_end, g1, g1_end, tpe;
-    int c_cur, c_end, e, n_act, n0;
+    int bi, n_b;
+    int c_cur, c_end, e, n_act;
+    const int2 *tiles;
     const int *act_list;
-    __device__ __forceinline__ void init(const FusedParams &P, const int *list, int n_active)
+    __device__ __forceinline__ void init(const FusedParams &P, const int2 *list, int n_list, const int *slots,
+                                         int n_active)
     {
-        act_list = list;
+        tiles = list;
+        n_b = n_list;
+        bi = 0;
+        act_list = slots;
         n_act = n_active;
-        n0 = (n_active + 1) >> 1;
-        tpe = (P.EFF + P.TB - 1) / P.TB;
-        const long long T0 = (long long)n0 * tpe, T = (long long)n_active * tpe;
-        const long long b = blockIdx.x, G = gridDim.x;
-        g0 = static_cast<int>(T0 * b / G);
-        g0_end = static_cast<int>(T0 * (b + 1) / G);
-        g1 = static_cast<int>(T0 + T * b / G - T0 * b / G);
-        g1_end = static_cast<int>(T0 + T * (b + 1) / G - T0 * (b + 1) / G);
-        c_cur = static_cast<int>((long long)P.H * b / G);
-        c_end = static_cast<int>((long long)P.H * (b + 1) / G);
+        c_cur = static_cast<int>((long long)P.H * blockIdx.x / gridDim.x);
+        c_end = static_cast<int>((long long)P.H * (blockIdx.x + 1) / gridDim.x);
         if (n_active == 0) c_end = c_cur;
         e = 0;
     }
-    __device__ __forceinline__ bool has_batch(int b) const { return b == 0 ? g0 < g0_end : g1 < g1_end; }
     __device__ __forceinline__ bool next(const FusedParams &P, FTile &t)
     {
-        int g = -1;
-        if (g0 < g0_end) {
-            g = g0++;
-            t.batch = 0;
-            t.last = (g0 == g0_end);
-        } else if (g1 < g1_end) {
-            g = g1++;
-            t.batch = 1;
-            t.last = (g1 == g1_end);
-        }
-        if (g >= 0) {
-            const int j = g / tpe;
+        if (bi < n_b) {
+            const int2 d = tiles[bi++];
             t.phase = 0;
-            t.j = j;
-            t.slot = act_list[j];
-            t.row0 = (g - j * tpe) * P.TB;
-            t.rows = min(P.TB, P.EFF - t.row0);
+            t.slot = d.x & 15;
+            t.j = (d.x >> 4) & 15;
+            t.batch = (d.x >> 8) & 15;
+            t.last = (d.x >> 12) & 1;
+            t.rows = d.x >> 16;
+            t.row0 = d.y;
             return true;
         }
         if (c_cur < c_end) {  // the same rows for every served slot in turn, then the next rows
             t.phase = 1;
-            t.batch = 0;
+            t.batch = e / kBatchSlots;
             t.last = 0;
             t.j = e;
             t.slot = act_list[e];
@@ -141,6 +156,47 @@ struct FWalk {
         return false;
     }
 };
+
+// One warp: reads the routed ids and weights (one round trip), compacts the slots served here, and
+// lists this CTA's gate/up tiles. Returns the number of served slots.
+__device__ __forceinline__ int build_tiles(const FusedParams &P, int lane, int *sid, float *swt, int *act_list,
+                                           int2 *tiles, int *n_tiles_p)
+{
+    int id = -1;
+    float w = 0.0f;
+    if (lane < P.n_slots) {
+        id = P.ids[lane];
+        w = P.wts[lane];
+    }
+    const bool here = lane < P.n_slots && id >= P.expert_lo && id - P.expert_lo < P.expert_cnt;  // empty slots have id < 0
+    const unsigned m = __ballot_sync(0xffffffffu, here);
+    const int n = __popc(m);
+    if (lane < P.n_slots) {
+        sid[lane] = here ? id - P.expert_lo : -1;
+        swt[lane] = here ? w : 0.0f;
+    }
+    if (here) act_list[__popc(m & ((1u << lane) - 1u))] = lane;
+    __syncwarp();
+    // Tiles are numbered through the served slots in order (tpe per slot) and dealt to the CTAs round
+    // robin: CTA b takes tiles b, b + G, b + 2G, ... -- in batch order, an equal share of every batch
+    // (to within one tile), and lane i lists the i-th of them.
+    const int tpe = (P.EFF + P.TB - 1) / P.TB;
+    const int T = n * tpe, G = gridDim.x;
+    const int g = blockIdx.x + lane * G;
+    const int total = (T > static_cast<int>(blockIdx.x)) ? (T - static_cast<int>(blockIdx.x) + G - 1) / G : 0;
+    if (lane < total && lane < kFusedMaxTiles) {
+        const int j = g / tpe;
+        const int row0 = (g - j * tpe) * P.TB;
+        const int rows = min(P.TB, P.EFF - row0);
+        const int batch = j / kBatchSlots;
+        const int gn = g + G;  // this CTA's next tile, if any
+        const int last = (gn >= T || (gn / tpe) / kBatchSlots != batch) ? 1 : 0;
+        tiles[lane] = make_int2(act_list[j] | (j << 4) | (batch << 8) | (last << 12) | (rows << 16), row0);
+    }
+    if (lane == 0) *n_tiles_p = min(total, kFusedMaxTiles);
+    __syncwarp();
+    return n;
+}
 
 template <class FD>
 __device__ __forceinline__ const uint8_t *down_src(const FusedParams &P, const FTile &t, const int *sid)
@@ -206,84 +262,6 @@ __device__ __forceinline__ void split_store(const float4 t, int c0, int lane, in
     }
 }
 
-// Device-wide barrier state: one 64-bit arrival counter per batch that only ever grows. Every
-// launch adds exactly gridDim.x arrivals to a counter it uses, so between launches its value is a
-// multiple of gridDim.x; a CTA that reads c at its start (when at most gridDim.x - 1 arrivals of its
-// own launch can be in) knows the launch is complete at c - c % gridDim.x + gridDim.x.
-__device__ __forceinline__ unsigned long long barrier_target(const unsigned long long *ctr)
-{
-    unsigned long long c;
-    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(ctr) : "memory");
-    return c - c % gridDim.x + gridDim.x;
-}
-// Release-arrive: every store this thread has made or observed (through the block-scope handshakes
-// between the warps that finished the CTA's tiles) is visible to whoever acquires the counter.
-__device__ __forceinline__ void barrier_arrive(unsigned long long *ctr)
-{
-    asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(ctr) : "memory");
-}
-// Lane 0 polls until the counter reaches `target`; the result is broadcast. Bounded.
-__device__ __forceinline__ bool barrier_wait(const unsigned long long *ctr, unsigned long long target,
-                                             volatile int *abort_flag, int lane)
-{
-    int ok = 0;
-    if (lane == 0) {
-        for (uint32_t i = 0; i < (1u << 20); i++) {
-            unsigned long long c;
-            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(ctr) : "memory");
-            if (c >= target) {
-                ok = 1;
-                break;
-            }
-            if (*abort_flag) break;
-            __nanosleep(40);
-        }
-    }
-    return __shfl_sync(0xffffffffu, ok, 0) != 0;
-}
-
-__device__ __forceinline__ void consumers_sync()
-{
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
-}
-
-// Before the first down tile of a batch: wait until every CTA has stored its act rows of the batch,
-// then split the batch's activation vectors (all loads in flight before the first use). Every
-// consumer warp calls this at the same points of the walk; the named barrier inside is matched by
-// the catch-up loop at the end of the kernel when a warp gave up early. Kept out of line so that
-// its registers do not weigh on the tile loops.
-template <class FD>
-__device__ __noinline__ void stage_batch(const FusedParams &P, uint8_t *smem, const int *act_list, int j0, int jn,
-                                         const unsigned long long *ctr, unsigned long long target,
-                                         volatile int *abort_flag, int stamp)
-{
-    const int tid = threadIdx.x, lane = tid & 31;
-    const bool met = !*abort_flag && barrier_wait(ctr, target, abort_flag, lane);
-    if (!met) *abort_flag = 1;
-    if (tid == 0) MB200_STAMP(stamp);
-    if (met) {
-        const Layout LC = stream::layout<FD>(P.bprC, 0, 0, 1, 1);
-        const int pitch = FD::kSlotsPerBlock * P.bprC + 1;
-        for (int c0 = tid * 4; c0 < P.EFF; c0 += kConsumers * 32 * 4) {
-            float4 v[kFusedMaxSlots / 2];
-#pragma unroll
-            for (int j = 0; j < kFusedMaxSlots / 2; j++)
-                if (j < jn) v[j] = __ldcg(reinterpret_cast<const float4 *>(P.act + (size_t)act_list[j0 + j] * P.EFF + c0));
-#pragma unroll
-            for (int j = 0; j < kFusedMaxSlots / 2; j++) {
-                if (j < jn) {
-                    uint8_t *xc = smem + P.off_xc + (j0 + j) * P.xc_stride - kXBase;
-                    split_store<FD>(v[j], c0, lane, pitch, reinterpret_cast<uint32_t *>(xc + LC.xq1),
-                                    reinterpret_cast<uint32_t *>(xc + LC.xq2), reinterpret_cast<float *>(xc + LC.xs1),
-                                    reinterpret_cast<float *>(xc + LC.xsum));
-                }
-            }
-        }
-    }
-    consumers_sync();
-    if (tid == 0) MB200_STAMP(stamp + 1);
-}
-
 // Finishes a gate/up tile: sums the column groups, SwiGLU, stores the act rows.
 __device__ __forceinline__ void finish_gate_up(const FusedParams &P, const FTile &t, const float *pt, int lane)
 {
@@ -329,7 +307,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     float *swt = reinterpret_cast<float *>(smem + 160);    // routing weight per slot
     int *act_list = reinterpret_cast<int *>(smem + 192);   // slots served here, in slot order
     int *n_act_p = reinterpret_cast<int *>(smem + 224);
-    float *run = reinterpret_cast<float *>(smem + 256);    // down: running sums of the tile's rows over the slots (<= 64)
+    int *n_tiles_p = reinterpret_cast<int *>(smem + 228);
+    int2 *tiles = reinterpret_cast<int2 *>(smem + 456);   // [kFusedMaxTiles] this CTA's gate/up tiles
+    uint64_t *rawfull = reinterpret_cast<uint64_t *>(smem + 232);   // [2] a batch's fp32 activation vectors have landed
+    uint64_t *rawempty = reinterpret_cast<uint64_t *>(smem + 248);  // [2] ... and every consumer warp has split its share
+    uint64_t *bdone = reinterpret_cast<uint64_t *>(smem + 264);     // [4] this CTA has stored its act rows of batch k
+    uint64_t *xready = reinterpret_cast<uint64_t *>(smem + 296);    // [4] the int8 levels of batch k are staged (all shares)
+    float *run = reinterpret_cast<float *>(smem + 328);    // down: running sums of the tile's rows over the slots (<= 32)
     float *part = reinterpret_cast<float *>(smem + P.off_part);
     uint8_t *stages = smem + P.off_stages;
     const int S = P.stages;
@@ -347,29 +331,35 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
                 mbar_init(&empty[s], kConsumers);
                 cnt[s] = 0;
             }
-            mbar_fence_init();
-            if (P.pdl) stream::grid_dep_wait();  // the routed ids come from the upstream kernel
-            int n = 0;
-            for (int e = 0; e < P.n_slots; e++) {
-                const int id = P.ids[e];
-                const bool here = id >= P.expert_lo && id - P.expert_lo < P.expert_cnt;  // empty slots have id < 0
-                sid[e] = here ? id - P.expert_lo : -1;
-                swt[e] = here ? P.wts[e] : 0.0f;
-                if (here) act_list[n++] = e;
+            for (int u = 0; u < 2; u++) {
+                mbar_init(&rawfull[u], 1);
+                mbar_init(&rawempty[u], kConsumers);
             }
+            for (int k = 0; k < kFusedMaxBatches; k++) {
+                mbar_init(&bdone[k], 1);
+                mbar_init(&xready[k], kConsumers);
+            }
+            mbar_fence_init();
+        }
+        if (P.pdl) stream::grid_dep_wait();  // the routed ids come from the upstream kernel
+        const int n = build_tiles(P, lane, sid, swt, act_list, tiles, n_tiles_p);
+        if (lane == 0) {
             *n_act_p = n;
-            walk.init(P, act_list, n);
+            walk.init(P, tiles, *n_tiles_p, act_list, n);
+            MB200_STAMP(40);
             FTile t;
             for (int s = 0; s < S; s++) {
                 mbar_arrive(&full[s]);  // first phase: no partial sums to drain yet
                 if (walk.next(P, t)) issue<FD>(P, t, stages + (size_t)s * P.stage_bytes, &full[s], sid);
             }
+            MB200_STAMP(41);
         }
         __syncthreads();
         if (lane == 0) {
             if (P.pdl) stream::grid_dep_launch();
             FTile t;
             int s = 0, ph = 0;
+            int ik = 0;
             while (walk.next(P, t)) {
                 if (!mbar_wait(&empty[s], ph)) {
                     *abort_flag = 1;
@@ -378,6 +368,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
                 }
                 if (*abort_flag) break;
                 issue<FD>(P, t, stages + (size_t)s * P.stage_bytes, &full[s], sid);
+                if (ik < 6) MB200_STAMP(42 + ik);
+                ik++;
                 if (++s == S) {
                     s = 0;
                     ph ^= 1;
@@ -387,14 +379,65 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         return;
     }
 
-    // ---------------- consumer warps ----------------
-    unsigned long long tgt0 = 0, tgt1 = 0;  // read before this CTA can have arrived
-    if (lane == 0) {
-        tgt0 = barrier_target(P.sync);
-        tgt1 = barrier_target(P.sync + 1);
+    if (warp == kConsumers + 1) {
+        // ---------------- courier ----------------
+        // One thread that does every slow device-wide step, so that no consumer warp ever waits on one:
+        // it arrives at a batch's barrier once this CTA's rows of the batch are stored (the release
+        // waits for those stores to be visible, which takes microseconds while weights stream in), and
+        // once every CTA has arrived it pulls the batch's fp32 activation vectors into shared memory.
+        unsigned long long tgt[kFusedMaxBatches];
+#pragma unroll
+        for (int b = 0; b < kFusedMaxBatches; b++) tgt[b] = barrier_target(P.sync + b);  // before this CTA can have arrived
+        __syncthreads();
+        if (lane != 0) return;
+        const int n_act = *n_act_p;
+        const int nb = (n_act + kBatchSlots - 1) / kBatchSlots;
+        const uint32_t vec_bytes = static_cast<uint32_t>(P.EFF) * 4u;
+        unsigned present = 0;  // batches this CTA has tiles in (the others it arrives at right away)
+        {
+            const int nt = *n_tiles_p;
+            for (int i = 0; i < nt; i++) present |= 1u << ((tiles[i].x >> 8) & 15);
+        }
+        int ka = 0, kc = 0;
+        for (uint32_t it = 0; it < (1u << 22) && (ka < nb || kc < nb); it++) {
+            if (*abort_flag) return;
+            bool progress = false;
+            if (ka < nb && (!(present & (1u << ka)) || mbar_test_wait(&bdone[ka], 0))) {
+                barrier_arrive(P.sync + ka);
+                MB200_STAMP(7 + ka);  // 7..10
+                ka++;
+                progress = true;
+            }
+            if (kc < nb && kc < ka) {
+                const int u = kc & 1;
+                if (kc < 2 || mbar_test_wait(&rawempty[u], ((kc >> 1) - 1) & 1)) {
+                    unsigned long long c;
+                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(P.sync + kc) : "memory");
+                    if (c >= (kc == 0 ? tgt[0] : kc == 1 ? tgt[1] : kc == 2 ? tgt[2] : tgt[3])) {
+                        MB200_STAMP(11 + kc);  // 11..14
+                        // the rows were stored through the generic proxy (by other SMs); the bulk copy reads through the async proxy
+                        asm volatile("fence.proxy.async.global;" ::: "memory");
+                        const int j0 = kc * kBatchSlots, jn = min(kBatchSlots, n_act - j0);
+                        uint8_t *dst = smem + P.off_raw + u * P.raw_bytes;
+                        mbar_expect_tx(&rawfull[u], jn * vec_bytes);
+                        for (int j = 0; j < jn; j++)
+                            bulk_g2s(dst + (size_t)j * vec_bytes, P.act + (size_t)act_list[j0 + j] * P.EFF, vec_bytes,
+                                     &rawfull[u]);
+                        kc++;
+                        progress = true;
+                    }
+                }
+            }
+            if (!progress) __nanosleep(64);
+        }
+        if (ka < nb || kc < nb) {
+            *abort_flag = 1;
+            atomicExch(P.err, MB200_ERR_TIMEOUT);
+        }
+        return;
     }
-    tgt0 = __shfl_sync(0xffffffffu, tgt0, 0);
-    tgt1 = __shfl_sync(0xffffffffu, tgt1, 0);
+
+    // ---------------- consumer warps ----------------
     if (P.pdl) stream::grid_dep_wait();  // x is produced upstream; act / y may still be in use there
     const Layout LB = stream::layout<Q4>(P.bprB, 0, 0, 1, 1);
     const Layout LC = stream::layout<FD>(P.bprC, 0, 0, 1, 1);
@@ -416,13 +459,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         }
         return;
     }
-    walk.init(P, act_list, n_act);
-    const int n0 = walk.n0;
-    const int n_sync = n_act > n0 ? 2 : 1;  // batches whose activations get staged (one named barrier each)
-    if (tid == 0) {  // a CTA without tiles in a batch still has to arrive at that batch's barrier
-        if (!walk.has_batch(0)) barrier_arrive(P.sync);
-        if (n_act > n0 && !walk.has_batch(1)) barrier_arrive(P.sync + 1);
-    }
+    walk.init(P, tiles, *n_tiles_p, act_list, n_act);
+    const int nb = (n_act + kBatchSlots - 1) / kBatchSlots;  // one device-wide barrier and one staging step each
 
     const int q = lane >> 2, sub = lane & 3;
     FTile t, nt;
@@ -446,6 +484,47 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         return __shfl_sync(0xffffffffu, old, 0) == kConsumers - 1;
     };
 
+    // Activation staging, spread over the consumer warps and over time: whenever a batch's fp32 vectors
+    // have landed in shared memory (courier), a warp that passes a tile boundary splits its share of
+    // them -- columns [128 w, 128 w + 128) of each vector -- into the int8 levels of the down phase.
+    // By the time the batch's first down tile comes up all twelve shares are normally long done.
+    int n_q = 0;  // batches this warp has done its share of
+    auto stage_share = [&](bool blocking) {
+        while (n_q < nb) {
+            const int u = n_q & 1, par = (n_q >> 1) & 1;
+            if (blocking) {
+                if (!mbar_wait(&rawfull[u], par)) {
+                    *abort_flag = 1;
+                    return;
+                }
+            } else if (!mbar_test_wait(&rawfull[u], par)) {
+                return;
+            }
+            const int pitch = FD::kSlotsPerBlock * P.bprC + 1;
+            const int j0 = n_q * kBatchSlots, jn = min(kBatchSlots, n_act - j0);
+            const float *raw = reinterpret_cast<const float *>(smem + P.off_raw + u * P.raw_bytes);
+            for (int c0 = warp * 128 + lane * 4; c0 < P.EFF; c0 += kConsumers * 128) {
+#pragma unroll
+                for (int j = 0; j < kBatchSlots; j++) {
+                    if (j < jn) {
+                        const float4 v = *reinterpret_cast<const float4 *>(raw + (size_t)j * P.EFF + c0);
+                        uint8_t *xc = smem + P.off_xc + (j0 + j) * P.xc_stride - kXBase;
+                        split_store<FD>(v, c0, lane, pitch, reinterpret_cast<uint32_t *>(xc + LC.xq1),
+                                        reinterpret_cast<uint32_t *>(xc + LC.xq2), reinterpret_cast<float *>(xc + LC.xs1),
+                                        reinterpret_cast<float *>(xc + LC.xsum));
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&xready[n_q]);   // release: this warp's share of the levels is visible to whoever waits
+                mbar_arrive(&rawempty[u]);   // and it no longer reads the raw buffer
+            }
+            n_q++;
+            if (blocking) return;
+        }
+    };
+
     // ---- gate/up: warp i of column group g takes gate rows 2i, 2i+1 and up rows 2i, 2i+1 of every tile ----
     {
         const int gB = warp / P.wpgB, iB = warp % P.wpgB;
@@ -457,6 +536,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         const uint32_t off_g = 2 * iB * row_bytes + lane_off, off_u = (P.TB + 2 * iB) * row_bytes + lane_off;
         int k = 0;
         while (have && t.phase == 0) {
+            stage_share(false);
             const bool hn = walk.next(P, nt);
             if (!mbar_wait(&full[s], ph)) *abort_flag = 1;
             if (warp == 0 && k < 8) MB200_STAMP(16 + k);
@@ -478,16 +558,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(&full[s]);  // the stage's partial sums may be rewritten
-                    if (t.last) {
-                        // Every act row this CTA owes to the batch is stored: arrive at the batch's barrier.
-                        // The finishing warps of a CTA are ordered one after the other through the stage
-                        // counters (block-scope fences), so the release also covers the rows they stored.
-                        barrier_arrive(P.sync + t.batch);
-                        MB200_STAMP(7 + t.batch);
-                    }
+                    // Every act row this CTA owes to the batch is stored: tell the courier. The finishing
+                    // warps of a CTA are ordered one after the other through the stage counters (block-scope
+                    // fences), so the courier's release also covers the rows the earlier ones stored.
+                    if (t.last) mbar_arrive(&bdone[t.batch]);
                 }
             }
-            if (*abort_flag) break;  // no early return: every consumer warp must reach the named barrier below
+            if (*abort_flag) break;
             if (++s == S) {
                 s = 0;
                 ph ^= 1;
@@ -512,13 +589,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         int cur_j = -1;
         int k = 0;
         while (have) {
-            if (n_staged == 0 && t.j == 0) {
-                stage_batch<FD>(P, smem, act_list, 0, n0, P.sync, tgt0, abort_flag, 9);
-                n_staged = 1;
-            }
-            if (n_staged == 1 && n_sync == 2 && t.j == n0) {
-                stage_batch<FD>(P, smem, act_list, n0, n_act - n0, P.sync + 1, tgt1, abort_flag, 11);
-                n_staged = 2;
+            stage_share(false);
+            if (n_staged < nb && t.j == n_staged * kBatchSlots) {  // first down tile of a batch: are its levels staged?
+                if (warp == 0) MB200_STAMP(32 + 2 * n_staged);
+                while (n_q <= n_staged && !*abort_flag) stage_share(true);  // this warp's own share first
+                if (!*abort_flag && !mbar_wait(&xready[n_staged], 0)) *abort_flag = 1;
+                if (warp == 0) MB200_STAMP(33 + 2 * n_staged);
+                n_staged++;
             }
             if (*abort_flag) break;
             if (t.j != cur_j) {
@@ -559,10 +636,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             have = hn;
             t = nt;
         }
-    }
-    while (n_staged < n_sync) {  // a warp that gave up early still owes the other warps its barrier arrivals
-        consumers_sync();
-        n_staged++;
     }
     if (*abort_flag && lane == 0) atomicExch(P.err, MB200_ERR_TIMEOUT);
     if (warp == 0) MB200_STAMP(5);
@@ -625,6 +698,10 @@ static bool fused_plan(FusedParams &P, int &smem_bytes)
     if (P.ngB > kConsumers || kConsumers % P.ngB) return false;
     P.wpgB = kConsumers / P.ngB;
     P.TB = 2 * P.wpgB;
+    {   // the issuer warp lists the CTA's gate/up tiles with one lane per tile
+        const int tpe = (EFF + P.TB - 1) / P.TB;
+        if ((P.n_slots * tpe + kSMs - 1) / kSMs + kFusedMaxBatches > kFusedMaxTiles) return false;
+    }
     int v = 1;
     while (v * 2 <= 8 && P.bprC % (v * 2) == 0) v *= 2;
     if (v < 2) return false;
@@ -634,7 +711,7 @@ static bool fused_plan(FusedParams &P, int &smem_bytes)
     if (P.ngC > kConsumers || kConsumers % P.ngC) return false;
     P.wpgC = kConsumers / P.ngC;
     P.TC = P.wpgC * P.rppC * 2;
-    if (P.TC > 64) P.TC = 64;  // the epilogue keeps two running sums per lane
+    if (P.TC > 32) P.TC = 32;  // one running sum per lane of the finishing warp
     return true;
 }
 
@@ -648,7 +725,7 @@ static bool fused_layout(FusedParams &P, int &smem_bytes)
     P.stage_bytes = ((tileB > tileC ? tileB : tileC) + 127) & ~127;
     const Layout LB = stream::layout<Q4>(P.bprB, 0, 0, 1, 1);
     const Layout LC = stream::layout<FD>(P.bprC, 0, 0, 1, 1);
-    int o = 512;
+    int o = kCtrlBytes;
     P.off_xb = o;
     o += LB.x_stride;
     P.off_xc = o;
@@ -657,13 +734,15 @@ static bool fused_layout(FusedParams &P, int &smem_bytes)
     const int pB = 2 * P.TB * P.ngB, pC = P.TC * P.ngC;
     P.part_pitch = pB > pC ? pB : pC;
     P.off_part = o;
+    P.raw_bytes = kBatchSlots * P.EFF * 4;
     for (int S = kFusedMaxStages; S >= 3; S--) {
         int t = o + S * P.part_pitch * 4;
         t = (t + 127) & ~127;
-        if (t + S * P.stage_bytes <= 227 * 1024) {
+        if (t + S * P.stage_bytes + 2 * P.raw_bytes <= 227 * 1024) {
             P.stages = S;
             P.off_stages = t;
-            smem_bytes = t + S * P.stage_bytes;
+            P.off_raw = t + S * P.stage_bytes;
+            smem_bytes = P.off_raw + 2 * P.raw_bytes;
             return true;
         }
     }

@@ -1,0 +1,181 @@
+"""The one-launch routed-expert kernel (mb200_moe_experts_fused) against the two-launch path
+(mb200_moe_gate_up_local + mb200_moe_down_local, itself checked against the oracle in
+test_gpu_moe.py) and against the CPU oracle's expert sequence (src/forward.c:1122-1142)."""
+import numpy as np
+import pytest
+import torch
+
+from mnemocuda_b200 import synth
+from oracle import oracle
+from tests.gpu_util import dev, host
+
+pytestmark = pytest.mark.gpu
+
+INT_MAX = 0x7FFFFFFF
+
+
+@pytest.fixture(scope="module")
+def K():
+    from mnemocuda_b200 import kernels
+    kernels.mb200_init()
+    yield kernels
+    torch.cuda.synchronize()
+    assert kernels.mb200_device_error() == 0
+
+
+def make_experts(seed, NE, H, EFF, down_type):
+    g, u, d = synth.expert_sizes(H, EFF, down_type)
+    blob = np.concatenate([synth.expert_blob(seed * 1000 + e, H, EFF, down_type) for e in range(NE)])
+    return blob, g + u + d, g, u
+
+
+def two_launch(K, d_exp, stride, g, u, down_type, ids, wts, k, lo, cnt, x, res, y, H, EFF):
+    act = torch.full((k, EFF), float("nan"), device="cuda")
+    K.mb200_moe_gate_up_local(d_exp, stride, 0, g, ids, k, lo, cnt, x, act, EFF, H)
+    K.mb200_moe_down_local(d_exp, stride, g + u, down_type, ids, wts, k, lo, cnt, act, res, y, H, EFF)
+    return act
+
+
+def fused(K, d_exp, stride, g, u, down_type, ids, wts, k, lo, cnt, x, res, y, H, EFF, sync):
+    act = torch.full((k, EFF), float("nan"), device="cuda")
+    K.mb200_moe_experts_fused(d_exp, stride, 0, g, g + u, down_type, ids, wts, k, lo, cnt, x, act, res, y, H, EFF, sync)
+    return act
+
+
+@pytest.mark.parametrize("H,EFF,down_type,slots", [
+    (4096, 1536, 14, [3, 7, 1, 5, 0, 6, 2, 4]),   # Qwen3-235B expert shape (benchmark config 2)
+    (4096, 1536, 12, [3, 7, 1, 5, 0, 6, 2, 4]),   # Q4_K down
+    (4096, 1536, 14, [5, 2, 6]),                  # three slots: an odd batch
+    (4096, 1536, 14, [4]),                        # one slot: a single batch
+    (4096, 1536, 14, [1, -1, 3, -1, 0, 2, -1, 7]),  # empty slots in between
+    (2048, 512, 14, [0, 3, 2, 1, 5, 4]),          # one gate/up column group, 24-row tiles; narrow down rows
+    (2048, 1024, 12, [2, 0, 1, 3]),
+    (6144, 1024, 14, [1, 0, 2, 3]),               # three gate/up column groups; two row chunks per CTA in the down phase
+])
+def test_fused_matches_two_launch_path_and_oracle(K, H, EFF, down_type, slots):
+    NE = 8
+    k = len(slots)
+    experts, stride, g, u = make_experts(21, NE, H, EFF, down_type)
+    x = synth.normal_f32(31, H)
+    res = synth.normal_f32(32, H)
+    w = np.abs(synth.normal_f32(33, k)) + 0.05
+    w[np.array(slots) < 0] = 0.0
+    w = (w / w.sum()).astype(np.float32)
+    d_exp, d_x, d_res = dev(experts), dev(x), dev(res)
+    ids, wts = dev(np.array(slots, np.int32)), dev(w)
+    sync = torch.zeros(4, dtype=torch.int64, device="cuda")
+    y_ref = torch.full((H,), float("nan"), device="cuda")
+    act_ref = two_launch(K, d_exp, stride, g, u, down_type, ids, wts, k, 0, INT_MAX, d_x, d_res, y_ref, H, EFF)
+    for rep in range(3):  # the barrier counters carry over from launch to launch
+        y = torch.full((H,), float("nan"), device="cuda")
+        act = fused(K, d_exp, stride, g, u, down_type, ids, wts, k, 0, INT_MAX, d_x, d_res, y, H, EFF, sync)
+        torch.cuda.synchronize()
+        assert K.mb200_device_error() == 0
+        for s, e in enumerate(slots):
+            if e >= 0:
+                np.testing.assert_allclose(host(act[s]), host(act_ref[s]), rtol=1e-5, atol=1e-6 * float(act_ref[s].abs().max()))
+            else:
+                assert torch.isnan(act[s]).all()  # skipped slots are never written
+        a, b = host(y).astype(np.float64), host(y_ref).astype(np.float64)
+        assert np.linalg.norm(a - b) <= 1e-5 * np.linalg.norm(b)
+    n_served = sum(e >= 0 for e in slots)
+    assert host(sync).tolist()[: (n_served + 1) // 2] == [3 * 148] * ((n_served + 1) // 2)
+    # the oracle's expert sequence on the same routing
+    moe = np.zeros(H, np.float32)
+    for s, e in enumerate(slots):
+        if e >= 0:
+            moe = oracle.expert_fwd(experts[e * stride:(e + 1) * stride], g, u, H, EFF, down_type, float(w[s]), x, moe)
+    want = res.astype(np.float64) + moe
+    assert np.linalg.norm(a - want) / np.linalg.norm(want) <= 1e-3
+
+
+def test_fused_without_served_experts_copies_the_residual(K):
+    H, EFF, NE = 4096, 1536, 4
+    experts, stride, g, u = make_experts(22, NE, H, EFF, 14)
+    d_exp = dev(experts)
+    ids, wts = dev(np.array([-1, -1, -1, -1], np.int32)), dev(np.zeros(4, np.float32))
+    x, res = dev(synth.normal_f32(1, H)), dev(synth.normal_f32(2, H))
+    sync = torch.zeros(4, dtype=torch.int64, device="cuda")
+    y = torch.full((H,), float("nan"), device="cuda")
+    fused(K, d_exp, stride, g, u, 14, ids, wts, 4, 0, INT_MAX, x, res, y, H, EFF, sync)
+    assert torch.equal(y, res)
+    assert host(sync).tolist() == [0, 0, 0, 0]
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_expert_shards_sum_to_the_full_block(K, world):
+    """Every rank of an expert partition in turn on one GPU: partial hidden vectors, no residual on ranks > 0."""
+    from mnemocuda_b200 import sharded
+    H, EFF, NE, k = 4096, 1536, 8, 8
+    experts, stride, g, u = make_experts(23, NE, H, EFF, 14)
+    d_exp = dev(experts)
+    slots = [6, 1, 3, 7, 0, 2, 5, 4]
+    w = np.full(k, 0.125, np.float32)
+    ids, wts = dev(np.array(slots, np.int32)), dev(w)
+    x, res = dev(synth.normal_f32(3, H)), dev(synth.normal_f32(4, H))
+    y_full = torch.empty(H, device="cuda")
+    two_launch(K, d_exp, stride, g, u, 14, ids, wts, k, 0, INT_MAX, x, res, y_full, H, EFF)
+    total = torch.zeros(H, dtype=torch.float64, device="cuda")
+    zero = torch.zeros(H, device="cuda")
+    sync = torch.zeros(4, dtype=torch.int64, device="cuda")
+    for rank in range(world):
+        lo, hi = sharded.expert_range(NE, world, rank)
+        part = torch.full((H,), float("nan"), device="cuda")
+        fused(K, d_exp[lo * stride:], stride, g, u, 14, ids, wts, k, lo, hi - lo, x, res if rank == 0 else zero, part, H,
+              EFF, sync)
+        assert torch.isfinite(part).all()
+        total += part.double()
+    a, b = host(total), host(y_full).astype(np.float64)
+    assert np.linalg.norm(a - b) <= 2e-6 * np.linalg.norm(b)
+
+
+def test_fused_accumulates_into_y_without_residual(K):
+    H, EFF, NE, k = 4096, 1536, 4, 2
+    experts, stride, g, u = make_experts(24, NE, H, EFF, 14)
+    d_exp = dev(experts)
+    ids, wts = dev(np.array([2, 1], np.int32)), dev(np.array([0.75, 0.25], np.float32))
+    x = dev(synth.normal_f32(5, H))
+    y0 = synth.normal_f32(6, H)
+    y_a, y_b = dev(y0.copy()), dev(y0.copy())
+    sync = torch.zeros(4, dtype=torch.int64, device="cuda")
+    two_launch(K, d_exp, stride, g, u, 14, ids, wts, k, 0, INT_MAX, x, None, y_a, H, EFF)
+    fused(K, d_exp, stride, g, u, 14, ids, wts, k, 0, INT_MAX, x, None, y_b, H, EFF, sync)
+    a, b = host(y_b).astype(np.float64), host(y_a).astype(np.float64)
+    assert np.linalg.norm(a - b) <= 1e-5 * np.linalg.norm(b)
+
+
+def test_fused_reports_unsupported_shapes_and_launches_nothing(K):
+    H, EFF, NE, k = 512, 256, 2, 2   # H / 256 is not a multiple of 8: outside the fused kernel's geometry
+    experts, stride, g, u = make_experts(25, NE, H, EFF, 14)
+    ids, wts = dev(np.array([0, 1], np.int32)), dev(np.array([0.5, 0.5], np.float32))
+    x, res = dev(synth.normal_f32(7, H)), dev(synth.normal_f32(8, H))
+    y = torch.full((H,), 7.0, device="cuda")
+    act = torch.zeros(k, EFF, device="cuda")
+    sync = torch.zeros(4, dtype=torch.int64, device="cuda")
+    with pytest.raises(RuntimeError, match="status 4"):
+        K.mb200_moe_experts_fused(dev(experts), stride, 0, g, g + u, 14, ids, wts, k, 0, INT_MAX, x, act, res, y, H, EFF, sync)
+    assert float(y.min()) == 7.0 and float(y.max()) == 7.0
+
+
+def test_block_gives_the_same_result_with_and_without_the_fused_kernel(K):
+    NE, k, H, EFF = 16, 8, 4096, 1536
+    g, u, d = synth.expert_sizes(H, EFF, 14)
+    experts, stride, g, u = make_experts(26, NE, H, EFF, 14)
+    router = synth.normal_f32(41, NE * H, 1.0 / np.sqrt(H))
+    x, res = synth.normal_f32(42, H), synth.normal_f32(43, H)
+    d_r, d_e, d_x, d_res = dev(router), dev(experts), dev(x), dev(res)
+    n = K.mb200_router_scratch_bytes(NE)
+    outs = []
+    try:
+        for on in (False, True):
+            K.mb200_set_fused(on)
+            scratch = torch.zeros((n + 15) // 16 * 16, dtype=torch.uint8, device="cuda")
+            ids = torch.empty(k, dtype=torch.int32, device="cuda"); wts = torch.empty(k, device="cuda")
+            act = torch.empty(k, EFF, device="cuda"); out = torch.empty(H, device="cuda")
+            for _ in range(2):
+                K.mb200_moe_block(d_r, d_e, stride, g, u, 14, NE, k, H, EFF, d_x, d_res, out, ids, wts, act, scratch)
+            torch.cuda.synchronize()
+            outs.append(host(out).astype(np.float64))
+    finally:
+        K.mb200_set_fused(True)
+    assert np.linalg.norm(outs[0] - outs[1]) <= 1e-5 * np.linalg.norm(outs[0])
