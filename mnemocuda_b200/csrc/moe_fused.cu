@@ -35,6 +35,22 @@
 #include "q4k_policy.cuh"
 #include "q6k_policy.cuh"
 
+#if defined(MB200_TRACE) && defined(MB200_WARPTRACE)
+// Developer aid: four stamps per consumer warp instead of the per-CTA phase stamps.
+#undef MB200_STAMP
+#define MB200_STAMP(slot) do {} while (0)
+#define MB200_WSTAMP(i)                                                                   \
+    do {                                                                                  \
+        if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) < 12) {                         \
+            long long t__;                                                                \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                       \
+            ::mb200::stream::g_trace[blockIdx.x][(threadIdx.x >> 5) * 4 + (i)] = t__;     \
+        }                                                                                 \
+    } while (0)
+#else
+#define MB200_WSTAMP(i) do {} while (0)
+#endif
+
 namespace mb200 {
 
 int pdl_enabled();
@@ -47,6 +63,7 @@ using stream::Layout;
 constexpr int kFusedMaxSlots = 8;
 constexpr int kFusedMaxStages = 6;
 constexpr int kFusedThreads = (kConsumers + 2) * 32;  // 12 consumer warps + tile issuer + courier
+constexpr int kSrcAlign = 128;                         // down-phase copies start on a 128-byte line
 constexpr int kBatchSlots = 2;                         // served slots per batch
 constexpr int kFusedMaxBatches = kFusedMaxSlots / kBatchSlots;
 constexpr int kFusedMaxTiles = 16;  // gate/up tiles per CTA (one lane of the issuer warp lists each)
@@ -78,6 +95,7 @@ struct FTile {
     int phase;  // 0: gate/up pair rows, 1: down rows
     int batch;  // gate/up: which half of the served slots the tile belongs to
     int last;   // gate/up: the CTA's last tile of that batch
+    int idx;    // gate/up: position in the CTA's tile list
     int j;      // position of the slot among the slots served here
     int slot;   // expert slot (index into ids / wts / act)
     int row0, rows;
@@ -97,7 +115,7 @@ __device__ __forceinline__ unsigned long long barrier_target(const unsigned long
 // between the warps that finished the CTA's tiles) is visible to whoever acquires the counter.
 __device__ __forceinline__ void barrier_arrive(unsigned long long *ctr)
 {
-    asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(ctr) : "memory");
+    asm volatile("red.relaxed.gpu.global.add.u64 [%0], 1;" ::"l"(ctr) : "memory"); // EXPERIMENT
 }
 // The CTA's tiles in issue order. Every role runs the same walk.
 //
@@ -129,6 +147,7 @@ struct FWalk {
     __device__ __forceinline__ bool next(const FusedParams &P, FTile &t)
     {
         if (bi < n_b) {
+            t.idx = bi;
             const int2 d = tiles[bi++];
             t.phase = 0;
             t.slot = d.x & 15;
@@ -215,11 +234,12 @@ __device__ __forceinline__ void issue(const FusedParams &P, const FTile &t, uint
         bulk_g2s(stage, e + P.off_gate, half, bar);
         bulk_g2s(stage + (size_t)P.TB * row_bytes, e + P.off_up, half, bar);  // up rows at a fixed offset: row slot TB + r
     } else {
-        // the 16-byte-aligned span enclosing the rows (Q6_K rows are only 2-byte aligned); the bytes read
-        // before / after them share a 16-byte granule with a valid byte, hence lie inside a mapped page
+        // The span enclosing the rows, from the 128-byte line the first row starts in to the 16-byte granule
+        // the last one ends in (Q6_K rows are only 2-byte aligned). The bytes read before / after the rows
+        // share a line / granule with a valid byte, hence lie inside a mapped page.
         const uintptr_t begin = reinterpret_cast<uintptr_t>(down_src<FD>(P, t, sid));
         const uintptr_t stop = begin + (size_t)t.rows * P.bprC * FD::kBlockBytes;
-        const uintptr_t a0 = begin & ~static_cast<uintptr_t>(15);
+        const uintptr_t a0 = begin & ~static_cast<uintptr_t>(kSrcAlign - 1);
         const uint32_t bytes = static_cast<uint32_t>(((stop + 15) & ~static_cast<uintptr_t>(15)) - a0);
         mbar_expect_tx(bar, bytes);
         bulk_g2s(stage, reinterpret_cast<const void *>(a0), bytes, bar);
@@ -262,8 +282,11 @@ __device__ __forceinline__ void split_store(const float4 t, int c0, int lane, in
     }
 }
 
-// Finishes a gate/up tile: sums the column groups, SwiGLU, stores the act rows.
-__device__ __forceinline__ void finish_gate_up(const FusedParams &P, const FTile &t, const float *pt, int lane)
+// Finishes a gate/up tile: sums the column groups, SwiGLU, and leaves the act rows in the CTA's outbox
+// (shared memory). The courier stores them to global memory: a consumer warp never touches global
+// memory, where every access queues behind the weight stream for microseconds.
+__device__ __forceinline__ void finish_gate_up(const FusedParams &P, const FTile &t, const float *pt, float *outbox,
+                                               int lane)
 {
     if (lane < t.rows) {
         const int NG = P.ngB;
@@ -272,7 +295,7 @@ __device__ __forceinline__ void finish_gate_up(const FusedParams &P, const FTile
             g += pt[lane * NG + c];
             u += pt[(P.TB + lane) * NG + c];
         }
-        P.act[(size_t)t.slot * P.EFF + t.row0 + lane] = g / (1.0f + expf(-g)) * u;
+        outbox[t.idx * 32 + lane] = g / (1.0f + expf(-g)) * u;
     }
 }
 
@@ -315,6 +338,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     uint64_t *xready = reinterpret_cast<uint64_t *>(smem + 296);    // [4] the int8 levels of batch k are staged (all shares)
     float *run = reinterpret_cast<float *>(smem + 328);    // down: running sums of the tile's rows over the slots (<= 32)
     float *part = reinterpret_cast<float *>(smem + P.off_part);
+    // act rows of the CTA's gate/up tiles (32 floats per tile) on their way to global memory. Lives where x was
+    // staged: every consumer warp has its x in registers before the first tile can be finished.
+    float *outbox = reinterpret_cast<float *>(smem + P.off_xb);
     uint8_t *stages = smem + P.off_stages;
     const int S = P.stages;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -346,13 +372,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         if (lane == 0) {
             *n_act_p = n;
             walk.init(P, tiles, *n_tiles_p, act_list, n);
-            MB200_STAMP(40);
             FTile t;
             for (int s = 0; s < S; s++) {
                 mbar_arrive(&full[s]);  // first phase: no partial sums to drain yet
                 if (walk.next(P, t)) issue<FD>(P, t, stages + (size_t)s * P.stage_bytes, &full[s], sid);
             }
-            MB200_STAMP(41);
         }
         __syncthreads();
         if (lane == 0) {
@@ -368,8 +392,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
                 }
                 if (*abort_flag) break;
                 issue<FD>(P, t, stages + (size_t)s * P.stage_bytes, &full[s], sid);
-                if (ik < 6) MB200_STAMP(42 + ik);
-                ik++;
+                if (t.phase == 1) {
+                    if (ik < 8) MB200_STAMP(40 + ik);  // issue time of the down tiles
+                    ik++;
+                }
                 if (++s == S) {
                     s = 0;
                     ph ^= 1;
@@ -403,6 +429,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             if (*abort_flag) return;
             bool progress = false;
             if (ka < nb && (!(present & (1u << ka)) || mbar_test_wait(&bdone[ka], 0))) {
+                const int nt = *n_tiles_p;
+                for (int i = 0; i < nt; i++) {  // this CTA's act rows of the batch: outbox -> global
+                    const int2 d = tiles[i];
+                    if (((d.x >> 8) & 15) != ka) continue;
+                    float *dst = P.act + (size_t)(d.x & 15) * P.EFF + d.y;
+                    const int rows = d.x >> 16;
+                    for (int r = 0; r < rows; r++) dst[r] = outbox[i * 32 + r];
+                }
                 barrier_arrive(P.sync + ka);
                 MB200_STAMP(7 + ka);  // 7..10
                 ka++;
@@ -539,7 +573,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             stage_share(false);
             const bool hn = walk.next(P, nt);
             if (!mbar_wait(&full[s], ph)) *abort_flag = 1;
-            if (warp == 0 && k < 8) MB200_STAMP(16 + k);
             k++;
             const uint8_t *st = stages + (size_t)s * P.stage_bytes;
             float acc[4];
@@ -554,13 +587,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             if ((lane & 7) == 0) pt[((which & 2 ? P.TB : 0) + 2 * iB + (which & 1)) * P.ngB + gB] = sum;
             if (stored_last(s)) {
                 __syncwarp();  // lane 0's acquire covers the whole warp
-                finish_gate_up(P, t, pt, lane);
+                finish_gate_up(P, t, pt, outbox, lane);
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(&full[s]);  // the stage's partial sums may be rewritten
-                    // Every act row this CTA owes to the batch is stored: tell the courier. The finishing
+                    // Every act row this CTA owes to the batch is in the outbox: tell the courier. The finishing
                     // warps of a CTA are ordered one after the other through the stage counters (block-scope
-                    // fences), so the courier's release also covers the rows the earlier ones stored.
+                    // fences), so the courier also sees the rows the earlier ones left there.
                     if (t.last) mbar_arrive(&bdone[t.batch]);
                 }
             }
@@ -574,6 +607,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         }
     }
     if (warp == 0) MB200_STAMP(2);
+    MB200_WSTAMP(0);
 
     int n_staged = 0;
 
@@ -595,6 +629,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
                 while (n_q <= n_staged && !*abort_flag) stage_share(true);  // this warp's own share first
                 if (!*abort_flag && !mbar_wait(&xready[n_staged], 0)) *abort_flag = 1;
                 if (warp == 0) MB200_STAMP(33 + 2 * n_staged);
+                if (n_staged == 0) MB200_WSTAMP(1);
                 n_staged++;
             }
             if (*abort_flag) break;
@@ -603,8 +638,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
                 FD::load_xregs(xr, smem + P.off_xc + cur_j * P.xc_stride - kXBase, LC, P.bprC, colC, sub, true);
             }
             uint32_t skew = 0;
-            if (FD::kBlockBytes % 16 != 0)
-                skew = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(down_src<FD>(P, t, sid)) & 15);
+            if (FD::kBlockBytes % kSrcAlign != 0)
+                skew = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(down_src<FD>(P, t, sid)) & (kSrcAlign - 1));
             const bool hn = walk.next(P, nt);
             if (!mbar_wait(&full[s], ph)) *abort_flag = 1;
             if (warp == 0 && k < 8) MB200_STAMP(24 + k);
@@ -622,6 +657,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             const int row = which ? rb : ra;
             float *pt = part + s * P.part_pitch;
             if ((lane & (W / 2 - 1)) == 0 && row < t.rows) pt[row * P.ngC + gC] = sum;
+            if (k <= 2) MB200_WSTAMP(1 + k);
             if (stored_last(s)) {
                 __syncwarp();
                 finish_down(P, t, pt, run, swt[t.slot], n_act, lane);
@@ -721,7 +757,7 @@ static bool fused_layout(FusedParams &P, int &smem_bytes)
     const int per_cta = (P.H + kSMs - 1) / kSMs;
     const int c_rows = per_cta < P.TC ? per_cta : P.TC;
     const int tileB = 2 * P.TB * P.bprB * kQ4KBlock;
-    const int tileC = c_rows * P.bprC * FD::kBlockBytes + 32;  // + alignment skew, word over-read
+    const int tileC = c_rows * P.bprC * FD::kBlockBytes + kSrcAlign + 32;  // + alignment skew, word over-read
     P.stage_bytes = ((tileB > tileC ? tileB : tileC) + 127) & ~127;
     const Layout LB = stream::layout<Q4>(P.bprB, 0, 0, 1, 1);
     const Layout LC = stream::layout<FD>(P.bprC, 0, 0, 1, 1);
