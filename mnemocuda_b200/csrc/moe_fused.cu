@@ -115,7 +115,7 @@ __device__ __forceinline__ unsigned long long barrier_target(const unsigned long
 // between the warps that finished the CTA's tiles) is visible to whoever acquires the counter.
 __device__ __forceinline__ void barrier_arrive(unsigned long long *ctr)
 {
-    asm volatile("red.relaxed.gpu.global.add.u64 [%0], 1;" ::"l"(ctr) : "memory"); // EXPERIMENT
+    asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(ctr) : "memory");
 }
 // The CTA's tiles in issue order. Every role runs the same walk.
 //
