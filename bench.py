@@ -38,6 +38,8 @@ WORKLOAD = ("configs[1]: MoE expert block, batch 1, Qwen3-235B shape -- router f
 # dram__bytes_read.sum + dram__bytes_write.sum of one routed gate/up launch (8 experts, 56 623 104
 # algorithmic bytes), from the ncu capture summarised in profiles/; None until captured.
 GATE_UP_TRAFFIC_BYTES = 56726784 + 569088  # profiles/moe_block_stream_kernels_ncu.md
+# same for one launch of the fused routed-expert kernel (98 041 856 algorithmic bytes); None until captured
+FUSED_TRAFFIC_BYTES = None
 
 
 def measured_peaks():
@@ -203,6 +205,7 @@ def run_ours(args):
     else:
         moe = ResidentMoE(shape, layers, dev, seed=1)
     K.mb200_set_pdl(not args.no_pdl)
+    K.mb200_set_fused(not args.no_fused)
     H = shape.H
     xs = torch.empty(layers, H, device=dev)
     rs = torch.empty(layers, H, device=dev)
@@ -267,8 +270,13 @@ def run_ours(args):
             gu_ms = timed_graph(lambda i: moe.gate_up(i % layers, xs[i % layers]), args.steps, args.warmup)
             dn_ms = timed_graph(lambda i: moe.down(i % layers, rs[i % layers], outs[i % layers]), args.steps, args.warmup)
             rt_ms = timed_graph(lambda i: moe.route(i % layers, xs[i % layers]), args.steps, args.warmup)
+            try:
+                fu_ms = timed_graph(lambda i: moe.experts_fused(i % layers, xs[i % layers], rs[i % layers], outs[i % layers]),
+                                    args.steps, args.warmup)
+            except RuntimeError:
+                fu_ms = None  # shape outside the fused kernel
         else:
-            gu_ms = dn_ms = rt_ms = None
+            gu_ms = dn_ms = rt_ms = fu_ms = None
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -308,8 +316,14 @@ def run_ours(args):
         return
 
     peak, which = measured_peaks()
+    fused = bool(fu_ms) and not args.no_fused
+    # dominant kernel: the fused routed-expert kernel (gate/up + down of the 8 routed experts in one launch);
+    # with --no-fused the routed gate/up kernel of the three-launch form
     gu_bytes = shape.K * (shape.gate_sz + shape.up_sz) + shape.H * 4 + shape.K * shape.EFF * 4
-    achieved = gu_bytes / (gu_ms * 1e-3) / 1e9 if gu_ms else None
+    dn_bytes = shape.K * shape.down_sz + shape.K * shape.EFF * 4 + 2 * shape.H * 4
+    dom_bytes = gu_bytes + dn_bytes if fused else gu_bytes
+    dom_ms = fu_ms if fused else gu_ms
+    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms else None
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
@@ -320,14 +334,17 @@ def run_ours(args):
                    "parallelism": (f"experts sharded {world}-way (router replicated), NCCL all-reduce of the 16 KB partial hidden vector"
                                    if world > 1 else "single GPU")},
         "clocks": clk.summary(),
-        "gpu_launches": 3 * args.steps,
-        "kernels_ms": {"router_topk": rt_ms, "moe_gate_up": gu_ms, "moe_down": dn_ms},
+        "gpu_launches": (2 if (world == 1 and fused) else 3) * args.steps,
+        "kernels_ms": {"router_topk": rt_ms, "moe_experts_fused": fu_ms, "moe_gate_up": gu_ms, "moe_down": dn_ms},
     }
     if world == 1:
-        line["roofline"] = {"bound": "hbm", "kernel": "stream_kernel<Q4,*> (routed gate/up + SwiGLU, 8 experts per launch)",
-                     "achieved": achieved, "peak": peak, "peak_source": which + " copy bandwidth (MEASURED_PEAKS.json)",
-                     "unit": "GB/s", "frac": achieved / peak, "frac_of_8TBs_nominal": achieved / 8000.0,
-                     "algorithmic_bytes_per_launch": gu_bytes, "traffic": GATE_UP_TRAFFIC_BYTES}
+        line["roofline"] = {"bound": "hbm",
+                            "kernel": ("moe_fused_kernel (routed gate/up + SwiGLU + down + weighted sum, 8 experts, one launch)"
+                                       if fused else "stream_kernel<Q4,*> (routed gate/up + SwiGLU, 8 experts per launch)"),
+                            "achieved": achieved, "peak": peak, "peak_source": which + " copy bandwidth (MEASURED_PEAKS.json)",
+                            "unit": "GB/s", "frac": achieved / peak, "frac_of_8TBs_nominal": achieved / 8000.0,
+                            "algorithmic_bytes_per_launch": dom_bytes,
+                            "traffic": FUSED_TRAFFIC_BYTES if fused else GATE_UP_TRAFFIC_BYTES}
     line["e2e"] = {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": host_block.h2d_bytes,
                    "d2h_bytes_per_step": host_block.d2h_bytes}
     if world == 1 and not args.no_cpu_baseline:
@@ -444,6 +461,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=12, help="resident MoE layers the steps rotate over")
     ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launch")
+    ap.add_argument("--no-fused", action="store_true", help="routed experts as two launches (gate/up, down) instead of the fused kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--workload", default="moe_block", choices=["moe_block", "matvec", "gemm", "prefill"],

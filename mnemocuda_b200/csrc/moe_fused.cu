@@ -62,7 +62,7 @@ using stream::Layout;
 
 constexpr int kFusedMaxSlots = 8;
 constexpr int kFusedMaxStages = 6;
-constexpr int kFusedThreads = (kConsumers + 2) * 32;  // 12 consumer warps + tile issuer + courier
+constexpr int kFusedThreads = (kConsumers + 3) * 32;  // 12 consumer warps + tile issuer + courier + epilogue
 constexpr int kSrcAlign = 128;                         // down-phase copies start on a 128-byte line
 constexpr int kBatchSlots = 2;                         // served slots per batch
 constexpr int kFusedMaxBatches = kFusedMaxSlots / kBatchSlots;
@@ -324,7 +324,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + kFusedMaxStages;
-    int *cnt = reinterpret_cast<int *>(smem + 96);         // per stage: consumer warps that stored their partial sums
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 120);
     int *sid = reinterpret_cast<int *>(smem + 128);        // expert (relative to expert_lo) per slot, -1 = not served
     float *swt = reinterpret_cast<float *>(smem + 160);    // routing weight per slot
@@ -355,7 +354,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             for (int s = 0; s < S; s++) {
                 mbar_init(&full[s], 2);  // the issuer's expect_tx arrival + "the stage's partial sums are free"
                 mbar_init(&empty[s], kConsumers);
-                cnt[s] = 0;
             }
             for (int u = 0; u < 2; u++) {
                 mbar_init(&rawfull[u], 1);
@@ -424,50 +422,98 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             const int nt = *n_tiles_p;
             for (int i = 0; i < nt; i++) present |= 1u << ((tiles[i].x >> 8) & 15);
         }
-        int ka = 0, kc = 0;
-        for (uint32_t it = 0; it < (1u << 22) && (ka < nb || kc < nb); it++) {
-            if (*abort_flag) return;
-            bool progress = false;
-            if (ka < nb && (!(present & (1u << ka)) || mbar_test_wait(&bdone[ka], 0))) {
+        // Pull batch kc's activation vectors into shared memory once every CTA has arrived at its barrier.
+        auto fetch = [&](int kc) -> bool {
+            const int u = kc & 1;
+            if (kc >= 2 && !mbar_wait(&rawempty[u], ((kc >> 1) - 1) & 1)) return false;  // consumers still split batch kc-2
+            const unsigned long long target = kc == 0 ? tgt[0] : kc == 1 ? tgt[1] : kc == 2 ? tgt[2] : tgt[3];
+            bool met = false;
+            for (uint32_t i = 0; i < (1u << 18) && !*abort_flag; i++) {
+                unsigned long long c;
+                asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(P.sync + kc) : "memory");
+                if (c >= target) {
+                    met = true;
+                    break;
+                }
+                __nanosleep(200);
+            }
+            if (!met) return false;
+            MB200_STAMP(11 + kc);  // 11..14
+            // the rows were stored through the generic proxy (by other SMs); the bulk copy reads through the async proxy
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            const int j0 = kc * kBatchSlots, jn = min(kBatchSlots, n_act - j0);
+            uint8_t *dst = smem + P.off_raw + u * P.raw_bytes;
+            mbar_expect_tx(&rawfull[u], jn * vec_bytes);
+            for (int j = 0; j < jn; j++)
+                bulk_g2s(dst + (size_t)j * vec_bytes, P.act + (size_t)act_list[j0 + j] * P.EFF, vec_bytes, &rawfull[u]);
+            return true;
+        };
+        // Batch k: wait (on a shared-memory barrier, no spinning) until this CTA's rows are in the outbox,
+        // store them, arrive; then fetch batch k-1, whose barrier every CTA has passed by now.
+        bool ok = true;
+        for (int k = 0; k < nb && ok; k++) {
+            if (present & (1u << k)) {
+                ok = mbar_wait(&bdone[k], 0);
+                if (!ok) break;
                 const int nt = *n_tiles_p;
                 for (int i = 0; i < nt; i++) {  // this CTA's act rows of the batch: outbox -> global
                     const int2 d = tiles[i];
-                    if (((d.x >> 8) & 15) != ka) continue;
+                    if (((d.x >> 8) & 15) != k) continue;
                     float *dst = P.act + (size_t)(d.x & 15) * P.EFF + d.y;
                     const int rows = d.x >> 16;
                     for (int r = 0; r < rows; r++) dst[r] = outbox[i * 32 + r];
                 }
-                barrier_arrive(P.sync + ka);
-                MB200_STAMP(7 + ka);  // 7..10
-                ka++;
-                progress = true;
             }
-            if (kc < nb && kc < ka) {
-                const int u = kc & 1;
-                if (kc < 2 || mbar_test_wait(&rawempty[u], ((kc >> 1) - 1) & 1)) {
-                    unsigned long long c;
-                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(P.sync + kc) : "memory");
-                    if (c >= (kc == 0 ? tgt[0] : kc == 1 ? tgt[1] : kc == 2 ? tgt[2] : tgt[3])) {
-                        MB200_STAMP(11 + kc);  // 11..14
-                        // the rows were stored through the generic proxy (by other SMs); the bulk copy reads through the async proxy
-                        asm volatile("fence.proxy.async.global;" ::: "memory");
-                        const int j0 = kc * kBatchSlots, jn = min(kBatchSlots, n_act - j0);
-                        uint8_t *dst = smem + P.off_raw + u * P.raw_bytes;
-                        mbar_expect_tx(&rawfull[u], jn * vec_bytes);
-                        for (int j = 0; j < jn; j++)
-                            bulk_g2s(dst + (size_t)j * vec_bytes, P.act + (size_t)act_list[j0 + j] * P.EFF, vec_bytes,
-                                     &rawfull[u]);
-                        kc++;
-                        progress = true;
-                    }
-                }
-            }
-            if (!progress) __nanosleep(64);
+            barrier_arrive(P.sync + k);
+            MB200_STAMP(7 + k);  // 7..10
+            if (k > 0) ok = fetch(k - 1);
         }
-        if (ka < nb || kc < nb) {
+        if (ok && nb > 0) ok = fetch(nb - 1);
+        if (!ok) {
             *abort_flag = 1;
             atomicExch(P.err, MB200_ERR_TIMEOUT);
         }
+        return;
+    }
+
+    if (warp == kConsumers + 2) {
+        // ---------------- epilogue warp ----------------
+        // Finishes every tile once all twelve consumer warps have stored their partial sums. A warp of its
+        // own, so that its latency (a serial chain of shared-memory reads, expf, a division) never delays a
+        // consumer: when consumers took turns at this, each finisher came late to its next tile and the
+        // delay was handed from tile to tile.
+        __syncthreads();
+        const int n_act = *n_act_p;
+        if (n_act == 0) return;
+        walk.init(P, tiles, *n_tiles_p, act_list, n_act);
+        FTile t;
+        int s = 0, ph = 0;
+        int ek = 0;
+        while (walk.next(P, t)) {
+            if (!mbar_wait(&empty[s], ph)) *abort_flag = 1;
+            if (*abort_flag) break;
+            const float *pt = part + s * P.part_pitch;
+            if (t.phase == 0) {
+                finish_gate_up(P, t, pt, outbox, lane);
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&full[s]);  // the stage's partial sums may be rewritten
+                    // every act row this CTA owes to the batch is in the outbox: tell the courier
+                    if (t.last) mbar_arrive(&bdone[t.batch]);
+                }
+            } else {
+                if (ek < 8) MB200_STAMP(16 + ek);  // all consumers done with down tile ek
+                finish_down(P, t, pt, run, swt[t.slot], n_act, lane);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full[s]);
+                ek++;
+            }
+            if (++s == S) {
+                s = 0;
+                ph ^= 1;
+            }
+        }
+        if (*abort_flag && lane == 0) atomicExch(P.err, MB200_ERR_TIMEOUT);
         return;
     }
 
@@ -500,23 +546,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     FTile t, nt;
     int s = 0, ph = 0;
     bool have = walk.next(P, t);
-
-    // After a warp has stored its partial sums of stage s: count it; the warp that completes the
-    // count finishes the tile (the other warps move on to the next tile at once).
-    auto stored_last = [&](int stage) -> bool {
-        int old = 0;
-        __syncwarp();
-        if (lane == 0) {
-            __threadfence_block();
-            old = atomicAdd(&cnt[stage], 1);
-            mbar_arrive(&empty[stage]);  // this warp no longer reads the stage's weights
-            if (old == kConsumers - 1) {
-                cnt[stage] = 0;
-                __threadfence_block();
-            }
-        }
-        return __shfl_sync(0xffffffffu, old, 0) == kConsumers - 1;
-    };
 
     // Activation staging, spread over the consumer warps and over time: whenever a batch's fp32 vectors
     // have landed in shared memory (courier), a warp that passes a tile boundary splits its share of
@@ -585,18 +614,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             const float sum = stream::packed_sum<4, true>(acc, 32, lane, which);
             float *pt = part + s * P.part_pitch;
             if ((lane & 7) == 0) pt[((which & 2 ? P.TB : 0) + 2 * iB + (which & 1)) * P.ngB + gB] = sum;
-            if (stored_last(s)) {
-                __syncwarp();  // lane 0's acquire covers the whole warp
-                finish_gate_up(P, t, pt, outbox, lane);
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&full[s]);  // the stage's partial sums may be rewritten
-                    // Every act row this CTA owes to the batch is in the outbox: tell the courier. The finishing
-                    // warps of a CTA are ordered one after the other through the stage counters (block-scope
-                    // fences), so the courier also sees the rows the earlier ones left there.
-                    if (t.last) mbar_arrive(&bdone[t.batch]);
-                }
-            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);  // partial sums stored, the stage's weights no longer read
             if (*abort_flag) break;
             if (++s == S) {
                 s = 0;
@@ -607,7 +626,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         }
     }
     if (warp == 0) MB200_STAMP(2);
-    MB200_WSTAMP(0);
 
     int n_staged = 0;
 
@@ -629,7 +647,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
                 while (n_q <= n_staged && !*abort_flag) stage_share(true);  // this warp's own share first
                 if (!*abort_flag && !mbar_wait(&xready[n_staged], 0)) *abort_flag = 1;
                 if (warp == 0) MB200_STAMP(33 + 2 * n_staged);
-                if (n_staged == 0) MB200_WSTAMP(1);
                 n_staged++;
             }
             if (*abort_flag) break;
@@ -657,13 +674,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             const int row = which ? rb : ra;
             float *pt = part + s * P.part_pitch;
             if ((lane & (W / 2 - 1)) == 0 && row < t.rows) pt[row * P.ngC + gC] = sum;
-            if (k <= 2) MB200_WSTAMP(1 + k);
-            if (stored_last(s)) {
-                __syncwarp();
-                finish_down(P, t, pt, run, swt[t.slot], n_act, lane);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&full[s]);
-            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
             if (*abort_flag) break;
             if (++s == S) {
                 s = 0;

@@ -56,6 +56,7 @@ class ResidentMoE:
         self.act = torch.zeros(s.K, s.EFF, dtype=torch.float32, device=self.device)
         n = K.mb200_router_scratch_bytes(s.NE)
         self.scratch = torch.zeros((n + 15) // 16 * 16, dtype=torch.uint8, device=self.device)
+        self.fused_sync = torch.zeros(4, dtype=torch.int64, device=self.device)  # barrier counters of experts_fused()
         torch.cuda.synchronize(self.device)
 
     def forward(self, layer: int, x: torch.Tensor, residual: torch.Tensor, out: torch.Tensor, stream=None) -> None:
@@ -74,6 +75,13 @@ class ResidentMoE:
         s = self.shape
         K.mb200_moe_gate_up(self.experts[layer], s.stride, 0, s.gate_sz, self.ids[layer], s.K, x, self.act, s.EFF,
                             s.H, stream)
+
+    def experts_fused(self, layer: int, x: torch.Tensor, residual, out: torch.Tensor, stream=None) -> None:
+        """Routed experts of the ids route() left, in one launch (raises if the shape is outside the fused kernel)."""
+        s = self.shape
+        K.mb200_moe_experts_fused(self.experts[layer], s.stride, 0, s.gate_sz, s.gate_sz + s.up_sz, s.down_type,
+                                  self.ids[layer], self.wts[layer], s.K, self.expert_lo, self.n_local, x, self.act,
+                                  residual, out, s.H, s.EFF, self.fused_sync, stream)
 
     def down(self, layer: int, residual, out: torch.Tensor, stream=None) -> None:
         s = self.shape
