@@ -38,8 +38,8 @@ WORKLOAD = ("configs[1]: MoE expert block, batch 1, Qwen3-235B shape -- router f
 # dram__bytes_read.sum + dram__bytes_write.sum of one routed gate/up launch (8 experts, 56 623 104
 # algorithmic bytes), from the ncu capture summarised in profiles/; None until captured.
 GATE_UP_TRAFFIC_BYTES = 56726784 + 569088  # profiles/moe_block_stream_kernels_ncu.md
-# same for one launch of the fused routed-expert kernel (98 041 856 algorithmic bytes); None until captured
-FUSED_TRAFFIC_BYTES = None
+# same for one launch of the fused routed-expert kernel (98 041 856 algorithmic bytes)
+FUSED_TRAFFIC_BYTES = 98054912 + 3864064  # profiles/moe_fused_kernel_ncu.md
 
 
 def measured_peaks():

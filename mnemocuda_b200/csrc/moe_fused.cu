@@ -35,22 +35,6 @@
 #include "q4k_policy.cuh"
 #include "q6k_policy.cuh"
 
-#if defined(MB200_TRACE) && defined(MB200_WARPTRACE)
-// Developer aid: four stamps per consumer warp instead of the per-CTA phase stamps.
-#undef MB200_STAMP
-#define MB200_STAMP(slot) do {} while (0)
-#define MB200_WSTAMP(i)                                                                   \
-    do {                                                                                  \
-        if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) < 12) {                         \
-            long long t__;                                                                \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                       \
-            ::mb200::stream::g_trace[blockIdx.x][(threadIdx.x >> 5) * 4 + (i)] = t__;     \
-        }                                                                                 \
-    } while (0)
-#else
-#define MB200_WSTAMP(i) do {} while (0)
-#endif
-
 namespace mb200 {
 
 int pdl_enabled();
@@ -64,10 +48,12 @@ constexpr int kFusedMaxSlots = 8;
 constexpr int kFusedMaxStages = 6;
 constexpr int kFusedThreads = (kConsumers + 3) * 32;  // 12 consumer warps + tile issuer + courier + epilogue
 constexpr int kSrcAlign = 128;                         // down-phase copies start on a 128-byte line
+constexpr int kDownPieces = 1;                         // bulk copies per down tile (more made no difference)
 constexpr int kBatchSlots = 2;                         // served slots per batch
 constexpr int kFusedMaxBatches = kFusedMaxSlots / kBatchSlots;
 constexpr int kFusedMaxTiles = 16;  // gate/up tiles per CTA (one lane of the issuer warp lists each)
-constexpr int kCtrlBytes = 592;     // mbarriers, routing tables, running sums, tile list
+constexpr int kCtrlBytes = 656;     // mbarriers, routing tables, running sums, tile list
+constexpr int kFusedMaxCStages = 4;
 constexpr int kXBase = 384;  // stream::layout<> puts the first staged vector at this offset of its base pointer
 
 struct FusedParams {
@@ -88,6 +74,8 @@ struct FusedParams {
     int stages, stage_bytes;
     int off_xb, off_xc, xc_stride, off_part, part_pitch, off_stages;  // shared-memory offsets (bytes; part_pitch in floats)
     int off_raw, raw_bytes;        // two buffers for the fp32 activation vectors of one batch
+    int c_stages, c_stage_bytes;   // the down phase re-cuts the ring into more, smaller stages
+    int off_cpart;                 // partial-sum slots of the down stages
     int pdl;
 };
 
@@ -242,7 +230,10 @@ __device__ __forceinline__ void issue(const FusedParams &P, const FTile &t, uint
         const uintptr_t a0 = begin & ~static_cast<uintptr_t>(kSrcAlign - 1);
         const uint32_t bytes = static_cast<uint32_t>(((stop + 15) & ~static_cast<uintptr_t>(15)) - a0);
         mbar_expect_tx(bar, bytes);
-        bulk_g2s(stage, reinterpret_cast<const void *>(a0), bytes, bar);
+        // several copies in flight per tile: one bulk copy alone does not reach the SM's share of the bandwidth
+        const uint32_t piece = ((bytes / kDownPieces) + 127u) & ~127u;
+        for (uint32_t o = 0; o < bytes; o += piece)
+            bulk_g2s(stage + o, reinterpret_cast<const void *>(a0 + o), min(piece, bytes - o), bar);
     }
 }
 
@@ -330,7 +321,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     int *act_list = reinterpret_cast<int *>(smem + 192);   // slots served here, in slot order
     int *n_act_p = reinterpret_cast<int *>(smem + 224);
     int *n_tiles_p = reinterpret_cast<int *>(smem + 228);
-    int2 *tiles = reinterpret_cast<int2 *>(smem + 456);   // [kFusedMaxTiles] this CTA's gate/up tiles
+    int2 *tiles = reinterpret_cast<int2 *>(smem + 456);
+    uint64_t *cfull = reinterpret_cast<uint64_t *>(smem + 592);    // [4] down-phase stages (re-cut ring)
+    uint64_t *cempty = reinterpret_cast<uint64_t *>(smem + 624);   // [4]
+    float *cpart = reinterpret_cast<float *>(smem + P.off_cpart);
+    const int CS = P.c_stages;   // [kFusedMaxTiles] this CTA's gate/up tiles
     uint64_t *rawfull = reinterpret_cast<uint64_t *>(smem + 232);   // [2] a batch's fp32 activation vectors have landed
     uint64_t *rawempty = reinterpret_cast<uint64_t *>(smem + 248);  // [2] ... and every consumer warp has split its share
     uint64_t *bdone = reinterpret_cast<uint64_t *>(smem + 264);     // [4] this CTA has stored its act rows of batch k
@@ -363,41 +358,56 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
                 mbar_init(&bdone[k], 1);
                 mbar_init(&xready[k], kConsumers);
             }
+            for (int c = 0; c < kFusedMaxCStages; c++) {
+                mbar_init(&cfull[c], 2);
+                mbar_init(&cempty[c], kConsumers);
+            }
             mbar_fence_init();
         }
         if (P.pdl) stream::grid_dep_wait();  // the routed ids come from the upstream kernel
         const int n = build_tiles(P, lane, sid, swt, act_list, tiles, n_tiles_p);
-        if (lane == 0) {
-            *n_act_p = n;
-            walk.init(P, tiles, *n_tiles_p, act_list, n);
-            FTile t;
-            for (int s = 0; s < S; s++) {
-                mbar_arrive(&full[s]);  // first phase: no partial sums to drain yet
-                if (walk.next(P, t)) issue<FD>(P, t, stages + (size_t)s * P.stage_bytes, &full[s], sid);
-            }
-        }
+        if (lane == 0) *n_act_p = n;
         __syncthreads();
         if (lane == 0) {
             if (P.pdl) stream::grid_dep_launch();
+            const int n_b = *n_tiles_p;
+            walk.init(P, tiles, n_b, act_list, n);
+            for (int s = 0; s < S; s++) mbar_arrive(&full[s]);     // first use: no partial sums to drain yet
+            for (int c = 0; c < CS; c++) mbar_arrive(&cfull[c]);
+            // Gate/up tile i lives in stage i % S of the ring. The down phase cuts the same memory into CS
+            // smaller stages (more copies in flight when the tiles are smaller): down tile m lives in down
+            // stage m % CS, and the first tile of a down stage may only be requested once the gate/up stages
+            // it overlaps have been read for the last time.
             FTile t;
-            int s = 0, ph = 0;
-            int ik = 0;
-            while (walk.next(P, t)) {
-                if (!mbar_wait(&empty[s], ph)) {
-                    *abort_flag = 1;
-                    atomicExch(P.err, MB200_ERR_TIMEOUT);
-                    break;
+            int ib = 0, ic = 0;
+            bool ok = true;
+            while (ok && walk.next(P, t)) {
+                if (t.phase == 0) {
+                    const int st = ib % S;
+                    if (ib >= S) ok = mbar_wait(&empty[st], ((ib / S) - 1) & 1);
+                    if (ok && !*abort_flag) issue<FD>(P, t, stages + (size_t)st * P.stage_bytes, &full[st], sid);
+                    ib++;
+                } else {
+                    const int c = ic % CS;
+                    if (ic < CS) {
+                        const int lo = (c * P.c_stage_bytes) / P.stage_bytes;
+                        const int hi = ((c + 1) * P.c_stage_bytes - 1) / P.stage_bytes;
+                        for (int s2 = lo; s2 <= hi && ok; s2++) {
+                            const int uses = n_b > s2 ? (n_b - s2 + S - 1) / S : 0;  // gate/up tiles that lived in stage s2
+                            if (uses > 0) ok = mbar_wait(&empty[s2], (uses - 1) & 1);
+                        }
+                    } else {
+                        ok = mbar_wait(&cempty[c], ((ic / CS) - 1) & 1);
+                    }
+                    if (ok && !*abort_flag) issue<FD>(P, t, stages + (size_t)c * P.c_stage_bytes, &cfull[c], sid);
+                    if (ic < 8) MB200_STAMP(40 + ic);  // issue time of the down tiles
+                    ic++;
                 }
                 if (*abort_flag) break;
-                issue<FD>(P, t, stages + (size_t)s * P.stage_bytes, &full[s], sid);
-                if (t.phase == 1) {
-                    if (ik < 8) MB200_STAMP(40 + ik);  // issue time of the down tiles
-                    ik++;
-                }
-                if (++s == S) {
-                    s = 0;
-                    ph ^= 1;
-                }
+            }
+            if (!ok) {
+                *abort_flag = 1;
+                atomicExch(P.err, MB200_ERR_TIMEOUT);
             }
         }
         return;
@@ -487,30 +497,29 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         if (n_act == 0) return;
         walk.init(P, tiles, *n_tiles_p, act_list, n_act);
         FTile t;
-        int s = 0, ph = 0;
-        int ek = 0;
+        int ib = 0, ic = 0;
         while (walk.next(P, t)) {
-            if (!mbar_wait(&empty[s], ph)) *abort_flag = 1;
-            if (*abort_flag) break;
-            const float *pt = part + s * P.part_pitch;
             if (t.phase == 0) {
-                finish_gate_up(P, t, pt, outbox, lane);
+                const int st = ib % S;
+                if (!mbar_wait(&empty[st], (ib / S) & 1)) *abort_flag = 1;
+                if (*abort_flag) break;
+                finish_gate_up(P, t, part + st * P.part_pitch, outbox, lane);
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(&full[s]);  // the stage's partial sums may be rewritten
+                    mbar_arrive(&full[st]);  // the stage's partial sums may be rewritten
                     // every act row this CTA owes to the batch is in the outbox: tell the courier
                     if (t.last) mbar_arrive(&bdone[t.batch]);
                 }
+                ib++;
             } else {
-                if (ek < 8) MB200_STAMP(16 + ek);  // all consumers done with down tile ek
-                finish_down(P, t, pt, run, swt[t.slot], n_act, lane);
+                const int c = ic % CS;
+                if (!mbar_wait(&cempty[c], (ic / CS) & 1)) *abort_flag = 1;
+                if (*abort_flag) break;
+                if (ic < 8) MB200_STAMP(16 + ic);  // all consumers done with down tile ic
+                finish_down(P, t, cpart + c * P.part_pitch, run, swt[t.slot], n_act, lane);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&full[s]);
-                ek++;
-            }
-            if (++s == S) {
-                s = 0;
-                ph ^= 1;
+                if (lane == 0) mbar_arrive(&cfull[c]);
+                ic++;
             }
         }
         if (*abort_flag && lane == 0) atomicExch(P.err, MB200_ERR_TIMEOUT);
@@ -594,6 +603,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         const int colB = gB * 8 + q;
         Q4::XRegs xr;
         Q4::load_xregs(xr, smem + P.off_xb - kXBase, LB, P.bprB, colB, sub, true);
+        // x lives in registers from here on; its staging area is reused (outbox, down-phase partial sums)
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
         const uint32_t row_bytes = P.bprB * kQ4KBlock;
         const uint32_t lane_off = colB * kQ4KBlock;
         const uint32_t off_g = 2 * iB * row_bytes + lane_off, off_u = (P.TB + 2 * iB) * row_bytes + lane_off;
@@ -640,6 +651,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         typename FD::XRegs xr;
         int cur_j = -1;
         int k = 0;
+        int cs = 0, cph = 0;  // down-phase stage and parity (the ring re-cut into CS stages)
         while (have) {
             stage_share(false);
             if (n_staged < nb && t.j == n_staged * kBatchSlots) {  // first down tile of a batch: are its levels staged?
@@ -658,10 +670,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             if (FD::kBlockBytes % kSrcAlign != 0)
                 skew = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(down_src<FD>(P, t, sid)) & (kSrcAlign - 1));
             const bool hn = walk.next(P, nt);
-            if (!mbar_wait(&full[s], ph)) *abort_flag = 1;
+            if (!mbar_wait(&cfull[cs], cph)) *abort_flag = 1;
             if (warp == 0 && k < 8) MB200_STAMP(24 + k);
             k++;
-            const uint8_t *base = stages + (size_t)s * P.stage_bytes + skew + colC * FD::kBlockBytes;
+            const uint8_t *base = stages + (size_t)cs * P.c_stage_bytes + skew + colC * FD::kBlockBytes;
             float acc[2];
             acc[0] = FD::block_dot(base + min(ra, t.rows - 1) * row_bytes, sub, xr);
             acc[1] = FD::block_dot(base + min(rb, t.rows - 1) * row_bytes, sub, xr);
@@ -672,14 +684,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             else
                 sum = stream::packed_sum<2, false>(acc, W, lane, which);
             const int row = which ? rb : ra;
-            float *pt = part + s * P.part_pitch;
+            float *pt = cpart + cs * P.part_pitch;
             if ((lane & (W / 2 - 1)) == 0 && row < t.rows) pt[row * P.ngC + gC] = sum;
             __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
+            if (lane == 0) mbar_arrive(&cempty[cs]);
             if (*abort_flag) break;
-            if (++s == S) {
-                s = 0;
-                ph ^= 1;
+            if (++cs == CS) {
+                cs = 0;
+                cph ^= 1;
             }
             have = hn;
             t = nt;
@@ -783,6 +795,11 @@ static bool fused_layout(FusedParams &P, int &smem_bytes)
     P.part_pitch = pB > pC ? pB : pC;
     P.off_part = o;
     P.raw_bytes = kBatchSlots * P.EFF * 4;
+    // x's staging area is reused once x is in registers: outbox (kFusedMaxTiles x 32 floats), then the
+    // partial-sum slots of the down stages
+    P.off_cpart = P.off_xb + kFusedMaxTiles * 32 * 4;
+    if (kFusedMaxTiles * 32 * 4 + kFusedMaxCStages * P.part_pitch * 4 > LB.x_stride) return false;
+    P.c_stage_bytes = (tileC + 127) & ~127;
     for (int S = kFusedMaxStages; S >= 3; S--) {
         int t = o + S * P.part_pitch * 4;
         t = (t + 127) & ~127;
@@ -791,6 +808,8 @@ static bool fused_layout(FusedParams &P, int &smem_bytes)
             P.off_stages = t;
             P.off_raw = t + S * P.stage_bytes;
             smem_bytes = P.off_raw + 2 * P.raw_bytes;
+            P.c_stages = (S * P.stage_bytes) / P.c_stage_bytes;
+            if (P.c_stages > kFusedMaxCStages) P.c_stages = kFusedMaxCStages;
             return true;
         }
     }

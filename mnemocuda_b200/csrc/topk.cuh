@@ -162,7 +162,73 @@ struct __align__(16) TopkShared {
     int byrank[512];
     float outv[16];
     int outid[16];
+    unsigned bal[16];  // block form: accept flags of each row of 32 candidates
+    int n_cand;        // block form: number of candidates
 };
+
+// Second half of the parallel form, one warp: `m` accepted candidates (values sh.aval, ids sh.aid, in
+// arrival order) -> ranks, tie check, slot chains, softmax. Returns false on a tie among the accepted.
+__device__ __forceinline__ bool topk_finish_warp(int m, int *indices, float *weights, int k, TopkShared &sh)
+{
+    const unsigned full = 0xffffffffu;
+    const int lane = threadIdx.x & 31;
+    const int mpad = (m + 3) & ~3;
+    __syncwarp();
+    if (lane < mpad - m) sh.aval[m + lane] = __int_as_float(0x7FC00000);
+    __syncwarp();
+
+    // ---- ranks among the accepted, and the tie check ----
+    bool tie = false;
+    for (int t0 = 0; t0 < m; t0 += 32) {
+        const int t = t0 + lane;
+        const float av = t < m ? sh.aval[t] : __int_as_float(0x7FC00000);
+        int r = 0, eq = 0;
+        for (int u = 0; u < mpad; u += 4) {
+            const float4 w = *reinterpret_cast<const float4 *>(&sh.aval[u]);
+            r += (w.x < av) + (w.y < av) + (w.z < av) + (w.w < av);
+            eq += (w.x == av) + (w.y == av) + (w.z == av) + (w.w == av);
+        }
+        if (t < m) {
+            if (eq > 1) tie = true;
+            sh.byrank[r] = t;
+            sh.cid[t] = r;  // cid is free now: rank by arrival index
+        }
+    }
+    if (__any_sync(full, tie)) return false;
+    __syncwarp();
+
+    // ---- survivors walk their slot chain ----
+    for (int t0 = 0; t0 < m; t0 += 32) {
+        const int t = t0 + lane;
+        if (t < m && sh.cid[t] >= m - k) {
+            int cur = t;
+            while (cur >= k) cur = sh.byrank[cur - k];
+            sh.outv[cur] = sh.aval[t];
+            sh.outid[cur] = sh.aid[t];
+        }
+    }
+    __syncwarp();
+    // ---- softmax over the k kept logits, summed in slot order like the reference ----
+    if (lane == 0) {
+        float mx = sh.outv[0];
+        for (int i = 1; i < k; i++) mx = fmaxf(mx, sh.outv[i]);
+        float e[16];
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+            if (i < k) {
+                e[i] = expf(sh.outv[i] - mx);
+                sum += e[i];
+            }
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+            if (i < k) {
+                weights[i] = e[i] / sum;
+                indices[i] = sh.outid[i];
+            }
+    }
+    return true;
+}
 
 template <int KW>
 __device__ __forceinline__ bool topk_softmax_warp_par(const float *scores, int *indices, float *weights,
@@ -286,62 +352,7 @@ __device__ __forceinline__ bool topk_softmax_warp_par(const float *scores, int *
             m += __popc(bal);
         }
     }
-    const int mpad = (m + 3) & ~3;
-    __syncwarp();
-    if (lane < mpad - m) sh.aval[m + lane] = __int_as_float(0x7FC00000);
-    __syncwarp();
-
-    // ---- ranks among the accepted, and the tie check ----
-    bool tie = false;
-    for (int t0 = 0; t0 < m; t0 += 32) {
-        const int t = t0 + lane;
-        const float av = t < m ? sh.aval[t] : __int_as_float(0x7FC00000);
-        int r = 0, eq = 0;
-        for (int u = 0; u < mpad; u += 4) {
-            const float4 w = *reinterpret_cast<const float4 *>(&sh.aval[u]);
-            r += (w.x < av) + (w.y < av) + (w.z < av) + (w.w < av);
-            eq += (w.x == av) + (w.y == av) + (w.z == av) + (w.w == av);
-        }
-        if (t < m) {
-            if (eq > 1) tie = true;
-            sh.byrank[r] = t;
-            sh.cid[t] = r;  // cid is free now: rank by arrival index
-        }
-    }
-    if (__any_sync(full, tie)) return false;
-    __syncwarp();
-
-    // ---- survivors walk their slot chain ----
-    for (int t0 = 0; t0 < m; t0 += 32) {
-        const int t = t0 + lane;
-        if (t < m && sh.cid[t] >= m - k) {
-            int cur = t;
-            while (cur >= k) cur = sh.byrank[cur - k];
-            sh.outv[cur] = sh.aval[t];
-            sh.outid[cur] = sh.aid[t];
-        }
-    }
-    __syncwarp();
-    // ---- softmax over the k kept logits, summed in slot order like the reference ----
-    if (lane == 0) {
-        float mx = sh.outv[0];
-        for (int i = 1; i < k; i++) mx = fmaxf(mx, sh.outv[i]);
-        float e[16];
-        float sum = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 16; i++)
-            if (i < k) {
-                e[i] = expf(sh.outv[i] - mx);
-                sum += e[i];
-            }
-#pragma unroll
-        for (int i = 0; i < 16; i++)
-            if (i < k) {
-                weights[i] = e[i] / sum;
-                indices[i] = sh.outid[i];
-            }
-    }
-    return true;
+    return topk_finish_warp(m, indices, weights, k, sh);
 }
 
 // One warp. `sh` is shared memory. Results are identical to the reference's kernel
@@ -355,6 +366,97 @@ __device__ __forceinline__ void topk_softmax_warp(const float *scores, int *indi
     else
         done = topk_softmax_warp_par<16>(scores, indices, weights, n_experts, k, sh);
     if (done) return;
+    __syncwarp();
+    // equal accepted values: the serial walk decides
+    if (k <= 8)
+        topk_softmax_warp_seq_kw<8>(scores, indices, weights, n_experts, k, sh.val, sh.cid);
+    else
+        topk_softmax_warp_seq_kw<16>(scores, indices, weights, n_experts, k, sh.val, sh.cid);
+}
+
+// The same selection by a whole CTA (blockDim.x a multiple of 32, every thread calls it): warp 0
+// lists the candidates, the rows of 32 candidates are then counted by all warps side by side, and
+// warp 0 finishes. Only for n_experts <= 32 * k (no score is dropped before the merge), which covers
+// the routers of the supported models; other shapes use the one-warp form on warp 0.
+__device__ __forceinline__ void topk_softmax_block(const float *scores, int *indices, float *weights, int n_experts,
+                                                   int k, TopkShared &sh)
+{
+    const unsigned full = 0xffffffffu;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    if (n_experts > 32 * k || k > 16 || n_experts > 512) {  // block-uniform
+        if (warp == 0) topk_softmax_warp(scores, indices, weights, n_experts, k, sh);
+        return;
+    }
+    // ---- candidates in the reference's (lane, slot) order: lane l holds scores l, l + 32, ... ----
+    if (warp == 0) {
+        float sv[16];
+        int cnt = 0;
+#pragma unroll
+        for (int u = 0; u < 16; u++) {
+            sv[u] = (u < k && lane + 32 * u < n_experts) ? scores[lane + 32 * u] : -1e30f;
+            cnt += (sv[u] > -1e30f) ? 1 : 0;
+        }
+        int base = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(full, base, o);
+            if (lane >= o) base += t;
+        }
+        const int M = __shfl_sync(full, base, 31);
+        base -= cnt;
+        int w = 0;
+#pragma unroll
+        for (int u = 0; u < 16; u++)
+            if (sv[u] > -1e30f) {
+                sh.val[base + w] = sv[u];
+                sh.cid[base + w] = lane + 32 * u;
+                w++;
+            }
+        const int Mpad = (M + 3) & ~3;
+        if (lane < Mpad - M) sh.val[M + lane] = __int_as_float(0x7FC00000);  // NaN padding: compares false
+        if (lane < 16) {
+            sh.outv[lane] = -1e30f;
+            sh.outid[lane] = -1;
+        }
+        if (lane == 0) sh.n_cand = M;
+    }
+    __syncthreads();
+    const int M = sh.n_cand;
+    const int Mpad = (M + 3) & ~3;
+    const int n_rows = (M + 31) >> 5;
+    // ---- accept(p) <=> #{q < p : v_q >= v_p} < k, one row of 32 candidates per warp at a time ----
+    for (int row = warp; row < n_rows; row += n_warps) {
+        const int p = row * 32 + lane;
+        const float v = p < M ? sh.val[p] : __int_as_float(0x7FC00000);
+        int c = 0;
+        for (int q = 0; q < row * 32; q += 4) {  // earlier rows: every q < p
+            const float4 w = *reinterpret_cast<const float4 *>(&sh.val[q]);
+            c += (w.x >= v) + (w.y >= v) + (w.z >= v) + (w.w >= v);
+        }
+        const int q_end = min(Mpad, (row + 1) * 32);
+        for (int q = row * 32; q < q_end; q += 4) {  // own row: q counts only if q < p
+            const float4 w = *reinterpret_cast<const float4 *>(&sh.val[q]);
+            c += (q + 0 < p && w.x >= v) + (q + 1 < p && w.y >= v) + (q + 2 < p && w.z >= v) + (q + 3 < p && w.w >= v);
+        }
+        const unsigned bal = __ballot_sync(full, p < M && c < k);
+        if (lane == 0) sh.bal[row] = bal;
+    }
+    __syncthreads();
+    // ---- arrival order: compact the accepted ----
+    int m = 0;
+    for (int row = 0; row < n_rows; row++) {
+        const unsigned bal = sh.bal[row];
+        if ((row % n_warps) == warp && (bal & (1u << lane))) {
+            const int p = row * 32 + lane;
+            const int t = m + __popc(bal & ((1u << lane) - 1u));
+            sh.aval[t] = sh.val[p];
+            sh.aid[t] = sh.cid[p];
+        }
+        m += __popc(bal);
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    if (topk_finish_warp(m, indices, weights, k, sh)) return;
     __syncwarp();
     // equal accepted values: the serial walk decides
     if (k <= 8)
