@@ -334,7 +334,8 @@ def run_ours(args):
                    "parallelism": (f"experts sharded {world}-way (router replicated), NCCL all-reduce of the 16 KB partial hidden vector"
                                    if world > 1 else "single GPU")},
         "clocks": clk.summary(),
-        "gpu_launches": (2 if (world == 1 and fused) else 3) * args.steps,
+        # one launch per block when the fused kernel also routes (single GPU); sharded: router + experts (+ NCCL)
+        "gpu_launches": (1 if (world == 1 and fused) else (2 if world > 1 else 3)) * args.steps,
         "kernels_ms": {"router_topk": rt_ms, "moe_experts_fused": fu_ms, "moe_gate_up": gu_ms, "moe_down": dn_ms},
     }
     if world == 1:

@@ -178,7 +178,13 @@ int mb200_moe_down_local(const void *experts, size_t expert_stride, size_t down_
                          const float *act, const float *residual, float *y, int H, int EFF,
                          cudaStream_t stream);
 
-/* The three calls in sequence. ids/wts: [k]; act: [k][EFF]; scratch as for mb200_router_topk. */
+/* The whole block: out = residual + sum over the k routed experts. ids/wts: [k] (outputs); act: [k][EFF]
+ * (workspace); scratch: mb200_router_scratch_bytes(n_experts) bytes, 16-byte aligned, zeroed once and then
+ * left to this function. Where the shape allows it (see mb200_moe_experts_fused; in addition n_experts
+ * <= 32 k and <= 512) this is ONE cooperative launch that also does the routing: every CTA computes one
+ * router row, the CTAs meet at a device-wide barrier, and each CTA runs the top-k itself. Otherwise the
+ * router kernel is followed by the fused expert kernel, or by the two separate expert kernels. The
+ * results do not depend on which form runs beyond the rounding of the router's dot products. */
 int mb200_moe_block(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz,
                     size_t up_sz, int down_type, int n_experts, int k, int H, int EFF,
                     const float *x, const float *residual, float *out, int *ids, float *wts,

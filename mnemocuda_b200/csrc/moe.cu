@@ -28,7 +28,8 @@ void moe_down_q6k(const void *experts, size_t stride, size_t down_off, const int
 int pdl_enabled();
 int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off, size_t down_off, int down_type,
               const int *ids, const float *wts, int n_slots, int expert_lo, int expert_cnt, const float *x, float *act,
-              const float *residual, float *y, int H, int EFF, unsigned long long *sync, cudaStream_t stream);
+              const float *residual, float *y, int H, int EFF, unsigned long long *sync, cudaStream_t stream,
+              const float *router_w, int n_experts, float *logits, int *ids_out, float *wts_out);
 void moe_fused_set_mode(int mode);
 int moe_fused_mode();
 
@@ -262,21 +263,32 @@ int mb200_moe_experts_fused(const void *experts, size_t expert_stride, size_t ga
         return MB200_ERR_ARG;
     if (reinterpret_cast<uintptr_t>(sync) & 7) return MB200_ERR_ARG;
     return moe_fused(experts, expert_stride, gate_off, up_off, down_off, down_type, ids, wts, n_slots, expert_lo,
-                     expert_cnt, x, act, residual, y, H, EFF, static_cast<unsigned long long *>(sync), stream);
+                     expert_cnt, x, act, residual, y, H, EFF, static_cast<unsigned long long *>(sync), stream, nullptr, 0,
+                     nullptr, nullptr, nullptr);
 }
 
 int mb200_moe_block(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz,
                     int down_type, int n_experts, int k, int H, int EFF, const float *x, const float *residual,
                     float *out, int *ids, float *wts, float *act, void *scratch, cudaStream_t stream)
 {
-    int rc = mb200_router_topk(router_w, x, scratch, ids, wts, n_experts, H, k, stream);
+    if (!router_w || !x || !scratch || !ids || !wts || n_experts < 1 || H < 1 || k < 1 || k > 16) return MB200_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(scratch) & 15) return MB200_ERR_ARG;
+    // the last 64 bytes of the scratch are the fused kernel's barrier counters
+    unsigned long long *sync =
+        reinterpret_cast<unsigned long long *>(static_cast<char *>(scratch) + router_part_bytes(n_experts));
+    float *logits = reinterpret_cast<float *>(static_cast<int *>(scratch) + 8);
+    int rc;
+    if (moe_fused_mode() && act) {
+        // one launch: routing, gate/up, down
+        rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, nullptr, nullptr, k, 0, 0x7fffffff,
+                       x, act, residual, out, H, EFF, sync, stream, router_w, n_experts, logits, ids, wts);
+        if (rc != MB200_ERR_UNSUPPORTED) return rc;
+    }
+    rc = mb200_router_topk(router_w, x, scratch, ids, wts, n_experts, H, k, stream);
     if (rc != MB200_OK) return rc;
     if (moe_fused_mode() && act) {
-        // the last 64 bytes of the scratch are the fused kernel's barrier counters
         rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, ids, wts, k, 0, 0x7fffffff, x, act,
-                       residual, out, H, EFF,
-                       reinterpret_cast<unsigned long long *>(static_cast<char *>(scratch) + router_part_bytes(n_experts)),
-                       stream);
+                       residual, out, H, EFF, sync, stream, nullptr, 0, nullptr, nullptr, nullptr);
         if (rc != MB200_ERR_UNSUPPORTED) return rc;
     }
     rc = mb200_moe_gate_up(experts, expert_stride, 0, gate_sz, ids, k, x, act, EFF, H, stream);

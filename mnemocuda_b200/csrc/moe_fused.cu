@@ -34,6 +34,13 @@
 
 #include "q4k_policy.cuh"
 #include "q6k_policy.cuh"
+#include "topk.cuh"
+
+#ifdef MB200_TRACE
+// Developer aid: entry / exit time of CTA 0's issuer and consumer warp 0 for the last 64 launches.
+static __device__ long long g_launch_times[64][4];
+static __device__ unsigned g_launch_ctr;
+#endif
 
 namespace mb200 {
 
@@ -61,6 +68,13 @@ struct FusedParams {
     size_t estride, off_gate, off_up, off_down;
     const int *ids;
     const float *wts;
+    // routing inside the kernel (router_w != nullptr): logits = router_w x, then the reference's top-k + softmax;
+    // the ids / weights are also written to ids_out / wts_out for the caller
+    const float *router_w;
+    float *logits;   // [n_experts] scratch in global memory
+    int *ids_out;
+    float *wts_out;
+    int n_experts;
     const float *x;
     const float *residual;
     float *y;
@@ -166,14 +180,14 @@ struct FWalk {
 
 // One warp: reads the routed ids and weights (one round trip), compacts the slots served here, and
 // lists this CTA's gate/up tiles. Returns the number of served slots.
-__device__ __forceinline__ int build_tiles(const FusedParams &P, int lane, int *sid, float *swt, int *act_list,
-                                           int2 *tiles, int *n_tiles_p)
+__device__ __forceinline__ int build_tiles(const FusedParams &P, const int *ids, const float *wts, int lane, int *sid,
+                                           float *swt, int *act_list, int2 *tiles, int *n_tiles_p)
 {
     int id = -1;
     float w = 0.0f;
     if (lane < P.n_slots) {
-        id = P.ids[lane];
-        w = P.wts[lane];
+        id = ids[lane];
+        w = wts[lane];
     }
     const bool here = lane < P.n_slots && id >= P.expert_lo && id - P.expert_lo < P.expert_cnt;  // empty slots have id < 0
     const unsigned m = __ballot_sync(0xffffffffu, here);
@@ -325,6 +339,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     uint64_t *cfull = reinterpret_cast<uint64_t *>(smem + 592);    // [4] down-phase stages (re-cut ring)
     uint64_t *cempty = reinterpret_cast<uint64_t *>(smem + 624);   // [4]
     float *cpart = reinterpret_cast<float *>(smem + P.off_cpart);
+    // routing inside the kernel: results and reduction scratch sit in the partial-sum region (idle until tiles flow)
+    int *rid = reinterpret_cast<int *>(smem + P.off_part);
+    float *rwt = reinterpret_cast<float *>(smem + P.off_part + 64);
+    float *rred = reinterpret_cast<float *>(smem + P.off_part + 128);
     const int CS = P.c_stages;   // [kFusedMaxTiles] this CTA's gate/up tiles
     uint64_t *rawfull = reinterpret_cast<uint64_t *>(smem + 232);   // [2] a batch's fp32 activation vectors have landed
     uint64_t *rawempty = reinterpret_cast<uint64_t *>(smem + 248);  // [2] ... and every consumer warp has split its share
@@ -339,6 +357,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     const int S = P.stages;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (warp == 0) MB200_STAMP(0);
+#ifdef MB200_TRACE
+    unsigned launch_no = 0;
+    if (blockIdx.x == 0 && tid == 0) {
+        launch_no = atomicAdd(&g_launch_ctr, 1u);
+        long long t__;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));
+        g_launch_times[launch_no & 63][0] = t__;
+    }
+#endif
 
     FWalk walk;
 
@@ -364,10 +391,19 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             }
             mbar_fence_init();
         }
-        if (P.pdl) stream::grid_dep_wait();  // the routed ids come from the upstream kernel
-        const int n = build_tiles(P, lane, sid, swt, act_list, tiles, n_tiles_p);
-        if (lane == 0) *n_act_p = n;
+        int n = 0;
+        if (!P.router_w) {
+            if (P.pdl) stream::grid_dep_wait();  // the routed ids come from the upstream kernel
+            n = build_tiles(P, P.ids, P.wts, lane, sid, swt, act_list, tiles, n_tiles_p);
+            if (lane == 0) *n_act_p = n;
+        }
         __syncthreads();
+        if (P.router_w) {  // the consumer warps have routed: ids and weights are in shared memory
+            n = build_tiles(P, rid, rwt, lane, sid, swt, act_list, tiles, n_tiles_p);
+            if (lane == 0) *n_act_p = n;
+            __syncthreads();
+        }
+        if (*abort_flag) return;
         if (lane == 0) {
             if (P.pdl) stream::grid_dep_launch();
             const int n_b = *n_tiles_p;
@@ -423,7 +459,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
 #pragma unroll
         for (int b = 0; b < kFusedMaxBatches; b++) tgt[b] = barrier_target(P.sync + b);  // before this CTA can have arrived
         __syncthreads();
-        if (lane != 0) return;
+        if (P.router_w) __syncthreads();
+        if (lane != 0 || *abort_flag) return;
         const int n_act = *n_act_p;
         const int nb = (n_act + kBatchSlots - 1) / kBatchSlots;
         const uint32_t vec_bytes = static_cast<uint32_t>(P.EFF) * 4u;
@@ -493,6 +530,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         // consumer: when consumers took turns at this, each finisher came late to its next tile and the
         // delay was handed from tile to tile.
         __syncthreads();
+        if (P.router_w) __syncthreads();
+        if (*abort_flag) return;
         const int n_act = *n_act_p;
         if (n_act == 0) return;
         walk.init(P, tiles, *n_tiles_p, act_list, n_act);
@@ -527,7 +566,48 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     }
 
     // ---------------- consumer warps ----------------
+    unsigned long long tgt_route = 0;
+    if (P.router_w && tid == 0) tgt_route = barrier_target(P.sync + kFusedMaxBatches);  // before this CTA arrives
     if (P.pdl) stream::grid_dep_wait();  // x is produced upstream; act / y may still be in use there
+    if (P.router_w) {
+        // ---- router logits (reference src/kernels.cu:859-880): expert row b, b + G, ... per CTA ----
+        const int n4 = P.H >> 2;
+        const float4 *x4 = reinterpret_cast<const float4 *>(P.x);
+        for (int row = blockIdx.x; row < P.n_experts; row += gridDim.x) {
+            const float4 *w4 = reinterpret_cast<const float4 *>(P.router_w + (size_t)row * P.H);
+            float acc = 0.0f;
+            for (int i0 = tid; i0 < n4; i0 += kConsumers * 32 * 4) {
+                float4 a[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int i = i0 + u * kConsumers * 32;
+                    a[u] = i < n4 ? __ldcs(w4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int i = i0 + u * kConsumers * 32;
+                    if (i < n4) {
+                        const float4 b = __ldg(x4 + i);
+                        acc = fmaf(a[u].x, b.x, acc);
+                        acc = fmaf(a[u].y, b.y, acc);
+                        acc = fmaf(a[u].z, b.z, acc);
+                        acc = fmaf(a[u].w, b.w, acc);
+                    }
+                }
+            }
+            acc = warp_sum(acc);
+            if (lane == 0) rred[warp] = acc;
+            asm volatile("bar.sync 3, %0;" ::"n"(kConsumers * 32) : "memory");
+            if (tid == 0) {
+                float v = 0.0f;
+                for (int w = 0; w < kConsumers; w++) v += rred[w];  // fixed order
+                P.logits[row] = v;
+            }
+            asm volatile("bar.sync 3, %0;" ::"n"(kConsumers * 32) : "memory");
+        }
+        if (tid == 0) barrier_arrive(P.sync + kFusedMaxBatches);  // release: this thread stored the CTA's logits
+        if (warp == 0) MB200_STAMP(3);
+    }
     const Layout LB = stream::layout<Q4>(P.bprB, 0, 0, 1, 1);
     const Layout LC = stream::layout<FD>(P.bprC, 0, 0, 1, 1);
     {
@@ -537,7 +617,44 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
                                   reinterpret_cast<float *>(xb + LB.xsum));
     }
     if (warp == 0) MB200_STAMP(1);
-    __syncthreads();  // x is staged, barriers are initialised, the served slots are known
+    bool routed_ok = true;
+    if (P.router_w && warp < 4) {
+        // ---- every CTA selects the experts itself, from the logits all CTAs have stored ----
+        if (tid == 0) {
+            routed_ok = false;
+            for (uint32_t i = 0; i < (1u << 19); i++) {
+                unsigned long long c;
+                asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(P.sync + kFusedMaxBatches) : "memory");
+                if (c >= tgt_route) {
+                    routed_ok = true;
+                    break;
+                }
+                __nanosleep(100);
+            }
+        }
+        topk_group_sync(2, 128);
+        if (warp == 0) MB200_STAMP(4);
+        TopkShared &tsh = *reinterpret_cast<TopkShared *>(stages);  // the ring is idle until the first tile is requested
+        topk_softmax_group(const_cast<const float *>(static_cast<volatile float *>(P.logits)), rid, rwt, P.n_experts,
+                           P.n_slots, tsh, 4, 2);
+        if (warp == 0) MB200_STAMP(6);
+        if (warp == 0) {
+            __syncwarp();
+            if (blockIdx.x == 0 && lane < P.n_slots) {  // for the caller
+                P.ids_out[lane] = rid[lane];
+                P.wts_out[lane] = rwt[lane];
+            }
+        }
+    }
+    __syncthreads();  // x is staged, barriers are initialised, the served slots are known (or the routing is done)
+    if (P.router_w) {
+        if (tid == 0 && !routed_ok) {
+            *abort_flag = 1;
+            atomicExch(P.err, MB200_ERR_TIMEOUT);
+        }
+        __syncthreads();  // the issuer warp has listed the tiles
+    }
+    if (*abort_flag) return;
     const int n_act = *n_act_p;
     if (n_act == 0) {
         // no routed expert is served here: the block reduces to the residual (if this call carries one)
@@ -699,6 +816,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     }
     if (*abort_flag && lane == 0) atomicExch(P.err, MB200_ERR_TIMEOUT);
     if (warp == 0) MB200_STAMP(5);
+#ifdef MB200_TRACE
+    if (blockIdx.x == 0 && tid == 0) {
+        long long t__;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));
+        g_launch_times[launch_no & 63][1] = t__;
+    }
+#endif
 }
 
 int g_fused_mode = 1;          // 0: never use the fused kernel
@@ -727,6 +851,10 @@ int launch_fused(FusedParams &P, int smem_bytes, cudaStream_t stream)
     cfg.attrs = attr;
     P.pdl = (pdl_enabled() && g_fused_pdl_ok) ? 1 : 0;
     cfg.numAttrs = P.pdl ? 2 : 1;
+#ifdef MB200_V_NOCOOP  // developer variant: timing without the cooperative attribute
+    cfg.attrs = attr + 1;
+    cfg.numAttrs = P.pdl ? 1 : 0;
+#endif
     cudaError_t e = cudaLaunchKernelEx(&cfg, moe_fused_kernel<FD>, P);
     if (e != cudaSuccess && P.pdl) {
         cudaGetLastError();
@@ -820,11 +948,25 @@ void moe_fused_set_mode(int mode) { g_fused_mode = mode; }
 int moe_fused_mode() { return g_fused_mode; }
 
 // Returns MB200_OK after a launch, MB200_ERR_UNSUPPORTED when the shape is not covered (nothing launched).
+// With router_w != nullptr the kernel routes itself (logits into `logits`, ids / weights also to ids_out /
+// wts_out); otherwise it reads the routed ids / weights from `ids` / `wts`.
 int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off, size_t down_off, int down_type,
               const int *ids, const float *wts, int n_slots, int expert_lo, int expert_cnt, const float *x, float *act,
-              const float *residual, float *y, int H, int EFF, unsigned long long *sync, cudaStream_t stream)
+              const float *residual, float *y, int H, int EFF, unsigned long long *sync, cudaStream_t stream,
+              const float *router_w, int n_experts, float *logits, int *ids_out, float *wts_out)
 {
     FusedParams P{};
+    if (router_w) {
+        // the group top-k covers n_experts <= 32 * k and <= 512; 16-byte loads of the router rows
+        if (n_experts < 1 || n_experts > 512 || n_experts > 32 * n_slots || !logits || !ids_out || !wts_out)
+            return MB200_ERR_UNSUPPORTED;
+        if ((reinterpret_cast<uintptr_t>(router_w) & 15) || (H & 3)) return MB200_ERR_UNSUPPORTED;
+        P.router_w = router_w;
+        P.n_experts = n_experts;
+        P.logits = logits;
+        P.ids_out = ids_out;
+        P.wts_out = wts_out;
+    }
     P.ebase = static_cast<const uint8_t *>(experts);
     P.estride = stride;
     P.off_gate = gate_off;
@@ -864,6 +1006,10 @@ int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off
 }  // namespace mb200
 
 #ifdef MB200_TRACE
+extern "C" void mb200_trace_read_launches(void *dst)
+{
+    cudaMemcpyFromSymbol(dst, g_launch_times, sizeof(long long) * 64 * 4, 0, cudaMemcpyDeviceToDevice);
+}
 extern "C" void mb200_trace_read_fused(void *dst)
 {
     cudaMemcpyFromSymbol(dst, mb200::stream::g_trace, sizeof(long long) * mb200::kSMs * 2 * 48, 0,

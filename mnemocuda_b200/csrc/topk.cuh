@@ -374,15 +374,20 @@ __device__ __forceinline__ void topk_softmax_warp(const float *scores, int *indi
         topk_softmax_warp_seq_kw<16>(scores, indices, weights, n_experts, k, sh.val, sh.cid);
 }
 
-// The same selection by a whole CTA (blockDim.x a multiple of 32, every thread calls it): warp 0
-// lists the candidates, the rows of 32 candidates are then counted by all warps side by side, and
-// warp 0 finishes. Only for n_experts <= 32 * k (no score is dropped before the merge), which covers
-// the routers of the supported models; other shapes use the one-warp form on warp 0.
-__device__ __forceinline__ void topk_softmax_block(const float *scores, int *indices, float *weights, int n_experts,
-                                                   int k, TopkShared &sh)
+// The same selection by a group of warps -- the first n_warps warps of the CTA, all of whose threads
+// call it; they meet on hardware barrier `bar_id`: warp 0 lists the candidates, the rows of 32
+// candidates are then counted by all warps side by side, and warp 0 finishes. Only for
+// n_experts <= 32 * k (no score is dropped before the merge), which covers the routers of the
+// supported models; other shapes use the one-warp form on warp 0.
+__device__ __forceinline__ void topk_group_sync(int bar_id, int n_threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(n_threads) : "memory");
+}
+__device__ __forceinline__ void topk_softmax_group(const float *scores, int *indices, float *weights, int n_experts,
+                                                   int k, TopkShared &sh, int n_warps, int bar_id)
 {
     const unsigned full = 0xffffffffu;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (n_experts > 32 * k || k > 16 || n_experts > 512) {  // block-uniform
         if (warp == 0) topk_softmax_warp(scores, indices, weights, n_experts, k, sh);
         return;
@@ -420,7 +425,7 @@ __device__ __forceinline__ void topk_softmax_block(const float *scores, int *ind
         }
         if (lane == 0) sh.n_cand = M;
     }
-    __syncthreads();
+    topk_group_sync(bar_id, n_warps * 32);
     const int M = sh.n_cand;
     const int Mpad = (M + 3) & ~3;
     const int n_rows = (M + 31) >> 5;
@@ -441,7 +446,7 @@ __device__ __forceinline__ void topk_softmax_block(const float *scores, int *ind
         const unsigned bal = __ballot_sync(full, p < M && c < k);
         if (lane == 0) sh.bal[row] = bal;
     }
-    __syncthreads();
+    topk_group_sync(bar_id, n_warps * 32);
     // ---- arrival order: compact the accepted ----
     int m = 0;
     for (int row = 0; row < n_rows; row++) {
@@ -454,7 +459,7 @@ __device__ __forceinline__ void topk_softmax_block(const float *scores, int *ind
         }
         m += __popc(bal);
     }
-    __syncthreads();
+    topk_group_sync(bar_id, n_warps * 32);
     if (warp != 0) return;
     if (topk_finish_warp(m, indices, weights, k, sh)) return;
     __syncwarp();
@@ -463,6 +468,14 @@ __device__ __forceinline__ void topk_softmax_block(const float *scores, int *ind
         topk_softmax_warp_seq_kw<8>(scores, indices, weights, n_experts, k, sh.val, sh.cid);
     else
         topk_softmax_warp_seq_kw<16>(scores, indices, weights, n_experts, k, sh.val, sh.cid);
+}
+
+
+// Whole CTA (blockDim.x a multiple of 32, every thread calls it).
+__device__ __forceinline__ void topk_softmax_block(const float *scores, int *indices, float *weights, int n_experts,
+                                                   int k, TopkShared &sh)
+{
+    topk_softmax_group(scores, indices, weights, n_experts, k, sh, blockDim.x >> 5, 0);
 }
 
 }  // namespace mb200
