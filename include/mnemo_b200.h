@@ -207,7 +207,9 @@ int mb200_moe_experts_fused(const void *experts, size_t expert_stride, size_t ga
                             int expert_lo, int expert_cnt, const float *x, float *act,
                             const float *residual, float *y, int H, int EFF, void *sync,
                             cudaStream_t stream);
-void mb200_set_fused(int on);
+/* How mb200_moe_block runs the block: 0 = router kernel + two expert kernels, 1 = router kernel + fused
+ * expert kernel, 2 = one launch that also routes. Forms that do not cover a shape fall back to the next. */
+void mb200_set_fused(int mode);
 
 /* ---- prefill GEMM on tcgen05 tensor cores ----
  * out[t][n] = sum_k f16(X[t][k]) * dequant(W)[n][k]; X fp16 [M x K] row-major (16-byte aligned),

@@ -251,7 +251,7 @@ int mb200_moe_down(const void *experts, size_t expert_stride, size_t down_off, i
                                 residual, y, H, EFF, stream);
 }
 
-void mb200_set_fused(int on) { moe_fused_set_mode(on ? 1 : 0); }
+void mb200_set_fused(int mode) { moe_fused_set_mode(mode < 0 ? 0 : (mode > 2 ? 2 : mode)); }
 
 int mb200_moe_experts_fused(const void *experts, size_t expert_stride, size_t gate_off, size_t up_off, size_t down_off,
                             int down_type, const int *ids, const float *wts, int n_slots, int expert_lo, int expert_cnt,
@@ -278,7 +278,7 @@ int mb200_moe_block(const float *router_w, const void *experts, size_t expert_st
         reinterpret_cast<unsigned long long *>(static_cast<char *>(scratch) + router_part_bytes(n_experts));
     float *logits = reinterpret_cast<float *>(static_cast<int *>(scratch) + 8);
     int rc;
-    if (moe_fused_mode() && act) {
+    if (moe_fused_mode() == 2 && act) {
         // one launch: routing, gate/up, down
         rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, nullptr, nullptr, k, 0, 0x7fffffff,
                        x, act, residual, out, H, EFF, sync, stream, router_w, n_experts, logits, ids, wts);

@@ -34,6 +34,9 @@
 
 #include "q4k_policy.cuh"
 #include "q6k_policy.cuh"
+#ifdef MB200_TRACE
+#define MB200_TOPK_STAMP(n) do { if (threadIdx.x == 0) MB200_STAMP(44 + (n)); } while (0)
+#endif
 #include "topk.cuh"
 
 #ifdef MB200_TRACE
@@ -825,7 +828,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
 #endif
 }
 
-int g_fused_mode = 1;          // 0: never use the fused kernel
+int g_fused_mode = 2;          // see mb200_set_fused
 int g_fused_pdl_ok = 1;        // cleared if the driver refuses cooperative + programmatic serialization together
 
 template <class FD>

@@ -1,5 +1,8 @@
 // Router selection shared by cuda_topk_softmax and the fused router kernel.
 #pragma once
+#ifndef MB200_TOPK_STAMP
+#define MB200_TOPK_STAMP(n) do {} while (0)
+#endif
 
 #include "common.cuh"
 
@@ -426,6 +429,7 @@ __device__ __forceinline__ void topk_softmax_group(const float *scores, int *ind
         if (lane == 0) sh.n_cand = M;
     }
     topk_group_sync(bar_id, n_warps * 32);
+    MB200_TOPK_STAMP(0);
     const int M = sh.n_cand;
     const int Mpad = (M + 3) & ~3;
     const int n_rows = (M + 31) >> 5;
@@ -447,6 +451,7 @@ __device__ __forceinline__ void topk_softmax_group(const float *scores, int *ind
         if (lane == 0) sh.bal[row] = bal;
     }
     topk_group_sync(bar_id, n_warps * 32);
+    MB200_TOPK_STAMP(1);
     // ---- arrival order: compact the accepted ----
     int m = 0;
     for (int row = 0; row < n_rows; row++) {
@@ -460,6 +465,7 @@ __device__ __forceinline__ void topk_softmax_group(const float *scores, int *ind
         m += __popc(bal);
     }
     topk_group_sync(bar_id, n_warps * 32);
+    MB200_TOPK_STAMP(2);
     if (warp != 0) return;
     if (topk_finish_warp(m, indices, weights, k, sh)) return;
     __syncwarp();

@@ -195,8 +195,9 @@ def mb200_moe_experts_fused(experts, expert_stride, gate_off, up_off, down_off, 
            "mb200_moe_experts_fused")
 
 
-def mb200_set_fused(on: bool) -> None:
-    _lib.lib().mb200_set_fused(1 if on else 0)
+def mb200_set_fused(mode) -> None:
+    """0 / False: separate expert kernels; 1 / True: router kernel + fused expert kernel; 2: one launch per block."""
+    _lib.lib().mb200_set_fused(int(mode))
 
 
 def mb200_gemm_q4k_f16(w, x_f16, out, M, N, K_, stream=None):
