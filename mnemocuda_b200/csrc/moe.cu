@@ -100,18 +100,11 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const float
         is_last = (ticket == n_experts - 1);
     }
     __syncthreads();
-#ifdef MB200_ROUTER_WARP_TOPK
-    if (!is_last || threadIdx.x >= 32) return;
-    __threadfence();
-    topk_softmax_warp(const_cast<const float *>(static_cast<volatile float *>(logits)), indices, weights, n_experts, k,
-                      topk_sh);
-#else
     if (!is_last) return;
     __threadfence();
     // the whole CTA: the candidate rows are counted by its four warps side by side
     topk_softmax_block(const_cast<const float *>(static_cast<volatile float *>(logits)), indices, weights, n_experts, k,
                        topk_sh);
-#endif
     if (threadIdx.x == 0) scratch[0] = 0;  // ready for the next call
 }
 

@@ -439,7 +439,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
                         ok = mbar_wait(&cempty[c], ((ic / CS) - 1) & 1);
                     }
                     if (ok && !*abort_flag) issue<FD>(P, t, stages + (size_t)c * P.c_stage_bytes, &cfull[c], sid);
-                    if (ic < 8) MB200_STAMP(40 + ic);  // issue time of the down tiles
+                    if (ic < 4) MB200_STAMP(40 + ic);  // issue time of the first down tiles
                     ic++;
                 }
                 if (*abort_flag) break;
@@ -854,10 +854,6 @@ int launch_fused(FusedParams &P, int smem_bytes, cudaStream_t stream)
     cfg.attrs = attr;
     P.pdl = (pdl_enabled() && g_fused_pdl_ok) ? 1 : 0;
     cfg.numAttrs = P.pdl ? 2 : 1;
-#ifdef MB200_V_NOCOOP  // developer variant: timing without the cooperative attribute
-    cfg.attrs = attr + 1;
-    cfg.numAttrs = P.pdl ? 1 : 0;
-#endif
     cudaError_t e = cudaLaunchKernelEx(&cfg, moe_fused_kernel<FD>, P);
     if (e != cudaSuccess && P.pdl) {
         cudaGetLastError();

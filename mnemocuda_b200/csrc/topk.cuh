@@ -212,23 +212,20 @@ __device__ __forceinline__ bool topk_finish_warp(int m, int *indices, float *wei
     }
     __syncwarp();
     // ---- softmax over the k kept logits, summed in slot order like the reference ----
-    if (lane == 0) {
-        float mx = sh.outv[0];
-        for (int i = 1; i < k; i++) mx = fmaxf(mx, sh.outv[i]);
-        float e[16];
+    // Lane i holds slot i; the sum runs over the slots in order (every lane repeats it), so the result
+    // is the reference's, without a serial pass over an array by one lane.
+    {
+        const float v = lane < k ? sh.outv[lane] : -3.0e38f;
+        float mx = v;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(full, mx, o));
+        const float e = lane < k ? expf(v - mx) : 0.0f;
         float sum = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 16; i++)
-            if (i < k) {
-                e[i] = expf(sh.outv[i] - mx);
-                sum += e[i];
-            }
-#pragma unroll
-        for (int i = 0; i < 16; i++)
-            if (i < k) {
-                weights[i] = e[i] / sum;
-                indices[i] = sh.outid[i];
-            }
+        for (int i = 0; i < k; i++) sum += __shfl_sync(full, e, i);
+        if (lane < k) {
+            weights[lane] = e / sum;
+            indices[lane] = sh.outid[lane];
+        }
     }
     return true;
 }
