@@ -205,7 +205,7 @@ def run_ours(args):
     else:
         moe = ResidentMoE(shape, layers, dev, seed=1)
     K.mb200_set_pdl(not args.no_pdl)
-    K.mb200_set_fused(not args.no_fused)
+    K.mb200_set_fused(0 if args.no_fused else args.fused_mode)
     H = shape.H
     xs = torch.empty(layers, H, device=dev)
     rs = torch.empty(layers, H, device=dev)
@@ -335,7 +335,7 @@ def run_ours(args):
                                    if world > 1 else "single GPU")},
         "clocks": clk.summary(),
         # one launch per block when the fused kernel also routes (single GPU); sharded: router + experts (+ NCCL)
-        "gpu_launches": (1 if (world == 1 and fused) else (2 if world > 1 else 3)) * args.steps,
+        "gpu_launches": ((1 if args.fused_mode == 2 else 2) if (world == 1 and fused) else (2 if world > 1 else 3)) * args.steps,
         "kernels_ms": {"router_topk": rt_ms, "moe_experts_fused": fu_ms, "moe_gate_up": gu_ms, "moe_down": dn_ms},
     }
     if world == 1:
@@ -463,6 +463,8 @@ def main():
     ap.add_argument("--layers", type=int, default=12, help="resident MoE layers the steps rotate over")
     ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launch")
     ap.add_argument("--no-fused", action="store_true", help="routed experts as two launches (gate/up, down) instead of the fused kernel")
+    ap.add_argument("--fused-mode", type=int, default=2, choices=[1, 2],
+                    help="2: one launch per block (routing inside the fused kernel); 1: router kernel + fused expert kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--workload", default="moe_block", choices=["moe_block", "matvec", "gemm", "prefill"],

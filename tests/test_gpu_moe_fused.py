@@ -157,7 +157,8 @@ def test_fused_reports_unsupported_shapes_and_launches_nothing(K):
     assert float(y.min()) == 7.0 and float(y.max()) == 7.0
 
 
-def test_block_gives_the_same_result_with_and_without_the_fused_kernel(K):
+def test_block_gives_the_same_result_in_all_three_forms(K):
+    """mb200_set_fused: 0 = three kernels, 1 = router kernel + fused expert kernel, 2 = one launch."""
     NE, k, H, EFF = 16, 8, 4096, 1536
     g, u, d = synth.expert_sizes(H, EFF, 14)
     experts, stride, g, u = make_experts(26, NE, H, EFF, 14)
@@ -167,15 +168,18 @@ def test_block_gives_the_same_result_with_and_without_the_fused_kernel(K):
     n = K.mb200_router_scratch_bytes(NE)
     outs = []
     try:
-        for on in (False, True):
-            K.mb200_set_fused(on)
+        for mode in (0, 1, 2):
+            K.mb200_set_fused(mode)
             scratch = torch.zeros((n + 15) // 16 * 16, dtype=torch.uint8, device="cuda")
             ids = torch.empty(k, dtype=torch.int32, device="cuda"); wts = torch.empty(k, device="cuda")
             act = torch.empty(k, EFF, device="cuda"); out = torch.empty(H, device="cuda")
             for _ in range(2):
                 K.mb200_moe_block(d_r, d_e, stride, g, u, 14, NE, k, H, EFF, d_x, d_res, out, ids, wts, act, scratch)
             torch.cuda.synchronize()
-            outs.append(host(out).astype(np.float64))
+            outs.append((host(out).astype(np.float64), host(ids).copy(), host(wts).copy()))
     finally:
-        K.mb200_set_fused(True)
-    assert np.linalg.norm(outs[0] - outs[1]) <= 1e-5 * np.linalg.norm(outs[0])
+        K.mb200_set_fused(2)
+    for o, i, w in outs[1:]:
+        assert np.array_equal(i, outs[0][1])
+        np.testing.assert_allclose(w, outs[0][2], rtol=1e-5)
+        assert np.linalg.norm(o - outs[0][0]) <= 1e-5 * np.linalg.norm(outs[0][0])
