@@ -326,6 +326,87 @@ __device__ __forceinline__ void finish_down(const FusedParams &P, const FTile &t
     }
 }
 
+// ---- routing inside the kernel; out of line so that this run-once code (and the stack frame of the
+// top-k's serial fallback) does not weigh on the registers and code layout of the tile loops ----
+
+// Router logits (reference src/kernels.cu:859-880): expert row b, b + G, ... per CTA, by the twelve
+// consumer warps; then the CTA arrives at the routing barrier.
+__device__ __noinline__ void route_logits(const FusedParams &P, float *rred)
+{
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n4 = P.H >> 2;
+    const float4 *x4 = reinterpret_cast<const float4 *>(P.x);
+    for (int row = blockIdx.x; row < P.n_experts; row += gridDim.x) {
+        const float4 *w4 = reinterpret_cast<const float4 *>(P.router_w + (size_t)row * P.H);
+        float acc = 0.0f;
+        for (int i0 = tid; i0 < n4; i0 += kConsumers * 32 * 4) {
+            float4 a[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u * kConsumers * 32;
+                a[u] = i < n4 ? __ldcs(w4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u * kConsumers * 32;
+                if (i < n4) {
+                    const float4 b = __ldg(x4 + i);
+                    acc = fmaf(a[u].x, b.x, acc);
+                    acc = fmaf(a[u].y, b.y, acc);
+                    acc = fmaf(a[u].z, b.z, acc);
+                    acc = fmaf(a[u].w, b.w, acc);
+                }
+            }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) rred[warp] = acc;
+        asm volatile("bar.sync 3, %0;" ::"n"(kConsumers * 32) : "memory");
+        if (tid == 0) {
+            float v = 0.0f;
+            for (int w = 0; w < kConsumers; w++) v += rred[w];  // fixed order
+            P.logits[row] = v;
+        }
+        asm volatile("bar.sync 3, %0;" ::"n"(kConsumers * 32) : "memory");
+    }
+    if (tid == 0) barrier_arrive(P.sync + kFusedMaxBatches);  // release: this thread stored the CTA's logits
+    if (warp == 0) MB200_STAMP(3);
+}
+
+// Every CTA selects the experts itself, from the logits all CTAs have stored: warps 0-3. Returns
+// false (on thread 0) if the routing barrier did not complete within the poll budget.
+__device__ __noinline__ bool route_select(const FusedParams &P, unsigned long long tgt_route, int *rid, float *rwt,
+                                          uint8_t *ring)
+{
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    bool ok = true;
+    if (tid == 0) {
+        ok = false;
+        for (uint32_t i = 0; i < (1u << 19); i++) {
+            unsigned long long c;
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(P.sync + kFusedMaxBatches) : "memory");
+            if (c >= tgt_route) {
+                ok = true;
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+    topk_group_sync(2, 128);
+    if (warp == 0) MB200_STAMP(4);
+    TopkShared &tsh = *reinterpret_cast<TopkShared *>(ring);  // the ring is idle until the first tile is requested
+    topk_softmax_group(const_cast<const float *>(static_cast<volatile float *>(P.logits)), rid, rwt, P.n_experts,
+                       P.n_slots, tsh, 4, 2);
+    if (warp == 0) {
+        MB200_STAMP(6);
+        __syncwarp();
+        if (blockIdx.x == 0 && lane < P.n_slots) {  // for the caller
+            P.ids_out[lane] = rid[lane];
+            P.wts_out[lane] = rwt[lane];
+        }
+    }
+    return ok;
+}
+
 template <class FD>
 __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __grid_constant__ FusedParams P)
 {
@@ -572,45 +653,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     unsigned long long tgt_route = 0;
     if (P.router_w && tid == 0) tgt_route = barrier_target(P.sync + kFusedMaxBatches);  // before this CTA arrives
     if (P.pdl) stream::grid_dep_wait();  // x is produced upstream; act / y may still be in use there
-    if (P.router_w) {
-        // ---- router logits (reference src/kernels.cu:859-880): expert row b, b + G, ... per CTA ----
-        const int n4 = P.H >> 2;
-        const float4 *x4 = reinterpret_cast<const float4 *>(P.x);
-        for (int row = blockIdx.x; row < P.n_experts; row += gridDim.x) {
-            const float4 *w4 = reinterpret_cast<const float4 *>(P.router_w + (size_t)row * P.H);
-            float acc = 0.0f;
-            for (int i0 = tid; i0 < n4; i0 += kConsumers * 32 * 4) {
-                float4 a[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int i = i0 + u * kConsumers * 32;
-                    a[u] = i < n4 ? __ldcs(w4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int i = i0 + u * kConsumers * 32;
-                    if (i < n4) {
-                        const float4 b = __ldg(x4 + i);
-                        acc = fmaf(a[u].x, b.x, acc);
-                        acc = fmaf(a[u].y, b.y, acc);
-                        acc = fmaf(a[u].z, b.z, acc);
-                        acc = fmaf(a[u].w, b.w, acc);
-                    }
-                }
-            }
-            acc = warp_sum(acc);
-            if (lane == 0) rred[warp] = acc;
-            asm volatile("bar.sync 3, %0;" ::"n"(kConsumers * 32) : "memory");
-            if (tid == 0) {
-                float v = 0.0f;
-                for (int w = 0; w < kConsumers; w++) v += rred[w];  // fixed order
-                P.logits[row] = v;
-            }
-            asm volatile("bar.sync 3, %0;" ::"n"(kConsumers * 32) : "memory");
-        }
-        if (tid == 0) barrier_arrive(P.sync + kFusedMaxBatches);  // release: this thread stored the CTA's logits
-        if (warp == 0) MB200_STAMP(3);
-    }
+    if (P.router_w) route_logits(P, rred);
     const Layout LB = stream::layout<Q4>(P.bprB, 0, 0, 1, 1);
     const Layout LC = stream::layout<FD>(P.bprC, 0, 0, 1, 1);
     {
@@ -621,34 +664,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     }
     if (warp == 0) MB200_STAMP(1);
     bool routed_ok = true;
-    if (P.router_w && warp < 4) {
-        // ---- every CTA selects the experts itself, from the logits all CTAs have stored ----
-        if (tid == 0) {
-            routed_ok = false;
-            for (uint32_t i = 0; i < (1u << 19); i++) {
-                unsigned long long c;
-                asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(P.sync + kFusedMaxBatches) : "memory");
-                if (c >= tgt_route) {
-                    routed_ok = true;
-                    break;
-                }
-                __nanosleep(100);
-            }
-        }
-        topk_group_sync(2, 128);
-        if (warp == 0) MB200_STAMP(4);
-        TopkShared &tsh = *reinterpret_cast<TopkShared *>(stages);  // the ring is idle until the first tile is requested
-        topk_softmax_group(const_cast<const float *>(static_cast<volatile float *>(P.logits)), rid, rwt, P.n_experts,
-                           P.n_slots, tsh, 4, 2);
-        if (warp == 0) MB200_STAMP(6);
-        if (warp == 0) {
-            __syncwarp();
-            if (blockIdx.x == 0 && lane < P.n_slots) {  // for the caller
-                P.ids_out[lane] = rid[lane];
-                P.wts_out[lane] = rwt[lane];
-            }
-        }
-    }
+    if (P.router_w && warp < 4) routed_ok = route_select(P, tgt_route, rid, rwt, stages);
     __syncthreads();  // x is staged, barriers are initialised, the served slots are known (or the routing is done)
     if (P.router_w) {
         if (tid == 0 && !routed_ok) {
