@@ -2,19 +2,24 @@
 """Benchmark of the quantized-weight hot path: one MoE expert block, batch 1, Qwen3-235B shape.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload moe_block|matvec|gemm|prefill] [--no-fused | --fused-mode 1|2] [--no-pdl]
 
 Workload (BASELINE config 2): router fp32 128x4096 -> top-8 of 128 experts; per routed expert a
 fused gate+up Q4_K matvec (2 x 1536x4096) with SwiGLU and a Q6_K down matvec (4096x1536), weighted
 sum + residual. Weights are seeded synthetic GGUF blocks with the benchmark's distributions
 (mnemocuda_b200/synth.py); no dataset or checkpoint is involved. A "step" is one block on one
 layer; steps rotate over `layers` resident layers (>= 18 GB), so every pass is cold in L2.
+By default a block is ONE launch of this library (mb200_moe_block: routing, gate/up, down in one
+cooperative kernel); --no-fused times the three-launch form.
 
 `value` is algorithmic GB/s (router + the 8 routed expert blobs = 100 007 936 B per step) with all
 inputs resident in HBM, timed with CUDA events around a CUDA graph of the K steps. `e2e` is the
 same metric through the host-buffer call (pinned host x/residual in, result out, every step).
-`roofline` is for the dominant kernel (the routed gate/up stream kernel). `cpu_baseline` and
-`--impl reference` time the C oracle (the CPU restatement of the reference's algorithm -- the
-reference has no CPU implementation of this path) on the box's host cores on a bounded sample.
+`roofline` is for the dominant kernel (the expert phases of the fused kernel, timed alone; with
+--no-fused the routed gate/up stream kernel). `cpu_baseline` and `--impl reference` time the C
+oracle (the CPU restatement of the reference's algorithm -- the reference has no CPU implementation
+of this path) on the box's host cores on a bounded sample. N > 1 shards the experts of the block
+over the GPUs (router replicated, NCCL all-reduce of the partial hidden vectors): strong scaling.
 """
 from __future__ import annotations
 
@@ -334,8 +339,8 @@ def run_ours(args):
                    "parallelism": (f"experts sharded {world}-way (router replicated), NCCL all-reduce of the 16 KB partial hidden vector"
                                    if world > 1 else "single GPU")},
         "clocks": clk.summary(),
-        # one launch per block when the fused kernel also routes (single GPU); sharded: router + experts (+ NCCL)
-        "gpu_launches": ((1 if args.fused_mode == 2 else 2) if (world == 1 and fused) else (2 if world > 1 else 3)) * args.steps,
+        # one launch per block when the fused kernel also routes (sharded: one launch + the NCCL all-reduce)
+        "gpu_launches": ((1 if args.fused_mode == 2 else 2) if (world == 1 and fused) else (1 if (world > 1 and not args.no_fused and args.fused_mode == 2) else (2 if world > 1 else 3))) * args.steps,
         "kernels_ms": {"router_topk": rt_ms, "moe_experts_fused": fu_ms, "moe_gate_up": gu_ms, "moe_down": dn_ms},
     }
     if world == 1:

@@ -211,6 +211,15 @@ int mb200_moe_experts_fused(const void *experts, size_t expert_stride, size_t ga
  * expert kernel, 2 = one launch that also routes. Forms that do not cover a shape fall back to the next. */
 void mb200_set_fused(int mode);
 
+/* mb200_moe_block for a device that holds only experts [expert_lo, expert_lo + expert_cnt) of the layer at
+ * `experts` (expert-sharded engines): the routing is done in full (the router is replicated), slots routed
+ * to other devices are skipped, `out` receives this device's partial sum (pass the residual on one device
+ * and zeros on the others, then all-reduce). No counterpart in the reference, which shards by layers. */
+int mb200_moe_block_local(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz,
+                          size_t up_sz, int down_type, int n_experts, int expert_lo, int expert_cnt, int k,
+                          int H, int EFF, const float *x, const float *residual, float *out, int *ids,
+                          float *wts, float *act, void *scratch, cudaStream_t stream);
+
 /* ---- prefill GEMM on tcgen05 tensor cores ----
  * out[t][n] = sum_k f16(X[t][k]) * dequant(W)[n][k]; X fp16 [M x K] row-major (16-byte aligned),
  * W Q4_K / Q6_K [N x K] as for the matvecs, out fp32 [M x N]; K a multiple of 256. Weights are

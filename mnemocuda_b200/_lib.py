@@ -46,6 +46,7 @@ SIGNATURES = {
     "mb200_moe_block": (_i, [_vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mb200_moe_experts_fused": (_i, [_vp, _sz, _sz, _sz, _sz, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
     "mb200_set_fused": (None, [_i]),
+    "mb200_moe_block_local": (_i, [_vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mb200_gemm_q4k_f16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "mb200_gemm_q6k_f16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "mb200_moe_prefill_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),

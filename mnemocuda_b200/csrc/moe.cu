@@ -260,11 +260,14 @@ int mb200_moe_experts_fused(const void *experts, size_t expert_stride, size_t ga
                      nullptr, nullptr, nullptr);
 }
 
-int mb200_moe_block(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz,
-                    int down_type, int n_experts, int k, int H, int EFF, const float *x, const float *residual,
-                    float *out, int *ids, float *wts, float *act, void *scratch, cudaStream_t stream)
+int mb200_moe_block_local(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz,
+                          size_t up_sz, int down_type, int n_experts, int expert_lo, int expert_cnt, int k, int H,
+                          int EFF, const float *x, const float *residual, float *out, int *ids, float *wts, float *act,
+                          void *scratch, cudaStream_t stream)
 {
-    if (!router_w || !x || !scratch || !ids || !wts || n_experts < 1 || H < 1 || k < 1 || k > 16) return MB200_ERR_ARG;
+    if (!router_w || !x || !scratch || !ids || !wts || n_experts < 1 || H < 1 || k < 1 || k > 16 || expert_lo < 0 ||
+        expert_cnt < 0)
+        return MB200_ERR_ARG;
     if (reinterpret_cast<uintptr_t>(scratch) & 15) return MB200_ERR_ARG;
     // the last 64 bytes of the scratch are the fused kernel's barrier counters
     unsigned long long *sync =
@@ -273,21 +276,30 @@ int mb200_moe_block(const float *router_w, const void *experts, size_t expert_st
     int rc;
     if (moe_fused_mode() == 2 && act) {
         // one launch: routing, gate/up, down
-        rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, nullptr, nullptr, k, 0, 0x7fffffff,
-                       x, act, residual, out, H, EFF, sync, stream, router_w, n_experts, logits, ids, wts);
+        rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, nullptr, nullptr, k, expert_lo,
+                       expert_cnt, x, act, residual, out, H, EFF, sync, stream, router_w, n_experts, logits, ids, wts);
         if (rc != MB200_ERR_UNSUPPORTED) return rc;
     }
     rc = mb200_router_topk(router_w, x, scratch, ids, wts, n_experts, H, k, stream);
     if (rc != MB200_OK) return rc;
     if (moe_fused_mode() && act) {
-        rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, ids, wts, k, 0, 0x7fffffff, x, act,
-                       residual, out, H, EFF, sync, stream, nullptr, 0, nullptr, nullptr, nullptr);
+        rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, ids, wts, k, expert_lo, expert_cnt,
+                       x, act, residual, out, H, EFF, sync, stream, nullptr, 0, nullptr, nullptr, nullptr);
         if (rc != MB200_ERR_UNSUPPORTED) return rc;
     }
-    rc = mb200_moe_gate_up(experts, expert_stride, 0, gate_sz, ids, k, x, act, EFF, H, stream);
+    rc = mb200_moe_gate_up_local(experts, expert_stride, 0, gate_sz, ids, k, expert_lo, expert_cnt, x, act, EFF, H,
+                                 stream);
     if (rc != MB200_OK) return rc;
-    return mb200_moe_down(experts, expert_stride, gate_sz + up_sz, down_type, ids, wts, k, act, residual, out, H, EFF,
-                          stream);
+    return mb200_moe_down_local(experts, expert_stride, gate_sz + up_sz, down_type, ids, wts, k, expert_lo, expert_cnt,
+                                act, residual, out, H, EFF, stream);
+}
+
+int mb200_moe_block(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz,
+                    int down_type, int n_experts, int k, int H, int EFF, const float *x, const float *residual,
+                    float *out, int *ids, float *wts, float *act, void *scratch, cudaStream_t stream)
+{
+    return mb200_moe_block_local(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts, 0, 0x7fffffff, k,
+                                 H, EFF, x, residual, out, ids, wts, act, scratch, stream);
 }
 
 }  // extern "C"

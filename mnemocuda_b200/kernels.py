@@ -186,6 +186,15 @@ def mb200_moe_block(router_w, experts, expert_stride, gate_sz, up_sz, down_type,
                                       _f32(wts), _f32(act), _ptr(scratch), _stream(stream)), "mb200_moe_block")
 
 
+def mb200_moe_block_local(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts, expert_lo, expert_cnt, k,
+                          H, EFF, x, residual, out, ids, wts, act, scratch, stream=None):
+    """mb200_moe_block on a device that holds experts [expert_lo, expert_lo + expert_cnt) only."""
+    _check(_lib.lib().mb200_moe_block_local(_f32(router_w), _ptr(experts), expert_stride, gate_sz, up_sz, down_type,
+                                            n_experts, expert_lo, expert_cnt, k, H, EFF, _f32(x), _ptr(residual),
+                                            _f32(out), _ptr(ids), _f32(wts), _f32(act), _ptr(scratch), _stream(stream)),
+           "mb200_moe_block_local")
+
+
 def mb200_moe_experts_fused(experts, expert_stride, gate_off, up_off, down_off, down_type, ids, wts, n_slots, expert_lo,
                             expert_cnt, x, act, residual, y, H, EFF, sync, stream=None):
     """Gate/up + SwiGLU + down + weighted sum + residual in one cooperative launch (include/mnemo_b200.h)."""

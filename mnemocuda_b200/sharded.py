@@ -11,7 +11,7 @@ by two partitions of the work itself:
   hidden vectors are summed with an all-reduce.
 
 The functions here are the host logic (ranges, collectives); the device work is the C ABI
-(`mb200_moe_gate_up_local`, `mb200_moe_down_local`, the plain matvecs on row slices).
+(`mb200_moe_block_local`, `mb200_moe_gate_up_local`, `mb200_moe_down_local`, the plain matvecs on row slices).
 """
 from __future__ import annotations
 
@@ -75,25 +75,13 @@ class ShardedMoE:
         self.K, self.moe, self.rank, self.world = K, moe, rank, world
         self.lo, self.cnt = moe.expert_lo, moe.n_local
         self.zero = torch.zeros(moe.shape.H, dtype=torch.float32, device=moe.device)
-        self.fused = True  # cleared by the first call if the shape is outside the one-launch expert kernel
 
     def forward(self, layer: int, x: torch.Tensor, residual: torch.Tensor, out: torch.Tensor, reduce=True) -> None:
+        """This rank's partial block (one launch where the fused kernel covers the shape), then the all-reduce."""
         s, m, K = self.moe.shape, self.moe, self.K
-        K.mb200_router_topk(m.router[layer], x, m.scratch, m.ids[layer], m.wts[layer], s.NE, s.H, s.K)
         res = residual if self.rank == 0 else self.zero
-        if self.fused:
-            try:
-                m.experts_fused(layer, x, res, out)
-                if reduce and self.world > 1:
-                    allreduce_partial(out)
-                return
-            except RuntimeError as exc:
-                if "status 4" not in str(exc):  # anything but "shape not covered"
-                    raise
-                self.fused = False
-        K.mb200_moe_gate_up_local(m.experts[layer], s.stride, 0, s.gate_sz, m.ids[layer], s.K, self.lo, self.cnt, x,
-                                  m.act, s.EFF, s.H)
-        K.mb200_moe_down_local(m.experts[layer], s.stride, s.gate_sz + s.up_sz, s.down_type, m.ids[layer],
-                               m.wts[layer], s.K, self.lo, self.cnt, m.act, res, out, s.H, s.EFF)
+        K.mb200_moe_block_local(m.router[layer], m.experts[layer], s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE,
+                                self.lo, self.cnt, s.K, s.H, s.EFF, x, res, out, m.ids[layer], m.wts[layer], m.act,
+                                m.scratch)
         if reduce and self.world > 1:
             allreduce_partial(out)

@@ -183,3 +183,31 @@ def test_block_gives_the_same_result_in_all_three_forms(K):
         assert np.array_equal(i, outs[0][1])
         np.testing.assert_allclose(w, outs[0][2], rtol=1e-5)
         assert np.linalg.norm(o - outs[0][0]) <= 1e-5 * np.linalg.norm(outs[0][0])
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_block_local_shards_sum_to_the_full_block(K, world):
+    """mb200_moe_block_local for every rank of an expert partition in turn (routing replicated on each)."""
+    from mnemocuda_b200 import sharded
+    NE, k, H, EFF = 16, 8, 4096, 1536
+    experts, stride, g, u = make_experts(27, NE, H, EFF, 14)
+    router = synth.normal_f32(51, NE * H, 1.0 / np.sqrt(H))
+    x, res = synth.normal_f32(52, H), synth.normal_f32(53, H)
+    want, i_ref, w_ref = oracle.moe_block(router, experts, stride, g, u, 14, NE, k, H, EFF, x, res)
+    d_r, d_e, d_x, d_res = dev(router), dev(experts), dev(x), dev(res)
+    zero = torch.zeros(H, device="cuda")
+    n = K.mb200_router_scratch_bytes(NE)
+    total = torch.zeros(H, dtype=torch.float64, device="cuda")
+    for rank in range(world):
+        lo, hi = sharded.expert_range(NE, world, rank)
+        scratch = torch.zeros((n + 15) // 16 * 16, dtype=torch.uint8, device="cuda")
+        ids = torch.empty(k, dtype=torch.int32, device="cuda"); wts = torch.empty(k, device="cuda")
+        act = torch.empty(k, EFF, device="cuda"); part = torch.full((H,), float("nan"), device="cuda")
+        for _ in range(2):
+            K.mb200_moe_block_local(d_r, d_e[lo * stride:], stride, g, u, 14, NE, lo, hi - lo, k, H, EFF, d_x,
+                                    d_res if rank == 0 else zero, part, ids, wts, act, scratch)
+        assert np.array_equal(host(ids), i_ref)
+        assert torch.isfinite(part).all()
+        total += part.double()
+    got = host(total)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
