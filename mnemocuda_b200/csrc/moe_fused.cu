@@ -388,7 +388,7 @@ __device__ __noinline__ bool route_select(const FusedParams &P, unsigned long lo
                 ok = true;
                 break;
             }
-            __nanosleep(100);
+            __nanosleep(40);
         }
     }
     topk_group_sync(2, 128);
@@ -501,6 +501,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             FTile t;
             int ib = 0, ic = 0;
             bool ok = true;
+            MB200_STAMP(47);  // tile list ready, first copy about to be requested
             while (ok && walk.next(P, t)) {
                 if (t.phase == 0) {
                     const int st = ib % S;
@@ -749,6 +750,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             stage_share(false);
             const bool hn = walk.next(P, nt);
             if (!mbar_wait(&full[s], ph)) *abort_flag = 1;
+            if (warp == 0 && k == 0) MB200_STAMP(15);  // first gate/up tile has landed
             k++;
             const uint8_t *st = stages + (size_t)s * P.stage_bytes;
             float acc[4];

@@ -435,11 +435,13 @@ __device__ __forceinline__ void topk_softmax_group(const float *scores, int *ind
         const int p = row * 32 + lane;
         const float v = p < M ? sh.val[p] : __int_as_float(0x7FC00000);
         int c = 0;
+#pragma unroll 8
         for (int q = 0; q < row * 32; q += 4) {  // earlier rows: every q < p
             const float4 w = *reinterpret_cast<const float4 *>(&sh.val[q]);
             c += (w.x >= v) + (w.y >= v) + (w.z >= v) + (w.w >= v);
         }
         const int q_end = min(Mpad, (row + 1) * 32);
+#pragma unroll 8
         for (int q = row * 32; q < q_end; q += 4) {  // own row: q counts only if q < p
             const float4 w = *reinterpret_cast<const float4 *>(&sh.val[q]);
             c += (q + 0 < p && w.x >= v) + (q + 1 < p && w.y >= v) + (q + 2 < p && w.z >= v) + (q + 3 < p && w.w >= v);
