@@ -44,7 +44,7 @@ WORKLOAD = ("configs[1]: MoE expert block, batch 1, Qwen3-235B shape -- router f
 # algorithmic bytes), from the ncu capture summarised in profiles/; None until captured.
 GATE_UP_TRAFFIC_BYTES = 56726784 + 569088  # profiles/moe_block_stream_kernels_ncu.md
 # same for one launch of the fused routed-expert kernel (98 041 856 algorithmic bytes)
-FUSED_TRAFFIC_BYTES = 98054912 + 3864064  # profiles/moe_fused_kernel_ncu.md
+FUSED_TRAFFIC_BYTES = 98054912 + 3864064  # profiles/moe_fused_kernel_ncu.md (expert phases alone, as timed for `roofline`)
 
 
 def measured_peaks():
