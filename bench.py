@@ -44,6 +44,8 @@ WORKLOAD = ("configs[1]: MoE expert block, batch 1, Qwen3-235B shape -- router f
 # algorithmic bytes), from the ncu capture summarised in profiles/; None until captured.
 GATE_UP_TRAFFIC_BYTES = 56726784 + 569088  # profiles/moe_block_stream_kernels_ncu.md
 # same for one launch of the fused routed-expert kernel (98 041 856 algorithmic bytes)
+# one launch of the whole block (100 007 936 algorithmic bytes): profiles/moe_block_one_launch_ncu.md
+BLOCK_TRAFFIC_BYTES = 100186880 + 4039680
 FUSED_TRAFFIC_BYTES = 98054912 + 3864064  # profiles/moe_fused_kernel_ncu.md (expert phases alone, as timed for `roofline`)
 
 
@@ -322,12 +324,22 @@ def run_ours(args):
 
     peak, which = measured_peaks()
     fused = bool(fu_ms) and not args.no_fused
-    # dominant kernel: the fused routed-expert kernel (gate/up + down of the 8 routed experts in one launch);
-    # with --no-fused the routed gate/up kernel of the three-launch form
+    one_launch = fused and args.fused_mode == 2 and world == 1
+    # Dominant kernel. One-launch form: the block IS one kernel (routing + gate/up + down), so its average
+    # duration is the step time of the timed graph (launch-to-launch, i.e. including the ~2.5 us between two
+    # launches) and its algorithmic bytes are the block's. Otherwise: the fused expert kernel, or with
+    # --no-fused the routed gate/up stream kernel, timed alone.
     gu_bytes = shape.K * (shape.gate_sz + shape.up_sz) + shape.H * 4 + shape.K * shape.EFF * 4
     dn_bytes = shape.K * shape.down_sz + shape.K * shape.EFF * 4 + 2 * shape.H * 4
-    dom_bytes = gu_bytes + dn_bytes if fused else gu_bytes
-    dom_ms = fu_ms if fused else gu_ms
+    if one_launch:
+        dom_name = "moe_fused_kernel (routing + gate/up + SwiGLU + down + weighted sum: the whole block in one launch)"
+        dom_bytes, dom_ms, dom_traffic = shape.algorithmic_bytes, ms, BLOCK_TRAFFIC_BYTES
+    elif fused:
+        dom_name = "moe_fused_kernel (routed gate/up + SwiGLU + down + weighted sum, 8 experts, one launch)"
+        dom_bytes, dom_ms, dom_traffic = gu_bytes + dn_bytes, fu_ms, FUSED_TRAFFIC_BYTES
+    else:
+        dom_name = "stream_kernel<Q4,*> (routed gate/up + SwiGLU, 8 experts per launch)"
+        dom_bytes, dom_ms, dom_traffic = gu_bytes, gu_ms, GATE_UP_TRAFFIC_BYTES
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms else None
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -344,13 +356,14 @@ def run_ours(args):
         "kernels_ms": {"router_topk": rt_ms, "moe_experts_fused": fu_ms, "moe_gate_up": gu_ms, "moe_down": dn_ms},
     }
     if world == 1:
-        line["roofline"] = {"bound": "hbm",
-                            "kernel": ("moe_fused_kernel (routed gate/up + SwiGLU + down + weighted sum, 8 experts, one launch)"
-                                       if fused else "stream_kernel<Q4,*> (routed gate/up + SwiGLU, 8 experts per launch)"),
+        line["roofline"] = {"bound": "hbm", "kernel": dom_name,
                             "achieved": achieved, "peak": peak, "peak_source": which + " copy bandwidth (MEASURED_PEAKS.json)",
                             "unit": "GB/s", "frac": achieved / peak, "frac_of_8TBs_nominal": achieved / 8000.0,
-                            "algorithmic_bytes_per_launch": dom_bytes,
-                            "traffic": FUSED_TRAFFIC_BYTES if fused else GATE_UP_TRAFFIC_BYTES}
+                            "algorithmic_bytes_per_launch": dom_bytes, "traffic": dom_traffic}
+        if fu_ms:  # the expert phases of the same kernel, timed alone (ids already routed)
+            line["roofline"]["expert_phases_alone"] = {
+                "ms": fu_ms, "achieved": (gu_bytes + dn_bytes) / (fu_ms * 1e-3) / 1e9,
+                "frac": (gu_bytes + dn_bytes) / (fu_ms * 1e-3) / 1e9 / peak, "algorithmic_bytes_per_launch": gu_bytes + dn_bytes}
     line["e2e"] = {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": host_block.h2d_bytes,
                    "d2h_bytes_per_step": host_block.d2h_bytes}
     if world == 1 and not args.no_cpu_baseline:
