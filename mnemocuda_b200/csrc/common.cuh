@@ -115,16 +115,9 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity)
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
 {
-#ifdef MB200_V_TESTWAIT
-    for (uint32_t i = 0; i < kWaitBudget * 64; i++) {
-        if (mbar_test_wait(bar, parity)) return true;
-    }
-    return false;
-#else
     for (uint32_t i = 0; i < kWaitBudget; i++)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
-#endif
 }
 
 // 1-D bulk copy; src and dst 16-byte aligned, bytes a multiple of 16.

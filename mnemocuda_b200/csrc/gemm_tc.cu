@@ -270,12 +270,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     break;
                 }
                 uint8_t *b_tile = stage_base + s * kStageBytes + kABytes;
-#ifdef MB200_V_NOTMA
-                mbar_arrive(&full[s]);
-#else
                 mbar_expect_tx(&full[s], kBBytes);
                 tma_load_2d(b_tile, &xmap, kb * kBK, t0, &full[s]);
-#endif
                 if (++s == kStages) {
                     s = 0;
                     ph ^= 1;
@@ -298,11 +294,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 if (kb == n_kb - 1) GSTAMP(6);
                 const uint32_t a_addr = smem_u32(stage_base + s * kStageBytes);
                 const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kABytes);
-#ifndef MB200_V_NOMMA
 #pragma unroll
                 for (int kk = 0; kk < kBK / 16; kk++)  // 16 fp16 = 32 bytes = 2 descriptor units per K step
                     umma_f16(tmem_base, da + 2 * kk, db + 2 * kk, kIdesc, (kb | kk) != 0);
-#endif
                 umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
                 if (kb >= 16 && kb < 24) GSTAMP(33 + (kb - 16) * 2);
                 if (++s == kStages) {

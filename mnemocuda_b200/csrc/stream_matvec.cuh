@@ -443,12 +443,6 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
 
     TileWalk walk;
 
-#ifdef MB200_V_NOWAIT
-    if (warp >= kConsumers) {
-        __syncthreads();
-        return;
-    }
-#endif
     if (warp == kConsumers) {
         // ---------------- issuer ----------------
         // The weights never depend on the upstream kernel, so the first stages are
@@ -620,9 +614,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
         const uint8_t *base = smem + L.stages + s * L.stage_bytes + skew;
         float *pt = part + s * part_pitch + ng;
 
-#ifndef MB200_V_NOWAIT
         if (!mbar_wait(&full[s], ph)) *abort_flag = 1;
-#endif
         if (warp == 0 && k == 0) MB200_STAMP(3);
         if (warp == 0) MB200_STAMP(4);
         if (warp == 0 && k < 8) MB200_STAMP(16 + k);
@@ -664,10 +656,8 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
             if ((lane & (wr - 1)) == 0 && row < R) pt[row * NG] = sum;
         }
         __syncwarp();
-#ifndef MB200_V_NOWAIT
         if (lane == 0) mbar_arrive(&empty[s]);
         if (*abort_flag) break;
-#endif
         if (warp == 0 && k <= 8) MB200_STAMP(24 + k - 1);
         if (++s == S) {
             s = 0;
@@ -826,9 +816,6 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
             ru = cand;
         }
     }
-#ifdef MB200_TUNING
-    if (const char *e = getenv("MB200_FORCE_RU")) ru = atoi(e);
-#endif
     // tile: a whole number of sweeps near the target size, never more than the range
     const int sweep = sweep1 * ru;
     int target = F::kTileTargetBytes / row_bytes;  // stage rows

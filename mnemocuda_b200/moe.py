@@ -1,5 +1,5 @@
-"""Host side of the decode-time MoE block: resident expert weights + the three-launch
-device path (router + top-k, routed gate/up + SwiGLU, routed down + weighted sum + residual).
+"""Host side of the decode-time MoE block: resident expert weights + the device path
+(mb200_moe_block: one launch where the fused kernel covers the shape, else router + expert kernels).
 
 Mirrors what the reference's forward_layer does between ffn_norm and the residual add
 (src/forward.c:810-823, 875, 1122-1142, 1114) with every expert resident in HBM, so there

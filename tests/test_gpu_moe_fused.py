@@ -211,3 +211,23 @@ def test_block_local_shards_sum_to_the_full_block(K, world):
         total += part.double()
     got = host(total)
     assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
+
+
+def test_host_buffer_block_matches_device_block(K):
+    """HostMoEBlock (pinned host buffers in and out, every call) against ResidentMoE.forward."""
+    from mnemocuda_b200.moe import HostMoEBlock, MoEShape, ResidentMoE
+    shape = MoEShape(n_experts=16)
+    moe = ResidentMoE(shape, 2, "cuda", seed=3)
+    hb = HostMoEBlock(moe)
+    H = shape.H
+    for it in range(5):
+        layer = it % 2
+        x = torch.from_numpy(synth.normal_f32(100 + it, H)).pin_memory()
+        r = torch.from_numpy(synth.normal_f32(200 + it, H)).pin_memory()
+        o = torch.empty(H).pin_memory()
+        hb(layer, x, r, o)
+        want = torch.empty(H, device="cuda")
+        moe.forward(layer, x.cuda(), r.cuda(), want)
+        torch.cuda.synchronize()
+        assert torch.equal(o, want.cpu())
+    assert K.mb200_device_error() == 0
