@@ -181,31 +181,51 @@ __device__ __forceinline__ void dequant32_q4k(const RawQ4 &raw, int grp, int h, 
 // Q6_K: a 64-wide K chunk c (0..3) of block b covers half hh = c >> 1 and the two thirty-two-groups
 // g = 2*(c&1) + {0,1} of that half (value order 128hh + 32g + l). Thread h takes group
 // g = 2*(c&1) + h, positions l = 0..31, i.e. k-local 32h + l  (reference src/kernels.cu:455-484).
-__device__ __forceinline__ void dequant32_q6k(const uint8_t *blk, int c, int h, float (&wv)[32])
+// Its raw bytes -- 32 of ql, 32 of qh, two scales, d -- are fetched one chunk ahead of their use
+// as aligned words (a Q6_K block is only 2-byte aligned: nine words + a funnel shift give eight).
+struct RawQ6 {
+    uint32_t ql[8], qh[8];
+    unsigned short scb, dbits;
+};
+__device__ __forceinline__ void load_words_2b(const uint8_t *p, uint32_t (&w)[8])
+{
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t *base = reinterpret_cast<const uint32_t *>(a & ~static_cast<uintptr_t>(3));
+    const uint32_t sh = static_cast<uint32_t>(a & 3) * 8;
+    uint32_t t[9];
+#pragma unroll
+    for (int i = 0; i < 9; i++) t[i] = __ldg(base + i);  // the ninth word still lies inside the 210-byte block
+#pragma unroll
+    for (int i = 0; i < 8; i++) w[i] = __funnelshift_r(t[i], t[i + 1], sh);
+}
+__device__ __forceinline__ void load_raw_q6k(RawQ6 &raw, const uint8_t *blk, int c, int h)
 {
     const int hh = c >> 1, g = 2 * (c & 1) + h;
-    const uint8_t *ql = blk + 64 * hh + 32 * (g & 1);  // 2-byte aligned only
-    const uint8_t *qh = blk + 128 + 32 * hh;
-    const unsigned short scb = __ldg(reinterpret_cast<const unsigned short *>(blk + 192 + 8 * hh + 2 * g));
-    const unsigned short dbits = __ldg(reinterpret_cast<const unsigned short *>(blk + 208));
-    const float d = __half2float(__ushort_as_half(dbits));
-    const float s0 = d * static_cast<float>(static_cast<int8_t>(scb & 0xFF));
-    const float s1 = d * static_cast<float>(static_cast<int8_t>(scb >> 8));
+    load_words_2b(blk + 64 * hh + 32 * (g & 1), raw.ql);
+    load_words_2b(blk + 128 + 32 * hh, raw.qh);
+    raw.scb = __ldg(reinterpret_cast<const unsigned short *>(blk + 192 + 8 * hh + 2 * g));
+    raw.dbits = __ldg(reinterpret_cast<const unsigned short *>(blk + 208));
+}
+__device__ __forceinline__ void dequant32_q6k(const RawQ6 &raw, int c, int h, float (&wv)[32])
+{
+    const int g = 2 * (c & 1) + h;
+    const float d = __half2float(__ushort_as_half(raw.dbits));
+    const float s0 = d * static_cast<float>(static_cast<int8_t>(raw.scb & 0xFF));
+    const float s1 = d * static_cast<float>(static_cast<int8_t>(raw.scb >> 8));
     const int lo_shift = 4 * (g >> 1), hi_shift = 2 * g;
-    unsigned short a[16], b[16];
+    // q = lo4 | hi2 << 4 rebuilt four bytes at a time; a byte dropped into byte 2 of 2.0f (0x40000000) is
+    // v = 2 + q/64, so  w = s*(q - 32) = (64 s) * v - 160 s  is one byte permute and one FMA per weight.
 #pragma unroll
-    for (int l2 = 0; l2 < 16; l2++) {  // all loads first
-        a[l2] = __ldg(reinterpret_cast<const unsigned short *>(ql + 2 * l2));
-        b[l2] = __ldg(reinterpret_cast<const unsigned short *>(qh + 2 * l2));
-    }
-#pragma unroll
-    for (int l2 = 0; l2 < 16; l2++) {
-#pragma unroll
-        for (int e = 0; e < 2; e++) {
-            const int lo4 = ((a[l2] >> (8 * e)) >> lo_shift) & 0xF;
-            const int hi2 = ((b[l2] >> (8 * e)) >> hi_shift) & 3;
-            wv[2 * l2 + e] = (l2 < 8 ? s0 : s1) * static_cast<float>(((hi2 << 4) | lo4) - 32);
-        }
+    for (int i = 0; i < 8; i++) {
+        const uint32_t lo = (raw.ql[i] >> lo_shift) & 0x0F0F0F0Fu;
+        const uint32_t hi = ((raw.qh[i] >> hi_shift) & 0x03030303u) << 4;
+        const uint32_t q4 = lo | hi;
+        const float s = i < 4 ? s0 : s1;
+        const float a = 64.0f * s, b = -160.0f * s;
+        wv[4 * i + 0] = fmaf(a, __uint_as_float(__byte_perm(q4, 0x40000000u, 0x7044)), b);
+        wv[4 * i + 1] = fmaf(a, __uint_as_float(__byte_perm(q4, 0x40000000u, 0x7144)), b);
+        wv[4 * i + 2] = fmaf(a, __uint_as_float(__byte_perm(q4, 0x40000000u, 0x7244)), b);
+        wv[4 * i + 3] = fmaf(a, __uint_as_float(__byte_perm(q4, 0x40000000u, 0x7344)), b);
     }
 }
 
@@ -339,10 +359,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             if (*abort_flag) stop = true;
         };
         if (P.q6) {
+            RawQ6 cur, nxt;
+            load_raw_q6k(cur, row + (size_t)(grp >> 2) * blk_bytes, grp & 3, h);
             for (int kb = grp; kb < n_kb && !stop; kb += 2) {
+                if (kb + 2 < n_kb) load_raw_q6k(nxt, row + (size_t)((kb + 2) >> 2) * blk_bytes, (kb + 2) & 3, h);  // one chunk ahead
                 float wv[32];
-                dequant32_q6k(row + (size_t)(kb >> 2) * blk_bytes, kb & 3, h, wv);
+                dequant32_q6k(cur, kb & 3, h, wv);
                 publish(wv, kb);
+                cur = nxt;
             }
         } else {
             RawQ4 cur, nxt;
