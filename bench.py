@@ -385,6 +385,7 @@ def run_secondary(args):
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: the kernels have no CPU fallback")
     K.mb200_init()
+    K.mb200_set_pdl(not args.no_pdl)
     dev = torch.device("cuda", 0)
     peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
     hbm = float(peaks.get("hbm_gbs", 6650.0))
@@ -424,7 +425,19 @@ def run_secondary(args):
                 by = nb * bb + 4 * (rows + cols)
                 out[name] = {"ms": ms, "GBs": by / ms / 1e6, "frac_of_measured_hbm": by / ms / 1e6 / hbm, "bytes": by}
                 del w
-            line = {"workload": "matvec 151936x4096 (lm_head shape), one CUDA graph of the steps", "results": out}
+            # BASELINE configs[0]: one Q4_K matvec 8192 x 4096 (18.9 MB per call): 16 weight copies in rotation (302 MB > L2)
+            rows1, copies = 8192, 16
+            nb1 = rows1 * cols // 256
+            w = torch.empty(copies * nb1 * 144, dtype=torch.uint8, device=dev)
+            K.mb200_fill_q4k(w, copies * nb1, 5)
+            ws = [w[i * nb1 * 144:(i + 1) * nb1 * 144] for i in range(copies)]
+            x = torch.randn(cols, device=dev)
+            y = torch.empty(rows1, device=dev)
+            ms = timed(lambda i: K.cuda_matvec_q4k(ws[i % copies], x, y, rows1, cols), max(steps, 32), warmup)
+            by = nb1 * 144 + 4 * (rows1 + cols)
+            out["cfg0_q4k_8192x4096"] = {"ms": ms, "GBs": by / ms / 1e6, "frac_of_measured_hbm": by / ms / 1e6 / hbm, "bytes": by}
+            line = {"workload": "matvec 151936x4096 (lm_head shape) and configs[0] 8192x4096, one CUDA graph of the steps each",
+                    "results": out}
         elif args.workload == "gemm":
             # configs 3a: dense prefill GEMM 512 tokens x (8192 x 4096), weights rotate over 8 copies
             M, N, Kd, copies = 512, 8192, 4096, 8
