@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload moe_block|matvec|gemm|prefill] [--no-fused | --fused-mode 1|2] [--no-pdl]
 
-Workload (BASELINE config 2): router fp32 128x4096 -> top-8 of 128 experts; per routed expert a
+Workload (the MoE-block configuration of the benchmark spec): router fp32 128x4096 -> top-8 of 128 experts; per routed expert a
 fused gate+up Q4_K matvec (2 x 1536x4096) with SwiGLU and a Q6_K down matvec (4096x1536), weighted
 sum + residual. Weights are seeded synthetic GGUF blocks with the benchmark's distributions
 (mnemocuda_b200/synth.py); no dataset or checkpoint is involved. A "step" is one block on one
@@ -425,7 +425,7 @@ def run_secondary(args):
                 by = nb * bb + 4 * (rows + cols)
                 out[name] = {"ms": ms, "GBs": by / ms / 1e6, "frac_of_measured_hbm": by / ms / 1e6 / hbm, "bytes": by}
                 del w
-            # BASELINE configs[0]: one Q4_K matvec 8192 x 4096 (18.9 MB per call): 16 weight copies in rotation (302 MB > L2)
+            # the single-matvec configuration of the benchmark spec: one Q4_K matvec 8192 x 4096 (18.9 MB per call): 16 weight copies in rotation (302 MB > L2)
             rows1, copies = 8192, 16
             nb1 = rows1 * cols // 256
             w = torch.empty(copies * nb1 * 144, dtype=torch.uint8, device=dev)
