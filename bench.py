@@ -108,8 +108,9 @@ def cpu_block_baseline(shape, experts_host, router_host, seconds=12.0, threads=N
     """Oracle MoE blocks per second on the host cores -> GB/s of algorithmic bytes."""
     from oracle import oracle
     from mnemocuda_b200 import synth
-    if threads:
-        oracle.set_num_threads(threads)
+    if not threads:  # all host cores, whatever OMP_NUM_THREADS says
+        threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    oracle.set_num_threads(threads)
     cores = oracle.num_threads()
     s = shape
     n, t0 = 0, time.perf_counter()
@@ -160,6 +161,8 @@ def run_reference(args):
     if experts is None:
         experts, router = host_layer(shape)
     from oracle import oracle
+    # all host cores, also under torchrun (which sets OMP_NUM_THREADS=1 for its workers)
+    oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     cores = oracle.num_threads()
     from mnemocuda_b200 import synth
     s = shape
