@@ -13,8 +13,13 @@ By default a block is ONE launch of this library (mb200_moe_block: routing, gate
 cooperative kernel); --no-fused times the three-launch form.
 
 `value` is algorithmic GB/s (router + the 8 routed expert blobs = 100 007 936 B per step) with all
-inputs resident in HBM, timed with CUDA events around a CUDA graph of the K steps. `e2e` is the
-same metric through the host-buffer call (pinned host x/residual in, result out, every step).
+inputs resident in HBM, timed with CUDA events around a CUDA graph of the K steps, replayed 20 times
+(median; the minimum is reported beside it). `e2e` is the same metric through the host-buffer call
+(mb200_moe_block_host: pinned host x/residual in, result out, every step).
+The same JSON line also carries, at N = 1: `parity` (the GPU result of one block against the oracle,
+outside the timed region; the run fails if it is off), `matvec` (the single Q4_K 8192x4096 matvec of the
+benchmark spec and the vocabulary-sized Q4_K / Q6_K matvecs) and `decode` (whole-token decode of the
+30B and 235B shapes: tokens/s and the fraction of the HBM roofline).
 `roofline` is for the dominant kernel (the expert phases of the fused kernel, timed alone; with
 --no-fused the routed gate/up stream kernel). `cpu_baseline` and `--impl reference` time the C
 oracle (the CPU restatement of the reference's algorithm -- the reference has no CPU implementation
@@ -40,13 +45,11 @@ UNIT = "GB/s"
 WORKLOAD = ("configs[1]: MoE expert block, batch 1, Qwen3-235B shape -- router fp32 128x4096 + top-8 of 128 "
             "experts, Q4_K gate/up 2x(1536x4096)+SwiGLU, Q6_K down 4096x1536, weighted sum + residual")
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one routed gate/up launch (8 experts, 56 623 104
-# algorithmic bytes), from the ncu capture summarised in profiles/; None until captured.
-GATE_UP_TRAFFIC_BYTES = 56726784 + 569088  # profiles/moe_block_stream_kernels_ncu.md
-# same for one launch of the fused routed-expert kernel (98 041 856 algorithmic bytes)
-# one launch of the whole block (100 007 936 algorithmic bytes): profiles/moe_block_one_launch_ncu.md
-BLOCK_TRAFFIC_BYTES = 100186880 + 4039680
-FUSED_TRAFFIC_BYTES = 98054912 + 3864064  # profiles/moe_fused_kernel_ncu.md (expert phases alone, as timed for `roofline`)
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the kernel at
+# this workload's shape; it cannot be measured inside a timed run, so it is recorded here):
+GATE_UP_TRAFFIC_BYTES = 56726784 + 569088    # routed gate/up stream kernel, 8 experts (56 623 104 algorithmic bytes)
+BLOCK_TRAFFIC_BYTES = 100186880 + 4039680    # the whole block in one launch (100 007 936 algorithmic bytes)
+FUSED_TRAFFIC_BYTES = 98054912 + 3864064     # the fused routed-expert kernel alone (98 041 856 algorithmic bytes)
 
 
 def measured_peaks():
@@ -113,17 +116,19 @@ def cpu_block_baseline(shape, experts_host, router_host, seconds=12.0, threads=N
     oracle.set_num_threads(threads)
     cores = oracle.num_threads()
     s = shape
-    n, t0 = 0, time.perf_counter()
+    n, t0, first = 0, time.perf_counter(), None
     while True:
         x = synth.normal_f32(900 + n, s.H)
         res = synth.normal_f32(1900 + n, s.H)
-        oracle.moe_block(router_host, experts_host, s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE, s.K, s.H, s.EFF,
-                         x, res)
+        r = oracle.moe_block(router_host, experts_host, s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE, s.K, s.H,
+                             s.EFF, x, res)
+        if first is None:
+            first = r  # (out, ids, weights) of the block on x = stream 900, residual = stream 1900: the parity check
         n += 1
         dt = time.perf_counter() - t0
         if dt >= seconds or n >= 4000:
             break
-    return s.algorithmic_bytes * n / dt / 1e9, cores, n, dt
+    return s.algorithmic_bytes * n / dt / 1e9, cores, n, dt, first
 
 
 def host_layer(shape, seed=1, layer=0):
@@ -145,21 +150,12 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from mnemocuda_b200.moe import MoEShape
-    shape = MoEShape()
-    experts, router = None, None
-    try:
-        import torch
-        if torch.cuda.is_available():
-            from mnemocuda_b200.moe import ResidentMoE
-            moe = ResidentMoE(shape, 1, "cuda:0", seed=1)
-            experts = moe.experts[0].reshape(-1).cpu().numpy()
-            router = moe.router[0].reshape(-1).cpu().numpy()
-            del moe
-    except Exception:
-        experts = None
-    if experts is None:
-        experts, router = host_layer(shape)
+    from types import SimpleNamespace
+    from mnemocuda_b200 import synth
+    g, u, d = synth.expert_sizes(4096, 1536, 14)
+    shape = SimpleNamespace(NE=128, K=8, H=4096, EFF=1536, down_type=14, gate_sz=g, up_sz=u, down_sz=d, stride=g + u + d,
+                            algorithmic_bytes=128 * 4096 * 4 + 8 * (g + u + d))
+    experts, router = host_layer(shape)  # numpy generator: nothing of the GPU library is loaded in this arm
     from oracle import oracle
     # all host cores, also under torchrun (which sets OMP_NUM_THREADS=1 for its workers)
     oracle.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
@@ -181,12 +177,118 @@ def run_reference(args):
     value = s.algorithmic_bytes * per_step * args.steps / dt / 1e9
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 dot, fp32 accumulate",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp32 (C oracle)",
             "data": "synthetic", "config": {"workload": WORKLOAD},
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": f"{per_step} MoE blocks per step on layer 0 (C oracle, OpenMP over rows)"},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+class Timer:
+    """CUDA-event timing of a CUDA graph that holds `steps` steps: `replays` replays, each bracketed by events
+    on the launching stream; returns (median, min) ms per step."""
+
+    def __init__(self, torch, barrier=None):
+        self.torch, self.barrier = torch, barrier or (lambda: torch.cuda.synchronize())
+
+    def graph(self, fn, steps, warmup, replays=20):
+        torch = self.torch
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(steps):
+                fn(warmup + i)
+        g.replay()  # untimed: instantiate / upload
+        self.barrier()
+        return self.replays(g, steps, replays)
+
+    def replays(self, g, steps, replays=20):
+        torch = self.torch
+        times = []
+        for _ in range(replays):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            self.barrier()
+            times.append(e0.elapsed_time(e1) / steps)
+        return float(np.median(times)), float(min(times))
+
+    def eager(self, fn, steps, warmup):
+        torch = self.torch
+        for i in range(warmup):
+            fn(i)
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        self.barrier()
+        ms = e0.elapsed_time(e1) / steps
+        return ms, ms
+
+
+def measure_matvec(torch, K, dev, timer, hbm, steps, warmup):
+    """The plain matvecs of the path: the single Q4_K 8192 x 4096 matvec of the benchmark spec (64 weight copies in
+    rotation = 1.2 GB, so every call is cold in L2; one PDL chain in one CUDA graph) and the vocabulary-sized
+    Q4_K / Q6_K matvecs (151936 x 4096: 350 / 510 MB per call)."""
+    out = {}
+    cols = 4096
+    rows1, copies = 8192, 64
+    nb1 = rows1 * cols // 256
+    w = torch.empty(copies * nb1 * 144, dtype=torch.uint8, device=dev)
+    K.mb200_fill_q4k(w, copies * nb1, 5)
+    ws = [w[i * nb1 * 144:(i + 1) * nb1 * 144] for i in range(copies)]
+    x = torch.randn(cols, device=dev)
+    y = torch.empty(rows1, device=dev)
+    med, mn = timer.graph(lambda i: K.cuda_matvec_q4k(ws[i % copies], x, y, rows1, cols), max(steps, 2 * copies), warmup)
+    by = nb1 * 144 + 4 * (rows1 + cols)
+    out["cfg0_q4k_8192x4096"] = {"ms": med, "ms_min": mn, "GBs": by / med / 1e6, "frac_of_measured_hbm": by / med / 1e6 / hbm,
+                                 "bytes": by, "weight_copies": copies}
+    del w, ws
+    rows = 151936
+    for name, bb, fill, call in (("q4k_151936x4096", 144, K.mb200_fill_q4k, K.cuda_matvec_q4k),
+                                 ("q6k_151936x4096", 210, K.mb200_fill_q6k, K.cuda_matvec_q6k)):
+        nb = rows * cols // 256
+        w = torch.empty(nb * bb, dtype=torch.uint8, device=dev)
+        fill(w, nb, 3)
+        y = torch.empty(rows, device=dev)
+        med, mn = timer.graph(lambda i: call(w, x, y, rows, cols), min(steps, 50), warmup, replays=5)
+        by = nb * bb + 4 * (rows + cols)
+        out[name] = {"ms": med, "ms_min": mn, "GBs": by / med / 1e6, "frac_of_measured_hbm": by / med / 1e6 / hbm, "bytes": by}
+        del w
+    torch.cuda.empty_cache()
+    return out
+
+
+def measure_decode(torch, K, dev, timer, hbm, which, tokens, expert_range=None):
+    """Whole-token decode of a model shape resident in HBM: `tokens` tokens in one CUDA graph at the last
+    position of the context (KV cache pre-filled up to it), replayed 5 times."""
+    from mnemocuda_b200.decode import DecodeConfig, ResidentModel
+    cfg = DecodeConfig.qwen3_30b() if which == "30b" else DecodeConfig.qwen3_235b()
+    t0 = time.perf_counter()
+    model = ResidentModel(cfg, dev, seed=1, expert_range=expert_range)
+    torch.cuda.synchronize()
+    build_s = time.perf_counter() - t0
+    model.set_state(1, cfg.ctx_len - 1)
+    g = model.capture(tokens, advance=False)
+    g.replay()
+    torch.cuda.synchronize()
+    med, mn = timer.replays(g, tokens, replays=5)
+    by = cfg.algorithmic_bytes_per_token()
+    res = {"config": (f"{cfg.name} decode, batch 1, context {cfg.ctx_len} (position {cfg.ctx_len - 1}), {cfg.n_layers} layers, "
+                      f"{cfg.n_experts} experts top-{cfg.top_k}, Q4_K_M-style types, all experts resident"),
+           "tok_s": 1e3 / med, "ms_per_token": med, "ms_per_token_min": mn, "bytes_per_token": by,
+           "GBs": by / med / 1e6, "frac": by / med / 1e6 / hbm, "resident_GB": round(cfg.resident_bytes() / 1e9, 1),
+           "tokens_per_graph": tokens, "launches_per_token": 2 + 8 * cfg.n_layers + 3, "build_s": round(build_s, 1),
+           "sampled_token": int(model.token.item())}
+    del model, g
+    torch.cuda.empty_cache()
+    return res
 
 
 def run_ours(args):
@@ -217,11 +319,12 @@ def run_ours(args):
     K.mb200_set_pdl(not args.no_pdl)
     K.mb200_set_fused(0 if args.no_fused else args.fused_mode)
     H = shape.H
-    xs = torch.empty(layers, H, device=dev)
-    rs = torch.empty(layers, H, device=dev)
-    outs = torch.empty(layers, H, device=dev)
-    K.mb200_fill_normal_f32(xs, layers * H, 4242, 1.0)
-    K.mb200_fill_normal_f32(rs, layers * H, 4243, 1.0)
+    n_x = max(layers, 48)  # distinct activation vectors: a layer sees a different x (hence other experts) each pass
+    xs = torch.empty(n_x, H, device=dev)
+    rs = torch.empty(n_x, H, device=dev)
+    outs = torch.empty(n_x, H, device=dev)
+    K.mb200_fill_normal_f32(xs, n_x * H, 4242, 1.0)
+    K.mb200_fill_normal_f32(rs, n_x * H, 4243, 1.0)
     torch.cuda.synchronize()
 
     def barrier():
@@ -229,84 +332,55 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed_graph(fn, steps, warmup):
-        """fn(i) enqueues step i; returns ms per step for `steps` steps captured in one CUDA graph."""
-        for i in range(warmup):
-            fn(i)
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            for i in range(steps):
-                fn(warmup + i)
-        g.replay()  # untimed: instantiate/upload
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        g.replay()
-        e1.record()
-        barrier()
-        return e0.elapsed_time(e1) / steps
+    timer = Timer(torch, barrier)
 
     # ---- device-resident: the whole block, K steps in one graph ----
     if world > 1:
-        block = lambda i: smoe.forward(i % layers, xs[i % layers], rs[i % layers], outs[i % layers])
+        block = lambda i: smoe.forward(i % layers, xs[i % n_x], rs[i % n_x], outs[i % n_x])
     else:
-        block = lambda i: moe.forward(i % layers, xs[i % layers], rs[i % layers], outs[i % layers])
+        block = lambda i: moe.forward(i % layers, xs[i % n_x], rs[i % n_x], outs[i % n_x])
 
-    def timed_eager(fn, steps, warmup):
-        for i in range(warmup):
-            fn(i)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(steps):
-            fn(warmup + i)
-        e1.record()
-        barrier()
-        return e0.elapsed_time(e1) / steps
-
-    timing_how = "CUDA events around one CUDA graph of the timed steps"
+    timing_how = "CUDA events around a CUDA graph of the timed steps, 20 replays, median"
     with ClockSampler(local) as clk:
         try:
-            ms = timed_graph(block, args.steps, args.warmup)
+            ms, ms_min = timer.graph(block, args.steps, args.warmup)
         except Exception as exc:  # a collective that cannot be captured: time the eager loop instead
             if world == 1:
                 raise
             torch.cuda.synchronize()
             timing_how = f"CUDA events around the eager loop (graph capture failed: {type(exc).__name__})"
-            ms = timed_eager(block, args.steps, args.warmup)
+            ms, ms_min = timer.eager(block, args.steps, args.warmup)
         # ---- dominant kernel alone (ids already routed by the runs above) ----
         if world == 1:
-            gu_ms = timed_graph(lambda i: moe.gate_up(i % layers, xs[i % layers]), args.steps, args.warmup)
-            dn_ms = timed_graph(lambda i: moe.down(i % layers, rs[i % layers], outs[i % layers]), args.steps, args.warmup)
-            rt_ms = timed_graph(lambda i: moe.route(i % layers, xs[i % layers]), args.steps, args.warmup)
+            gu_ms, _ = timer.graph(lambda i: moe.gate_up(i % layers, xs[i % layers]), args.steps, args.warmup, 5)
+            dn_ms, _ = timer.graph(lambda i: moe.down(i % layers, rs[i % layers], outs[i % layers]), args.steps, args.warmup, 5)
+            rt_ms, _ = timer.graph(lambda i: moe.route(i % layers, xs[i % layers]), args.steps, args.warmup, 5)
             try:
-                fu_ms = timed_graph(lambda i: moe.experts_fused(i % layers, xs[i % layers], rs[i % layers], outs[i % layers]),
-                                    args.steps, args.warmup)
+                fu_ms, _ = timer.graph(lambda i: moe.experts_fused(i % layers, xs[i % layers], rs[i % layers], outs[i % layers]),
+                                       args.steps, args.warmup, 5)
             except RuntimeError:
                 fu_ms = None  # shape outside the fused kernel
         else:
             gu_ms = dn_ms = rt_ms = fu_ms = None
     if world > 1:
-        t = torch.tensor([ms], device=dev)
+        t = torch.tensor([ms, ms_min], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        ms, ms_min = float(t[0].item()), float(t[1].item())
     # N > 1 shards ONE block over the GPUs (strong scaling): the job's bytes per step stay those of one block
     value = shape.algorithmic_bytes / (ms * 1e-3) / 1e9
 
     # ---- end to end through host buffers ----
     host_block = HostMoEBlock(moe, smoe if world > 1 else None)
-    hx = torch.randn(layers, H).pin_memory()
-    hr = torch.randn(layers, H).pin_memory()
-    ho = torch.empty(layers, H).pin_memory()
+    hxr = torch.randn(n_x, 2, H).pin_memory()
+    ho = torch.empty(n_x, H).pin_memory()
     for i in range(args.warmup):
-        host_block(i % layers, hx[i % layers], hr[i % layers], ho[i % layers])
+        host_block(i % layers, hxr[i % n_x], ho[i % n_x])
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
-        j = (args.warmup + i) % layers
-        host_block(j, hx[j], hr[j], ho[j])
+        j = args.warmup + i
+        host_block(j % layers, hxr[j % n_x], ho[j % n_x])
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / args.steps
@@ -329,7 +403,7 @@ def run_ours(args):
     fused = bool(fu_ms) and not args.no_fused
     one_launch = fused and args.fused_mode == 2 and world == 1
     # Dominant kernel. One-launch form: the block IS one kernel (routing + gate/up + down), so its average
-    # duration is the step time of the timed graph (launch-to-launch, i.e. including the ~2.5 us between two
+    # duration is the step time of the timed graph (launch-to-launch, i.e. including the gap between two
     # launches) and its algorithmic bytes are the block's. Otherwise: the fused expert kernel, or with
     # --no-fused the routed gate/up stream kernel, timed alone.
     gu_bytes = shape.K * (shape.gate_sz + shape.up_sz) + shape.H * 4 + shape.K * shape.EFF * 4
@@ -344,18 +418,20 @@ def run_ours(args):
         dom_name = "stream_kernel<Q4,*> (routed gate/up + SwiGLU, 8 experts per launch)"
         dom_bytes, dom_ms, dom_traffic = gu_bytes, gu_ms, GATE_UP_TRAFFIC_BYTES
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms else None
+    per_rank_gb = moe.experts.numel() / 1e9
+    launches_per_step = ((1 if args.fused_mode == 2 else 2) if fused or (world > 1 and not args.no_fused) else 3)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+        "ms_per_step": ms, "ms_per_step_min": ms_min, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8 dot (u8 x s8 dp4a), fp32 accumulate", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers_resident": layers, "resident_GB": round(moe.experts.numel() / 1e9, 2),
-                   "l2": "inputs larger than L2: steps rotate over resident layers, 1.57 GB of experts each",
+        "config": {"workload": WORKLOAD, "layers_resident": layers, "resident_GB_per_rank": round(per_rank_gb, 2),
+                   "l2": (f"inputs larger than L2: steps rotate over {layers} resident layers and {n_x} activation vectors; "
+                          f"{per_rank_gb:.1f} GB of expert weights per rank, any of which a step may route to"),
                    "timing": timing_how, "pdl": not args.no_pdl,
                    "parallelism": (f"experts sharded {world}-way (router replicated), NCCL all-reduce of the 16 KB partial hidden vector"
                                    if world > 1 else "single GPU")},
         "clocks": clk.summary(),
-        # one launch per block when the fused kernel also routes (sharded: one launch + the NCCL all-reduce)
-        "gpu_launches": ((1 if args.fused_mode == 2 else 2) if (world == 1 and fused) else (1 if (world > 1 and not args.no_fused and args.fused_mode == 2) else (2 if world > 1 else 3))) * args.steps,
+        "gpu_launches": launches_per_step * args.steps,
         "kernels_ms": {"router_topk": rt_ms, "moe_experts_fused": fu_ms, "moe_gate_up": gu_ms, "moe_down": dn_ms},
     }
     if world == 1:
@@ -370,11 +446,43 @@ def run_ours(args):
     line["e2e"] = {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": host_block.h2d_bytes,
                    "d2h_bytes_per_step": host_block.d2h_bytes}
     if world == 1 and not args.no_cpu_baseline:
+        from mnemocuda_b200 import synth
         experts_host = moe.experts[0].reshape(-1).cpu().numpy()
         router_host = moe.router[0].reshape(-1).cpu().numpy()
-        v, cores, n, dt = cpu_block_baseline(shape, experts_host, router_host, seconds=args.cpu_seconds)
+        v, cores, n, dt, first = cpu_block_baseline(shape, experts_host, router_host, seconds=args.cpu_seconds)
         line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
                                 "sample": f"{n} MoE blocks on layer 0 in {dt:.1f} s (C oracle, OpenMP over rows)"}
+        # parity, outside any timed region: the same block (layer 0, x = stream 900, residual = stream 1900) on the GPU
+        want, i_ref, w_ref = first
+        dx = torch.from_numpy(synth.normal_f32(900, H)).to(dev)
+        dr = torch.from_numpy(synth.normal_f32(1900, H)).to(dev)
+        do = torch.empty(H, device=dev)
+        moe.forward(0, dx, dr, do)
+        torch.cuda.synchronize()
+        got = do.cpu().numpy().astype(np.float64)
+        rel = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+        ids_equal = bool(np.array_equal(moe.ids[0].cpu().numpy(), i_ref))
+        line["parity"] = {"rel_l2": rel, "ids_equal": ids_equal, "tolerance": 1e-3,
+                          "against": "C oracle (CPU restatement of the reference), same layer and inputs"}
+        if rel > 1e-3 or not ids_equal:
+            print(json.dumps(line), flush=True)
+            raise RuntimeError(f"parity check failed: rel L2 {rel:.3e}, ids equal {ids_equal}")
+    if world == 1 and not args.no_extras:
+        del moe, host_block
+        torch.cuda.empty_cache()
+        with ClockSampler(local) as clk2:
+            line["matvec"] = measure_matvec(torch, K, dev, timer, peak, args.steps, args.warmup)
+            line["decode"] = {}
+            for which_model in ("30b", "235b"):
+                try:
+                    line["decode"][which_model] = measure_decode(torch, K, dev, timer, peak, which_model, args.decode_tokens)
+                except torch.OutOfMemoryError as exc:
+                    line["decode"][which_model] = {"unavailable": f"out of device memory: {exc}"[:200]}
+                    torch.cuda.empty_cache()
+        line["clocks_extras"] = clk2.summary()
+        err = K.mb200_device_error()
+        if err != 0:
+            raise RuntimeError(f"a kernel reported device error {err}")
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -393,56 +501,20 @@ def run_secondary(args):
     peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
     hbm = float(peaks.get("hbm_gbs", 6650.0))
     tf = float(peaks.get("bf16_tflops", 1590.0))
-
-    def timed(fn, steps, warmup):
-        """ms per step of `steps` steps replayed as one CUDA graph, CUDA events around the replay."""
-        for i in range(warmup):
-            fn(i)
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            for i in range(steps):
-                fn(warmup + i)
-        g.replay()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        g.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / steps
+    timer = Timer(torch)
+    timed = lambda fn, steps, warmup: timer.graph(fn, steps, warmup, replays=5)[0]
 
     steps, warmup = args.steps, args.warmup
     with ClockSampler(0) as clk:
         if args.workload == "matvec":
-            # the vocabulary-sized matvec (151936 x 4096): 350 MB (Q4_K) / 510 MB (Q6_K) per pass, larger than L2
-            rows, cols = 151936, 4096
-            out = {}
-            for name, bb, fill, call in (("q4k", 144, K.mb200_fill_q4k, K.cuda_matvec_q4k), ("q6k", 210, K.mb200_fill_q6k, K.cuda_matvec_q6k)):
-                nb = rows * cols // 256
-                w = torch.empty(nb * bb, dtype=torch.uint8, device=dev)
-                fill(w, nb, 3)
-                x = torch.randn(cols, device=dev)
-                y = torch.empty(rows, device=dev)
-                ms = timed(lambda i: call(w, x, y, rows, cols), steps, warmup)
-                by = nb * bb + 4 * (rows + cols)
-                out[name] = {"ms": ms, "GBs": by / ms / 1e6, "frac_of_measured_hbm": by / ms / 1e6 / hbm, "bytes": by}
-                del w
-            # the single-matvec configuration of the benchmark spec: one Q4_K matvec 8192 x 4096 (18.9 MB per call): 16 weight copies in rotation (302 MB > L2)
-            rows1, copies = 8192, 16
-            nb1 = rows1 * cols // 256
-            w = torch.empty(copies * nb1 * 144, dtype=torch.uint8, device=dev)
-            K.mb200_fill_q4k(w, copies * nb1, 5)
-            ws = [w[i * nb1 * 144:(i + 1) * nb1 * 144] for i in range(copies)]
-            x = torch.randn(cols, device=dev)
-            y = torch.empty(rows1, device=dev)
-            ms = timed(lambda i: K.cuda_matvec_q4k(ws[i % copies], x, y, rows1, cols), max(steps, 32), warmup)
-            by = nb1 * 144 + 4 * (rows1 + cols)
-            out["cfg0_q4k_8192x4096"] = {"ms": ms, "GBs": by / ms / 1e6, "frac_of_measured_hbm": by / ms / 1e6 / hbm, "bytes": by}
-            line = {"workload": "matvec 151936x4096 (lm_head shape) and configs[0] 8192x4096, one CUDA graph of the steps each",
-                    "results": out}
+            line = {"workload": "single Q4_K matvec 8192x4096 (64 weight copies, PDL chain) and 151936x4096 matvecs",
+                    "results": measure_matvec(torch, K, dev, timer, hbm, steps, warmup)}
+        elif args.workload in ("decode30b", "decode235b"):
+            which_model = args.workload[6:]
+            line = {"workload": f"whole-token decode, {which_model} shape",
+                    "results": measure_decode(torch, K, dev, timer, hbm, which_model, args.decode_tokens)}
         elif args.workload == "gemm":
-            # configs 3a: dense prefill GEMM 512 tokens x (8192 x 4096), weights rotate over 8 copies
+            # prefill configuration, dense part: GEMM 512 tokens x (8192 x 4096), weights rotate over 8 copies
             M, N, Kd, copies = 512, 8192, 4096, 8
             out = {}
             for name, bb, fill, call in (("q4k", 144, K.mb200_fill_q4k, K.mb200_gemm_q4k_f16), ("q6k", 210, K.mb200_fill_q6k, K.mb200_gemm_q6k_f16)):
@@ -456,9 +528,9 @@ def run_secondary(args):
                 fl = 2.0 * M * N * Kd
                 out[name] = {"ms": ms, "TFLOPs": fl / ms / 1e9, "frac_of_measured_bf16_burst": fl / ms / 1e9 / tf}
                 del w
-            line = {"workload": "configs 3a: prefill GEMM 512 x 8192 x 4096, fp16 tcgen05 with in-kernel dequant", "results": out}
+            line = {"workload": "prefill GEMM 512 x 8192 x 4096, fp16 tcgen05 with in-kernel dequant", "results": out}
         else:
-            # configs 3b: grouped per-expert prefill, 512 tokens, top-8 of 128 experts
+            # prefill configuration, grouped part: 512 tokens, top-8 of 128 experts
             shape = MoEShape()
             s = shape
             moe = ResidentMoE(shape, 1, dev, seed=1)
@@ -478,7 +550,7 @@ def run_secondary(args):
                                                      s.EFF, x, ids, wts, res, y, M, cap, ws), steps, warmup)
             fl = 2.0 * M * k * 3 * s.EFF * s.H
             wb = s.NE * s.stride
-            line = {"workload": "configs 3b: grouped per-expert prefill MoE block, 512 tokens, top-8 of 128 experts",
+            line = {"workload": "grouped per-expert prefill MoE block, 512 tokens, top-8 of 128 experts",
                     "results": {"ms": ms, "TFLOPs": fl / ms / 1e9, "weights_GBs": wb / ms / 1e6,
                                 "hbm_floor_ms": wb / hbm / 1e6, "tokens_per_expert_max": int(cnt.max()), "cap": cap}}
     err = K.mb200_device_error()
@@ -501,8 +573,12 @@ def main():
                     help="2: one launch per block (routing inside the fused kernel); 1: router kernel + fused expert kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    ap.add_argument("--workload", default="moe_block", choices=["moe_block", "matvec", "gemm", "prefill"],
+    ap.add_argument("--workload", default="moe_block",
+                    choices=["moe_block", "matvec", "gemm", "prefill", "decode30b", "decode235b"],
                     help="moe_block is the headline; the others print a secondary line for the same path")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="headline only: skip the matvec and whole-token decode sections of the JSON line")
+    ap.add_argument("--decode-tokens", type=int, default=8, help="tokens per timed CUDA graph of the decode section")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -83,6 +83,59 @@ void cuda_swiglu(const float *gate, const float *up, float *out, int n, cudaStre
 /* out += scale * x. Replaces src/kernels.cu:1293-1299 (kernel :980-988). */
 void cuda_scaled_add(float *out, const float *x, float scale, int n, cudaStream_t stream);
 
+/* ---- support operators of a decode step (same names and signatures as the reference) ----
+ * Not part of the quantized-weight hot path, but a decode token needs them between the
+ * matvecs, and the reference's forward.c / engine.c import them (src/forward.c:24-152). */
+
+/* out = in * weight / sqrt(mean(in^2) + eps). Replaces src/kernels.cu:1187-1193 (kernel :692-722). */
+void cuda_rms_norm(const float *input, const float *weight, float *output, int n, float eps,
+                   cudaStream_t stream);
+/* Same, and copies the input to residual_output. Replaces src/kernels.cu:1178-1185 (kernel :725-749). */
+void cuda_rms_norm_residual(const float *input, const float *weight, float *normed_output,
+                            float *residual_output, int n, float eps, cudaStream_t stream);
+/* RMSNorm of each of n_heads vectors of head_dim with one shared weight. Replaces src/kernels.cu:1221-1227. */
+void cuda_rms_norm_batched(const float *input, const float *weight, float *output, int head_dim,
+                           int n_heads, float eps, cudaStream_t stream);
+/* In-place per-head RMSNorm of q (n_q heads) and k (n_k heads). Replaces src/kernels.cu:1229-1236 (kernel :1196-1219). */
+void cuda_rms_norm_qk(float *q, float *k, const float *q_weight, const float *k_weight, int head_dim,
+                      int n_q, int n_k, float eps, cudaStream_t stream);
+/* Half-split rotary embedding of q and k at `pos`, in place; angles and their sine / cosine are evaluated
+ * in double precision (as tools/validate_rope_norm.py:168-197 does). Replaces src/kernels.cu:1256-1273
+ * (kernel :818-852); unlike the reference wrapper it copies nothing lazily, so the first call is legal
+ * during stream capture. */
+void cuda_rope(float *q, float *k, int head_dim, int pos, float theta, int n_heads_q, int n_heads_k,
+               cudaStream_t stream);
+/* fp32 -> fp16 (round to nearest even): the KV-cache store. Replace src/kernels.cu:1314-1333. */
+void cuda_f32_to_f16(const float *in, void *out, int n, cudaStream_t stream);
+void cuda_f32_to_f16_dual(const float *a, const float *b, void *oa, void *ob, int n, cudaStream_t stream);
+/* Decode attention of one token over an fp16 KV cache laid out [position][kv head][head_dim]:
+ * out[h] = softmax_p(scale * q[h] . K[p][h / gqa_ratio]) V[p][h / gqa_ratio], p < seq_len.
+ * Replaces src/kernels.cu:1662-1671 (kernel :1550-1660). head_dim 128 runs on tensor cores with all
+ * query heads of a KV head in one CTA and the positions split over the SMs (the partial results pass
+ * through a workspace inside the library image, about 2 MB per device); other head sizes (<= 1024)
+ * run a plain kernel. q, the cache and out must be 16-byte aligned for the fast path. */
+void cuda_attention_f16kv(const void *q, const void *kv_k, const void *kv_v, float *out, int n_heads_q,
+                          int head_dim, int n_kv_heads, int seq_len, int gqa_ratio, float scale,
+                          cudaStream_t stream);
+/* out = a + b. Replaces src/kernels.cu:1238-1244 (kernel :784-793). */
+void cuda_residual_add(const float *a, const float *b, float *out, int n, cudaStream_t stream);
+/* output[0..hidden_size) = dequantised row token_id of a Q4_K table (w = d*sc*q - dmin*m, products and
+ * difference rounded separately as in tools/validate_dequant.py:68-115). Replaces src/kernels.cu:2192-2198
+ * (kernel :1901-1951, whose nibble indexing differs from the reference's own matvec, validator and CPU
+ * fallback src/forward.c:1189-1229; this follows the latter three). */
+void cuda_embedding_lookup_q4k(const void *embd_table, float *output, int token_id, int hidden_size,
+                               int row_bytes, cudaStream_t stream);
+/* Greedy sampling: *d_result = argmax(logits), ties resolved as the reference's scan does
+ * (src/kernels.cu:2048-2071). temperature > 0 (nucleus sampling, :2073-2174) is not implemented:
+ * the argmax is returned and mb200_last_status() reports MB200_ERR_UNSUPPORTED. Replaces :2208-2215. */
+void cuda_sample_token(const float *logits, int vocab_size, float temperature, float top_p,
+                       unsigned long long rng_state, int *d_result, cudaStream_t stream);
+/* Addresses of the RoPE, KV-store and attention kernels, whose parameter order is the reference's, for a
+ * caller that patches graph nodes by parameter index (src/forward.c:1295-1297, 636-661). Replace src/kernels.cu:2243-2245. */
+void *cuda_get_rope_kernel_ptr(void);
+void *cuda_get_f16dual_kernel_ptr(void);
+void *cuda_get_attn_f16kv_kernel_ptr(void);
+
 /* ===================== Part 2: additions (status-returning) ===================== */
 
 enum {
@@ -100,6 +153,8 @@ const char *mb200_last_status_where(void);
 void mb200_clear_status(void);
 /* Synchronises the device and returns the device-side error word (0 = no kernel gave up on a wait). */
 int mb200_device_error(void);
+/* Zeroes the current device's error word in stream order, so that later checks report new failures only. */
+int mb200_clear_device_error(cudaStream_t stream);
 
 /* Programmatic dependent launch for the streaming matvec kernels. 0 (default): plain
  * launches. 1: each kernel may start while the previous kernel of the stream is still
@@ -144,8 +199,9 @@ int mb200_router_topk(const float *router_w, const float *x, void *scratch, int 
  * logits live in an array inside the library image instead (about 4 KB, held on each device
  * that loads the library until the process exits), so n_experts is limited to 1024; larger
  * values are refused with MB200_ERR_UNSUPPORTED. Nothing is allocated or freed by the call.
- * The first call on a device looks up the array's device address (the device must be current);
- * make that first call before starting any stream capture. All calls on a device share the one
+ * cuda_kernels_init() / mb200_init() look up the array's device address for the device that is current
+ * when they run; on a device they were not called for, the first call here does the lookup (the device
+ * must be current), so make that first call before starting any stream capture. All calls on a device share the one
  * array: calls whose kernels can overlap on the GPU (different streams) race on it -- serialise
  * them or use mb200_router_topk with separate scratch buffers. */
 int mb200_router_topk_static(const float *router_w, const float *x, int *indices, float *weights,
@@ -220,6 +276,17 @@ int mb200_moe_block_local(const float *router_w, const void *experts, size_t exp
                           int H, int EFF, const float *x, const float *residual, float *out, int *ids,
                           float *wts, float *act, void *scratch, cudaStream_t stream);
 
+/* The block for a caller that keeps the hidden state in HOST memory (pinned, for the copies to be
+ * asynchronous): host_x_res = [x | residual], 2*H floats; host_out receives H floats. dev_io is 3*H floats
+ * of device memory the caller lends (x, residual, result). One copy in, the block (mb200_moe_block_local's
+ * arguments; expert_cnt 0 = all experts are here), one copy out, and the stream is synchronised before the
+ * call returns. The reference's engine moves hidden vectors through the host the same way when peer
+ * access is unavailable (src/forward.c:1573-1578). */
+int mb200_moe_block_host(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz,
+                         size_t up_sz, int down_type, int n_experts, int expert_lo, int expert_cnt, int k, int H,
+                         int EFF, const float *host_x_res, float *host_out, float *dev_io, int *ids, float *wts,
+                         float *act, void *scratch, cudaStream_t stream);
+
 /* ---- prefill GEMM on tcgen05 tensor cores ----
  * out[t][n] = sum_k f16(X[t][k]) * dequant(W)[n][k]; X fp16 [M x K] row-major (16-byte aligned),
  * W Q4_K / Q6_K [N x K] as for the matvecs, out fp32 [M x N]; K a multiple of 256. Weights are
@@ -247,6 +314,51 @@ int mb200_moe_prefill(const void *experts, size_t expert_stride, size_t gate_sz,
                       int n_experts, int k, int H, int EFF, const void *x_f16, const int *ids,
                       const float *wts, const float *residual, float *y, int M, int max_tokens_per_expert,
                       void *workspace, cudaStream_t stream);
+
+/* ---- whole-token decode (the op order of src/forward.c:1635-1707 and :604-1117, no host round trip) ----
+ * The caller owns every buffer: weights, KV cache, workspace, token / position / logits. Nothing is
+ * allocated here. Tensor types are GGUF ids: 0 = fp32, 12 = Q4_K, 14 = Q6_K. */
+typedef struct mb200_layer_weights {
+    const float *attn_norm;          /* [hidden] */
+    const void *wq, *wk, *wv, *wo;   /* [n_heads*head_dim x hidden], [n_kv_heads*head_dim x hidden] x2, [hidden x n_heads*head_dim] */
+    int wq_type, wk_type, wv_type, wo_type;
+    const float *q_norm, *k_norm;    /* [head_dim] each, or NULL for a model without q/k norm */
+    const float *ffn_norm;           /* [hidden] */
+    const float *router;             /* fp32 [n_experts x hidden] */
+    const void *experts;             /* blob of expert expert_lo, then the following ones (expert_stride apart) */
+    void *kv_k, *kv_v;               /* this layer's fp16 cache, [ctx_len][n_kv_heads][head_dim] each */
+} mb200_layer_weights;
+
+typedef struct mb200_decode_model {
+    int n_layers, hidden, n_heads, n_kv_heads, head_dim, n_experts, top_k, moe_inter, vocab, ctx_len;
+    float rms_eps, rope_theta;
+    int down_type, embd_type, lm_head_type;
+    size_t expert_stride, gate_sz, up_sz;   /* expert blob = [gate][up][down] (src/forward.c:1127-1136) */
+    int expert_lo, expert_cnt;              /* experts held on this device (0, 0 = all) */
+    const mb200_layer_weights *layers;      /* host array [n_layers] */
+    const void *token_embd;                 /* Q4_K [vocab x hidden] */
+    const float *output_norm;               /* [hidden] */
+    const void *lm_head;                    /* [vocab x hidden], lm_head_type */
+} mb200_decode_model;
+
+/* Bytes of device workspace a model needs (256-byte aligned; zero it once before the first token:
+ * it holds barrier / ticket counters that the kernels keep consistent afterwards). 0 = bad model. */
+size_t mb200_decode_workspace_bytes(const mb200_decode_model *m);
+/* The hidden state inside the workspace, fp32 [hidden] (input and output of mb200_decode_layer). */
+float *mb200_decode_hidden(const mb200_decode_model *m, void *workspace);
+/* One token: embedding of *d_token, all layers at position *d_pos, final norm, lm_head into d_logits
+ * [vocab], greedy sample into *d_token, *d_pos += 1. d_token / d_pos are device ints, read and written
+ * by kernels only, so a CUDA graph captured around this call decodes one more token on every replay.
+ * = mb200_decode_begin, mb200_decode_layer for each layer, mb200_decode_finish (which a caller that
+ * shards the model over devices issues itself, with its collectives in between). */
+int mb200_decode_step(const mb200_decode_model *m, void *workspace, int *d_token, int *d_pos, float *d_logits,
+                      cudaStream_t stream);
+int mb200_decode_begin(const mb200_decode_model *m, void *workspace, const int *d_token, const int *d_pos,
+                       cudaStream_t stream);
+int mb200_decode_layer(const mb200_decode_model *m, int layer, void *workspace, const int *d_pos,
+                       cudaStream_t stream);
+int mb200_decode_finish(const mb200_decode_model *m, void *workspace, float *d_logits, int *d_token, int *d_pos,
+                        cudaStream_t stream);
 
 /* Seeded synthetic tensors written on the device (benchmark workloads). */
 int mb200_fill_q4k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream);

@@ -28,11 +28,26 @@ SIGNATURES = {
     "cuda_topk_softmax": (None, [_vp, _vp, _vp, _i, _i, _vp]),
     "cuda_swiglu": (None, [_vp, _vp, _vp, _i, _vp]),
     "cuda_scaled_add": (None, [_vp, _vp, _f, _i, _vp]),
+    "cuda_rms_norm": (None, [_vp, _vp, _vp, _i, _f, _vp]),
+    "cuda_rms_norm_residual": (None, [_vp, _vp, _vp, _vp, _i, _f, _vp]),
+    "cuda_rms_norm_batched": (None, [_vp, _vp, _vp, _i, _i, _f, _vp]),
+    "cuda_rms_norm_qk": (None, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp]),
+    "cuda_rope": (None, [_vp, _vp, _i, _i, _f, _i, _i, _vp]),
+    "cuda_f32_to_f16": (None, [_vp, _vp, _i, _vp]),
+    "cuda_f32_to_f16_dual": (None, [_vp, _vp, _vp, _vp, _i, _vp]),
+    "cuda_attention_f16kv": (None, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
+    "cuda_residual_add": (None, [_vp, _vp, _vp, _i, _vp]),
+    "cuda_embedding_lookup_q4k": (None, [_vp, _vp, _i, _i, _i, _vp]),
+    "cuda_sample_token": (None, [_vp, _i, _f, _f, C.c_ulonglong, _vp, _vp]),
+    "cuda_get_rope_kernel_ptr": (_vp, []),
+    "cuda_get_f16dual_kernel_ptr": (_vp, []),
+    "cuda_get_attn_f16kv_kernel_ptr": (_vp, []),
     "mb200_init": (_i, []),
     "mb200_last_status": (_i, []),
     "mb200_last_status_where": (C.c_char_p, []),
     "mb200_clear_status": (None, []),
     "mb200_device_error": (_i, []),
+    "mb200_clear_device_error": (_i, [_vp]),
     "mb200_set_pdl": (_i, [_i]),
     "mb200_matvec_q4k_dual_swiglu": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "mb200_matvec_q6k_scaled_add": (_i, [_vp, _vp, _vp, _i, _i, _f, _vp]),
@@ -47,10 +62,17 @@ SIGNATURES = {
     "mb200_moe_experts_fused": (_i, [_vp, _sz, _sz, _sz, _sz, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
     "mb200_set_fused": (None, [_i]),
     "mb200_moe_block_local": (_i, [_vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mb200_moe_block_host": (_i, [_vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mb200_gemm_q4k_f16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "mb200_gemm_q6k_f16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "mb200_moe_prefill_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "mb200_moe_prefill": (_i, [_vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
+    "mb200_decode_workspace_bytes": (_sz, [_vp]),
+    "mb200_decode_hidden": (_vp, [_vp, _vp]),
+    "mb200_decode_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "mb200_decode_begin": (_i, [_vp, _vp, _vp, _vp, _vp]),
+    "mb200_decode_layer": (_i, [_vp, _i, _vp, _vp, _vp]),
+    "mb200_decode_finish": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "mb200_fill_q4k": (_i, [_vp, _sz, _u64, _vp]),
     "mb200_fill_q6k": (_i, [_vp, _sz, _u64, _vp]),
     "mb200_fill_normal_f32": (_i, [_vp, _sz, _u64, _f, _vp]),

@@ -10,13 +10,35 @@ namespace mb200 {
 void q4k_init();
 void q6k_init();
 void gemm_init();
+void moe_fused_init();
+void router_static_init();
+void support_init();
 
 namespace {
 int g_status = MB200_OK;
 char g_where[96] = "";
 __device__ int g_device_error;  // one copy per device that loads the library
-int *g_err_ptr[64] = {nullptr};
+int *g_err_ptr[kMaxDevices] = {nullptr};
+int g_sms[kMaxDevices] = {0};
 }  // namespace
+
+int current_device()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+    return dev;
+}
+
+int device_sms()
+{
+    const int dev = current_device();
+    if (!g_sms[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) n = kSMs;
+        g_sms[dev] = n;
+    }
+    return g_sms[dev];
+}
 
 void set_status(int code, const char *where)
 {
@@ -31,9 +53,7 @@ void set_status(int code, const char *where)
 // it never happens during stream capture.
 int *device_error_word()
 {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) dev = 0;
+    const int dev = current_device();
     if (!g_err_ptr[dev]) {
         void *p = nullptr;
         if (cudaGetSymbolAddress(&p, g_device_error) != cudaSuccess) {
@@ -53,9 +73,14 @@ extern "C" {
 
 void cuda_kernels_init(void)
 {
+    // Everything here is per device: call once per device the engine drives, with that device current.
     q4k_init();
     q6k_init();
     gemm_init();
+    moe_fused_init();
+    support_init();
+    router_static_init();
+    (void)device_sms();
     (void)device_error_word();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
@@ -77,6 +102,13 @@ void mb200_clear_status(void)
 {
     g_status = MB200_OK;
     g_where[0] = 0;
+}
+
+int mb200_clear_device_error(cudaStream_t stream)
+{
+    int *p = device_error_word();
+    if (!p) return MB200_ERR_LAUNCH;
+    return cudaMemsetAsync(p, 0, sizeof(int), stream) == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
 }
 
 int mb200_device_error(void)

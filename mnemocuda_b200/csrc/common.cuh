@@ -12,13 +12,19 @@ namespace mb200 {
 
 constexpr int kQ4KBlock = 144;
 constexpr int kQ6KBlock = 210;
-constexpr int kSMs = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this
+constexpr int kSMs = 148;      // B200: 2 dies x 74 SMs; used where no device is known yet (fills, table sizes)
+constexpr int kMaxDevices = 64;  // per-device host-side state is kept in arrays of this length
 
 // ---- library-wide status --------------------------------------------------
 // The reference wrappers return void (errors are printed: kernels.cu:1062-1067).
 // Ours record the first failure here as well so a caller can poll it.
 void set_status(int code, const char *where);
 int *device_error_word();  // device int, non-zero after a kernel gave up on a wait
+// Ordinal of the current device, clamped to [0, kMaxDevices). Function attributes (the shared-memory
+// opt-in) and symbol addresses are per device, and one process may drive several devices (the
+// reference engine does: src/forward.c:606), so every "done once" flag is indexed by this.
+int current_device();
+int device_sms();          // SM count of the current device (grids of the persistent kernels)
 
 #define MB200_CHECK_LAUNCH(where)                                                        \
     do {                                                                                 \

@@ -451,10 +451,10 @@ int launch_gemm_bt(GemmParams &P, const void *x_f16, int rows_x, dim3 grid, cuda
         fprintf(stderr, "[mnemo_b200] %s: tensor map for X could not be encoded\n", where);
         return MB200_ERR_ARG;
     }
-    static bool attr_done = false;
-    if (!attr_done) {
+    static bool attr_done[kMaxDevices] = {false};  // the opt-in is a per-device attribute
+    if (!attr_done[current_device()]) {
         cudaFuncSetAttribute(gemm_tc_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BT>::kSmemBytes);
-        attr_done = true;
+        attr_done[current_device()] = true;
     }
     P.bpr = P.K / 256;
     P.err = device_error_word();

@@ -25,6 +25,21 @@ using stream::Params;
 void q4k_init() { stream::init_attrs<Q4>(); }
 int pdl_enabled() { return stream::pdl_mode(); }
 
+// Two Q4_K tensors of different heights that share x, one launch (the decode path's Q and K projections;
+// the reference's three-tensor form, cuda_matvec_q4k_qkv, needs V to be Q4_K too, which Q4_K_M files are not).
+void q4k_matvec2(const void *wa, float *ya, int rows_a, const void *wb, float *yb, int rows_b, const float *x,
+                 int n_cols, cudaStream_t stream, const char *where)
+{
+    Params P{};
+    P.seg[0] = {static_cast<const uint8_t *>(wa), ya, rows_a, 0};
+    P.seg[1] = {static_cast<const uint8_t *>(wb), yb, rows_b, 0};
+    P.nseg = 2;
+    P.x = x;
+    P.n_cols = n_cols;
+    P.mode = stream::kStore;
+    stream::launch<Q4>(P, stream, where);
+}
+
 void moe_gate_up_q4k(const void *experts, size_t stride, size_t gate_off, size_t up_off, const int *ids, int n_slots,
                      int expert_lo, int expert_cnt, const float *x, float *act, int EFF, int H, cudaStream_t stream,
                      const char *where)

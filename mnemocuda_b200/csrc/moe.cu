@@ -140,14 +140,14 @@ int launch_router(const float *router_w, const float *x, void *scratch, int *ids
 // One copy exists on every device that loads the library, for the life of the process.
 constexpr int kStaticRouterMaxExperts = 1024;
 static __device__ __align__(256) int g_router_scratch[8 + kStaticRouterMaxExperts];
-static int *g_router_scratch_ptr[64] = {nullptr};  // device address of the array, per device ordinal
+static int *g_router_scratch_ptr[kMaxDevices] = {nullptr};  // device address of the array, per device ordinal
 
 // The array's name is only a host-side handle; kernels need its device address, which the
 // runtime hands out per device. Looked up once per device, with that device current.
 static int *static_router_scratch()
 {
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
     if (!g_router_scratch_ptr[dev]) {
         int *ptr = nullptr;
         if (cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_router_scratch) != cudaSuccess) return nullptr;
@@ -155,6 +155,10 @@ static int *static_router_scratch()
     }
     return g_router_scratch_ptr[dev];
 }
+
+// cuda_kernels_init() resolves the array on the current device, so that an engine that initialises
+// each device at load never pays the lookup (and the module load behind it) on a hot call.
+void router_static_init() { (void)static_router_scratch(); }
 
 }  // namespace mb200
 
@@ -278,20 +282,41 @@ int mb200_moe_block_local(const float *router_w, const void *experts, size_t exp
         // one launch: routing, gate/up, down
         rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, nullptr, nullptr, k, expert_lo,
                        expert_cnt, x, act, residual, out, H, EFF, sync, stream, router_w, n_experts, logits, ids, wts);
-        if (rc != MB200_ERR_UNSUPPORTED) return rc;
+        // not covered, or the device refused the cooperative launch (fewer SMs available than the grid
+        // needs): nothing ran, the separate kernels below do the block
+        if (rc != MB200_ERR_UNSUPPORTED && rc != MB200_ERR_LAUNCH) return rc;
     }
     rc = mb200_router_topk(router_w, x, scratch, ids, wts, n_experts, H, k, stream);
     if (rc != MB200_OK) return rc;
     if (moe_fused_mode() && act) {
         rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, ids, wts, k, expert_lo, expert_cnt,
                        x, act, residual, out, H, EFF, sync, stream, nullptr, 0, nullptr, nullptr, nullptr);
-        if (rc != MB200_ERR_UNSUPPORTED) return rc;
+        if (rc != MB200_ERR_UNSUPPORTED && rc != MB200_ERR_LAUNCH) return rc;
     }
     rc = mb200_moe_gate_up_local(experts, expert_stride, 0, gate_sz, ids, k, expert_lo, expert_cnt, x, act, EFF, H,
                                  stream);
     if (rc != MB200_OK) return rc;
     return mb200_moe_down_local(experts, expert_stride, gate_sz + up_sz, down_type, ids, wts, k, expert_lo, expert_cnt,
                                 act, residual, out, H, EFF, stream);
+}
+
+int mb200_moe_block_host(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz,
+                         size_t up_sz, int down_type, int n_experts, int expert_lo, int expert_cnt, int k, int H,
+                         int EFF, const float *host_x_res, float *host_out, float *dev_io, int *ids, float *wts,
+                         float *act, void *scratch, cudaStream_t stream)
+{
+    if (!host_x_res || !host_out || !dev_io || H < 1) return MB200_ERR_ARG;
+    // one copy in (x and the residual are adjacent), the block, one copy out, one wait
+    if (cudaMemcpyAsync(dev_io, host_x_res, sizeof(float) * 2 * (size_t)H, cudaMemcpyHostToDevice, stream) != cudaSuccess)
+        return MB200_ERR_LAUNCH;
+    const int rc = mb200_moe_block_local(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts, expert_lo,
+                                         expert_cnt > 0 ? expert_cnt : 0x7fffffff, k, H, EFF, dev_io, dev_io + H,
+                                         dev_io + 2 * (size_t)H, ids, wts, act, scratch, stream);
+    if (rc != MB200_OK) return rc;
+    if (cudaMemcpyAsync(host_out, dev_io + 2 * (size_t)H, sizeof(float) * (size_t)H, cudaMemcpyDeviceToHost, stream) !=
+        cudaSuccess)
+        return MB200_ERR_LAUNCH;
+    return cudaStreamSynchronize(stream) == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
 }
 
 int mb200_moe_block(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz,

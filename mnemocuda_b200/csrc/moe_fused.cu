@@ -94,6 +94,7 @@ struct FusedParams {
     int c_stages, c_stage_bytes;   // the down phase re-cuts the ring into more, smaller stages
     int off_cpart;                 // partial-sum slots of the down stages
     int pdl;
+    int grid;                      // CTAs of the launch = SMs of the device (one CTA per SM, all co-resident)
 };
 
 struct FTile {
@@ -849,18 +850,28 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
 int g_fused_mode = 2;          // see mb200_set_fused
 int g_fused_pdl_ok = 1;        // cleared if the driver refuses cooperative + programmatic serialization together
 
+// Shared-memory opt-in of the kernel, once per device (a per-device attribute).
+template <class FD>
+bool fused_attr()
+{
+    static bool done[kMaxDevices] = {false};
+    const int dev = current_device();
+    if (done[dev]) return true;
+    if (cudaFuncSetAttribute(moe_fused_kernel<FD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+        cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    done[dev] = true;
+    return true;
+}
+
 template <class FD>
 int launch_fused(FusedParams &P, int smem_bytes, cudaStream_t stream)
 {
-    static bool attr_done = false;
-    if (!attr_done) {
-        if (cudaFuncSetAttribute(moe_fused_kernel<FD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
-            cudaSuccess)
-            return MB200_ERR_LAUNCH;
-        attr_done = true;
-    }
+    if (!fused_attr<FD>()) return MB200_ERR_LAUNCH;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(kSMs);
+    cfg.gridDim = dim3(P.grid);
     cfg.blockDim = dim3(kFusedThreads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
@@ -905,7 +916,7 @@ static bool fused_plan(FusedParams &P, int &smem_bytes)
     P.TB = 2 * P.wpgB;
     {   // the issuer warp lists the CTA's gate/up tiles with one lane per tile
         const int tpe = (EFF + P.TB - 1) / P.TB;
-        if ((P.n_slots * tpe + kSMs - 1) / kSMs + kFusedMaxBatches > kFusedMaxTiles) return false;
+        if ((P.n_slots * tpe + P.grid - 1) / P.grid + kFusedMaxBatches > kFusedMaxTiles) return false;
     }
     int v = 1;
     while (v * 2 <= 8 && P.bprC % (v * 2) == 0) v *= 2;
@@ -923,7 +934,7 @@ static bool fused_plan(FusedParams &P, int &smem_bytes)
 template <class FD>
 static bool fused_layout(FusedParams &P, int &smem_bytes)
 {
-    const int per_cta = (P.H + kSMs - 1) / kSMs;
+    const int per_cta = (P.H + P.grid - 1) / P.grid;
     const int c_rows = per_cta < P.TC ? per_cta : P.TC;
     const int tileB = 2 * P.TB * P.bprB * kQ4KBlock;
     const int tileC = c_rows * P.bprC * FD::kBlockBytes + kSrcAlign + 32;  // + alignment skew, word over-read
@@ -961,6 +972,11 @@ static bool fused_layout(FusedParams &P, int &smem_bytes)
     return false;
 }
 
+void moe_fused_init()
+{
+    fused_attr<Q6>();
+    fused_attr<Q4>();
+}
 void moe_fused_set_mode(int mode) { g_fused_mode = mode; }
 int moe_fused_mode() { return g_fused_mode; }
 
@@ -1002,6 +1018,7 @@ int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off
     P.expert_cnt = expert_cnt;
     P.H = H;
     P.EFF = EFF;
+    P.grid = device_sms();
     int smem_bytes = 0;
     if (!fused_plan(P, smem_bytes)) return MB200_ERR_UNSUPPORTED;
     const uintptr_t b = reinterpret_cast<uintptr_t>(experts);

@@ -694,23 +694,25 @@ inline void launch_one(Params &P, const Layout &L, int grid, cudaStream_t stream
     cudaLaunchKernelEx(&cfg, stream_kernel<F, RU>, P);
 }
 
+// The shared-memory opt-in is a per-device attribute of each kernel: done once per device, with that
+// device current (cuda_kernels_init() does it up front so that it never happens during a capture).
 template <class F>
 inline void init_attrs()
 {
+    static bool done[kMaxDevices] = {false};
+    const int dev = current_device();
+    if (done[dev]) return;
     cudaFuncSetAttribute(stream_kernel<F, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(stream_kernel<F, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(stream_kernel<F, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    done[dev] = true;
 }
 
 // Host-side geometry + launch. Segment pointers/rows, x, mode etc. are set by the caller.
 template <class F>
 inline void launch(Params &P, cudaStream_t stream, const char *where)
 {
-    static bool attrs_done = false;
-    if (!attrs_done) {
-        init_attrs<F>();
-        attrs_done = true;
-    }
+    init_attrs<F>();
     if (P.n_cols <= 0) return;
     if (P.n_cols > F::kMaxCols) {
         fprintf(stderr, "[mnemo_b200] %s: n_cols=%d exceeds the supported %d\n", where, P.n_cols, F::kMaxCols);
@@ -801,7 +803,8 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
     }
     if (vrows <= 0) return;
     P.vrows = vrows;
-    const int grid = vrows < kSMs ? vrows : kSMs;
+    const int sms = device_sms();
+    const int grid = vrows < sms ? vrows : sms;
     const int per_cta = (vrows + grid - 1) / grid;  // rows of the longest range
     const int mult = (P.mode == kSwiGLU || P.mode == kMoeGateUp) ? 2 : 1;  // stage rows per virtual row
     const int n_x = (P.mode == kMoeDown) ? P.n_slots : 1;

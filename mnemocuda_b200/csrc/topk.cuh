@@ -71,9 +71,6 @@ __device__ __noinline__ void topk_softmax_warp_seq_kw(const float *scores, int *
 {
     const unsigned full = 0xffffffffu;
     const int lane = threadIdx.x & 31;
-#ifdef MB200_TRACE
-    long long t0 = clock64();
-#endif
     SortedSlots<KW> loc;
     loc.reset(k);
     int cnt = 0;  // live entries of this lane (slots 0..cnt-1: stage 1 fills them in order before it ever replaces)
@@ -100,9 +97,6 @@ __device__ __noinline__ void topk_softmax_warp_seq_kw(const float *scores, int *
         }
     const int cmax = __reduce_max_sync(full, cnt);
     __syncwarp();
-#ifdef MB200_TRACE
-    long long t1 = clock64();
-#endif
 
     SortedSlots<KW> top;
     top.reset(k);
@@ -119,10 +113,6 @@ __device__ __noinline__ void topk_softmax_warp_seq_kw(const float *scores, int *
                 top.replace_min(cv[i], s_ids[l * 16 + i]);
         }
     }
-#ifdef MB200_TRACE
-    long long t2 = clock64();
-    if (lane == 0) printf("topk: stage1 %lld cycles, stage2 %lld cycles\n", t1 - t0, t2 - t1);
-#endif
     // back to slot order through the (now free) table, then softmax summed in slot order like the reference
     __syncwarp();
     if (lane == 0) {

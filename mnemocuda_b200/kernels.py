@@ -113,6 +113,71 @@ def cuda_scaled_add(out, x, scale, n, stream=None):
     _raise_if_failed("cuda_scaled_add")
 
 
+# ---- support operators of a decode step (reference names) -------------------
+
+def cuda_rms_norm(x, weight, out, n, eps, stream=None):
+    _lib.lib().cuda_rms_norm(_f32(x), _f32(weight), _f32(out), n, float(eps), _stream(stream))
+    _raise_if_failed("cuda_rms_norm")
+
+
+def cuda_rms_norm_residual(x, weight, normed, residual, n, eps, stream=None):
+    _lib.lib().cuda_rms_norm_residual(_f32(x), _f32(weight), _f32(normed), _f32(residual), n, float(eps),
+                                      _stream(stream))
+    _raise_if_failed("cuda_rms_norm_residual")
+
+
+def cuda_rms_norm_batched(x, weight, out, head_dim, n_heads, eps, stream=None):
+    _lib.lib().cuda_rms_norm_batched(_f32(x), _f32(weight), _f32(out), head_dim, n_heads, float(eps), _stream(stream))
+    _raise_if_failed("cuda_rms_norm_batched")
+
+
+def cuda_rms_norm_qk(q, k, q_weight, k_weight, head_dim, n_q, n_k, eps, stream=None):
+    _lib.lib().cuda_rms_norm_qk(_f32(q), _f32(k), _f32(q_weight), _f32(k_weight), head_dim, n_q, n_k, float(eps),
+                                _stream(stream))
+    _raise_if_failed("cuda_rms_norm_qk")
+
+
+def cuda_rope(q, k, head_dim, pos, theta, n_heads_q, n_heads_k, stream=None):
+    _lib.lib().cuda_rope(_f32(q), _f32(k), head_dim, pos, float(theta), n_heads_q, n_heads_k, _stream(stream))
+    _raise_if_failed("cuda_rope")
+
+
+def cuda_f32_to_f16(x, out, n, stream=None):
+    _lib.lib().cuda_f32_to_f16(_f32(x), _ptr(out), n, _stream(stream))
+    _raise_if_failed("cuda_f32_to_f16")
+
+
+def cuda_f32_to_f16_dual(a, b, oa, ob, n, stream=None):
+    _lib.lib().cuda_f32_to_f16_dual(_f32(a), _f32(b), _ptr(oa), _ptr(ob), n, _stream(stream))
+    _raise_if_failed("cuda_f32_to_f16_dual")
+
+
+def cuda_attention_f16kv(q, kv_k, kv_v, out, n_heads_q, head_dim, n_kv_heads, seq_len, gqa_ratio, scale, stream=None):
+    if kv_k.dtype != torch.float16 or kv_v.dtype != torch.float16:
+        raise TypeError("the KV cache must be float16")
+    _lib.lib().cuda_attention_f16kv(_f32(q), _ptr(kv_k), _ptr(kv_v), _f32(out), n_heads_q, head_dim, n_kv_heads,
+                                    seq_len, gqa_ratio, float(scale), _stream(stream))
+    _raise_if_failed("cuda_attention_f16kv")
+
+
+def cuda_residual_add(a, b, out, n, stream=None):
+    _lib.lib().cuda_residual_add(_f32(a), _f32(b), _f32(out), n, _stream(stream))
+    _raise_if_failed("cuda_residual_add")
+
+
+def cuda_embedding_lookup_q4k(table, out, token_id, hidden, row_bytes, stream=None):
+    _lib.lib().cuda_embedding_lookup_q4k(_ptr(table), _f32(out), token_id, hidden, row_bytes, _stream(stream))
+    _raise_if_failed("cuda_embedding_lookup_q4k")
+
+
+def cuda_sample_token(logits, vocab, temperature, top_p, rng_state, result, stream=None):
+    if result.dtype != torch.int32:
+        raise TypeError("result must be int32")
+    _lib.lib().cuda_sample_token(_f32(logits), vocab, float(temperature), float(top_p), int(rng_state), _ptr(result),
+                                 _stream(stream))
+    _raise_if_failed("cuda_sample_token")
+
+
 # ---- additions --------------------------------------------------------------
 
 def mb200_init() -> None:
@@ -121,6 +186,10 @@ def mb200_init() -> None:
 
 def mb200_device_error() -> int:
     return _lib.lib().mb200_device_error()
+
+
+def mb200_clear_device_error(stream=None) -> None:
+    _check(_lib.lib().mb200_clear_device_error(_stream(stream)), "mb200_clear_device_error")
 
 
 def mb200_set_pdl(enabled: bool) -> bool:

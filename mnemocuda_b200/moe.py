@@ -90,27 +90,33 @@ class ResidentMoE:
 
 
 class HostMoEBlock:
-    """The call a user of host buffers makes: hidden state in, hidden state out.
+    """The call a user of host buffers makes: hidden state in, hidden state out (mb200_moe_block_host).
 
-    Copies x and the residual from pinned host memory, runs the block, copies the result back
-    and waits for it (the reference's engine does the same per token for the logits)."""
+    One copy of [x | residual] from pinned host memory, the block, one copy of the result back, and a
+    wait for it (the reference's engine does the same per token for the logits). With experts sharded over
+    several GPUs the partial results are all-reduced on the device before the copy back."""
 
     def __init__(self, moe: ResidentMoE, sharded=None):
         self.moe = moe
         self.sharded = sharded  # a sharded.ShardedMoE when the experts are split over several GPUs
         H = moe.shape.H
-        self.x = torch.empty(H, dtype=torch.float32, device=moe.device)
-        self.res = torch.empty(H, dtype=torch.float32, device=moe.device)
-        self.out = torch.empty(H, dtype=torch.float32, device=moe.device)
+        self.io = torch.empty(3, H, dtype=torch.float32, device=moe.device)  # x, residual, result
         self.h2d_bytes = 2 * H * 4
         self.d2h_bytes = H * 4
 
-    def __call__(self, layer: int, x_host: torch.Tensor, res_host: torch.Tensor, out_host: torch.Tensor) -> None:
-        self.x.copy_(x_host, non_blocking=True)
-        self.res.copy_(res_host, non_blocking=True)
+    def __call__(self, layer: int, x_res_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        """x_res_host: pinned [2][H] (x, residual); out_host: pinned [H]."""
+        m, s = self.moe, self.moe.shape
         if self.sharded is not None:
-            self.sharded.forward(layer, self.x, self.res, self.out)
-        else:
-            self.moe.forward(layer, self.x, self.res, self.out)
-        out_host.copy_(self.out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+            self.io[:2].copy_(x_res_host, non_blocking=True)
+            self.sharded.forward(layer, self.io[0], self.io[1], self.io[2])
+            out_host.copy_(self.io[2], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return
+        if not (x_res_host.is_pinned() and out_host.is_pinned()):
+            raise ValueError("pinned host tensors expected")
+        K._check(K._lib.lib().mb200_moe_block_host(
+            m.router[layer].data_ptr(), m.experts[layer].data_ptr(), s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE,
+            m.expert_lo, m.n_local, s.K, s.H, s.EFF, x_res_host.data_ptr(), out_host.data_ptr(), self.io.data_ptr(),
+            m.ids[layer].data_ptr(), m.wts[layer].data_ptr(), m.act.data_ptr(), m.scratch.data_ptr(),
+            torch.cuda.current_stream().cuda_stream), "mb200_moe_block_host")

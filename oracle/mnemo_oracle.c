@@ -528,6 +528,123 @@ void mo_gemm_q6k_f16(const uint8_t *w, const uint16_t *x_f16, float *out, int M,
     gemm_f16(w, 1, x_f16, out, M, N, K);
 }
 
+/* ======================================================================== */
+/* Support operators of a decode step (not the hot path; they surround it). */
+/* Each is computed in double and rounded to fp32 once.                     */
+/* ======================================================================== */
+
+/* kernels.cu:692-722 / 725-749; tools/validate_rope_norm.py:47-59 (kernel_rms_norm):
+ * scale = 1 / sqrt(sum(x^2) / n + eps); out = x * scale * w. */
+void mo_rms_norm(const float *x, const float *w, float *out, int n, float eps)
+{
+    double ss = 0.0;
+    for (int i = 0; i < n; i++) ss += (double)x[i] * (double)x[i];
+    const double scale = 1.0 / sqrt(ss / (double)n + (double)eps);
+    for (int i = 0; i < n; i++) out[i] = (float)((double)x[i] * scale * (double)w[i]);
+}
+
+/* kernels.cu:754-780, 1196-1219: the same norm per head, one weight vector for all heads. */
+void mo_rms_norm_heads(const float *x, const float *w, float *out, int head_dim, int n_heads, float eps)
+{
+    for (int h = 0; h < n_heads; h++) mo_rms_norm(x + (size_t)h * head_dim, w, out + (size_t)h * head_dim, head_dim, eps);
+}
+
+/* kernels.cu:818-852 as restated by tools/validate_rope_norm.py:168-197 (kernel_rope): half-split
+ * pairs (j, j + head_dim/2), freq = 1 / theta^(2j/head_dim), angle = pos * freq, all in double. */
+void mo_rope(float *vec, int n_heads, int head_dim, int pos, float theta)
+{
+    const int half = head_dim / 2;
+    for (int h = 0; h < n_heads; h++)
+        for (int j = 0; j < half; j++) {
+            const double freq = 1.0 / pow((double)theta, (2.0 * j) / (double)head_dim);
+            const double a = (double)pos * freq, c = cos(a), s = sin(a);
+            float *v = vec + (size_t)h * head_dim;
+            const double v0 = v[j], v1 = v[j + half];
+            v[j] = (float)(v0 * c - v1 * s);
+            v[j + half] = (float)(v0 * s + v1 * c);
+        }
+}
+
+/* kernels.cu:1309-1326: fp32 -> fp16 round-to-nearest-even. */
+void mo_f32_to_f16_array(const float *in, uint16_t *out, int n)
+{
+    for (int i = 0; i < n; i++) out[i] = mo_f32_to_f16(in[i]);
+}
+
+/* kernels.cu:1550-1660 (attention over an fp16 KV cache, [position][kv head][head_dim]):
+ * out[h] = sum_p softmax_p(scale * q[h].K[p][h / gqa]) * V[p][h / gqa], in double. */
+void mo_attention_f16kv(const float *q, const uint16_t *kv_k, const uint16_t *kv_v, float *out, int n_heads_q,
+                        int head_dim, int n_kv_heads, int seq_len, int gqa_ratio, float scale)
+{
+    const size_t stride = (size_t)n_kv_heads * head_dim;
+#pragma omp parallel for schedule(dynamic)
+    for (int h = 0; h < n_heads_q; h++) {
+        const int kvh = h / gqa_ratio;
+        double *sc = (double *)malloc(sizeof(double) * (size_t)seq_len);
+        double *acc = (double *)calloc((size_t)head_dim, sizeof(double));
+        double mx = -1e300;
+        for (int p = 0; p < seq_len; p++) {
+            const uint16_t *kp = kv_k + (size_t)p * stride + (size_t)kvh * head_dim;
+            double s = 0.0;
+            for (int d = 0; d < head_dim; d++) s += (double)q[(size_t)h * head_dim + d] * (double)mo_f16_to_f32(kp[d]);
+            sc[p] = s * (double)scale;
+            if (sc[p] > mx) mx = sc[p];
+        }
+        double sum = 0.0;
+        for (int p = 0; p < seq_len; p++) {
+            const double e = exp(sc[p] - mx);
+            sum += e;
+            const uint16_t *vp = kv_v + (size_t)p * stride + (size_t)kvh * head_dim;
+            for (int d = 0; d < head_dim; d++) acc[d] += e * (double)mo_f16_to_f32(vp[d]);
+        }
+        for (int d = 0; d < head_dim; d++) out[(size_t)h * head_dim + d] = (float)(sum > 0.0 ? acc[d] / sum : 0.0);
+        free(sc);
+        free(acc);
+    }
+}
+
+/* kernels.cu:784-793 */
+void mo_residual_add(const float *a, const float *b, float *out, int n)
+{
+    for (int i = 0; i < n; i++) out[i] = a[i] + b[i];
+}
+
+/* Row `token` of a Q4_K table, dequantised (forward.c:1189-1229, the reference's CPU embedding;
+ * same arithmetic as tools/validate_dequant.py:68-115). */
+void mo_embedding_q4k(const uint8_t *table, int token, int hidden, float *out)
+{
+    const int bpr = bpr_of(hidden);
+    float tmp[256];
+    for (int b = 0; b < bpr; b++) {
+        dequant_q4k_block(table + ((size_t)token * bpr + b) * MO_Q4K_BLOCK_BYTES, tmp);
+        for (int j = 0; j < 256 && b * 256 + j < hidden; j++) out[b * 256 + j] = tmp[j];
+    }
+}
+
+/* kernels.cu:2048-2071 (greedy branch of sample_token_kernel): thread t of 256 scans i = t, t + 256, ...
+ * keeping the first strict maximum; the tree keeps the lower thread on ties. */
+int mo_argmax(const float *logits, int n)
+{
+    float bv[256];
+    int bi[256];
+    for (int t = 0; t < 256; t++) {
+        bv[t] = -1e30f;
+        bi[t] = 0;
+        for (int i = t; i < n; i += 256)
+            if (logits[i] > bv[t]) {
+                bv[t] = logits[i];
+                bi[t] = i;
+            }
+    }
+    for (int s = 128; s > 0; s >>= 1)
+        for (int t = 0; t < s; t++)
+            if (bv[t + s] > bv[t]) {
+                bv[t] = bv[t + s];
+                bi[t] = bi[t + s];
+            }
+    return bi[0];
+}
+
 int mo_num_threads(void)
 {
 #ifdef _OPENMP

@@ -93,6 +93,19 @@ void mo_gemm_q4k_f16(const uint8_t *w, const uint16_t *x_f16 /*[M][K]*/, float *
                      int M, int N, int K);
 void mo_gemm_q6k_f16(const uint8_t *w, const uint16_t *x_f16, float *out, int M, int N, int K);
 
+/* ---- support operators of a decode step (computed in double, rounded once) ---- */
+void mo_rms_norm(const float *x, const float *w, float *out, int n, float eps);       /* kernels.cu:692-749; validate_rope_norm.py:47-59 */
+void mo_rms_norm_heads(const float *x, const float *w, float *out, int head_dim, int n_heads,
+                       float eps);                                                       /* kernels.cu:754-780, 1196-1219 */
+void mo_rope(float *vec, int n_heads, int head_dim, int pos, float theta);              /* kernels.cu:818-852; validate_rope_norm.py:168-197 */
+void mo_f32_to_f16_array(const float *in, uint16_t *out, int n);                        /* kernels.cu:1309-1326 */
+void mo_attention_f16kv(const float *q, const uint16_t *kv_k, const uint16_t *kv_v, float *out, int n_heads_q,
+                        int head_dim, int n_kv_heads, int seq_len, int gqa_ratio,
+                        float scale);                                                    /* kernels.cu:1550-1660 */
+void mo_residual_add(const float *a, const float *b, float *out, int n);                /* kernels.cu:784-793 */
+void mo_embedding_q4k(const uint8_t *table, int token, int hidden, float *out);         /* forward.c:1189-1229 */
+int mo_argmax(const float *logits, int n);                                              /* kernels.cu:2048-2071 */
+
 int mo_num_threads(void);
 void mo_set_num_threads(int n);
 

@@ -15,15 +15,26 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 
 
+def reference_dir() -> str | None:
+    """Root of the reference checkout: $MNEMO_REFERENCE_DIR, else a `reference` directory beside this
+    repository. None when neither exists (the GPU box: only prebuilt files travel there)."""
+    for cand in (os.environ.get("MNEMO_REFERENCE_DIR"), os.path.join(_HERE, "..", "..", "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "src")):
+            return os.path.abspath(cand)
+    return None
+
+
 def build(force: bool = False) -> str:
     """Compile liboracle.so (and the reference's own kernels, if its tree is here)."""
     src = os.path.join(_HERE, "mnemo_oracle.c")
-    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+    hdr = os.path.join(_HERE, "mnemo_oracle.h")
+    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < max(os.path.getmtime(src),
+                                                                                  os.path.getmtime(hdr)):
         subprocess.check_call(["make", "-C", _HERE, "all"], stdout=subprocess.DEVNULL)
-    if os.path.isdir("/root/reference/src") and not os.path.exists(
-        os.path.join(_HERE, "_ref", "libmnemo_ref_kernels.so")
-    ):
-        subprocess.call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+    ref = reference_dir()
+    if ref and not os.path.exists(os.path.join(_HERE, "_ref", "libmnemo_ref_kernels.so")):
+        subprocess.call(["make", "-C", _HERE, "ref", "REFERENCE=" + ref], stdout=subprocess.DEVNULL,
+                        stderr=subprocess.DEVNULL)
     return _LIB_PATH
 
 
@@ -230,3 +241,84 @@ def gemm_q6k_f16(w, x_f16, M: int, N: int, K: int) -> np.ndarray:
     out = np.zeros((M, N), np.float32)
     lib().mo_gemm_q6k_f16(_p(w), _p(x), _p(out), C.c_int(M), C.c_int(N), C.c_int(K))
     return out
+
+
+# ---- support operators of a decode step --------------------------------------
+
+def rms_norm(x, w, eps: float) -> np.ndarray:
+    x, w = _f32(x), _f32(w)
+    out = np.zeros_like(x)
+    lib().mo_rms_norm(_p(x), _p(w), _p(out), C.c_int(x.size), C.c_float(eps))
+    return out
+
+
+def rms_norm_heads(x, w, head_dim: int, n_heads: int, eps: float) -> np.ndarray:
+    x, w = _f32(x), _f32(w)
+    out = np.zeros_like(x)
+    lib().mo_rms_norm_heads(_p(x), _p(w), _p(out), C.c_int(head_dim), C.c_int(n_heads), C.c_float(eps))
+    return out
+
+
+def rope(vec, n_heads: int, head_dim: int, pos: int, theta: float) -> np.ndarray:
+    out = _f32(vec).copy()
+    lib().mo_rope(_p(out), C.c_int(n_heads), C.c_int(head_dim), C.c_int(pos), C.c_float(theta))
+    return out
+
+
+def f32_to_f16_bits(x) -> np.ndarray:
+    x = _f32(x)
+    out = np.zeros(x.size, np.uint16)
+    lib().mo_f32_to_f16_array(_p(x), _p(out), C.c_int(x.size))
+    return out
+
+
+def attention_f16kv(q, kv_k_bits, kv_v_bits, n_heads_q: int, head_dim: int, n_kv_heads: int, seq_len: int,
+                    gqa_ratio: int, scale: float) -> np.ndarray:
+    """kv_*_bits: uint16 views of the fp16 cache, [position][kv head][head_dim]."""
+    q = _f32(q)
+    k = np.ascontiguousarray(np.asarray(kv_k_bits)).view(np.uint16)
+    v = np.ascontiguousarray(np.asarray(kv_v_bits)).view(np.uint16)
+    out = np.zeros(n_heads_q * head_dim, np.float32)
+    lib().mo_attention_f16kv(_p(q), _p(k), _p(v), _p(out), C.c_int(n_heads_q), C.c_int(head_dim), C.c_int(n_kv_heads),
+                             C.c_int(seq_len), C.c_int(gqa_ratio), C.c_float(scale))
+    return out
+
+
+def embedding_q4k(table, token: int, hidden: int) -> np.ndarray:
+    table = _u8(table)
+    out = np.zeros(hidden, np.float32)
+    lib().mo_embedding_q4k(_p(table), C.c_int(token), C.c_int(hidden), _p(out))
+    return out
+
+
+def argmax(logits) -> int:
+    logits = _f32(logits)
+    lib().mo_argmax.restype = C.c_int
+    return int(lib().mo_argmax(_p(logits), C.c_int(logits.size)))
+
+
+def decode_layer(hidden, L: dict, cfg: dict, pos: int, kv_k_bits: np.ndarray, kv_v_bits: np.ndarray):
+    """One transformer layer in the reference's op order (src/forward.c:670-823, 1114) on host arrays.
+    L: the layer's tensors (attn_norm, wq, wk, wv, wo, q_norm, k_norm, ffn_norm, router, experts; types in
+    cfg). The KV cache (uint16 fp16 bits, [ctx][n_kv][hd]) is updated in place at `pos`.
+    Returns (new hidden, routed ids)."""
+    H, NH, NKV, HD = cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"]
+    eps, theta = cfg["rms_eps"], cfg["rope_theta"]
+    mv = {12: matvec_q4k, 14: matvec_q6k}
+    normed = rms_norm(hidden, L["attn_norm"], eps)
+    q = mv[cfg["wq_type"]](L["wq"], normed, NH * HD, H)
+    k = mv[cfg["wk_type"]](L["wk"], normed, NKV * HD, H)
+    v = mv[cfg["wv_type"]](L["wv"], normed, NKV * HD, H)
+    if L.get("q_norm") is not None:
+        q = rms_norm_heads(q, L["q_norm"], HD, NH, eps)
+        k = rms_norm_heads(k, L["k_norm"], HD, NKV, eps)
+    q = rope(q, NH, HD, pos, theta)
+    k = rope(k, NKV, HD, pos, theta)
+    kv_k_bits.reshape(-1, NKV * HD)[pos] = f32_to_f16_bits(k)
+    kv_v_bits.reshape(-1, NKV * HD)[pos] = f32_to_f16_bits(v)
+    attn = attention_f16kv(q, kv_k_bits, kv_v_bits, NH, HD, NKV, pos + 1, NH // NKV, 1.0 / np.sqrt(HD))
+    hidden2 = mv[cfg["wo_type"]](L["wo"], attn, H, NH * HD) + _f32(hidden)
+    normed2 = rms_norm(hidden2, L["ffn_norm"], eps)
+    out, ids, _ = moe_block(L["router"], L["experts"], cfg["expert_stride"], cfg["gate_sz"], cfg["up_sz"],
+                            cfg["down_type"], cfg["n_experts"], cfg["top_k"], H, cfg["moe_inter"], normed2, hidden2)
+    return out, ids

@@ -3,7 +3,7 @@
 
 Run in a container that has the reference checkout and the `gguf` package:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference      (or MNEMO_REFERENCE_DIR=...)
 
 It imports tools/validate_dequant.py from the reference (its functions, not
 its main(), which needs a private model file) and gguf.quants, feeds them
@@ -17,6 +17,9 @@ Vectors:
                             nibble, subnormal and negative d, max scales)
   ragged                  : n_cols not a multiple of 256
   scale_min               : get_scale_min_k4 on every j for random 12-byte rows
+support_golden.npz (from tools/validate_rope_norm.py's kernel replicas):
+  rms_*                   : kernel_rms_norm on seeded vectors (hidden 2048 / 4096, head 128)
+  rope_*                  : kernel_rope at positions 0, 1, 17, 4095, 8191 (16 + 2 heads of 128)
 """
 from __future__ import annotations
 
@@ -31,12 +34,31 @@ sys.path.insert(0, os.path.abspath(os.path.join(HERE, "..", "..")))
 from mnemocuda_b200 import synth  # noqa: E402
 
 
-def load_reference(ref_root: str):
-    path = os.path.join(ref_root, "tools", "validate_dequant.py")
-    spec = importlib.util.spec_from_file_location("validate_dequant", path)
+def load_reference(ref_root: str, name: str = "validate_dequant"):
+    path = os.path.join(ref_root, "tools", name + ".py")
+    spec = importlib.util.spec_from_file_location(name, path)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     return mod
+
+
+def support_vectors(ref_root: str) -> dict:
+    """RMSNorm and RoPE: outputs of the reference's own numpy replicas of its kernels."""
+    vr = load_reference(ref_root, "validate_rope_norm")
+    out = {}
+    for tag, n, seed in (("h2048", 2048, 31), ("h4096", 4096, 32), ("head128", 128, 33)):
+        x = synth.normal_f32(seed, n, 3.0)
+        w = (1.0 + 0.1 * synth.normal_f32(seed + 100, n)).astype(np.float32)
+        out[f"rms_{tag}_x"], out[f"rms_{tag}_w"] = x, w
+        out[f"rms_{tag}_ref"] = np.asarray(vr.kernel_rms_norm(x.astype(np.float64), w.astype(np.float64), 1e-6), np.float64)
+    nh, hd, theta = 18, 128, 1_000_000.0
+    vec = synth.normal_f32(41, nh * hd)
+    out["rope_in"] = vec
+    out["rope_pos"] = np.array([0, 1, 17, 4095, 8191], np.int32)
+    out["rope_ref"] = np.stack([np.asarray(vr.kernel_rope(vec.astype(np.float64), nh, hd, int(p), theta), np.float64)
+                                for p in out["rope_pos"]])
+    out["rope_meta"] = np.array([nh, hd, theta], np.float64)
+    return out
 
 
 def known_q4k() -> np.ndarray:
@@ -89,7 +111,9 @@ def known_q6k() -> np.ndarray:
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MNEMO_REFERENCE_DIR", "")
+    if not ref_root or not os.path.isdir(ref_root):
+        sys.exit("usage: make_golden.py /path/to/reference (or set MNEMO_REFERENCE_DIR)")
     vd = load_reference(ref_root)
     from gguf import dequantize
     from gguf.quants import GGMLQuantizationType as T
@@ -145,6 +169,10 @@ def main() -> None:
     # stored as a checksum only; the test regenerates it with numpy
     out["f16_probe"] = np.array(probe, np.uint16)
     out["f16_probe_ref"] = np.array([vd.f16_to_f32(h) for h in probe], np.float32)
+
+    sup = support_vectors(ref_root)
+    np.savez_compressed(os.path.join(HERE, "support_golden.npz"), **sup)
+    print("wrote", os.path.join(HERE, "support_golden.npz"), {k: v.shape for k, v in sup.items()})
 
     np.savez_compressed(os.path.join(HERE, "dequant_golden.npz"), **out)
     print("wrote", os.path.join(HERE, "dequant_golden.npz"),

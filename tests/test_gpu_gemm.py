@@ -52,6 +52,21 @@ def test_gemm_q6k(K, M, N, Kd):
     _check_rows(host(out), want)
 
 
+def test_gemm_at_the_benchmark_shapes(K):
+    """The timed prefill shapes: Q4_K 512 x 8192 x 4096 (dense part of the prefill configuration) and Q6_K
+    512 x 4096 x 1536 (an expert's down projection), every token row against the oracle."""
+    for kind, M, N, Kd in (("q4k", 512, 8192, 4096), ("q6k", 512, 4096, 1536)):
+        if kind == "q4k":
+            w, fn, call = synth.q4k_matrix(730, N, Kd), oracle.gemm_q4k_f16, K.mb200_gemm_q4k_f16
+        else:
+            w, fn, call = synth.q6k_matrix(731, N, Kd), oracle.gemm_q6k_f16, K.mb200_gemm_q6k_f16
+        x = synth.normal_f16(732, M * Kd).reshape(M, Kd)
+        want = fn(w, x, M, N, Kd)
+        out = torch.full((M, N), float("nan"), device="cuda")
+        call(dev(w), dev(x), out, M, N, Kd)
+        _check_rows(host(out), want)
+
+
 def test_gemm_matches_matvec_per_token(K):
     """Token t of the GEMM equals the decode matvec on x_t (both within tolerance of the oracle)."""
     M, N, Kd = 8, 256, 1024
@@ -139,3 +154,28 @@ def test_moe_prefill_grouped(K, M, NE, k, H, EFF, down_type):
     composed = host(acc).astype(np.float64)
     d2 = np.linalg.norm((got - res) - composed, axis=1) / np.linalg.norm(composed, axis=1)
     assert float(d2.max()) <= 2e-4, float(d2.max())
+
+
+def test_device_error_word_is_raised_and_can_be_cleared(K):
+    """An expert that receives more tokens than the launch was sized for raises the device error word
+    (nothing waits, nothing hangs: the surplus rows are simply not computed); mb200_clear_device_error
+    zeroes it so that later checks see new failures only."""
+    M, NE, k, H, EFF = 40, 4, 2, 512, 256
+    g, u, d = synth.expert_sizes(H, EFF, 14)
+    stride = g + u + d
+    experts = dev(np.concatenate([synth.expert_blob(850 + e, H, EFF, 14) for e in range(NE)]))
+    x = dev(synth.normal_f16(851, M * H).reshape(M, H))
+    ids = torch.zeros(M, k, dtype=torch.int32, device="cuda")  # every token routed to experts 0 and 1
+    ids[:, 1] = 1
+    wts = torch.full((M, k), 0.5, device="cuda")
+    n = K.mb200_moe_prefill_workspace_bytes(M, k, H, EFF, NE)
+    ws = torch.zeros(n + 256, dtype=torch.uint8, device="cuda")
+    ws = ws[(256 - ws.data_ptr() % 256) % 256:]
+    y = torch.zeros(M, H, device="cuda")
+    assert K.mb200_device_error() == 0
+    K.mb200_moe_prefill(experts, stride, g, u, 14, NE, k, H, EFF, x, ids, wts, None, y, M, 8, ws)  # cap 8 < 40
+    assert K.mb200_device_error() == 4  # MB200_ERR_UNSUPPORTED
+    K.mb200_clear_device_error()
+    assert K.mb200_device_error() == 0
+    K.mb200_moe_prefill(experts, stride, g, u, 14, NE, k, H, EFF, x, ids, wts, None, y, M, 0, ws)  # sized for M
+    assert K.mb200_device_error() == 0

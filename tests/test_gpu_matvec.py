@@ -206,3 +206,85 @@ def test_bad_alignment_is_reported_not_run(K):
         K.cuda_matvec_q4k(buf[4:], torch.zeros(cols, device="cuda"), y, rows, cols)
     with pytest.raises(RuntimeError):
         K.cuda_matvec_q4k(buf, torch.zeros(20000, device="cuda"), y, rows, 20000)
+
+
+def _one_hot_rows(K, call, w_dev, rows, cols, positions):
+    """y for x = e_c, for each c in positions: column c of the dequantised matrix as the kernel sees it."""
+    y = torch.empty(rows, device="cuda")
+    x = torch.zeros(cols, device="cuda")
+    out = np.zeros((len(positions), rows), np.float32)
+    for i, c in enumerate(positions):
+        x.zero_()
+        x[c] = 1.0
+        call(w_dev, x, y, rows, cols)
+        out[i] = host(y)
+    return out
+
+
+def _q4k_term_scale(w_blocks):
+    """|d*sc*q| + |dmin*m| per weight, [rows][256]: the magnitude the kernel's fp32 arithmetic works at."""
+    out = np.zeros((w_blocks.shape[0], 256), np.float64)
+    for r, blk in enumerate(w_blocks):
+        d, dm, sc, m, q = oracle.unpack_q4k_block(blk)
+        df, dmf = abs(oracle.f16_to_f32(d)), abs(oracle.f16_to_f32(dm))
+        out[r] = df * np.repeat(sc.astype(np.float64), 32) * q + dmf * np.repeat(m.astype(np.float64), 32)
+    return out
+
+
+def _q6k_term_scale(w_blocks):
+    """|d*sc|*(q + 32 + 32) per weight: the kernel forms d*sc*(q_raw*x - 32*x)."""
+    out = np.zeros((w_blocks.shape[0], 256), np.float64)
+    for r, blk in enumerate(w_blocks):
+        d, sc, q = oracle.unpack_q6k_block(blk)
+        out[r] = abs(oracle.f16_to_f32(d)) * np.abs(np.repeat(sc.astype(np.float64), 16)) * (q.astype(np.float64) + 64)
+    return out
+
+
+ONE_HOT_TOL = 2.0 ** -20  # a few fp32 roundings at the magnitude of the terms; a wrong integer field is off by >= 1 step
+
+
+def test_one_hot_sweep_q4k_known_blocks(K, golden):
+    """Bit-exact integer unpack on the GPU side: with x a one-hot vector (exactly representable in the
+    kernel's two-level int8 split up to one rounding of 1/127) output row r is the dequantised weight
+    W[r][c] itself. Every one of the 256 positions of the hand-built blocks and of seeded blocks must
+    reproduce the reference validator's value to a few fp32 roundings of its terms -- a wrong scale, min
+    or nibble would be off by whole quantisation steps."""
+    w = np.concatenate([golden["q4k_known_w"][:6], synth.q4k_blocks(91, 26)])  # 32 rows of one block each
+    ref = oracle.dequant_q4k(w.reshape(-1), w.shape[0], 256)
+    assert np.array_equal(ref[:6], golden["q4k_known_ref"][:6], equal_nan=True)
+    got = _one_hot_rows(K, K.cuda_matvec_q4k, dev(w.reshape(-1)), w.shape[0], 256, range(256)).T  # [row][col]
+    scale = _q4k_term_scale(w)
+    finite = np.isfinite(ref)
+    assert np.all(np.isfinite(got[finite]))
+    err = np.abs(got.astype(np.float64) - ref)[finite]
+    assert np.all(err <= ONE_HOT_TOL * scale[finite] + 1e-45), float((err / (scale[finite] + 1e-300)).max())
+    # the distinct values of a sub-block are d*sc apart: an error of one integer step would be >= 2^-4 of the scale
+    assert ONE_HOT_TOL < 2.0 ** -10
+
+
+def test_one_hot_sweep_q6k_known_blocks(K, golden):
+    w = np.concatenate([golden["q6k_known_w"], synth.q6k_blocks(92, 26)])
+    ref = oracle.dequant_q6k(w.reshape(-1), w.shape[0], 256)
+    n_known = golden["q6k_known_w"].shape[0]
+    assert np.array_equal(ref[:n_known], golden["q6k_known_ref"], equal_nan=True)
+    got = _one_hot_rows(K, K.cuda_matvec_q6k, dev(w.reshape(-1)), w.shape[0], 256, range(256)).T
+    scale = _q6k_term_scale(w)
+    finite = np.isfinite(ref)
+    err = np.abs(got.astype(np.float64) - ref)[finite]
+    assert np.all(err <= ONE_HOT_TOL * scale[finite] + 1e-45), float((err / (scale[finite] + 1e-300)).max())
+
+
+def test_one_hot_multi_block_rows(K):
+    """Same check on rows of several blocks (the column-group split of the kernel): 4096 and 1536 columns."""
+    for call, gen, deq, cols in ((K.cuda_matvec_q4k, synth.q4k_matrix, oracle.dequant_q4k, 4096),
+                                 (K.cuda_matvec_q6k, synth.q6k_matrix, oracle.dequant_q6k, 1536)):
+        rows = 40
+        w = gen(93, rows, cols)
+        ref = deq(w, rows, cols)
+        pos = list(range(0, cols, 37)) + [cols - 1]
+        got = _one_hot_rows(K, call, dev(w), rows, cols, pos)
+        bb = 144 if cols == 4096 else 210
+        blocks = w.reshape(rows * (cols // 256), bb)
+        scale = (_q4k_term_scale if cols == 4096 else _q6k_term_scale)(blocks).reshape(rows, cols)
+        err = np.abs(got.astype(np.float64) - ref.T[pos])
+        assert np.all(err <= ONE_HOT_TOL * scale.T[pos] + 1e-45), (cols, float((err / (scale.T[pos] + 1e-300)).max()))

@@ -222,12 +222,49 @@ def test_host_buffer_block_matches_device_block(K):
     H = shape.H
     for it in range(5):
         layer = it % 2
-        x = torch.from_numpy(synth.normal_f32(100 + it, H)).pin_memory()
-        r = torch.from_numpy(synth.normal_f32(200 + it, H)).pin_memory()
+        xr = torch.from_numpy(np.stack([synth.normal_f32(100 + it, H), synth.normal_f32(200 + it, H)])).pin_memory()
         o = torch.empty(H).pin_memory()
-        hb(layer, x, r, o)
+        hb(layer, xr, o)
         want = torch.empty(H, device="cuda")
-        moe.forward(layer, x.cuda(), r.cuda(), want)
+        moe.forward(layer, xr[0].cuda(), xr[1].cuda(), want)
         torch.cuda.synchronize()
         assert torch.equal(o, want.cpu())
+    assert K.mb200_device_error() == 0
+
+
+@pytest.mark.parametrize("pdl", [False, True])
+def test_block_at_the_benchmark_shape_all_forms(K, pdl):
+    """The timed configuration itself: 128 experts, top-8, hidden 4096, intermediate 1536, Q6_K down, in
+    all three forms of mb200_moe_block, with and without programmatic dependent launch, two calls in a
+    row each, against the oracle. The layer is written on the device (as the benchmark does) and copied
+    to the host for the oracle."""
+    from mnemocuda_b200.moe import MoEShape, ResidentMoE
+    shape = MoEShape()  # 128 experts, top-8, 4096, 1536, Q6_K down
+    s = shape
+    moe = ResidentMoE(shape, 1, "cuda", seed=5)
+    experts = moe.experts[0].reshape(-1).cpu().numpy()
+    router = moe.router[0].reshape(-1).cpu().numpy()
+    prev = K.mb200_set_pdl(pdl)
+    try:
+        for trial, (sx, sr) in enumerate(((61, 62), (63, 64))):
+            x, res = synth.normal_f32(sx, s.H), synth.normal_f32(sr, s.H)
+            want, i_ref, w_ref = oracle.moe_block(router, experts, s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE, s.K,
+                                                  s.H, s.EFF, x, res)
+            d_x, d_res = dev(x), dev(res)
+            for mode in (2, 1, 0):
+                K.mb200_set_fused(mode)
+                out = torch.full((s.H,), float("nan"), device="cuda")
+                for _ in range(2):
+                    moe.forward(0, d_x, d_res, out)
+                torch.cuda.synchronize()
+                assert np.array_equal(host(moe.ids[0]), i_ref), (mode, trial)
+                np.testing.assert_allclose(host(moe.wts[0]), w_ref, rtol=1e-5, atol=1e-7)
+                got = host(out).astype(np.float64)
+                rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+                assert rel <= 1e-3, (mode, trial, rel)
+                rel_moe = np.linalg.norm((got - res) - (want.astype(np.float64) - res)) / np.linalg.norm(want.astype(np.float64) - res)
+                assert rel_moe <= 1e-3, (mode, trial, rel_moe)
+    finally:
+        K.mb200_set_fused(2)
+        K.mb200_set_pdl(prev)
     assert K.mb200_device_error() == 0

@@ -67,3 +67,52 @@ def test_static_scratch_router_refuses_oversize(K):
     wts = torch.empty(k, device="cuda")
     with pytest.raises(RuntimeError):
         K.mb200_router_topk_static(router, x, ids, wts, NE, H, k)
+
+
+def test_static_scratch_router_allocates_nothing(K):
+    """Free device memory is the same before and after the calls (outputs and inputs exist beforehand; the
+    kernel's code is already loaded because the regular entry point, which launches the same kernel, ran)."""
+    NE, H, k = 128, 4096, 8
+    router = dev(synth.normal_f32(521, NE * H, H ** -0.5))
+    x = dev(synth.normal_f32(522, H))
+    ids = torch.empty(k, dtype=torch.int32, device="cuda")
+    wts = torch.empty(k, device="cuda")
+    want_ids, _ = _reference_call(K, router, x, NE, H, k)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        K.mb200_router_topk_static(router, x, ids, wts, NE, H, k)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
+    assert np.array_equal(host(ids), want_ids)
+
+
+@pytest.mark.parametrize("pdl", [False, True])
+def test_static_scratch_router_in_a_captured_graph(K, pdl):
+    """Two calls captured in one CUDA graph (after an eager call, which is where the array's address is
+    looked up), with and without programmatic dependent launch, replayed twice."""
+    NE, H, k = 128, 2048, 8
+    router = dev(synth.normal_f32(531, NE * H, H ** -0.5))
+    xs = [dev(synth.normal_f32(532 + i, H)) for i in range(2)]
+    ids = [torch.empty(k, dtype=torch.int32, device="cuda") for _ in range(2)]
+    wts = [torch.empty(k, device="cuda") for _ in range(2)]
+    want = [_reference_call(K, router, x, NE, H, k) for x in xs]
+    prev = K.mb200_set_pdl(pdl)
+    try:
+        K.mb200_router_topk_static(router, xs[0], ids[0], wts[0], NE, H, k)  # eager first
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(2):
+                K.mb200_router_topk_static(router, xs[i], ids[i], wts[i], NE, H, k)
+        for _ in range(2):
+            for t in ids:
+                t.fill_(-1)
+            g.replay()
+            torch.cuda.synchronize()
+            for i in range(2):
+                assert np.array_equal(host(ids[i]), want[i][0])
+                np.testing.assert_allclose(host(wts[i]), want[i][1], rtol=1e-5, atol=1e-7)
+    finally:
+        K.mb200_set_pdl(prev)
