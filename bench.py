@@ -265,11 +265,13 @@ def measure_matvec(torch, K, dev, timer, hbm, steps, warmup):
     return out
 
 
-def measure_decode(torch, K, dev, timer, hbm, which, tokens, expert_range=None):
+def measure_decode(torch, K, dev, timer, hbm, which, tokens, expert_range=None, n_layers=None):
     """Whole-token decode of a model shape resident in HBM: `tokens` tokens in one CUDA graph at the last
     position of the context (KV cache pre-filled up to it), replayed 5 times."""
     from mnemocuda_b200.decode import DecodeConfig, ResidentModel
     cfg = DecodeConfig.qwen3_30b() if which == "30b" else DecodeConfig.qwen3_235b()
+    if n_layers:
+        cfg.n_layers = n_layers  # a slice of the model (profiling captures): same per-layer work
     t0 = time.perf_counter()
     model = ResidentModel(cfg, dev, seed=1, expert_range=expert_range)
     torch.cuda.synchronize()
@@ -512,7 +514,8 @@ def run_secondary(args):
         elif args.workload in ("decode30b", "decode235b"):
             which_model = args.workload[6:]
             line = {"workload": f"whole-token decode, {which_model} shape",
-                    "results": measure_decode(torch, K, dev, timer, hbm, which_model, args.decode_tokens)}
+                    "results": measure_decode(torch, K, dev, timer, hbm, which_model, args.decode_tokens,
+                                              n_layers=args.decode_layers)}
         elif args.workload == "gemm":
             # prefill configuration, dense part: GEMM 512 tokens x (8192 x 4096), weights rotate over 8 copies
             M, N, Kd, copies = 512, 8192, 4096, 8
@@ -579,6 +582,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="headline only: skip the matvec and whole-token decode sections of the JSON line")
     ap.add_argument("--decode-tokens", type=int, default=8, help="tokens per timed CUDA graph of the decode section")
+    ap.add_argument("--decode-layers", type=int, default=0,
+                    help="--workload decode30b|decode235b only: build this many layers instead of the full model")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

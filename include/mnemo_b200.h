@@ -19,6 +19,12 @@
  * tensors to 256 B, src/engine.c:874, and expert parts to multiples of 144 B);
  * Q6_K tensors need 2-byte alignment only.
  *
+ * Not exported: cuda_gemm_q4k / cuda_quantize_mmq_q8_1 (src/gemm_q4k.cu:272-324, 360-364), the reference's
+ * env-gated int8 mma.sync experiment (batch 1 only, never validated, src/forward.c:683-698). An engine that
+ * still calls them keeps the reference's gemm_q4k.o for those two symbols; the tensor-core
+ * path of this library is mb200_gemm_q4k_f16 / mb200_moe_prefill below. Likewise the other GGUF types'
+ * matvecs (q3k, q5k, q8_0), the INT8-KV and GDN kernels stay with the reference's kernels.o.
+ *
  * Part 2 (mb200_*) are additions that return a status code.
  */
 #ifndef MNEMO_B200_H

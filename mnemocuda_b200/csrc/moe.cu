@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const float
             for (int u = 0; u < 8; u++) {
                 const int i = i0 + u * kRouterThreads;
                 if (i < n4) {
-                    const float4 b = x4[i];
+                    const float4 b = __ldcg(x4 + i);  // produced upstream: from L2, never the non-coherent path
                     acc = fmaf(a[u].x, b.x, acc);
                     acc = fmaf(a[u].y, b.y, acc);
                     acc = fmaf(a[u].z, b.z, acc);
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const float
         if (PDL && !waited) asm volatile("griddepcontrol.wait;" ::: "memory");
     } else {
         if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
-        for (int c = threadIdx.x; c < n_cols; c += kRouterThreads) acc = fmaf(wr[c], x[c], acc);
+        for (int c = threadIdx.x; c < n_cols; c += kRouterThreads) acc = fmaf(wr[c], __ldcg(x + c), acc);
     }
     if (PDL) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     acc = warp_sum(acc);

@@ -190,8 +190,10 @@ __device__ __forceinline__ int build_tiles(const FusedParams &P, const int *ids,
     int id = -1;
     float w = 0.0f;
     if (lane < P.n_slots) {
-        id = ids[lane];
-        w = wts[lane];
+        // shared memory (in-kernel routing) or global memory written by the upstream kernel: a volatile load
+        // is right for both (it cannot be served by a stale L1 line)
+        id = *static_cast<const volatile int *>(ids + lane);
+        w = *static_cast<const volatile float *>(wts + lane);
     }
     const bool here = lane < P.n_slots && id >= P.expert_lo && id - P.expert_lo < P.expert_cnt;  // empty slots have id < 0
     const unsigned m = __ballot_sync(0xffffffffu, here);
@@ -320,7 +322,7 @@ __device__ __forceinline__ void finish_down(const FusedParams &P, const FTile &t
         const float a = fmaf(w, v, t.j == 0 ? 0.0f : run[r]);
         if (t.j == n_act - 1) {
             const int row = t.row0 + r;
-            P.y[row] = (P.residual ? P.residual[row] : P.y[row]) + a;
+            P.y[row] = __ldcg(P.residual ? P.residual + row : P.y + row) + a;
         } else {
             run[r] = a;
         }
@@ -351,7 +353,7 @@ __device__ __noinline__ void route_logits(const FusedParams &P, float *rred)
             for (int u = 0; u < 4; u++) {
                 const int i = i0 + u * kConsumers * 32;
                 if (i < n4) {
-                    const float4 b = __ldg(x4 + i);
+                    const float4 b = __ldcg(x4 + i);
                     acc = fmaf(a[u].x, b.x, acc);
                     acc = fmaf(a[u].y, b.y, acc);
                     acc = fmaf(a[u].z, b.z, acc);
@@ -682,7 +684,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         if (warp == 0 && P.residual) {
             const int r0 = static_cast<int>((long long)P.H * blockIdx.x / gridDim.x);
             const int r1 = static_cast<int>((long long)P.H * (blockIdx.x + 1) / gridDim.x);
-            for (int r = r0 + lane; r < r1; r += 32) P.y[r] = P.residual[r];
+            for (int r = r0 + lane; r < r1; r += 32) P.y[r] = __ldcg(P.residual + r);
         }
         return;
     }

@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(kF32Threads) matvec_f32_kernel(const float *__
             for (int u = 0; u < 8; u++) {
                 const int i = i0 + u * kF32Threads;
                 if (i < n4) {
-                    const float4 b = __ldg(x4 + i);
+                    const float4 b = __ldcg(x4 + i);
                     acc = fmaf(a[u].x, b.x, acc);
                     acc = fmaf(a[u].y, b.y, acc);
                     acc = fmaf(a[u].z, b.z, acc);

@@ -291,6 +291,10 @@ static __device__ long long g_trace[kSMs * 2][48];  // one copy per translation 
 // with an odd row pitch, so that the consumer lanes' register loads and these
 // stores are both free of bank conflicts. All loads of a thread are issued
 // before the first use: one memory round trip for K <= 3 * 4 * kQuantThreads.
+// x (and everything else an upstream kernel produces: the routed ids and weights, the residual) is read
+// with ld.global.cg, i.e. from L2: under programmatic dependent launch this kernel is resident before
+// its producer has finished, so neither the non-coherent path (__ldg) nor lines an SM's L1 may still
+// hold from an earlier use of the same buffer can be trusted.
 // Called by the consumer warps only (threadIdx.x < kQuantThreads).
 template <class F, int UN>
 __device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_cols, int bpr,
@@ -306,13 +310,13 @@ __device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_co
         for (int u = 0; u < UN; u++) {
             const int c0 = base + u * kQuantThreads * 4;
             if (vec_ok && c0 + 3 < n_cols) {
-                const float4 t = __ldg(reinterpret_cast<const float4 *>(x + c0));
+                const float4 t = __ldcg(reinterpret_cast<const float4 *>(x + c0));
                 v[u][0] = t.x; v[u][1] = t.y; v[u][2] = t.z; v[u][3] = t.w;
             } else {
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     const bool in = F::kGroup4Tail ? (c0 + 3) < n_cols : (c0 + i) < n_cols;
-                    v[u][i] = in ? __ldg(x + c0 + i) : 0.0f;
+                    v[u][i] = in ? __ldcg(x + c0 + i) : 0.0f;
                 }
             }
         }
@@ -369,13 +373,13 @@ __device__ __forceinline__ void quantize_x_warp(const float *__restrict__ x, int
         for (int u = 0; u < UN; u++) {
             const int c0 = base + u * 128;
             if (vec_ok && c0 + 3 < n_cols) {
-                const float4 t = __ldg(reinterpret_cast<const float4 *>(x + c0));
+                const float4 t = __ldcg(reinterpret_cast<const float4 *>(x + c0));
                 v[u][0] = t.x; v[u][1] = t.y; v[u][2] = t.z; v[u][3] = t.w;
             } else {
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     const bool in = F::kGroup4Tail ? (c0 + 3) < n_cols : (c0 + i) < n_cols;
-                    v[u][i] = in ? __ldg(x + c0 + i) : 0.0f;
+                    v[u][i] = in ? __ldcg(x + c0 + i) : 0.0f;
                 }
             }
         }
@@ -460,10 +464,10 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
                 if (P.pdl) grid_dep_wait();
                 int n = 0;
                 for (int e = 0; e < P.n_slots; e++) {
-                    const int id = P.ids[e];
+                    const int id = __ldcg(P.ids + e);
                     const bool here = id >= P.expert_lo && id - P.expert_lo < P.expert_cnt;  // empty slots have id < 0
                     sid[e] = here ? id - P.expert_lo : -1;
-                    swt[e] = (!here || P.wts == nullptr) ? 0.0f : P.wts[e];  // gate/up has no routing weights
+                    swt[e] = (!here || P.wts == nullptr) ? 0.0f : __ldcg(P.wts + e);  // gate/up has no routing weights
                     if (here) act_list[n++] = e;
                 }
                 *n_act_p = n;
@@ -503,7 +507,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
             // no routed expert lives on this device: the block reduces to the residual
             const int r0 = static_cast<int>((long long)P.vrows * blockIdx.x / gridDim.x);
             const int r1 = static_cast<int>((long long)P.vrows * (blockIdx.x + 1) / gridDim.x);
-            for (int r = r0 + lane; r < r1; r += 32) P.seg[0].y[r] = P.residual[r];
+            for (int r = r0 + lane; r < r1; r += 32) P.seg[0].y[r] = __ldcg(P.residual + r);
         }
         Tile t, ahead;
         float eacc0 = 0.0f, eacc1 = 0.0f;  // kMoeDown: per-row running sums (tiles hold at most 64 rows)
@@ -525,16 +529,16 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
                 if (P.mode == kStore) {
                     seg_y(P, t.seg)[row] = v;
                 } else if (P.mode == kAddResidual) {
-                    seg_y(P, t.seg)[row] = v + P.residual[row];
+                    seg_y(P, t.seg)[row] = v + __ldcg(P.residual + row);
                 } else if (P.mode == kScaledAdd) {
-                    seg_y(P, t.seg)[row] += P.scale * v;
+                    seg_y(P, t.seg)[row] = __ldcg(seg_y(P, t.seg) + row) + P.scale * v;
                 } else if (P.mode == kMoeDown) {
                     // slots arrive in order 0..n_slots-1 for the same rows: keep the running sum in registers
                     float a = (t.j == 0) ? 0.0f : (it == 0 ? eacc0 : eacc1);
                     a = fmaf(swt[t.seg], v, a);
                     if (it == 0) eacc0 = a; else eacc1 = a;
                     if (t.j == walk.n_act - 1)
-                        P.seg[0].y[row] = (P.residual ? P.residual[row] : P.seg[0].y[row]) + a;
+                        P.seg[0].y[row] = __ldcg(P.residual ? P.residual + row : P.seg[0].y + row) + a;
                 } else {
                     float u = 0.0f;
                     for (int c = 0; c < NG; c++) u += pt[(r + t.rows) * NG + c];
@@ -568,7 +572,7 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
     } else {
         // one activation vector per slot; warps take slots round-robin so the loads of all slots are in flight together
         for (int e = warp; e < n_x; e += kConsumers) {
-            const int id = P.ids[e];
+            const int id = __ldcg(P.ids + e);
             if (id < P.expert_lo || id - P.expert_lo >= P.expert_cnt) continue;  // not served here: its activations do not exist
             uint8_t *xb = smem + e * L.x_stride;
             quantize_x_warp<F>(P.x + (size_t)e * P.x_stride, P.n_cols, P.bpr, reinterpret_cast<uint32_t *>(xb + L.xq1),
@@ -831,7 +835,12 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
     if (P.mode == kMoeDown && P.tile_rows > 64) P.tile_rows = 64;  // the epilogue keeps two running sums per lane
     stage_rows = P.tile_rows * mult;
 
-    int S = kMaxStages;
+    // no more stages than the longest range has tiles: a small matvec then takes little shared memory and can
+    // be resident beside another kernel (its copies start while the upstream kernel is still running)
+    int n_tiles = (per_cta + P.tile_rows - 1) / P.tile_rows;
+    if (P.mode == kMoeDown) n_tiles *= P.n_slots;
+    else if (P.mode != kSwiGLU && P.mode != kMoeGateUp) n_tiles += P.nseg - 1;  // a range may cross segment ends
+    int S = n_tiles < 2 ? 2 : (n_tiles > kMaxStages ? kMaxStages : n_tiles);
     Layout L = layout<F>(P.bpr, stage_rows, S, NG, n_x);
     while (S > 2 && L.total > 200 * 1024) {
         S--;

@@ -22,7 +22,36 @@
 #include "support.cuh"
 
 namespace mb200 {
+int pdl_enabled();
+
 namespace {
+
+// Programmatic dependent launch (mb200_set_pdl): every kernel here lets its successor launch at once
+// (the successor's own wait still orders it after this kernel's completion) and waits for its
+// predecessor before it touches memory. In a decode chain this lets the next matvec stream its first
+// weight tiles into shared memory while these small kernels run. Both instructions do nothing in a
+// launch without the attribute.
+__device__ __forceinline__ void pdl_enter()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // ---------------------------------------------------------------- RMSNorm ----
 // out[i] = in[i] * w[i] / sqrt(mean(in^2) + eps); optionally copies `in` to res_out
@@ -48,16 +77,19 @@ __global__ void __launch_bounds__(kNormThreads) rms_norm_kernel(const float *__r
                                                                 const float *__restrict__ w, float *out,
                                                                 float *res_out, int n, float eps)
 {
+    pdl_enter();
     __shared__ float red[33];
     float ss = 0.0f;
+    // inputs an upstream kernel wrote are read from L2 (ld.global.cg) in every kernel of this file: under
+    // programmatic dependent launch the kernel is resident before its producer has finished
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = in[i];
+        const float v = __ldcg(in + i);
         ss = fmaf(v, v, ss);
         if (res_out) res_out[i] = v;
     }
     const float tot = block_sum(ss, red);
     const float scale = 1.0f / sqrtf(tot / static_cast<float>(n) + eps);
-    for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] = in[i] * scale * w[i];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) out[i] = __ldcg(in + i) * scale * w[i];
 }
 
 // One warp per head: head h of `a` (n_a heads, weight wa) or of `b` (n_b heads, weight wb),
@@ -67,6 +99,7 @@ __global__ void __launch_bounds__(128) rms_norm_heads_kernel(const float *a_in, 
                                                              const float *__restrict__ wb, int n_b, int head_dim,
                                                              float eps)
 {
+    pdl_enter();
     const int head = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (head >= n_a + n_b) return;
     const bool is_a = head < n_a;
@@ -74,10 +107,10 @@ __global__ void __launch_bounds__(128) rms_norm_heads_kernel(const float *a_in, 
     float *out = is_a ? a_out + (size_t)head * head_dim : b_out + (size_t)(head - n_a) * head_dim;
     const float *w = is_a ? wa : wb;
     float ss = 0.0f;
-    for (int i = lane; i < head_dim; i += 32) ss = fmaf(in[i], in[i], ss);
+    for (int i = lane; i < head_dim; i += 32) ss = fmaf(__ldcg(in + i), __ldcg(in + i), ss);
     ss = warp_sum(ss);
     const float scale = 1.0f / sqrtf(ss / static_cast<float>(head_dim) + eps);
-    for (int i = lane; i < head_dim; i += 32) out[i] = in[i] * scale * w[i];
+    for (int i = lane; i < head_dim; i += 32) out[i] = __ldcg(in + i) * scale * w[i];
 }
 
 // ------------------------------------------------------------------- RoPE ----
@@ -89,6 +122,7 @@ __global__ void __launch_bounds__(128) rms_norm_heads_kernel(const float *a_in, 
 // graph builder patches `pos` (parameter 3) per token (src/forward.c:636-662).
 __global__ void rope_kernel(float *q, float *k, int head_dim, int pos, float theta, int n_heads_q, int n_heads_k)
 {
+    pdl_enter();
     const int tid = blockIdx.x * blockDim.x + threadIdx.x;
     const int half = head_dim / 2;
     if (tid >= (n_heads_q + n_heads_k) * half) return;
@@ -98,7 +132,7 @@ __global__ void rope_kernel(float *q, float *k, int head_dim, int pos, float the
     double s, c;
     sincos(static_cast<double>(pos) * freq, &s, &c);
     const float cf = static_cast<float>(c), sf = static_cast<float>(s);
-    const float v0 = vec[j], v1 = vec[j + half];
+    const float v0 = __ldcg(vec + j), v1 = __ldcg(vec + j + half);
     vec[j] = v0 * cf - v1 * sf;
     vec[j + half] = v0 * sf + v1 * cf;
 }
@@ -108,9 +142,10 @@ __global__ void rope_kernel(float *q, float *k, int head_dim, int pos, float the
 __global__ void rope_table_kernel(float *cos_out, float *sin_out, int head_dim, const int *pos_ptr, int pos_imm,
                                   float theta)
 {
+    pdl_enter();
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= head_dim / 2) return;
-    const int pos = pos_ptr ? *pos_ptr : pos_imm;
+    const int pos = pos_ptr ? __ldcg(pos_ptr) : pos_imm;
     const double freq = 1.0 / pow(static_cast<double>(theta), (2.0 * j) / head_dim);
     double s, c;
     sincos(static_cast<double>(pos) * freq, &s, &c);
@@ -121,8 +156,9 @@ __global__ void rope_table_kernel(float *cos_out, float *sin_out, int head_dim, 
 // ---------------------------------------------------------- fp32 -> fp16 ----
 __global__ void f32_to_f16_kernel(const float *__restrict__ in, __half *__restrict__ out, int n)
 {
+    pdl_enter();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = __float2half_rn(in[i]);
+    if (i < n) out[i] = __float2half_rn(__ldcg(in + i));
 }
 
 // Parameter order of the reference kernel: its graph builder patches the two destination
@@ -130,10 +166,11 @@ __global__ void f32_to_f16_kernel(const float *__restrict__ in, __half *__restri
 __global__ void f32_to_f16_dual_kernel(const float *__restrict__ a, const float *__restrict__ b,
                                        __half *__restrict__ oa, __half *__restrict__ ob, int n)
 {
+    pdl_enter();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
-        oa[i] = __float2half_rn(a[i]);
-        ob[i] = __float2half_rn(b[i]);
+        oa[i] = __float2half_rn(__ldcg(a + i));
+        ob[i] = __float2half_rn(__ldcg(b + i));
     }
 }
 
@@ -152,6 +189,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(float *q, const
                                                                  __half *kv_v, int n_q, int n_k, int head_dim,
                                                                  float eps, const int *pos_ptr, int pos_imm)
 {
+    pdl_enter();
     const int head = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (head >= n_q + n_k) return;
     const bool is_q = head < n_q;
@@ -160,15 +198,15 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(float *q, const
     const float *w = is_q ? wq : wk;
     const int half = head_dim / 2;
     float ss = 0.0f;
-    for (int i = lane; i < head_dim; i += 32) ss = fmaf(in[i], in[i], ss);
+    for (int i = lane; i < head_dim; i += 32) ss = fmaf(__ldcg(in + i), __ldcg(in + i), ss);
     ss = warp_sum(ss);
     const float scale = w ? 1.0f / sqrtf(ss / static_cast<float>(head_dim) + eps) : 1.0f;
-    const int pos = pos_ptr ? *pos_ptr : pos_imm;
+    const int pos = pos_ptr ? __ldcg(pos_ptr) : pos_imm;
     const size_t row = ((size_t)pos * n_k + (is_q ? 0 : hk)) * head_dim;
     for (int j = lane; j < half; j += 32) {
-        const float v0 = in[j] * scale * (w ? w[j] : 1.0f);
-        const float v1 = in[j + half] * scale * (w ? w[j + half] : 1.0f);
-        const float c = cos_t[j], s = sin_t[j];
+        const float v0 = __ldcg(in + j) * scale * (w ? w[j] : 1.0f);
+        const float v1 = __ldcg(in + j + half) * scale * (w ? w[j + half] : 1.0f);
+        const float c = __ldcg(cos_t + j), s = __ldcg(sin_t + j);
         const float r0 = v0 * c - v1 * s, r1 = v0 * s + v1 * c;
         if (is_q) {
             q[(size_t)head * head_dim + j] = r0;
@@ -179,7 +217,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(float *q, const
         }
     }
     if (!is_q)
-        for (int i = lane; i < head_dim; i += 32) kv_v[row + i] = __float2half_rn(v[(size_t)hk * head_dim + i]);
+        for (int i = lane; i < head_dim; i += 32) kv_v[row + i] = __float2half_rn(__ldcg(v + (size_t)hk * head_dim + i));
 }
 
 // ------------------------------------------------------------ attention ----
@@ -223,6 +261,7 @@ attn_decode_kernel(const float *__restrict__ q, const __half *__restrict__ kv_k,
                    float *part, float *ml, int *tickets, const int *pos_ptr)
 {
     (void)head_dim_unused;  // always kHD here
+    pdl_enter();
     AttnParams P;
     P.q = q; P.kv_k = kv_k; P.kv_v = kv_v; P.out = out; P.n_kv_heads = n_kv_heads; P.gqa = gqa;
     P.seq_len = seq_len_arg; P.pos_ptr = pos_ptr; P.scale = scale; P.part = part; P.ml = ml; P.tickets = tickets;
@@ -239,7 +278,7 @@ attn_decode_kernel(const float *__restrict__ q, const __half *__restrict__ kv_k,
     const int h0 = kvh * P.gqa + blk * 16;       // first query head of this CTA
     const int nh = min(16, P.gqa - blk * 16);    // query heads handled here
     const int S = gridDim.y, chunk = blockIdx.y;
-    const int seq_len = P.pos_ptr ? *P.pos_ptr + 1 : P.seq_len;
+    const int seq_len = P.pos_ptr ? __ldcg(P.pos_ptr) + 1 : P.seq_len;
     const int tiles_total = (seq_len + kTile - 1) / kTile;
     const int tpc = (tiles_total + S - 1) / S;
     const int p_begin = min(seq_len, chunk * tpc * kTile), p_end = min(seq_len, (chunk + 1) * tpc * kTile);
@@ -252,8 +291,8 @@ attn_decode_kernel(const float *__restrict__ q, const __half *__restrict__ kv_k,
         const int j = warp, d0 = (j >> 1) * 32 + t * 8 + (j & 1) * 4;
         const float sc = P.scale * kLog2e;
         float4 r0 = make_float4(0.f, 0.f, 0.f, 0.f), r1 = r0;
-        if (g < nh) r0 = *reinterpret_cast<const float4 *>(P.q + (size_t)(h0 + g) * kHD + d0);
-        if (g + 8 < nh) r1 = *reinterpret_cast<const float4 *>(P.q + (size_t)(h0 + g + 8) * kHD + d0);
+        if (g < nh) r0 = __ldcg(reinterpret_cast<const float4 *>(P.q + (size_t)(h0 + g) * kHD + d0));
+        if (g + 8 < nh) r1 = __ldcg(reinterpret_cast<const float4 *>(P.q + (size_t)(h0 + g + 8) * kHD + d0));
         const float v[8] = {r0.x * sc, r0.y * sc, r0.z * sc, r0.w * sc, r1.x * sc, r1.y * sc, r1.z * sc, r1.w * sc};
         float hi[8], lo[8];
 #pragma unroll
@@ -288,7 +327,7 @@ attn_decode_kernel(const float *__restrict__ q, const __half *__restrict__ kv_k,
             const int p = min(base + nt * 8 + g, last_row);
             const uint4 *src = reinterpret_cast<const uint4 *>(kbase + (size_t)p * row_stride) + t;
 #pragma unroll
-            for (int i = 0; i < 4; i++) dst[nt][i] = __ldg(src + i * 4);  // bytes 64 i + 16 t of the row
+            for (int i = 0; i < 4; i++) dst[nt][i] = __ldcg(src + i * 4);  // bytes 64 i + 16 t of the row
         }
     };
     if (warp < n_tiles) load_k(warp, kq);
@@ -300,8 +339,8 @@ attn_decode_kernel(const float *__restrict__ q, const __half *__restrict__ kv_k,
         for (int r = 0; r < 4; r++) {
             const int p = min(base + 2 * t + (r & 1) + (r >> 1) * 8, last_row);
             const uint4 *src = reinterpret_cast<const uint4 *>(vbase + (size_t)p * row_stride) + g * 2;
-            vr[r][0] = __ldg(src);
-            vr[r][1] = __ldg(src + 1);
+            vr[r][0] = __ldcg(src);
+            vr[r][1] = __ldcg(src + 1);
         }
         uint4 kn[2][4];
         const bool more = tile + kAttnWarps < n_tiles;
@@ -469,6 +508,7 @@ __global__ void __launch_bounds__(256) attn_generic_kernel(const float *__restri
                                                            const __half *__restrict__ kv_v, float *out, int head_dim,
                                                            int n_kv_heads, int seq_len, int gqa_ratio, float scale)
 {
+    pdl_enter();
     extern __shared__ float gsm[];  // [8 warps][head_dim] + [8] m + [8] l
     const int head = blockIdx.x, kvh = head / gqa_ratio, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t stride = (size_t)n_kv_heads * head_dim;
@@ -476,7 +516,7 @@ __global__ void __launch_bounds__(256) attn_generic_kernel(const float *__restri
     float qv[32], acc[32];
     for (int i = 0; i < per; i++) {
         const int d = lane + 32 * i;
-        qv[i] = d < head_dim ? q[(size_t)head * head_dim + d] * scale : 0.0f;
+        qv[i] = d < head_dim ? __ldcg(q + (size_t)head * head_dim + d) * scale : 0.0f;
         acc[i] = 0.0f;
     }
     float m = -INFINITY, l = 0.0f;
@@ -485,14 +525,14 @@ __global__ void __launch_bounds__(256) attn_generic_kernel(const float *__restri
         float s = 0.0f;
         for (int i = 0; i < per; i++) {
             const int d = lane + 32 * i;
-            if (d < head_dim) s = fmaf(qv[i], __half2float(kp[d]), s);
+            if (d < head_dim) s = fmaf(qv[i], __half2float(__ldcg(kp + d)), s);
         }
         s = warp_sum(s);
         const float mn = fmaxf(m, s), r = expf(m - mn), pw = expf(s - mn);
         const __half *vp = kv_v + (size_t)p * stride + (size_t)kvh * head_dim;
         for (int i = 0; i < per; i++) {
             const int d = lane + 32 * i;
-            acc[i] = acc[i] * r + (d < head_dim ? pw * __half2float(vp[d]) : 0.0f);
+            acc[i] = acc[i] * r + (d < head_dim ? pw * __half2float(__ldcg(vp + d)) : 0.0f);
         }
         l = l * r + pw;
         m = mn;
@@ -521,8 +561,9 @@ __global__ void __launch_bounds__(256) attn_generic_kernel(const float *__restri
 // --------------------------------------------------------- residual add ----
 __global__ void residual_add_kernel(const float *__restrict__ a, const float *__restrict__ b, float *out, int n)
 {
+    pdl_enter();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = a[i] + b[i];
+    if (i < n) out[i] = __ldcg(a + i) + __ldcg(b + i);
 }
 
 // ----------------------------------------------------- Q4_K embedding row ----
@@ -533,7 +574,8 @@ __global__ void residual_add_kernel(const float *__restrict__ a, const float *__
 __global__ void __launch_bounds__(256) embed_q4k_kernel(const uint8_t *__restrict__ table, float *__restrict__ out,
                                                         const int *token_ptr, int token_imm, int hidden, int row_bytes)
 {
-    const int token = token_ptr ? *token_ptr : token_imm;
+    pdl_enter();
+    const int token = token_ptr ? __ldcg(token_ptr) : token_imm;
     const int c = blockIdx.x * 256 + threadIdx.x;
     if (c >= hidden) return;
     const uint8_t *blk = table + (size_t)token * row_bytes + (size_t)blockIdx.x * kQ4KBlock;
@@ -558,30 +600,26 @@ __global__ void __launch_bounds__(256) embed_q4k_kernel(const uint8_t *__restric
 
 // --------------------------------------------------------------- argmax ----
 // Greedy sampling (reference src/kernels.cu:2048-2071): the index of the largest logit.
-// Ties resolve as in the reference's 256-thread strided scan + tree: the smallest
-// index modulo 256 wins, then the smallest index.
+// Ties resolve as in the reference's 256-thread strided scan + shared-memory tree: thread
+// t = index % 256 keeps its first maximum, and of two tied threads the tree keeps the one
+// whose lowest differing bit of t is 0 -- i.e. the smaller bit-reversed t wins.
 __device__ __forceinline__ bool argmax_better(float v, int i, float bv, int bi)
 {
     if (v > bv) return true;
     if (v < bv || !(v == bv)) return false;
-    const int a = i & 255, b = bi & 255;
+    const unsigned a = __brev(static_cast<unsigned>(i & 255)), b = __brev(static_cast<unsigned>(bi & 255));
     return a < b || (a == b && i < bi);
 }
 
-__global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ logits, int n, int *result,
-                                                      int *pos_ptr)
+// Candidates of the CTAs of one launch: a slot per CTA plus a ticket. It lives in the library image (the
+// reference's cuda_sample_token has no workspace argument); launches that overlap on a device would race on it.
+constexpr int kArgmaxCtas = 128;
+__device__ float g_argmax_val[kArgmaxCtas];
+__device__ int g_argmax_idx[kArgmaxCtas];
+__device__ int g_argmax_ticket;
+
+__device__ __forceinline__ void argmax_warp(float &bv, int &bi)
 {
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    float bv = -1e30f;
-    int bi = 0;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = logits[i];
-        if (argmax_better(v, i, bv, bi)) {
-            bv = v;
-            bi = i;
-        }
-    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -591,28 +629,60 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
             bi = oi;
         }
     }
+}
+
+// Every CTA scans a strided share of the logits; the last one to finish (ticket) picks among the CTAs'
+// candidates. The preference order is total, so the result does not depend on how the scan is split.
+__global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ logits, int n, int *result, int *pos_ptr)
+{
+    pdl_enter();
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    __shared__ int is_last;
+    float bv = -1e30f;
+    int bi = 0;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float v = __ldcg(logits + i);
+        if (argmax_better(v, i, bv, bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+    argmax_warp(bv, bi);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) {
         sv[warp] = bv;
         si[warp] = bi;
     }
     __syncthreads();
-    if (warp == 0) {
-        bv = sv[lane];
-        bi = si[lane];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (argmax_better(ov, oi, bv, bi)) {
-                bv = ov;
-                bi = oi;
-            }
+    if (warp != 0) return;
+    bv = lane < 8 ? sv[lane] : -1e30f;
+    bi = lane < 8 ? si[lane] : 0;
+    argmax_warp(bv, bi);
+    if (lane == 0) {
+        g_argmax_val[blockIdx.x] = bv;
+        g_argmax_idx[blockIdx.x] = bi;
+        __threadfence();
+        is_last = (atomicAdd(&g_argmax_ticket, 1) == static_cast<int>(gridDim.x) - 1);
+    }
+    __syncwarp();
+    if (!is_last) return;
+    __threadfence();
+    bv = -1e30f;
+    bi = 0;
+    for (int c = lane; c < static_cast<int>(gridDim.x); c += 32) {
+        const float v = __ldcg(&g_argmax_val[c]);
+        const int i = __ldcg(&g_argmax_idx[c]);
+        if (argmax_better(v, i, bv, bi)) {
+            bv = v;
+            bi = i;
         }
-        if (lane == 0) {
-            *result = bi;
-            if (pos_ptr) *pos_ptr += 1;  // decode path: the next replay of the graph handles the next position
-        }
+    }
+    argmax_warp(bv, bi);
+    if (lane == 0) {
+        *result = bi;
+        if (pos_ptr) *pos_ptr += 1;  // decode path: the next replay of the graph handles the next position
+        g_argmax_ticket = 0;
     }
 }
 
@@ -708,43 +778,43 @@ int launch_attn_decode(const float *q, const void *kv_k, const void *kv_v, float
     P.part = static_cast<float *>(workspace);
     P.ml = P.part + slots * 16 * kHD;
     P.tickets = reinterpret_cast<int *>(P.ml + slots * 2 * 16);
-    attn_decode_kernel<<<dim3(blocks, S), kAttnThreads, kAttnSmem, stream>>>(P.q, P.kv_k, P.kv_v, P.out, kHD, P.n_kv_heads,
-                                                                             P.seq_len, P.gqa, P.scale, P.part, P.ml,
-                                                                             P.tickets, P.pos_ptr);
+    launch_k(attn_decode_kernel, dim3(blocks, S), dim3(kAttnThreads), kAttnSmem, stream, P.q, P.kv_k, P.kv_v, P.out, kHD,
+             P.n_kv_heads, P.seq_len, P.gqa, P.scale, P.part, P.ml, P.tickets, P.pos_ptr);
     return cudaGetLastError() == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
 }
 
 void launch_rms_norm(const float *in, const float *w, float *out, float *res_out, int n, float eps, cudaStream_t stream)
 {
-    rms_norm_kernel<<<1, kNormThreads, 0, stream>>>(in, w, out, res_out, n, eps);
+    launch_k(rms_norm_kernel, dim3(1), dim3(kNormThreads), 0, stream, in, w, out, res_out, n, eps);
 }
 
 void launch_rope_table(float *cos_out, float *sin_out, int head_dim, const int *pos_ptr, int pos, float theta,
                        cudaStream_t stream)
 {
-    rope_table_kernel<<<(head_dim / 2 + 63) / 64, 64, 0, stream>>>(cos_out, sin_out, head_dim, pos_ptr, pos, theta);
+    launch_k(rope_table_kernel, dim3((head_dim / 2 + 63) / 64), dim3(64), 0, stream, cos_out, sin_out, head_dim, pos_ptr, pos,
+             theta);
 }
 
 void launch_qk_norm_rope_store(float *q, const float *k, const float *v, const float *wq, const float *wk,
                                const float *cos_t, const float *sin_t, void *kv_k, void *kv_v, int n_q, int n_k,
                                int head_dim, float eps, const int *pos_ptr, int pos, cudaStream_t stream)
 {
-    qk_norm_rope_store_kernel<<<(n_q + n_k + 3) / 4, 128, 0, stream>>>(q, k, v, wq, wk, cos_t, sin_t,
-                                                                       static_cast<__half *>(kv_k),
-                                                                       static_cast<__half *>(kv_v), n_q, n_k, head_dim,
-                                                                       eps, pos_ptr, pos);
+    launch_k(qk_norm_rope_store_kernel, dim3((n_q + n_k + 3) / 4), dim3(128), 0, stream, q, k, v, wq, wk, cos_t, sin_t,
+             static_cast<__half *>(kv_k), static_cast<__half *>(kv_v), n_q, n_k, head_dim, eps, pos_ptr, pos);
 }
 
 void launch_embed_q4k(const void *table, float *out, const int *token_ptr, int token, int hidden, int row_bytes,
                       cudaStream_t stream)
 {
-    embed_q4k_kernel<<<(hidden + 255) / 256, 256, 0, stream>>>(static_cast<const uint8_t *>(table), out, token_ptr, token,
-                                                               hidden, row_bytes);
+    launch_k(embed_q4k_kernel, dim3((hidden + 255) / 256), dim3(256), 0, stream, static_cast<const uint8_t *>(table), out,
+             token_ptr, token, hidden, row_bytes);
 }
 
 void launch_argmax(const float *logits, int n, int *result, int *pos_ptr, cudaStream_t stream)
 {
-    argmax_kernel<<<1, 1024, 0, stream>>>(logits, n, result, pos_ptr);
+    int ctas = (n + 2047) / 2048;  // eight logits per thread
+    ctas = ctas < 1 ? 1 : (ctas > kArgmaxCtas ? kArgmaxCtas : ctas);
+    launch_k(argmax_kernel, dim3(ctas), dim3(256), 0, stream, logits, n, result, pos_ptr);
 }
 
 }  // namespace mb200
@@ -772,8 +842,9 @@ void cuda_rms_norm_batched(const float *input, const float *weight, float *outpu
                            float eps, cudaStream_t stream)
 {
     if (n_heads <= 0 || head_dim <= 0) return;
-    rms_norm_heads_kernel<<<(n_heads + 3) / 4, 128, 0, stream>>>(input, output, weight, n_heads, nullptr, nullptr,
-                                                                 nullptr, 0, head_dim, eps);
+    launch_k(rms_norm_heads_kernel, dim3((n_heads + 3) / 4), dim3(128), 0, stream, input, output, weight, n_heads,
+             static_cast<const float *>(nullptr), static_cast<float *>(nullptr), static_cast<const float *>(nullptr), 0,
+             head_dim, eps);
     MB200_CHECK_LAUNCH("cuda_rms_norm_batched");
 }
 
@@ -781,8 +852,8 @@ void cuda_rms_norm_qk(float *q, float *k, const float *q_weight, const float *k_
                       int n_k, float eps, cudaStream_t stream)
 {
     if (n_q + n_k <= 0 || head_dim <= 0) return;
-    rms_norm_heads_kernel<<<(n_q + n_k + 3) / 4, 128, 0, stream>>>(q, q, q_weight, n_q, k, k, k_weight, n_k, head_dim,
-                                                                   eps);
+    launch_k(rms_norm_heads_kernel, dim3((n_q + n_k + 3) / 4), dim3(128), 0, stream, q, q, q_weight, n_q, k, k, k_weight,
+             n_k, head_dim, eps);
     MB200_CHECK_LAUNCH("cuda_rms_norm_qk");
 }
 
@@ -791,22 +862,22 @@ void cuda_rope(float *q, float *k, int head_dim, int pos, float theta, int n_hea
 {
     const int total = (n_heads_q + n_heads_k) * (head_dim / 2);
     if (total <= 0) return;
-    rope_kernel<<<(total + 127) / 128, 128, 0, stream>>>(q, k, head_dim, pos, theta, n_heads_q, n_heads_k);
+    launch_k(rope_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, q, k, head_dim, pos, theta, n_heads_q, n_heads_k);
     MB200_CHECK_LAUNCH("cuda_rope");
 }
 
 void cuda_f32_to_f16(const float *in, void *out, int n, cudaStream_t stream)
 {
     if (n <= 0) return;
-    f32_to_f16_kernel<<<(n + 255) / 256, 256, 0, stream>>>(in, static_cast<__half *>(out), n);
+    launch_k(f32_to_f16_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, in, static_cast<__half *>(out), n);
     MB200_CHECK_LAUNCH("cuda_f32_to_f16");
 }
 
 void cuda_f32_to_f16_dual(const float *a, const float *b, void *oa, void *ob, int n, cudaStream_t stream)
 {
     if (n <= 0) return;
-    f32_to_f16_dual_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a, b, static_cast<__half *>(oa),
-                                                                static_cast<__half *>(ob), n);
+    launch_k(f32_to_f16_dual_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, a, b, static_cast<__half *>(oa),
+             static_cast<__half *>(ob), n);
     MB200_CHECK_LAUNCH("cuda_f32_to_f16_dual");
 }
 
@@ -833,9 +904,8 @@ void cuda_attention_f16kv(const void *q, const void *kv_k, const void *kv_v, flo
         P.ml = ws->ml;
         P.tickets = ws->tickets;
         const int S = attn_chunks_for(n_kv_heads, gqa_ratio, kStaticAttnSlots);
-        attn_decode_kernel<<<dim3(blocks, S), kAttnThreads, kAttnSmem, stream>>>(P.q, P.kv_k, P.kv_v, P.out, kHD,
-                                                                                 P.n_kv_heads, P.seq_len, P.gqa, P.scale,
-                                                                                 P.part, P.ml, P.tickets, nullptr);
+        launch_k(attn_decode_kernel, dim3(blocks, S), dim3(kAttnThreads), kAttnSmem, stream, P.q, P.kv_k, P.kv_v, P.out, kHD,
+                 P.n_kv_heads, P.seq_len, P.gqa, P.scale, P.part, P.ml, P.tickets, static_cast<const int *>(nullptr));
     } else {
         if (head_dim > 1024 || !attn_attr()) {
             fprintf(stderr, "[mnemo_b200] cuda_attention_f16kv: head_dim=%d not supported\n", head_dim);
@@ -843,10 +913,9 @@ void cuda_attention_f16kv(const void *q, const void *kv_k, const void *kv_v, flo
             return;
         }
         const size_t smem = (8 * (size_t)head_dim + 16) * sizeof(float);
-        attn_generic_kernel<<<n_heads_q, 256, smem, stream>>>(static_cast<const float *>(q),
-                                                              static_cast<const __half *>(kv_k),
-                                                              static_cast<const __half *>(kv_v), out, head_dim,
-                                                              n_kv_heads, seq_len, gqa_ratio, scale);
+        launch_k(attn_generic_kernel, dim3(n_heads_q), dim3(256), smem, stream, static_cast<const float *>(q),
+                 static_cast<const __half *>(kv_k), static_cast<const __half *>(kv_v), out, head_dim, n_kv_heads, seq_len,
+                 gqa_ratio, scale);
     }
     MB200_CHECK_LAUNCH("cuda_attention_f16kv");
 }
@@ -861,7 +930,7 @@ void *cuda_get_attn_f16kv_kernel_ptr(void) { return reinterpret_cast<void *>(att
 void cuda_residual_add(const float *a, const float *b, float *out, int n, cudaStream_t stream)
 {
     if (n <= 0) return;
-    residual_add_kernel<<<(n + 255) / 256, 256, 0, stream>>>(a, b, out, n);
+    launch_k(residual_add_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, a, b, out, n);
     MB200_CHECK_LAUNCH("cuda_residual_add");
 }
 

@@ -58,8 +58,16 @@ SHAPES = {
 }
 
 
+@pytest.fixture(params=[False, True], ids=["plain", "pdl"])
+def pdl(request, K):
+    """Every decode test runs with plain launches and with programmatic dependent launch."""
+    prev = K.mb200_set_pdl(request.param)
+    yield request.param
+    K.mb200_set_pdl(prev)
+
+
 @pytest.mark.parametrize("shape", ["tiny", "mid"])
-def test_layers_and_logits_match_oracle(K, shape):
+def test_layers_and_logits_match_oracle(K, shape, pdl):
     from mnemocuda_b200.decode import DecodeConfig, ResidentModel
     cfg = DecodeConfig(**SHAPES[shape])
     pos0 = cfg.ctx_len - 5
@@ -96,7 +104,7 @@ def test_layers_and_logits_match_oracle(K, shape):
     assert int(model.pos.item()) == pos0 + 1
 
 
-def test_greedy_tokens_match_oracle_and_graph_replay(K):
+def test_greedy_tokens_match_oracle_and_graph_replay(K, pdl):
     from mnemocuda_b200.decode import DecodeConfig, ResidentModel
     cfg = DecodeConfig(**SHAPES["tiny"])
     pos0, n_tok, tok0 = 20, 6, 3
@@ -136,7 +144,37 @@ def test_greedy_tokens_match_oracle_and_graph_replay(K):
     assert replay == want
 
 
-def test_one_layer_at_the_235b_shape(K):
+def test_launch_overlap_does_not_change_the_tokens(K):
+    """Programmatic dependent launch lets each kernel of the chain become resident before its producer has
+    finished; the tokens must be those of plain launches. Buffers are reused from layer to layer with different
+    contents, so a kernel that read a producer's output through a non-coherent or stale cached path would show
+    here (the 30B expert shape takes the router kernel + two routed stream kernels, the 235B one the fused kernel)."""
+    from mnemocuda_b200.decode import DecodeConfig, ResidentModel
+    for cfg in (DecodeConfig.qwen3_30b(ctx_len=512, n_layers=6), DecodeConfig.qwen3_235b(ctx_len=512, n_layers=3)):
+        cfg.vocab = 8192
+        model = ResidentModel(cfg, "cuda", seed=13)
+        kv0 = [(T["kv_k"].clone(), T["kv_v"].clone()) for T in model.layers]
+        runs = {}
+        for mode in (False, True, True):
+            prev = K.mb200_set_pdl(mode)
+            try:
+                for T, (a, b) in zip(model.layers, kv0):
+                    T["kv_k"].copy_(a)
+                    T["kv_v"].copy_(b)
+                model.set_state(3, cfg.ctx_len - 8)
+                toks = []
+                for _ in range(6):
+                    model.step()
+                    toks.append(int(model.token.item()))
+                runs.setdefault(mode, []).append(toks)
+            finally:
+                K.mb200_set_pdl(prev)
+        assert runs[True][0] == runs[False][0] == runs[True][1], (cfg.name, runs)
+        del model
+        torch.cuda.empty_cache()
+
+
+def test_one_layer_at_the_235b_shape(K, pdl):
     """A single layer with the benchmark's 235B geometry (hidden 4096, 64/4 heads, 128 experts top-8,
     intermediate 1536) at the last position of an 8192-token context, against the oracle."""
     from mnemocuda_b200.decode import DecodeConfig, ResidentModel

@@ -76,10 +76,14 @@ def test_argmax_follows_the_reference_scan_order():
     x = synth.normal_f32(9, 5000)
     assert oracle.argmax(x) == int(np.argmax(x))
     x[:] = 0.0
-    x[[700, 300, 4396]] = 5.0  # ties: 300 % 256 = 44 beats 700 % 256 = 188; 4396 % 256 = 44 too, but 300 comes first
+    # ties: thread = index % 256 keeps its first maximum; between threads the shared-memory tree keeps the one
+    # whose lowest differing bit is 0 (44 = 0b00101100 beats 188 = 0b10111100; 4396 % 256 = 44 comes after 300)
+    x[[700, 300, 4396]] = 5.0
     assert oracle.argmax(x) == 300
     x[44] = 5.0
     assert oracle.argmax(x) == 44
+    x[4848] = 5.0  # thread 240 = 0b11110000: differs from 44 first in bit 2, where it has the 0
+    assert oracle.argmax(x) == 4848
     assert oracle.argmax(np.full(10, -np.inf, np.float32)) == 0
 
 
