@@ -19,6 +19,13 @@
 //   * the 16 producer warps read the accumulator back with tcgen05.ld and store out[t][n]
 //     (coalesced over n).
 // 4-stage ring (48 KB per stage); every mbarrier wait is bounded; TMEM is always released.
+//
+// Split-precision variants (template parameter HL) for the grouped per-expert form, where two GEMMs are
+// chained and one fp16 rounding per operand per GEMM would add up to more than 1e-3 on some token rows:
+//   HL = 1: every weight is written as hi = fp16(w) and lo = fp16(w - hi), and the stage is multiplied
+//           twice into the same TMEM accumulator (D += A_hi B, D += A_lo B): weights carry ~22 bits;
+//   HL = 2: the activations come as hi and lo halves too (two TMA tiles): D += A_hi B_hi + A_lo B_hi + A_hi B_lo.
+// The tensor pipe has the time: the grouped form is bound by the weight stream.
 #include <cuda.h>
 
 #include <cstdio>
@@ -35,11 +42,12 @@ constexpr int kBK = 64;    // K per stage: 64 fp16 = one 128-byte swizzle row
 constexpr int kDequantWarps = 16;
 constexpr int kThreads = (2 + kDequantWarps) * 32;  // warp 0: TMA, warp 1: MMA + TMEM, warps 2..17: dequant (+ epilogue)
 constexpr int kABytes = kBN * kBK * 2;               // 16 KB
-template <int BT>
+template <int BT, int HL = 0>
 struct Cfg {
     static constexpr int kBBytes = BT * kBK * 2;  // 32 KB (BT = 256) / 8 KB (BT = 64)
-    static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages = BT == 256 ? 4 : 8;  // 192 KB of operands in flight either way
+    static constexpr int kATotal = kABytes * (HL ? 2 : 1), kBTotal = kBBytes * (HL == 2 ? 2 : 1);
+    static constexpr int kStageBytes = kATotal + kBTotal;
+    static constexpr int kStages = (192 * 1024) / kStageBytes;  // 192 KB of operands in flight
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
     static constexpr int kTmemCols = BT;  // power of two >= 32
     // Instruction descriptor: fp16 x fp16 -> fp32, both operands K-major, M = kBN, N = BT.
@@ -130,6 +138,7 @@ struct GemmParams {
     const int *seg_off, *seg_cnt;
     int tiles_per_expert;  // 0 = dense
     size_t expert_stride;
+    int x_lo_row0;         // HL = 2: the lo halves of the activations are rows x_lo_row0 .. of the same tensor map
 };
 
 // ---- one thread's 32 weights of a 64-wide K chunk, as fp32 ----------------------
@@ -229,12 +238,13 @@ __device__ __forceinline__ void dequant32_q6k(const RawQ6 &raw, int c, int h, fl
     }
 }
 
-template <int BT>
+template <int BT, int HL>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap,
                                                                const __grid_constant__ GemmParams P)
 {
-    using C = Cfg<BT>;
+    using C = Cfg<BT, HL>;
     constexpr int kStages = C::kStages, kStageBytes = C::kStageBytes, kBBytes = C::kBBytes, kTmemCols = C::kTmemCols;
+    constexpr int kATotal = C::kATotal, kBTotal = C::kBTotal;
     constexpr uint32_t kIdesc = C::kIdesc;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -289,9 +299,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                     *abort_flag = 1;
                     break;
                 }
-                uint8_t *b_tile = stage_base + s * kStageBytes + kABytes;
-                mbar_expect_tx(&full[s], kBBytes);
+                uint8_t *b_tile = stage_base + s * kStageBytes + kATotal;
+                mbar_expect_tx(&full[s], kBTotal);
                 tma_load_2d(b_tile, &xmap, kb * kBK, t0, &full[s]);
+                if (HL == 2) tma_load_2d(b_tile + kBBytes, &xmap, kb * kBK, P.x_lo_row0 + t0, &full[s]);
                 if (++s == kStages) {
                     s = 0;
                     ph ^= 1;
@@ -313,10 +324,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
                 if (kb == 8) GSTAMP(5);
                 if (kb == n_kb - 1) GSTAMP(6);
                 const uint32_t a_addr = smem_u32(stage_base + s * kStageBytes);
-                const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kABytes);
+                const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + kATotal);
 #pragma unroll
                 for (int kk = 0; kk < kBK / 16; kk++)  // 16 fp16 = 32 bytes = 2 descriptor units per K step
                     umma_f16(tmem_base, da + 2 * kk, db + 2 * kk, kIdesc, (kb | kk) != 0);
+                if (HL) {  // the lo halves of the weights against the same activations
+                    const uint64_t dal = smem_desc_sw128(a_addr + kABytes);
+#pragma unroll
+                    for (int kk = 0; kk < kBK / 16; kk++) umma_f16(tmem_base, dal + 2 * kk, db + 2 * kk, kIdesc, 1u);
+                }
+                if (HL == 2) {  // the hi halves of the weights against the lo halves of the activations
+                    const uint64_t dbl = smem_desc_sw128(a_addr + kATotal + kBBytes);
+#pragma unroll
+                    for (int kk = 0; kk < kBK / 16; kk++) umma_f16(tmem_base, da + 2 * kk, dbl + 2 * kk, kIdesc, 1u);
+                }
                 umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
                 if (kb >= 16 && kb < 24) GSTAMP(33 + (kb - 16) * 2);
                 if (++s == kStages) {
@@ -343,15 +364,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
             uint8_t *a_row = stage_base + s * kStageBytes + r * 128;
 #pragma unroll
             for (int j = 0; j < 4; j++) {  // four 16-byte chunks of 8 fp16: logical chunk 4h + j, XOR-swizzled by the row
-                uint32_t pk[4];
+                uint32_t pk[4], pl[4];
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
-                    const __half2 hv = row_ok ? __floats2half2_rn(wv[8 * j + 2 * e], wv[8 * j + 2 * e + 1])
-                                              : __floats2half2_rn(0.0f, 0.0f);
+                    const float w0 = row_ok ? wv[8 * j + 2 * e] : 0.0f, w1 = row_ok ? wv[8 * j + 2 * e + 1] : 0.0f;
+                    const __half2 hv = __floats2half2_rn(w0, w1);
                     pk[e] = *reinterpret_cast<const uint32_t *>(&hv);
+                    if (HL) {  // what the fp16 rounding dropped, as a second fp16
+                        const float2 back = __half22float2(hv);
+                        const __half2 lv = __floats2half2_rn(w0 - back.x, w1 - back.y);
+                        pl[e] = *reinterpret_cast<const uint32_t *>(&lv);
+                    }
                 }
                 const int chunk = (4 * h + j) ^ (r & 7);
                 *reinterpret_cast<uint4 *>(a_row + chunk * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                if (HL) *reinterpret_cast<uint4 *>(a_row + kABytes + chunk * 16) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
             }
             proxy_fence_async();  // generic-proxy stores above must be visible to the tensor core's async proxy
             __syncwarp();
@@ -432,7 +459,7 @@ EncodeTiledFn encode_tiled()
 }
 
 // X: fp16 [rows_x][K] row-major. Launches gemm_tc_kernel<BT> over grid (weight tiles [x experts], token tiles).
-template <int BT>
+template <int BT, int HL = 0>
 int launch_gemm_bt(GemmParams &P, const void *x_f16, int rows_x, dim3 grid, cudaStream_t stream, const char *where)
 {
     EncodeTiledFn enc = encode_tiled();
@@ -453,12 +480,12 @@ int launch_gemm_bt(GemmParams &P, const void *x_f16, int rows_x, dim3 grid, cuda
     }
     static bool attr_done[kMaxDevices] = {false};  // the opt-in is a per-device attribute
     if (!attr_done[current_device()]) {
-        cudaFuncSetAttribute(gemm_tc_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BT>::kSmemBytes);
+        cudaFuncSetAttribute(gemm_tc_kernel<BT, HL>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BT, HL>::kSmemBytes);
         attr_done[current_device()] = true;
     }
     P.bpr = P.K / 256;
     P.err = device_error_word();
-    gemm_tc_kernel<BT><<<grid, kThreads, Cfg<BT>::kSmemBytes, stream>>>(xmap, P);
+    gemm_tc_kernel<BT, HL><<<grid, kThreads, Cfg<BT, HL>::kSmemBytes, stream>>>(xmap, P);
     return cudaGetLastError() == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
 }
 
@@ -541,15 +568,19 @@ __global__ void moe_gather_kernel(const uint4 *__restrict__ x, uint4 *__restrict
 // act16[row][j] = fp16(silu(gate) * up * 2^-4): the 2^-4 keeps SwiGLU outputs inside fp16's range
 // (they reach ~2.5e4 with the benchmark's weights); the combine step multiplies it back exactly.
 constexpr float kActScale = 1.0f / 16.0f;
-__global__ void moe_swiglu_rows_kernel(const float *__restrict__ gu, __half *__restrict__ act, const int *__restrict__ off,
-                                       int n_experts, int EFF)
+// The activation keeps ~22 bits as two fp16 arrays: act_hi = fp16(a), act_lo = fp16(a - act_hi).
+__global__ void moe_swiglu_rows_kernel(const float *__restrict__ gu, __half *__restrict__ act_hi,
+                                       __half *__restrict__ act_lo, const int *__restrict__ off, int n_experts, int EFF)
 {
     const int row = blockIdx.x;
     if (row >= off[n_experts]) return;
     const float *g = gu + (size_t)row * 2 * EFF;
     for (int j = threadIdx.x; j < EFF; j += blockDim.x) {
         const float gv = g[j];
-        act[(size_t)row * EFF + j] = __float2half_rn(gv / (1.0f + expf(-gv)) * g[EFF + j] * kActScale);
+        const float a = gv / (1.0f + expf(-gv)) * g[EFF + j] * kActScale;
+        const __half hi = __float2half_rn(a);
+        act_hi[(size_t)row * EFF + j] = hi;
+        act_lo[(size_t)row * EFF + j] = __float2half_rn(a - __half2float(hi));
     }
 }
 
@@ -585,7 +616,7 @@ Workspace workspace_layout(int M, int k, int H, int EFF, int n_experts)
     w.pair_of_row = o;  o = align_up(o + sizeof(int) * P);
     w.xs = o;           o = align_up(o + 2 * P * H);
     w.gu = o;           o = align_up(o + 4 * P * 2 * EFF);
-    w.act = o;          o = align_up(o + 2 * P * EFF);
+    w.act = o;          o = align_up(o + 2 * 2 * P * EFF);  // hi halves [P][EFF], then lo halves [P][EFF]
     w.dn = o;           o = align_up(o + 4 * P * H);
     w.total = o;
     return w;
@@ -595,8 +626,8 @@ Workspace workspace_layout(int M, int k, int H, int EFF, int n_experts)
 
 void gemm_init()
 {
-    cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<256>::kSmemBytes);
-    cudaFuncSetAttribute(gemm_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<64>::kSmemBytes);
+    cudaFuncSetAttribute(gemm_tc_kernel<256, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<256>::kSmemBytes);
+    cudaFuncSetAttribute(gemm_tc_kernel<64, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<64>::kSmemBytes);
     (void)encode_tiled();
 }
 
@@ -663,10 +694,11 @@ int mb200_moe_prefill(const void *experts, size_t expert_stride, size_t gate_sz,
     G.seg_cnt = so.cnt;
     G.tiles_per_expert = (2 * EFF + kBN - 1) / kBN;
     G.expert_stride = expert_stride;
-    int rc = launch_gemm_bt<kGroupBT>(G, xs, P, dim3(n_experts * G.tiles_per_expert, token_tiles), stream, where);
+    // weights as hi + lo fp16 (x is fp16 already): the gate / up values keep fp32 accuracy
+    int rc = launch_gemm_bt<kGroupBT, 1>(G, xs, P, dim3(n_experts * G.tiles_per_expert, token_tiles), stream, where);
     if (rc != MB200_OK) return rc;
 
-    moe_swiglu_rows_kernel<<<P, 256, 0, stream>>>(gu, act, so.off, n_experts, EFF);
+    moe_swiglu_rows_kernel<<<P, 256, 0, stream>>>(gu, act, act + (size_t)P * EFF, so.off, n_experts, EFF);
 
     GemmParams D{};
     D.w = static_cast<const uint8_t *>(experts) + gate_sz + up_sz;
@@ -679,7 +711,8 @@ int mb200_moe_prefill(const void *experts, size_t expert_stride, size_t gate_sz,
     D.seg_cnt = so.cnt;
     D.tiles_per_expert = (H + kBN - 1) / kBN;
     D.expert_stride = expert_stride;
-    rc = launch_gemm_bt<kGroupBT>(D, act, P, dim3(n_experts * D.tiles_per_expert, token_tiles), stream, where);
+    D.x_lo_row0 = P;  // the tensor map covers [2 P][EFF]: hi rows, then lo rows
+    rc = launch_gemm_bt<kGroupBT, 2>(D, act, 2 * P, dim3(n_experts * D.tiles_per_expert, token_tiles), stream, where);
     if (rc != MB200_OK) return rc;
 
     moe_combine_kernel<<<M, 256, 0, stream>>>(dn, so.row_of_pair, wts, residual, y, k, H);

@@ -129,31 +129,44 @@ def test_moe_prefill_grouped(K, M, NE, k, H, EFF, down_type):
     num = np.linalg.norm((got - res) - moe_ref, axis=1)
     den = np.linalg.norm(moe_ref, axis=1)
     rel = num / den
-    # Two chained GEMMs with fp16 weight tiles: each GEMM is within 1e-3 of fp32 on its own inputs
-    # (tests above, and the stage check below); end to end the two roundings of W compound to a median
-    # of ~4.5e-4 per token row with a tail up to ~2e-3 on rows whose output happens to be small.
-    assert float(np.median(rel)) <= 1e-3, float(np.median(rel))
-    assert float(rel.max()) <= 2.5e-3, float(rel.max())
+    # every token row within the stated tolerance (weights and SwiGLU activations are carried as hi + lo fp16
+    # pairs through the two chained GEMMs, so the result is far inside it)
+    assert float(rel.max()) <= 1e-3, float(rel.max())
+    assert float(np.median(rel)) <= 1e-4, float(np.median(rel))
 
-    # stage check: the grouped launches give what the dense GEMM gives on each expert's gathered tokens
-    d_exp, d_x = dev(experts), dev(x)
-    acc = torch.zeros(M, H, device="cuda")
-    for e in range(NE):
-        rows, slots = np.nonzero(ids == e)
-        if rows.size == 0:
-            continue
-        xe = d_x[torch.from_numpy(rows).cuda()].contiguous()
-        gu = torch.empty(rows.size, 2 * EFF, device="cuda")
-        K.mb200_gemm_q4k_f16(d_exp[e * stride:], xe, gu, rows.size, 2 * EFF, H)
-        act = (torch.nn.functional.silu(gu[:, :EFF]) * gu[:, EFF:] / 16).half().contiguous()
-        dn = torch.empty(rows.size, H, device="cuda")
-        (K.mb200_gemm_q6k_f16 if down_type == 14 else K.mb200_gemm_q4k_f16)(d_exp[e * stride + g + u:], act, dn,
-                                                                             rows.size, H, EFF)
-        wv = torch.from_numpy(wts[rows, slots]).cuda()[:, None] * 16
-        acc.index_add_(0, torch.from_numpy(rows).cuda(), dn * wv)
-    composed = host(acc).astype(np.float64)
-    d2 = np.linalg.norm((got - res) - composed, axis=1) / np.linalg.norm(composed, axis=1)
-    assert float(d2.max()) <= 2e-4, float(d2.max())
+
+def test_moe_prefill_at_the_benchmark_shape(K):
+    """The grouped prefill configuration itself: 512 tokens routed top-8 over 128 experts (hidden 4096,
+    intermediate 1536, Q6_K down) by a seeded router, every token row against the oracle's per-token
+    expert sequence."""
+    from mnemocuda_b200.moe import MoEShape, ResidentMoE
+    s = MoEShape()
+    moe = ResidentMoE(s, 1, "cuda", seed=21)
+    M, k = 512, s.K
+    x = synth.normal_f16(901, M * s.H).reshape(M, s.H)
+    res = synth.normal_f32(902, M * s.H).reshape(M, s.H)
+    d_x = dev(x)
+    top = torch.topk(d_x.float() @ moe.router[0].T, k, dim=1)
+    ids_t = top.indices.int().contiguous()
+    wts_t = torch.softmax(top.values, dim=1).contiguous()
+    ids, wts = host(ids_t), host(wts_t)
+    experts = moe.experts[0].reshape(-1).cpu().numpy()
+    want = _moe_prefill_oracle(experts, s.stride, s.gate_sz, s.up_sz, s.down_type, s.H, s.EFF, x, ids, wts, res)
+    n = K.mb200_moe_prefill_workspace_bytes(M, k, s.H, s.EFF, s.NE)
+    ws = torch.empty(n + 256, dtype=torch.uint8, device="cuda")
+    ws = ws[(256 - ws.data_ptr() % 256) % 256:]
+    y = torch.full((M, s.H), float("nan"), device="cuda")
+    cnt = np.bincount(ids.reshape(-1), minlength=s.NE)
+    for cap in (0, int(cnt.max())):  # sized for M tokens per expert, and sized exactly
+        y.fill_(float("nan"))
+        K.mb200_moe_prefill(moe.experts[0], s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE, k, s.H, s.EFF, d_x, ids_t,
+                            wts_t, dev(res), y, M, cap, ws)
+        got = host(y).astype(np.float64)
+        assert np.all(np.isfinite(got))
+        moe_ref = want - res
+        rel = np.linalg.norm((got - res) - moe_ref, axis=1) / np.linalg.norm(moe_ref, axis=1)
+        assert float(rel.max()) <= 1e-3, (cap, float(rel.max()))
+    assert K.mb200_device_error() == 0
 
 
 def test_device_error_word_is_raised_and_can_be_cleared(K):
