@@ -315,7 +315,11 @@ def run_ours(args):
         # expert-sharded: this rank holds experts [lo, hi) of every layer; the router is replicated
         from mnemocuda_b200.sharded import ShardedMoE, expert_range
         moe = ResidentMoE(shape, layers, dev, seed=1, expert_range=expert_range(shape.NE, world, rank))
-        smoe = ShardedMoE(moe, rank, world)
+        comm = None
+        if args.collective == "push":
+            from mnemocuda_b200.peer import PeerComm
+            comm = PeerComm(rank, world, 8192)  # pieces up to 32 KB
+        smoe = ShardedMoE(moe, rank, world, comm=comm)
     else:
         moe = ResidentMoE(shape, layers, dev, seed=1)
     K.mb200_set_pdl(not args.no_pdl)
@@ -392,6 +396,46 @@ def run_ours(args):
         e2e_ms = float(t.item())
     e2e_value = shape.algorithmic_bytes / (e2e_ms * 1e-3) / 1e9
 
+    # ---- N > 1: the other collective variant of the block, and the row-sharded matvec + all-gather ----
+    sharded_extra = None
+    if world > 1:
+        from mnemocuda_b200.sharded import RowShardedMatvec, row_range
+        sharded_extra = {}
+        other = ShardedMoE(moe, rank, world, comm=None)
+        if comm is not None:  # the NCCL all-reduce baseline for the same block
+            blk2 = lambda i: other.forward(i % layers, xs[i % n_x], rs[i % n_x], outs[i % n_x])
+            try:
+                m2, _ = timer.graph(blk2, args.steps, args.warmup, replays=5)
+            except Exception:
+                torch.cuda.synchronize()
+                m2, _ = timer.eager(blk2, args.steps, args.warmup)
+            t = torch.tensor([m2], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sharded_extra["moe_block_nccl_allreduce_ms"] = float(t.item())
+        # the single Q4_K 8192 x 4096 matvec of the benchmark spec, rows split over the ranks, output all-gathered
+        rows, cols, copies = 8192, 4096, 32
+        rl, rh = row_range(rows, world, rank)
+        rb = cols // 256 * 144
+        wl = torch.empty(copies * (rh - rl) * rb, dtype=torch.uint8, device=dev)
+        K.mb200_fill_q4k(wl, copies * (rh - rl) * cols // 256, 50 + rank)
+        yv = torch.empty(rows, device=dev)
+        for name, cm in (("push_allgather", comm), ("nccl_allgather", None)):
+            if name == "push_allgather" and comm is None:
+                continue
+            mvs = [RowShardedMatvec(wl[i * (rh - rl) * rb:(i + 1) * (rh - rl) * rb], rows, cols, rank, world, "q4k", cm)
+                   for i in range(copies)]
+            f = lambda i: mvs[i % copies].forward(xs[i % n_x], yv)
+            try:
+                m3, _ = timer.graph(f, max(args.steps, 2 * copies), args.warmup, replays=5)
+            except Exception:
+                torch.cuda.synchronize()
+                m3, _ = timer.eager(f, max(args.steps, 2 * copies), args.warmup)
+            t = torch.tensor([m3], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            by = rows * rb + 4 * (rows + cols)
+            sharded_extra["row_sharded_q4k_8192x4096_" + name] = {"ms": float(t.item()), "GBs": by / float(t.item()) / 1e6}
+        del wl, mvs
+
     err = K.mb200_device_error()
     if err != 0:
         raise RuntimeError(f"a kernel reported device error {err}")
@@ -422,6 +466,8 @@ def run_ours(args):
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms else None
     per_rank_gb = moe.experts.numel() / 1e9
     launches_per_step = ((1 if args.fused_mode == 2 else 2) if fused or (world > 1 and not args.no_fused) else 3)
+    if world > 1 and args.collective == "push":
+        launches_per_step += 1  # the push all-reduce kernel
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "ms_per_step_min": ms_min, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -430,7 +476,9 @@ def run_ours(args):
                    "l2": (f"inputs larger than L2: steps rotate over {layers} resident layers and {n_x} activation vectors; "
                           f"{per_rank_gb:.1f} GB of expert weights per rank, any of which a step may route to"),
                    "timing": timing_how, "pdl": not args.no_pdl,
-                   "parallelism": (f"experts sharded {world}-way (router replicated), NCCL all-reduce of the 16 KB partial hidden vector"
+                   "parallelism": (f"experts sharded {world}-way (router replicated), "
+                                   + ("push all-reduce of the 16 KB partial hidden vector over NVLink peer memory (one kernel per rank)"
+                                      if args.collective == "push" else "NCCL all-reduce of the 16 KB partial hidden vector")
                                    if world > 1 else "single GPU")},
         "clocks": clk.summary(),
         "gpu_launches": launches_per_step * args.steps,
@@ -445,6 +493,8 @@ def run_ours(args):
             line["roofline"]["expert_phases_alone"] = {
                 "ms": fu_ms, "achieved": (gu_bytes + dn_bytes) / (fu_ms * 1e-3) / 1e9,
                 "frac": (gu_bytes + dn_bytes) / (fu_ms * 1e-3) / 1e9 / peak, "algorithmic_bytes_per_launch": gu_bytes + dn_bytes}
+    if sharded_extra:
+        line["sharded"] = sharded_extra
     line["e2e"] = {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": host_block.h2d_bytes,
                    "d2h_bytes_per_step": host_block.d2h_bytes}
     if world == 1 and not args.no_cpu_baseline:
@@ -579,6 +629,8 @@ def main():
     ap.add_argument("--workload", default="moe_block",
                     choices=["moe_block", "matvec", "gemm", "prefill", "decode30b", "decode235b"],
                     help="moe_block is the headline; the others print a secondary line for the same path")
+    ap.add_argument("--collective", default="push", choices=["push", "nccl"],
+                    help="N > 1: how the partial hidden vectors are summed (push: this library's peer-memory kernel)")
     ap.add_argument("--no-extras", action="store_true",
                     help="headline only: skip the matvec and whole-token decode sections of the JSON line")
     ap.add_argument("--decode-tokens", type=int, default=8, help="tokens per timed CUDA graph of the decode section")

@@ -366,6 +366,33 @@ int mb200_decode_layer(const mb200_decode_model *m, int layer, void *workspace, 
 int mb200_decode_finish(const mb200_decode_model *m, void *workspace, float *d_logits, int *d_token, int *d_pos,
                         cudaStream_t stream);
 
+/* ---- push collectives over NVLink peer memory (one process per GPU) ----
+ * These replace the reference's only inter-GPU traffic, the hidden-vector copy at a layer-range boundary
+ * (src/forward.c:1555-1581, src/engine.c:1238-1262), for a model whose matvec rows and experts are sharded
+ * over the GPUs: the pieces are 16-32 KB, so the collectives are latency-bound, and every rank stores its
+ * piece straight into every peer's receive buffer (plain peer stores), raises an arrival counter there, and
+ * the receiver sums (all-reduce, in rank order: deterministic and identical on all ranks) or concatenates
+ * (all-gather) once all pieces are in. All ranks must issue the same sequence of collectives on a comm.
+ * A wait that is not satisfied within ~2 s raises the device error word (MB200_ERR_TIMEOUT) and the kernel
+ * returns; nothing hangs. Legal inside stream capture (the sequence number lives in device memory).
+ *
+ * Set-up (not capturable): each rank calls mb200_comm_alloc (cudaMalloc + zero + CUDA IPC handle), the 64-byte
+ * handles of all ranks are exchanged by the caller (MPI, torch.distributed, a file ...), and
+ * mb200_comm_create opens the peers' buffers. ipc_handles_64 = world * 64 bytes, rank order. */
+size_t mb200_comm_buffer_bytes(int world, size_t max_floats);
+int mb200_comm_alloc(int world, size_t max_floats, void **dev_ptr, void *ipc_handle_64);
+int mb200_comm_create(int rank, int world, size_t max_floats, void *local_ptr, const void *ipc_handles_64,
+                      void **comm_out);
+/* The same for ONE process that drives all GPUs itself (the reference engine's model, src/forward.c:606):
+ * bases[q] = rank q's buffer (mb200_comm_buffer_bytes bytes, zeroed, on device q with peer access enabled
+ * from the device of `rank`); one comm per rank. */
+int mb200_comm_create_ptrs(int rank, int world, size_t max_floats, void *const *bases, void **comm_out);
+void mb200_comm_destroy(void *comm, int free_local);
+/* out[i] = sum over ranks q = 0..world-1 of in_q[i]; n a multiple of 4, n <= max_floats; in / out 16-byte aligned. */
+int mb200_push_allreduce(void *comm, const float *in, float *out, int n, cudaStream_t stream);
+/* out[q * n_per_rank + i] = in_q[i] (equal-sized pieces). */
+int mb200_push_allgather(void *comm, const float *in, float *out, int n_per_rank, cudaStream_t stream);
+
 /* Seeded synthetic tensors written on the device (benchmark workloads). */
 int mb200_fill_q4k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream);
 int mb200_fill_q6k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream);

@@ -73,6 +73,13 @@ SIGNATURES = {
     "mb200_decode_begin": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "mb200_decode_layer": (_i, [_vp, _i, _vp, _vp, _vp]),
     "mb200_decode_finish": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "mb200_comm_buffer_bytes": (_sz, [_i, _sz]),
+    "mb200_comm_alloc": (_i, [_i, _sz, _vp, _vp]),
+    "mb200_comm_create": (_i, [_i, _i, _sz, _vp, _vp, _vp]),
+    "mb200_comm_create_ptrs": (_i, [_i, _i, _sz, _vp, _vp]),
+    "mb200_comm_destroy": (None, [_vp, _i]),
+    "mb200_push_allreduce": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "mb200_push_allgather": (_i, [_vp, _vp, _vp, _i, _vp]),
     "mb200_fill_q4k": (_i, [_vp, _sz, _u64, _vp]),
     "mb200_fill_q6k": (_i, [_vp, _sz, _u64, _vp]),
     "mb200_fill_normal_f32": (_i, [_vp, _sz, _u64, _f, _vp]),

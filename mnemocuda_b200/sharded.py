@@ -68,20 +68,51 @@ def allreduce_partial(partial: torch.Tensor, group=None) -> torch.Tensor:
 
 class ShardedMoE:
     """Expert-sharded MoE block on this rank's GPU. `moe` is a ResidentMoE built with
-    expert_range=expert_range(NE, world, rank)."""
+    expert_range=expert_range(NE, world, rank). The partial hidden vectors are summed either by the push
+    all-reduce over peer memory (`comm`, a peer.PeerComm: one kernel per rank, the pieces stored straight
+    into the peers' buffers) or, without one, by an NCCL all-reduce (the baseline)."""
 
-    def __init__(self, moe, rank: int, world: int):
+    def __init__(self, moe, rank: int, world: int, comm=None):
         from . import kernels as K
-        self.K, self.moe, self.rank, self.world = K, moe, rank, world
+        self.K, self.moe, self.rank, self.world, self.comm = K, moe, rank, world, comm
         self.lo, self.cnt = moe.expert_lo, moe.n_local
         self.zero = torch.zeros(moe.shape.H, dtype=torch.float32, device=moe.device)
+        self.partial = torch.zeros(moe.shape.H, dtype=torch.float32, device=moe.device)
 
     def forward(self, layer: int, x: torch.Tensor, residual: torch.Tensor, out: torch.Tensor, reduce=True) -> None:
         """This rank's partial block (one launch where the fused kernel covers the shape), then the all-reduce."""
         s, m, K = self.moe.shape, self.moe, self.K
         res = residual if self.rank == 0 else self.zero
+        push = reduce and self.world > 1 and self.comm is not None
+        dst = self.partial if push else out
         K.mb200_moe_block_local(m.router[layer], m.experts[layer], s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE,
-                                self.lo, self.cnt, s.K, s.H, s.EFF, x, res, out, m.ids[layer], m.wts[layer], m.act,
+                                self.lo, self.cnt, s.K, s.H, s.EFF, x, res, dst, m.ids[layer], m.wts[layer], m.act,
                                 m.scratch)
-        if reduce and self.world > 1:
+        if push:
+            self.comm.allreduce(self.partial, out)
+        elif reduce and self.world > 1:
             allreduce_partial(out)
+
+
+class RowShardedMatvec:
+    """A Q4_K / Q6_K matvec split by output rows over the ranks: this rank holds rows [lo, hi) of the tensor
+    (a contiguous byte range of the GGUF tensor) and computes that slice of y; the slices are all-gathered
+    by the push collective (`comm`) or by NCCL. n_rows must divide evenly for the push path."""
+
+    def __init__(self, weights_local: torch.Tensor, n_rows: int, n_cols: int, rank: int, world: int, kind: str = "q4k",
+                 comm=None):
+        from . import kernels as K
+        self.K, self.w, self.n_rows, self.n_cols, self.rank, self.world, self.comm = K, weights_local, n_rows, n_cols, rank, world, comm
+        self.lo, self.hi = row_range(n_rows, world, rank)
+        self.call = K.cuda_matvec_q4k if kind == "q4k" else K.cuda_matvec_q6k
+        self.y_local = torch.empty(self.hi - self.lo, dtype=torch.float32, device=weights_local.device)
+        self.even = n_rows % world == 0 and (n_rows // world) % 4 == 0
+
+    def forward(self, x: torch.Tensor, y: torch.Tensor) -> None:
+        self.call(self.w, x, self.y_local, self.hi - self.lo, self.n_cols)
+        if self.world == 1:
+            y.copy_(self.y_local)
+        elif self.comm is not None and self.even:
+            self.comm.allgather(self.y_local, y)
+        else:
+            y.copy_(allgather_rows(self.y_local, self.n_rows))

@@ -88,3 +88,35 @@ def test_world_size_2_gloo_shards_reassemble():
     for rank, err_moe, gathered_ok in results:
         assert err_moe < 1e-5, (rank, err_moe)  # fp32 reassociation of the expert sum only
         assert gathered_ok
+
+
+def _handle_worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from mnemocuda_b200.peer import exchange_handles
+    mine = bytes([rank + 1]) * 64
+    got = exchange_handles(mine)
+    ok = got == [bytes([r + 1]) * 64 for r in range(world)]
+    try:
+        exchange_handles(b"short")
+        ok = False
+    except ValueError:
+        pass
+    q.put((rank, ok))
+    dist.destroy_process_group()
+
+
+def test_ipc_handle_exchange_over_gloo():
+    """The 64-byte buffer handles of the push collectives travel through torch.distributed in rank order."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    world = 2
+    procs = [ctx.Process(target=_handle_worker, args=(r, world, 29611, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+    assert res == [(0, True), (1, True)]
