@@ -370,9 +370,9 @@ int mb200_decode_finish(const mb200_decode_model *m, void *workspace, float *d_l
  * These replace the reference's only inter-GPU traffic, the hidden-vector copy at a layer-range boundary
  * (src/forward.c:1555-1581, src/engine.c:1238-1262), for a model whose matvec rows and experts are sharded
  * over the GPUs: the pieces are 16-32 KB, so the collectives are latency-bound, and every rank stores its
- * piece straight into every peer's receive buffer (plain peer stores), raises an arrival counter there, and
- * the receiver sums (all-reduce, in rank order: deterministic and identical on all ranks) or concatenates
- * (all-gather) once all pieces are in. All ranks must issue the same sequence of collectives on a comm.
+ * piece straight into every peer's receive buffer (plain 8-byte peer stores, each carrying the collective's
+ * sequence number beside the value, so no fence or flag follows), and the receiver sums (all-reduce, in rank
+ * order: deterministic and identical on all ranks) or concatenates (all-gather) the pieces as they land. All ranks must issue the same sequence of collectives on a comm.
  * A wait that is not satisfied within ~2 s raises the device error word (MB200_ERR_TIMEOUT) and the kernel
  * returns; nothing hangs. Legal inside stream capture (the sequence number lives in device memory).
  *
@@ -388,7 +388,7 @@ int mb200_comm_create(int rank, int world, size_t max_floats, void *local_ptr, c
  * from the device of `rank`); one comm per rank. */
 int mb200_comm_create_ptrs(int rank, int world, size_t max_floats, void *const *bases, void **comm_out);
 void mb200_comm_destroy(void *comm, int free_local);
-/* out[i] = sum over ranks q = 0..world-1 of in_q[i]; n a multiple of 4, n <= max_floats; in / out 16-byte aligned. */
+/* out[i] = sum over ranks q = 0..world-1 of in_q[i]; n <= max_floats. */
 int mb200_push_allreduce(void *comm, const float *in, float *out, int n, cudaStream_t stream);
 /* out[q * n_per_rank + i] = in_q[i] (equal-sized pieces). */
 int mb200_push_allgather(void *comm, const float *in, float *out, int n_per_rank, cudaStream_t stream);

@@ -4,15 +4,17 @@
 // boundary (cudaMemcpyPeerAsync, src/forward.c:1555-1581). Sharding the work itself (rows of a matvec,
 // experts of a MoE block) needs an all-gather / all-reduce of 16-32 KB several times per layer: far too
 // small for a bandwidth-oriented collective, so the cost is latency. Here every rank STORES its piece
-// straight into every peer's receive buffer (plain 16-byte peer stores through NVSwitch; no bulk / TMA
-// copy and no multicast touches peer memory), then raises a per-source arrival counter on the peer with
-// a system-scope release; the receiver spins on its own local counters (bounded), then sums the pieces
-// in rank order -- deterministic, identical on every rank -- or just concatenates them (all-gather).
+// straight into every peer's receive buffer (plain 8-byte peer stores through NVSwitch; no bulk / TMA
+// copy and no multicast touches peer memory). Every float travels with the collective's sequence number
+// in the same 8-byte store, so the receiver needs no fence and no separate flag: it spins on its own
+// local cells (bounded) until they carry the number, then sums the pieces in rank order -- deterministic,
+// identical on every rank -- or just concatenates them (all-gather). One one-way NVLink trip per piece.
 //
 // One process per GPU. Buffers are cudaMalloc'ed here and shared through CUDA IPC handles that the host
 // side exchanges (torch.distributed, or anything else); the library itself never talks to other ranks.
-// Receive slots are double-buffered by the parity of a sequence number kept in device memory (so a CUDA
-// graph that contains the call can be replayed), counters only grow, and a wait that runs out of its
+// Receive cells are double-buffered by the parity of the sequence number, which is kept in device memory
+// (so a CUDA graph that contains the call can be replayed); a rank can be at most one collective ahead of
+// the slowest one, so a cell is never overwritten before it has been read. A wait that runs out of its
 // budget raises the device error word (MB200_ERR_TIMEOUT) and returns instead of hanging.
 #include <cstdio>
 #include <cstring>
@@ -25,17 +27,18 @@ int pdl_enabled();
 namespace {
 
 constexpr int kMaxWorld = 8;
-constexpr int kPushCtas = 4;        // CTAs of a collective launch; each raises every peer's counter once
+constexpr int kPushCtas = 8;
 constexpr int kPushThreads = 256;
 constexpr long long kSpinBudgetNs = 2000000000ll;  // 2 s of wall clock, then MB200_ERR_TIMEOUT
 
-// Receive area of one rank: [2 parities][world sources][max_floats] payload, then the arrival counters
-// [2][world] (64-bit, only ever incremented), then the sequence word and a launch ticket.
+// Receive area of one rank: [2 parities][world sources][max_floats] cells of 8 bytes -- a float and the
+// 32-bit sequence number of the collective that wrote it, stored together with ONE 8-byte store (single-copy
+// atomic, also across NVLink), so a cell whose number matches is valid: no fence, no separate flag, one
+// one-way trip per piece. Then the sequence word and a launch ticket (local use).
 struct CommBuf {
-    float *slots;
-    unsigned long long *arrived;
-    unsigned long long *seq;     // sequence number of the last completed collective (local use)
-    unsigned int *ticket;        // CTAs of the running launch that have finished (local use)
+    uint2 *cells;
+    unsigned long long *seq;     // sequence number of the last completed collective
+    unsigned int *ticket;        // CTAs of the running launch that have finished
 };
 
 struct Comm {
@@ -47,44 +50,56 @@ struct Comm {
     CommBuf buf[kMaxWorld];
 };
 
-size_t slots_bytes(int world, size_t max_floats) { return 2 * (size_t)world * max_floats * sizeof(float); }
-size_t comm_bytes(int world, size_t max_floats)
-{
-    return slots_bytes(world, max_floats) + 2 * (size_t)world * 8 + 64;
-}
+size_t cells_bytes(int world, size_t max_floats) { return 2 * (size_t)world * max_floats * sizeof(uint2); }
+size_t comm_bytes(int world, size_t max_floats) { return cells_bytes(world, max_floats) + 64; }
 CommBuf carve(void *base, int world, size_t max_floats)
 {
     CommBuf b;
     uint8_t *p = static_cast<uint8_t *>(base);
-    b.slots = reinterpret_cast<float *>(p);
-    b.arrived = reinterpret_cast<unsigned long long *>(p + slots_bytes(world, max_floats));
-    b.seq = b.arrived + 2 * world;
+    b.cells = reinterpret_cast<uint2 *>(p);
+    b.seq = reinterpret_cast<unsigned long long *>(p + cells_bytes(world, max_floats));
     b.ticket = reinterpret_cast<unsigned int *>(b.seq + 1);
     return b;
 }
 
 struct PushParams {
     CommBuf self;
-    float *peer_slots[kMaxWorld];
-    unsigned long long *peer_arrived[kMaxWorld];
+    uint2 *peer_cells[kMaxWorld];
     int rank, world;
     size_t max_floats;
     const float *in;   // this rank's piece
     float *out;        // all-reduce: [n]; all-gather: [world * n] (piece of rank q at q * n)
-    int n;             // floats per piece (multiple of 4)
+    int n;             // floats per piece
     int reduce;        // 1: sum of the pieces in rank order; 0: concatenation
     int *err;
 };
 
-__device__ __forceinline__ void st_release_sys_add(unsigned long long *p)
+__device__ __forceinline__ void st_cell(uint2 *p, float v, uint32_t tag)
 {
-    asm volatile("red.release.sys.global.add.u64 [%0], 1;" ::"l"(p) : "memory");
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
 }
-__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long *p)
+__device__ __forceinline__ uint2 ld_cell(const uint2 *p)
 {
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
+}
+
+// Spins until the cell carries `tag`; false once the time budget is spent.
+__device__ __forceinline__ bool wait_cell(const uint2 *p, uint32_t tag, float &v, long long t0)
+{
+    for (unsigned it = 0;; it++) {
+        const uint2 c = ld_cell(p);
+        if (c.y == tag) {
+            v = __uint_as_float(c.x);
+            return true;
+        }
+        if ((it & 255) == 255) {
+            long long t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > kSpinBudgetNs) return false;
+        }
+    }
 }
 
 __global__ void __launch_bounds__(kPushThreads) push_collective_kernel(const PushParams P)
@@ -93,73 +108,40 @@ __global__ void __launch_bounds__(kPushThreads) push_collective_kernel(const Pus
     // the producer of `in`
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    __shared__ int ok_flag;
-    const int tid = threadIdx.x;
+    const int tid = blockIdx.x * kPushThreads + threadIdx.x, nthr = gridDim.x * kPushThreads;
     const unsigned long long seq = __ldcg(P.self.seq) + 1;  // the same on every CTA: written only by the last CTA of a launch
-    const int par = static_cast<int>(seq & 1);
-    const int n4 = P.n >> 2;
-    // ---- push: this CTA's share of the piece into every rank's slot for (parity, source = this rank) ----
-    const int per = (n4 + gridDim.x - 1) / gridDim.x;
-    const int lo = blockIdx.x * per, hi = min(n4, lo + per);
-    const float4 *src = reinterpret_cast<const float4 *>(P.in);
-    for (int p = 0; p < P.world; p++) {
-        float4 *dst = reinterpret_cast<float4 *>(P.peer_slots[p] + ((size_t)par * P.world + P.rank) * P.max_floats);
-        for (int i = lo + tid; i < hi; i += kPushThreads) dst[i] = __ldcg(src + i);
+    const uint32_t tag = static_cast<uint32_t>(seq);        // never 0 in the first 2^32 collectives; the buffers start zeroed
+    const size_t par_off = (size_t)(seq & 1) * P.world * P.max_floats;
+    // ---- push: element i of this rank's piece into cell (parity, source = this rank, i) of every rank ----
+    for (int i = tid; i < P.n; i += nthr) {
+        const float v = __ldcg(P.in + i);
+#pragma unroll 1
+        for (int p = 0; p < P.world; p++) st_cell(P.peer_cells[p] + par_off + (size_t)P.rank * P.max_floats + i, v, tag);
     }
-    __threadfence_system();  // the stores above are performed system-wide before the counters move
-    __syncthreads();
-    if (tid < P.world) st_release_sys_add(P.peer_arrived[tid] + (size_t)par * P.world + P.rank);
-    // ---- wait until every source's gridDim.x CTAs have arrived for this sequence number (bounded) ----
-    // sequence numbers of one parity are seq, seq - 2, ...: the counter of (parity, source) must reach
-    // gridDim.x * ceil(seq / 2)
-    if (tid == 0) ok_flag = 1;
-    __syncthreads();
-    if (tid < P.world) {
-        const unsigned long long target = static_cast<unsigned long long>(gridDim.x) * ((seq + 1) >> 1);
-        const unsigned long long *ctr = P.self.arrived + (size_t)par * P.world + tid;
-        long long t0;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-        bool ok = false;
-        for (unsigned it = 0;; it++) {
-            if (ld_acquire_sys(ctr) >= target) {
-                ok = true;
+    // ---- receive: the same elements from every source, as they land ----
+    long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    bool ok = true;
+    const uint2 *mine = P.self.cells + par_off;
+    for (int i = tid; i < P.n && ok; i += nthr) {
+        float acc = 0.0f;
+        for (int q = 0; q < P.world; q++) {  // fixed order: every rank computes the same bits
+            float v;
+            if (!wait_cell(mine + (size_t)q * P.max_floats + i, tag, v, t0)) {
+                ok = false;
                 break;
             }
-            if ((it & 63) == 63) {
-                long long t1;
-                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-                if (t1 - t0 > kSpinBudgetNs) break;
-            }
+            if (P.reduce)
+                acc = q == 0 ? v : acc + v;
+            else
+                P.out[(size_t)q * P.n + i] = v;
         }
-        if (!ok) {
-            ok_flag = 0;
-            atomicExch(P.err, MB200_ERR_TIMEOUT);
-        }
+        if (ok && P.reduce) P.out[i] = acc;
     }
-    __syncthreads();
-    if (ok_flag) {
-        const float *slots = P.self.slots + (size_t)par * P.world * P.max_floats;
-        if (P.reduce) {
-            float4 *out = reinterpret_cast<float4 *>(P.out);
-            for (int i = lo + tid; i < hi; i += kPushThreads) {
-                float4 a = __ldcg(reinterpret_cast<const float4 *>(slots) + i);
-                for (int q = 1; q < P.world; q++) {  // fixed order: every rank computes the same bits
-                    const float4 b = __ldcg(reinterpret_cast<const float4 *>(slots + (size_t)q * P.max_floats) + i);
-                    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
-                }
-                out[i] = a;
-            }
-        } else {
-            for (int q = 0; q < P.world; q++) {
-                float4 *out = reinterpret_cast<float4 *>(P.out + (size_t)q * P.n);
-                for (int i = lo + tid; i < hi; i += kPushThreads)
-                    out[i] = __ldcg(reinterpret_cast<const float4 *>(slots + (size_t)q * P.max_floats) + i);
-            }
-        }
-    }
+    if (!ok) atomicExch(P.err, MB200_ERR_TIMEOUT);
     // ---- the last CTA to finish publishes the sequence number for the next launch ----
     __syncthreads();
-    if (tid == 0) {
+    if (threadIdx.x == 0) {
         __threadfence();
         if (atomicAdd(P.self.ticket, 1u) == gridDim.x - 1) {
             *P.self.ticket = 0;
@@ -172,14 +154,10 @@ __global__ void __launch_bounds__(kPushThreads) push_collective_kernel(const Pus
 
 int launch_push(Comm *c, const float *in, float *out, int n, int reduce, cudaStream_t stream)
 {
-    if (!c || !in || !out || n < 4 || (n & 3) || static_cast<size_t>(n) > c->max_floats) return MB200_ERR_ARG;
-    if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) return MB200_ERR_ARG;
+    if (!c || !in || !out || n < 1 || static_cast<size_t>(n) > c->max_floats) return MB200_ERR_ARG;
     PushParams P{};
     P.self = c->buf[c->rank];
-    for (int p = 0; p < c->world; p++) {
-        P.peer_slots[p] = c->buf[p].slots;
-        P.peer_arrived[p] = c->buf[p].arrived;
-    }
+    for (int p = 0; p < c->world; p++) P.peer_cells[p] = c->buf[p].cells;
     P.rank = c->rank;
     P.world = c->world;
     P.max_floats = c->max_floats;
@@ -189,7 +167,9 @@ int launch_push(Comm *c, const float *in, float *out, int n, int reduce, cudaStr
     P.reduce = reduce;
     P.err = device_error_word();
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(kPushCtas);
+    int ctas = (n + kPushThreads * 2 - 1) / (kPushThreads * 2);  // two elements per thread
+    ctas = ctas < 1 ? 1 : (ctas > kPushCtas ? kPushCtas : ctas);
+    cfg.gridDim = dim3(ctas);
     cfg.blockDim = dim3(kPushThreads);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];

@@ -106,7 +106,7 @@ class RowShardedMatvec:
         self.lo, self.hi = row_range(n_rows, world, rank)
         self.call = K.cuda_matvec_q4k if kind == "q4k" else K.cuda_matvec_q6k
         self.y_local = torch.empty(self.hi - self.lo, dtype=torch.float32, device=weights_local.device)
-        self.even = n_rows % world == 0 and (n_rows // world) % 4 == 0
+        self.even = n_rows % world == 0
 
     def forward(self, x: torch.Tensor, y: torch.Tensor) -> None:
         self.call(self.w, x, self.y_local, self.hi - self.lo, self.n_cols)
