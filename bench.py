@@ -265,7 +265,7 @@ def measure_matvec(torch, K, dev, timer, hbm, steps, warmup):
     return out
 
 
-def measure_decode(torch, K, dev, timer, hbm, which, tokens, expert_range=None, n_layers=None):
+def measure_decode(torch, K, dev, timer, hbm, which, tokens, n_layers=None, rank=0, world=1, comm=None):
     """Whole-token decode of a model shape resident in HBM: `tokens` tokens in one CUDA graph at the last
     position of the context (KV cache pre-filled up to it), replayed 5 times."""
     from mnemocuda_b200.decode import DecodeConfig, ResidentModel
@@ -273,7 +273,7 @@ def measure_decode(torch, K, dev, timer, hbm, which, tokens, expert_range=None, 
     if n_layers:
         cfg.n_layers = n_layers  # a slice of the model (profiling captures): same per-layer work
     t0 = time.perf_counter()
-    model = ResidentModel(cfg, dev, seed=1, expert_range=expert_range)
+    model = ResidentModel(cfg, dev, seed=1, rank=rank, world=world, comm=comm)
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t0
     model.set_state(1, cfg.ctx_len - 1)
@@ -281,13 +281,21 @@ def measure_decode(torch, K, dev, timer, hbm, which, tokens, expert_range=None, 
     g.replay()
     torch.cuda.synchronize()
     med, mn = timer.replays(g, tokens, replays=5)
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([med, mn], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        med, mn = float(t[0].item()), float(t[1].item())
     by = cfg.algorithmic_bytes_per_token()
     res = {"config": (f"{cfg.name} decode, batch 1, context {cfg.ctx_len} (position {cfg.ctx_len - 1}), {cfg.n_layers} layers, "
-                      f"{cfg.n_experts} experts top-{cfg.top_k}, Q4_K_M-style types, all experts resident"),
+                      f"{cfg.n_experts} experts top-{cfg.top_k}, Q4_K_M-style types, all experts resident"
+                      + (f"; heads, output-projection / lm_head rows and experts sharded {world}-way, push all-gather / "
+                         f"all-reduce over NVLink peer memory" if world > 1 else "")),
            "tok_s": 1e3 / med, "ms_per_token": med, "ms_per_token_min": mn, "bytes_per_token": by,
-           "GBs": by / med / 1e6, "frac": by / med / 1e6 / hbm, "resident_GB": round(cfg.resident_bytes() / 1e9, 1),
-           "tokens_per_graph": tokens, "launches_per_token": 2 + 8 * cfg.n_layers + 3, "build_s": round(build_s, 1),
-           "sampled_token": int(model.token.item())}
+           "GBs": by / med / 1e6, "frac": by / med / 1e6 / (hbm * world), "frac_of": f"{world} x measured copy bandwidth",
+           "resident_GB_per_rank": round(cfg.resident_bytes(cfg.n_experts // world) / 1e9, 1),
+           "tokens_per_graph": tokens, "launches_per_token": 2 + (8 if world == 1 else 11) * cfg.n_layers + (3 if world == 1 else 4),
+           "build_s": round(build_s, 1), "sampled_token": int(model.token.item())}
     del model, g
     torch.cuda.empty_cache()
     return res
@@ -435,6 +443,15 @@ def run_ours(args):
             by = rows * rb + 4 * (rows + cols)
             sharded_extra["row_sharded_q4k_8192x4096_" + name] = {"ms": float(t.item()), "GBs": by / float(t.item()) / 1e6}
         del wl, mvs
+        # whole-token decode with the model sharded over the ranks (needs the push collectives)
+        if comm is not None and not args.no_extras:
+            del moe, smoe, other
+            torch.cuda.empty_cache()
+            sharded_extra["decode"] = {}
+            for which_model in ("30b", "235b"):
+                sharded_extra["decode"][which_model] = measure_decode(torch, K, dev, timer, measured_peaks()[0], which_model,
+                                                                      args.decode_tokens, rank=rank, world=world, comm=comm)
+            moe = None
 
     err = K.mb200_device_error()
     if err != 0:
@@ -464,7 +481,7 @@ def run_ours(args):
         dom_name = "stream_kernel<Q4,*> (routed gate/up + SwiGLU, 8 experts per launch)"
         dom_bytes, dom_ms, dom_traffic = gu_bytes, gu_ms, GATE_UP_TRAFFIC_BYTES
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms else None
-    per_rank_gb = moe.experts.numel() / 1e9
+    per_rank_gb = (shape.NE // world) * layers * shape.stride / 1e9
     launches_per_step = ((1 if args.fused_mode == 2 else 2) if fused or (world > 1 and not args.no_fused) else 3)
     if world > 1 and args.collective == "push":
         launches_per_step += 1  # the push all-reduce kernel

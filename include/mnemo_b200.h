@@ -344,7 +344,12 @@ typedef struct mb200_decode_model {
     const mb200_layer_weights *layers;      /* host array [n_layers] */
     const void *token_embd;                 /* Q4_K [vocab x hidden] */
     const float *output_norm;               /* [hidden] */
-    const void *lm_head;                    /* [vocab x hidden], lm_head_type */
+    const void *lm_head;                    /* [vocab x hidden], lm_head_type (a sharded rank: its rows, see below) */
+    /* A rank of a model sharded over devices describes ITS SHARD above (n_heads / n_kv_heads = the heads it
+     * holds, wq / wk / wv / kv_k / kv_v = their rows, wo = rows [o_row0, o_row0 + o_rows) of the output
+     * projection, lm_head = rows [lm_row0, lm_row0 + lm_rows)) and fills these in; all zero = not sharded. */
+    int n_heads_total;                      /* query heads of the whole model (width of the O projection's input) */
+    int o_row0, o_rows, lm_row0, lm_rows;
 } mb200_decode_model;
 
 /* Bytes of device workspace a model needs (256-byte aligned; zero it once before the first token:
@@ -365,6 +370,23 @@ int mb200_decode_layer(const mb200_decode_model *m, int layer, void *workspace, 
                        cudaStream_t stream);
 int mb200_decode_finish(const mb200_decode_model *m, void *workspace, float *d_logits, int *d_token, int *d_pos,
                         cudaStream_t stream);
+/* The layer in three pieces for a model sharded over devices (this replaces the reference's layer-range split,
+ * src/engine.c:761-775): attention over the rank's heads -> attn_local [n_heads * head_dim]; [all-gather];
+ * the rank's rows of the output projection + residual -> hidden_rows [o_rows]; [all-gather into the hidden
+ * state, mb200_decode_hidden]; the rank's experts (+ the residual on the rank that passes add_residual) ->
+ * out [hidden]; [all-reduce into the hidden state]. Then the rank's rows of the lm_head with the best
+ * (logit, vocabulary index) pair of those rows in best_pair[2] (the index as int bits); [all-gather of the
+ * pairs]; mb200_decode_pick writes the token and advances the position. The collectives are the caller's
+ * (mb200_push_allgather / mb200_push_allreduce, or NCCL). */
+int mb200_decode_layer_attn(const mb200_decode_model *m, int layer, void *workspace, const int *d_pos, float *attn_local,
+                            cudaStream_t stream);
+int mb200_decode_layer_oproj(const mb200_decode_model *m, int layer, void *workspace, const float *attn_full,
+                             float *hidden_rows, cudaStream_t stream);
+int mb200_decode_layer_moe(const mb200_decode_model *m, int layer, void *workspace, int add_residual, float *out,
+                           cudaStream_t stream);
+int mb200_decode_logits_local(const mb200_decode_model *m, void *workspace, float *logits_rows, float *best_pair,
+                              cudaStream_t stream);
+int mb200_decode_pick(const float *pairs, int n_pairs, int *d_token, int *d_pos, cudaStream_t stream);
 
 /* ---- push collectives over NVLink peer memory (one process per GPU) ----
  * These replace the reference's only inter-GPU traffic, the hidden-vector copy at a layer-range boundary
@@ -396,6 +418,9 @@ int mb200_push_allgather(void *comm, const float *in, float *out, int n_per_rank
 /* Seeded synthetic tensors written on the device (benchmark workloads). */
 int mb200_fill_q4k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream);
 int mb200_fill_q6k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream);
+/* Blocks [first_block, first_block + n_blocks) of the same stream (a shard of a tensor gets the bytes it has in the whole). */
+int mb200_fill_q4k_at(void *dst, size_t first_block, size_t n_blocks, uint64_t seed, cudaStream_t stream);
+int mb200_fill_q6k_at(void *dst, size_t first_block, size_t n_blocks, uint64_t seed, cudaStream_t stream);
 int mb200_fill_normal_f32(float *dst, size_t n, uint64_t seed, float scale, cudaStream_t stream);
 int mb200_fill_normal_f16(void *dst, size_t n, uint64_t seed, float scale, cudaStream_t stream);
 

@@ -80,6 +80,13 @@ SIGNATURES = {
     "mb200_comm_destroy": (None, [_vp, _i]),
     "mb200_push_allreduce": (_i, [_vp, _vp, _vp, _i, _vp]),
     "mb200_push_allgather": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "mb200_decode_layer_attn": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),
+    "mb200_decode_layer_oproj": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),
+    "mb200_decode_layer_moe": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
+    "mb200_decode_logits_local": (_i, [_vp, _vp, _vp, _vp, _vp]),
+    "mb200_decode_pick": (_i, [_vp, _i, _vp, _vp, _vp]),
+    "mb200_fill_q4k_at": (_i, [_vp, _sz, _sz, _u64, _vp]),
+    "mb200_fill_q6k_at": (_i, [_vp, _sz, _sz, _u64, _vp]),
     "mb200_fill_q4k": (_i, [_vp, _sz, _u64, _vp]),
     "mb200_fill_q6k": (_i, [_vp, _sz, _u64, _vp]),
     "mb200_fill_normal_f32": (_i, [_vp, _sz, _u64, _f, _vp]),

@@ -27,7 +27,7 @@ namespace {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Workspace {
-    size_t hidden, normed, q, k, v, attn, rope, ids, wts, act, scratch, attn_ws, total;
+    size_t hidden, normed, q, k, v, attn, rope, ids, wts, act, scratch, attn_ws, zero, total;
 };
 
 Workspace layout(const mb200_decode_model &m)
@@ -43,6 +43,7 @@ Workspace layout(const mb200_decode_model &m)
     // counters first: the caller zeroes the workspace once, these must start at zero
     w.scratch = take(mb200_router_scratch_bytes(m.n_experts));
     w.attn_ws = take(attn_workspace_bytes(m.n_kv_heads, m.n_heads / (m.n_kv_heads > 0 ? m.n_kv_heads : 1)));
+    w.zero = take(H * 4);  // stays zero: the "residual" of a rank that must not add one
     w.hidden = take(H * 4);
     w.normed = take(H * 4);
     w.q = take(QD * 4);
@@ -78,46 +79,92 @@ int matvec(const void *w, int type, const float *x, float *y, int rows, int cols
     }
 }
 
-int run_layer(const mb200_decode_model &m, const mb200_layer_weights &L, uint8_t *ws, const Workspace &W,
-              const int *d_pos, cudaStream_t s)
+struct Bufs {
+    float *hidden, *normed, *q, *k, *v, *attn, *cos_t, *sin_t;
+};
+Bufs bufs(const mb200_decode_model &m, uint8_t *ws, const Workspace &W)
 {
-    float *hidden = reinterpret_cast<float *>(ws + W.hidden), *normed = reinterpret_cast<float *>(ws + W.normed);
-    float *q = reinterpret_cast<float *>(ws + W.q), *k = reinterpret_cast<float *>(ws + W.k);
-    float *v = reinterpret_cast<float *>(ws + W.v), *attn = reinterpret_cast<float *>(ws + W.attn);
-    float *cos_t = reinterpret_cast<float *>(ws + W.rope), *sin_t = cos_t + m.head_dim / 2;
+    Bufs b;
+    b.hidden = reinterpret_cast<float *>(ws + W.hidden);
+    b.normed = reinterpret_cast<float *>(ws + W.normed);
+    b.q = reinterpret_cast<float *>(ws + W.q);
+    b.k = reinterpret_cast<float *>(ws + W.k);
+    b.v = reinterpret_cast<float *>(ws + W.v);
+    b.attn = reinterpret_cast<float *>(ws + W.attn);
+    b.cos_t = reinterpret_cast<float *>(ws + W.rope);
+    b.sin_t = b.cos_t + m.head_dim / 2;
+    return b;
+}
+
+// Steps 1-6 of forward_layer (src/forward.c:670-768): norm, Q/K/V projections, q/k norm + RoPE + KV store,
+// attention -- over the heads this descriptor holds (all of them, or a rank's share). attn_out: [n_heads * head_dim].
+int run_attention(const mb200_decode_model &m, const mb200_layer_weights &L, uint8_t *ws, const Workspace &W,
+                  const int *d_pos, float *attn_out, cudaStream_t s)
+{
+    const Bufs B = bufs(m, ws, W);
     const int H = m.hidden, QD = m.n_heads * m.head_dim, KD = m.n_kv_heads * m.head_dim;
     int rc;
     // 1. pre-attention norm (the residual stays in `hidden`: the O projection adds it back in place)
-    launch_rms_norm(hidden, L.attn_norm, normed, nullptr, H, m.rms_eps, s);
+    launch_rms_norm(B.hidden, L.attn_norm, B.normed, nullptr, H, m.rms_eps, s);
     // 2. Q, K, V projections
     if (L.wq_type == 12 && L.wk_type == 12) {
-        q4k_matvec2(L.wq, q, QD, L.wk, k, KD, normed, H, s, "mb200_decode: Q,K projection");
+        q4k_matvec2(L.wq, B.q, QD, L.wk, B.k, KD, B.normed, H, s, "mb200_decode: Q,K projection");
     } else {
-        if ((rc = matvec(L.wq, L.wq_type, normed, q, QD, H, s)) != MB200_OK) return rc;
-        if ((rc = matvec(L.wk, L.wk_type, normed, k, KD, H, s)) != MB200_OK) return rc;
+        if ((rc = matvec(L.wq, L.wq_type, B.normed, B.q, QD, H, s)) != MB200_OK) return rc;
+        if ((rc = matvec(L.wk, L.wk_type, B.normed, B.k, KD, H, s)) != MB200_OK) return rc;
     }
-    if ((rc = matvec(L.wv, L.wv_type, normed, v, KD, H, s)) != MB200_OK) return rc;
+    if ((rc = matvec(L.wv, L.wv_type, B.normed, B.v, KD, H, s)) != MB200_OK) return rc;
     // 3-5. q/k norm, RoPE, fp16 KV store at the position
-    launch_qk_norm_rope_store(q, k, v, L.q_norm, L.k_norm, cos_t, sin_t, L.kv_k, L.kv_v, m.n_heads, m.n_kv_heads,
-                              m.head_dim, m.rms_eps, d_pos, 0, s);
+    launch_qk_norm_rope_store(B.q, B.k, B.v, L.q_norm, L.k_norm, B.cos_t, B.sin_t, L.kv_k, L.kv_v, m.n_heads,
+                              m.n_kv_heads, m.head_dim, m.rms_eps, d_pos, 0, s);
     // 6. attention over positions 0..pos
-    rc = launch_attn_decode(q, L.kv_k, L.kv_v, attn, m.n_heads, m.n_kv_heads, 0, d_pos,
-                            1.0f / sqrtf(static_cast<float>(m.head_dim)), ws + W.attn_ws, s);
-    if (rc != MB200_OK) return rc;
-    // 7. output projection + residual
+    return launch_attn_decode(B.q, L.kv_k, L.kv_v, attn_out, m.n_heads, m.n_kv_heads, 0, d_pos,
+                              1.0f / sqrtf(static_cast<float>(m.head_dim)), ws + W.attn_ws, s);
+}
+
+// Step 7: rows [row0, row0 + rows) of hidden = Wo[rows] . attn + hidden[rows] (L.wo points at the first of those rows).
+int run_oproj(const mb200_decode_model &m, const mb200_layer_weights &L, uint8_t *ws, const Workspace &W,
+              const float *attn_full, int qd_total, int row0, int rows, float *out_rows, cudaStream_t s)
+{
+    const Bufs B = bufs(m, ws, W);
     if (L.wo_type == 12) {
-        cuda_matvec_q4k_add(L.wo, attn, hidden, hidden, H, QD, s);
-    } else {
-        if ((rc = matvec(L.wo, L.wo_type, attn, normed, H, QD, s)) != MB200_OK) return rc;
-        cuda_residual_add(normed, hidden, hidden, H, s);
+        cuda_matvec_q4k_add(L.wo, attn_full, B.hidden + row0, out_rows, rows, qd_total, s);
+        return MB200_OK;
     }
-    // 8. pre-FFN norm, 9-13. router, top-k, routed experts, weighted sum + residual
-    launch_rms_norm(hidden, L.ffn_norm, normed, nullptr, H, m.rms_eps, s);
+    const int rc = matvec(L.wo, L.wo_type, attn_full, B.normed, rows, qd_total, s);
+    if (rc != MB200_OK) return rc;
+    cuda_residual_add(B.normed, B.hidden + row0, out_rows, rows, s);
+    return MB200_OK;
+}
+
+// Steps 8-13: pre-FFN norm, router, top-k, the routed experts held here, weighted sum (+ residual if asked).
+int run_moe(const mb200_decode_model &m, const mb200_layer_weights &L, uint8_t *ws, const Workspace &W, bool with_residual,
+            float *out, cudaStream_t s)
+{
+    const Bufs B = bufs(m, ws, W);
+    const int H = m.hidden;
+    launch_rms_norm(B.hidden, L.ffn_norm, B.normed, nullptr, H, m.rms_eps, s);
+    const float *res = B.hidden;
+    if (!with_residual) {  // another rank adds the residual: this one contributes its experts only
+        float *zero = reinterpret_cast<float *>(ws + W.zero);
+        res = zero;
+    }
     return mb200_moe_block_local(L.router, L.experts, m.expert_stride, m.gate_sz, m.up_sz, m.down_type, m.n_experts,
                                  m.expert_lo, m.expert_cnt > 0 ? m.expert_cnt : 0x7fffffff, m.top_k, H, m.moe_inter,
-                                 normed, hidden, hidden, reinterpret_cast<int *>(ws + W.ids),
+                                 B.normed, res, out, reinterpret_cast<int *>(ws + W.ids),
                                  reinterpret_cast<float *>(ws + W.wts), reinterpret_cast<float *>(ws + W.act),
                                  ws + W.scratch, s);
+}
+
+int run_layer(const mb200_decode_model &m, const mb200_layer_weights &L, uint8_t *ws, const Workspace &W,
+              const int *d_pos, cudaStream_t s)
+{
+    const Bufs B = bufs(m, ws, W);
+    int rc = run_attention(m, L, ws, W, d_pos, B.attn, s);
+    if (rc != MB200_OK) return rc;
+    rc = run_oproj(m, L, ws, W, B.attn, m.n_heads * m.head_dim, 0, m.hidden, B.hidden, s);
+    if (rc != MB200_OK) return rc;
+    return run_moe(m, L, ws, W, true, B.hidden, s);
 }
 
 }  // namespace
@@ -167,6 +214,76 @@ int mb200_decode_layer(const mb200_decode_model *m, int layer, void *workspace, 
     if (rc != MB200_OK) return rc;
     if (cudaGetLastError() != cudaSuccess) return MB200_ERR_LAUNCH;
     return mb200_last_status();
+}
+
+// ---- the same layer in three pieces, for a model sharded over devices ----
+int mb200_decode_layer_attn(const mb200_decode_model *m, int layer, void *workspace, const int *d_pos, float *attn_local,
+                            cudaStream_t stream)
+{
+    int rc = check_model(m);
+    if (rc != MB200_OK) return rc;
+    if (!workspace || !d_pos || !attn_local || layer < 0 || layer >= m->n_layers) return MB200_ERR_ARG;
+    mb200_clear_status();
+    rc = run_attention(*m, m->layers[layer], static_cast<uint8_t *>(workspace), layout(*m), d_pos, attn_local, stream);
+    if (rc != MB200_OK) return rc;
+    if (cudaGetLastError() != cudaSuccess) return MB200_ERR_LAUNCH;
+    return mb200_last_status();
+}
+
+int mb200_decode_layer_oproj(const mb200_decode_model *m, int layer, void *workspace, const float *attn_full,
+                             float *hidden_rows, cudaStream_t stream)
+{
+    int rc = check_model(m);
+    if (rc != MB200_OK) return rc;
+    if (!workspace || !attn_full || !hidden_rows || layer < 0 || layer >= m->n_layers) return MB200_ERR_ARG;
+    const int total_heads = m->n_heads_total > 0 ? m->n_heads_total : m->n_heads;
+    const int rows = m->o_rows > 0 ? m->o_rows : m->hidden;
+    if (m->o_row0 < 0 || m->o_row0 + rows > m->hidden) return MB200_ERR_ARG;
+    mb200_clear_status();
+    rc = run_oproj(*m, m->layers[layer], static_cast<uint8_t *>(workspace), layout(*m), attn_full,
+                   total_heads * m->head_dim, m->o_row0, rows, hidden_rows, stream);
+    if (rc != MB200_OK) return rc;
+    if (cudaGetLastError() != cudaSuccess) return MB200_ERR_LAUNCH;
+    return mb200_last_status();
+}
+
+int mb200_decode_layer_moe(const mb200_decode_model *m, int layer, void *workspace, int add_residual, float *out,
+                           cudaStream_t stream)
+{
+    int rc = check_model(m);
+    if (rc != MB200_OK) return rc;
+    if (!workspace || !out || layer < 0 || layer >= m->n_layers) return MB200_ERR_ARG;
+    mb200_clear_status();
+    rc = run_moe(*m, m->layers[layer], static_cast<uint8_t *>(workspace), layout(*m), add_residual != 0, out, stream);
+    if (rc != MB200_OK) return rc;
+    if (cudaGetLastError() != cudaSuccess) return MB200_ERR_LAUNCH;
+    return mb200_last_status();
+}
+
+int mb200_decode_logits_local(const mb200_decode_model *m, void *workspace, float *logits_rows, float *best_pair,
+                              cudaStream_t stream)
+{
+    int rc = check_model(m);
+    if (rc != MB200_OK) return rc;
+    if (!workspace || !logits_rows || !best_pair || !m->output_norm || !m->lm_head) return MB200_ERR_ARG;
+    const int rows = m->lm_rows > 0 ? m->lm_rows : m->vocab;
+    if (rows < 1 || m->lm_row0 < 0) return MB200_ERR_ARG;
+    const Workspace W = layout(*m);
+    uint8_t *ws = static_cast<uint8_t *>(workspace);
+    float *hidden = reinterpret_cast<float *>(ws + W.hidden), *normed = reinterpret_cast<float *>(ws + W.normed);
+    mb200_clear_status();
+    launch_rms_norm(hidden, m->output_norm, normed, nullptr, m->hidden, m->rms_eps, stream);
+    if ((rc = matvec(m->lm_head, m->lm_head_type, normed, logits_rows, rows, m->hidden, stream)) != MB200_OK) return rc;
+    launch_argmax_pair(logits_rows, rows, m->lm_row0, best_pair, stream);
+    if (cudaGetLastError() != cudaSuccess) return MB200_ERR_LAUNCH;
+    return mb200_last_status();
+}
+
+int mb200_decode_pick(const float *pairs, int n_pairs, int *d_token, int *d_pos, cudaStream_t stream)
+{
+    if (!pairs || n_pairs < 1 || !d_token) return MB200_ERR_ARG;
+    launch_argmax_merge(pairs, n_pairs, d_token, d_pos, stream);
+    return cudaGetLastError() == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
 }
 
 int mb200_decode_finish(const mb200_decode_model *m, void *workspace, float *d_logits, int *d_token, int *d_pos,

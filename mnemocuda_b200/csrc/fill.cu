@@ -109,6 +109,28 @@ int mb200_fill_q4k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t strea
     return cudaGetLastError() == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
 }
 
+// Blocks [first_block, first_block + n_blocks) of the same stream: a row range of a tensor gets the bytes it has
+// inside the whole tensor (a rank that holds only its shard of a sharded model).
+int mb200_fill_q4k_at(void *dst, size_t first_block, size_t n_blocks, uint64_t seed, cudaStream_t stream)
+{
+    if (!dst || (reinterpret_cast<uintptr_t>(dst) & 7)) return MB200_ERR_ARG;
+    if (n_blocks == 0) return MB200_OK;
+    fill_q4k_kernel<<<grid_for(n_blocks * 18), 256, 0, stream>>>(
+        static_cast<uint8_t *>(dst), n_blocks, mix(seed) + first_block * 18,
+        mix((seed ^ 0xD0D0ull) ^ 0x5EEDFACEull) + 2 * first_block);
+    return cudaGetLastError() == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
+}
+
+int mb200_fill_q6k_at(void *dst, size_t first_block, size_t n_blocks, uint64_t seed, cudaStream_t stream)
+{
+    if (!dst) return MB200_ERR_ARG;
+    if (n_blocks == 0) return MB200_OK;
+    fill_q6k_kernel<<<grid_for(n_blocks * 27), 256, 0, stream>>>(
+        static_cast<uint8_t *>(dst), n_blocks, mix(seed) + first_block * 27,
+        mix((seed ^ 0xD0D0ull) ^ 0x5EEDFACEull) + first_block);
+    return cudaGetLastError() == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
+}
+
 int mb200_fill_q6k(void *dst, size_t n_blocks, uint64_t seed, cudaStream_t stream)
 {
     if (!dst) return MB200_ERR_ARG;

@@ -633,7 +633,8 @@ __device__ __forceinline__ void argmax_warp(float &bv, int &bi)
 
 // Every CTA scans a strided share of the logits; the last one to finish (ticket) picks among the CTAs'
 // candidates. The preference order is total, so the result does not depend on how the scan is split.
-__global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ logits, int n, int *result, int *pos_ptr)
+__global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ logits, int n, int *result, int *pos_ptr,
+                                                     float *pair_out, int index_offset)
 {
     pdl_enter();
     __shared__ float sv[8];
@@ -641,13 +642,16 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
     __shared__ int is_last;
     float bv = -1e30f;
     int bi = 0;
+    // candidates are compared by their index in the whole vocabulary (index_offset + i), so that a row shard
+    // orders ties as the whole vector would; bi stays shard-local until the end
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const float v = __ldcg(logits + i);
-        if (argmax_better(v, i, bv, bi)) {
+        if (argmax_better(v, i + index_offset, bv, bi + index_offset)) {
             bv = v;
             bi = i;
         }
     }
+    bi += index_offset;
     argmax_warp(bv, bi);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) {
@@ -657,7 +661,7 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
     __syncthreads();
     if (warp != 0) return;
     bv = lane < 8 ? sv[lane] : -1e30f;
-    bi = lane < 8 ? si[lane] : 0;
+    bi = lane < 8 ? si[lane] : index_offset;
     argmax_warp(bv, bi);
     if (lane == 0) {
         g_argmax_val[blockIdx.x] = bv;
@@ -669,7 +673,7 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
     if (!is_last) return;
     __threadfence();
     bv = -1e30f;
-    bi = 0;
+    bi = index_offset;
     for (int c = lane; c < static_cast<int>(gridDim.x); c += 32) {
         const float v = __ldcg(&g_argmax_val[c]);
         const int i = __ldcg(&g_argmax_idx[c]);
@@ -680,10 +684,34 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
     }
     argmax_warp(bv, bi);
     if (lane == 0) {
-        *result = bi;
-        if (pos_ptr) *pos_ptr += 1;  // decode path: the next replay of the graph handles the next position
+        if (pair_out) {  // a row shard of the logits: (value, index in the whole vocabulary) for the merge over the shards
+            pair_out[0] = bv;
+            pair_out[1] = __int_as_float(bi);
+        } else {
+            *result = bi;
+            if (pos_ptr) *pos_ptr = __ldcg(pos_ptr) + 1;  // decode path: the next replay of the graph handles the next position
+        }
         g_argmax_ticket = 0;
     }
+}
+
+// The best of the shards' (value, index) pairs, by the same order as above; writes the token and advances the position.
+__global__ void argmax_merge_kernel(const float *__restrict__ pairs, int n, int *result, int *pos_ptr)
+{
+    pdl_enter();
+    if (threadIdx.x != 0) return;
+    float bv = -1e30f;
+    int bi = 0;
+    for (int q = 0; q < n; q++) {
+        const float v = __ldcg(pairs + 2 * q);
+        const int i = __float_as_int(__ldcg(pairs + 2 * q + 1));
+        if (q == 0 || argmax_better(v, i, bv, bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+    *result = bi;
+    if (pos_ptr) *pos_ptr = __ldcg(pos_ptr) + 1;
 }
 
 // ---- attention workspace that lives in the library image (for the reference-named entry
@@ -814,7 +842,20 @@ void launch_argmax(const float *logits, int n, int *result, int *pos_ptr, cudaSt
 {
     int ctas = (n + 2047) / 2048;  // eight logits per thread
     ctas = ctas < 1 ? 1 : (ctas > kArgmaxCtas ? kArgmaxCtas : ctas);
-    launch_k(argmax_kernel, dim3(ctas), dim3(256), 0, stream, logits, n, result, pos_ptr);
+    launch_k(argmax_kernel, dim3(ctas), dim3(256), 0, stream, logits, n, result, pos_ptr, static_cast<float *>(nullptr), 0);
+}
+
+void launch_argmax_pair(const float *logits, int n, int index_offset, float *pair_out, cudaStream_t stream)
+{
+    int ctas = (n + 2047) / 2048;
+    ctas = ctas < 1 ? 1 : (ctas > kArgmaxCtas ? kArgmaxCtas : ctas);
+    launch_k(argmax_kernel, dim3(ctas), dim3(256), 0, stream, logits, n, static_cast<int *>(nullptr),
+             static_cast<int *>(nullptr), pair_out, index_offset);
+}
+
+void launch_argmax_merge(const float *pairs, int n, int *result, int *pos_ptr, cudaStream_t stream)
+{
+    launch_k(argmax_merge_kernel, dim3(1), dim3(32), 0, stream, pairs, n, result, pos_ptr);
 }
 
 }  // namespace mb200

@@ -33,5 +33,7 @@ void launch_qk_norm_rope_store(float *q, const float *k, const float *v, const f
 void launch_embed_q4k(const void *table, float *out, const int *token_ptr, int token, int hidden, int row_bytes,
                       cudaStream_t stream);
 void launch_argmax(const float *logits, int n, int *result, int *pos_ptr, cudaStream_t stream);
+void launch_argmax_pair(const float *logits, int n, int index_offset, float *pair_out, cudaStream_t stream);
+void launch_argmax_merge(const float *pairs, int n, int *result, int *pos_ptr, cudaStream_t stream);
 
 }  // namespace mb200

@@ -112,36 +112,71 @@ class DecodeModel(C.Structure):
                 ("down_type", C.c_int), ("embd_type", C.c_int), ("lm_head_type", C.c_int),
                 ("expert_stride", C.c_size_t), ("gate_sz", C.c_size_t), ("up_sz", C.c_size_t),
                 ("expert_lo", C.c_int), ("expert_cnt", C.c_int), ("layers", C.POINTER(LayerWeights)),
-                ("token_embd", C.c_void_p), ("output_norm", C.c_void_p), ("lm_head", C.c_void_p)]
+                ("token_embd", C.c_void_p), ("output_norm", C.c_void_p), ("lm_head", C.c_void_p),
+                ("n_heads_total", C.c_int), ("o_row0", C.c_int), ("o_rows", C.c_int), ("lm_row0", C.c_int),
+                ("lm_rows", C.c_int)]
 
 
 def _tensor_seed(seed: int, layer: int, which: int) -> int:
     return (seed * 1000 + layer) * 64 + which
 
 
+def shard_plan(cfg: DecodeConfig, rank: int, world: int) -> dict:
+    """Which part of the model rank `rank` of `world` holds: query heads [q0, q0 + nq), KV heads [kv0, kv0 + nkv)
+    (a KV head is replicated when there are more ranks than KV heads), rows of the output projection and of the
+    lm_head, experts. Everything divides evenly for the supported world sizes (1, 2, 4, 8)."""
+    c = cfg
+    if c.n_heads % world or c.hidden % world or c.vocab % world or c.n_experts % world:
+        raise ValueError(f"the model does not split evenly over {world} ranks")
+    nq = c.n_heads // world
+    if world <= c.n_kv_heads:
+        if c.n_kv_heads % world:
+            raise ValueError("KV heads do not split evenly")
+        nkv = c.n_kv_heads // world
+        kv0 = rank * nkv
+    else:
+        if world % c.n_kv_heads:
+            raise ValueError("ranks per KV head must be whole")
+        nkv, kv0 = 1, rank // (world // c.n_kv_heads)
+    ne = c.n_experts // world
+    return dict(q0=rank * nq, nq=nq, kv0=kv0, nkv=nkv, o_row0=rank * (c.hidden // world), o_rows=c.hidden // world,
+                lm_row0=rank * (c.vocab // world), lm_rows=c.vocab // world, e0=rank * ne, ne=ne)
+
+
 class ResidentModel:
-    """A model of shape `cfg` resident on one device. Tensor values are seeded synthetic GGUF blocks with
-    the benchmark's distributions (see synth.py); RMSNorm weights are 1.0; the KV cache is pre-filled
-    with N(0,1) for positions [0, kv_prefill). `expert_range` keeps only experts [lo, hi) of every layer
-    (expert-sharded engines)."""
+    """A model of shape `cfg` resident on one device, or one rank's shard of it (rank / world / comm).
+
+    Tensor values are seeded synthetic GGUF blocks with the benchmark's distributions (see synth.py), written on
+    the device; a shard gets exactly the bytes it has inside the whole tensors, so a sharded model computes the
+    same network. RMSNorm weights are 1.0; the KV cache is pre-filled with N(0,1) for positions [0, kv_prefill).
+    Sharding (this replaces the reference's layer-range split, src/engine.c:761-775): query / KV heads, rows of the
+    output projection and of the lm_head, and experts are split over the ranks; per layer the attention outputs and
+    the projected rows are all-gathered and the experts' partial sums all-reduced through `comm` (peer.PeerComm)."""
 
     def __init__(self, cfg: DecodeConfig, device="cuda", seed: int = 1, kv_prefill: int | None = None,
-                 expert_range=None, norm_weights: str = "ones"):
+                 norm_weights: str = "ones", rank: int = 0, world: int = 1, comm=None):
         self.cfg, self.device = cfg, torch.device(device)
+        self.rank, self.world, self.comm = rank, world, comm
+        if world > 1 and comm is None:
+            raise ValueError("a sharded model needs a PeerComm")
         K.mb200_init()
         c = cfg
-        lo, hi = expert_range if expert_range is not None else (0, c.n_experts)
-        self.expert_lo, self.n_local = lo, hi - lo
+        sp = self.plan = shard_plan(cfg, rank, world)
+        self.expert_lo, self.n_local = sp["e0"], sp["ne"]
         g, u, d = c.expert_sizes()
-        tb = c.layer_tensor_bytes()
+        HD, QDT = c.head_dim, c.n_heads * c.head_dim
         u8 = lambda n: torch.empty(n, dtype=torch.uint8, device=self.device)
         self.layers = []
-        self._keep = []
-        fills = {12: (K.mb200_fill_q4k, synth.Q4K_BLOCK), 14: (K.mb200_fill_q6k, synth.Q6K_BLOCK)}
+        blk = {12: synth.Q4K_BLOCK, 14: synth.Q6K_BLOCK}
+        fill_at = {12: _lib.lib().mb200_fill_q4k_at, 14: _lib.lib().mb200_fill_q6k_at}
+        st = lambda: torch.cuda.current_stream().cuda_stream
 
-        def fill(t, type_id, sd):
-            fn, bb = fills[type_id]
-            fn(t, t.numel() // bb, sd)
+        def rows_of(type_id, row0, rows, cols, sd):
+            """Rows [row0, row0 + rows) of a [* x cols] tensor of the stream `sd`."""
+            bpr = (cols + 255) // 256
+            t = u8(rows * bpr * blk[type_id])
+            K._check(fill_at[type_id](t.data_ptr(), row0 * bpr, rows * bpr, sd, st()), "mb200_fill_*_at")
+            return t
 
         def norm_vec(n, sd):
             if norm_weights == "ones":
@@ -151,34 +186,39 @@ class ResidentModel:
             return t + 1.0
 
         kv_prefill = c.ctx_len - 1 if kv_prefill is None else kv_prefill
+        kv_tmp = torch.zeros(c.ctx_len, c.n_kv_heads, HD, dtype=torch.float16, device=self.device) if world > 1 else None
         for l in range(c.n_layers):
             T = {}
-            for i, (name, ty) in enumerate((("wq", c.wq_type), ("wk", c.wk_type), ("wv", c.wv_type), ("wo", c.wo_type))):
-                T[name] = u8(tb[name])
-                fill(T[name], ty, _tensor_seed(seed, l, i))
+            T["wq"] = rows_of(c.wq_type, sp["q0"] * HD, sp["nq"] * HD, c.hidden, _tensor_seed(seed, l, 0))
+            T["wk"] = rows_of(c.wk_type, sp["kv0"] * HD, sp["nkv"] * HD, c.hidden, _tensor_seed(seed, l, 1))
+            T["wv"] = rows_of(c.wv_type, sp["kv0"] * HD, sp["nkv"] * HD, c.hidden, _tensor_seed(seed, l, 2))
+            T["wo"] = rows_of(c.wo_type, sp["o_row0"], sp["o_rows"], QDT, _tensor_seed(seed, l, 3))
             T["router"] = torch.empty(c.n_experts, c.hidden, dtype=torch.float32, device=self.device)
             K.mb200_fill_normal_f32(T["router"], c.n_experts * c.hidden, _tensor_seed(seed, l, 4), c.hidden ** -0.5)
             T["attn_norm"], T["ffn_norm"] = norm_vec(c.hidden, _tensor_seed(seed, l, 5)), norm_vec(c.hidden, _tensor_seed(seed, l, 6))
-            T["q_norm"], T["k_norm"] = norm_vec(c.head_dim, _tensor_seed(seed, l, 7)), norm_vec(c.head_dim, _tensor_seed(seed, l, 8))
+            T["q_norm"], T["k_norm"] = norm_vec(HD, _tensor_seed(seed, l, 7)), norm_vec(HD, _tensor_seed(seed, l, 8))
             T["experts"] = torch.empty(self.n_local, c.expert_stride, dtype=torch.uint8, device=self.device)
             for e in range(self.n_local):
-                tid = ((seed * 1000 + l) * 1000 + lo + e) * 2 + (1 << 40)
+                tid = ((seed * 1000 + l) * 1000 + self.expert_lo + e) * 2 + (1 << 40)
                 blob = T["experts"][e]
                 K.mb200_fill_q4k(blob, (g + u) // synth.Q4K_BLOCK, tid)
-                fill(blob[g + u:], c.down_type, tid + 1)
-            T["kv_k"] = torch.zeros(c.ctx_len, c.n_kv_heads, c.head_dim, dtype=torch.float16, device=self.device)
-            T["kv_v"] = torch.zeros(c.ctx_len, c.n_kv_heads, c.head_dim, dtype=torch.float16, device=self.device)
+                (K.mb200_fill_q6k if c.down_type == 14 else K.mb200_fill_q4k)(blob[g + u:], d // blk[c.down_type], tid + 1)
+            T["kv_k"] = torch.zeros(c.ctx_len, sp["nkv"], HD, dtype=torch.float16, device=self.device)
+            T["kv_v"] = torch.zeros(c.ctx_len, sp["nkv"], HD, dtype=torch.float16, device=self.device)
             if kv_prefill > 0:
-                K.mb200_fill_normal_f16(T["kv_k"], kv_prefill * c.kv_dim, _tensor_seed(seed, l, 9), 1.0)
-                K.mb200_fill_normal_f16(T["kv_v"], kv_prefill * c.kv_dim, _tensor_seed(seed, l, 10), 1.0)
+                for name, which in (("kv_k", 9), ("kv_v", 10)):
+                    if world == 1:
+                        K.mb200_fill_normal_f16(T[name], kv_prefill * c.n_kv_heads * HD, _tensor_seed(seed, l, which), 1.0)
+                    else:  # the whole cache's stream, then this rank's heads of it
+                        K.mb200_fill_normal_f16(kv_tmp, kv_prefill * c.n_kv_heads * HD, _tensor_seed(seed, l, which), 1.0)
+                        T[name][:kv_prefill].copy_(kv_tmp[:kv_prefill, sp["kv0"]:sp["kv0"] + sp["nkv"]])
             self.layers.append(T)
-        self.token_embd = u8(c._bytes(c.vocab, c.hidden, 12))
-        fill(self.token_embd, 12, _tensor_seed(seed, 9999, 0))
-        self.lm_head = u8(c._bytes(c.vocab, c.hidden, c.lm_head_type))
-        fill(self.lm_head, c.lm_head_type, _tensor_seed(seed, 9999, 1))
+        del kv_tmp
+        self.token_embd = rows_of(12, 0, c.vocab, c.hidden, _tensor_seed(seed, 9999, 0))
+        self.lm_head = rows_of(c.lm_head_type, sp["lm_row0"], sp["lm_rows"], c.hidden, _tensor_seed(seed, 9999, 1))
         self.output_norm = norm_vec(c.hidden, _tensor_seed(seed, 9999, 2))
 
-        # ---- descriptor of raw pointers ----
+        # ---- descriptor of raw pointers (a rank describes its shard) ----
         self._layer_array = (LayerWeights * c.n_layers)()
         for l, T in enumerate(self.layers):
             lw = self._layer_array[l]
@@ -188,14 +228,15 @@ class ResidentModel:
             lw.wq_type, lw.wk_type, lw.wv_type, lw.wo_type = c.wq_type, c.wk_type, c.wv_type, c.wo_type
         m = DecodeModel()
         (m.n_layers, m.hidden, m.n_heads, m.n_kv_heads, m.head_dim, m.n_experts, m.top_k, m.moe_inter, m.vocab,
-         m.ctx_len) = (c.n_layers, c.hidden, c.n_heads, c.n_kv_heads, c.head_dim, c.n_experts, c.top_k, c.moe_inter,
-                       c.vocab, c.ctx_len)
+         m.ctx_len) = (c.n_layers, c.hidden, sp["nq"], sp["nkv"], HD, c.n_experts, c.top_k, c.moe_inter, c.vocab, c.ctx_len)
         m.rms_eps, m.rope_theta = c.rms_eps, c.rope_theta
         m.down_type, m.embd_type, m.lm_head_type = c.down_type, 12, c.lm_head_type
         m.expert_stride, m.gate_sz, m.up_sz = c.expert_stride, g, u
-        m.expert_lo, m.expert_cnt = lo, self.n_local
+        m.expert_lo, m.expert_cnt = self.expert_lo, self.n_local
         m.layers = C.cast(self._layer_array, C.POINTER(LayerWeights))
         m.token_embd, m.output_norm, m.lm_head = self.token_embd.data_ptr(), self.output_norm.data_ptr(), self.lm_head.data_ptr()
+        if world > 1:
+            m.n_heads_total, m.o_row0, m.o_rows, m.lm_row0, m.lm_rows = c.n_heads, sp["o_row0"], sp["o_rows"], sp["lm_row0"], sp["lm_rows"]
         self.desc = m
         lib = _lib.lib()
         n = lib.mb200_decode_workspace_bytes(C.byref(m))
@@ -206,9 +247,14 @@ class ResidentModel:
         self.workspace = self.workspace[off:off + n]
         self.token = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.pos = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.logits = torch.empty(c.vocab, dtype=torch.float32, device=self.device)
+        self.logits = torch.empty(sp["lm_rows"], dtype=torch.float32, device=self.device)  # a shard: its rows only
         hp = lib.mb200_decode_hidden(C.byref(m), self.workspace.data_ptr())
         self._hidden_off = hp - self.workspace.data_ptr()
+        if world > 1:
+            f32 = lambda n_: torch.zeros(n_, dtype=torch.float32, device=self.device)
+            self.attn_local, self.attn_full = f32(sp["nq"] * HD), f32(QDT)
+            self.hidden_rows, self.partial = f32(sp["o_rows"]), f32(c.hidden)
+            self.pair, self.pairs = f32(2), f32(2 * world)
         torch.cuda.synchronize(self.device)
 
     # ---- state ----
@@ -230,18 +276,33 @@ class ResidentModel:
                                                self.pos.data_ptr(), self._st(stream)), "mb200_decode_begin")
 
     def layer(self, l: int, stream=None):
-        K._check(_lib.lib().mb200_decode_layer(C.byref(self.desc), l, self.workspace.data_ptr(), self.pos.data_ptr(),
-                                               self._st(stream)), "mb200_decode_layer")
+        lib, d, ws, st = _lib.lib(), C.byref(self.desc), self.workspace.data_ptr(), self._st(stream)
+        if self.world == 1:
+            K._check(lib.mb200_decode_layer(d, l, ws, self.pos.data_ptr(), st), "mb200_decode_layer")
+            return
+        K._check(lib.mb200_decode_layer_attn(d, l, ws, self.pos.data_ptr(), self.attn_local.data_ptr(), st), "mb200_decode_layer_attn")
+        self.comm.allgather(self.attn_local, self.attn_full, stream)
+        K._check(lib.mb200_decode_layer_oproj(d, l, ws, self.attn_full.data_ptr(), self.hidden_rows.data_ptr(), st),
+                 "mb200_decode_layer_oproj")
+        self.comm.allgather(self.hidden_rows, self.hidden, stream)
+        K._check(lib.mb200_decode_layer_moe(d, l, ws, 1 if self.rank == 0 else 0, self.partial.data_ptr(), st),
+                 "mb200_decode_layer_moe")
+        self.comm.allreduce(self.partial, self.hidden, stream)
 
     def finish(self, advance: bool = True, stream=None):
-        K._check(_lib.lib().mb200_decode_finish(C.byref(self.desc), self.workspace.data_ptr(), self.logits.data_ptr(),
-                                                self.token.data_ptr(), self.pos.data_ptr() if advance else None,
-                                                self._st(stream)), "mb200_decode_finish")
+        lib, d, ws, st = _lib.lib(), C.byref(self.desc), self.workspace.data_ptr(), self._st(stream)
+        pos = self.pos.data_ptr() if advance else None
+        if self.world == 1:
+            K._check(lib.mb200_decode_finish(d, ws, self.logits.data_ptr(), self.token.data_ptr(), pos, st), "mb200_decode_finish")
+            return
+        K._check(lib.mb200_decode_logits_local(d, ws, self.logits.data_ptr(), self.pair.data_ptr(), st), "mb200_decode_logits_local")
+        self.comm.allgather(self.pair, self.pairs, stream)
+        K._check(lib.mb200_decode_pick(self.pairs.data_ptr(), self.world, self.token.data_ptr(), pos, st), "mb200_decode_pick")
 
     def step(self, advance: bool = True, stream=None):
         """Enqueue one token: embedding, all layers, lm_head, greedy sample. With advance=False the
         position stays (benchmarks that time the same position repeatedly)."""
-        if advance:
+        if advance and self.world == 1:
             K._check(_lib.lib().mb200_decode_step(C.byref(self.desc), self.workspace.data_ptr(), self.token.data_ptr(),
                                                   self.pos.data_ptr(), self.logits.data_ptr(), self._st(stream)),
                      "mb200_decode_step")
@@ -249,7 +310,7 @@ class ResidentModel:
         self.begin(stream)
         for l in range(self.cfg.n_layers):
             self.layer(l, stream)
-        self.finish(False, stream)
+        self.finish(advance, stream)
 
     def capture(self, steps: int = 1, advance: bool = True) -> torch.cuda.CUDAGraph:
         """A CUDA graph of `steps` tokens (after one eager token, so that nothing is set up during capture)."""

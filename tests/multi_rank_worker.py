@@ -101,6 +101,44 @@ def main():
     torch.cuda.synchronize()
     assert torch.equal(y, y_full)  # rows are computed independently: sharding does not change a bit
 
+    # ---- whole-token decode, model sharded over the ranks, against the unsharded model on every rank ----
+    from mnemocuda_b200.decode import DecodeConfig, ResidentModel
+    cfg = DecodeConfig(n_layers=2, hidden=1024, n_heads=8, n_kv_heads=4, head_dim=128, n_experts=16, top_k=4, moe_inter=256,
+                       vocab=2048, ctx_len=64)
+    pos0, tok0, n_tok = 40, 7, 5
+    whole = ResidentModel(cfg, dev, seed=17, kv_prefill=pos0, norm_weights="random")
+    shard = ResidentModel(cfg, dev, seed=17, kv_prefill=pos0, norm_weights="random", rank=rank, world=world, comm=comm)
+    sp = shard.plan
+    # the shard holds the bytes it has inside the whole tensors
+    rbq = (cfg.hidden // 256) * 144
+    assert torch.equal(shard.layers[0]["wq"], whole.layers[0]["wq"][sp["q0"] * 128 * rbq:(sp["q0"] + sp["nq"]) * 128 * rbq])
+    assert torch.equal(shard.layers[1]["kv_k"][:pos0], whole.layers[1]["kv_k"][:pos0, sp["kv0"]:sp["kv0"] + sp["nkv"]])
+    for pdl in (False, True):
+        K.mb200_set_pdl(pdl)
+        whole.set_state(tok0, pos0)
+        shard.set_state(tok0, pos0)
+        want, got = [], []
+        for _ in range(n_tok):
+            whole.step()
+            want.append(int(whole.token.item()))
+        for i in range(n_tok):
+            shard.step()
+            got.append(int(shard.token.item()))
+            if i == 0:
+                wl = whole.logits  # after n_tok steps: not comparable; only the tokens are compared beyond step 0
+        assert got == want, (rank, pdl, got, want)
+        assert int(shard.pos.item()) == pos0 + n_tok
+    # and replayed from one CUDA graph
+    shard.set_state(tok0, pos0)
+    g = shard.capture(1)
+    shard.set_state(tok0, pos0)
+    replay = []
+    for _ in range(n_tok):
+        g.replay()
+        replay.append(int(shard.token.item()))
+    assert replay == want, (rank, replay, want)
+    K.mb200_set_pdl(False)
+
     assert K.mb200_device_error() == 0
     dist.barrier()
     comm.close()
