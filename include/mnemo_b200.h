@@ -179,6 +179,17 @@ int mb200_matvec_q4k_dual_swiglu(const void *w_gate, const void *w_up, const flo
 int mb200_matvec_q6k_scaled_add(const void *weights, const float *x, float *y, int n_rows,
                                 int n_cols, float scale, cudaStream_t stream);
 
+/* y = W RMSNorm(x): the norm (x * norm_w / sqrt(mean(x^2) + eps), src/kernels.cu:692-722) folded into the matvec's
+ * staging of x -- every CTA reads x once anyway, adds up x^2 itself and normalises on the way to shared memory,
+ * so the reference's norm kernel and the round trip of the normalised vector through memory
+ * (src/forward.c:672-676, 687-720) disappear. n_cols <= 4608. The two-tensor form is the decode path's Q and K. */
+int mb200_norm_matvec_q4k(const void *weights, const float *x, const float *norm_w, float eps, float *y, int n_rows,
+                          int n_cols, cudaStream_t stream);
+int mb200_norm_matvec_q6k(const void *weights, const float *x, const float *norm_w, float eps, float *y, int n_rows,
+                          int n_cols, cudaStream_t stream);
+int mb200_norm_matvec2_q4k(const void *wa, float *ya, int rows_a, const void *wb, float *yb, int rows_b, const float *x,
+                           const float *norm_w, float eps, int n_cols, cudaStream_t stream);
+
 /* ---- decode-time MoE block with the routed expert ids kept on the device ----
  * The reference copies the k routed ids to the host and synchronises in every layer
  * (src/forward.c:849-882) before issuing 3-4 launches per expert (src/forward.c:1122-1142).
@@ -281,6 +292,15 @@ int mb200_moe_block_local(const float *router_w, const void *experts, size_t exp
                           size_t up_sz, int down_type, int n_experts, int expert_lo, int expert_cnt, int k,
                           int H, int EFF, const float *x, const float *residual, float *out, int *ids,
                           float *wts, float *act, void *scratch, cudaStream_t stream);
+
+/* mb200_moe_block_local on RMSNorm(x) (the pre-FFN norm of src/forward.c:810, folded in): norm_w [H], eps; in the
+ * one-launch form the router and the gate/up products normalise x on the fly, the other forms run a norm
+ * kernel into normed_scratch [H] first. norm_w NULL = x is used as given. */
+int mb200_moe_block_norm(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz,
+                         int down_type, int n_experts, int expert_lo, int expert_cnt, int k, int H, int EFF,
+                         const float *x, const float *norm_w, float norm_eps, float *normed_scratch,
+                         const float *residual, float *out, int *ids, float *wts, float *act, void *scratch,
+                         cudaStream_t stream);
 
 /* The block for a caller that keeps the hidden state in HOST memory (pinned, for the copies to be
  * asynchronous): host_x_res = [x | residual], 2*H floats; host_out receives H floats. dev_io is 3*H floats

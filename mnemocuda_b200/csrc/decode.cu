@@ -20,7 +20,7 @@
 
 namespace mb200 {
 void q4k_matvec2(const void *wa, float *ya, int rows_a, const void *wb, float *yb, int rows_b, const float *x,
-                 int n_cols, cudaStream_t stream, const char *where);
+                 int n_cols, cudaStream_t stream, const char *where, const float *norm_w, float norm_eps);
 
 namespace {
 
@@ -79,6 +79,19 @@ int matvec(const void *w, int type, const float *x, float *y, int rows, int cols
     }
 }
 
+constexpr int kNormFoldMax = 4608;  // widest vector the matvecs' fused RMSNorm takes (one round of loads per CTA)
+
+// A matvec on RMSNorm(x): folded into the matvec for the quantized types, norm kernel + matvec otherwise.
+int matvec_norm(const void *w, int type, const float *x, const float *norm_w, float eps, float *normed_tmp, float *y,
+                int rows, int cols, cudaStream_t s)
+{
+    if (!norm_w) return matvec(w, type, x, y, rows, cols, s);
+    if (type == 12) return mb200_norm_matvec_q4k(w, x, norm_w, eps, y, rows, cols, s);
+    if (type == 14) return mb200_norm_matvec_q6k(w, x, norm_w, eps, y, rows, cols, s);
+    launch_rms_norm(x, norm_w, normed_tmp, nullptr, cols, eps, s);
+    return matvec(w, type, normed_tmp, y, rows, cols, s);
+}
+
 struct Bufs {
     float *hidden, *normed, *q, *k, *v, *attn, *cos_t, *sin_t;
 };
@@ -104,16 +117,20 @@ int run_attention(const mb200_decode_model &m, const mb200_layer_weights &L, uin
     const Bufs B = bufs(m, ws, W);
     const int H = m.hidden, QD = m.n_heads * m.head_dim, KD = m.n_kv_heads * m.head_dim;
     int rc;
-    // 1. pre-attention norm (the residual stays in `hidden`: the O projection adds it back in place)
-    launch_rms_norm(B.hidden, L.attn_norm, B.normed, nullptr, H, m.rms_eps, s);
-    // 2. Q, K, V projections
+    // 1 + 2. pre-attention norm and the Q, K, V projections. The norm is folded into the matvecs' staging of x
+    // (each CTA normalises the vector it reads anyway) where the width allows: no norm kernel, no `normed` round
+    // trip. The residual stays in `hidden`: the O projection adds it back in place.
+    const bool fold = H <= kNormFoldMax && (L.wv_type == 12 || L.wv_type == 14);
+    if (!fold) launch_rms_norm(B.hidden, L.attn_norm, B.normed, nullptr, H, m.rms_eps, s);
+    const float *x = fold ? B.hidden : B.normed;
+    const float *nw = fold ? L.attn_norm : nullptr;
     if (L.wq_type == 12 && L.wk_type == 12) {
-        q4k_matvec2(L.wq, B.q, QD, L.wk, B.k, KD, B.normed, H, s, "mb200_decode: Q,K projection");
+        q4k_matvec2(L.wq, B.q, QD, L.wk, B.k, KD, x, H, s, "mb200_decode: Q,K projection", nw, m.rms_eps);
     } else {
-        if ((rc = matvec(L.wq, L.wq_type, B.normed, B.q, QD, H, s)) != MB200_OK) return rc;
-        if ((rc = matvec(L.wk, L.wk_type, B.normed, B.k, KD, H, s)) != MB200_OK) return rc;
+        if ((rc = matvec_norm(L.wq, L.wq_type, x, nw, m.rms_eps, B.normed, B.q, QD, H, s)) != MB200_OK) return rc;
+        if ((rc = matvec_norm(L.wk, L.wk_type, x, nw, m.rms_eps, B.normed, B.k, KD, H, s)) != MB200_OK) return rc;
     }
-    if ((rc = matvec(L.wv, L.wv_type, B.normed, B.v, KD, H, s)) != MB200_OK) return rc;
+    if ((rc = matvec_norm(L.wv, L.wv_type, x, nw, m.rms_eps, B.normed, B.v, KD, H, s)) != MB200_OK) return rc;
     // 3-5. q/k norm, RoPE, fp16 KV store at the position
     launch_qk_norm_rope_store(B.q, B.k, B.v, L.q_norm, L.k_norm, B.cos_t, B.sin_t, L.kv_k, L.kv_v, m.n_heads,
                               m.n_kv_heads, m.head_dim, m.rms_eps, d_pos, 0, s);
@@ -143,17 +160,17 @@ int run_moe(const mb200_decode_model &m, const mb200_layer_weights &L, uint8_t *
 {
     const Bufs B = bufs(m, ws, W);
     const int H = m.hidden;
-    launch_rms_norm(B.hidden, L.ffn_norm, B.normed, nullptr, H, m.rms_eps, s);
     const float *res = B.hidden;
     if (!with_residual) {  // another rank adds the residual: this one contributes its experts only
         float *zero = reinterpret_cast<float *>(ws + W.zero);
         res = zero;
     }
-    return mb200_moe_block_local(L.router, L.experts, m.expert_stride, m.gate_sz, m.up_sz, m.down_type, m.n_experts,
-                                 m.expert_lo, m.expert_cnt > 0 ? m.expert_cnt : 0x7fffffff, m.top_k, H, m.moe_inter,
-                                 B.normed, res, out, reinterpret_cast<int *>(ws + W.ids),
-                                 reinterpret_cast<float *>(ws + W.wts), reinterpret_cast<float *>(ws + W.act),
-                                 ws + W.scratch, s);
+    // the pre-FFN norm is folded into the one-launch block where that form applies (else it runs as a kernel inside)
+    return mb200_moe_block_norm(L.router, L.experts, m.expert_stride, m.gate_sz, m.up_sz, m.down_type, m.n_experts,
+                                m.expert_lo, m.expert_cnt > 0 ? m.expert_cnt : 0x7fffffff, m.top_k, H, m.moe_inter,
+                                B.hidden, L.ffn_norm, m.rms_eps, B.normed, res, out, reinterpret_cast<int *>(ws + W.ids),
+                                reinterpret_cast<float *>(ws + W.wts), reinterpret_cast<float *>(ws + W.act),
+                                ws + W.scratch, s);
 }
 
 int run_layer(const mb200_decode_model &m, const mb200_layer_weights &L, uint8_t *ws, const Workspace &W,
@@ -272,8 +289,9 @@ int mb200_decode_logits_local(const mb200_decode_model *m, void *workspace, floa
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     float *hidden = reinterpret_cast<float *>(ws + W.hidden), *normed = reinterpret_cast<float *>(ws + W.normed);
     mb200_clear_status();
-    launch_rms_norm(hidden, m->output_norm, normed, nullptr, m->hidden, m->rms_eps, stream);
-    if ((rc = matvec(m->lm_head, m->lm_head_type, normed, logits_rows, rows, m->hidden, stream)) != MB200_OK) return rc;
+    if ((rc = matvec_norm(m->lm_head, m->lm_head_type, hidden, m->hidden <= kNormFoldMax ? m->output_norm : nullptr,
+                          m->rms_eps, normed, logits_rows, rows, m->hidden, stream)) != MB200_OK)
+        return rc;
     launch_argmax_pair(logits_rows, rows, m->lm_row0, best_pair, stream);
     if (cudaGetLastError() != cudaSuccess) return MB200_ERR_LAUNCH;
     return mb200_last_status();
@@ -296,8 +314,9 @@ int mb200_decode_finish(const mb200_decode_model *m, void *workspace, float *d_l
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     float *hidden = reinterpret_cast<float *>(ws + W.hidden), *normed = reinterpret_cast<float *>(ws + W.normed);
     mb200_clear_status();
-    launch_rms_norm(hidden, m->output_norm, normed, nullptr, m->hidden, m->rms_eps, stream);
-    if ((rc = matvec(m->lm_head, m->lm_head_type, normed, d_logits, m->vocab, m->hidden, stream)) != MB200_OK) return rc;
+    if ((rc = matvec_norm(m->lm_head, m->lm_head_type, hidden, m->hidden <= kNormFoldMax ? m->output_norm : nullptr,
+                          m->rms_eps, normed, d_logits, m->vocab, m->hidden, stream)) != MB200_OK)
+        return rc;
     launch_argmax(d_logits, m->vocab, d_token, d_pos, stream);
     if (cudaGetLastError() != cudaSuccess) return MB200_ERR_LAUNCH;
     return mb200_last_status();

@@ -28,9 +28,11 @@ int pdl_enabled() { return stream::pdl_mode(); }
 // Two Q4_K tensors of different heights that share x, one launch (the decode path's Q and K projections;
 // the reference's three-tensor form, cuda_matvec_q4k_qkv, needs V to be Q4_K too, which Q4_K_M files are not).
 void q4k_matvec2(const void *wa, float *ya, int rows_a, const void *wb, float *yb, int rows_b, const float *x,
-                 int n_cols, cudaStream_t stream, const char *where)
+                 int n_cols, cudaStream_t stream, const char *where, const float *norm_w, float norm_eps)
 {
     Params P{};
+    P.norm_w = norm_w;
+    P.norm_eps = norm_eps;
     P.seg[0] = {static_cast<const uint8_t *>(wa), ya, rows_a, 0};
     P.seg[1] = {static_cast<const uint8_t *>(wb), yb, rows_b, 0};
     P.nseg = 2;
@@ -156,6 +158,32 @@ void cuda_matvec_q4k_scaled_add(const void *weights, const float *x, float *y, i
     P.n_cols = n_cols;
     P.mode = stream::kScaledAdd;
     stream::launch<Q4>(P, stream, "cuda_matvec_q4k_scaled_add");
+}
+
+int mb200_norm_matvec_q4k(const void *weights, const float *x, const float *norm_w, float eps, float *y, int n_rows,
+                          int n_cols, cudaStream_t stream)
+{
+    if (!weights || !x || !norm_w || !y || n_rows < 0 || n_cols <= 0) return MB200_ERR_ARG;
+    Params P{};
+    P.seg[0] = {static_cast<const uint8_t *>(weights), y, n_rows, 0};
+    P.nseg = 1;
+    P.x = x;
+    P.norm_w = norm_w;
+    P.norm_eps = eps;
+    P.n_cols = n_cols;
+    P.mode = stream::kStore;
+    mb200_clear_status();
+    stream::launch<Q4>(P, stream, "mb200_norm_matvec_q4k");
+    return mb200_last_status();
+}
+
+int mb200_norm_matvec2_q4k(const void *wa, float *ya, int rows_a, const void *wb, float *yb, int rows_b, const float *x,
+                           const float *norm_w, float eps, int n_cols, cudaStream_t stream)
+{
+    if (!wa || !wb || !ya || !yb || !x || !norm_w || rows_a < 0 || rows_b < 0 || n_cols <= 0) return MB200_ERR_ARG;
+    mb200_clear_status();
+    q4k_matvec2(wa, ya, rows_a, wb, yb, rows_b, x, n_cols, stream, "mb200_norm_matvec2_q4k", norm_w, eps);
+    return mb200_last_status();
 }
 
 int mb200_set_pdl(int enabled)

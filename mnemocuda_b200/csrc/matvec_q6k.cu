@@ -65,6 +65,23 @@ void cuda_matvec_q6k(const void *weights, const float *x, float *y, int n_rows, 
     stream::launch<Q6>(P, stream, "cuda_matvec_q6k");
 }
 
+int mb200_norm_matvec_q6k(const void *weights, const float *x, const float *norm_w, float eps, float *y, int n_rows,
+                          int n_cols, cudaStream_t stream)
+{
+    if (!weights || !x || !norm_w || !y || n_rows < 0 || n_cols <= 0) return MB200_ERR_ARG;
+    Params P{};
+    P.seg[0] = {static_cast<const uint8_t *>(weights), y, n_rows, 0};
+    P.nseg = 1;
+    P.x = x;
+    P.norm_w = norm_w;
+    P.norm_eps = eps;
+    P.n_cols = n_cols;
+    P.mode = stream::kStore;
+    mb200_clear_status();
+    stream::launch<Q6>(P, stream, "mb200_norm_matvec_q6k");
+    return mb200_last_status();
+}
+
 int mb200_matvec_q6k_scaled_add(const void *weights, const float *x, float *y, int n_rows,
                                 int n_cols, float scale, cudaStream_t stream)
 {

@@ -29,7 +29,9 @@ int pdl_enabled();
 int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off, size_t down_off, int down_type,
               const int *ids, const float *wts, int n_slots, int expert_lo, int expert_cnt, const float *x, float *act,
               const float *residual, float *y, int H, int EFF, unsigned long long *sync, cudaStream_t stream,
-              const float *router_w, int n_experts, float *logits, int *ids_out, float *wts_out);
+              const float *router_w, int n_experts, float *logits, int *ids_out, float *wts_out, const float *norm_w,
+              float norm_eps);
+void launch_rms_norm(const float *in, const float *w, float *out, float *res_out, int n, float eps, cudaStream_t stream);
 void moe_fused_set_mode(int mode);
 int moe_fused_mode();
 
@@ -261,7 +263,7 @@ int mb200_moe_experts_fused(const void *experts, size_t expert_stride, size_t ga
     if (reinterpret_cast<uintptr_t>(sync) & 7) return MB200_ERR_ARG;
     return moe_fused(experts, expert_stride, gate_off, up_off, down_off, down_type, ids, wts, n_slots, expert_lo,
                      expert_cnt, x, act, residual, y, H, EFF, static_cast<unsigned long long *>(sync), stream, nullptr, 0,
-                     nullptr, nullptr, nullptr);
+                     nullptr, nullptr, nullptr, nullptr, 0.0f);
 }
 
 int mb200_moe_block_local(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz,
@@ -269,9 +271,20 @@ int mb200_moe_block_local(const float *router_w, const void *experts, size_t exp
                           int EFF, const float *x, const float *residual, float *out, int *ids, float *wts, float *act,
                           void *scratch, cudaStream_t stream)
 {
+    return mb200_moe_block_norm(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts, expert_lo, expert_cnt,
+                                k, H, EFF, x, nullptr, 0.0f, nullptr, residual, out, ids, wts, act, scratch, stream);
+}
+
+int mb200_moe_block_norm(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz,
+                         int down_type, int n_experts, int expert_lo, int expert_cnt, int k, int H, int EFF,
+                         const float *x, const float *norm_w, float norm_eps, float *normed_scratch,
+                         const float *residual, float *out, int *ids, float *wts, float *act, void *scratch,
+                         cudaStream_t stream)
+{
     if (!router_w || !x || !scratch || !ids || !wts || n_experts < 1 || H < 1 || k < 1 || k > 16 || expert_lo < 0 ||
         expert_cnt < 0)
         return MB200_ERR_ARG;
+    if (norm_w && !normed_scratch) return MB200_ERR_ARG;
     if (reinterpret_cast<uintptr_t>(scratch) & 15) return MB200_ERR_ARG;
     // the last 64 bytes of the scratch are the fused kernel's barrier counters
     unsigned long long *sync =
@@ -281,16 +294,21 @@ int mb200_moe_block_local(const float *router_w, const void *experts, size_t exp
     if (moe_fused_mode() == 2 && act) {
         // one launch: routing, gate/up, down
         rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, nullptr, nullptr, k, expert_lo,
-                       expert_cnt, x, act, residual, out, H, EFF, sync, stream, router_w, n_experts, logits, ids, wts);
+                       expert_cnt, x, act, residual, out, H, EFF, sync, stream, router_w, n_experts, logits, ids, wts,
+                       norm_w, norm_eps);
         // not covered, or the device refused the cooperative launch (fewer SMs available than the grid
         // needs): nothing ran, the separate kernels below do the block
         if (rc != MB200_ERR_UNSUPPORTED && rc != MB200_ERR_LAUNCH) return rc;
+    }
+    if (norm_w) {  // the other forms take the normalised vector from memory: one small kernel more
+        launch_rms_norm(x, norm_w, normed_scratch, nullptr, H, norm_eps, stream);
+        x = normed_scratch;
     }
     rc = mb200_router_topk(router_w, x, scratch, ids, wts, n_experts, H, k, stream);
     if (rc != MB200_OK) return rc;
     if (moe_fused_mode() && act) {
         rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, ids, wts, k, expert_lo, expert_cnt,
-                       x, act, residual, out, H, EFF, sync, stream, nullptr, 0, nullptr, nullptr, nullptr);
+                       x, act, residual, out, H, EFF, sync, stream, nullptr, 0, nullptr, nullptr, nullptr, nullptr, 0.0f);
         if (rc != MB200_ERR_UNSUPPORTED && rc != MB200_ERR_LAUNCH) return rc;
     }
     rc = mb200_moe_gate_up_local(experts, expert_stride, 0, gate_sz, ids, k, expert_lo, expert_cnt, x, act, EFF, H,

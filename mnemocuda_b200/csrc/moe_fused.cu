@@ -95,6 +95,9 @@ struct FusedParams {
     int off_cpart;                 // partial-sum slots of the down stages
     int pdl;
     int grid;                      // CTAs of the launch = SMs of the device (one CTA per SM, all co-resident)
+    // RMSNorm of x folded in (x' = x * norm_w / sqrt(mean(x^2) + norm_eps)): the router and the gate/up products use x'
+    const float *norm_w;
+    float norm_eps;
 };
 
 struct FTile {
@@ -339,9 +342,10 @@ __device__ __noinline__ void route_logits(const FusedParams &P, float *rred)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n4 = P.H >> 2;
     const float4 *x4 = reinterpret_cast<const float4 *>(P.x);
+    const float4 *n4w = reinterpret_cast<const float4 *>(P.norm_w);  // fused RMSNorm: logit = scale * sum Wr (x w)
     for (int row = blockIdx.x; row < P.n_experts; row += gridDim.x) {
         const float4 *w4 = reinterpret_cast<const float4 *>(P.router_w + (size_t)row * P.H);
-        float acc = 0.0f;
+        float acc = 0.0f, ss = 0.0f;
         for (int i0 = tid; i0 < n4; i0 += kConsumers * 32 * 4) {
             float4 a[4];
 #pragma unroll
@@ -353,7 +357,12 @@ __device__ __noinline__ void route_logits(const FusedParams &P, float *rred)
             for (int u = 0; u < 4; u++) {
                 const int i = i0 + u * kConsumers * 32;
                 if (i < n4) {
-                    const float4 b = __ldcg(x4 + i);
+                    float4 b = __ldcg(x4 + i);
+                    if (n4w) {
+                        const float4 g = __ldg(n4w + i);
+                        ss = fmaf(b.x, b.x, fmaf(b.y, b.y, fmaf(b.z, b.z, fmaf(b.w, b.w, ss))));
+                        b.x *= g.x; b.y *= g.y; b.z *= g.z; b.w *= g.w;
+                    }
                     acc = fmaf(a[u].x, b.x, acc);
                     acc = fmaf(a[u].y, b.y, acc);
                     acc = fmaf(a[u].z, b.z, acc);
@@ -362,11 +371,19 @@ __device__ __noinline__ void route_logits(const FusedParams &P, float *rred)
             }
         }
         acc = warp_sum(acc);
-        if (lane == 0) rred[warp] = acc;
+        if (n4w) ss = warp_sum(ss);
+        if (lane == 0) {
+            rred[warp] = acc;
+            rred[kConsumers + warp] = ss;
+        }
         asm volatile("bar.sync 3, %0;" ::"n"(kConsumers * 32) : "memory");
         if (tid == 0) {
-            float v = 0.0f;
+            float v = 0.0f, t = 0.0f;
             for (int w = 0; w < kConsumers; w++) v += rred[w];  // fixed order
+            if (n4w) {
+                for (int w = 0; w < kConsumers; w++) t += rred[kConsumers + w];
+                v *= 1.0f / sqrtf(t / static_cast<float>(P.H) + P.norm_eps);
+            }
             P.logits[row] = v;
         }
         asm volatile("bar.sync 3, %0;" ::"n"(kConsumers * 32) : "memory");
@@ -664,7 +681,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         uint8_t *xb = smem + P.off_xb - kXBase;
         stream::quantize_x<Q4, 3>(P.x, P.H, P.bprB, reinterpret_cast<uint32_t *>(xb + LB.xq1),
                                   reinterpret_cast<uint32_t *>(xb + LB.xq2), reinterpret_cast<float *>(xb + LB.xs1),
-                                  reinterpret_cast<float *>(xb + LB.xsum));
+                                  reinterpret_cast<float *>(xb + LB.xsum), P.norm_w, P.norm_eps, rred + 2 * kConsumers);
     }
     if (warp == 0) MB200_STAMP(1);
     bool routed_ok = true;
@@ -988,9 +1005,13 @@ int moe_fused_mode() { return g_fused_mode; }
 int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off, size_t down_off, int down_type,
               const int *ids, const float *wts, int n_slots, int expert_lo, int expert_cnt, const float *x, float *act,
               const float *residual, float *y, int H, int EFF, unsigned long long *sync, cudaStream_t stream,
-              const float *router_w, int n_experts, float *logits, int *ids_out, float *wts_out)
+              const float *router_w, int n_experts, float *logits, int *ids_out, float *wts_out, const float *norm_w,
+              float norm_eps)
 {
     FusedParams P{};
+    if (norm_w && (H > 4 * 3 * stream::kQuantThreads || (reinterpret_cast<uintptr_t>(norm_w) & 15))) return MB200_ERR_UNSUPPORTED;
+    P.norm_w = norm_w;
+    P.norm_eps = norm_eps;
     if (router_w) {
         // the group top-k covers n_experts <= 32 * k and <= 512; 16-byte loads of the router rows
         if (n_experts < 1 || n_experts > 512 || n_experts > 32 * n_slots || !logits || !ids_out || !wts_out)

@@ -81,6 +81,10 @@ struct Params {
     int n_slots, erows;      // experts per token; rows per expert tensor
     int expert_lo, expert_cnt;  // this device holds experts [expert_lo, expert_lo + expert_cnt) at ebase; other ids are skipped
     int x_stride;            // kMoeDown: floats between the activation vectors of consecutive slots
+    // RMSNorm folded into the staging of x: x'[c] = x[c] * norm_w[c] / sqrt(mean(x^2) + norm_eps); every CTA
+    // computes the sum of squares itself (x is read once per CTA anyway). nullptr = x is used as given.
+    const float *norm_w;
+    float norm_eps;
     int n_groups;   // column groups (= partial sums per row)
     // per consumer warp: group | first column << 5 | columns v << 12 | rows per pass << 16 | index in group << 20 | warps of group << 24
     uint32_t warp_cfg[kConsumers];
@@ -296,15 +300,23 @@ static __device__ long long g_trace[kSMs * 2][48];  // one copy per translation 
 // its producer has finished, so neither the non-coherent path (__ldg) nor lines an SM's L1 may still
 // hold from an earlier use of the same buffer can be trusted.
 // Called by the consumer warps only (threadIdx.x < kQuantThreads).
+// With norm_w the vector is RMS-normalised on the way (needs the whole vector in one round of loads,
+// n_cols <= 4 * UN * kQuantThreads, which the host checks): the consumer warps add up x^2 through `red`
+// (kConsumers floats of shared memory) and hardware barrier 2.
 template <class F, int UN>
 __device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_cols, int bpr,
-                                           uint32_t *q1, uint32_t *q2, float *s1, float *xsum)
+                                           uint32_t *q1, uint32_t *q2, float *s1, float *xsum,
+                                           const float *__restrict__ norm_w = nullptr, float norm_eps = 0.0f,
+                                           float *red = nullptr)
 {
     const int kpad = bpr * 256;
     const int pitch = F::kSlotsPerBlock * bpr + 1;
     const int lane = threadIdx.x & 31;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-    for (int base = threadIdx.x * 4; base < kpad; base += kQuantThreads * 4 * UN) {
+    // The first round runs on every thread, also one whose columns lie beyond the vector (it loads nothing and
+    // stores nothing): the fused norm below has a barrier that all consumer threads must reach.
+    int base = threadIdx.x * 4;
+    do {
         float v[UN][4];
 #pragma unroll
         for (int u = 0; u < UN; u++) {
@@ -319,6 +331,32 @@ __device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_co
                     v[u][i] = in ? __ldcg(x + c0 + i) : 0.0f;
                 }
             }
+        }
+        if (norm_w) {  // block-uniform
+            float wv[UN][4];
+            float ss = 0.0f;
+#pragma unroll
+            for (int u = 0; u < UN; u++) {
+                const int c0 = base + u * kQuantThreads * 4;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    wv[u][i] = (c0 + i < n_cols) ? __ldg(norm_w + c0 + i) : 0.0f;
+                    // the sum runs over every column of x, also those a group-of-four tail rule drops below
+                    const float xv = (F::kGroup4Tail && c0 + i < n_cols && !(c0 + 3 < n_cols)) ? __ldcg(x + c0 + i) : v[u][i];
+                    ss = fmaf(xv, xv, ss);
+                }
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) red[threadIdx.x >> 5] = ss;
+            asm volatile("bar.sync 2, %0;" ::"n"(kQuantThreads) : "memory");
+            float tot = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kConsumers; w++) tot += red[w];  // fixed order: the same scale on every thread and CTA
+            const float scale = 1.0f / sqrtf(tot / static_cast<float>(n_cols) + norm_eps);
+#pragma unroll
+            for (int u = 0; u < UN; u++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) v[u][i] = v[u][i] * scale * wv[u][i];
         }
 #pragma unroll
         for (int u = 0; u < UN; u++) {
@@ -353,7 +391,8 @@ __device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_co
                 if ((lane & 1) == 0) xsum[c0 >> 3] = sum;
             }
         }
-    }
+        base += kQuantThreads * 4 * UN;
+    } while (base < kpad);
 }
 
 // Same split done by a single warp for one whole vector (routed down-projection:
@@ -568,7 +607,8 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
     if (n_x == 1) {
         quantize_x<F, 3>(P.x, P.n_cols, P.bpr, reinterpret_cast<uint32_t *>(smem + L.xq1),
                          reinterpret_cast<uint32_t *>(smem + L.xq2), reinterpret_cast<float *>(smem + L.xs1),
-                         reinterpret_cast<float *>(smem + L.xsum));
+                         reinterpret_cast<float *>(smem + L.xsum), P.norm_w, P.norm_eps,
+                         reinterpret_cast<float *>(smem + L.bars + 328));
     } else {
         // one activation vector per slot; warps take slots round-robin so the loads of all slots are in flight together
         for (int e = warp; e < n_x; e += kConsumers) {
@@ -720,6 +760,12 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
     if (P.n_cols <= 0) return;
     if (P.n_cols > F::kMaxCols) {
         fprintf(stderr, "[mnemo_b200] %s: n_cols=%d exceeds the supported %d\n", where, P.n_cols, F::kMaxCols);
+        set_status(MB200_ERR_UNSUPPORTED, where);
+        return;
+    }
+    if (P.norm_w && (P.mode == kMoeDown || P.n_cols > 4 * 3 * kQuantThreads)) {
+        fprintf(stderr, "[mnemo_b200] %s: the fused RMSNorm covers one activation vector of at most %d columns\n", where,
+                4 * 3 * kQuantThreads);
         set_status(MB200_ERR_UNSUPPORTED, where);
         return;
     }

@@ -207,6 +207,31 @@ def mb200_matvec_q6k_scaled_add(weights, x, y, n_rows, n_cols, scale, stream=Non
                                                   float(scale), _stream(stream)), "mb200_matvec_q6k_scaled_add")
 
 
+def mb200_norm_matvec_q4k(weights, x, norm_w, eps, y, n_rows, n_cols, stream=None):
+    """y = W RMSNorm(x), the norm folded into the matvec (include/mnemo_b200.h)."""
+    _check(_lib.lib().mb200_norm_matvec_q4k(_ptr(weights), _f32(x), _f32(norm_w), float(eps), _f32(y), n_rows, n_cols,
+                                            _stream(stream)), "mb200_norm_matvec_q4k")
+
+
+def mb200_norm_matvec_q6k(weights, x, norm_w, eps, y, n_rows, n_cols, stream=None):
+    _check(_lib.lib().mb200_norm_matvec_q6k(_ptr(weights), _f32(x), _f32(norm_w), float(eps), _f32(y), n_rows, n_cols,
+                                            _stream(stream)), "mb200_norm_matvec_q6k")
+
+
+def mb200_norm_matvec2_q4k(wa, ya, rows_a, wb, yb, rows_b, x, norm_w, eps, n_cols, stream=None):
+    _check(_lib.lib().mb200_norm_matvec2_q4k(_ptr(wa), _f32(ya), rows_a, _ptr(wb), _f32(yb), rows_b, _f32(x), _f32(norm_w),
+                                             float(eps), n_cols, _stream(stream)), "mb200_norm_matvec2_q4k")
+
+
+def mb200_moe_block_norm(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts, expert_lo, expert_cnt, k,
+                         H, EFF, x, norm_w, eps, normed_scratch, residual, out, ids, wts, act, scratch, stream=None):
+    """mb200_moe_block_local on RMSNorm(x), the norm folded into the one-launch form."""
+    _check(_lib.lib().mb200_moe_block_norm(_f32(router_w), _ptr(experts), expert_stride, gate_sz, up_sz, down_type,
+                                           n_experts, expert_lo, expert_cnt, k, H, EFF, _f32(x), _ptr(norm_w), float(eps),
+                                           _ptr(normed_scratch), _ptr(residual), _f32(out), _ptr(ids), _f32(wts),
+                                           _f32(act), _ptr(scratch), _stream(stream)), "mb200_moe_block_norm")
+
+
 def mb200_router_scratch_bytes(n_experts: int) -> int:
     return int(_lib.lib().mb200_router_scratch_bytes(n_experts))
 

@@ -7,6 +7,7 @@ without it. This module builds the instrumented copy next to the product library
 
     python -m mnemocuda_b200.trace moe_block      # one-launch MoE block, 235B shape: phase timeline
     python -m mnemocuda_b200.trace moe_experts    # the fused expert kernel alone (ids given)
+    python -m mnemocuda_b200.trace moe_block_after_matvec   # the block alternating with a 4096 x 8192 Q4_K matvec
 
 Slots of the fused kernel (ns after the earliest CTA entry; median over CTAs):
   0 entry | 3 logits stored, routing barrier arrived | 1 x split done | 4 routing barrier complete |
@@ -75,8 +76,14 @@ def _run(which: str) -> None:
     p = lambda t: C.c_void_p(t.data_ptr())
     sz = C.c_size_t
 
+    wo = torch.randint(0, 255, (H * (2 * H // 256) * 144,), dtype=torch.uint8, device="cuda")  # a 4096 x 8192 Q4_K matrix
+    attn = torch.randn(2 * H, device="cuda")
+    hid = torch.randn(H, device="cuda")
+
     def call(stream):
-        if which == "moe_block":
+        if which == "moe_block_after_matvec":  # the block as it runs inside a decode layer: after the O projection
+            lib.cuda_matvec_q4k_add(p(wo), p(attn), p(hid), p(hid), C.c_int(H), C.c_int(2 * H), stream)
+        if which in ("moe_block", "moe_block_after_matvec"):
             return lib.mb200_moe_block(p(router), p(ex), sz(stride), sz(g), sz(g), C.c_int(14), C.c_int(NE), C.c_int(K),
                                        C.c_int(H), C.c_int(EFF), p(x), p(res), p(y), p(ids), p(wts), p(act), p(scratch), stream)
         return lib.mb200_moe_experts_fused(p(ex), sz(stride), sz(0), sz(g), sz(2 * g), C.c_int(14), p(ids), p(wts), C.c_int(K),

@@ -288,3 +288,49 @@ def test_one_hot_multi_block_rows(K):
         scale = (_q4k_term_scale if cols == 4096 else _q6k_term_scale)(blocks).reshape(rows, cols)
         err = np.abs(got.astype(np.float64) - ref.T[pos])
         assert np.all(err <= ONE_HOT_TOL * scale.T[pos] + 1e-45), (cols, float((err / (scale.T[pos] + 1e-300)).max()))
+
+
+@pytest.mark.parametrize("kind,rows,cols", [("q4k", 8192, 4096), ("q4k", 4096, 2048), ("q4k", 100, 300), ("q4k", 40, 256),
+                                            ("q6k", 512, 4096), ("q6k", 512, 2048), ("q6k", 33, 1536), ("q6k", 7, 300)])
+def test_rmsnorm_folded_into_the_matvec(K, kind, rows, cols):
+    """mb200_norm_matvec_*: y = W RMSNorm(x) with the norm done inside the matvec's staging of x, against the
+    oracle's RMSNorm followed by its matvec (and against the two separate kernels)."""
+    gen = synth.q4k_matrix if kind == "q4k" else synth.q6k_matrix
+    mv = oracle.matvec_q4k if kind == "q4k" else oracle.matvec_q6k
+    call = K.mb200_norm_matvec_q4k if kind == "q4k" else K.mb200_norm_matvec_q6k
+    plain = K.cuda_matvec_q4k if kind == "q4k" else K.cuda_matvec_q6k
+    w = gen(300 + rows, rows, cols)
+    x = synth.normal_f32(301, cols, 3.0)
+    nw = (1 + 0.1 * synth.normal_f32(302, cols)).astype(np.float32)
+    xn = oracle.rms_norm(x, nw, 1e-6)
+    _, want, ad = mv(w, xn, rows, cols, full=True)
+    y = torch.full((rows,), float("nan"), device="cuda")
+    call(dev(w), dev(x), dev(nw), 1e-6, y, rows, cols)
+    assert_close_matvec(host(y), want, ad, f"norm+matvec {kind} {rows}x{cols}")
+    # the two-kernel path gives the same up to the rounding of the norm's sum of squares
+    xn_d = torch.empty(cols, device="cuda")
+    K.cuda_rms_norm(dev(x), dev(nw), xn_d, cols, 1e-6)
+    y2 = torch.empty(rows, device="cuda")
+    plain(dev(w), xn_d, y2, rows, cols)
+    a, b = host(y).astype(np.float64), host(y2).astype(np.float64)
+    assert np.linalg.norm(a - b) <= 2e-5 * np.linalg.norm(b)
+
+
+def test_rmsnorm_folded_two_tensors_and_width_limit(K):
+    rows_a, rows_b, cols = 4096, 512, 2048
+    wa, wb = synth.q4k_matrix(310, rows_a, cols), synth.q4k_matrix(311, rows_b, cols)
+    x = synth.normal_f32(312, cols, 0.5)
+    nw = (1 + 0.1 * synth.normal_f32(313, cols)).astype(np.float32)
+    xn = oracle.rms_norm(x, nw, 1e-6)
+    ya, yb = torch.empty(rows_a, device="cuda"), torch.empty(rows_b, device="cuda")
+    K.mb200_norm_matvec2_q4k(dev(wa), ya, rows_a, dev(wb), yb, rows_b, dev(x), dev(nw), 1e-6, cols)
+    for y, w, r in ((ya, wa, rows_a), (yb, wb, rows_b)):
+        _, want, ad = oracle.matvec_q4k(w, xn, r, cols, full=True)
+        assert_close_matvec(host(y), want, ad, "norm + two tensors")
+    # wider than one round of loads per CTA: refused, nothing launched
+    wide = 8192
+    yw = torch.full((4,), 5.0, device="cuda")
+    with pytest.raises(RuntimeError, match="status 4"):
+        K.mb200_norm_matvec_q4k(dev(synth.q4k_matrix(314, 4, wide)), dev(synth.normal_f32(315, wide)),
+                                dev(np.ones(wide, np.float32)), 1e-6, yw, 4, wide)
+    assert float(yw.min()) == 5.0

@@ -268,3 +268,34 @@ def test_block_at_the_benchmark_shape_all_forms(K, pdl):
         K.mb200_set_fused(2)
         K.mb200_set_pdl(prev)
     assert K.mb200_device_error() == 0
+
+
+@pytest.mark.parametrize("NE,k,H,EFF", [(128, 8, 4096, 1536), (16, 8, 2048, 768)])
+def test_block_with_the_rmsnorm_folded_in(K, NE, k, H, EFF):
+    """mb200_moe_block_norm (the pre-FFN norm inside the block) against the oracle's norm followed by its block,
+    in every form (the one-launch form normalises on the fly, the others run the norm kernel first)."""
+    from mnemocuda_b200.moe import MoEShape, ResidentMoE
+    s = MoEShape(n_experts=NE, top_k=k, hidden=H, eff=EFF)
+    moe = ResidentMoE(s, 1, "cuda", seed=9)
+    experts = moe.experts[0].reshape(-1).cpu().numpy()
+    router = moe.router[0].reshape(-1).cpu().numpy()
+    x, res = synth.normal_f32(71, H, 4.0), synth.normal_f32(72, H)
+    nw = (1 + 0.1 * synth.normal_f32(73, H)).astype(np.float32)
+    xn = oracle.rms_norm(x, nw, 1e-6)
+    want, i_ref, w_ref = oracle.moe_block(router, experts, s.stride, s.gate_sz, s.up_sz, s.down_type, NE, k, H, EFF, xn, res)
+    d_x, d_res, d_nw = dev(x), dev(res), dev(nw)
+    tmp = torch.empty(H, device="cuda")
+    try:
+        for mode in (2, 1, 0):
+            K.mb200_set_fused(mode)
+            out = torch.full((H,), float("nan"), device="cuda")
+            for _ in range(2):
+                K.mb200_moe_block_norm(moe.router[0], moe.experts[0], s.stride, s.gate_sz, s.up_sz, s.down_type, NE, 0, NE, k, H,
+                                       EFF, d_x, d_nw, 1e-6, tmp, d_res, out, moe.ids[0], moe.wts[0], moe.act, moe.scratch)
+            torch.cuda.synchronize()
+            assert np.array_equal(host(moe.ids[0]), i_ref), mode
+            got = host(out).astype(np.float64)
+            assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3, mode
+    finally:
+        K.mb200_set_fused(2)
+    assert K.mb200_device_error() == 0
