@@ -23,7 +23,7 @@
  * env-gated int8 mma.sync experiment (batch 1 only, never validated, src/forward.c:683-698). An engine that
  * still calls them keeps the reference's gemm_q4k.o for those two symbols; the tensor-core
  * path of this library is mb200_gemm_q4k_f16 / mb200_moe_prefill below. Likewise the other GGUF types'
- * matvecs (q3k, q5k, q8_0), the INT8-KV and GDN kernels stay with the reference's kernels.o.
+ * GDN kernels, the gated norm and the cache-statistics kernels stay with the reference's kernels.o.
  *
  * Part 2 (mb200_*) are additions that return a status code.
  */
@@ -131,6 +131,31 @@ void cuda_residual_add(const float *a, const float *b, float *out, int n, cudaSt
  * fallback src/forward.c:1189-1229; this follows the latter three). */
 void cuda_embedding_lookup_q4k(const void *embd_table, float *output, int token_id, int hidden_size,
                                int row_bytes, cudaStream_t stream);
+/* The other weight types of the reference's matvec() switch (src/forward.c:160-173): y = dequant(W) x with
+ * W in Q8_0 (34-byte blocks of 32), Q5_K (176-byte blocks of 256) or Q3_K (110-byte blocks of 256). Bit layouts are
+ * the reference kernels' (src/kernels.cu:644-673, 578-640, 497-575), which for Q5_K's fifth bits and Q3_K's scale
+ * high bits are not the GGUF specification's. Replace src/kernels.cu:1159-1168, 1137-1146, 1148-1157. weights must be
+ * 2-byte aligned; n_cols up to about 32k. */
+void cuda_matvec_q8_0(const void *weights, const float *x, float *y, int n_rows, int n_cols, cudaStream_t stream);
+void cuda_matvec_q5k(const void *weights, const float *x, float *y, int n_rows, int n_cols, cudaStream_t stream);
+void cuda_matvec_q3k(const void *weights, const float *x, float *y, int n_rows, int n_cols, cudaStream_t stream);
+/* Dequantised row token_id of a Q3_K table. Replaces src/kernels.cu:2200-2206 (kernel :1955-2030). */
+void cuda_embedding_lookup_q3k(const void *embd_table, float *output, int token_id, int hidden_size,
+                               int row_bytes, cudaStream_t stream);
+/* INT8 KV cache: per head, scale = absmax / 127 and q = clamp(rint(v * 127 / absmax), -127, 127), both divisions
+ * correctly rounded (the reference builds with fast-math, so its quotient can differ in the last place).
+ * Replace src/kernels.cu:1484-1491 (kernel :1339-1376) and :1526-1534 (kernel :1493-1524). */
+void cuda_f32_to_int8_kv(const float *in, void *out, float *scales, int head_dim, int n_kv_heads,
+                         cudaStream_t stream);
+void cuda_f32_to_int8_kv_dual(const float *k, const float *v, void *out_k, void *out_v, float *k_scales,
+                              float *v_scales, int head_dim, int n_kv_heads, cudaStream_t stream);
+/* Decode attention over the INT8 cache ([position][kv head][head_dim] int8, scales [position][kv head]).
+ * Replaces src/kernels.cu:1536-1546 (kernel :1382-1480). head_dim 128 with 4 or 8 | gqa_ratio shares each
+ * K / V read among the query heads of a CTA and splits the positions over the SMs (partials pass through a
+ * workspace inside the library image); anything else runs one CTA per query head. */
+void cuda_attention_int8kv(const float *q, const void *kv_k, const void *kv_v, const float *k_scales,
+                           const float *v_scales, float *out, int n_heads_q, int head_dim, int n_kv_heads,
+                           int seq_len, int gqa_ratio, float scale, cudaStream_t stream);
 /* Greedy sampling: *d_result = argmax(logits), ties resolved as the reference's scan does
  * (src/kernels.cu:2048-2071). temperature > 0 (nucleus sampling, :2073-2174) is not implemented:
  * the argmax is returned and mb200_last_status() reports MB200_ERR_UNSUPPORTED. Replaces :2208-2215. */
@@ -343,7 +368,8 @@ int mb200_moe_prefill(const void *experts, size_t expert_stride, size_t gate_sz,
 
 /* ---- whole-token decode (the op order of src/forward.c:1635-1707 and :604-1117, no host round trip) ----
  * The caller owns every buffer: weights, KV cache, workspace, token / position / logits. Nothing is
- * allocated here. Tensor types are GGUF ids: 0 = fp32, 12 = Q4_K, 14 = Q6_K. */
+ * allocated here. Tensor types are GGUF ids: 0 = fp32, 8 = Q8_0, 11 = Q3_K, 12 = Q4_K, 13 = Q5_K, 14 = Q6_K
+ * (projections and lm_head: any of them; experts: Q4_K gate / up with a Q4_K or Q6_K down; embedding: Q4_K or Q3_K). */
 typedef struct mb200_layer_weights {
     const float *attn_norm;          /* [hidden] */
     const void *wq, *wk, *wv, *wo;   /* [n_heads*head_dim x hidden], [n_kv_heads*head_dim x hidden] x2, [hidden x n_heads*head_dim] */
@@ -353,6 +379,11 @@ typedef struct mb200_layer_weights {
     const float *router;             /* fp32 [n_experts x hidden] */
     const void *experts;             /* blob of expert expert_lo, then the following ones (expert_stride apart) */
     void *kv_k, *kv_v;               /* this layer's fp16 cache, [ctx_len][n_kv_heads][head_dim] each */
+    /* This layer's expert blob layout where it differs from the model's (a Q4_K_M file mixes Q4_K and Q6_K down
+     * projections from layer to layer; the reference derives the layout per layer file, src/forward.c:867-872).
+     * expert_stride 0 = the model's expert_stride / gate_sz / up_sz / down_type. */
+    size_t expert_stride, gate_sz, up_sz;
+    int down_type;
 } mb200_layer_weights;
 
 typedef struct mb200_decode_model {
@@ -362,7 +393,7 @@ typedef struct mb200_decode_model {
     size_t expert_stride, gate_sz, up_sz;   /* expert blob = [gate][up][down] (src/forward.c:1127-1136) */
     int expert_lo, expert_cnt;              /* experts held on this device (0, 0 = all) */
     const mb200_layer_weights *layers;      /* host array [n_layers] */
-    const void *token_embd;                 /* Q4_K [vocab x hidden] */
+    const void *token_embd;                 /* [vocab x hidden], embd_type 12 (Q4_K) or 11 (Q3_K) */
     const float *output_norm;               /* [hidden] */
     const void *lm_head;                    /* [vocab x hidden], lm_head_type (a sharded rank: its rows, see below) */
     /* A rank of a model sharded over devices describes ITS SHARD above (n_heads / n_kv_heads = the heads it

@@ -38,6 +38,13 @@ SIGNATURES = {
     "cuda_attention_f16kv": (None, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
     "cuda_residual_add": (None, [_vp, _vp, _vp, _i, _vp]),
     "cuda_embedding_lookup_q4k": (None, [_vp, _vp, _i, _i, _i, _vp]),
+    "cuda_matvec_q8_0": (None, [_vp, _vp, _vp, _i, _i, _vp]),
+    "cuda_matvec_q5k": (None, [_vp, _vp, _vp, _i, _i, _vp]),
+    "cuda_matvec_q3k": (None, [_vp, _vp, _vp, _i, _i, _vp]),
+    "cuda_embedding_lookup_q3k": (None, [_vp, _vp, _i, _i, _i, _vp]),
+    "cuda_f32_to_int8_kv": (None, [_vp, _vp, _vp, _i, _i, _vp]),
+    "cuda_f32_to_int8_kv_dual": (None, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "cuda_attention_int8kv": (None, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp]),
     "cuda_sample_token": (None, [_vp, _i, _f, _f, C.c_ulonglong, _vp, _vp]),
     "cuda_get_rope_kernel_ptr": (_vp, []),
     "cuda_get_f16dual_kernel_ptr": (_vp, []),

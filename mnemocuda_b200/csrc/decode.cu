@@ -75,6 +75,9 @@ int matvec(const void *w, int type, const float *x, float *y, int rows, int cols
         case 0: cuda_matvec_f32(static_cast<const float *>(w), x, y, rows, cols, s); return MB200_OK;
         case 12: cuda_matvec_q4k(w, x, y, rows, cols, s); return MB200_OK;
         case 14: cuda_matvec_q6k(w, x, y, rows, cols, s); return MB200_OK;
+        case 8: cuda_matvec_q8_0(w, x, y, rows, cols, s); return MB200_OK;
+        case 11: cuda_matvec_q3k(w, x, y, rows, cols, s); return MB200_OK;
+        case 13: cuda_matvec_q5k(w, x, y, rows, cols, s); return MB200_OK;
         default: return MB200_ERR_UNSUPPORTED;
     }
 }
@@ -166,7 +169,9 @@ int run_moe(const mb200_decode_model &m, const mb200_layer_weights &L, uint8_t *
         res = zero;
     }
     // the pre-FFN norm is folded into the one-launch block where that form applies (else it runs as a kernel inside)
-    return mb200_moe_block_norm(L.router, L.experts, m.expert_stride, m.gate_sz, m.up_sz, m.down_type, m.n_experts,
+    const bool own = L.expert_stride != 0;  // this layer's own blob layout
+    return mb200_moe_block_norm(L.router, L.experts, own ? L.expert_stride : m.expert_stride, own ? L.gate_sz : m.gate_sz,
+                                own ? L.up_sz : m.up_sz, own ? L.down_type : m.down_type, m.n_experts,
                                 m.expert_lo, m.expert_cnt > 0 ? m.expert_cnt : 0x7fffffff, m.top_k, H, m.moe_inter,
                                 B.hidden, L.ffn_norm, m.rms_eps, B.normed, res, out, reinterpret_cast<int *>(ws + W.ids),
                                 reinterpret_cast<float *>(ws + W.wts), reinterpret_cast<float *>(ws + W.act),
@@ -209,12 +214,16 @@ int mb200_decode_begin(const mb200_decode_model *m, void *workspace, const int *
     int rc = check_model(m);
     if (rc != MB200_OK) return rc;
     if (!workspace || !d_token || !d_pos || !m->token_embd) return MB200_ERR_ARG;
-    if (m->embd_type != 12) return MB200_ERR_UNSUPPORTED;
+    if (m->embd_type != 12 && m->embd_type != 11) return MB200_ERR_UNSUPPORTED;  // src/forward.c:1176-1187
     const Workspace W = layout(*m);
     uint8_t *ws = static_cast<uint8_t *>(workspace);
     mb200_clear_status();
-    launch_embed_q4k(m->token_embd, reinterpret_cast<float *>(ws + W.hidden), d_token, 0, m->hidden,
-                     (m->hidden + 255) / 256 * kQ4KBlock, stream);
+    if (m->embd_type == 12)
+        launch_embed_q4k(m->token_embd, reinterpret_cast<float *>(ws + W.hidden), d_token, 0, m->hidden,
+                         (m->hidden + 255) / 256 * kQ4KBlock, stream);
+    else
+        launch_embed_q3k(m->token_embd, reinterpret_cast<float *>(ws + W.hidden), d_token, 0, m->hidden,
+                         (m->hidden + 255) / 256 * 110, stream);
     float *cos_t = reinterpret_cast<float *>(ws + W.rope);
     launch_rope_table(cos_t, cos_t + m->head_dim / 2, m->head_dim, d_pos, 0, m->rope_theta, stream);
     if (cudaGetLastError() != cudaSuccess) return MB200_ERR_LAUNCH;

@@ -32,6 +32,8 @@ void launch_qk_norm_rope_store(float *q, const float *k, const float *v, const f
                                int head_dim, float eps, const int *pos_ptr, int pos, cudaStream_t stream);
 void launch_embed_q4k(const void *table, float *out, const int *token_ptr, int token, int hidden, int row_bytes,
                       cudaStream_t stream);
+void launch_embed_q3k(const void *table, float *out, const int *token_ptr, int token, int hidden, int row_bytes,
+                      cudaStream_t stream);  // other_types.cu
 void launch_argmax(const float *logits, int n, int *result, int *pos_ptr, cudaStream_t stream);
 void launch_argmax_pair(const float *logits, int n, int index_offset, float *pair_out, cudaStream_t stream);
 void launch_argmax_merge(const float *pairs, int n, int *result, int *pos_ptr, cudaStream_t stream);

@@ -102,7 +102,8 @@ class LayerWeights(C.Structure):
     _fields_ = [("attn_norm", C.c_void_p), ("wq", C.c_void_p), ("wk", C.c_void_p), ("wv", C.c_void_p),
                 ("wo", C.c_void_p), ("wq_type", C.c_int), ("wk_type", C.c_int), ("wv_type", C.c_int),
                 ("wo_type", C.c_int), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("ffn_norm", C.c_void_p),
-                ("router", C.c_void_p), ("experts", C.c_void_p), ("kv_k", C.c_void_p), ("kv_v", C.c_void_p)]
+                ("router", C.c_void_p), ("experts", C.c_void_p), ("kv_k", C.c_void_p), ("kv_v", C.c_void_p),
+                ("expert_stride", C.c_size_t), ("gate_sz", C.c_size_t), ("up_sz", C.c_size_t), ("down_type", C.c_int)]
 
 
 class DecodeModel(C.Structure):
@@ -217,20 +218,82 @@ class ResidentModel:
         self.token_embd = rows_of(12, 0, c.vocab, c.hidden, _tensor_seed(seed, 9999, 0))
         self.lm_head = rows_of(c.lm_head_type, sp["lm_row0"], sp["lm_rows"], c.hidden, _tensor_seed(seed, 9999, 1))
         self.output_norm = norm_vec(c.hidden, _tensor_seed(seed, 9999, 2))
+        self._finalize()
 
-        # ---- descriptor of raw pointers (a rank describes its shard) ----
+    @classmethod
+    def from_host(cls, cfg: DecodeConfig, layers: list, token_embd, lm_head, output_norm, embd_type: int = 12,
+                  device="cuda", rank: int = 0, world: int = 1, comm=None) -> "ResidentModel":
+        """A model from host tensors (numpy arrays or memory maps, as a loader of the reference's split-model
+        directory hands them over: split_model.py). `layers[l]` maps the names of the descriptor (attn_norm, wq, wk,
+        wv, wo, q_norm, k_norm, ffn_norm, router, experts) to whole tensors, plus "types" = (wq, wk, wv, wo) type ids
+        and optionally "expert_layout" = (stride, gate bytes, up bytes, down type). Each rank uploads its part:
+        the rows of its heads, of its slice of the output projection and of the lm_head, and its experts."""
+        import numpy as np
+        self = cls.__new__(cls)
+        self.cfg, self.device = cfg, torch.device(device)
+        self.rank, self.world, self.comm = rank, world, comm
+        if world > 1 and comm is None:
+            raise ValueError("a sharded model needs a PeerComm")
+        K.mb200_init()
+        c = cfg
+        sp = self.plan = shard_plan(cfg, rank, world)
+        self.expert_lo, self.n_local = sp["e0"], sp["ne"]
+        HD, QDT = c.head_dim, c.n_heads * c.head_dim
+
+        def up(a):
+            return torch.from_numpy(np.ascontiguousarray(a)).to(self.device)
+
+        def rows(a, type_id, row0, n, cols):
+            per, bb = synth.TYPE_BLOCK[type_id]
+            rb = (cols + per - 1) // per * bb
+            flat = np.asarray(a).reshape(-1).view(np.uint8)
+            return up(flat[row0 * rb:(row0 + n) * rb])
+
+        self.layers = []
+        for l, src in enumerate(layers):
+            tq, tk, tv, to = src["types"]
+            T = {"types": (tq, tk, tv, to)}
+            T["wq"] = rows(src["wq"], tq, sp["q0"] * HD, sp["nq"] * HD, c.hidden)
+            T["wk"] = rows(src["wk"], tk, sp["kv0"] * HD, sp["nkv"] * HD, c.hidden)
+            T["wv"] = rows(src["wv"], tv, sp["kv0"] * HD, sp["nkv"] * HD, c.hidden)
+            T["wo"] = rows(src["wo"], to, sp["o_row0"], sp["o_rows"], QDT)
+            for name in ("attn_norm", "ffn_norm", "q_norm", "k_norm", "router"):
+                T[name] = up(np.asarray(src[name], dtype=np.float32)) if src.get(name) is not None else None
+            stride = src.get("expert_layout", (c.expert_stride,))[0]
+            blob = np.asarray(src["experts"]).reshape(-1).view(np.uint8)
+            T["experts"] = up(blob[self.expert_lo * stride:(self.expert_lo + self.n_local) * stride]).reshape(self.n_local, stride)
+            if "expert_layout" in src:
+                T["expert_layout"] = tuple(src["expert_layout"])
+            T["kv_k"] = torch.zeros(c.ctx_len, sp["nkv"], HD, dtype=torch.float16, device=self.device)
+            T["kv_v"] = torch.zeros(c.ctx_len, sp["nkv"], HD, dtype=torch.float16, device=self.device)
+            self.layers.append(T)
+        self.token_embd = rows(token_embd, embd_type, 0, c.vocab, c.hidden)
+        self.lm_head = rows(lm_head, c.lm_head_type, sp["lm_row0"], sp["lm_rows"], c.hidden)
+        self.output_norm = up(np.asarray(output_norm, dtype=np.float32))
+        self._finalize(embd_type)
+        return self
+
+    def _finalize(self, embd_type: int = 12) -> None:
+        """Descriptor of raw pointers (a rank describes its shard), workspace, token / position / logits."""
+        c, sp = self.cfg, self.plan
+        world = self.world
+        g, u, d = c.expert_sizes()
+        HD, QDT = c.head_dim, c.n_heads * c.head_dim
         self._layer_array = (LayerWeights * c.n_layers)()
         for l, T in enumerate(self.layers):
             lw = self._layer_array[l]
             for name in ("attn_norm", "wq", "wk", "wv", "wo", "q_norm", "k_norm", "ffn_norm", "router", "experts",
                          "kv_k", "kv_v"):
-                setattr(lw, name, T[name].data_ptr())
-            lw.wq_type, lw.wk_type, lw.wv_type, lw.wo_type = c.wq_type, c.wk_type, c.wv_type, c.wo_type
+                setattr(lw, name, T[name].data_ptr() if T.get(name) is not None else None)
+            types = T.get("types", (c.wq_type, c.wk_type, c.wv_type, c.wo_type))
+            lw.wq_type, lw.wk_type, lw.wv_type, lw.wo_type = types
+            if "expert_layout" in T:  # (stride, gate bytes, up bytes, down type) of this layer's blobs
+                lw.expert_stride, lw.gate_sz, lw.up_sz, lw.down_type = T["expert_layout"]
         m = DecodeModel()
         (m.n_layers, m.hidden, m.n_heads, m.n_kv_heads, m.head_dim, m.n_experts, m.top_k, m.moe_inter, m.vocab,
          m.ctx_len) = (c.n_layers, c.hidden, sp["nq"], sp["nkv"], HD, c.n_experts, c.top_k, c.moe_inter, c.vocab, c.ctx_len)
         m.rms_eps, m.rope_theta = c.rms_eps, c.rope_theta
-        m.down_type, m.embd_type, m.lm_head_type = c.down_type, 12, c.lm_head_type
+        m.down_type, m.embd_type, m.lm_head_type = c.down_type, embd_type, c.lm_head_type
         m.expert_stride, m.gate_sz, m.up_sz = c.expert_stride, g, u
         m.expert_lo, m.expert_cnt = self.expert_lo, self.n_local
         m.layers = C.cast(self._layer_array, C.POINTER(LayerWeights))

@@ -165,6 +165,42 @@ def cuda_residual_add(a, b, out, n, stream=None):
     _raise_if_failed("cuda_residual_add")
 
 
+def _typed_matvec(name):
+    def call(weights, x, y, n_rows, n_cols, stream=None):
+        getattr(_lib.lib(), name)(_ptr(weights), _f32(x), _f32(y), n_rows, n_cols, _stream(stream))
+        _raise_if_failed(name)
+    call.__name__ = name
+    return call
+
+
+cuda_matvec_q8_0 = _typed_matvec("cuda_matvec_q8_0")
+cuda_matvec_q5k = _typed_matvec("cuda_matvec_q5k")
+cuda_matvec_q3k = _typed_matvec("cuda_matvec_q3k")
+
+
+def cuda_embedding_lookup_q3k(table, out, token_id, hidden, row_bytes, stream=None):
+    _lib.lib().cuda_embedding_lookup_q3k(_ptr(table), _f32(out), token_id, hidden, row_bytes, _stream(stream))
+    _raise_if_failed("cuda_embedding_lookup_q3k")
+
+
+def cuda_f32_to_int8_kv(x, out, scales, head_dim, n_kv_heads, stream=None):
+    _lib.lib().cuda_f32_to_int8_kv(_f32(x), _ptr(out), _f32(scales), head_dim, n_kv_heads, _stream(stream))
+    _raise_if_failed("cuda_f32_to_int8_kv")
+
+
+def cuda_f32_to_int8_kv_dual(k, v, out_k, out_v, k_scales, v_scales, head_dim, n_kv_heads, stream=None):
+    _lib.lib().cuda_f32_to_int8_kv_dual(_f32(k), _f32(v), _ptr(out_k), _ptr(out_v), _f32(k_scales), _f32(v_scales),
+                                        head_dim, n_kv_heads, _stream(stream))
+    _raise_if_failed("cuda_f32_to_int8_kv_dual")
+
+
+def cuda_attention_int8kv(q, kv_k, kv_v, k_scales, v_scales, out, n_heads_q, head_dim, n_kv_heads, seq_len, gqa_ratio,
+                          scale, stream=None):
+    _lib.lib().cuda_attention_int8kv(_f32(q), _ptr(kv_k), _ptr(kv_v), _f32(k_scales), _f32(v_scales), _f32(out),
+                                     n_heads_q, head_dim, n_kv_heads, seq_len, gqa_ratio, float(scale), _stream(stream))
+    _raise_if_failed("cuda_attention_int8kv")
+
+
 def cuda_embedding_lookup_q4k(table, out, token_id, hidden, row_bytes, stream=None):
     _lib.lib().cuda_embedding_lookup_q4k(_ptr(table), _f32(out), token_id, hidden, row_bytes, _stream(stream))
     _raise_if_failed("cuda_embedding_lookup_q4k")

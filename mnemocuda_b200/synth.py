@@ -111,3 +111,46 @@ def expert_blob(seed: int, H: int, EFF: int, down_type: int = 14) -> np.ndarray:
     up = q4k_matrix(seed * 3 + 1, EFF, H)
     down = q6k_matrix(seed * 3 + 2, H, EFF) if down_type == 14 else q4k_matrix(seed * 3 + 2, H, EFF)
     return np.concatenate([gate, up, down])
+
+
+# ---- other GGUF block types (test inputs for the reference's Q8_0 / Q5_K / Q3_K matvecs) ----
+Q8_0_BLOCK, Q5K_BLOCK, Q3K_BLOCK = 34, 176, 110
+
+
+def q8_0_blocks(seed: int, n_blocks: int) -> np.ndarray:
+    """uint8 [n_blocks, 34]: d = fp16(|N(0,1)| * 2e-3), 32 int8 weights uniform."""
+    w = words(seed, 0, n_blocks * 5)
+    blk = w.view(np.uint8).reshape(n_blocks, 40)[:, :Q8_0_BLOCK].copy()
+    z = np.abs(normals(seed ^ 0xD0D0, 0, n_blocks)) * 2e-3
+    blk[:, 0:2] = z.astype(np.float32).astype(np.float16).view(np.uint8).reshape(n_blocks, 2)
+    return blk
+
+
+def q5k_blocks(seed: int, n_blocks: int) -> np.ndarray:
+    """uint8 [n_blocks, 176]: Q4_K's header and scale packing, 32 bytes of fifth bits, 128 bytes of nibbles."""
+    w = words(seed, 0, n_blocks * 22)
+    blk = w.view(np.uint8).reshape(n_blocks, Q5K_BLOCK).copy()
+    z = np.abs(normals(seed ^ 0xD0D0, 0, n_blocks * 2)) * 2e-3
+    blk[:, 0:4] = z.astype(np.float32).astype(np.float16).view(np.uint8).reshape(n_blocks, 4)
+    return blk
+
+
+def q3k_blocks(seed: int, n_blocks: int) -> np.ndarray:
+    """uint8 [n_blocks, 110]: hmask 32, qs 64, scales 12, d = fp16(|N(0,1)| * 2e-3)."""
+    w = words(seed, 0, n_blocks * 14)
+    blk = w.view(np.uint8).reshape(n_blocks, 112)[:, :Q3K_BLOCK].copy()
+    z = np.abs(normals(seed ^ 0xD0D0, 0, n_blocks)) * 2e-3
+    blk[:, 108:110] = z.astype(np.float32).astype(np.float16).view(np.uint8).reshape(n_blocks, 2)
+    return blk
+
+
+TYPE_BLOCK = {0: (1, 4), 8: (32, Q8_0_BLOCK), 11: (QK_K, Q3K_BLOCK), 12: (QK_K, Q4K_BLOCK), 13: (QK_K, Q5K_BLOCK),
+              14: (QK_K, Q6K_BLOCK)}  # GGUF type id -> (weights per block, bytes per block)
+
+
+def typed_matrix(type_id: int, seed: int, n_rows: int, n_cols: int) -> np.ndarray:
+    """Row-major tensor bytes of GGUF type 8 (Q8_0), 11 (Q3_K), 12 (Q4_K), 13 (Q5_K) or 14 (Q6_K)."""
+    per = 32 if type_id == 8 else QK_K
+    n = n_rows * ((n_cols + per - 1) // per)
+    gen = {8: q8_0_blocks, 11: q3k_blocks, 12: q4k_blocks, 13: q5k_blocks, 14: q6k_blocks}[type_id]
+    return gen(seed, n).reshape(-1)

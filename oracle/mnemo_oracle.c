@@ -645,6 +645,191 @@ int mo_argmax(const float *logits, int n)
     return bi[0];
 }
 
+/* ======================================================================== */
+/* Other GGUF types on the reference's matvec() switch (forward.c:160-173).  */
+/* ======================================================================== */
+
+/* Q8_0: 34-byte blocks of 32 weights, w = d * q (kernels.cu:34-37, 644-673; validate_dequant.py:326-356). */
+static void dequant_q8_0_block(const uint8_t *blk, float out[32])
+{
+    const float d = mo_f16_to_f32(rd16(blk));
+    for (int j = 0; j < 32; j++) out[j] = d * (float)(int8_t)blk[2 + j];
+}
+
+/* Q5_K: 176-byte blocks [d][dmin][scales 12][qh 32][qs 128]; w = d*sc*(lo4 | hi << 4) - dmin*m
+ * (kernels.cu:578-640; validate_dequant.py:122-183). */
+static void dequant_q5k_block(const uint8_t *blk, float out[256])
+{
+    const float d = mo_f16_to_f32(rd16(blk)), dmin = mo_f16_to_f32(rd16(blk + 2));
+    const uint8_t *scales = blk + 4, *qh = blk + 16, *q = blk + 48;
+    int is = 0;
+    for (int j = 0; j < 256; j += 64) {
+        uint8_t sc1, m1, sc2, m2;
+        mo_get_scale_min_k4(is, scales, &sc1, &m1);
+        mo_get_scale_min_k4(is + 1, scales, &sc2, &m2);
+        const float d1 = d * sc1, m1f = dmin * m1, d2 = d * sc2, m2f = dmin * m2;
+        for (int l = 0; l < 32; l++) {
+            const int lo = q[l] & 0xF, hi = (qh[(j + l) / 8] >> ((j + l) % 8)) & 1;
+            out[j + l] = d1 * (float)(lo | (hi << 4)) - m1f;
+        }
+        for (int l = 0; l < 32; l++) {
+            const int lo = q[l] >> 4, hi = (qh[(j + 32 + l) / 8] >> ((j + 32 + l) % 8)) & 1;
+            out[j + 32 + l] = d2 * (float)(lo | (hi << 4)) - m2f;
+        }
+        q += 32;
+        is += 2;
+    }
+}
+
+/* Q3_K: 110-byte blocks [hmask 32][qs 64][scales 12][d]; w = d * (sc - 32) * (q2 - (hbit ? 0 : 4))
+ * (kernels.cu:497-575). */
+static void dequant_q3k_block(const uint8_t *blk, float out[256])
+{
+    const uint8_t *hmask = blk, *q = blk + 32, *scales = blk + 96;
+    const float d_all = mo_f16_to_f32(rd16(blk + 108));
+    int sc16[16];
+    for (int i = 0; i < 8; i++) {
+        sc16[i] = (int8_t)((scales[i] & 0xF) | (((scales[8 + (i >> 2)] >> (2 * (i & 3))) & 3) << 4)) - 32;
+        sc16[i + 8] = (int8_t)((scales[i] >> 4) | (((scales[8 + (i >> 2)] >> (2 * (i & 3) + 4)) & 3) << 4)) - 32;
+    }
+    int is = 0, val = 0;
+    uint8_t m = 1;
+    for (int chunk = 0; chunk < 2; chunk++) {
+        int shift = 0;
+        for (int grp = 0; grp < 4; grp++) {
+            const float dl = d_all * (float)sc16[is++];
+            for (int l = 0; l < 16; l++) {
+                const int q2 = (q[l] >> shift) & 3;
+                out[val++] = dl * (float)(q2 - ((hmask[l] & m) ? 0 : 4));
+            }
+            const float dl2 = d_all * (float)sc16[is++];
+            for (int l = 0; l < 16; l++) {
+                const int q2 = (q[l + 16] >> shift) & 3;
+                out[val++] = dl2 * (float)(q2 - ((hmask[l + 16] & m) ? 0 : 4));
+            }
+            shift += 2;
+            m = (uint8_t)(m << 1);
+        }
+        q += 32;
+    }
+}
+
+/* type ids as in forward.c:160-173: 8 = Q8_0, 11 = Q3_K, 13 = Q5_K (12 = Q4_K, 14 = Q6_K) */
+static int block_weights(int type) { return type == 8 ? 32 : 256; }
+static int block_bytes(int type)
+{
+    switch (type) {
+        case 8: return 34;
+        case 11: return 110;
+        case 12: return 144;
+        case 13: return 176;
+        case 14: return 210;
+        default: return 0;
+    }
+}
+static void dequant_block(int type, const uint8_t *blk, float *out)
+{
+    switch (type) {
+        case 8: dequant_q8_0_block(blk, out); break;
+        case 11: dequant_q3k_block(blk, out); break;
+        case 12: dequant_q4k_block(blk, out); break;
+        case 13: dequant_q5k_block(blk, out); break;
+        default: dequant_q6k_block(blk, out); break;
+    }
+}
+
+int mo_dequant_type(int type, const uint8_t *w, int n_rows, int n_cols, float *out)
+{
+    const int bw = block_weights(type), bb = block_bytes(type);
+    if (!bb) return -1;
+    const int bpr = (n_cols + bw - 1) / bw;
+    for (int r = 0; r < n_rows; r++)
+        for (int b = 0; b < bpr; b++) {
+            float tmp[256];
+            dequant_block(type, w + ((size_t)r * bpr + b) * bb, tmp);
+            for (int j = 0; j < bw && b * bw + j < n_cols; j++) out[(size_t)r * n_cols + b * bw + j] = tmp[j];
+        }
+    return 0;
+}
+
+/* y = dequant(W) x for any of the types above; fp32 result, optional fp64 result and sum |w x| per row. */
+int mo_matvec_type(int type, const uint8_t *w, const float *x, float *y, double *y64, double *abs_dot, int n_rows,
+                   int n_cols)
+{
+    const int bw = block_weights(type), bb = block_bytes(type);
+    if (!bb) return -1;
+    const int bpr = (n_cols + bw - 1) / bw;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < n_rows; r++) {
+        float s32 = 0.0f;
+        double s64 = 0.0, ad = 0.0;
+        for (int b = 0; b < bpr; b++) {
+            float tmp[256];
+            dequant_block(type, w + ((size_t)r * bpr + b) * bb, tmp);
+            for (int j = 0; j < bw && b * bw + j < n_cols; j++) {
+                const float xv = x[b * bw + j];
+                s32 += tmp[j] * xv;
+                s64 += (double)tmp[j] * (double)xv;
+                ad += fabs((double)tmp[j] * (double)xv);
+            }
+        }
+        y[r] = s32;
+        if (y64) y64[r] = s64;
+        if (abs_dot) abs_dot[r] = ad;
+    }
+    return 0;
+}
+
+/* INT8 KV cache: per-head absmax quantisation (kernels.cu:1339-1376): scale = absmax / 127,
+ * q = clamp(rint(v * 127 / absmax), -127, 127). */
+void mo_f32_to_int8_kv(const float *in, int8_t *out, float *scales, int head_dim, int n_kv_heads)
+{
+    for (int h = 0; h < n_kv_heads; h++) {
+        float absmax = 0.0f;
+        for (int d = 0; d < head_dim; d++) absmax = fmaxf(absmax, fabsf(in[h * head_dim + d]));
+        const float inv = absmax > 0.0f ? 127.0f / absmax : 0.0f;
+        scales[h] = absmax > 0.0f ? absmax / 127.0f : 0.0f;
+        for (int d = 0; d < head_dim; d++) {
+            int iv = (int)rintf(in[h * head_dim + d] * inv);
+            iv = iv > 127 ? 127 : (iv < -127 ? -127 : iv);
+            out[h * head_dim + d] = (int8_t)iv;
+        }
+    }
+}
+
+/* Attention over an INT8 KV cache with per-position per-head scales (kernels.cu:1382-1480), in double. */
+void mo_attention_int8kv(const float *q, const int8_t *kv_k, const int8_t *kv_v, const float *k_scales,
+                         const float *v_scales, float *out, int n_heads_q, int head_dim, int n_kv_heads, int seq_len,
+                         int gqa_ratio, float scale)
+{
+    const size_t stride = (size_t)n_kv_heads * head_dim;
+#pragma omp parallel for schedule(dynamic)
+    for (int h = 0; h < n_heads_q; h++) {
+        const int kvh = h / gqa_ratio;
+        double *sc = (double *)malloc(sizeof(double) * (size_t)seq_len);
+        double *acc = (double *)calloc((size_t)head_dim, sizeof(double));
+        double mx = -1e300;
+        for (int p = 0; p < seq_len; p++) {
+            const int8_t *kp = kv_k + (size_t)p * stride + (size_t)kvh * head_dim;
+            double s = 0.0;
+            for (int d = 0; d < head_dim; d++) s += (double)q[(size_t)h * head_dim + d] * (double)kp[d];
+            sc[p] = s * (double)k_scales[(size_t)p * n_kv_heads + kvh] * (double)scale;
+            if (sc[p] > mx) mx = sc[p];
+        }
+        double sum = 0.0;
+        for (int p = 0; p < seq_len; p++) {
+            const double e = exp(sc[p] - mx);
+            sum += e;
+            const int8_t *vp = kv_v + (size_t)p * stride + (size_t)kvh * head_dim;
+            const double vs = (double)v_scales[(size_t)p * n_kv_heads + kvh];
+            for (int d = 0; d < head_dim; d++) acc[d] += e * vs * (double)vp[d];
+        }
+        for (int d = 0; d < head_dim; d++) out[(size_t)h * head_dim + d] = (float)(sum > 0.0 ? acc[d] / sum : 0.0);
+        free(sc);
+        free(acc);
+    }
+}
+
 int mo_num_threads(void)
 {
 #ifdef _OPENMP

@@ -106,6 +106,17 @@ void mo_residual_add(const float *a, const float *b, float *out, int n);        
 void mo_embedding_q4k(const uint8_t *table, int token, int hidden, float *out);         /* forward.c:1189-1229 */
 int mo_argmax(const float *logits, int n);                                              /* kernels.cu:2048-2071 */
 
+/* ---- other GGUF types of the reference's matvec() switch (forward.c:160-173): 8 = Q8_0 (kernels.cu:644-673),
+ * 11 = Q3_K (:497-575), 13 = Q5_K (:578-640); 12 / 14 as above. Returns -1 for an unknown type. */
+int mo_dequant_type(int type, const uint8_t *w, int n_rows, int n_cols, float *out);
+int mo_matvec_type(int type, const uint8_t *w, const float *x, float *y, double *y64, double *abs_dot, int n_rows,
+                   int n_cols);
+/* ---- INT8 KV cache: kernels.cu:1339-1376 (store), :1382-1480 (attention) ---- */
+void mo_f32_to_int8_kv(const float *in, int8_t *out, float *scales, int head_dim, int n_kv_heads);
+void mo_attention_int8kv(const float *q, const int8_t *kv_k, const int8_t *kv_v, const float *k_scales,
+                         const float *v_scales, float *out, int n_heads_q, int head_dim, int n_kv_heads, int seq_len,
+                         int gqa_ratio, float scale);
+
 int mo_num_threads(void);
 void mo_set_num_threads(int n);
 

@@ -297,6 +297,47 @@ def argmax(logits) -> int:
     return int(lib().mo_argmax(_p(logits), C.c_int(logits.size)))
 
 
+TYPE_BLOCK = {8: (32, 34), 11: (256, 110), 12: (256, 144), 13: (256, 176), 14: (256, 210)}  # weights, bytes per block
+
+
+def dequant_type(type_id: int, w, n_rows: int, n_cols: int) -> np.ndarray:
+    w = _u8(w)
+    out = np.zeros((n_rows, n_cols), np.float32)
+    lib().mo_dequant_type.restype = C.c_int
+    assert lib().mo_dequant_type(C.c_int(type_id), _p(w), C.c_int(n_rows), C.c_int(n_cols), _p(out)) == 0
+    return out
+
+
+def matvec_type(type_id: int, w, x, n_rows: int, n_cols: int, full: bool = False):
+    w, x = _u8(w), _f32(x)
+    y = np.zeros(n_rows, np.float32)
+    y64 = np.zeros(n_rows, np.float64) if full else None
+    ad = np.zeros(n_rows, np.float64) if full else None
+    lib().mo_matvec_type.restype = C.c_int
+    assert lib().mo_matvec_type(C.c_int(type_id), _p(w), _p(x), _p(y), _p(y64), _p(ad), C.c_int(n_rows), C.c_int(n_cols)) == 0
+    return (y, y64, ad) if full else y
+
+
+def f32_to_int8_kv(x, head_dim: int, n_kv_heads: int):
+    x = _f32(x)
+    out = np.zeros(n_kv_heads * head_dim, np.int8)
+    scales = np.zeros(n_kv_heads, np.float32)
+    lib().mo_f32_to_int8_kv(_p(x), _p(out), _p(scales), C.c_int(head_dim), C.c_int(n_kv_heads))
+    return out, scales
+
+
+def attention_int8kv(q, kv_k, kv_v, k_scales, v_scales, n_heads_q: int, head_dim: int, n_kv_heads: int, seq_len: int,
+                     gqa_ratio: int, scale: float) -> np.ndarray:
+    q = _f32(q)
+    k = np.ascontiguousarray(np.asarray(kv_k, dtype=np.int8))
+    v = np.ascontiguousarray(np.asarray(kv_v, dtype=np.int8))
+    ks, vs = _f32(k_scales), _f32(v_scales)
+    out = np.zeros(n_heads_q * head_dim, np.float32)
+    lib().mo_attention_int8kv(_p(q), _p(k), _p(v), _p(ks), _p(vs), _p(out), C.c_int(n_heads_q), C.c_int(head_dim),
+                              C.c_int(n_kv_heads), C.c_int(seq_len), C.c_int(gqa_ratio), C.c_float(scale))
+    return out
+
+
 def decode_layer(hidden, L: dict, cfg: dict, pos: int, kv_k_bits: np.ndarray, kv_v_bits: np.ndarray):
     """One transformer layer in the reference's op order (src/forward.c:670-823, 1114) on host arrays.
     L: the layer's tensors (attn_norm, wq, wk, wv, wo, q_norm, k_norm, ffn_norm, router, experts; types in
@@ -305,6 +346,8 @@ def decode_layer(hidden, L: dict, cfg: dict, pos: int, kv_k_bits: np.ndarray, kv
     H, NH, NKV, HD = cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"]
     eps, theta = cfg["rms_eps"], cfg["rope_theta"]
     mv = {12: matvec_q4k, 14: matvec_q6k}
+    for tid in (8, 11, 13):  # the other cases of the reference's matvec() switch (src/forward.c:160-173)
+        mv[tid] = (lambda t: lambda w, x, r, c: matvec_type(t, w, x, r, c))(tid)
     normed = rms_norm(hidden, L["attn_norm"], eps)
     q = mv[cfg["wq_type"]](L["wq"], normed, NH * HD, H)
     k = mv[cfg["wk_type"]](L["wk"], normed, NKV * HD, H)

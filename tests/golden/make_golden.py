@@ -17,6 +17,9 @@ Vectors:
                             nibble, subnormal and negative d, max scales)
   ragged                  : n_cols not a multiple of 256
   scale_min               : get_scale_min_k4 on every j for random 12-byte rows
+  q5k_* / q8_0_*          : seeded and ragged blocks through dequant_q5k_cuda_style / dequant_q8_0_cuda_style
+                            (the validator has no Q3_K function; that type is checked on the GPU against
+                            the reference's compiled kernel instead)
 support_golden.npz (from tools/validate_rope_norm.py's kernel replicas):
   rms_*                   : kernel_rms_norm on seeded vectors (hidden 2048 / 4096, head 128)
   rope_*                  : kernel_rope at positions 0, 1, 17, 4095, 8191 (16 + 2 heads of 128)
@@ -151,6 +154,15 @@ def main() -> None:
     w = synth.q6k_matrix(14, 2, 300)
     out["q6k_ragged_w"] = w
     out["q6k_ragged_ref"] = vd.dequant_q6k_reference(w.tobytes(), 2, 300)
+
+    # --- Q5_K and Q8_0 (the validator's restatements of the reference kernels) ---
+    for tag, tid, fn, gt in (("q5k", 13, vd.dequant_q5k_cuda_style, None), ("q8_0", 8, vd.dequant_q8_0_cuda_style, T.Q8_0)):
+        for name, seed, rows, cols in (("seeded", 16, 3, 1024), ("ragged", 17, 2, 300)):
+            w = synth.typed_matrix(tid, seed, rows, cols)
+            out[f"{tag}_{name}_w"] = w
+            out[f"{tag}_{name}_ref"] = np.asarray(fn(w.tobytes(), rows, cols), np.float32)
+            if gt is not None and name == "seeded":
+                assert np.array_equal(dequantize(w.reshape(rows, -1), gt), out[f"{tag}_{name}_ref"])
 
     # --- get_scale_min_k4 --------------------------------------------------
     sc_in = synth.words(15, 0, 48).view(np.uint8).reshape(32, 12)

@@ -196,3 +196,54 @@ def test_one_layer_at_the_235b_shape(K, pdl):
         rel = np.linalg.norm(got - want) / np.linalg.norm(want)
         assert rel <= 1e-3, rel
     assert K.mb200_device_error() == 0
+
+
+def test_split_model_directory_decodes_like_the_oracle(K, pdl, tmp_path):
+    """A model written in the reference's split-model layout (docs/model-format.md) with a different
+    weight type on every projection, Q4_K and Q6_K down projections on alternating layers and a Q3_K
+    embedding; loaded through split_model.read_split_dir and decoded: every layer and the greedy tokens
+    against the oracle on the same files."""
+    from mnemocuda_b200 import split_model as sm
+    from mnemocuda_b200.decode import DecodeConfig
+    cfg = DecodeConfig(**dict(SHAPES["tiny"], n_layers=2, ctx_len=128))
+    cfg.lm_head_type = 13
+    types = [(13, 8, 11, 12), (12, 12, 14, 8)]
+    parts = sm.synthetic_host_model(cfg, seed=11, types=types, down_types=[12, 14], embd_type=11)
+    sm.write_split_dir(str(tmp_path), cfg, *parts, embd_type=11)
+    split = sm.read_split_dir(str(tmp_path))
+    assert split.cfg.lm_head_type == 13 and [e.down_type for e in split.experts] == [12, 14]
+    model = split.to_device("cuda")
+    c = split.cfg
+    Ls = [split.host_layer(l) for l in range(c.n_layers)]
+    kv = [(np.zeros((c.ctx_len, c.n_kv_heads * c.head_dim), np.uint16), np.zeros((c.ctx_len, c.n_kv_heads * c.head_dim), np.uint16))
+          for _ in range(c.n_layers)]
+
+    def layer_cfg(l):
+        d = cfg_dict(c)
+        d["wq_type"], d["wk_type"], d["wv_type"], d["wo_type"] = Ls[l]["types"]
+        d["expert_stride"], d["gate_sz"], d["up_sz"], d["down_type"] = Ls[l]["expert_layout"]
+        return d
+
+    embd, lm, onorm = split.tensor("token_embd.weight"), split.tensor("output.weight"), split.tensor("output_norm.weight")
+    token, want_tokens, got_tokens = 5, [], []
+    model.set_state(token, 0)
+    for pos in range(4):
+        h = oracle.dequant_type(11, embd, c.vocab, c.hidden)[token]
+        model.begin()
+        assert np.array_equal(model.hidden.cpu().numpy(), h)
+        for l in range(c.n_layers):
+            h, _ = oracle.decode_layer(h, Ls[l], layer_cfg(l), pos, kv[l][0], kv[l][1])
+            model.layer(l)
+            got = model.hidden.cpu().numpy().astype(np.float64)
+            rel = np.linalg.norm(got - h) / np.linalg.norm(h)
+            assert rel <= 1e-3, (pos, l, rel)
+            h = got.astype(np.float32)  # teacher forcing: the next layer starts from the device's state
+            kv[l][0][pos] = model.layers[l]["kv_k"].cpu().numpy().view(np.uint16)[pos].reshape(-1)
+            kv[l][1][pos] = model.layers[l]["kv_v"].cpu().numpy().view(np.uint16)[pos].reshape(-1)
+        model.finish()
+        logits = oracle.matvec_type(13, lm, oracle.rms_norm(h, onorm, c.rms_eps), c.vocab, c.hidden)
+        got_logits = model.logits.cpu().numpy()
+        assert np.linalg.norm(got_logits - logits) <= 1e-3 * np.linalg.norm(logits)
+        token = int(model.token.item())
+        assert token == oracle.argmax(got_logits)
+        assert int(model.pos.item()) == pos + 1

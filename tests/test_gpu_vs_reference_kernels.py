@@ -104,3 +104,63 @@ def test_topk_matches_reference_kernel_bit_exact(ref, K, seed):
     torch.cuda.synchronize()
     assert torch.equal(i_got, i_ref)
     np.testing.assert_allclose(host(w_got), host(w_ref), rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("tid,name", [(8, "cuda_matvec_q8_0"), (13, "cuda_matvec_q5k"), (11, "cuda_matvec_q3k")])
+@pytest.mark.parametrize("rows,cols", [(4096, 4096), (512, 1536), (33, 1024)])
+def test_other_types_match_reference_kernels(ref, K, tid, name, rows, cols):
+    """Q8_0 / Q5_K / Q3_K: the reference's bit layouts (which for Q5_K and Q3_K are its own) through its
+    compiled kernels; this is what pins the Q3_K restatement, for which the validator has no function."""
+    w, x = dev(synth.typed_matrix(tid, 9, rows, cols)), dev(synth.normal_f32(10, cols))
+    y_ref, y = torch.empty(rows, device="cuda"), torch.empty(rows, device="cuda")
+    getattr(ref, name)(_p(w), _p(x), _p(y_ref), C.c_int(rows), C.c_int(cols), _s())
+    getattr(K, name)(w, x, y, rows, cols)
+    torch.cuda.synchronize()
+    assert _rel(y, y_ref) <= 1e-3
+
+
+def test_q3k_embedding_row_matches_reference_kernel(ref, K):
+    vocab, hidden = 40, 2048
+    w = dev(synth.typed_matrix(11, 11, vocab, hidden))
+    a, b = torch.empty(hidden, device="cuda"), torch.empty(hidden, device="cuda")
+    for tok in (0, 39):
+        ref.cuda_embedding_lookup_q3k(_p(w), _p(a), C.c_int(tok), C.c_int(hidden), C.c_int(hidden // 256 * 110), _s())
+        K.cuda_embedding_lookup_q3k(w, b, tok, hidden, hidden // 256 * 110)
+        torch.cuda.synchronize()
+        assert torch.equal(a, b)
+
+
+def test_int8_kv_store_and_attention_match_reference_kernels(ref, K):
+    """The reference is built with fast-math, so its 127 / absmax may differ in the last place: quantised
+    values may differ by one step on a few elements; scales to 1 ulp; attention to 1e-3."""
+    nh, nkv, hd, S = 32, 4, 128, 300
+    k, v = dev(synth.normal_f32(12, nkv * hd, 2.0)), dev(synth.normal_f32(13, nkv * hd))
+    outs = []
+    for which in ("ref", "ours"):
+        k8 = torch.empty(nkv * hd, dtype=torch.int8, device="cuda")
+        v8 = torch.empty(nkv * hd, dtype=torch.int8, device="cuda")
+        ks, vs = torch.empty(nkv, device="cuda"), torch.empty(nkv, device="cuda")
+        if which == "ref":
+            ref.cuda_f32_to_int8_kv_dual(_p(k), _p(v), _p(k8), _p(v8), _p(ks), _p(vs), C.c_int(hd), C.c_int(nkv), _s())
+        else:
+            K.cuda_f32_to_int8_kv_dual(k, v, k8, v8, ks, vs, hd, nkv)
+        torch.cuda.synchronize()
+        outs.append((host(k8).astype(np.int32), host(v8).astype(np.int32), host(ks), host(vs)))
+    for i in (0, 1):
+        d = np.abs(outs[0][i] - outs[1][i])
+        assert d.max() <= 1 and (d != 0).mean() <= 0.02
+    np.testing.assert_allclose(outs[0][2], outs[1][2], rtol=3e-7)
+    np.testing.assert_allclose(outs[0][3], outs[1][3], rtol=3e-7)
+    rng = np.random.default_rng(14)
+    k8 = dev(rng.integers(-127, 128, (S, nkv, hd), dtype=np.int8))
+    v8 = dev(rng.integers(-127, 128, (S, nkv, hd), dtype=np.int8))
+    ks = dev(((0.5 + rng.random((S, nkv))) / 127).astype(np.float32))
+    vs = dev(((0.5 + rng.random((S, nkv))) / 127).astype(np.float32))
+    q = dev(synth.normal_f32(15, nh * hd))
+    a, b = torch.empty(nh * hd, device="cuda"), torch.empty(nh * hd, device="cuda")
+    ref.cuda_attention_int8kv(_p(q), _p(k8), _p(v8), _p(ks), _p(vs), _p(a), C.c_int(nh), C.c_int(hd), C.c_int(nkv),
+                              C.c_int(S), C.c_int(nh // nkv), C.c_float(hd ** -0.5), _s())
+    K.cuda_attention_int8kv(q, k8, v8, ks, vs, b, nh, hd, nkv, S, nh // nkv, hd ** -0.5)
+    torch.cuda.synchronize()
+    a, b = host(a).reshape(nh, hd).astype(np.float64), host(b).reshape(nh, hd).astype(np.float64)
+    assert (np.linalg.norm(a - b, axis=1) / np.linalg.norm(a, axis=1)).max() <= 1e-3
