@@ -271,12 +271,12 @@ __global__ void __launch_bounds__(128) int8_kv_kernel(const float *in_a, const f
 // are merged by the last CTA of the KV head to arrive (ticket in the workspace).
 constexpr int kI8Warps = 8;
 constexpr int kI8MaxGqa = 8;    // query heads per CTA (registers: q and the running sums of each)
-constexpr int kI8Chunks = 8;
 constexpr int kI8Groups = 64;   // head groups per launch
+constexpr int kI8Slots = 512;   // (group, chunk) pairs per launch
 
-struct I8Work {  // library-resident workspace: 64 groups x 8 chunks x 8 query heads x (128 + 2) floats
-    float part[kI8Groups * kI8Chunks * kI8MaxGqa * 128];
-    float ml[kI8Groups * kI8Chunks * kI8MaxGqa * 2];
+struct I8Work {  // library-resident workspace: 512 slots x 8 query heads x (128 + 2) floats (2.1 MB per device)
+    float part[kI8Slots * kI8MaxGqa * 128];
+    float ml[kI8Slots * kI8MaxGqa * 2];
     int tickets[kI8Groups];
 };
 __device__ I8Work g_i8;
@@ -337,8 +337,8 @@ __global__ void __launch_bounds__(kI8Warps * 32) attn_int8_kernel(const float *q
     }
     __syncthreads();
     // the CTA's partial for this chunk
-    float *part = g_i8.part + ((size_t)(grp * kI8Chunks + chunk) * kI8MaxGqa) * 128;
-    float *ml = g_i8.ml + ((size_t)(grp * kI8Chunks + chunk) * kI8MaxGqa) * 2;
+    float *part = g_i8.part + ((size_t)(grp * chunks + chunk) * kI8MaxGqa) * 128;
+    float *ml = g_i8.ml + ((size_t)(grp * chunks + chunk) * kI8MaxGqa) * 2;
     for (int i = threadIdx.x; i < GQA * 128; i += blockDim.x) {
         const int h = i >> 7, d = i & 127;
         float M = -INFINITY;
@@ -364,10 +364,10 @@ __global__ void __launch_bounds__(kI8Warps * 32) attn_int8_kernel(const float *q
     for (int i = threadIdx.x; i < GQA * 128; i += blockDim.x) {
         const int h = i >> 7;
         float M = -INFINITY;
-        for (int c = 0; c < chunks; c++) M = fmaxf(M, __ldcg(g_i8.ml + ((size_t)(grp * kI8Chunks + c) * kI8MaxGqa + h) * 2));
+        for (int c = 0; c < chunks; c++) M = fmaxf(M, __ldcg(g_i8.ml + ((size_t)(grp * chunks + c) * kI8MaxGqa + h) * 2));
         float o = 0.0f, L = 0.0f;
         for (int c = 0; c < chunks; c++) {
-            const size_t b = (size_t)(grp * kI8Chunks + c) * kI8MaxGqa;
+            const size_t b = (size_t)(grp * chunks + c) * kI8MaxGqa;
             const float mc = __ldcg(g_i8.ml + (b + h) * 2);
             const float f = mc == -INFINITY ? 0.0f : __expf(mc - M);
             o += __ldcg(g_i8.part + b * 128 + i) * f;
@@ -440,8 +440,9 @@ void launch_attn_int8(const float *q, const void *kv_k, const void *kv_v, const 
                       int n_heads_q, int n_kv_heads, int gqa_ratio, int seq_len, float scale, cudaStream_t stream)
 {
     const int groups = n_heads_q / GQA;
-    int chunks = device_sms() / groups;
-    chunks = chunks < 1 ? 1 : (chunks > kI8Chunks ? kI8Chunks : chunks);
+    int chunks = 2 * device_sms() / groups;  // two CTAs per SM
+    if (chunks > kI8Slots / groups) chunks = kI8Slots / groups;
+    if (chunks < 1) chunks = 1;
     if (chunks > (seq_len + kI8Warps - 1) / kI8Warps) chunks = (seq_len + kI8Warps - 1) / kI8Warps;
     launch_k(attn_int8_kernel<GQA>, dim3(groups, chunks), dim3(kI8Warps * 32), 0, stream, q,
              static_cast<const int8_t *>(kv_k), static_cast<const int8_t *>(kv_v), ks, vs, out, n_kv_heads, seq_len, scale,
