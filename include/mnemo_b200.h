@@ -214,6 +214,11 @@ int mb200_norm_matvec_q6k(const void *weights, const float *x, const float *norm
                           int n_cols, cudaStream_t stream);
 int mb200_norm_matvec2_q4k(const void *wa, float *ya, int rows_a, const void *wb, float *yb, int rows_b, const float *x,
                            const float *norm_w, float eps, int n_cols, cudaStream_t stream);
+/* The decode path's three projections in one launch: Q and K in Q4_K, V in Q6_K (the Q4_K_M layout), sharing x.
+ * norm_w NULL = x is used as it is. Replaces the three launches of src/forward.c:688-704. */
+int mb200_norm_matvec_qkv(const void *wq, float *q, int q_rows, const void *wk, float *k, const void *wv, float *v,
+                          int kv_rows, const float *x, const float *norm_w, float eps, int n_cols,
+                          cudaStream_t stream);
 
 /* ---- decode-time MoE block with the routed expert ids kept on the device ----
  * The reference copies the k routed ids to the host and synchronises in every layer

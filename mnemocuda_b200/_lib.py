@@ -61,6 +61,7 @@ SIGNATURES = {
     "mb200_norm_matvec_q4k": (_i, [_vp, _vp, _vp, _f, _vp, _i, _i, _vp]),
     "mb200_norm_matvec_q6k": (_i, [_vp, _vp, _vp, _f, _vp, _i, _i, _vp]),
     "mb200_norm_matvec2_q4k": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _f, _i, _vp]),
+    "mb200_norm_matvec_qkv": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _f, _i, _vp]),
     "mb200_moe_block_norm": (_i, [_vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mb200_router_scratch_bytes": (_sz, [_i]),
     "mb200_router_topk": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),

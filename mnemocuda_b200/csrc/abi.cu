@@ -9,6 +9,7 @@ namespace mb200 {
 
 void q4k_init();
 void q6k_init();
+void pair_init();
 void gemm_init();
 void moe_fused_init();
 void router_static_init();
@@ -76,6 +77,7 @@ void cuda_kernels_init(void)
     // Everything here is per device: call once per device the engine drives, with that device current.
     q4k_init();
     q6k_init();
+    pair_init();
     gemm_init();
     moe_fused_init();
     support_init();

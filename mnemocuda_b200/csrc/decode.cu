@@ -19,6 +19,8 @@
 #include "support.cuh"
 
 namespace mb200 {
+void qkv_q4k_q6k(const void *wq, float *q, int q_rows, const void *wk, float *k, const void *wv, float *v, int kv_rows,
+                 const float *x, int n_cols, const float *norm_w, float norm_eps, cudaStream_t stream, const char *where);
 void q4k_matvec2(const void *wa, float *ya, int rows_a, const void *wb, float *yb, int rows_b, const float *x,
                  int n_cols, cudaStream_t stream, const char *where, const float *norm_w, float norm_eps);
 
@@ -127,13 +129,17 @@ int run_attention(const mb200_decode_model &m, const mb200_layer_weights &L, uin
     if (!fold) launch_rms_norm(B.hidden, L.attn_norm, B.normed, nullptr, H, m.rms_eps, s);
     const float *x = fold ? B.hidden : B.normed;
     const float *nw = fold ? L.attn_norm : nullptr;
-    if (L.wq_type == 12 && L.wk_type == 12) {
-        q4k_matvec2(L.wq, B.q, QD, L.wk, B.k, KD, x, H, s, "mb200_decode: Q,K projection", nw, m.rms_eps);
+    if (L.wq_type == 12 && L.wk_type == 12 && L.wv_type == 14) {  // the Q4_K_M layout: one launch for all three
+        qkv_q4k_q6k(L.wq, B.q, QD, L.wk, B.k, L.wv, B.v, KD, x, H, nw, m.rms_eps, s, "mb200_decode: Q,K,V projection");
     } else {
-        if ((rc = matvec_norm(L.wq, L.wq_type, x, nw, m.rms_eps, B.normed, B.q, QD, H, s)) != MB200_OK) return rc;
-        if ((rc = matvec_norm(L.wk, L.wk_type, x, nw, m.rms_eps, B.normed, B.k, KD, H, s)) != MB200_OK) return rc;
+        if (L.wq_type == 12 && L.wk_type == 12) {
+            q4k_matvec2(L.wq, B.q, QD, L.wk, B.k, KD, x, H, s, "mb200_decode: Q,K projection", nw, m.rms_eps);
+        } else {
+            if ((rc = matvec_norm(L.wq, L.wq_type, x, nw, m.rms_eps, B.normed, B.q, QD, H, s)) != MB200_OK) return rc;
+            if ((rc = matvec_norm(L.wk, L.wk_type, x, nw, m.rms_eps, B.normed, B.k, KD, H, s)) != MB200_OK) return rc;
+        }
+        if ((rc = matvec_norm(L.wv, L.wv_type, x, nw, m.rms_eps, B.normed, B.v, KD, H, s)) != MB200_OK) return rc;
     }
-    if ((rc = matvec_norm(L.wv, L.wv_type, x, nw, m.rms_eps, B.normed, B.v, KD, H, s)) != MB200_OK) return rc;
     // 3-5. q/k norm, RoPE, fp16 KV store at the position
     launch_qk_norm_rope_store(B.q, B.k, B.v, L.q_norm, L.k_norm, B.cos_t, B.sin_t, L.kv_k, L.kv_v, m.n_heads,
                               m.n_kv_heads, m.head_dim, m.rms_eps, d_pos, 0, s);

@@ -414,7 +414,7 @@ __device__ __noinline__ bool route_select(const FusedParams &P, unsigned long lo
     topk_group_sync(2, 128);
     if (warp == 0) MB200_STAMP(4);
     TopkShared &tsh = *reinterpret_cast<TopkShared *>(ring);  // the ring is idle until the first tile is requested
-    topk_softmax_group(const_cast<const float *>(static_cast<volatile float *>(P.logits)), rid, rwt, P.n_experts,
+    topk_softmax_group<false>(const_cast<const float *>(static_cast<volatile float *>(P.logits)), rid, rwt, P.n_experts,
                        P.n_slots, tsh, 4, 2);
     if (warp == 0) {
         MB200_STAMP(6);
@@ -425,6 +425,34 @@ __device__ __noinline__ bool route_select(const FusedParams &P, unsigned long lo
         }
     }
     return ok;
+}
+
+// A consumer warp's share of the activation staging of batch `batch` (whose fp32 vectors have landed in the raw
+// buffer): columns [128 w, 128 w + 128) of each vector of the batch -> the int8 levels of the down phase.
+template <class FD>
+__device__ __noinline__ void split_share(const FusedParams &P, uint8_t *smem, const Layout &LC, int batch, int n_act,
+                                         uint64_t *rawempty, uint64_t *xready)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int u = batch & 1;
+    const int pitch = FD::kSlotsPerBlock * P.bprC + 1;
+    const int j0 = batch * kBatchSlots, jn = min(kBatchSlots, n_act - j0);
+    const float *raw = reinterpret_cast<const float *>(smem + P.off_raw + u * P.raw_bytes);
+    for (int c0 = warp * 128 + lane * 4; c0 < P.EFF; c0 += kConsumers * 128) {
+#pragma unroll 1
+        for (int j = 0; j < jn; j++) {
+            const float4 v = *reinterpret_cast<const float4 *>(raw + (size_t)j * P.EFF + c0);
+            uint8_t *xc = smem + P.off_xc + (j0 + j) * P.xc_stride - kXBase;
+            split_store<FD>(v, c0, lane, pitch, reinterpret_cast<uint32_t *>(xc + LC.xq1),
+                            reinterpret_cast<uint32_t *>(xc + LC.xq2), reinterpret_cast<float *>(xc + LC.xs1),
+                            reinterpret_cast<float *>(xc + LC.xsum));
+        }
+    }
+    __syncwarp();
+    if (lane == 0) {
+        mbar_arrive(&xready[batch]);  // release: this warp's share of the levels is visible to whoever waits
+        mbar_arrive(&rawempty[u]);    // and it no longer reads the raw buffer
+    }
 }
 
 template <class FD>
@@ -718,6 +746,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     // them -- columns [128 w, 128 w + 128) of each vector -- into the int8 levels of the down phase.
     // By the time the batch's first down tile comes up all twelve shares are normally long done.
     int n_q = 0;  // batches this warp has done its share of
+    // The test is inline (one mbarrier probe per tile); the split itself is a call, so that the two hot loops
+    // below stay small (instruction fetch is what they stall on most).
     auto stage_share = [&](bool blocking) {
         while (n_q < nb) {
             const int u = n_q & 1, par = (n_q >> 1) & 1;
@@ -729,26 +759,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             } else if (!mbar_test_wait(&rawfull[u], par)) {
                 return;
             }
-            const int pitch = FD::kSlotsPerBlock * P.bprC + 1;
-            const int j0 = n_q * kBatchSlots, jn = min(kBatchSlots, n_act - j0);
-            const float *raw = reinterpret_cast<const float *>(smem + P.off_raw + u * P.raw_bytes);
-            for (int c0 = warp * 128 + lane * 4; c0 < P.EFF; c0 += kConsumers * 128) {
-#pragma unroll
-                for (int j = 0; j < kBatchSlots; j++) {
-                    if (j < jn) {
-                        const float4 v = *reinterpret_cast<const float4 *>(raw + (size_t)j * P.EFF + c0);
-                        uint8_t *xc = smem + P.off_xc + (j0 + j) * P.xc_stride - kXBase;
-                        split_store<FD>(v, c0, lane, pitch, reinterpret_cast<uint32_t *>(xc + LC.xq1),
-                                        reinterpret_cast<uint32_t *>(xc + LC.xq2), reinterpret_cast<float *>(xc + LC.xs1),
-                                        reinterpret_cast<float *>(xc + LC.xsum));
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&xready[n_q]);   // release: this warp's share of the levels is visible to whoever waits
-                mbar_arrive(&rawempty[u]);   // and it no longer reads the raw buffer
-            }
+            split_share<FD>(P, smem, LC, n_q, n_act, rawempty, xready);
             n_q++;
             if (blocking) return;
         }
@@ -1014,7 +1025,7 @@ int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off
     P.norm_eps = norm_eps;
     if (router_w) {
         // the group top-k covers n_experts <= 32 * k and <= 512; 16-byte loads of the router rows
-        if (n_experts < 1 || n_experts > 512 || n_experts > 32 * n_slots || !logits || !ids_out || !wts_out)
+        if (n_experts < 1 || n_experts > 512 || n_experts > 32 * n_slots || n_slots > 16 || !logits || !ids_out || !wts_out)
             return MB200_ERR_UNSUPPORTED;
         if ((reinterpret_cast<uintptr_t>(router_w) & 15) || (H & 3)) return MB200_ERR_UNSUPPORTED;
         P.router_w = router_w;

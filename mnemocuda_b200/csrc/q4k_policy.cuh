@@ -21,6 +21,7 @@ namespace {
 struct Q4 {
     static constexpr int kBlockBytes = kQ4KBlock;
     static constexpr int kLanesPerBlock = 4;
+    static constexpr float kByteCost = 1.0f;  // relative consumer time per weight byte (splits a shared launch)
     static constexpr int kG = 8;
     static constexpr int kSumCols = 16;
     static constexpr bool kGroup4Tail = true;  // reference src/kernels.cu:124,131

@@ -47,6 +47,7 @@ __device__ __forceinline__ void lds8(const uint8_t *p, uint32_t &w0, uint32_t &w
 struct Q6 {
     static constexpr int kBlockBytes = kQ6KBlock;
     static constexpr int kLanesPerBlock = 4;
+    static constexpr float kByteCost = 2.0f;  // relative consumer time per weight byte (splits a shared launch)
     static constexpr int kG = 8;
     static constexpr int kSumCols = 16;
     static constexpr bool kGroup4Tail = false;  // per-element tail, reference src/kernels.cu:474

@@ -72,6 +72,8 @@ struct Params {
     float scale;
     int n_cols, bpr, mode, stages;
     int pdl;        // launched with programmatic stream serialization: wait for the upstream grid before touching x / y
+    int cta0, ncta; // this problem's CTAs are blockIdx.x in [cta0, cta0 + ncta) (two problems may share one launch)
+    int ru;         // row unroll chosen by the host (read by the pair kernel, which holds all three bodies)
     int *err;
     // routed-expert modes
     const int *ids;          // [n_slots] expert index per slot (device); < 0 = empty slot
@@ -143,8 +145,9 @@ struct TileWalk {
         act = act_list;
         n_act = n_active;
         const int vrows = (P.mode == kMoeGateUp) ? n_active * P.erows : P.vrows;
-        cur = static_cast<int>((long long)vrows * blockIdx.x / gridDim.x);
-        end = static_cast<int>((long long)vrows * (blockIdx.x + 1) / gridDim.x);
+        const int cta = static_cast<int>(blockIdx.x) - P.cta0;
+        cur = static_cast<int>((long long)vrows * cta / P.ncta);
+        end = static_cast<int>((long long)vrows * (cta + 1) / P.ncta);
         if (P.mode == kMoeDown && n_active == 0) end = cur;
         e = 0;
     }
@@ -461,9 +464,8 @@ __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.w
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <class F, int RU>
-__global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_constant__ Params P)
+__device__ __forceinline__ void stream_body(const Params &P, uint8_t *smem)
 {
-    extern __shared__ __align__(128) uint8_t smem[];
     const int S = P.stages;
     const bool pairs = pair_mode(P.mode);
     const bool routed = (P.mode == kMoeGateUp || P.mode == kMoeDown);
@@ -544,8 +546,9 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
         walk.init(P, act_list, routed ? *n_act_p : 0);
         if (P.mode == kMoeDown && walk.n_act == 0 && P.residual) {
             // no routed expert lives on this device: the block reduces to the residual
-            const int r0 = static_cast<int>((long long)P.vrows * blockIdx.x / gridDim.x);
-            const int r1 = static_cast<int>((long long)P.vrows * (blockIdx.x + 1) / gridDim.x);
+            const int cta = static_cast<int>(blockIdx.x) - P.cta0;
+            const int r0 = static_cast<int>((long long)P.vrows * cta / P.ncta);
+            const int r1 = static_cast<int>((long long)P.vrows * (cta + 1) / P.ncta);
             for (int r = r0 + lane; r < r1; r += 32) P.seg[0].y[r] = __ldcg(P.residual + r);
         }
         Tile t, ahead;
@@ -711,6 +714,36 @@ __global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_consta
     if (warp == 0) MB200_STAMP(5);
 }
 
+template <class F, int RU>
+__global__ void __launch_bounds__(kThreads, 1) stream_kernel(const __grid_constant__ Params P)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    stream_body<F, RU>(P, smem);
+}
+
+// Two independent problems with different block types in one launch: CTAs [0, PA.ncta) run A, the others B
+// (the decode path's Q4_K Q / K projections and Q6_K V projection, which share x).
+template <class F>
+__device__ __forceinline__ void stream_body_any(const Params &P, uint8_t *smem)
+{
+    if (P.ru == 4)
+        stream_body<F, 4>(P, smem);
+    else if (P.ru == 2)
+        stream_body<F, 2>(P, smem);
+    else
+        stream_body<F, 1>(P, smem);
+}
+template <class FA, class FB>
+__global__ void __launch_bounds__(kThreads, 1) stream_pair_kernel(const __grid_constant__ Params PA,
+                                                                  const __grid_constant__ Params PB)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    if (static_cast<int>(blockIdx.x) < PA.ncta)
+        stream_body_any<FA>(PA, smem);
+    else
+        stream_body_any<FB>(PB, smem);
+}
+
 // 0: plain launches. 1: launches carry the programmatic-stream-serialization
 // attribute, so a kernel may start while the previous kernel of the stream is
 // still draining; it then prefetches weights early and waits for that kernel
@@ -752,22 +785,23 @@ inline void init_attrs()
     done[dev] = true;
 }
 
-// Host-side geometry + launch. Segment pointers/rows, x, mode etc. are set by the caller.
+// Host-side geometry. Segment pointers/rows, x, mode etc. are set by the caller; fills in the rest of P, the
+// shared-memory layout, the grid (at most grid_cap CTAs when that is > 0) and the row unroll (force_ru > 0 fixes it).
+// Returns false when there is nothing to launch (empty problem, or an error that has been recorded).
 template <class F>
-inline void launch(Params &P, cudaStream_t stream, const char *where)
+inline bool prepare(Params &P, const char *where, int grid_cap, int force_ru, Layout &L_out, int &grid_out, int &ru_out)
 {
-    init_attrs<F>();
-    if (P.n_cols <= 0) return;
+    if (P.n_cols <= 0) return false;
     if (P.n_cols > F::kMaxCols) {
         fprintf(stderr, "[mnemo_b200] %s: n_cols=%d exceeds the supported %d\n", where, P.n_cols, F::kMaxCols);
         set_status(MB200_ERR_UNSUPPORTED, where);
-        return;
+        return false;
     }
     if (P.norm_w && (P.mode == kMoeDown || P.n_cols > 4 * 3 * kQuantThreads)) {
         fprintf(stderr, "[mnemo_b200] %s: the fused RMSNorm covers one activation vector of at most %d columns\n", where,
                 4 * 3 * kQuantThreads);
         set_status(MB200_ERR_UNSUPPORTED, where);
-        return;
+        return false;
     }
     const bool routed = (P.mode == kMoeGateUp || P.mode == kMoeDown);
     bool misaligned = false;
@@ -784,7 +818,7 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
         fprintf(stderr, "[mnemo_b200] %s: a weight tensor is not %d-byte aligned (or bad slot count)\n", where,
                 F::kBaseAlign);
         set_status(MB200_ERR_ARG, where);
-        return;
+        return false;
     }
     P.bpr = (P.n_cols + 255) / 256;
     const int row_bytes = P.bpr * F::kBlockBytes;
@@ -805,7 +839,7 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
         if (NG > kConsumers) {
             fprintf(stderr, "[mnemo_b200] %s: n_cols=%d needs more column groups than consumer warps\n", where, P.n_cols);
             set_status(MB200_ERR_UNSUPPORTED, where);
-            return;
+            return false;
         }
         for (int g = 0; g < NG; g++) {
             const int vv = (g == NG - 1) ? P.bpr - g * F::kG : F::kG;
@@ -851,9 +885,9 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
             vrows += P.seg[i].rows > 0 ? P.seg[i].rows : 0;
         }
     }
-    if (vrows <= 0) return;
+    if (vrows <= 0) return false;
     P.vrows = vrows;
-    const int sms = device_sms();
+    const int sms = grid_cap > 0 ? grid_cap : device_sms();
     const int grid = vrows < sms ? vrows : sms;
     const int per_cta = (vrows + grid - 1) / grid;  // rows of the longest range
     const int mult = (P.mode == kSwiGLU || P.mode == kMoeGateUp) ? 2 : 1;  // stage rows per virtual row
@@ -869,6 +903,7 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
             ru = cand;
         }
     }
+    if (force_ru > 0) ru = force_ru;
     // tile: a whole number of sweeps near the target size, never more than the range
     const int sweep = sweep1 * ru;
     int target = F::kTileTargetBytes / row_bytes;  // stage rows
@@ -900,11 +935,27 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
     if (L.total > 227 * 1024) {
         fprintf(stderr, "[mnemo_b200] %s: shape does not fit shared memory\n", where);
         set_status(MB200_ERR_UNSUPPORTED, where);
-        return;
+        return false;
     }
     P.stages = S;
     P.pdl = pdl_mode();
     P.err = device_error_word();
+    P.cta0 = 0;
+    P.ncta = grid;
+    P.ru = ru;
+    L_out = L;
+    grid_out = grid;
+    ru_out = ru;
+    return true;
+}
+
+template <class F>
+inline void launch(Params &P, cudaStream_t stream, const char *where)
+{
+    init_attrs<F>();
+    Layout L;
+    int grid, ru;
+    if (!prepare<F>(P, where, 0, 0, L, grid, ru)) return;
     if (ru == 4)
         launch_one<F, 4>(P, L, grid, stream);
     else if (ru == 2)
@@ -912,6 +963,52 @@ inline void launch(Params &P, cudaStream_t stream, const char *where)
     else
         launch_one<F, 1>(P, L, grid, stream);
     MB200_CHECK_LAUNCH(where);
+}
+
+// Two problems of block types FA and FB in one launch, the SMs divided between them in proportion to their
+// cost; each half runs with the row unroll it would choose alone.
+// Returns false (nothing launched) when a half is empty or invalid: the caller then issues single launches.
+template <class FA, class FB>
+inline bool launch_pair(Params &PA, Params &PB, cudaStream_t stream, const char *where)
+{
+    static bool done[kMaxDevices] = {false};
+    const int dev = current_device();
+    if (!done[dev]) {
+        cudaFuncSetAttribute(stream_pair_kernel<FA, FB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        done[dev] = true;
+    }
+    auto bytes = [](const Params &P, int block_bytes) {
+        double b = 0.0;
+        for (int i = 0; i < P.nseg; i++) b += (double)(P.seg[i].rows > 0 ? P.seg[i].rows : 0) * ((P.n_cols + 255) / 256) * block_bytes;
+        return b;
+    };
+    // cost, not bytes: a CTA's few hundred KB arrive faster than its warps get through them, and a type's dot
+    // product costs kByteCost per byte (Q6_K about twice Q4_K: measured best split of the Q / K / V launch)
+    const double ba = bytes(PA, FA::kBlockBytes) * FA::kByteCost, bb = bytes(PB, FB::kBlockBytes) * FB::kByteCost;
+    const int sms = device_sms();
+    int gb = static_cast<int>(sms * bb / (ba + bb) + 0.5);
+    gb = gb < 1 ? 1 : (gb > sms - 1 ? sms - 1 : gb);
+    Layout LA, LB;
+    int ga = sms - gb, rua = 0, rub = 0;
+    Params A2 = PA, B2 = PB;
+    const bool ok = prepare<FA>(A2, where, ga, 0, LA, ga, rua) && prepare<FB>(B2, where, gb, 0, LB, gb, rub);
+    if (!ok) return false;
+    PA = A2;
+    PB = B2;
+    PB.cta0 = ga;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ga + gb);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = LA.total > LB.total ? LA.total : LB.total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = PA.pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, stream_pair_kernel<FA, FB>, PA, PB);
+    MB200_CHECK_LAUNCH(where);
+    return true;
 }
 
 }  // namespace stream

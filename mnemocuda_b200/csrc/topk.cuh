@@ -373,13 +373,16 @@ __device__ __forceinline__ void topk_group_sync(int bar_id, int n_threads)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(n_threads) : "memory");
 }
+// kBigShapes = false leaves out the one-warp general form for n_experts > 32 k or > 512 (a third of a megabyte of
+// code): for a caller that has checked the shape on the host.
+template <bool kBigShapes = true>
 __device__ __forceinline__ void topk_softmax_group(const float *scores, int *indices, float *weights, int n_experts,
                                                    int k, TopkShared &sh, int n_warps, int bar_id)
 {
     const unsigned full = 0xffffffffu;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (n_experts > 32 * k || k > 16 || n_experts > 512) {  // block-uniform
-        if (warp == 0) topk_softmax_warp(scores, indices, weights, n_experts, k, sh);
+        if (kBigShapes && warp == 0) topk_softmax_warp(scores, indices, weights, n_experts, k, sh);
         return;
     }
     // ---- candidates in the reference's (lane, slot) order: lane l holds scores l, l + 32, ... ----

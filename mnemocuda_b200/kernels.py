@@ -259,6 +259,13 @@ def mb200_norm_matvec2_q4k(wa, ya, rows_a, wb, yb, rows_b, x, norm_w, eps, n_col
                                              float(eps), n_cols, _stream(stream)), "mb200_norm_matvec2_q4k")
 
 
+def mb200_norm_matvec_qkv(wq, q, q_rows, wk, k, wv, v, kv_rows, x, norm_w, eps, n_cols, stream=None):
+    """Q, K (Q4_K) and V (Q6_K) projections of RMSNorm(x) (norm_w None: of x) in one launch."""
+    _check(_lib.lib().mb200_norm_matvec_qkv(_ptr(wq), _f32(q), q_rows, _ptr(wk), _f32(k), _ptr(wv), _f32(v), kv_rows,
+                                            _f32(x), _ptr(norm_w) if norm_w is not None else None, float(eps), n_cols,
+                                            _stream(stream)), "mb200_norm_matvec_qkv")
+
+
 def mb200_moe_block_norm(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts, expert_lo, expert_cnt, k,
                          H, EFF, x, norm_w, eps, normed_scratch, residual, out, ids, wts, act, scratch, stream=None):
     """mb200_moe_block_local on RMSNorm(x), the norm folded into the one-launch form."""

@@ -128,8 +128,10 @@ def _run(which: str) -> None:
         if col.size:
             print(f"  {name:28s} min {col.min() / 1e3:7.2f}  median {np.median(col) / 1e3:7.2f}  max {col.max() / 1e3:7.2f} us")
     for base, name in ((40, "down tile requested"), (24, "down tile landed"), (16, "down tile finished")):
-        cols = [np.median(t[:, base + k] - t0) / 1e3 for k in range(4 if base == 40 else 8)]
-        print(f"  {name:28s} " + " ".join(f"{c:7.2f}" for c in cols))
+        n = 4 if base == 40 else 8
+        for fn, tag in ((np.min, "min"), (np.median, "median"), (np.max, "max")):
+            cols = [fn(t[:, base + k] - t0) / 1e3 for k in range(n)]
+            print(f"  {name:21s} {tag:6s} " + " ".join(f"{c:7.2f}" for c in cols))
 
 
 if __name__ == "__main__":

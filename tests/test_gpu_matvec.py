@@ -334,3 +334,24 @@ def test_rmsnorm_folded_two_tensors_and_width_limit(K):
         K.mb200_norm_matvec_q4k(dev(synth.q4k_matrix(314, 4, wide)), dev(synth.normal_f32(315, wide)),
                                 dev(np.ones(wide, np.float32)), 1e-6, yw, 4, wide)
     assert float(yw.min()) == 5.0
+
+
+@pytest.mark.parametrize("q_rows,kv_rows,cols,with_norm", [(8192, 512, 4096, True), (4096, 512, 2048, True),
+                                                           (2048, 256, 4096, False), (512, 256, 512, True),
+                                                           (130, 7, 768, True), (64, 8, 256, False)])
+def test_qkv_in_one_launch(K, q_rows, kv_rows, cols, with_norm):
+    """Q, K (Q4_K) and V (Q6_K) projections of RMSNorm(x) in one launch of the pair kernel, against the oracle's
+    three matvecs (shapes: the 235B and 30B projections, a KV shard of one head pair, ragged ones)."""
+    wq, wk = synth.q4k_matrix(5000, q_rows, cols), synth.q4k_matrix(5001, kv_rows, cols)
+    wv = synth.q6k_matrix(5002, kv_rows, cols)
+    x = synth.normal_f32(5003, cols, 3.0)
+    nw = (1.0 + 0.1 * synth.normal_f32(5004, cols)).astype(np.float32)
+    xn = oracle.rms_norm(x, nw, 1e-6) if with_norm else x
+    q, k, v = (torch.full((n,), float("nan"), device="cuda") for n in (q_rows, kv_rows, kv_rows))
+    for rep in range(2):
+        K.mb200_norm_matvec_qkv(dev(wq), q, q_rows, dev(wk), k, dev(wv), v, kv_rows, dev(x), dev(nw) if with_norm else None,
+                                1e-6, cols)
+        for got, (w, fn, rows) in ((q, (wq, oracle.matvec_q4k, q_rows)), (k, (wk, oracle.matvec_q4k, kv_rows)),
+                                   (v, (wv, oracle.matvec_q6k, kv_rows))):
+            _, y64, ad = fn(w, xn, rows, cols, full=True)
+            assert_close_matvec(host(got), y64, ad, f"qkv {rows}x{cols} rep {rep}")
