@@ -187,8 +187,8 @@ struct FWalk {
 
 // One warp: reads the routed ids and weights (one round trip), compacts the slots served here, and
 // lists this CTA's gate/up tiles. Returns the number of served slots.
-__device__ __forceinline__ int build_tiles(const FusedParams &P, const int *ids, const float *wts, int lane, int *sid,
-                                           float *swt, int *act_list, int2 *tiles, int *n_tiles_p)
+__device__ __noinline__ int build_tiles(const FusedParams &P, const int *ids, const float *wts, int lane, int *sid,
+                                        float *swt, int *act_list, int2 *tiles, int *n_tiles_p)
 {
     int id = -1;
     float w = 0.0f;
@@ -394,6 +394,40 @@ __device__ __noinline__ void route_logits(const FusedParams &P, float *rred)
 
 // Every CTA selects the experts itself, from the logits all CTAs have stored: warps 0-3. Returns
 // false (on thread 0) if the routing barrier did not complete within the poll budget.
+// The group top-k as a function of its own (one copy of the code: the warm-up pass below runs the very
+// instructions the routing warps will run).
+__device__ __noinline__ void route_topk(const float *scores, int *ids, float *wts, int n_experts, int k, TopkShared *sh,
+                                        int n_warps, int bar_id, int warp0)
+{
+    topk_softmax_group<false>(scores, ids, wts, n_experts, k, *sh, n_warps, bar_id, warp0);
+}
+
+// Instruction-cache warm-up. The selection is a few thousand instructions of run-once code; fetched cold it
+// takes 5-7 us during which nothing streams. The three service warps have nothing to do until the routing is
+// done, so at kernel entry they run the same code on made-up scores (distinct values, hence the tie-free path
+// the real logits take) with outputs in an idle part of the ring; when the routing warps get there, the
+// instructions are in the SM's instruction cache.
+__device__ __forceinline__ void route_warmup(const FusedParams &P, uint8_t *ring)
+{
+    const int lane = threadIdx.x & 31;
+    uint8_t *base = ring + 64 * 1024;  // the routing warps use the first bytes of the ring
+    float *scores = reinterpret_cast<float *>(base);
+    int *ids = reinterpret_cast<int *>(base + 2048);
+    float *wts = reinterpret_cast<float *>(base + 2048 + 64);
+    TopkShared *sh = reinterpret_cast<TopkShared *>(base + 4096);
+    const int warp = static_cast<int>(threadIdx.x >> 5) - kConsumers;
+    for (int i = warp * 32 + lane; i < P.n_experts; i += 96)
+        scores[i] = static_cast<float>((i * 37) % 509) * 0.01f - 2.0f;  // distinct for i < 509
+    asm volatile("bar.sync 5, 96;" ::: "memory");
+    route_topk(scores, ids, wts, P.n_experts, P.n_slots, sh, 3, 5, kConsumers);
+    if (warp == 0) {  // the issuer's tile list from the made-up selection: same idea, its code is run-once too
+        __syncwarp();
+        int *scratch = reinterpret_cast<int *>(base + 3072);
+        build_tiles(P, ids, wts, lane, scratch, reinterpret_cast<float *>(scratch + 16), scratch + 32,
+                    reinterpret_cast<int2 *>(scratch + 64), scratch + 48);
+    }
+}
+
 __device__ __noinline__ bool route_select(const FusedParams &P, unsigned long long tgt_route, int *rid, float *rwt,
                                           uint8_t *ring)
 {
@@ -414,8 +448,8 @@ __device__ __noinline__ bool route_select(const FusedParams &P, unsigned long lo
     topk_group_sync(2, 128);
     if (warp == 0) MB200_STAMP(4);
     TopkShared &tsh = *reinterpret_cast<TopkShared *>(ring);  // the ring is idle until the first tile is requested
-    topk_softmax_group<false>(const_cast<const float *>(static_cast<volatile float *>(P.logits)), rid, rwt, P.n_experts,
-                       P.n_slots, tsh, 4, 2);
+    route_topk(const_cast<const float *>(static_cast<volatile float *>(P.logits)), rid, rwt, P.n_experts, P.n_slots, &tsh,
+               4, 2, 0);
     if (warp == 0) {
         MB200_STAMP(6);
         __syncwarp();
@@ -489,6 +523,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     const int S = P.stages;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (warp == 0) MB200_STAMP(0);
+    if (P.router_w && warp >= kConsumers) route_warmup(P, stages);
 #ifdef MB200_TRACE
     unsigned launch_no = 0;
     if (blockIdx.x == 0 && tid == 0) {

@@ -375,12 +375,13 @@ __device__ __forceinline__ void topk_group_sync(int bar_id, int n_threads)
 }
 // kBigShapes = false leaves out the one-warp general form for n_experts > 32 k or > 512 (a third of a megabyte of
 // code): for a caller that has checked the shape on the host.
+// The group is warps [warp0, warp0 + n_warps) of the CTA.
 template <bool kBigShapes = true>
 __device__ __forceinline__ void topk_softmax_group(const float *scores, int *indices, float *weights, int n_experts,
-                                                   int k, TopkShared &sh, int n_warps, int bar_id)
+                                                   int k, TopkShared &sh, int n_warps, int bar_id, int warp0 = 0)
 {
     const unsigned full = 0xffffffffu;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = static_cast<int>(threadIdx.x >> 5) - warp0;
     if (n_experts > 32 * k || k > 16 || n_experts > 512) {  // block-uniform
         if (kBigShapes && warp == 0) topk_softmax_warp(scores, indices, weights, n_experts, k, sh);
         return;
