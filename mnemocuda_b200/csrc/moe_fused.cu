@@ -473,13 +473,15 @@ __device__ __noinline__ void split_share(const FusedParams &P, uint8_t *smem, co
     const int j0 = batch * kBatchSlots, jn = min(kBatchSlots, n_act - j0);
     const float *raw = reinterpret_cast<const float *>(smem + P.off_raw + u * P.raw_bytes);
     for (int c0 = warp * 128 + lane * 4; c0 < P.EFF; c0 += kConsumers * 128) {
-#pragma unroll 1
-        for (int j = 0; j < jn; j++) {
-            const float4 v = *reinterpret_cast<const float4 *>(raw + (size_t)j * P.EFF + c0);
-            uint8_t *xc = smem + P.off_xc + (j0 + j) * P.xc_stride - kXBase;
-            split_store<FD>(v, c0, lane, pitch, reinterpret_cast<uint32_t *>(xc + LC.xq1),
-                            reinterpret_cast<uint32_t *>(xc + LC.xq2), reinterpret_cast<float *>(xc + LC.xs1),
-                            reinterpret_cast<float *>(xc + LC.xsum));
+#pragma unroll
+        for (int j = 0; j < kBatchSlots; j++) {  // unrolled: the two vectors' shuffle chains overlap
+            if (j < jn) {
+                const float4 v = *reinterpret_cast<const float4 *>(raw + (size_t)j * P.EFF + c0);
+                uint8_t *xc = smem + P.off_xc + (j0 + j) * P.xc_stride - kXBase;
+                split_store<FD>(v, c0, lane, pitch, reinterpret_cast<uint32_t *>(xc + LC.xq1),
+                                reinterpret_cast<uint32_t *>(xc + LC.xq2), reinterpret_cast<float *>(xc + LC.xs1),
+                                reinterpret_cast<float *>(xc + LC.xsum));
+            }
         }
     }
     __syncwarp();
