@@ -156,9 +156,13 @@ void cuda_f32_to_int8_kv_dual(const float *k, const float *v, void *out_k, void 
 void cuda_attention_int8kv(const float *q, const void *kv_k, const void *kv_v, const float *k_scales,
                            const float *v_scales, float *out, int n_heads_q, int head_dim, int n_kv_heads,
                            int seq_len, int gqa_ratio, float scale, cudaStream_t stream);
-/* Greedy sampling: *d_result = argmax(logits), ties resolved as the reference's scan does
- * (src/kernels.cu:2048-2071). temperature > 0 (nucleus sampling, :2073-2174) is not implemented:
- * the argmax is returned and mb200_last_status() reports MB200_ERR_UNSUPPORTED. Replaces :2208-2215. */
+/* Sampling of one token. temperature <= 0: *d_result = argmax(logits), ties resolved as the reference's scan does
+ * (src/kernels.cu:2048-2071). temperature > 0: softmax with temperature and top-p nucleus sampling with the
+ * reference's candidate rule (the eight most probable tokens of every residue class mod 256), its xoroshiro128+
+ * draw from rng_state and its walk over the nucleus (src/kernels.cu:2073-2174); the same token as the reference
+ * unless the cut or the draw falls within float rounding of a boundary (the reference is built with fast-math and
+ * adds the probabilities in another order). Two launches; scratch inside the library image, so calls on one
+ * device must not overlap. Replaces :2208-2215. */
 void cuda_sample_token(const float *logits, int vocab_size, float temperature, float top_p,
                        unsigned long long rng_state, int *d_result, cudaStream_t stream);
 /* Addresses of the RoPE, KV-store and attention kernels, whose parameter order is the reference's, for a

@@ -695,6 +695,188 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ l
     }
 }
 
+// ------------------------------------------------- temperature + top-p ----
+// The reference samples in one 256-thread block (src/kernels.cu:2073-2174): p_i = exp((l_i - max) / T), every
+// thread keeps the eight largest p of its residue class i mod 256, thread 0 picks the 2048 candidates largest
+// first until their sum reaches top_p * sum(p), draws once from xoroshiro128+ and walks the nucleus. Here:
+// the maximum comes from the argmax scan above; 32 CTAs scan eight residue classes each (so that a warp's loads
+// are whole 32-byte sectors), merge the classes' candidates, and the last CTA to finish (ticket) sorts the 2048
+// candidates and walks them with the reference's arithmetic (float sums in descending order). Among equal
+// probabilities the smaller token id is preferred; the sum of all p is added in another order than the
+// reference's, so a cut that falls within rounding of top_p * sum can come out one candidate apart.
+constexpr int kSampleClasses = 256, kSampleKeep = 8, kSampleCands = kSampleClasses * kSampleKeep;
+constexpr int kSampleCtas = kSampleClasses / 8;
+__device__ float g_sample_pair[2];
+__device__ float g_sample_p[kSampleCands];
+__device__ int g_sample_id[kSampleCands];
+__device__ float g_sample_sum[kSampleCtas];
+__device__ int g_sample_ticket;
+
+__device__ __forceinline__ bool cand_better(float p, int id, float bp, int bid)
+{
+    return p > bp || (p == bp && id >= 0 && (bid < 0 || id < bid));
+}
+
+__global__ void __launch_bounds__(256) sample_top_p_kernel(const float *__restrict__ logits, int n, float temperature,
+                                                           float top_p, unsigned long long seed, int *result)
+{
+    pdl_enter();
+    __shared__ float sp[256 * kSampleKeep];
+    __shared__ int si[256 * kSampleKeep];
+    __shared__ float ssum[8];
+    __shared__ int is_last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float mx = __ldcg(&g_sample_pair[0]);
+    const float inv_t = 1.0f / temperature;
+    // ---- scan: thread (jj = tid / 8, k = tid % 8) takes i = 256 (jj + 32 m) + 8 blockIdx.x + k ----
+    const int k = tid & 7, jj = tid >> 3;
+    float vp[kSampleKeep];
+    int vi[kSampleKeep];
+#pragma unroll
+    for (int q = 0; q < kSampleKeep; q++) {
+        vp[q] = -1.0f;
+        vi[q] = -1;
+    }
+    float sum = 0.0f;
+    for (int i = 256 * jj + 8 * blockIdx.x + k; i < n; i += 256 * 32) {
+        const float p = expf((__ldcg(logits + i) - mx) * inv_t);
+        sum += p;
+        int mi = 0;
+#pragma unroll
+        for (int q = 1; q < kSampleKeep; q++)
+            if (vp[q] < vp[mi]) mi = q;
+#pragma unroll
+        for (int q = 0; q < kSampleKeep; q++)
+            if (q == mi && p > vp[q]) {
+                vp[q] = p;
+                vi[q] = i;
+            }
+    }
+    // lists to shared memory, class-major: class k holds 32 threads x 8 = 256 candidates
+#pragma unroll
+    for (int q = 0; q < kSampleKeep; q++) {
+        sp[(k * 32 + jj) * kSampleKeep + q] = vp[q];
+        si[(k * 32 + jj) * kSampleKeep + q] = vi[q];
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) ssum[warp] = sum;
+    __syncthreads();
+    // ---- warp w keeps the eight best of class w: eight rounds of a warp-wide maximum ----
+    {
+        float cp[kSampleKeep];
+        int ci[kSampleKeep];
+#pragma unroll
+        for (int q = 0; q < kSampleKeep; q++) {
+            cp[q] = sp[(warp * 32 + lane) * kSampleKeep + q];
+            ci[q] = si[(warp * 32 + lane) * kSampleKeep + q];
+        }
+        for (int round = 0; round < kSampleKeep; round++) {
+            float bp = -1.0f;
+            int bi = -1;
+#pragma unroll
+            for (int q = 0; q < kSampleKeep; q++)
+                if (cand_better(cp[q], ci[q], bp, bi)) {
+                    bp = cp[q];
+                    bi = ci[q];
+                }
+            float wp = bp;
+            int wi = bi;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float op = __shfl_xor_sync(0xffffffffu, wp, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, wi, o);
+                if (cand_better(op, oi, wp, wi)) {
+                    wp = op;
+                    wi = oi;
+                }
+            }
+            if (wi >= 0 && wi == bi) {  // the winner's owner retires it
+#pragma unroll
+                for (int q = 0; q < kSampleKeep; q++)
+                    if (ci[q] == wi) {
+                        cp[q] = -1.0f;
+                        ci[q] = -1;
+                    }
+            }
+            if (lane == 0) {
+                const int c = (8 * blockIdx.x + warp) * kSampleKeep + round;
+                g_sample_p[c] = wi >= 0 ? wp : -1.0f;
+                g_sample_id[c] = wi;
+            }
+        }
+    }
+    if (tid == 0) {
+        float s = 0.0f;
+        for (int w = 0; w < 8; w++) s += ssum[w];
+        g_sample_sum[blockIdx.x] = s;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) is_last = (atomicAdd(&g_sample_ticket, 1) == static_cast<int>(gridDim.x) - 1);
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // ---- last CTA: sort the candidates (probability descending, token id ascending), walk them ----
+    for (int c = tid; c < kSampleCands; c += 256) {
+        sp[c] = __ldcg(&g_sample_p[c]);
+        si[c] = __ldcg(&g_sample_id[c]);
+    }
+    __syncthreads();
+    for (int size = 2; size <= kSampleCands; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int t = tid; t < kSampleCands / 2; t += 256) {
+                const int lo = 2 * t - (t & (stride - 1));
+                const int hi = lo + stride;
+                const bool desc = ((lo & size) == 0);
+                const bool hi_first = cand_better(sp[hi], si[hi], sp[lo], si[lo]);
+                if (hi_first == desc) {
+                    const float tp = sp[lo];
+                    const int ti = si[lo];
+                    sp[lo] = sp[hi];
+                    si[lo] = si[hi];
+                    sp[hi] = tp;
+                    si[hi] = ti;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (tid == 0) {
+        float total = 0.0f;
+        for (int c = 0; c < static_cast<int>(gridDim.x); c++) total += __ldcg(&g_sample_sum[c]);
+        unsigned long long rs0 = seed, rs1 = seed ^ 0xDEADBEEFCAFEBABEULL;
+        for (int w = 0; w < 4; w++) {  // three warm-up rounds and the draw
+            const unsigned long long t = rs0 ^ (rs0 << 23);
+            rs0 = rs1;
+            rs1 = t ^ rs1 ^ (t >> 17) ^ (rs1 >> 26);
+        }
+        const float r = static_cast<float>((rs0 + rs1) >> 11) * (1.0f / 9007199254740992.0f);
+        const float mass = top_p * total;
+        float cumul = 0.0f;
+        int nucleus = 0;
+        for (int c = 0; c < kSampleCands; c++) {
+            if (sp[c] <= 0.0f) break;
+            cumul += sp[c];
+            nucleus = c + 1;
+            if (cumul >= mass) break;
+        }
+        float nsum = 0.0f;
+        for (int c = 0; c < nucleus; c++) nsum += sp[c];
+        const float target = r * nsum;
+        float acc = 0.0f;
+        int sampled = si[0];
+        for (int c = 0; c < nucleus; c++) {
+            acc += sp[c];
+            if (acc >= target) {
+                sampled = si[c];
+                break;
+            }
+        }
+        *result = sampled;
+        g_sample_ticket = 0;
+    }
+}
+
 // The best of the shards' (value, index) pairs, by the same order as above; writes the token and advances the position.
 __global__ void argmax_merge_kernel(const float *__restrict__ pairs, int n, int *result, int *pos_ptr)
 {
@@ -762,10 +944,25 @@ bool attn_attr()
 
 }  // namespace
 
+// Device address of the sampling kernels' (max, index) pair, looked up once per device (cuda_kernels_init does it,
+// so that no symbol is resolved inside a stream capture).
+float *sample_pair_addr()
+{
+    static float *addr[kMaxDevices] = {};
+    const int dev = current_device();
+    if (!addr[dev]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_sample_pair) != cudaSuccess) return nullptr;
+        addr[dev] = static_cast<float *>(p);
+    }
+    return addr[dev];
+}
+
 void support_init()
 {
     attn_attr();
     (void)static_attn();
+    (void)sample_pair_addr();
 }
 
 int attn_chunks_for(int n_kv_heads, int gqa, int max_slots)
@@ -986,13 +1183,18 @@ void cuda_embedding_lookup_q4k(const void *embd_table, float *output, int token_
 void cuda_sample_token(const float *logits, int vocab_size, float temperature, float top_p,
                        unsigned long long rng_state, int *d_result, cudaStream_t stream)
 {
-    (void)top_p;
-    (void)rng_state;
     if (vocab_size <= 0) return;
     if (temperature > 0.0f) {
-        // nucleus sampling is outside this library's scope: greedy result, and the status says so
-        fprintf(stderr, "[mnemo_b200] cuda_sample_token: temperature > 0 is not implemented; returning the argmax\n");
-        set_status(MB200_ERR_UNSUPPORTED, "cuda_sample_token");
+        float *pair = sample_pair_addr();
+        if (!pair) {
+            set_status(MB200_ERR_LAUNCH, "cuda_sample_token");
+            return;
+        }
+        launch_argmax_pair(logits, vocab_size, 0, pair, stream);  // the maximum, for exp(l - max)
+        launch_k(sample_top_p_kernel, dim3(kSampleCtas), dim3(256), 0, stream, logits, vocab_size, temperature, top_p,
+                 rng_state, d_result);
+        MB200_CHECK_LAUNCH("cuda_sample_token");
+        return;
     }
     launch_argmax(logits, vocab_size, d_result, nullptr, stream);
     MB200_CHECK_LAUNCH("cuda_sample_token");

@@ -830,6 +830,64 @@ void mo_attention_int8kv(const float *q, const int8_t *kv_k, const int8_t *kv_v,
     }
 }
 
+/* Temperature + top-p sampling of one token (kernels.cu:2073-2174), the reference's own order of
+ * operations restated serially: p_i = exp((l_i - max) / T); total = sum p; per residue class i mod 256
+ * the eight largest p (first minimum replaced, a later equal value does not enter); the 2048
+ * candidates picked largest first (first maximum) until their running sum reaches top_p * total;
+ * a xoroshiro128+ draw (seed, seed ^ 0xDEADBEEFCAFEBABE, three warm-up rounds) scaled by the nucleus
+ * sum; the first candidate at which the running sum reaches it. The sums are taken in double here
+ * (the reference adds floats in a thread-strided / tree order this restatement does not reproduce):
+ * tests use logits whose cut and draw are not within rounding of a boundary. */
+int mo_sample_top_p(const float *logits, int n, float temperature, float top_p, unsigned long long seed)
+{
+    float mx = -1e30f;
+    for (int i = 0; i < n; i++) mx = fmaxf(mx, logits[i]);
+    double total = 0.0;
+    static float cand_p[2048];
+    static int cand_id[2048];
+    for (int c = 0; c < 2048; c++) { cand_p[c] = -1.0f; cand_id[c] = -1; }
+    for (int i = 0; i < n; i++) {
+        const float p = expf((logits[i] - mx) / temperature);
+        total += p;
+        float *v = cand_p + (i % 256) * 8;
+        int *id = cand_id + (i % 256) * 8;
+        int mi = 0;
+        for (int k = 1; k < 8; k++) if (v[k] < v[mi]) mi = k;
+        if (p > v[mi]) { v[mi] = p; id[mi] = i; }
+    }
+    unsigned long long rs0 = seed, rs1 = seed ^ 0xDEADBEEFCAFEBABEULL, t;
+    for (int w = 0; w < 4; w++) {
+        t = rs0 ^ (rs0 << 23);
+        rs0 = rs1;
+        rs1 = t ^ rs1 ^ (t >> 17) ^ (rs1 >> 26);
+    }
+    const float r = (float)((rs0 + rs1) >> 11) * (1.0f / 9007199254740992.0f);
+    const double mass = (double)top_p * total;
+    double cumul = 0.0;
+    int nucleus = 0;
+    for (int pick = 0; pick < 2048; pick++) {
+        int best = pick;
+        for (int j = pick + 1; j < 2048; j++) if (cand_p[j] > cand_p[best]) best = j;
+        if (cand_p[best] <= 0.0f) break;
+        const float tp = cand_p[pick]; const int ti = cand_id[pick];
+        cand_p[pick] = cand_p[best]; cand_id[pick] = cand_id[best];
+        cand_p[best] = tp; cand_id[best] = ti;
+        cumul += cand_p[pick];
+        nucleus = pick + 1;
+        if (cumul >= mass) break;
+    }
+    double nsum = 0.0;
+    for (int i = 0; i < nucleus; i++) nsum += cand_p[i];
+    const double target = (double)r * nsum;
+    double acc = 0.0;
+    int sampled = cand_id[0];
+    for (int i = 0; i < nucleus; i++) {
+        acc += cand_p[i];
+        if (acc >= target) { sampled = cand_id[i]; break; }
+    }
+    return sampled;
+}
+
 int mo_num_threads(void)
 {
 #ifdef _OPENMP

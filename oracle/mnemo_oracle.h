@@ -1,5 +1,5 @@
 /*
- * mnemo_oracle.h -- CPU restatement (plain C, fp32 with an fp64 judge) of the
+ * mnemo_oracle.h -- CPU restatement (plain C, fp32 with fp64 reference sums) of the
  * reference's quantized-weight hot path.
  *
  * THIS IS TEST INFRASTRUCTURE. It is the checker for the CUDA library and the
@@ -12,7 +12,12 @@
  * Parity pin: the reference ships no golden vectors for this path; the dequant
  * routines here are pinned by equality (==, not a tolerance) against
  * tools/validate_dequant.py's dequant_q4k_cuda_style / dequant_q6k_reference
- * and against gguf.quants.dequantize on seeded blocks (tests/golden/).
+ * and against gguf.quants.dequantize on seeded blocks (tests/golden/). Q5_K and
+ * Q8_0 are pinned the same way against dequant_q5k_cuda_style /
+ * dequant_q8_0_cuda_style; RMSNorm and RoPE against the numpy replicas in
+ * tools/validate_rope_norm.py. Q3_K has no counterpart in the validator:
+ * its parity is UNPINNED on the CPU (it is checked against the reference's
+ * compiled kernel on the GPU by tests/test_gpu_vs_reference_kernels.py).
  */
 #ifndef MNEMO_ORACLE_H
 #define MNEMO_ORACLE_H
@@ -116,6 +121,9 @@ void mo_f32_to_int8_kv(const float *in, int8_t *out, float *scales, int head_dim
 void mo_attention_int8kv(const float *q, const int8_t *kv_k, const int8_t *kv_v, const float *k_scales,
                          const float *v_scales, float *out, int n_heads_q, int head_dim, int n_kv_heads, int seq_len,
                          int gqa_ratio, float scale);
+
+/* temperature + top-p sampling: kernels.cu:2073-2174 (sums in double; see the .c file) */
+int mo_sample_top_p(const float *logits, int n, float temperature, float top_p, unsigned long long seed);
 
 int mo_num_threads(void);
 void mo_set_num_threads(int n);

@@ -297,6 +297,13 @@ def argmax(logits) -> int:
     return int(lib().mo_argmax(_p(logits), C.c_int(logits.size)))
 
 
+def sample_top_p(logits, temperature: float, top_p: float, seed: int) -> int:
+    logits = _f32(logits)
+    lib().mo_sample_top_p.restype = C.c_int
+    return int(lib().mo_sample_top_p(_p(logits), C.c_int(logits.size), C.c_float(temperature), C.c_float(top_p),
+                                     C.c_ulonglong(seed)))
+
+
 TYPE_BLOCK = {8: (32, 34), 11: (256, 110), 12: (256, 144), 13: (256, 176), 14: (256, 210)}  # weights, bytes per block
 
 

@@ -168,8 +168,49 @@ def test_sample_token_greedy_and_ties(K):
     K.cuda_sample_token(dev(x), V, 0.0, 0.9, 1234, res)
     # thread = index % 256: 188, 44, 44, 240; the tree prefers the smaller bit-reversed thread id: 240 (0b11110000)
     assert int(res.item()) == oracle.argmax(x) == 150000
-    with pytest.raises(RuntimeError, match="status 4"):  # nucleus sampling is not implemented
-        K.cuda_sample_token(dev(x), V, 0.7, 0.9, 1234, res)
+
+
+@pytest.mark.parametrize("V,scale,temp,top_p", [(151936, 3.0, 0.7, 0.9), (151936, 1.0, 1.0, 0.5), (32000, 6.0, 0.3, 0.95),
+                                                (1000, 2.0, 1.5, 1.0), (300, 1.0, 0.8, 0.8), (151936, 0.5, 1.0, 0.99)])
+def test_sample_token_top_p_matches_the_oracle(K, V, scale, temp, top_p):
+    """Temperature + top-p sampling: the same token as the oracle's serial restatement of the reference for a set
+    of random 64-bit generator states (a draw within float rounding of a boundary may legitimately differ: at most
+    one of the states may disagree, and then only by a neighbour in the nucleus)."""
+    logits = (synth.normal_f32(96 + V, V) * scale).astype(np.float32)
+    d_l = dev(logits)
+    res = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    rng = np.random.default_rng(97)
+    seeds = [int(s) for s in rng.integers(1, 2 ** 63, 40)]
+    miss = 0
+    for seed in seeds:
+        K.cuda_sample_token(d_l, V, temp, top_p, seed, res)
+        got, want = int(res.item()), oracle.sample_top_p(logits, temp, top_p, seed)
+        assert 0 <= got < V
+        miss += got != want
+    assert miss <= 1, miss
+    if V == 151936 and scale == 3.0:
+        assert len({oracle.sample_top_p(logits, temp, top_p, s) for s in seeds}) > 5  # the draw does vary
+
+
+def test_sample_token_top_p_degenerate_and_repeat(K):
+    V = 50000
+    logits = np.full(V, -5.0, np.float32)
+    logits[4321] = 30.0
+    res = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    for seed in (1, 2 ** 40 + 7, 2 ** 62 + 1):
+        K.cuda_sample_token(dev(logits), V, 0.8, 0.9, seed, res)
+        assert int(res.item()) == 4321
+    # equal logits everywhere: every class keeps its eight smallest ids; the result is one of those and repeats
+    logits[:] = 0.0
+    picks = set()
+    for rep in range(3):
+        K.cuda_sample_token(dev(logits), V, 1.0, 0.9, 123456789123, res)
+        picks.add(int(res.item()))
+    assert len(picks) == 1 and next(iter(picks)) < 256 * 8
+    # greedy still works after the sampling kernels have used the library's scratch
+    logits[777] = 1.0
+    K.cuda_sample_token(dev(logits), V, 0.0, 0.9, 5, res)
+    assert int(res.item()) == 777
 
 
 def test_kernel_pointer_exports(K):

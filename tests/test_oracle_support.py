@@ -92,3 +92,56 @@ def test_f32_to_f16_array_matches_numpy():
     with np.errstate(over="ignore"):  # values beyond 65504 round to infinity in both
         want = x.astype(np.float16).view(np.uint16)
     assert np.array_equal(oracle.f32_to_f16_bits(x), want)
+
+
+def _sample_bruteforce(logits, temperature, top_p, seed):
+    """An independent reading of the reference's sampler (src/kernels.cu:2073-2174) in numpy."""
+    l = logits.astype(np.float32)
+    p = np.exp(((l - l.max()) / np.float32(temperature)).astype(np.float32)).astype(np.float32)
+    total = float(p.astype(np.float64).sum())
+    cand = []
+    for c in range(256):
+        idx = np.arange(c, l.size, 256)
+        order = sorted(idx, key=lambda i: (-p[i], i))[:8]
+        cand += order
+    cand = sorted(cand, key=lambda i: (-p[i], i))
+    M = (1 << 64) - 1
+    rs0, rs1 = seed & M, (seed ^ 0xDEADBEEFCAFEBABE) & M
+    for _ in range(4):
+        t = (rs0 ^ (rs0 << 23)) & M
+        rs0 = rs1
+        rs1 = (t ^ rs1 ^ (t >> 17) ^ (rs1 >> 26)) & M
+    r = float(np.float32(((rs0 + rs1) & M) >> 11) * np.float32(1.0 / 9007199254740992.0))
+    cumul, nucleus = 0.0, []
+    for i in cand:
+        if p[i] <= 0:
+            break
+        cumul += float(p[i])
+        nucleus.append(i)
+        if cumul >= top_p * total:
+            break
+    target, acc = r * sum(float(p[i]) for i in nucleus), 0.0
+    for i in nucleus:
+        acc += float(p[i])
+        if acc >= target:
+            return int(i)
+    return int(nucleus[0])
+
+
+def test_top_p_sampler_matches_an_independent_reading():
+    rng = np.random.default_rng(5)
+    for n, scale, temp, top_p in ((5000, 3.0, 0.7, 0.9), (5000, 1.0, 1.0, 0.5), (1000, 6.0, 0.3, 0.95), (300, 2.0, 1.5, 1.0)):
+        logits = (rng.standard_normal(n) * scale).astype(np.float32)
+        for seed in rng.integers(1, 2 ** 63, 12):
+            assert oracle.sample_top_p(logits, temp, top_p, int(seed)) == _sample_bruteforce(logits, temp, top_p, int(seed))
+
+
+def test_top_p_sampler_degenerate_cases():
+    logits = np.full(1000, -5.0, np.float32)
+    logits[123] = 30.0  # one token holds all the mass
+    for seed in (1, 2 ** 40 + 7, 2 ** 62 + 1):
+        assert oracle.sample_top_p(logits, 0.8, 0.9, seed) == 123
+    # top_p -> 0 keeps only the most probable token
+    rng = np.random.default_rng(6)
+    l = rng.standard_normal(4000).astype(np.float32)
+    assert oracle.sample_top_p(l, 1.0, 1e-6, 99) == int(l.argmax())
