@@ -2,7 +2,8 @@
 """Benchmark of the quantized-weight hot path: one MoE expert block, batch 1, Qwen3-235B shape.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload moe_block|matvec|gemm|prefill] [--no-fused | --fused-mode 1|2] [--no-pdl]
+                    [--workload moe_block|matvec|gemm|prefill|decode30b|decode235b] [--no-fused | --fused-mode 1|2]
+                    [--no-pdl] [--collective push|nccl] [--no-extras] [--decode-tokens T] [--decode-layers L]
 
 Workload (the MoE-block configuration of the benchmark spec): router fp32 128x4096 -> top-8 of 128 experts; per routed expert a
 fused gate+up Q4_K matvec (2 x 1536x4096) with SwiGLU and a Q6_K down matvec (4096x1536), weighted
@@ -23,8 +24,11 @@ benchmark spec and the vocabulary-sized Q4_K / Q6_K matvecs) and `decode` (whole
 `roofline` is for the dominant kernel (the expert phases of the fused kernel, timed alone; with
 --no-fused the routed gate/up stream kernel). `cpu_baseline` and `--impl reference` time the C
 oracle (the CPU restatement of the reference's algorithm -- the reference has no CPU implementation
-of this path) on the box's host cores on a bounded sample. N > 1 shards the experts of the block
-over the GPUs (router replicated, NCCL all-reduce of the partial hidden vectors): strong scaling.
+of this path) on the box's host cores on a bounded sample (the reference arm runs numpy host logic and
+the oracle only: no GPU library is loaded). N > 1 shards the experts of the block over the GPUs (router
+replicated, the partial hidden vectors summed by the library's push all-reduce over NVLink peer memory;
+--collective nccl times NCCL's instead): strong scaling, and the line's `sharded` key adds the NCCL
+baseline, a row-sharded matvec and the sharded whole-token decode.
 """
 from __future__ import annotations
 
@@ -50,6 +54,15 @@ WORKLOAD = ("configs[1]: MoE expert block, batch 1, Qwen3-235B shape -- router f
 GATE_UP_TRAFFIC_BYTES = 56726784 + 569088    # routed gate/up stream kernel, 8 experts (56 623 104 algorithmic bytes)
 BLOCK_TRAFFIC_BYTES = 100186880 + 4039680    # the whole block in one launch (100 007 936 algorithmic bytes)
 FUSED_TRAFFIC_BYTES = 98054912 + 3864064     # the fused routed-expert kernel alone (98 041 856 algorithmic bytes)
+
+
+def _launches_per_token(cfg, world: int) -> int:
+    """Kernels of this library per decoded token: embedding + RoPE table; per layer Q/K/V (one launch), q/k-norm +
+    RoPE + KV store, attention, O projection, MoE block (one launch where the one-launch form covers the shape,
+    else router + gate/up + down), plus the three exchanges of a sharded layer; lm_head + sampling."""
+    moe = 1 if (cfg.hidden % 2048 == 0 and cfg.moe_inter % 512 == 0) else 3
+    per_layer = 4 + moe + (3 if world > 1 else 0)
+    return 2 + per_layer * cfg.n_layers + (2 if world == 1 else 4)
 
 
 def measured_peaks():
@@ -261,6 +274,17 @@ def measure_matvec(torch, K, dev, timer, hbm, steps, warmup):
         by = nb * bb + 4 * (rows + cols)
         out[name] = {"ms": med, "ms_min": mn, "GBs": by / med / 1e6, "frac_of_measured_hbm": by / med / 1e6 / hbm, "bytes": by}
         del w
+    # the other weight types of the reference's matvec switch at the vocabulary size (random bytes with small fp16
+    # block scales: the values do not matter for the timing)
+    for name, bb, per, call in (("q8_0_151936x4096", 34, 32, K.cuda_matvec_q8_0), ("q5k_151936x4096", 176, 256, K.cuda_matvec_q5k),
+                                ("q3k_151936x4096", 110, 256, K.cuda_matvec_q3k)):
+        nb = rows * cols // per
+        w = torch.randint(0, 60, (nb * bb,), dtype=torch.uint8, device=dev)
+        y = torch.empty(rows, device=dev)
+        med, mn = timer.graph(lambda i: call(w, x, y, rows, cols), min(steps, 50), warmup, replays=5)
+        by = nb * bb + 4 * (rows + cols)
+        out[name] = {"ms": med, "ms_min": mn, "GBs": by / med / 1e6, "frac_of_measured_hbm": by / med / 1e6 / hbm, "bytes": by}
+        del w
     torch.cuda.empty_cache()
     return out
 
@@ -294,7 +318,7 @@ def measure_decode(torch, K, dev, timer, hbm, which, tokens, n_layers=None, rank
            "tok_s": 1e3 / med, "ms_per_token": med, "ms_per_token_min": mn, "bytes_per_token": by,
            "GBs": by / med / 1e6, "frac": by / med / 1e6 / (hbm * world), "frac_of": f"{world} x measured copy bandwidth",
            "resident_GB_per_rank": round(cfg.resident_bytes(cfg.n_experts // world) / 1e9, 1),
-           "tokens_per_graph": tokens, "launches_per_token": 2 + (8 if world == 1 else 11) * cfg.n_layers + (3 if world == 1 else 4),
+           "tokens_per_graph": tokens, "launches_per_token": _launches_per_token(cfg, world),
            "build_s": round(build_s, 1), "sampled_token": int(model.token.item())}
     del model, g
     torch.cuda.empty_cache()

@@ -10,6 +10,7 @@ namespace mb200 {
 void q4k_init();
 void q6k_init();
 void pair_init();
+void other_types_init();
 void gemm_init();
 void moe_fused_init();
 void router_static_init();
@@ -78,6 +79,7 @@ void cuda_kernels_init(void)
     q4k_init();
     q6k_init();
     pair_init();
+    other_types_init();
     gemm_init();
     moe_fused_init();
     support_init();

@@ -12,7 +12,8 @@
 // Q3_K (the two high bits of scale i taken from byte 8 + i/4) are not the ones of the GGUF
 // specification; a drop-in has to give the answers of the code it replaces.
 //
-// Matvec: one warp per row, grid-stride. The warp copies the row's bytes into its slice of shared
+// Matvec: whole 256-column blocks at the type's alignment run on the streaming skeleton (matvec_other.cu,
+// other_policies.cuh: bulk-copied tiles, dp4a against the int8 split of x). Anything else: one warp per row, grid-stride. The warp copies the row's bytes into its slice of shared
 // memory with 16-byte loads (2-byte loads at a ragged head or tail), then each lane decodes whole
 // 32-weight groups (scale decode once per group) against x, which the CTA holds in shared memory
 // padded by one float per 32 so that lanes on different groups hit different banks.
@@ -23,6 +24,10 @@
 
 namespace mb200 {
 int pdl_enabled();
+// the streaming forms (matvec_other.cu); false = shape or alignment they do not take
+bool stream_matvec_q8_0(const void *w, const float *x, float *y, int n_rows, int n_cols, cudaStream_t s);
+bool stream_matvec_q5k(const void *w, const float *x, float *y, int n_rows, int n_cols, cudaStream_t s);
+bool stream_matvec_q3k(const void *w, const float *x, float *y, int n_rows, int n_cols, cudaStream_t s);
 
 namespace {
 
@@ -466,16 +471,19 @@ extern "C" {
 
 void cuda_matvec_q8_0(const void *weights, const float *x, float *y, int n_rows, int n_cols, cudaStream_t stream)
 {
+    if (n_rows > 0 && stream_matvec_q8_0(weights, x, y, n_rows, n_cols, stream)) return;
     typed_matvec<Q8_0>(weights, x, y, n_rows, n_cols, stream, "cuda_matvec_q8_0");
 }
 
 void cuda_matvec_q5k(const void *weights, const float *x, float *y, int n_rows, int n_cols, cudaStream_t stream)
 {
+    if (n_rows > 0 && stream_matvec_q5k(weights, x, y, n_rows, n_cols, stream)) return;
     typed_matvec<Q5K>(weights, x, y, n_rows, n_cols, stream, "cuda_matvec_q5k");
 }
 
 void cuda_matvec_q3k(const void *weights, const float *x, float *y, int n_rows, int n_cols, cudaStream_t stream)
 {
+    if (n_rows > 0 && stream_matvec_q3k(weights, x, y, n_rows, n_cols, stream)) return;
     typed_matvec<Q3K>(weights, x, y, n_rows, n_cols, stream, "cuda_matvec_q3k");
 }
 

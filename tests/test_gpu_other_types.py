@@ -52,22 +52,25 @@ def test_typed_matvec_at_an_odd_address(K, tid, name):
     assert_close_matvec(host(y), y64, ad, name)
 
 
-def test_typed_matvec_one_hot_x_reads_single_weights(K):
-    """x = e_c picks weight c of every row: a direct check of the unpacking of each bit field."""
-    rows, cols = 16, 512
+@pytest.mark.parametrize("cols", [512, 300])
+def test_typed_matvec_one_hot_x_reads_single_weights(K, cols):
+    """x = e_c picks weight c of every row: a direct check of the unpacking of each bit field, in the streaming
+    kernels (whole 256-column blocks) and in the row-per-warp kernels (ragged width)."""
+    rows = 16
     for tid, name in ((8, "cuda_matvec_q8_0"), (13, "cuda_matvec_q5k"), (11, "cuda_matvec_q3k")):
         w = synth.typed_matrix(tid, 3300 + tid, rows, cols)
         full = oracle.dequant_type(tid, w, rows, cols)
         d_w = dev(w)
         y = torch.empty(rows, device="cuda")
-        for c in list(range(0, 256)) + [300, 511]:
+        for c in list(range(0, 256)) + [c for c in (299, 300, 511) if c < cols]:
             x = np.zeros(cols, np.float32)
             x[c] = 1.0
             getattr(K, name)(d_w, dev(x), y, rows, cols)
             got = host(y)
-            # Q5_K evaluates d*sc*q - dmin*m from two partial sums: allow a few ulps of the larger term
-            tol = 1e-6 * np.abs(full).max() if tid == 13 else 0.0
-            assert np.all(np.abs(got - full[:, c]) <= tol + 1e-7 * np.abs(full[:, c])), (name, c)
+            # a weight is evaluated as a difference of scaled partial sums (d*sc*q - dmin*m, or (q + 4h) - 4):
+            # a few ulps of the larger term, 2^-20 of the largest weight magnitude
+            tol = 2.0 ** -20 * np.abs(full).max()
+            assert np.all(np.abs(got - full[:, c]) <= tol), (name, c, float(np.abs(got - full[:, c]).max()), tol)
 
 
 def test_embedding_lookup_q3k_is_bit_exact(K):
