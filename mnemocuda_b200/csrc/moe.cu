@@ -164,6 +164,23 @@ void router_static_init() { (void)static_router_scratch(); }
 
 }  // namespace mb200
 
+namespace mb200 {
+namespace {
+// x and the residual from mapped host memory into device memory: volatile loads (the host rewrites the buffer
+// between calls; nothing of it may be served from a cache), one 16-byte load per thread and round.
+__global__ void __launch_bounds__(1024) host_stage_in_kernel(const float4 *src, float4 *dst, int n4)
+{
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+        float4 v;
+        asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                     : "l"(src + i));
+        dst[i] = v;
+    }
+}
+}  // namespace
+}  // namespace mb200
+
 using namespace mb200;
 
 extern "C" {
@@ -324,12 +341,30 @@ int mb200_moe_block_host(const float *router_w, const void *experts, size_t expe
                          float *act, void *scratch, cudaStream_t stream)
 {
     if (!host_x_res || !host_out || !dev_io || H < 1) return MB200_ERR_ARG;
+    const int cnt = expert_cnt > 0 ? expert_cnt : 0x7fffffff;
+    // Pinned (page-locked, mapped) host buffers are reachable from the device: a one-CTA kernel pulls x and the
+    // residual across PCIe into dev_io (one round trip instead of a copy-engine launch), and the block writes its
+    // result rows straight into the host buffer (each row is written once). Two or three kernel launches and one
+    // wait per call; no copy-engine work.
+    void *d_in = nullptr, *d_out = nullptr;
+    const bool mapped = (H % 4 == 0) && cudaHostGetDevicePointer(&d_in, const_cast<float *>(host_x_res), 0) == cudaSuccess &&
+                        cudaHostGetDevicePointer(&d_out, host_out, 0) == cudaSuccess;
+    if (mapped) {
+        host_stage_in_kernel<<<1, 1024, 0, stream>>>(static_cast<const float4 *>(d_in), reinterpret_cast<float4 *>(dev_io),
+                                                     2 * H / 4);
+        const int rc = mb200_moe_block_local(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts,
+                                             expert_lo, cnt, k, H, EFF, dev_io, dev_io + H, static_cast<float *>(d_out), ids,
+                                             wts, act, scratch, stream);
+        if (rc != MB200_OK) return rc;
+        return cudaStreamSynchronize(stream) == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
+    }
+    (void)cudaGetLastError();  // pageable buffers: the query above failed, which is not an error of this call
     // one copy in (x and the residual are adjacent), the block, one copy out, one wait
     if (cudaMemcpyAsync(dev_io, host_x_res, sizeof(float) * 2 * (size_t)H, cudaMemcpyHostToDevice, stream) != cudaSuccess)
         return MB200_ERR_LAUNCH;
     const int rc = mb200_moe_block_local(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts, expert_lo,
-                                         expert_cnt > 0 ? expert_cnt : 0x7fffffff, k, H, EFF, dev_io, dev_io + H,
-                                         dev_io + 2 * (size_t)H, ids, wts, act, scratch, stream);
+                                         cnt, k, H, EFF, dev_io, dev_io + H, dev_io + 2 * (size_t)H, ids, wts, act, scratch,
+                                         stream);
     if (rc != MB200_OK) return rc;
     if (cudaMemcpyAsync(host_out, dev_io + 2 * (size_t)H, sizeof(float) * (size_t)H, cudaMemcpyDeviceToHost, stream) !=
         cudaSuccess)

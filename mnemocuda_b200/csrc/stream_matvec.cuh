@@ -306,6 +306,56 @@ static __device__ long long g_trace[kSMs * 2][48];  // one copy per translation 
 // With norm_w the vector is RMS-normalised on the way (needs the whole vector in one round of loads,
 // n_cols <= 4 * UN * kQuantThreads, which the host checks): the consumer warps add up x^2 through `red`
 // (kConsumers floats of shared memory) and hardware barrier 2.
+// One quad of columns -> the two int8 levels, the group's scale and the column sums.
+template <class F>
+__device__ __forceinline__ void split_quad(const float (&v)[4], int c0, int lane, int pitch, uint32_t *q1, uint32_t *q2,
+                                           float *s1, float *xsum)
+{
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    float sum = (v[0] + v[1]) + (v[2] + v[3]);
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));  // 8 lanes = 32 columns share a scale
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    if (F::kSumCols == 16) sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    const float sc = amax * (1.0f / 127.0f);
+    const float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+    uint32_t p1 = 0, p2 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        // |x| <= amax, so |a| <= 127; |r| <= sc/2 (+ rounding), so |b| <= 127: clamp only guards NaN/Inf input
+        const float a = rintf(v[i] * inv);
+        const float r = fmaf(-a, sc, v[i]);
+        const float b = fminf(fmaxf(rintf(r * inv * 254.0f), -127.0f), 127.0f);
+        p1 |= (static_cast<uint32_t>(__float2int_rn(a)) & 0xFFu) << (8 * i);
+        p2 |= (static_cast<uint32_t>(__float2int_rn(b)) & 0xFFu) << (8 * i);
+    }
+    const int idx = F::xword(c0) * pitch + F::xslot(c0);
+    q1[idx] = p1;
+    q2[idx] = p2;
+    if ((lane & 7) == 0) s1[c0 >> 5] = sc;
+    if (F::kSumCols == 16) {
+        if ((lane & 3) == 0) xsum[c0 >> 4] = sum;
+    } else {
+        if ((lane & 1) == 0) xsum[c0 >> 3] = sum;
+    }
+}
+
+template <class F>
+__device__ __forceinline__ void load_quad(const float *__restrict__ x, int c0, int n_cols, bool vec_ok, float (&v)[4])
+{
+    if (vec_ok && c0 + 3 < n_cols) {
+        const float4 t = __ldcg(reinterpret_cast<const float4 *>(x + c0));
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const bool in = F::kGroup4Tail ? (c0 + 3) < n_cols : (c0 + i) < n_cols;
+            v[i] = in ? __ldcg(x + c0 + i) : 0.0f;
+        }
+    }
+}
+
 template <class F, int UN>
 __device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_cols, int bpr,
                                            uint32_t *q1, uint32_t *q2, float *s1, float *xsum,
@@ -316,86 +366,57 @@ __device__ __forceinline__ void quantize_x(const float *__restrict__ x, int n_co
     const int pitch = F::kSlotsPerBlock * bpr + 1;
     const int lane = threadIdx.x & 31;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-    // The first round runs on every thread, also one whose columns lie beyond the vector (it loads nothing and
-    // stores nothing): the fused norm below has a barrier that all consumer threads must reach.
-    int base = threadIdx.x * 4;
-    do {
-        float v[UN][4];
+    if (!norm_w) {
+        // all loads of a round in flight, then the splits side by side (a rolled loop, one quad ahead, was
+        // measured 10 % slower on the 8192 x 4096 matvec: the splits' shuffle chains need each other's company)
+        for (int base = threadIdx.x * 4; base < kpad; base += kQuantThreads * 4 * UN) {
+            float v[UN][4];
 #pragma unroll
-        for (int u = 0; u < UN; u++) {
-            const int c0 = base + u * kQuantThreads * 4;
-            if (vec_ok && c0 + 3 < n_cols) {
-                const float4 t = __ldcg(reinterpret_cast<const float4 *>(x + c0));
-                v[u][0] = t.x; v[u][1] = t.y; v[u][2] = t.z; v[u][3] = t.w;
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const bool in = F::kGroup4Tail ? (c0 + 3) < n_cols : (c0 + i) < n_cols;
-                    v[u][i] = in ? __ldcg(x + c0 + i) : 0.0f;
-                }
-            }
-        }
-        if (norm_w) {  // block-uniform
-            float wv[UN][4];
-            float ss = 0.0f;
+            for (int u = 0; u < UN; u++) load_quad<F>(x, base + u * kQuantThreads * 4, n_cols, vec_ok, v[u]);
 #pragma unroll
             for (int u = 0; u < UN; u++) {
                 const int c0 = base + u * kQuantThreads * 4;
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    wv[u][i] = (c0 + i < n_cols) ? __ldg(norm_w + c0 + i) : 0.0f;
-                    // the sum runs over every column of x, also those a group-of-four tail rule drops below
-                    const float xv = (F::kGroup4Tail && c0 + i < n_cols && !(c0 + 3 < n_cols)) ? __ldcg(x + c0 + i) : v[u][i];
-                    ss = fmaf(xv, xv, ss);
-                }
-            }
-            ss = warp_sum(ss);
-            if (lane == 0) red[threadIdx.x >> 5] = ss;
-            asm volatile("bar.sync 2, %0;" ::"n"(kQuantThreads) : "memory");
-            float tot = 0.0f;
-#pragma unroll
-            for (int w = 0; w < kConsumers; w++) tot += red[w];  // fixed order: the same scale on every thread and CTA
-            const float scale = 1.0f / sqrtf(tot / static_cast<float>(n_cols) + norm_eps);
-#pragma unroll
-            for (int u = 0; u < UN; u++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) v[u][i] = v[u][i] * scale * wv[u][i];
-        }
-#pragma unroll
-        for (int u = 0; u < UN; u++) {
-            const int c0 = base + u * kQuantThreads * 4;
-            if (c0 >= kpad) break;  // warp-uniform: a warp covers 128 columns, kpad is a multiple of 256
-            float amax = fmaxf(fmaxf(fabsf(v[u][0]), fabsf(v[u][1])), fmaxf(fabsf(v[u][2]), fabsf(v[u][3])));
-            float sum = (v[u][0] + v[u][1]) + (v[u][2] + v[u][3]);
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));  // 8 lanes = 32 columns share a scale
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            if (F::kSumCols == 16) sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            const float sc = amax * (1.0f / 127.0f);
-            const float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
-            uint32_t p1 = 0, p2 = 0;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                // |x| <= amax, so |a| <= 127; |r| <= sc/2 (+ rounding), so |b| <= 127: clamp only guards NaN/Inf input
-                const float a = rintf(v[u][i] * inv);
-                const float r = fmaf(-a, sc, v[u][i]);
-                const float b = fminf(fmaxf(rintf(r * inv * 254.0f), -127.0f), 127.0f);
-                p1 |= (static_cast<uint32_t>(__float2int_rn(a)) & 0xFFu) << (8 * i);
-                p2 |= (static_cast<uint32_t>(__float2int_rn(b)) & 0xFFu) << (8 * i);
-            }
-            const int idx = F::xword(c0) * pitch + F::xslot(c0);
-            q1[idx] = p1;
-            q2[idx] = p2;
-            if ((lane & 7) == 0) s1[c0 >> 5] = sc;
-            if (F::kSumCols == 16) {
-                if ((lane & 3) == 0) xsum[c0 >> 4] = sum;
-            } else {
-                if ((lane & 1) == 0) xsum[c0 >> 3] = sum;
+                if (c0 >= kpad) break;  // warp-uniform: a warp covers 128 columns, kpad is a multiple of 256
+                split_quad<F>(v[u], c0, lane, pitch, q1, q2, s1, xsum);
             }
         }
-        base += kQuantThreads * 4 * UN;
-    } while (base < kpad);
+        return;
+    }
+    // With the norm: every thread runs the round (also one whose columns lie beyond the vector: it loads nothing
+    // and stores nothing), because all consumer threads must reach the barrier below. One round of loads (the
+    // host has checked n_cols <= 4 * UN * kQuantThreads).
+    const int base = threadIdx.x * 4;
+    float v[UN][4];
+#pragma unroll
+    for (int u = 0; u < UN; u++) load_quad<F>(x, base + u * kQuantThreads * 4, n_cols, vec_ok, v[u]);
+    float wv[UN][4];
+    float ss = 0.0f;
+#pragma unroll
+    for (int u = 0; u < UN; u++) {
+        const int c0 = base + u * kQuantThreads * 4;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            wv[u][i] = (c0 + i < n_cols) ? __ldg(norm_w + c0 + i) : 0.0f;
+            // the sum runs over every column of x, also those a group-of-four tail rule drops below
+            const float xv = (F::kGroup4Tail && c0 + i < n_cols && !(c0 + 3 < n_cols)) ? __ldcg(x + c0 + i) : v[u][i];
+            ss = fmaf(xv, xv, ss);
+        }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) red[threadIdx.x >> 5] = ss;
+    asm volatile("bar.sync 2, %0;" ::"n"(kQuantThreads) : "memory");
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kConsumers; w++) tot += red[w];  // fixed order: the same scale on every thread and CTA
+    const float scale = 1.0f / sqrtf(tot / static_cast<float>(n_cols) + norm_eps);
+#pragma unroll
+    for (int u = 0; u < UN; u++) {
+        const int c0 = base + u * kQuantThreads * 4;
+        if (c0 >= kpad) break;  // warp-uniform
+#pragma unroll
+        for (int i = 0; i < 4; i++) v[u][i] = v[u][i] * scale * wv[u][i];
+        split_quad<F>(v[u], c0, lane, pitch, q1, q2, s1, xsum);
+    }
 }
 
 // Same split done by a single warp for one whole vector (routed down-projection:
@@ -412,50 +433,12 @@ __device__ __forceinline__ void quantize_x_warp(const float *__restrict__ x, int
     for (int base = lane * 4; base < kpad; base += 128 * UN) {
         float v[UN][4];
 #pragma unroll
-        for (int u = 0; u < UN; u++) {
-            const int c0 = base + u * 128;
-            if (vec_ok && c0 + 3 < n_cols) {
-                const float4 t = __ldcg(reinterpret_cast<const float4 *>(x + c0));
-                v[u][0] = t.x; v[u][1] = t.y; v[u][2] = t.z; v[u][3] = t.w;
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const bool in = F::kGroup4Tail ? (c0 + 3) < n_cols : (c0 + i) < n_cols;
-                    v[u][i] = in ? __ldcg(x + c0 + i) : 0.0f;
-                }
-            }
-        }
+        for (int u = 0; u < UN; u++) load_quad<F>(x, base + u * 128, n_cols, vec_ok, v[u]);
 #pragma unroll
         for (int u = 0; u < UN; u++) {
             const int c0 = base + u * 128;
             if (c0 - lane * 4 >= kpad) break;  // warp-uniform
-            float amax = fmaxf(fmaxf(fabsf(v[u][0]), fabsf(v[u][1])), fmaxf(fabsf(v[u][2]), fabsf(v[u][3])));
-            float sum = (v[u][0] + v[u][1]) + (v[u][2] + v[u][3]);
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            if (F::kSumCols == 16) sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            const float sc = amax * (1.0f / 127.0f);
-            const float inv = amax > 0.0f ? 127.0f / amax : 0.0f;
-            uint32_t p1 = 0, p2 = 0;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const float a = rintf(v[u][i] * inv);
-                const float r = fmaf(-a, sc, v[u][i]);
-                const float b = fminf(fmaxf(rintf(r * inv * 254.0f), -127.0f), 127.0f);
-                p1 |= (static_cast<uint32_t>(__float2int_rn(a)) & 0xFFu) << (8 * i);
-                p2 |= (static_cast<uint32_t>(__float2int_rn(b)) & 0xFFu) << (8 * i);
-            }
-            const int idx = F::xword(c0) * pitch + F::xslot(c0);
-            q1[idx] = p1;
-            q2[idx] = p2;
-            if ((lane & 7) == 0) s1[c0 >> 5] = sc;
-            if (F::kSumCols == 16) {
-                if ((lane & 3) == 0) xsum[c0 >> 4] = sum;
-            } else {
-                if ((lane & 1) == 0) xsum[c0 >> 3] = sum;
-            }
+            split_quad<F>(v[u], c0, lane, pitch, q1, q2, s1, xsum);
         }
     }
 }

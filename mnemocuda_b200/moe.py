@@ -92,9 +92,10 @@ class ResidentMoE:
 class HostMoEBlock:
     """The call a user of host buffers makes: hidden state in, hidden state out (mb200_moe_block_host).
 
-    One copy of [x | residual] from pinned host memory, the block, one copy of the result back, and a
-    wait for it (the reference's engine does the same per token for the logits). With experts sharded over
-    several GPUs the partial results are all-reduced on the device before the copy back."""
+    [x | residual] come from pinned host memory and the result goes back to pinned host memory inside the call: the
+    device reads and writes the mapped buffers itself (a staging kernel in, the block's own stores out), then the
+    call waits for the stream (the reference's engine does the same per token for the logits). With experts sharded
+    over several GPUs the partial results are all-reduced on the device before the copy back."""
 
     def __init__(self, moe: ResidentMoE, sharded=None):
         self.moe = moe
@@ -103,6 +104,7 @@ class HostMoEBlock:
         self.io = torch.empty(3, H, dtype=torch.float32, device=moe.device)  # x, residual, result
         self.h2d_bytes = 2 * H * 4
         self.d2h_bytes = H * 4
+        self._fixed = {}  # per layer: the arguments that do not change from call to call
 
     def __call__(self, layer: int, x_res_host: torch.Tensor, out_host: torch.Tensor) -> None:
         """x_res_host: pinned [2][H] (x, residual); out_host: pinned [H]."""
@@ -115,8 +117,11 @@ class HostMoEBlock:
             return
         if not (x_res_host.is_pinned() and out_host.is_pinned()):
             raise ValueError("pinned host tensors expected")
-        K._check(K._lib.lib().mb200_moe_block_host(
-            m.router[layer].data_ptr(), m.experts[layer].data_ptr(), s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE,
-            m.expert_lo, m.n_local, s.K, s.H, s.EFF, x_res_host.data_ptr(), out_host.data_ptr(), self.io.data_ptr(),
-            m.ids[layer].data_ptr(), m.wts[layer].data_ptr(), m.act.data_ptr(), m.scratch.data_ptr(),
-            torch.cuda.current_stream().cuda_stream), "mb200_moe_block_host")
+        fx = self._fixed.get(layer)
+        if fx is None:
+            fx = self._fixed[layer] = (
+                (m.router[layer].data_ptr(), m.experts[layer].data_ptr(), s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE,
+                 m.expert_lo, m.n_local, s.K, s.H, s.EFF),
+                (self.io.data_ptr(), m.ids[layer].data_ptr(), m.wts[layer].data_ptr(), m.act.data_ptr(), m.scratch.data_ptr()))
+        K._check(K._lib.lib().mb200_moe_block_host(*fx[0], x_res_host.data_ptr(), out_host.data_ptr(), *fx[1],
+                                                   torch.cuda.current_stream().cuda_stream), "mb200_moe_block_host")

@@ -214,21 +214,44 @@ def test_block_local_shards_sum_to_the_full_block(K, world):
 
 
 def test_host_buffer_block_matches_device_block(K):
-    """HostMoEBlock (pinned host buffers in and out, every call) against ResidentMoE.forward."""
+    """HostMoEBlock (pinned host buffers in and out, every call: the device reads and writes them in place) against
+    ResidentMoE.forward, in every form of the block; the same buffer reused with new contents (nothing may be served
+    from a cache); and the C entry point with pageable buffers (copy-engine path)."""
+    import ctypes as C
+    from mnemocuda_b200 import _lib
     from mnemocuda_b200.moe import HostMoEBlock, MoEShape, ResidentMoE
     shape = MoEShape(n_experts=16)
     moe = ResidentMoE(shape, 2, "cuda", seed=3)
     hb = HostMoEBlock(moe)
     H = shape.H
-    for it in range(5):
-        layer = it % 2
-        xr = torch.from_numpy(np.stack([synth.normal_f32(100 + it, H), synth.normal_f32(200 + it, H)])).pin_memory()
-        o = torch.empty(H).pin_memory()
-        hb(layer, xr, o)
-        want = torch.empty(H, device="cuda")
-        moe.forward(layer, xr[0].cuda(), xr[1].cuda(), want)
-        torch.cuda.synchronize()
-        assert torch.equal(o, want.cpu())
+    xr = torch.empty(2, H).pin_memory()
+    o = torch.empty(H).pin_memory()
+    for mode in (2, 1, 0):
+        K.mb200_set_fused(mode)
+        for it in range(4):
+            layer = it % 2
+            xr.copy_(torch.from_numpy(np.stack([synth.normal_f32(100 + it, H), synth.normal_f32(200 + it, H)])))
+            o.fill_(float("nan"))
+            hb(layer, xr, o)
+            want = torch.empty(H, device="cuda")
+            moe.forward(layer, xr[0].cuda(), xr[1].cuda(), want)
+            torch.cuda.synchronize()
+            assert torch.equal(o, want.cpu()), (mode, it)
+    K.mb200_set_fused(2)
+    # pageable host memory through the C ABI
+    s = shape
+    x_np = np.stack([synth.normal_f32(300, H), synth.normal_f32(301, H)]).astype(np.float32)
+    out_np = np.full(H, np.nan, np.float32)
+    rc = _lib.lib().mb200_moe_block_host(
+        moe.router[0].data_ptr(), moe.experts[0].data_ptr(), s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE, 0, 0, s.K,
+        s.H, s.EFF, x_np.ctypes.data_as(C.c_void_p), out_np.ctypes.data_as(C.c_void_p), hb.io.data_ptr(),
+        moe.ids[0].data_ptr(), moe.wts[0].data_ptr(), moe.act.data_ptr(), moe.scratch.data_ptr(),
+        C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    want = torch.empty(H, device="cuda")
+    moe.forward(0, torch.from_numpy(x_np[0]).cuda(), torch.from_numpy(x_np[1]).cuda(), want)
+    torch.cuda.synchronize()
+    assert np.array_equal(out_np, want.cpu().numpy())
     assert K.mb200_device_error() == 0
 
 
