@@ -82,6 +82,32 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
         : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// A operand in tensor memory (128 lanes = rows, two fp16 per 32-bit column), B operand through a shared-memory descriptor.
+__device__ __forceinline__ void umma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 consecutive 32-bit columns of this thread's TMEM lane (lane = 32 * (warp % 4) + lane id)
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        :
+        : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t *bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -441,6 +467,207 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const __grid_const
     if (tid == 0 && *abort_flag) atomicExch(P.err, MB200_ERR_TIMEOUT);
 }
 
+// ---- dense Q4_K form with the weight operand in TENSOR MEMORY -------------------------------------------
+// In the kernel above each 64-wide K chunk moves 96 KB through shared memory (the producers' 16 KB of fp16
+// weights in, the same 16 KB out to the tensor core, 32 KB of activations in by TMA and out again), which at
+// 128 B per clock is 750 cycles against 524 for the MMAs, and every CTA pulls its 256-token activation tile
+// from L2 again (256 MB per 512 x 8192 x 4096 GEMM: about 10 TB/s at the rate the tensor cores could go).
+// Here the dequantised weights never touch shared memory: a producer thread owns one weight row (= one TMEM
+// lane), dequantises its 64 weights of a K chunk into 32 registers of packed fp16 and writes them with
+// tcgen05.st into a 32-column TMEM stage, from where the MMA takes its A operand. Shared memory carries only
+// the activations (six 32 KB stages). The tile shape is a
+// parameter (kAtmSlabs M = 128 slabs of weight rows x kAtmBT tokens): 1 x 256 is what is built -- 2 x 128, which
+// halves the activation traffic from L2 (the next limit: 256 MB per GEMM), was measured slower (55 vs 34 us)
+// because every weight is then dequantised twice as often and the producers become the bottleneck.
+constexpr int kAtmBT = 256;                              // tokens per CTA (UMMA N)
+constexpr int kAtmSlabs = 1;                             // M = 128 slabs of weight rows per CTA
+constexpr int kAtmRows = kAtmSlabs * kBN;
+constexpr int kAtmGroups = 4 / kAtmSlabs;                // producer groups; group g dequantises chunks kb = g (mod kAtmGroups)
+constexpr int kAtmAStages = 6, kAtmBStages = 6;  // one ring: equal by construction
+static_assert(kAtmAStages == kAtmBStages, "the weight and activation stages share their barriers");
+constexpr int kAtmBBytes = kAtmBT * kBK * 2;             // 32 KB
+constexpr int kAtmACols = kBK / 2;                       // 32 columns: 64 fp16 per row
+constexpr int kAtmAccCols = kAtmSlabs * kAtmBT;          // 256
+constexpr int kAtmTmemCols = 512;                        // 256 accumulator + 6 x 32 operand columns -> next power of two
+constexpr int kAtmSmemBytes = kAtmBStages * kAtmBBytes + 1024 + 512;
+constexpr uint32_t kAtmIdesc = Cfg<kAtmBT, 0>::kIdesc;
+static_assert(kAtmAccCols + kAtmAStages * kAtmSlabs * kAtmACols <= kAtmTmemCols, "tensor memory budget");
+
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_atm_kernel(const __grid_constant__ CUtensorMap xmap,
+                                                                 const __grid_constant__ GemmParams P)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    // one ring: stage s holds the weights of a chunk in TMEM and its activations in shared memory
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + kAtmBStages * kAtmBBytes);
+    uint64_t *empty = full + kAtmBStages;
+    uint64_t *acc_full = empty + kAtmBStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n0 = blockIdx.x * kAtmRows, t0 = blockIdx.y * kAtmBT, t_end = P.M;
+    if (t0 >= P.M) return;
+    const int n_kb = P.K / kBK;
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < kAtmBStages; s++) {
+            mbar_init(&full[s], 4 * kAtmSlabs + 1);  // the warps (slabs x four lane quarters) of a producer group + the TMA thread
+            mbar_init(&empty[s], 1);                 // tcgen05.commit
+        }
+        mbar_init(acc_full, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, kAtmTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_a0 = tmem_base + kAtmAccCols;  // operand stages behind the accumulator columns
+
+    if (warp == 0) {
+        if (lane == 0) {  // ---- TMA: activations ----
+            int s = 0, ph = 0;
+            for (int kb = 0; kb < n_kb; kb++) {
+                if (kb >= kAtmBStages && !mbar_wait(&empty[s], ph ^ 1)) {
+                    *abort_flag = 1;
+                    break;
+                }
+                mbar_expect_tx(&full[s], kAtmBBytes);
+                tma_load_2d(smem + s * kAtmBBytes, &xmap, kb * kBK, t0, &full[s]);
+                if (++s == kAtmBStages) {
+                    s = 0;
+                    ph ^= 1;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {  // ---- MMA issuer ----
+            int s = 0, ph = 0;
+            for (int kb = 0; kb < n_kb; kb++) {
+                if (!mbar_wait(&full[s], ph)) {
+                    *abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint64_t db = smem_desc_sw128(smem_u32(smem + s * kAtmBBytes));
+                const uint32_t ta = tmem_a0 + s * (kAtmSlabs * kAtmACols);
+#pragma unroll
+                for (int kk = 0; kk < kBK / 16; kk++)  // 16 fp16 of K = 8 operand columns = 2 descriptor units
+#pragma unroll
+                    for (int sl = 0; sl < kAtmSlabs; sl++)
+                        umma_f16_ta(tmem_base + sl * kAtmBT, ta + sl * kAtmACols + 8 * kk, db + 2 * kk, kAtmIdesc, (kb | kk) != 0);
+                umma_commit(&empty[s]);
+                if (++s == kAtmBStages) {
+                    s = 0;
+                    ph ^= 1;
+                }
+            }
+            umma_commit(acc_full);
+        }
+    } else {
+        // ---- producers: lane quarter q = warp % 4 (a warp may only touch TMEM lanes 32 q ..), idx = (warp - 2) / 4,
+        // slab = idx % slabs, group par = idx / slabs: the thread owns row 128 slab + 32 q + lane of the tile and
+        // the K chunks kb = par (mod groups): chunks par, par + groups, ... of every block of its row ----
+        const int quarter = warp & 3, idx = (warp - 2) >> 2, slab = idx % kAtmSlabs, par = idx / kAtmSlabs;
+        const int r = slab * kBN + quarter * 32 + lane, n = n0 + r;
+        const bool row_ok = n < P.N;
+        const uint8_t *row = P.w + (size_t)(row_ok ? n : 0) * P.bpr * kQ4KBlock;
+        const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+        constexpr int kPer = 4 / kAtmGroups;  // chunks of a block this thread dequantises
+        struct Raw {
+            uint4 hdr;
+            uint4 q[kPer][2];
+        } cur, nxt;
+        auto load_raw = [&](Raw &raw, const uint8_t *blk) {
+            raw.hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
+#pragma unroll
+            for (int i = 0; i < kPer; i++) {
+                const uint8_t *q = blk + 16 + 32 * (par + kAtmGroups * i);
+                raw.q[i][0] = __ldg(reinterpret_cast<const uint4 *>(q));
+                raw.q[i][1] = __ldg(reinterpret_cast<const uint4 *>(q + 16));
+            }
+        };
+        load_raw(cur, row);
+        bool stop = false;
+        for (int b = 0; b < P.bpr && !stop; b++) {
+            if (b + 1 < P.bpr) load_raw(nxt, row + (size_t)(b + 1) * kQ4KBlock);  // one block ahead
+#pragma unroll
+            for (int I = 0; I < kPer; I++) {
+                // 64 weights of chunk c = par + groups I: low nibbles of its 32 bytes are k-local 0..31 (sub-block 2c),
+                // high nibbles 32..63 (sub-block 2c + 1)
+                uint32_t sc2, m2;
+                q4k_scale_pair(cur.hdr.y, cur.hdr.z, cur.hdr.w, par + kAtmGroups * I, sc2, m2);
+                const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&cur.hdr.x));
+                const float live = row_ok ? 1.0f : 0.0f;  // rows past the matrix contribute zeros
+                const float a_lo = live * 64.0f * (dd.x * static_cast<float>(sc2 & 0xFFu));
+                const float a_hi = live * 64.0f * (dd.x * static_cast<float>(sc2 >> 8));
+                const float b_lo = -(2.0f * a_lo + live * dd.y * static_cast<float>(m2 & 0xFFu));
+                const float b_hi = -(2.0f * a_hi + live * dd.y * static_cast<float>(m2 >> 8));
+                const uint32_t qs[8] = {cur.q[I][0].x, cur.q[I][0].y, cur.q[I][0].z, cur.q[I][0].w,
+                                        cur.q[I][1].x, cur.q[I][1].y, cur.q[I][1].z, cur.q[I][1].w};
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const uint32_t lo = qs[i] & 0x0F0F0F0Fu, hi = (qs[i] >> 4) & 0x0F0F0F0Fu;
+                    // a nibble byte dropped into byte 2 of 2.0f is 2 + n / 64: w = (64 d sc) v - (128 d sc + dmin m)
+                    const float l0 = fmaf(a_lo, __uint_as_float(__byte_perm(lo, 0x40000000u, 0x7054)), b_lo);
+                    const float l1 = fmaf(a_lo, __uint_as_float(__byte_perm(lo, 0x40000000u, 0x7154)), b_lo);
+                    const float l2 = fmaf(a_lo, __uint_as_float(__byte_perm(lo, 0x40000000u, 0x7254)), b_lo);
+                    const float l3 = fmaf(a_lo, __uint_as_float(__byte_perm(lo, 0x40000000u, 0x7354)), b_lo);
+                    const float h0 = fmaf(a_hi, __uint_as_float(__byte_perm(hi, 0x40000000u, 0x7054)), b_hi);
+                    const float h1 = fmaf(a_hi, __uint_as_float(__byte_perm(hi, 0x40000000u, 0x7154)), b_hi);
+                    const float h2 = fmaf(a_hi, __uint_as_float(__byte_perm(hi, 0x40000000u, 0x7254)), b_hi);
+                    const float h3 = fmaf(a_hi, __uint_as_float(__byte_perm(hi, 0x40000000u, 0x7354)), b_hi);
+                    const __half2 p0 = __floats2half2_rn(l0, l1), p1 = __floats2half2_rn(l2, l3);
+                    const __half2 p2 = __floats2half2_rn(h0, h1), p3 = __floats2half2_rn(h2, h3);
+                    pk[2 * i] = *reinterpret_cast<const uint32_t *>(&p0);       // k = 4 i, 4 i + 1
+                    pk[2 * i + 1] = *reinterpret_cast<const uint32_t *>(&p1);   // k = 4 i + 2, 4 i + 3
+                    pk[16 + 2 * i] = *reinterpret_cast<const uint32_t *>(&p2);  // k = 32 + 4 i ...
+                    pk[16 + 2 * i + 1] = *reinterpret_cast<const uint32_t *>(&p3);
+                }
+                const int kb = 4 * b + par + kAtmGroups * I, s = kb % kAtmAStages, use = kb / kAtmAStages;
+                if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1)) *abort_flag = 1;
+                if (*abort_flag) {
+                    stop = true;
+                    break;
+                }
+                tc_fence_after();  // the MMAs that read this stage are complete: the overwrite is ordered after them
+                tmem_st32(tmem_a0 + lane_addr + (s * kAtmSlabs + slab) * kAtmACols, pk);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full[s]);
+            }
+            cur = nxt;
+        }
+        // ---- epilogue: the warp reads its lane quarter of its slab's accumulator, its group's share of the token columns ----
+        {
+            if (!mbar_wait(acc_full, 0)) *abort_flag = 1;
+            tc_fence_after();
+            if (!*abort_flag) {
+                const int nrow = n0 + r;
+#pragma unroll 1
+                constexpr int kShare = kAtmBT / kAtmGroups;
+                for (int c0 = par * kShare; c0 < (par + 1) * kShare; c0 += 32) {
+                    if (t0 + c0 >= t_end) break;
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + lane_addr + slab * kAtmBT + c0, v);
+                    if (nrow < P.N) {
+                        float *o = P.out + (size_t)(t0 + c0) * P.N + nrow;
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (t0 + c0 + j < t_end) o[(size_t)j * P.N] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, kAtmTmemCols);
+    if (tid == 0 && *abort_flag) atomicExch(P.err, MB200_ERR_TIMEOUT);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -489,6 +716,36 @@ int launch_gemm_bt(GemmParams &P, const void *x_f16, int rows_x, dim3 grid, cuda
     return cudaGetLastError() == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
 }
 
+// The dense Q4_K form with the weight operand in tensor memory (gemm_tc_atm_kernel).
+int launch_gemm_atm(GemmParams &P, const void *x_f16, int rows_x, dim3 grid, cudaStream_t stream, const char *where)
+{
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) {
+        fprintf(stderr, "[mnemo_b200] %s: cuTensorMapEncodeTiled is not available\n", where);
+        return MB200_ERR_LAUNCH;
+    }
+    CUtensorMap xmap;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(P.K), static_cast<cuuint64_t>(rows_x)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(P.K) * 2};
+    const cuuint32_t box[2] = {kBK, kAtmBT};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x_f16), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+        fprintf(stderr, "[mnemo_b200] %s: tensor map for X could not be encoded\n", where);
+        return MB200_ERR_ARG;
+    }
+    static bool attr_done[kMaxDevices] = {false};
+    if (!attr_done[current_device()]) {
+        cudaFuncSetAttribute(gemm_tc_atm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtmSmemBytes);
+        attr_done[current_device()] = true;
+    }
+    P.bpr = P.K / 256;
+    P.err = device_error_word();
+    gemm_tc_atm_kernel<<<grid, kThreads, kAtmSmemBytes, stream>>>(xmap, P);
+    return cudaGetLastError() == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
+}
+
 int launch_gemm(const void *w, const void *x_f16, float *out, int M, int N, int K, int q6, cudaStream_t stream,
                 const char *where)
 {
@@ -509,6 +766,7 @@ int launch_gemm(const void *w, const void *x_f16, float *out, int M, int N, int 
     P.q6 = q6;
     if (M <= 64)
         return launch_gemm_bt<64>(P, x_f16, M, dim3((N + kBN - 1) / kBN, 1), stream, where);
+    if (!q6) return launch_gemm_atm(P, x_f16, M, dim3((N + kAtmRows - 1) / kAtmRows, (M + kAtmBT - 1) / kAtmBT), stream, where);
     return launch_gemm_bt<256>(P, x_f16, M, dim3((N + kBN - 1) / kBN, (M + 255) / 256), stream, where);
 }
 
@@ -628,6 +886,7 @@ void gemm_init()
 {
     cudaFuncSetAttribute(gemm_tc_kernel<256, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<256>::kSmemBytes);
     cudaFuncSetAttribute(gemm_tc_kernel<64, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<64>::kSmemBytes);
+    cudaFuncSetAttribute(gemm_tc_atm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAtmSmemBytes);
     (void)encode_tiled();
 }
 
