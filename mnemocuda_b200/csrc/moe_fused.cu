@@ -987,6 +987,8 @@ static bool fused_plan(FusedParams &P, int &smem_bytes)
     }
     int v = 1;
     while (v * 2 <= 8 && P.bprC % (v * 2) == 0) v *= 2;
+    // one column per lane group (three blocks per down row: the 30B expert shape) works but does not pay: with
+    // experts that small the block is faster as router kernel + two stream kernels (3.37 vs 3.50 ms per token)
     if (v < 2) return false;
     P.vC = v;
     P.rppC = 8 / v;
