@@ -339,9 +339,12 @@ int mb200_moe_block_norm(const float *router_w, const void *experts, size_t expe
 /* The block for a caller that keeps the hidden state in HOST memory: host_x_res = [x | residual], 2*H floats;
  * host_out receives H floats. dev_io is 3*H floats of device memory the caller lends. With page-locked (pinned,
  * mapped) host buffers no copy engine is involved: a one-CTA kernel reads x and the residual across PCIe into
- * dev_io and the block writes its H result floats straight into host_out (kernel launches only, one wait). With
- * pageable buffers: one copy in, the block, one copy out. Either way the stream is synchronised before the call
- * returns (mb200_moe_block_local's arguments; expert_cnt 0 = all experts are here). The reference's engine moves
+ * dev_io, the block writes its H result floats straight into host_out, and a last one-thread kernel raises a word
+ * in host memory that the call spins on; the launches of a call are kept as an instantiated graph per argument
+ * set (64 most recent), so a repeated call is one graph launch. With pageable buffers: one copy in, the block, one
+ * copy out, a stream synchronisation. Either way the work is complete and the result in host_out when the call
+ * returns (mb200_moe_block_local's arguments; expert_cnt 0 = all experts are here). One host call at a time per
+ * device; not to be called while the stream is being captured by the caller (it then takes plain launches). The reference's engine moves
  * hidden vectors through the host the same way when peer access is unavailable (src/forward.c:1573-1578). */
 int mb200_moe_block_host(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz,
                          size_t up_sz, int down_type, int n_experts, int expert_lo, int expert_cnt, int k, int H,

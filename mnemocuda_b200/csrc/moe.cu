@@ -10,6 +10,7 @@
 //      (stream kernel, mode kMoeDown),
 // and the sequence can be captured in a CUDA graph.
 #include <cstdio>
+#include <cstring>
 
 #include "common.cuh"
 #include "topk.cuh"
@@ -178,6 +179,61 @@ __global__ void __launch_bounds__(1024) host_stage_in_kernel(const float4 *src, 
         dst[i] = v;
     }
 }
+
+// Last node of a host call: the kernels before it have completed (stream order), so the result rows are on their
+// way to host memory ahead of this store; the host spins on the word instead of asking the driver to wait.
+__global__ void host_signal_kernel(unsigned int *dev_counter, volatile unsigned int *host_flag)
+{
+    const unsigned int v = *dev_counter + 1;
+    *dev_counter = v;
+    __threadfence_system();
+    *host_flag = v;
+}
+
+// Per device: the completion word (mapped host memory) and its device-side counter; and the instantiated graphs
+// of recent host calls. A host call is a fixed little sequence of launches whose arguments repeat from token to
+// token (same layer, same buffers): replaying an instantiated graph costs one driver call instead of three
+// launches. Keyed by every argument; least recently used entry replaced.
+struct HostKey {
+    const void *router_w, *experts, *d_in, *d_out, *dev_io, *ids, *wts, *act, *scratch;
+    size_t stride, gate_sz, up_sz;
+    int down_type, n_experts, expert_lo, cnt, k, H, EFF, fused, pdl;
+    cudaStream_t stream;
+    bool operator==(const HostKey &o) const { return memcmp(this, &o, sizeof(HostKey)) == 0; }
+};
+struct HostEntry {
+    HostKey key;
+    cudaGraphExec_t exec;
+    unsigned long long used;
+};
+constexpr int kHostEntries = 64;
+struct HostState {
+    volatile unsigned int *flag = nullptr;  // mapped host word
+    unsigned int *flag_dev = nullptr;       // its device alias
+    unsigned int *counter = nullptr;        // device counter
+    unsigned int expected = 0;
+    unsigned long long tick = 0;
+    int n = 0;
+    HostEntry e[kHostEntries];
+};
+HostState g_host[kMaxDevices];
+
+bool host_state_ready(HostState &st)
+{
+    if (st.flag) return true;
+    void *h = nullptr, *d = nullptr, *c = nullptr;
+    if (cudaHostAlloc(&h, 64, cudaHostAllocMapped) != cudaSuccess) return false;
+    memset(h, 0, 64);
+    if (cudaHostGetDevicePointer(&d, h, 0) != cudaSuccess || cudaMalloc(&c, 64) != cudaSuccess || cudaMemset(c, 0, 64) != cudaSuccess) {
+        cudaFreeHost(h);
+        (void)cudaGetLastError();
+        return false;
+    }
+    st.flag = static_cast<volatile unsigned int *>(h);
+    st.flag_dev = static_cast<unsigned int *>(d);
+    st.counter = static_cast<unsigned int *>(c);
+    return true;
+}
 }  // namespace
 }  // namespace mb200
 
@@ -343,20 +399,92 @@ int mb200_moe_block_host(const float *router_w, const void *experts, size_t expe
     if (!host_x_res || !host_out || !dev_io || H < 1) return MB200_ERR_ARG;
     const int cnt = expert_cnt > 0 ? expert_cnt : 0x7fffffff;
     // Pinned (page-locked, mapped) host buffers are reachable from the device: a one-CTA kernel pulls x and the
-    // residual across PCIe into dev_io (one round trip instead of a copy-engine launch), and the block writes its
-    // result rows straight into the host buffer (each row is written once). Two or three kernel launches and one
-    // wait per call; no copy-engine work.
+    // residual across PCIe into dev_io (one round trip instead of a copy-engine launch), the block writes its
+    // result rows straight into the host buffer (each row is written once), and a last one-thread kernel raises a
+    // word in host memory that this call spins on. The launches of a call are kept as an instantiated graph per
+    // argument set, so a repeated call (the same layer and buffers, token after token) is one graph launch.
     void *d_in = nullptr, *d_out = nullptr;
     const bool mapped = (H % 4 == 0) && cudaHostGetDevicePointer(&d_in, const_cast<float *>(host_x_res), 0) == cudaSuccess &&
                         cudaHostGetDevicePointer(&d_out, host_out, 0) == cudaSuccess;
     if (mapped) {
-        host_stage_in_kernel<<<1, 1024, 0, stream>>>(static_cast<const float4 *>(d_in), reinterpret_cast<float4 *>(dev_io),
-                                                     2 * H / 4);
-        const int rc = mb200_moe_block_local(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts,
-                                             expert_lo, cnt, k, H, EFF, dev_io, dev_io + H, static_cast<float *>(d_out), ids,
-                                             wts, act, scratch, stream);
-        if (rc != MB200_OK) return rc;
-        return cudaStreamSynchronize(stream) == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
+        HostState &st = g_host[current_device()];
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        const bool plain = !host_state_ready(st) || cudaStreamIsCapturing(stream, &cap) != cudaSuccess ||
+                           cap != cudaStreamCaptureStatusNone;
+        auto enqueue = [&](bool signal) -> int {
+            host_stage_in_kernel<<<1, 1024, 0, stream>>>(static_cast<const float4 *>(d_in), reinterpret_cast<float4 *>(dev_io),
+                                                         2 * H / 4);
+            const int rc = mb200_moe_block_local(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts,
+                                                 expert_lo, cnt, k, H, EFF, dev_io, dev_io + H, static_cast<float *>(d_out),
+                                                 ids, wts, act, scratch, stream);
+            if (rc == MB200_OK && signal) host_signal_kernel<<<1, 1, 0, stream>>>(st.counter, st.flag_dev);
+            return rc;
+        };
+        if (plain) {  // no completion word, or the caller is capturing this stream itself
+            const int rc = enqueue(false);
+            if (rc != MB200_OK) return rc;
+            return cudaStreamSynchronize(stream) == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
+        }
+        HostKey key;
+        memset(&key, 0, sizeof(key));
+        key.router_w = router_w; key.experts = experts; key.d_in = d_in; key.d_out = d_out; key.dev_io = dev_io;
+        key.ids = ids; key.wts = wts; key.act = act; key.scratch = scratch;
+        key.stride = expert_stride; key.gate_sz = gate_sz; key.up_sz = up_sz;
+        key.down_type = down_type; key.n_experts = n_experts; key.expert_lo = expert_lo; key.cnt = cnt; key.k = k;
+        key.H = H; key.EFF = EFF; key.fused = moe_fused_mode(); key.pdl = pdl_enabled(); key.stream = stream;
+        HostEntry *hit = nullptr;
+        for (int i = 0; i < st.n; i++)
+            if (st.e[i].key == key) hit = &st.e[i];
+        bool direct = false;
+        if (!hit && cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+            (void)cudaGetLastError();  // the legacy default stream cannot be captured: plain launches, same completion word
+            direct = true;
+        }
+        if (direct) {
+            const int rc = enqueue(true);
+            if (rc != MB200_OK) return rc;
+        } else if (!hit) {
+            const int rc = enqueue(true);
+            cudaGraph_t graph = nullptr;
+            const cudaError_t ce = cudaStreamEndCapture(stream, &graph);
+            if (rc != MB200_OK || ce != cudaSuccess || !graph) {
+                if (graph) cudaGraphDestroy(graph);
+                (void)cudaGetLastError();
+                return rc != MB200_OK ? rc : MB200_ERR_LAUNCH;
+            }
+            cudaGraphExec_t exec = nullptr;
+            const cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
+            cudaGraphDestroy(graph);
+            if (ie != cudaSuccess) return MB200_ERR_LAUNCH;
+            int slot = st.n;
+            if (st.n < kHostEntries) {
+                st.n++;
+            } else {  // replace the least recently used
+                slot = 0;
+                for (int i = 1; i < kHostEntries; i++)
+                    if (st.e[i].used < st.e[slot].used) slot = i;
+                cudaGraphExecDestroy(st.e[slot].exec);
+            }
+            st.e[slot].key = key;
+            st.e[slot].exec = exec;
+            hit = &st.e[slot];
+        }
+        if (!direct) {
+            hit->used = ++st.tick;
+            if (cudaGraphLaunch(hit->exec, stream) != cudaSuccess) return MB200_ERR_LAUNCH;
+        }
+        const unsigned int want = ++st.expected;
+        // spin on the completion word (bounded: two seconds, then ask the driver)
+        for (unsigned long long spins = 0;; spins++) {
+            if (*st.flag == want) return MB200_OK;
+            if ((spins & 0xFFFFF) == 0xFFFFF) {
+                if (cudaStreamQuery(stream) != cudaErrorNotReady) break;  // finished (or failed) without the word matching
+                if (spins > (1ull << 33)) break;
+            }
+        }
+        const cudaError_t se = cudaStreamSynchronize(stream);
+        st.expected = *st.flag;  // re-align with the device counter
+        return se == cudaSuccess ? MB200_OK : MB200_ERR_LAUNCH;
     }
     (void)cudaGetLastError();  // pageable buffers: the query above failed, which is not an error of this call
     // one copy in (x and the residual are adjacent), the block, one copy out, one wait

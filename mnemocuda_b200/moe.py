@@ -105,6 +105,9 @@ class HostMoEBlock:
         self.h2d_bytes = 2 * H * 4
         self.d2h_bytes = H * 4
         self._fixed = {}  # per layer: the arguments that do not change from call to call
+        # a stream of its own: the library replays an instantiated graph per argument set, and the legacy default
+        # stream cannot be captured (there it falls back to plain launches)
+        self.stream = torch.cuda.Stream(device=moe.device)
 
     def __call__(self, layer: int, x_res_host: torch.Tensor, out_host: torch.Tensor) -> None:
         """x_res_host: pinned [2][H] (x, residual); out_host: pinned [H]."""
@@ -124,4 +127,4 @@ class HostMoEBlock:
                  m.expert_lo, m.n_local, s.K, s.H, s.EFF),
                 (self.io.data_ptr(), m.ids[layer].data_ptr(), m.wts[layer].data_ptr(), m.act.data_ptr(), m.scratch.data_ptr()))
         K._check(K._lib.lib().mb200_moe_block_host(*fx[0], x_res_host.data_ptr(), out_host.data_ptr(), *fx[1],
-                                                   torch.cuda.current_stream().cuda_stream), "mb200_moe_block_host")
+                                                   self.stream.cuda_stream), "mb200_moe_block_host")
