@@ -187,9 +187,12 @@ struct FWalk {
 
 // One warp: reads the routed ids and weights (one round trip), compacts the slots served here, and
 // lists this CTA's gate/up tiles. Returns the number of served slots.
-__device__ __noinline__ int build_tiles(const FusedParams &P, const int *ids, const float *wts, int lane, int *sid,
-                                        float *swt, int *act_list, int2 *tiles, int *n_tiles_p)
+// (Arguments by value: see split_share.)
+__device__ __noinline__ int build_tiles(int n_slots, int expert_lo, int expert_cnt, int EFF, int TB, const int *ids,
+                                        const float *wts, int lane, int *sid, float *swt, int *act_list, int2 *tiles,
+                                        int *n_tiles_p)
 {
+    struct { int n_slots, expert_lo, expert_cnt, EFF, TB; } P = {n_slots, expert_lo, expert_cnt, EFF, TB};
     int id = -1;
     float w = 0.0f;
     if (lane < P.n_slots) {
@@ -337,8 +340,15 @@ __device__ __forceinline__ void finish_down(const FusedParams &P, const FTile &t
 
 // Router logits (reference src/kernels.cu:859-880): expert row b, b + G, ... per CTA, by the twelve
 // consumer warps; then the CTA arrives at the routing barrier.
-__device__ __noinline__ void route_logits(const FusedParams &P, float *rred)
+__device__ __noinline__ void route_logits(const float *router_w, const float *x, const float *norm_w, float norm_eps,
+                                          float *logits, unsigned long long *route_ctr, int H, int n_experts, float *rred)
 {
+    struct {
+        const float *router_w, *x, *norm_w;
+        float norm_eps;
+        float *logits;
+        int H, n_experts;
+    } P = {router_w, x, norm_w, norm_eps, logits, H, n_experts};
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n4 = P.H >> 2;
     const float4 *x4 = reinterpret_cast<const float4 *>(P.x);
@@ -388,7 +398,7 @@ __device__ __noinline__ void route_logits(const FusedParams &P, float *rred)
         }
         asm volatile("bar.sync 3, %0;" ::"n"(kConsumers * 32) : "memory");
     }
-    if (tid == 0) barrier_arrive(P.sync + kFusedMaxBatches);  // release: this thread stored the CTA's logits
+    if (tid == 0) barrier_arrive(route_ctr);  // release: this thread stored the CTA's logits
     if (warp == 0) MB200_STAMP(3);
 }
 
@@ -423,21 +433,28 @@ __device__ __forceinline__ void route_warmup(const FusedParams &P, uint8_t *ring
     if (warp == 0) {  // the issuer's tile list from the made-up selection: same idea, its code is run-once too
         __syncwarp();
         int *scratch = reinterpret_cast<int *>(base + 3072);
-        build_tiles(P, ids, wts, lane, scratch, reinterpret_cast<float *>(scratch + 16), scratch + 32,
-                    reinterpret_cast<int2 *>(scratch + 64), scratch + 48);
+        build_tiles(P.n_slots, P.expert_lo, P.expert_cnt, P.EFF, P.TB, ids, wts, lane, scratch,
+                    reinterpret_cast<float *>(scratch + 16), scratch + 32, reinterpret_cast<int2 *>(scratch + 64), scratch + 48);
     }
 }
 
-__device__ __noinline__ bool route_select(const FusedParams &P, unsigned long long tgt_route, int *rid, float *rwt,
-                                          uint8_t *ring)
+__device__ __noinline__ bool route_select(const unsigned long long *route_ctr, const float *logits, int n_experts,
+                                          int n_slots, int *ids_out, float *wts_out, unsigned long long tgt_route,
+                                          int *rid, float *rwt, uint8_t *ring)
 {
+    struct {
+        const float *logits;
+        int n_experts, n_slots;
+        int *ids_out;
+        float *wts_out;
+    } P = {logits, n_experts, n_slots, ids_out, wts_out};
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     bool ok = true;
     if (tid == 0) {
         ok = false;
         for (uint32_t i = 0; i < (1u << 19); i++) {
             unsigned long long c;
-            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(P.sync + kFusedMaxBatches) : "memory");
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(route_ctr) : "memory");
             if (c >= tgt_route) {
                 ok = true;
                 break;
@@ -448,7 +465,7 @@ __device__ __noinline__ bool route_select(const FusedParams &P, unsigned long lo
     topk_group_sync(2, 128);
     if (warp == 0) MB200_STAMP(4);
     TopkShared &tsh = *reinterpret_cast<TopkShared *>(ring);  // the ring is idle until the first tile is requested
-    route_topk(const_cast<const float *>(static_cast<volatile float *>(P.logits)), rid, rwt, P.n_experts, P.n_slots, &tsh,
+    route_topk(P.logits, rid, rwt, P.n_experts, P.n_slots, &tsh,
                4, 2, 0);
     if (warp == 0) {
         MB200_STAMP(6);
@@ -463,21 +480,23 @@ __device__ __noinline__ bool route_select(const FusedParams &P, unsigned long lo
 
 // A consumer warp's share of the activation staging of batch `batch` (whose fp32 vectors have landed in the raw
 // buffer): columns [128 w, 128 w + 128) of each vector of the batch -> the int8 levels of the down phase.
+// Everything it needs comes by value. A reference to the kernel's parameter block or to a struct of the caller
+// would be read with ordinary loads (parameter space / local memory through a generic address), and any load that
+// misses L1 queues behind the weight stream for microseconds.
 template <class FD>
-__device__ __noinline__ void split_share(const FusedParams &P, uint8_t *smem, const Layout &LC, int batch, int n_act,
-                                         uint64_t *rawempty, uint64_t *xready)
+__device__ __noinline__ void split_share(const float *raw, uint8_t *xc0, int xc_stride, int EFF, int bprC, int batch,
+                                         int n_act, uint64_t *rawempty_u, uint64_t *xready_b)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int u = batch & 1;
-    const int pitch = FD::kSlotsPerBlock * P.bprC + 1;
+    const Layout LC = stream::layout<FD>(bprC, 0, 0, 1, 1);
+    const int pitch = FD::kSlotsPerBlock * bprC + 1;
     const int j0 = batch * kBatchSlots, jn = min(kBatchSlots, n_act - j0);
-    const float *raw = reinterpret_cast<const float *>(smem + P.off_raw + u * P.raw_bytes);
-    for (int c0 = warp * 128 + lane * 4; c0 < P.EFF; c0 += kConsumers * 128) {
+    for (int c0 = warp * 128 + lane * 4; c0 < EFF; c0 += kConsumers * 128) {
 #pragma unroll
         for (int j = 0; j < kBatchSlots; j++) {  // unrolled: the two vectors' shuffle chains overlap
             if (j < jn) {
-                const float4 v = *reinterpret_cast<const float4 *>(raw + (size_t)j * P.EFF + c0);
-                uint8_t *xc = smem + P.off_xc + (j0 + j) * P.xc_stride - kXBase;
+                const float4 v = *reinterpret_cast<const float4 *>(raw + (size_t)j * EFF + c0);
+                uint8_t *xc = xc0 + (j0 + j) * xc_stride;
                 split_store<FD>(v, c0, lane, pitch, reinterpret_cast<uint32_t *>(xc + LC.xq1),
                                 reinterpret_cast<uint32_t *>(xc + LC.xq2), reinterpret_cast<float *>(xc + LC.xs1),
                                 reinterpret_cast<float *>(xc + LC.xsum));
@@ -486,8 +505,8 @@ __device__ __noinline__ void split_share(const FusedParams &P, uint8_t *smem, co
     }
     __syncwarp();
     if (lane == 0) {
-        mbar_arrive(&xready[batch]);  // release: this warp's share of the levels is visible to whoever waits
-        mbar_arrive(&rawempty[u]);    // and it no longer reads the raw buffer
+        mbar_arrive(xready_b);    // release: this warp's share of the levels is visible to whoever waits
+        mbar_arrive(rawempty_u);  // and it no longer reads the raw buffer
     }
 }
 
@@ -563,12 +582,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         int n = 0;
         if (!P.router_w) {
             if (P.pdl) stream::grid_dep_wait();  // the routed ids come from the upstream kernel
-            n = build_tiles(P, P.ids, P.wts, lane, sid, swt, act_list, tiles, n_tiles_p);
+            n = build_tiles(P.n_slots, P.expert_lo, P.expert_cnt, P.EFF, P.TB, P.ids, P.wts, lane, sid, swt, act_list, tiles, n_tiles_p);
             if (lane == 0) *n_act_p = n;
         }
         __syncthreads();
         if (P.router_w) {  // the consumer warps have routed: ids and weights are in shared memory
-            n = build_tiles(P, rid, rwt, lane, sid, swt, act_list, tiles, n_tiles_p);
+            n = build_tiles(P.n_slots, P.expert_lo, P.expert_cnt, P.EFF, P.TB, rid, rwt, lane, sid, swt, act_list, tiles, n_tiles_p);
             if (lane == 0) *n_act_p = n;
             __syncthreads();
         }
@@ -739,7 +758,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     unsigned long long tgt_route = 0;
     if (P.router_w && tid == 0) tgt_route = barrier_target(P.sync + kFusedMaxBatches);  // before this CTA arrives
     if (P.pdl) stream::grid_dep_wait();  // x is produced upstream; act / y may still be in use there
-    if (P.router_w) route_logits(P, rred);
+    if (P.router_w)
+        route_logits(P.router_w, P.x, P.norm_w, P.norm_eps, P.logits, P.sync + kFusedMaxBatches, P.H, P.n_experts, rred);
     const Layout LB = stream::layout<Q4>(P.bprB, 0, 0, 1, 1);
     const Layout LC = stream::layout<FD>(P.bprC, 0, 0, 1, 1);
     {
@@ -750,7 +770,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     }
     if (warp == 0) MB200_STAMP(1);
     bool routed_ok = true;
-    if (P.router_w && warp < 4) routed_ok = route_select(P, tgt_route, rid, rwt, stages);
+    if (P.router_w && warp < 4) routed_ok = route_select(P.sync + kFusedMaxBatches, P.logits, P.n_experts, P.n_slots, P.ids_out, P.wts_out,
+                                                              tgt_route, rid, rwt, stages);
     __syncthreads();  // x is staged, barriers are initialised, the served slots are known (or the routing is done)
     if (P.router_w) {
         if (tid == 0 && !routed_ok) {
@@ -796,7 +817,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             } else if (!mbar_test_wait(&rawfull[u], par)) {
                 return;
             }
-            split_share<FD>(P, smem, LC, n_q, n_act, rawempty, xready);
+            split_share<FD>(reinterpret_cast<const float *>(smem + P.off_raw + u * P.raw_bytes), smem + P.off_xc - kXBase,
+                            P.xc_stride, P.EFF, P.bprC, n_q, n_act, &rawempty[u], &xready[n_q]);
             n_q++;
             if (blocking) return;
         }
