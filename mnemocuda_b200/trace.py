@@ -66,7 +66,11 @@ def _run(which: str) -> None:
     ex = torch.randint(0, 255, (NE * stride,), dtype=torch.uint8, device="cuda")
     # plausible block headers: d / dmin small positive halves (random bytes would give NaN / Inf scales)
     router = torch.randn(NE, H, device="cuda") / 64
-    x, res = torch.randn(H, device="cuda"), torch.randn(H, device="cuda")
+    # one activation vector per launch of the timed graph: every launch routes to other experts, so the weights
+    # come from HBM as in a decode (with one vector the 98 MB of routed experts would stay in the 126 MB L2)
+    NX = 20
+    xs, res = torch.randn(NX, H, device="cuda"), torch.randn(H, device="cuda")
+    x = xs[0]
     y, act = torch.empty(H, device="cuda"), torch.zeros(K, EFF, device="cuda")
     ids = torch.zeros(K, dtype=torch.int32, device="cuda")
     wts = torch.zeros(K, device="cuda")
@@ -80,7 +84,8 @@ def _run(which: str) -> None:
     attn = torch.randn(2 * H, device="cuda")
     hid = torch.randn(H, device="cuda")
 
-    def call(stream):
+    def call(stream, i=0):
+        x = xs[i % NX]
         if which == "moe_block_after_matvec":  # the block as it runs inside a decode layer: after the O projection
             lib.cuda_matvec_q4k_add(p(wo), p(attn), p(hid), p(hid), C.c_int(H), C.c_int(2 * H), stream)
         if which in ("moe_block", "moe_block_after_matvec"):
@@ -100,8 +105,8 @@ def _run(which: str) -> None:
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         st2 = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-        for _ in range(20):
-            call(st2)
+        for i in range(20):
+            call(st2, i)
     graph.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
