@@ -646,8 +646,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_atm_kernel(const __grid_c
             tc_fence_after();
             if (!*abort_flag) {
                 const int nrow = n0 + r;
-#pragma unroll 1
                 constexpr int kShare = kAtmBT / kAtmGroups;
+#pragma unroll 1
                 for (int c0 = par * kShare; c0 < (par + 1) * kShare; c0 += 32) {
                     if (t0 + c0 >= t_end) break;
                     uint32_t v[32];
@@ -779,38 +779,84 @@ struct SortOut {
     int *cnt, *off, *row_of_pair, *pair_of_row;
 };
 
-// One block. Thread e counts and then places the pairs routed to expert e, in pair order, so the
-// layout is deterministic. Pairs with id < 0 (empty slots) or id >= n_experts get row -1.
+// One block of 1024 threads, deterministic layout: the rows of an expert hold its pairs in pair order.
+// Pairs with id < 0 (empty slots) or id >= n_experts get row -1.
+// Counts: a shared-memory histogram (the order of the additions does not matter). Placement: the pairs are taken
+// 1024 at a time, one per thread; within a warp a pair's rank among the pairs of the same expert comes from
+// __match_any_sync, and the warps add their counts to the expert's running total one after the other, so a pair's
+// row is offset + (pairs of that expert in earlier chunks and earlier warps) + rank. (Up to 256 experts the warps
+// post their counts in a table instead of taking turns.)
 __global__ void moe_sort_kernel(const int *__restrict__ ids, int n_pairs, int n_experts, int cap, SortOut o, int *err)
 {
     __shared__ int s_off[1025];
-    const int e = threadIdx.x;
-    int c = 0;
-    if (e < n_experts)
-        for (int p = 0; p < n_pairs; p++) c += (ids[p] == e);
-    if (e < n_experts) {
-        o.cnt[e] = c;
-        s_off[e + 1] = c;
+    __shared__ int s_run[1024];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int e = tid; e < 1024; e += blockDim.x) s_run[e] = 0;
+    __syncthreads();
+    for (int p = tid; p < n_pairs; p += blockDim.x) {
+        const int id = ids[p];
+        if (id >= 0 && id < n_experts) atomicAdd(&s_run[id], 1);
+    }
+    __syncthreads();
+    if (tid < n_experts) {
+        const int c = s_run[tid];
+        o.cnt[tid] = c;
+        s_off[tid + 1] = c;
         if (c > cap) atomicExch(err, MB200_ERR_UNSUPPORTED);  // more tokens on one expert than the launch was sized for
     }
-    if (e == 0) s_off[0] = 0;
+    if (tid == 0) s_off[0] = 0;
     __syncthreads();
-    if (e == 0)
+    if (tid == 0)
         for (int i = 0; i < n_experts; i++) s_off[i + 1] += s_off[i];
     __syncthreads();
-    if (e < n_experts) o.off[e] = s_off[e];
-    if (e == 0) o.off[n_experts] = s_off[n_experts];
-    if (e < n_experts) {
-        int r = s_off[e];
-        for (int p = 0; p < n_pairs; p++)
-            if (ids[p] == e) {
+    if (tid < n_experts) o.off[tid] = s_off[tid];
+    if (tid == 0) o.off[n_experts] = s_off[n_experts];
+    for (int e = tid; e < 1024; e += blockDim.x) s_run[e] = 0;
+    __syncthreads();
+    const int n_warps = blockDim.x >> 5;
+    constexpr int kTabExperts = 256;
+    __shared__ int s_tab[32][kTabExperts];  // up to 256 experts: pairs of expert e seen by warp w in the current chunk
+    const bool tabbed = n_experts <= kTabExperts;
+    for (int p0 = 0; p0 < n_pairs; p0 += blockDim.x) {
+        const int p = p0 + tid;
+        const int id = p < n_pairs ? ids[p] : -1;
+        const bool valid = id >= 0 && id < n_experts;
+        // lanes with the same expert (invalid pairs form a group of their own that is not counted)
+        const unsigned same = __match_any_sync(0xffffffffu, valid ? id : -1);
+        const int rank = __popc(same & ((1u << lane) - 1u));
+        int base = 0;
+        if (tabbed) {
+            // three barriers per chunk: every warp posts its counts, every pair adds up the warps before its own
+            for (int i = tid; i < 32 * n_experts; i += blockDim.x) s_tab[i / n_experts][i % n_experts] = 0;
+            __syncthreads();
+            if (valid && rank == 0) s_tab[warp][id] = __popc(same);
+            __syncthreads();
+            if (valid) {
+                base = s_run[id];
+                for (int w = 0; w < warp; w++) base += s_tab[w][id];
+            }
+            __syncthreads();
+            if (valid && rank == 0) atomicAdd(&s_run[id], __popc(same));  // integer adds: the order does not matter
+        } else {
+            for (int w = 0; w < n_warps; w++) {  // the warps take turns
+                if (warp == w && valid) {
+                    base = s_run[id];
+                    __syncwarp(same);
+                    if (rank == 0) s_run[id] = base + __popc(same);
+                }
+                __syncthreads();
+            }
+        }
+        if (p < n_pairs) {
+            if (valid) {
+                const int r = s_off[id] + base + rank;
                 o.row_of_pair[p] = r;
                 o.pair_of_row[r] = p;
-                r++;
+            } else {
+                o.row_of_pair[p] = -1;
             }
+        }
     }
-    for (int p = e; p < n_pairs; p += blockDim.x)
-        if (ids[p] < 0 || ids[p] >= n_experts) o.row_of_pair[p] = -1;
 }
 
 // Xs[row] = X[token of the pair in that row]; one block per row, 16-byte copies

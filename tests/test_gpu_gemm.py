@@ -104,7 +104,8 @@ def _moe_prefill_oracle(experts, stride, g, u, down_type, H, EFF, x16, ids, wts,
 
 
 @pytest.mark.parametrize("M,NE,k,H,EFF,down_type", [(48, 8, 2, 512, 256, 14), (96, 16, 4, 1024, 512, 14),
-                                                     (40, 8, 3, 512, 256, 12), (130, 4, 2, 512, 256, 14)])
+                                                     (40, 8, 3, 512, 256, 12), (130, 4, 2, 512, 256, 14),
+                                                     (40, 300, 2, 512, 256, 14)])  # > 256 experts: the sort's turn-taking path
 def test_moe_prefill_grouped(K, M, NE, k, H, EFF, down_type):
     g, u, d = synth.expert_sizes(H, EFF, down_type)
     stride = g + u + d
