@@ -11,7 +11,7 @@ without it. This module builds the instrumented copy next to the product library
 
 Slots of the fused kernel (ns after the earliest CTA entry; median over CTAs):
   0 entry | 3 logits stored, routing barrier arrived | 1 x split done | 4 routing barrier complete |
-  6 top-k done | 47 tile list ready, first copy requested | 15 first gate/up tile landed |
+  44-46 top-k: candidates listed / accept flags counted / accepted compacted | 6 top-k done | 47 tile list ready, first copy requested | 15 first gate/up tile landed |
   7-10 arrival at batch barrier 0-3 | 11-14 batch barrier 0-3 complete, activations being fetched |
   2 gate/up phase done (consumer warp 0) | 32,34,36,38 / 33,35,37,39 down phase needs / has batch 0-3 |
   24-31 down tile k landed | 16-23 down tile k finished by all consumers | 40-43 down tile k requested |
@@ -32,6 +32,7 @@ CSRC = os.path.join(HERE, "csrc")
 TRACE_LIB = os.path.join(HERE, "libmnemo_b200_trace.so")
 
 FUSED_SLOTS = {0: "entry", 3: "logits stored + arrived", 1: "x split done", 4: "routing barrier complete",
+               44: "top-k: candidates listed", 45: "top-k: accept flags counted", 46: "top-k: accepted compacted",
                6: "top-k done", 47: "first copy requested", 15: "first gate/up tile landed",
                7: "arrive batch 0", 8: "arrive batch 1", 9: "arrive batch 2", 10: "arrive batch 3",
                11: "batch 0 complete", 12: "batch 1 complete", 13: "batch 2 complete", 14: "batch 3 complete",
