@@ -59,9 +59,10 @@ FUSED_TRAFFIC_BYTES = 98054912 + 3864064     # the fused routed-expert kernel al
 def _launches_per_token(cfg, world: int) -> int:
     """Kernels of this library per decoded token: embedding + RoPE table; per layer Q/K/V (one launch), q/k-norm +
     RoPE + KV store, attention, O projection, MoE block (one launch where the one-launch form covers the shape,
-    else router + gate/up + down), plus the three exchanges of a sharded layer; lm_head + sampling."""
+    else router + gate/up + down), plus the exchanges of a sharded layer (two all-gathers and, where the block is not
+    one launch with its all-reduce inside, the all-reduce); lm_head + sampling."""
     moe = 1 if (cfg.hidden % 2048 == 0 and cfg.moe_inter % 512 == 0) else 3
-    per_layer = 4 + moe + (3 if world > 1 else 0)
+    per_layer = 4 + moe + ((2 if moe == 1 else 3) if world > 1 else 0)
     return 2 + per_layer * cfg.n_layers + (2 if world == 1 else 4)
 
 

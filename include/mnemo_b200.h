@@ -327,6 +327,21 @@ int mb200_moe_block_local(const float *router_w, const void *experts, size_t exp
                           int H, int EFF, const float *x, const float *residual, float *out, int *ids,
                           float *wts, float *act, void *scratch, cudaStream_t stream);
 
+/* The expert-sharded block WITH its all-reduce, in the same launch: the warp that finishes a row of the down
+ * projection stores this rank's partial value into the receive cells of every rank of `comm` (mb200_comm_create;
+ * plain 8-byte stores over NVLink, value and sequence tag together), and once a CTA's rows are out it collects the
+ * other ranks' values of the same rows (bounded wait -> MB200_ERR_TIMEOUT in the device error word) and writes
+ * out = sum over the ranks in rank order: identical bits on every rank, the same bits as mb200_moe_block_local
+ * followed by mb200_push_allreduce, one launch and one kernel tail less. `residual` may be null (pass it on one rank).
+ * norm_w != NULL folds the RMSNorm of x in (as mb200_moe_block_norm). Every rank of the communicator must make the
+ * call, in the same order relative to its other collectives. Only the one-launch form has it: returns
+ * MB200_ERR_UNSUPPORTED, with nothing launched, where that form does not cover the shape or after
+ * mb200_set_fused(0 / 1); the caller then uses the two calls named above. */
+int mb200_moe_block_push(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz,
+                         int down_type, int n_experts, int expert_lo, int expert_cnt, int k, int H, int EFF,
+                         const float *x, const float *norm_w, float norm_eps, const float *residual, float *out, int *ids,
+                         float *wts, float *act, void *scratch, void *comm, cudaStream_t stream);
+
 /* mb200_moe_block_local on RMSNorm(x) (the pre-FFN norm of src/forward.c:810, folded in): norm_w [H], eps; in the
  * one-launch form the router and the gate/up products normalise x on the fly, the other forms run a norm
  * kernel into normed_scratch [H] first. norm_w NULL = x is used as given. */
@@ -448,6 +463,10 @@ int mb200_decode_layer_oproj(const mb200_decode_model *m, int layer, void *works
                              float *hidden_rows, cudaStream_t stream);
 int mb200_decode_layer_moe(const mb200_decode_model *m, int layer, void *workspace, int add_residual, float *out,
                            cudaStream_t stream);
+/* mb200_decode_layer_moe followed by the all-reduce over `comm` into `out`: one launch where mb200_moe_block_push
+ * applies, else the block into `partial` [hidden] and mb200_push_allreduce. */
+int mb200_decode_layer_moe_reduce(const mb200_decode_model *m, int layer, void *workspace, int add_residual,
+                                  float *partial, float *out, void *comm, cudaStream_t stream);
 int mb200_decode_logits_local(const mb200_decode_model *m, void *workspace, float *logits_rows, float *best_pair,
                               cudaStream_t stream);
 int mb200_decode_pick(const float *pairs, int n_pairs, int *d_token, int *d_pos, cudaStream_t stream);

@@ -91,6 +91,8 @@ SIGNATURES = {
     "mb200_comm_create_ptrs": (_i, [_i, _i, _sz, _vp, _vp]),
     "mb200_comm_destroy": (None, [_vp, _i]),
     "mb200_push_allreduce": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "mb200_moe_block_push": (_i, [_vp, _vp, _sz, _sz, _sz, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mb200_decode_layer_moe_reduce": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp]),
     "mb200_push_allgather": (_i, [_vp, _vp, _vp, _i, _vp]),
     "mb200_decode_layer_attn": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),
     "mb200_decode_layer_oproj": (_i, [_vp, _i, _vp, _vp, _vp, _vp]),

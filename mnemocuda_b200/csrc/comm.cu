@@ -19,17 +19,15 @@
 #include <cstdio>
 #include <cstring>
 
-#include "common.cuh"
+#include "comm.cuh"
 
 namespace mb200 {
 int pdl_enabled();
 
 namespace {
 
-constexpr int kMaxWorld = 8;
 constexpr int kPushCtas = 8;
 constexpr int kPushThreads = 256;
-constexpr long long kSpinBudgetNs = 2000000000ll;  // 2 s of wall clock, then MB200_ERR_TIMEOUT
 
 // Receive area of one rank: [2 parities][world sources][max_floats] cells of 8 bytes -- a float and the
 // 32-bit sequence number of the collective that wrote it, stored together with ONE 8-byte store (single-copy
@@ -73,34 +71,6 @@ struct PushParams {
     int reduce;        // 1: sum of the pieces in rank order; 0: concatenation
     int *err;
 };
-
-__device__ __forceinline__ void st_cell(uint2 *p, float v, uint32_t tag)
-{
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
-}
-__device__ __forceinline__ uint2 ld_cell(const uint2 *p)
-{
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
-}
-
-// Spins until the cell carries `tag`; false once the time budget is spent.
-__device__ __forceinline__ bool wait_cell(const uint2 *p, uint32_t tag, float &v, long long t0)
-{
-    for (unsigned it = 0;; it++) {
-        const uint2 c = ld_cell(p);
-        if (c.y == tag) {
-            v = __uint_as_float(c.x);
-            return true;
-        }
-        if ((it & 255) == 255) {
-            long long t1;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-            if (t1 - t0 > kSpinBudgetNs) return false;
-        }
-    }
-}
 
 __global__ void __launch_bounds__(kPushThreads) push_collective_kernel(const PushParams P)
 {
@@ -185,6 +155,21 @@ int launch_push(Comm *c, const float *in, float *out, int n, int reduce, cudaStr
 }
 
 }  // namespace
+
+bool comm_describe(void *comm, PushDesc *d)
+{
+    const Comm *c = static_cast<const Comm *>(comm);
+    if (!c || !d) return false;
+    for (int p = 0; p < kMaxWorld; p++) d->peer_cells[p] = p < c->world ? c->buf[p].cells : nullptr;
+    d->self_cells = c->buf[c->rank].cells;
+    d->seq = c->buf[c->rank].seq;
+    d->ticket = c->buf[c->rank].ticket;
+    d->rank = c->rank;
+    d->world = c->world;
+    d->max_floats = c->max_floats;
+    return true;
+}
+
 }  // namespace mb200
 
 using namespace mb200;

@@ -292,6 +292,37 @@ int mb200_decode_layer_moe(const mb200_decode_model *m, int layer, void *workspa
     return mb200_last_status();
 }
 
+int mb200_decode_layer_moe_reduce(const mb200_decode_model *m, int layer, void *workspace, int add_residual,
+                                  float *partial, float *out, void *comm, cudaStream_t stream)
+{
+    int rc = check_model(m);
+    if (rc != MB200_OK) return rc;
+    if (!workspace || !out || !partial || !comm || layer < 0 || layer >= m->n_layers) return MB200_ERR_ARG;
+    mb200_clear_status();
+    {   // the block and its all-reduce in one launch, where that form exists
+        const mb200_layer_weights &L = m->layers[layer];
+        uint8_t *ws = static_cast<uint8_t *>(workspace);
+        const Workspace W = layout(*m);
+        const Bufs B = bufs(*m, ws, W);
+        const bool own = L.expert_stride != 0;
+        rc = mb200_moe_block_push(L.router, L.experts, own ? L.expert_stride : m->expert_stride, own ? L.gate_sz : m->gate_sz,
+                                  own ? L.up_sz : m->up_sz, own ? L.down_type : m->down_type, m->n_experts, m->expert_lo,
+                                  m->expert_cnt > 0 ? m->expert_cnt : 0x7fffffff, m->top_k, m->hidden, m->moe_inter, B.hidden,
+                                  L.ffn_norm, m->rms_eps, add_residual ? B.hidden : nullptr, out,
+                                  reinterpret_cast<int *>(ws + W.ids), reinterpret_cast<float *>(ws + W.wts),
+                                  reinterpret_cast<float *>(ws + W.act), ws + W.scratch, comm, stream);
+        if (rc == MB200_OK) return cudaGetLastError() == cudaSuccess ? mb200_last_status() : MB200_ERR_LAUNCH;
+        if (rc != MB200_ERR_UNSUPPORTED && rc != MB200_ERR_LAUNCH) return rc;
+        (void)cudaGetLastError();
+    }
+    rc = run_moe(*m, m->layers[layer], static_cast<uint8_t *>(workspace), layout(*m), add_residual != 0, partial, stream);
+    if (rc != MB200_OK) return rc;
+    rc = mb200_push_allreduce(comm, partial, out, m->hidden, stream);
+    if (rc != MB200_OK) return rc;
+    if (cudaGetLastError() != cudaSuccess) return MB200_ERR_LAUNCH;
+    return mb200_last_status();
+}
+
 int mb200_decode_logits_local(const mb200_decode_model *m, void *workspace, float *logits_rows, float *best_pair,
                               cudaStream_t stream)
 {

@@ -12,7 +12,7 @@
 #include <cstdio>
 #include <cstring>
 
-#include "common.cuh"
+#include "comm.cuh"
 #include "topk.cuh"
 
 namespace mb200 {
@@ -31,7 +31,7 @@ int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off
               const int *ids, const float *wts, int n_slots, int expert_lo, int expert_cnt, const float *x, float *act,
               const float *residual, float *y, int H, int EFF, unsigned long long *sync, cudaStream_t stream,
               const float *router_w, int n_experts, float *logits, int *ids_out, float *wts_out, const float *norm_w,
-              float norm_eps);
+              float norm_eps, const PushDesc *push = nullptr);
 void launch_rms_norm(const float *in, const float *w, float *out, float *res_out, int n, float eps, cudaStream_t stream);
 void moe_fused_set_mode(int mode);
 int moe_fused_mode();
@@ -346,6 +346,26 @@ int mb200_moe_block_local(const float *router_w, const void *experts, size_t exp
 {
     return mb200_moe_block_norm(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts, expert_lo, expert_cnt,
                                 k, H, EFF, x, nullptr, 0.0f, nullptr, residual, out, ids, wts, act, scratch, stream);
+}
+
+int mb200_moe_block_push(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz,
+                         int down_type, int n_experts, int expert_lo, int expert_cnt, int k, int H, int EFF,
+                         const float *x, const float *norm_w, float norm_eps, const float *residual, float *out, int *ids,
+                         float *wts, float *act, void *scratch, void *comm, cudaStream_t stream)
+{
+    if (!router_w || !x || !scratch || !ids || !wts || !act || !out || !comm || n_experts < 1 || H < 1 || k < 1 || k > 16 ||
+        expert_lo < 0 || expert_cnt < 0)
+        return MB200_ERR_ARG;
+    if (reinterpret_cast<uintptr_t>(scratch) & 15) return MB200_ERR_ARG;
+    if (moe_fused_mode() != 2) return MB200_ERR_UNSUPPORTED;
+    PushDesc d;
+    if (!comm_describe(comm, &d)) return MB200_ERR_ARG;
+    unsigned long long *sync =
+        reinterpret_cast<unsigned long long *>(static_cast<char *>(scratch) + router_part_bytes(n_experts));
+    float *logits = reinterpret_cast<float *>(static_cast<int *>(scratch) + 8);
+    return moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, nullptr, nullptr, k, expert_lo,
+                     expert_cnt, x, act, residual, out, H, EFF, sync, stream, router_w, n_experts, logits, ids, wts, norm_w,
+                     norm_eps, &d);
 }
 
 int mb200_moe_block_norm(const float *router_w, const void *experts, size_t expert_stride, size_t gate_sz, size_t up_sz,

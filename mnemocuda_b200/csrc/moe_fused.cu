@@ -32,6 +32,7 @@
 // number of polls, setting the library's device error word instead of hanging.
 #include <cstdio>
 
+#include "comm.cuh"
 #include "q4k_policy.cuh"
 #include "q6k_policy.cuh"
 #ifdef MB200_TRACE
@@ -98,6 +99,11 @@ struct FusedParams {
     // RMSNorm of x folded in (x' = x * norm_w / sqrt(mean(x^2) + norm_eps)): the router and the gate/up products use x'
     const float *norm_w;
     float norm_eps;
+    // Expert-sharded engines (push.world > 0): the block's all-reduce inside the kernel. The warp that finishes a row
+    // stores this rank's partial value ((residual +) weighted sum over the slots served here) into every rank's
+    // receive cells, and once the CTA's rows are out it collects the other ranks' values for the same rows and writes
+    // y = their sum in rank order (CTA b owns the same rows on every rank).
+    PushDesc push;
 };
 
 struct FTile {
@@ -318,8 +324,9 @@ __device__ __forceinline__ void finish_gate_up(const FusedParams &P, const FTile
 
 // Finishes a down tile: adds the slot's weighted rows to the running sums (slot order), and after the
 // last served slot writes y.
+template <bool PUSH>
 __device__ __forceinline__ void finish_down(const FusedParams &P, const FTile &t, const float *pt, float *run,
-                                            float w, int n_act, int lane)
+                                            float w, int n_act, int lane, uint32_t push_tag, size_t push_off)
 {
     const int NG = P.ngC;
     for (int r = lane; r < t.rows; r += 32) {
@@ -328,9 +335,60 @@ __device__ __forceinline__ void finish_down(const FusedParams &P, const FTile &t
         const float a = fmaf(w, v, t.j == 0 ? 0.0f : run[r]);
         if (t.j == n_act - 1) {
             const int row = t.row0 + r;
-            P.y[row] = __ldcg(P.residual ? P.residual + row : P.y + row) + a;
+            if (PUSH) {
+                const float mine = (P.residual ? __ldcg(P.residual + row) : 0.0f) + a;
+#pragma unroll 1
+                for (int p = 0; p < P.push.world; p++) st_cell(P.push.peer_cells[p] + push_off + row, mine, push_tag);
+            } else {
+                P.y[row] = __ldcg(P.residual ? P.residual + row : P.y + row) + a;
+            }
         } else {
             run[r] = a;
+        }
+    }
+}
+
+// Push mode, one warp, after this CTA's rows [r0, r1) have been stored to every rank: collect every rank's value of
+// those rows from the local cells (bounded wait), y = sum in rank order; then the launch ticket (the last CTA of
+// the launch publishes the sequence number for the next collective). `zero_mine`: this CTA had nothing to add, its
+// rows go out here first ((residual +) 0).
+__device__ __forceinline__ void push_collect(const FusedParams &P, unsigned long long seq, bool zero_mine, int lane)
+{
+    const uint32_t tag = static_cast<uint32_t>(seq);
+    const size_t par_off = (size_t)(seq & 1) * P.push.world * P.push.max_floats;
+    const int r0 = static_cast<int>((long long)P.H * blockIdx.x / gridDim.x);
+    const int r1 = static_cast<int>((long long)P.H * (blockIdx.x + 1) / gridDim.x);
+    if (zero_mine)
+        for (int row = r0 + lane; row < r1; row += 32) {
+            const float mine = P.residual ? __ldcg(P.residual + row) : 0.0f;
+#pragma unroll 1
+            for (int p = 0; p < P.push.world; p++)
+                st_cell(P.push.peer_cells[p] + par_off + (size_t)P.push.rank * P.push.max_floats + row, mine, tag);
+        }
+    long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    bool ok = true;
+    for (int row = r0 + lane; row < r1 && ok; row += 32) {
+        float acc = 0.0f;
+        for (int q = 0; q < P.push.world; q++) {  // fixed order: every rank computes the same bits
+            float v;
+            if (!wait_cell(P.push.self_cells + par_off + (size_t)q * P.push.max_floats + row, tag, v, t0)) {
+                ok = false;
+                break;
+            }
+            acc = q == 0 ? v : acc + v;
+        }
+        if (ok) P.y[row] = acc;
+    }
+    if (!ok) atomicExch(P.err, MB200_ERR_TIMEOUT);
+    __syncwarp();
+    if (lane == 0) {
+        __threadfence();
+        if (atomicAdd(P.push.ticket, 1u) == gridDim.x - 1) {
+            *P.push.ticket = 0;
+            // after a timeout the sequence still advances, so that the ranks stay in step if the caller retries
+            *P.push.seq = seq;
+            __threadfence();
         }
     }
 }
@@ -510,7 +568,7 @@ __device__ __noinline__ void split_share(const float *raw, uint8_t *xc0, int xc_
     }
 }
 
-template <class FD>
+template <class FD, bool PUSH>
 __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __grid_constant__ FusedParams P)
 {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -649,6 +707,30 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         for (int b = 0; b < kFusedMaxBatches; b++) tgt[b] = barrier_target(P.sync + b);  // before this CTA can have arrived
         __syncthreads();
         if (P.router_w) __syncthreads();
+        if (PUSH && *n_act_p == 0 && !*abort_flag) {
+            // No routed expert lives on this rank: its share of the all-reduce is (residual +) 0. `out` may be the very
+            // vector the CTAs have just read as x, so the rows are only written once every CTA is past its reads: the
+            // first batch barrier (otherwise unused in such a launch) counts them.
+            bool met = true;
+            if (lane == 0) {
+                barrier_arrive(P.sync + 0);
+                met = false;
+                for (uint32_t i = 0; i < (1u << 18); i++) {
+                    unsigned long long c;
+                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(P.sync + 0) : "memory");
+                    if (c >= tgt[0]) {
+                        met = true;
+                        break;
+                    }
+                    __nanosleep(200);
+                }
+                if (!met) atomicExch(P.err, MB200_ERR_TIMEOUT);
+            }
+            met = __shfl_sync(0xffffffffu, met, 0);
+            if (P.pdl) stream::grid_dep_wait();  // the previous collective on this communicator has published its number
+            if (met) push_collect(P, __ldcg(P.push.seq) + 1, true, lane);
+            return;
+        }
         if (lane != 0 || *abort_flag) return;
         const int n_act = *n_act_p;
         const int nb = (n_act + kBatchSlots - 1) / kBatchSlots;
@@ -722,7 +804,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         if (P.router_w) __syncthreads();
         if (*abort_flag) return;
         const int n_act = *n_act_p;
-        if (n_act == 0) return;
+        if (n_act == 0) return;  // (push mode: the courier warp sends and collects this CTA's rows)
+        unsigned long long pseq = 0;
+        if (PUSH) {
+            if (P.pdl) stream::grid_dep_wait();  // the previous collective on this communicator has published its number
+            pseq = __ldcg(P.push.seq) + 1;       // the same on every CTA: written only by the last CTA of a launch
+        }
+        const size_t push_off = ((size_t)(pseq & 1) * P.push.world + P.push.rank) * P.push.max_floats;
         walk.init(P, tiles, *n_tiles_p, act_list, n_act);
         FTile t;
         int ib = 0, ic = 0;
@@ -744,13 +832,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
                 if (!mbar_wait(&cempty[c], (ic / CS) & 1)) *abort_flag = 1;
                 if (*abort_flag) break;
                 if (ic < 8) MB200_STAMP(16 + ic);  // all consumers done with down tile ic
-                finish_down(P, t, cpart + c * P.part_pitch, run, swt[t.slot], n_act, lane);
+                finish_down<PUSH>(P, t, cpart + c * P.part_pitch, run, swt[t.slot], n_act, lane, static_cast<uint32_t>(pseq), push_off);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&cfull[c]);
                 ic++;
             }
         }
         if (*abort_flag && lane == 0) atomicExch(P.err, MB200_ERR_TIMEOUT);
+        if (PUSH && !*abort_flag) push_collect(P, pseq, false, lane);
         return;
     }
 
@@ -784,7 +873,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     const int n_act = *n_act_p;
     if (n_act == 0) {
         // no routed expert is served here: the block reduces to the residual (if this call carries one)
-        if (warp == 0 && P.residual) {
+        if (PUSH) {
+            // (the courier warp sends and collects this CTA's rows, once every CTA has read x: out may be x)
+        } else if (warp == 0 && P.residual) {
             const int r0 = static_cast<int>((long long)P.H * blockIdx.x / gridDim.x);
             const int r1 = static_cast<int>((long long)P.H * (blockIdx.x + 1) / gridDim.x);
             for (int r = r0 + lane; r < r1; r += 32) P.y[r] = __ldcg(P.residual + r);
@@ -940,13 +1031,13 @@ int g_fused_mode = 2;          // see mb200_set_fused
 int g_fused_pdl_ok = 1;        // cleared if the driver refuses cooperative + programmatic serialization together
 
 // Shared-memory opt-in of the kernel, once per device (a per-device attribute).
-template <class FD>
+template <class FD, bool PUSH>
 bool fused_attr()
 {
     static bool done[kMaxDevices] = {false};
     const int dev = current_device();
     if (done[dev]) return true;
-    if (cudaFuncSetAttribute(moe_fused_kernel<FD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+    if (cudaFuncSetAttribute(moe_fused_kernel<FD, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
         cudaSuccess) {
         cudaGetLastError();
         return false;
@@ -955,10 +1046,12 @@ bool fused_attr()
     return true;
 }
 
-template <class FD>
-int launch_fused(FusedParams &P, int smem_bytes, cudaStream_t stream)
+// PUSH: the instantiation with the all-reduce over the ranks in its epilogue (a kernel of its own, so that the
+// single-device kernel's instruction layout is what it was without it).
+template <class FD, bool PUSH>
+int launch_fused_as(FusedParams &P, int smem_bytes, cudaStream_t stream)
 {
-    if (!fused_attr<FD>()) return MB200_ERR_LAUNCH;
+    if (!fused_attr<FD, PUSH>()) return MB200_ERR_LAUNCH;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(P.grid);
     cfg.blockDim = dim3(kFusedThreads);
@@ -972,13 +1065,13 @@ int launch_fused(FusedParams &P, int smem_bytes, cudaStream_t stream)
     cfg.attrs = attr;
     P.pdl = (pdl_enabled() && g_fused_pdl_ok) ? 1 : 0;
     cfg.numAttrs = P.pdl ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, moe_fused_kernel<FD>, P);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, moe_fused_kernel<FD, PUSH>, P);
     if (e != cudaSuccess && P.pdl) {
         cudaGetLastError();
         g_fused_pdl_ok = 0;
         P.pdl = 0;
         cfg.numAttrs = 1;
-        e = cudaLaunchKernelEx(&cfg, moe_fused_kernel<FD>, P);
+        e = cudaLaunchKernelEx(&cfg, moe_fused_kernel<FD, PUSH>, P);
     }
     if (e != cudaSuccess) {
         fprintf(stderr, "[mnemo_b200] fused expert kernel launch failed: %s\n", cudaGetErrorString(e));
@@ -986,6 +1079,11 @@ int launch_fused(FusedParams &P, int smem_bytes, cudaStream_t stream)
         return MB200_ERR_LAUNCH;
     }
     return MB200_OK;
+}
+template <class FD>
+int launch_fused(FusedParams &P, int smem_bytes, cudaStream_t stream)
+{
+    return P.push.world > 0 ? launch_fused_as<FD, true>(P, smem_bytes, stream) : launch_fused_as<FD, false>(P, smem_bytes, stream);
 }
 
 }  // namespace
@@ -1065,8 +1163,10 @@ static bool fused_layout(FusedParams &P, int &smem_bytes)
 
 void moe_fused_init()
 {
-    fused_attr<Q6>();
-    fused_attr<Q4>();
+    fused_attr<Q6, false>();
+    fused_attr<Q4, false>();
+    fused_attr<Q6, true>();
+    fused_attr<Q4, true>();
 }
 void moe_fused_set_mode(int mode) { g_fused_mode = mode; }
 int moe_fused_mode() { return g_fused_mode; }
@@ -1078,9 +1178,14 @@ int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off
               const int *ids, const float *wts, int n_slots, int expert_lo, int expert_cnt, const float *x, float *act,
               const float *residual, float *y, int H, int EFF, unsigned long long *sync, cudaStream_t stream,
               const float *router_w, int n_experts, float *logits, int *ids_out, float *wts_out, const float *norm_w,
-              float norm_eps)
+              float norm_eps, const PushDesc *push)
 {
     FusedParams P{};
+    if (push) {  // the all-reduce over the ranks inside the kernel: only with the routing inside as well
+        if (!router_w || push->world < 1 || push->world > kMaxWorld || static_cast<unsigned long long>(H) > push->max_floats)
+            return MB200_ERR_UNSUPPORTED;
+        P.push = *push;
+    }
     if (norm_w && (H > 4 * 3 * stream::kQuantThreads || (reinterpret_cast<uintptr_t>(norm_w) & 15))) return MB200_ERR_UNSUPPORTED;
     P.norm_w = norm_w;
     P.norm_eps = norm_eps;

@@ -318,6 +318,7 @@ class ResidentModel:
             self.attn_local, self.attn_full = f32(sp["nq"] * HD), f32(QDT)
             self.hidden_rows, self.partial = f32(sp["o_rows"]), f32(c.hidden)
             self.pair, self.pairs = f32(2), f32(2 * world)
+            self.fused_push = True  # the MoE block's all-reduce inside its kernel (False: block, then push all-reduce)
         torch.cuda.synchronize(self.device)
 
     # ---- state ----
@@ -348,6 +349,11 @@ class ResidentModel:
         K._check(lib.mb200_decode_layer_oproj(d, l, ws, self.attn_full.data_ptr(), self.hidden_rows.data_ptr(), st),
                  "mb200_decode_layer_oproj")
         self.comm.allgather(self.hidden_rows, self.hidden, stream)
+        if self.fused_push:  # the block and its all-reduce in one launch where that form applies
+            K._check(lib.mb200_decode_layer_moe_reduce(d, l, ws, 1 if self.rank == 0 else 0, self.partial.data_ptr(),
+                                                       self.hidden.data_ptr(), self.comm._comm, st),
+                     "mb200_decode_layer_moe_reduce")
+            return
         K._check(lib.mb200_decode_layer_moe(d, l, ws, 1 if self.rank == 0 else 0, self.partial.data_ptr(), st),
                  "mb200_decode_layer_moe")
         self.comm.allreduce(self.partial, self.hidden, stream)

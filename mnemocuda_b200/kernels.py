@@ -12,6 +12,7 @@ import torch
 from . import _lib
 
 MB200_OK = 0
+MB200_ERR_UNSUPPORTED = 4  # include/mnemo_b200.h
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:
@@ -330,6 +331,21 @@ def mb200_moe_block_local(router_w, experts, expert_stride, gate_sz, up_sz, down
                                             n_experts, expert_lo, expert_cnt, k, H, EFF, _f32(x), _ptr(residual),
                                             _f32(out), _ptr(ids), _f32(wts), _f32(act), _ptr(scratch), _stream(stream)),
            "mb200_moe_block_local")
+
+
+def mb200_moe_block_push(router_w, experts, expert_stride, gate_sz, up_sz, down_type, n_experts, expert_lo, expert_cnt, k,
+                         H, EFF, x, norm_w, norm_eps, residual, out, ids, wts, act, scratch, comm, stream=None) -> bool:
+    """The expert-sharded block with its all-reduce over `comm` (a communicator handle) in the same launch.
+    Returns False, with nothing launched, where the one-launch form does not apply (the caller then uses
+    mb200_moe_block_local + a push all-reduce)."""
+    rc = _lib.lib().mb200_moe_block_push(_f32(router_w), _ptr(experts), expert_stride, gate_sz, up_sz, down_type,
+                                         n_experts, expert_lo, expert_cnt, k, H, EFF, _f32(x), _ptr(norm_w),
+                                         float(norm_eps), _ptr(residual), _f32(out), _ptr(ids), _f32(wts), _f32(act),
+                                         _ptr(scratch), comm, _stream(stream))
+    if rc == MB200_ERR_UNSUPPORTED:
+        return False
+    _check(rc, "mb200_moe_block_push")
+    return True
 
 
 def mb200_moe_experts_fused(experts, expert_stride, gate_off, up_off, down_off, down_type, ids, wts, n_slots, expert_lo,

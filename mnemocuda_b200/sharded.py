@@ -78,12 +78,19 @@ class ShardedMoE:
         self.lo, self.cnt = moe.expert_lo, moe.n_local
         self.zero = torch.zeros(moe.shape.H, dtype=torch.float32, device=moe.device)
         self.partial = torch.zeros(moe.shape.H, dtype=torch.float32, device=moe.device)
+        self.fused_push = True  # False: block and push all-reduce as two launches (A/B runs, tests)
 
     def forward(self, layer: int, x: torch.Tensor, residual: torch.Tensor, out: torch.Tensor, reduce=True) -> None:
         """This rank's partial block (one launch where the fused kernel covers the shape), then the all-reduce."""
         s, m, K = self.moe.shape, self.moe, self.K
-        res = residual if self.rank == 0 else self.zero
         push = reduce and self.world > 1 and self.comm is not None
+        if push and self.fused_push:
+            # the block and its all-reduce in one launch (the kernel's epilogue pushes the rows to the peers)
+            if K.mb200_moe_block_push(m.router[layer], m.experts[layer], s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE,
+                                      self.lo, self.cnt, s.K, s.H, s.EFF, x, None, 0.0, residual if self.rank == 0 else None,
+                                      out, m.ids[layer], m.wts[layer], m.act, m.scratch, self.comm._comm):
+                return
+        res = residual if self.rank == 0 else self.zero
         dst = self.partial if push else out
         K.mb200_moe_block_local(m.router[layer], m.experts[layer], s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE,
                                 self.lo, self.cnt, s.K, s.H, s.EFF, x, res, dst, m.ids[layer], m.wts[layer], m.act,

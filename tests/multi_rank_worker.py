@@ -72,6 +72,42 @@ def main():
         rel = float((out.double() - want.double()).norm() / want.double().norm())
         assert rel <= 1e-5, (rank, use_comm is not None, rel)
         assert torch.equal(part.ids[0], full.ids[0])
+    # the all-reduce inside the block's kernel (the default with a communicator) against block + push all-reduce:
+    # the same bits, on every rank
+    outs = []
+    for fused_push in (True, False):
+        sm = sharded.ShardedMoE(part, rank, world, comm=comm)
+        sm.fused_push = fused_push
+        out = torch.full((s.H,), float("nan"), device=dev)
+        for _ in range(3):
+            sm.forward(0, xh, rh, out)
+        torch.cuda.synchronize()
+        outs.append(out.clone())
+    assert torch.equal(outs[0], outs[1]), (rank, float((outs[0] - outs[1]).abs().max()))
+    ref = outs[0].clone()
+    dist.broadcast(ref, 0)
+    assert torch.equal(outs[0], ref)
+    # every routed expert on rank 0 (the other ranks contribute zeros from a launch that serves no slot)
+    keep_f, keep_p = full.router[0].clone(), part.router[0].clone()
+    n_first = sharded.expert_range(s.NE, world, 0)[1]
+    if n_first >= s.K:
+        for m_ in (full, part):
+            m_.router[0][n_first:] = (-10.0 / float(xh.double().dot(xh.double()))) * xh
+        full.forward(0, xh, rh, want)
+        assert int(full.ids[0].max()) < n_first
+        for fused_push in (True, False):
+            sm = sharded.ShardedMoE(part, rank, world, comm=comm)
+            sm.fused_push = fused_push
+            out = torch.full((s.H,), float("nan"), device=dev)
+            for _ in range(2):
+                sm.forward(0, xh, rh, out)
+            torch.cuda.synchronize()
+            rel = float((out.double() - want.double()).norm() / want.double().norm())
+            assert rel <= 1e-5, (rank, fused_push, rel)
+        full.router[0].copy_(keep_f)
+        part.router[0].copy_(keep_p)
+        full.forward(0, xh, rh, want)
+    assert K.mb200_device_error() == 0
     # replay from a CUDA graph (push reduction)
     sm = sharded.ShardedMoE(part, rank, world, comm=comm)
     out = torch.empty(s.H, device=dev)

@@ -322,3 +322,58 @@ def test_block_with_the_rmsnorm_folded_in(K, NE, k, H, EFF):
     finally:
         K.mb200_set_fused(2)
     assert K.mb200_device_error() == 0
+
+
+def test_block_with_its_allreduce_inside_on_a_world_of_one(K):
+    """mb200_moe_block_push with a communicator of one rank (the rows are pushed into this GPU's own receive
+    cells and collected from there): the same bits as mb200_moe_block, eagerly, twice in a row (the two
+    buffer halves) and replayed from a CUDA graph; the aliasing a decode layer uses (out = x = residual) works;
+    shapes the one-launch form does not cover are refused with nothing launched."""
+    from mnemocuda_b200.moe import MoEShape, ResidentMoE
+    from mnemocuda_b200.peer import PeerComm
+    s = MoEShape(n_experts=32)
+    moe = ResidentMoE(s, 1, "cuda", seed=9)
+    comm = PeerComm(0, 1, 8192)
+    try:
+        x, res = dev(synth.normal_f32(61, s.H)), dev(synth.normal_f32(62, s.H))
+        want = torch.empty(s.H, device="cuda")
+        moe.forward(0, x, res, want)
+        ids_want = moe.ids[0].clone()
+        call = lambda xx, rr, oo: K.mb200_moe_block_push(moe.router[0], moe.experts[0], s.stride, s.gate_sz, s.up_sz,
+                                                        s.down_type, s.NE, 0, s.NE, s.K, s.H, s.EFF, xx, None, 0.0, rr, oo,
+                                                        moe.ids[0], moe.wts[0], moe.act, moe.scratch, comm._comm)
+        for _ in range(3):
+            got = torch.full((s.H,), float("nan"), device="cuda")
+            assert call(x, res, got)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want)
+            assert torch.equal(moe.ids[0], ids_want)
+        h = x.clone()  # in place, as the hidden state of a decode layer
+        assert call(h, h, h)
+        torch.cuda.synchronize()
+        want2 = torch.empty(s.H, device="cuda")
+        moe.forward(0, x, x, want2)
+        torch.cuda.synchronize()
+        assert torch.equal(h, want2)
+        got = torch.empty(s.H, device="cuda")
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            call(x, res, got)
+        for _ in range(3):
+            got.zero_()
+            g.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(got, want)
+        # a shape outside the one-launch form (hidden 1024): refused, nothing launched
+        s2 = MoEShape(n_experts=8, top_k=2, hidden=1024, eff=256)
+        moe2 = ResidentMoE(s2, 1, "cuda", seed=10)
+        x2 = dev(synth.normal_f32(63, s2.H))
+        out2 = torch.full((s2.H,), 7.0, device="cuda")
+        assert not K.mb200_moe_block_push(moe2.router[0], moe2.experts[0], s2.stride, s2.gate_sz, s2.up_sz, s2.down_type,
+                                          s2.NE, 0, s2.NE, s2.K, s2.H, s2.EFF, x2, None, 0.0, x2, out2, moe2.ids[0],
+                                          moe2.wts[0], moe2.act, moe2.scratch, comm._comm)
+        torch.cuda.synchronize()
+        assert torch.all(out2 == 7.0)
+    finally:
+        comm.close()
+    assert K.mb200_device_error() == 0
