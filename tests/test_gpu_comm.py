@@ -98,3 +98,40 @@ def test_wait_for_a_rank_that_never_arrives_times_out(K):
     y = torch.empty(8, device="cuda")
     K.cuda_matvec_f32(torch.ones(8, 4, device="cuda"), torch.ones(4, device="cuda"), y, 8, 4)
     assert float(y.sum()) == 32.0
+
+
+def test_block_with_allreduce_inside_times_out_on_a_missing_rank(K):
+    """The in-kernel all-reduce of mb200_moe_block_push with a world of two of which only rank 0 ever launches: the
+    collecting warps give up after the bounded wait, the device error word reports it, nothing is written to `out`,
+    rank 0's rows did reach the other buffer, and the context stays usable."""
+    from mnemocuda_b200 import _lib
+    from mnemocuda_b200.moe import MoEShape, ResidentMoE
+    lib = _lib.lib()
+    s = MoEShape(n_experts=16)
+    moe = ResidentMoE(s, 1, "cuda", seed=12)
+    world, n = 2, s.H
+    nbytes = lib.mb200_comm_buffer_bytes(world, n)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    bases = (C.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    comm = C.c_void_p()
+    assert lib.mb200_comm_create_ptrs(0, world, n, bases, C.byref(comm)) == 0
+    x, res = dev(synth.normal_f32(19, s.H)), dev(synth.normal_f32(20, s.H))
+    want = torch.empty(s.H, device="cuda")
+    moe.forward(0, x, res, want)
+    out = torch.full((s.H,), 7.0, device="cuda")
+    assert K.mb200_device_error() == 0
+    assert K.mb200_moe_block_push(moe.router[0], moe.experts[0], s.stride, s.gate_sz, s.up_sz, s.down_type, s.NE, 0, s.NE,
+                                  s.K, s.H, s.EFF, x, None, 0.0, res, out, moe.ids[0], moe.wts[0], moe.act, moe.scratch,
+                                  comm.value)
+    assert K.mb200_device_error() == 3  # MB200_ERR_TIMEOUT, after about two seconds
+    assert float(out.min()) == 7.0 and float(out.max()) == 7.0  # nothing was written
+    cells = bufs[1][: 2 * world * n * 8].view(torch.int32).reshape(2, world, n, 2)[1, 0]
+    assert bool((cells[:, 1] == 1).all()) and torch.equal(cells[:, 0].view(torch.float32), want)
+    K.mb200_clear_device_error()
+    assert K.mb200_device_error() == 0
+    lib.mb200_comm_destroy(comm, 0)
+    moe.scratch.zero_()  # the block's barrier counters are to be zeroed after a timeout
+    got = torch.empty(s.H, device="cuda")
+    moe.forward(0, x, res, got)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
