@@ -75,7 +75,8 @@ def main():
     # the all-reduce inside the block's kernel (the default with a communicator) against block + push all-reduce:
     # the same bits, on every rank
     outs = []
-    for fused_push in (True, False):
+    for fused_push, pdl in ((True, False), (False, False), (True, True)):
+        K.mb200_set_pdl(pdl)
         sm = sharded.ShardedMoE(part, rank, world, comm=comm)
         sm.fused_push = fused_push
         out = torch.full((s.H,), float("nan"), device=dev)
@@ -83,7 +84,9 @@ def main():
             sm.forward(0, xh, rh, out)
         torch.cuda.synchronize()
         outs.append(out.clone())
+    K.mb200_set_pdl(False)
     assert torch.equal(outs[0], outs[1]), (rank, float((outs[0] - outs[1]).abs().max()))
+    assert torch.equal(outs[0], outs[2]), rank
     ref = outs[0].clone()
     dist.broadcast(ref, 0)
     assert torch.equal(outs[0], ref)
