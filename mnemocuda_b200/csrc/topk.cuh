@@ -376,25 +376,27 @@ __device__ __forceinline__ void topk_group_sync(int bar_id, int n_threads)
 // kBigShapes = false leaves out the one-warp general form for n_experts > 32 k or > 512 (a third of a megabyte of
 // code): for a caller that has checked the shape on the host.
 // The group is warps [warp0, warp0 + n_warps) of the CTA.
-template <bool kBigShapes = true>
+// KW: scores per lane the candidate listing is unrolled for (k <= KW). UNR: unrolling of the counting loops -- 8 where
+// the code stays resident (a kernel of its own that is launched back to back), 2 where it is fetched cold at every
+// launch and its size is what its first run costs (inside the one-launch MoE kernel).
+template <bool kBigShapes = true, int KW = 16, int UNR = 8>
 __device__ __forceinline__ void topk_softmax_group(const float *scores, int *indices, float *weights, int n_experts,
                                                    int k, TopkShared &sh, int n_warps, int bar_id, int warp0 = 0)
 {
     const unsigned full = 0xffffffffu;
     const int lane = threadIdx.x & 31, warp = static_cast<int>(threadIdx.x >> 5) - warp0;
-    if (n_experts > 32 * k || k > 16 || n_experts > 512) {  // block-uniform
+    if (n_experts > 32 * k || k > KW || n_experts > 512) {  // block-uniform
         if (kBigShapes && warp == 0) topk_softmax_warp(scores, indices, weights, n_experts, k, sh);
         return;
     }
     // ---- candidates in the reference's (lane, slot) order: lane l holds scores l, l + 32, ... ----
     if (warp == 0) {
-        float sv[16];
+        float sv[KW];
         int cnt = 0;
 #pragma unroll
-        for (int u = 0; u < 16; u++) {
-            sv[u] = (u < k && lane + 32 * u < n_experts) ? scores[lane + 32 * u] : -1e30f;
-            cnt += (sv[u] > -1e30f) ? 1 : 0;
-        }
+        for (int u = 0; u < KW; u++) sv[u] = (u < k && lane + 32 * u < n_experts) ? scores[lane + 32 * u] : -1e30f;
+#pragma unroll
+        for (int u = 0; u < KW; u++) cnt += (sv[u] > -1e30f) ? 1 : 0;
         int base = cnt;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -405,7 +407,7 @@ __device__ __forceinline__ void topk_softmax_group(const float *scores, int *ind
         base -= cnt;
         int w = 0;
 #pragma unroll
-        for (int u = 0; u < 16; u++)
+        for (int u = 0; u < KW; u++)
             if (sv[u] > -1e30f) {
                 sh.val[base + w] = sv[u];
                 sh.cid[base + w] = lane + 32 * u;
@@ -429,13 +431,13 @@ __device__ __forceinline__ void topk_softmax_group(const float *scores, int *ind
         const int p = row * 32 + lane;
         const float v = p < M ? sh.val[p] : __int_as_float(0x7FC00000);
         int c = 0;
-#pragma unroll 8
+#pragma unroll UNR
         for (int q = 0; q < row * 32; q += 4) {  // earlier rows: every q < p
             const float4 w = *reinterpret_cast<const float4 *>(&sh.val[q]);
             c += (w.x >= v) + (w.y >= v) + (w.z >= v) + (w.w >= v);
         }
         const int q_end = min(Mpad, (row + 1) * 32);
-#pragma unroll 8
+#pragma unroll UNR
         for (int q = row * 32; q < q_end; q += 4) {  // own row: q counts only if q < p
             const float4 w = *reinterpret_cast<const float4 *>(&sh.val[q]);
             c += (q + 0 < p && w.x >= v) + (q + 1 < p && w.y >= v) + (q + 2 < p && w.z >= v) + (q + 3 < p && w.w >= v);
