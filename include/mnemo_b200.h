@@ -232,9 +232,8 @@ int mb200_norm_matvec_qkv(const void *wq, float *q, int q_rows, const void *wk, 
  * An expert blob is [gate Q4_K EFF x H][up Q4_K EFF x H][down H x EFF], expert e at
  * experts + e * expert_stride (src/forward.c:1127-1136). */
 
-/* Bytes of scratch mb200_router_topk / mb200_moe_block need: a ticket counter, the logits, (16-byte aligned) 64 bytes
- * of barrier counters for mb200_moe_block, and the one-launch form's logit cells (2 x n_experts pairs of a value and the
- * number of the launch that wrote it). All of it zero before the first use. */
+/* Bytes of scratch mb200_router_topk / mb200_moe_block need: a ticket counter, the logits, and
+ * (16-byte aligned, at the end) 64 bytes of barrier counters for mb200_moe_block. */
 size_t mb200_router_scratch_bytes(int n_experts);
 
 /* logits = router_w x (fp32 [n_experts x n_cols], src/kernels.cu:859-880), then the

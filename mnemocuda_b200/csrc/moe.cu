@@ -30,7 +30,7 @@ int pdl_enabled();
 int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off, size_t down_off, int down_type,
               const int *ids, const float *wts, int n_slots, int expert_lo, int expert_cnt, const float *x, float *act,
               const float *residual, float *y, int H, int EFF, unsigned long long *sync, cudaStream_t stream,
-              const float *router_w, int n_experts, void *logit_cells, int *ids_out, float *wts_out, const float *norm_w,
+              const float *router_w, int n_experts, float *logits, int *ids_out, float *wts_out, const float *norm_w,
               float norm_eps, const PushDesc *push = nullptr);
 void launch_rms_norm(const float *in, const float *w, float *out, float *res_out, int n, float eps, cudaStream_t stream);
 void moe_fused_set_mode(int mode);
@@ -242,14 +242,12 @@ using namespace mb200;
 extern "C" {
 
 // ticket + padding (8 words), the logits, then (16-byte aligned) the 64 bytes of barrier counters that
-// mb200_moe_block hands to the fused expert kernel, then the one-launch form's logit cells: two halves (launch
-// parity) of n_experts {value, launch number} pairs
+// mb200_moe_block hands to the fused expert kernel
 static size_t router_part_bytes(int n_experts)
 {
     return (sizeof(int) * 8 + sizeof(float) * (size_t)(n_experts > 0 ? n_experts : 0) + 15) & ~static_cast<size_t>(15);
 }
-static size_t logit_cells_bytes(int n_experts) { return 2 * sizeof(uint2) * (size_t)(n_experts > 0 ? n_experts : 0); }
-size_t mb200_router_scratch_bytes(int n_experts) { return router_part_bytes(n_experts) + 64 + logit_cells_bytes(n_experts); }
+size_t mb200_router_scratch_bytes(int n_experts) { return router_part_bytes(n_experts) + 64; }
 
 int mb200_router_topk(const float *router_w, const float *x, void *scratch, int *indices, float *weights,
                       int n_experts, int n_cols, int k, cudaStream_t stream)
@@ -364,9 +362,9 @@ int mb200_moe_block_push(const float *router_w, const void *experts, size_t expe
     if (!comm_describe(comm, &d)) return MB200_ERR_ARG;
     unsigned long long *sync =
         reinterpret_cast<unsigned long long *>(static_cast<char *>(scratch) + router_part_bytes(n_experts));
-    void *cells = static_cast<char *>(scratch) + router_part_bytes(n_experts) + 64;
+    float *logits = reinterpret_cast<float *>(static_cast<int *>(scratch) + 8);
     return moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, nullptr, nullptr, k, expert_lo,
-                     expert_cnt, x, act, residual, out, H, EFF, sync, stream, router_w, n_experts, cells, ids, wts, norm_w,
+                     expert_cnt, x, act, residual, out, H, EFF, sync, stream, router_w, n_experts, logits, ids, wts, norm_w,
                      norm_eps, &d);
 }
 
@@ -381,15 +379,16 @@ int mb200_moe_block_norm(const float *router_w, const void *experts, size_t expe
         return MB200_ERR_ARG;
     if (norm_w && !normed_scratch) return MB200_ERR_ARG;
     if (reinterpret_cast<uintptr_t>(scratch) & 15) return MB200_ERR_ARG;
-    // behind the router's part of the scratch: 64 bytes of barrier counters of the fused kernel, then its logit cells
+    // the last 64 bytes of the scratch are the fused kernel's barrier counters
     unsigned long long *sync =
         reinterpret_cast<unsigned long long *>(static_cast<char *>(scratch) + router_part_bytes(n_experts));
+    float *logits = reinterpret_cast<float *>(static_cast<int *>(scratch) + 8);
     int rc;
     if (moe_fused_mode() == 2 && act) {
         // one launch: routing, gate/up, down
         rc = moe_fused(experts, expert_stride, 0, gate_sz, gate_sz + up_sz, down_type, nullptr, nullptr, k, expert_lo,
-                       expert_cnt, x, act, residual, out, H, EFF, sync, stream, router_w, n_experts,
-                       static_cast<char *>(scratch) + router_part_bytes(n_experts) + 64, ids, wts, norm_w, norm_eps);
+                       expert_cnt, x, act, residual, out, H, EFF, sync, stream, router_w, n_experts, logits, ids, wts,
+                       norm_w, norm_eps);
         // not covered, or the device refused the cooperative launch (fewer SMs available than the grid
         // needs): nothing ran, the separate kernels below do the block
         if (rc != MB200_ERR_UNSUPPORTED && rc != MB200_ERR_LAUNCH) return rc;

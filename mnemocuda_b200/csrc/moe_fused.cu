@@ -75,7 +75,7 @@ struct FusedParams {
     // routing inside the kernel (router_w != nullptr): logits = router_w x, then the reference's top-k + softmax;
     // the ids / weights are also written to ids_out / wts_out for the caller
     const float *router_w;
-    uint2 *logits;   // [2][n_experts] cells {logit, launch tag} in global memory (two halves by launch parity)
+    float *logits;   // [n_experts] scratch in global memory
     int *ids_out;
     float *wts_out;
     int n_experts;
@@ -399,13 +399,12 @@ __device__ __forceinline__ void push_collect(const FusedParams &P, unsigned long
 // Router logits (reference src/kernels.cu:859-880): expert row b, b + G, ... per CTA, by the twelve
 // consumer warps; then the CTA arrives at the routing barrier.
 __device__ __noinline__ void route_logits(const float *router_w, const float *x, const float *norm_w, float norm_eps,
-                                          uint2 *logits, unsigned long long *route_ctr, unsigned long long launch_no,
-                                          int H, int n_experts, float *rred)
+                                          float *logits, unsigned long long *route_ctr, int H, int n_experts, float *rred)
 {
     struct {
         const float *router_w, *x, *norm_w;
         float norm_eps;
-        uint2 *logits;
+        float *logits;
         int H, n_experts;
     } P = {router_w, x, norm_w, norm_eps, logits, H, n_experts};
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -453,14 +452,11 @@ __device__ __noinline__ void route_logits(const float *router_w, const float *x,
                 for (int w = 0; w < kConsumers; w++) t += rred[kConsumers + w];
                 v *= 1.0f / sqrtf(t / static_cast<float>(P.H) + P.norm_eps);
             }
-            // value and launch number in one 8-byte store: whoever reads the number has the value (no release, no
-            // separate flag); the halves alternate with the launch parity
-            st_cell(P.logits + (launch_no & 1) * P.n_experts + row, v, static_cast<uint32_t>(launch_no));
+            P.logits[row] = v;
         }
         asm volatile("bar.sync 3, %0;" ::"n"(kConsumers * 32) : "memory");
     }
-    // the counter only numbers the launches now (nobody waits on it): every CTA adds one per launch
-    if (tid == 0) asm volatile("red.relaxed.gpu.global.add.u64 [%0], 1;" ::"l"(route_ctr) : "memory");
+    if (tid == 0) barrier_arrive(route_ctr);  // release: this thread stored the CTA's logits
     if (warp == 0) MB200_STAMP(3);
 }
 
@@ -471,6 +467,7 @@ __device__ __noinline__ void route_logits(const float *router_w, const float *x,
 __device__ __noinline__ void route_topk(const float *scores, int *ids, float *wts, int n_experts, int k, TopkShared *sh,
                                         int n_warps, int bar_id, int warp0)
 {
+    // the small forms of the selection (see topk_softmax_group): this code is fetched cold at every launch
     if (k <= 8)  // (the shapes are checked on the host: n_experts <= 32 k, k <= 16)
         topk_softmax_group<false, 8, 2>(scores, ids, wts, n_experts, k, *sh, n_warps, bar_id, warp0);
     else
@@ -503,46 +500,35 @@ __device__ __forceinline__ void route_warmup(const FusedParams &P, uint8_t *ring
     }
 }
 
-__device__ __noinline__ bool route_select(const uint2 *logits, int n_experts, int n_slots, int *ids_out, float *wts_out,
-                                          unsigned long long launch_no, int *rid, float *rwt, uint8_t *ring)
+__device__ __noinline__ bool route_select(const unsigned long long *route_ctr, const float *logits, int n_experts,
+                                          int n_slots, int *ids_out, float *wts_out, unsigned long long tgt_route,
+                                          int *rid, float *rwt, uint8_t *ring)
 {
     struct {
+        const float *logits;
         int n_experts, n_slots;
         int *ids_out;
         float *wts_out;
-    } P = {n_experts, n_slots, ids_out, wts_out};
+    } P = {logits, n_experts, n_slots, ids_out, wts_out};
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // 128 threads collect the logits as the CTAs that computed them store them: thread i polls the cells of experts
-    // i, i + 128, ... of this launch's half until they carry this launch's number (bounded), and leaves the values
-    // in shared memory for the selection. Thread 0 knows the number (it read the counter at entry).
-    unsigned long long *tag_word = reinterpret_cast<unsigned long long *>(ring + 14 * 1024);
-    float *s_logit = reinterpret_cast<float *>(ring + 12 * 1024);  // [<= 512], behind the selection's tables
-    volatile int *failed = reinterpret_cast<volatile int *>(ring + 14 * 1024 + 8);
+    bool ok = true;
     if (tid == 0) {
-        *tag_word = launch_no;
-        *failed = 0;
-    }
-    topk_group_sync(2, 128);
-    const unsigned long long no = *tag_word;
-    const uint2 *cells = logits + (no & 1) * P.n_experts;
-    for (int e = tid; e < P.n_experts; e += 128) {
-        bool got = false;
+        ok = false;
         for (uint32_t i = 0; i < (1u << 19); i++) {
-            const uint2 c = ld_cell(cells + e);
-            if (c.y == static_cast<uint32_t>(no)) {
-                s_logit[e] = __uint_as_float(c.x);
-                got = true;
+            unsigned long long c;
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(route_ctr) : "memory");
+            if (c >= tgt_route) {
+                ok = true;
                 break;
             }
-            __nanosleep(20);
+            __nanosleep(40);
         }
-        if (!got) *failed = 1;
     }
     topk_group_sync(2, 128);
     if (warp == 0) MB200_STAMP(4);
     TopkShared &tsh = *reinterpret_cast<TopkShared *>(ring);  // the ring is idle until the first tile is requested
-    const bool ok = *failed == 0;
-    route_topk(s_logit, rid, rwt, P.n_experts, P.n_slots, &tsh, 4, 2, 0);
+    route_topk(P.logits, rid, rwt, P.n_experts, P.n_slots, &tsh,
+               4, 2, 0);
     if (warp == 0) {
         MB200_STAMP(6);
         __syncwarp();
@@ -866,8 +852,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     if (P.router_w && tid == 0) tgt_route = barrier_target(P.sync + kFusedMaxBatches);  // before this CTA arrives
     if (P.pdl) stream::grid_dep_wait();  // x is produced upstream; act / y may still be in use there
     if (P.router_w)
-        route_logits(P.router_w, P.x, P.norm_w, P.norm_eps, P.logits, P.sync + kFusedMaxBatches, tgt_route / gridDim.x, P.H,
-                     P.n_experts, rred);
+        route_logits(P.router_w, P.x, P.norm_w, P.norm_eps, P.logits, P.sync + kFusedMaxBatches, P.H, P.n_experts, rred);
     const Layout LB = stream::layout<Q4>(P.bprB, 0, 0, 1, 1);
     const Layout LC = stream::layout<FD>(P.bprC, 0, 0, 1, 1);
     {
@@ -878,8 +863,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     }
     if (warp == 0) MB200_STAMP(1);
     bool routed_ok = true;
-    if (P.router_w && warp < 4) routed_ok = route_select(P.logits, P.n_experts, P.n_slots, P.ids_out, P.wts_out, tgt_route / gridDim.x,
-                                                              rid, rwt, stages);
+    if (P.router_w && warp < 4) routed_ok = route_select(P.sync + kFusedMaxBatches, P.logits, P.n_experts, P.n_slots, P.ids_out, P.wts_out,
+                                                              tgt_route, rid, rwt, stages);
     __syncthreads();  // x is staged, barriers are initialised, the served slots are known (or the routing is done)
     if (P.router_w) {
         if (tid == 0 && !routed_ok) {
@@ -1196,7 +1181,7 @@ int moe_fused_mode() { return g_fused_mode; }
 int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off, size_t down_off, int down_type,
               const int *ids, const float *wts, int n_slots, int expert_lo, int expert_cnt, const float *x, float *act,
               const float *residual, float *y, int H, int EFF, unsigned long long *sync, cudaStream_t stream,
-              const float *router_w, int n_experts, void *logit_cells, int *ids_out, float *wts_out, const float *norm_w,
+              const float *router_w, int n_experts, float *logits, int *ids_out, float *wts_out, const float *norm_w,
               float norm_eps, const PushDesc *push)
 {
     FusedParams P{};
@@ -1210,12 +1195,12 @@ int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off
     P.norm_eps = norm_eps;
     if (router_w) {
         // the group top-k covers n_experts <= 32 * k and <= 512; 16-byte loads of the router rows
-        if (n_experts < 1 || n_experts > 512 || n_experts > 32 * n_slots || n_slots > 16 || !logit_cells || !ids_out || !wts_out)
+        if (n_experts < 1 || n_experts > 512 || n_experts > 32 * n_slots || n_slots > 16 || !logits || !ids_out || !wts_out)
             return MB200_ERR_UNSUPPORTED;
         if ((reinterpret_cast<uintptr_t>(router_w) & 15) || (H & 3)) return MB200_ERR_UNSUPPORTED;
         P.router_w = router_w;
         P.n_experts = n_experts;
-        P.logits = static_cast<uint2 *>(logit_cells);
+        P.logits = logits;
         P.ids_out = ids_out;
         P.wts_out = wts_out;
     }
