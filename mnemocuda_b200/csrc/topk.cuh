@@ -161,6 +161,8 @@ struct __align__(16) TopkShared {
 
 // Second half of the parallel form, one warp: `m` accepted candidates (values sh.aval, ids sh.aid, in
 // arrival order) -> ranks, tie check, slot chains, softmax. Returns false on a tie among the accepted.
+// kSmall: loops kept rolled (for code that is fetched cold at every launch).
+template <bool kSmall = false>
 __device__ __forceinline__ bool topk_finish_warp(int m, int *indices, float *weights, int k, TopkShared &sh)
 {
     const unsigned full = 0xffffffffu;
@@ -176,6 +178,7 @@ __device__ __forceinline__ bool topk_finish_warp(int m, int *indices, float *wei
         const int t = t0 + lane;
         const float av = t < m ? sh.aval[t] : __int_as_float(0x7FC00000);
         int r = 0, eq = 0;
+#pragma unroll(kSmall ? 1 : 4)
         for (int u = 0; u < mpad; u += 4) {
             const float4 w = *reinterpret_cast<const float4 *>(&sh.aval[u]);
             r += (w.x < av) + (w.y < av) + (w.z < av) + (w.w < av);
@@ -211,6 +214,7 @@ __device__ __forceinline__ bool topk_finish_warp(int m, int *indices, float *wei
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(full, mx, o));
         const float e = lane < k ? expf(v - mx) : 0.0f;
         float sum = 0.0f;
+#pragma unroll(kSmall ? 1 : 4)
         for (int i = 0; i < k; i++) sum += __shfl_sync(full, e, i);
         if (lane < k) {
             weights[lane] = e / sum;
@@ -449,6 +453,7 @@ __device__ __forceinline__ void topk_softmax_group(const float *scores, int *ind
     MB200_TOPK_STAMP(1);
     // ---- arrival order: compact the accepted ----
     int m = 0;
+#pragma unroll(UNR < 8 ? 1 : 4)
     for (int row = 0; row < n_rows; row++) {
         const unsigned bal = sh.bal[row];
         if ((row % n_warps) == warp && (bal & (1u << lane))) {
@@ -462,7 +467,7 @@ __device__ __forceinline__ void topk_softmax_group(const float *scores, int *ind
     topk_group_sync(bar_id, n_warps * 32);
     MB200_TOPK_STAMP(2);
     if (warp != 0) return;
-    if (topk_finish_warp(m, indices, weights, k, sh)) return;
+    if (topk_finish_warp<(UNR < 8)>(m, indices, weights, k, sh)) return;
     __syncwarp();
     // equal accepted values: the serial walk decides
     if (k <= 8)
