@@ -154,8 +154,8 @@ struct FWalk {
         bi = 0;
         act_list = slots;
         n_act = n_active;
-        c_cur = static_cast<int>((long long)P.H * blockIdx.x / gridDim.x);
-        c_end = static_cast<int>((long long)P.H * (blockIdx.x + 1) / gridDim.x);
+        c_cur = static_cast<int>(static_cast<unsigned>(P.H) * blockIdx.x / gridDim.x);
+        c_end = static_cast<int>(static_cast<unsigned>(P.H) * (blockIdx.x + 1) / gridDim.x);
         if (n_active == 0) c_end = c_cur;
         e = 0;
     }
@@ -356,8 +356,8 @@ __device__ __forceinline__ void push_collect(const FusedParams &P, unsigned long
 {
     const uint32_t tag = static_cast<uint32_t>(seq);
     const size_t par_off = (size_t)(seq & 1) * P.push.world * P.push.max_floats;
-    const int r0 = static_cast<int>((long long)P.H * blockIdx.x / gridDim.x);
-    const int r1 = static_cast<int>((long long)P.H * (blockIdx.x + 1) / gridDim.x);
+    const int r0 = static_cast<int>(static_cast<unsigned>(P.H) * blockIdx.x / gridDim.x);
+    const int r1 = static_cast<int>(static_cast<unsigned>(P.H) * (blockIdx.x + 1) / gridDim.x);
     if (zero_mine)
         for (int row = r0 + lane; row < r1; row += 32) {
             const float mine = P.residual ? __ldcg(P.residual + row) : 0.0f;
@@ -880,8 +880,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         if (PUSH) {
             // (the courier warp sends and collects this CTA's rows, once every CTA has read x: out may be x)
         } else if (warp == 0 && P.residual) {
-            const int r0 = static_cast<int>((long long)P.H * blockIdx.x / gridDim.x);
-            const int r1 = static_cast<int>((long long)P.H * (blockIdx.x + 1) / gridDim.x);
+            const int r0 = static_cast<int>(static_cast<unsigned>(P.H) * blockIdx.x / gridDim.x);
+            const int r1 = static_cast<int>(static_cast<unsigned>(P.H) * (blockIdx.x + 1) / gridDim.x);
             for (int r = r0 + lane; r < r1; r += 32) P.y[r] = __ldcg(P.residual + r);
         }
         return;
@@ -1098,6 +1098,7 @@ static bool fused_plan(FusedParams &P, int &smem_bytes)
 {
     const int H = P.H, EFF = P.EFF;
     if (H % 256 || EFF % 256 || P.n_slots < 1 || P.n_slots > kFusedMaxSlots) return false;
+    if (static_cast<unsigned long long>(H) * (P.grid + 1) >= (1ull << 32)) return false;  // row ranges in 32-bit arithmetic
     P.bprB = H / 256;
     P.bprC = EFF / 256;
     if (P.bprB % 8) return false;
