@@ -96,6 +96,7 @@ struct FusedParams {
     int off_cpart;                 // partial-sum slots of the down stages
     int pdl;
     int grid;                      // CTAs of the launch = SMs of the device (one CTA per SM, all co-resident)
+    double inv_grid;               // 1 / grid
     // RMSNorm of x folded in (x' = x * norm_w / sqrt(mean(x^2) + norm_eps)): the router and the gate/up products use x'
     const float *norm_w;
     float norm_eps;
@@ -120,11 +121,22 @@ struct FTile {
 // launch adds exactly gridDim.x arrivals to a counter it uses, so between launches its value is a
 // multiple of gridDim.x; a CTA that reads c at its start (when at most gridDim.x - 1 arrivals of its
 // own launch can be in) knows the launch is complete at c - c % gridDim.x + gridDim.x.
-__device__ __forceinline__ unsigned long long barrier_target(const unsigned long long *ctr)
+// (The remainder comes from a multiplication by 1 / gridDim.x in double precision with a correction step, exact for
+// counters below 2^52: a 64-bit division is a subroutine of a hundred instructions that every CTA would fetch cold
+// at its very start, with all its other warps waiting for the result.)
+__device__ __forceinline__ unsigned long long barrier_target(const unsigned long long *ctr, double inv_grid)
 {
     unsigned long long c;
     asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(c) : "l"(ctr) : "memory");
-    return c - c % gridDim.x + gridDim.x;
+    const unsigned long long G = gridDim.x;
+    unsigned long long q = static_cast<unsigned long long>(__ull2double_rz(c) * inv_grid);  // inv_grid = 1 / gridDim.x
+    long long r = static_cast<long long>(c - q * G);
+    if (r < 0) {
+        q--;
+        r += static_cast<long long>(G);
+    }
+    if (r >= static_cast<long long>(G)) q++;
+    return (q + 1) * G;
 }
 // Release-arrive: every store this thread has made or observed (through the block-scope handshakes
 // between the warps that finished the CTA's tiles) is visible to whoever acquires the counter.
@@ -708,7 +720,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         // once every CTA has arrived it pulls the batch's fp32 activation vectors into shared memory.
         unsigned long long tgt[kFusedMaxBatches];
 #pragma unroll
-        for (int b = 0; b < kFusedMaxBatches; b++) tgt[b] = barrier_target(P.sync + b);  // before this CTA can have arrived
+        for (int b = 0; b < kFusedMaxBatches; b++) tgt[b] = barrier_target(P.sync + b, P.inv_grid);  // before this CTA can have arrived
         __syncthreads();
         if (P.router_w) __syncthreads();
         if (PUSH && *n_act_p == 0 && !*abort_flag) {
@@ -849,7 +861,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
 
     // ---------------- consumer warps ----------------
     unsigned long long tgt_route = 0;
-    if (P.router_w && tid == 0) tgt_route = barrier_target(P.sync + kFusedMaxBatches);  // before this CTA arrives
+    if (P.router_w && tid == 0) tgt_route = barrier_target(P.sync + kFusedMaxBatches, P.inv_grid);  // before this CTA arrives
     if (P.pdl) stream::grid_dep_wait();  // x is produced upstream; act / y may still be in use there
     if (P.router_w)
         route_logits(P.router_w, P.x, P.norm_w, P.norm_eps, P.logits, P.sync + kFusedMaxBatches, P.H, P.n_experts, rred);
@@ -1224,6 +1236,7 @@ int moe_fused(const void *experts, size_t stride, size_t gate_off, size_t up_off
     P.H = H;
     P.EFF = EFF;
     P.grid = device_sms();
+    P.inv_grid = 1.0 / static_cast<double>(P.grid);
     int smem_bytes = 0;
     if (!fused_plan(P, smem_bytes)) return MB200_ERR_UNSUPPORTED;
     const uintptr_t b = reinterpret_cast<uintptr_t>(experts);
