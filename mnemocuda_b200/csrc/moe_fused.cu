@@ -88,6 +88,7 @@ struct FusedParams {
     int n_slots, expert_lo, expert_cnt;
     int H, EFF, bprB, bprC;
     int ngB, wpgB, TB;             // gate/up: column groups, warps per group, pair rows per tile (= 2 * wpgB)
+    int tpe;                       // gate/up tiles per expert = ceil(EFF / TB)
     int ngC, wpgC, vC, rppC, TC;   // down: column groups, warps per group, blocks per row group, rows per pass, rows per tile
     int stages, stage_bytes;
     int off_xb, off_xc, xc_stride, off_part, part_pitch, off_stages;  // shared-memory offsets (bytes; part_pitch in floats)
@@ -206,11 +207,12 @@ struct FWalk {
 // One warp: reads the routed ids and weights (one round trip), compacts the slots served here, and
 // lists this CTA's gate/up tiles. Returns the number of served slots.
 // (Arguments by value: see split_share.)
-__device__ __noinline__ int build_tiles(int n_slots, int expert_lo, int expert_cnt, int EFF, int TB, const int *ids,
+__device__ __noinline__ int build_tiles(int n_slots, int expert_lo, int expert_cnt, int EFF, int TB, int tpe, const int *ids,
                                         const float *wts, int lane, int *sid, float *swt, int *act_list, int2 *tiles,
                                         int *n_tiles_p)
 {
     struct { int n_slots, expert_lo, expert_cnt, EFF, TB; } P = {n_slots, expert_lo, expert_cnt, EFF, TB};
+    // tpe = ceil(EFF / TB), computed on the host
     int id = -1;
     float w = 0.0f;
     if (lane < P.n_slots) {
@@ -231,7 +233,6 @@ __device__ __noinline__ int build_tiles(int n_slots, int expert_lo, int expert_c
     // Tiles are numbered through the served slots in order (tpe per slot) and dealt to the CTAs round
     // robin: CTA b takes tiles b, b + G, b + 2G, ... -- in batch order, an equal share of every batch
     // (to within one tile), and lane i lists the i-th of them.
-    const int tpe = (P.EFF + P.TB - 1) / P.TB;
     const int T = n * tpe, G = gridDim.x;
     const int g = blockIdx.x + lane * G;
     const int total = (T > static_cast<int>(blockIdx.x)) ? (T - static_cast<int>(blockIdx.x) + G - 1) / G : 0;
@@ -507,7 +508,7 @@ __device__ __forceinline__ void route_warmup(const FusedParams &P, uint8_t *ring
     if (warp == 0) {  // the issuer's tile list from the made-up selection: same idea, its code is run-once too
         __syncwarp();
         int *scratch = reinterpret_cast<int *>(base + 3072);
-        build_tiles(P.n_slots, P.expert_lo, P.expert_cnt, P.EFF, P.TB, ids, wts, lane, scratch,
+        build_tiles(P.n_slots, P.expert_lo, P.expert_cnt, P.EFF, P.TB, P.tpe, ids, wts, lane, scratch,
                     reinterpret_cast<float *>(scratch + 16), scratch + 32, reinterpret_cast<int2 *>(scratch + 64), scratch + 48);
     }
 }
@@ -656,12 +657,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         int n = 0;
         if (!P.router_w) {
             if (P.pdl) stream::grid_dep_wait();  // the routed ids come from the upstream kernel
-            n = build_tiles(P.n_slots, P.expert_lo, P.expert_cnt, P.EFF, P.TB, P.ids, P.wts, lane, sid, swt, act_list, tiles, n_tiles_p);
+            n = build_tiles(P.n_slots, P.expert_lo, P.expert_cnt, P.EFF, P.TB, P.tpe, P.ids, P.wts, lane, sid, swt, act_list, tiles, n_tiles_p);
             if (lane == 0) *n_act_p = n;
         }
         __syncthreads();
         if (P.router_w) {  // the consumer warps have routed: ids and weights are in shared memory
-            n = build_tiles(P.n_slots, P.expert_lo, P.expert_cnt, P.EFF, P.TB, rid, rwt, lane, sid, swt, act_list, tiles, n_tiles_p);
+            n = build_tiles(P.n_slots, P.expert_lo, P.expert_cnt, P.EFF, P.TB, P.tpe, rid, rwt, lane, sid, swt, act_list, tiles, n_tiles_p);
             if (lane == 0) *n_act_p = n;
             __syncthreads();
         }
@@ -678,16 +679,22 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
             // it overlaps have been read for the last time.
             FTile t;
             int ib = 0, ic = 0;
+            int ist = 0, iuse = 0, ics = 0, icuse = 0;  // stage and number of earlier uses of it, both rings
             bool ok = true;
             MB200_STAMP(47);  // tile list ready, first copy about to be requested
             while (ok && walk.next(P, t)) {
                 if (t.phase == 0) {
-                    const int st = ib % S;
-                    if (ib >= S) ok = mbar_wait(&empty[st], ((ib / S) - 1) & 1);
+                    // (stage and use counters are kept by increments: a division by a run-time S is a subroutine)
+                    const int st = ist;
+                    if (ib >= S) ok = mbar_wait(&empty[st], (iuse - 1) & 1);
                     if (ok && !*abort_flag) issue<FD>(P, t, stages + (size_t)st * P.stage_bytes, &full[st], sid);
                     ib++;
+                    if (++ist == S) {
+                        ist = 0;
+                        iuse++;
+                    }
                 } else {
-                    const int c = ic % CS;
+                    const int c = ics;
                     if (ic < CS) {
                         const int lo = (c * P.c_stage_bytes) / P.stage_bytes;
                         const int hi = ((c + 1) * P.c_stage_bytes - 1) / P.stage_bytes;
@@ -696,11 +703,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
                             if (uses > 0) ok = mbar_wait(&empty[s2], (uses - 1) & 1);
                         }
                     } else {
-                        ok = mbar_wait(&cempty[c], ((ic / CS) - 1) & 1);
+                        ok = mbar_wait(&cempty[c], (icuse - 1) & 1);
                     }
                     if (ok && !*abort_flag) issue<FD>(P, t, stages + (size_t)c * P.c_stage_bytes, &cfull[c], sid);
                     if (ic < 4) MB200_STAMP(40 + ic);  // issue time of the first down tiles
                     ic++;
+                    if (++ics == CS) {
+                        ics = 0;
+                        icuse++;
+                    }
                 }
                 if (*abort_flag) break;
             }
@@ -830,10 +841,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
         walk.init(P, tiles, *n_tiles_p, act_list, n_act);
         FTile t;
         int ib = 0, ic = 0;
+        int est = 0, euse = 0, ecs = 0, ecuse = 0;  // stage and number of earlier uses of it, both rings
         while (walk.next(P, t)) {
             if (t.phase == 0) {
-                const int st = ib % S;
-                if (!mbar_wait(&empty[st], (ib / S) & 1)) *abort_flag = 1;
+                const int st = est;
+                if (!mbar_wait(&empty[st], euse & 1)) *abort_flag = 1;
                 if (*abort_flag) break;
                 finish_gate_up(P, t, part + st * P.part_pitch, outbox, lane);
                 __syncwarp();
@@ -843,15 +855,23 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
                     if (t.last) mbar_arrive(&bdone[t.batch]);
                 }
                 ib++;
+                if (++est == S) {
+                    est = 0;
+                    euse++;
+                }
             } else {
-                const int c = ic % CS;
-                if (!mbar_wait(&cempty[c], (ic / CS) & 1)) *abort_flag = 1;
+                const int c = ecs;
+                if (!mbar_wait(&cempty[c], ecuse & 1)) *abort_flag = 1;
                 if (*abort_flag) break;
                 if (ic < 8) MB200_STAMP(16 + ic);  // all consumers done with down tile ic
                 finish_down<PUSH>(P, t, cpart + c * P.part_pitch, run, swt[t.slot], n_act, lane, static_cast<uint32_t>(pseq), push_off);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&cfull[c]);
                 ic++;
+                if (++ecs == CS) {
+                    ecs = 0;
+                    ecuse++;
+                }
             }
         }
         if (*abort_flag && lane == 0) atomicExch(P.err, MB200_ERR_TIMEOUT);
@@ -1118,8 +1138,9 @@ static bool fused_plan(FusedParams &P, int &smem_bytes)
     if (P.ngB > kConsumers || kConsumers % P.ngB) return false;
     P.wpgB = kConsumers / P.ngB;
     P.TB = 2 * P.wpgB;
+    P.tpe = (EFF + P.TB - 1) / P.TB;
     {   // the issuer warp lists the CTA's gate/up tiles with one lane per tile
-        const int tpe = (EFF + P.TB - 1) / P.TB;
+        const int tpe = P.tpe;
         if ((P.n_slots * tpe + P.grid - 1) / P.grid + kFusedMaxBatches > kFusedMaxTiles) return false;
     }
     int v = 1;
