@@ -73,6 +73,7 @@ struct Params {
     int n_cols, bpr, mode, stages;
     int pdl;        // launched with programmatic stream serialization: wait for the upstream grid before touching x / y
     int cta0, ncta; // this problem's CTAs are blockIdx.x in [cta0, cta0 + ncta) (two problems may share one launch)
+    int per_cta, rem_cta;  // vrows / ncta and vrows % ncta: CTA c takes per_cta rows, the first rem_cta CTAs one more
     int ru;         // row unroll chosen by the host (read by the pair kernel, which holds all three bodies)
     int *err;
     // routed-expert modes
@@ -135,6 +136,20 @@ struct Tile {
     int j;                // routed modes: position of the slot in the active list
 };
 
+// Rows [cur, end) of CTA `cta` out of P.ncta. Quotient and remainder come from the host (a division, let alone a
+// 64-bit one, is a subroutine that every role of every CTA would fetch cold at the start of every launch); only the
+// routed gate/up mode, whose row count depends on the slots served here, divides on the device (32-bit).
+__device__ __forceinline__ void cta_rows(const Params &P, int vrows, int cta, int &cur, int &end)
+{
+    int per = P.per_cta, rem = P.rem_cta;
+    if (vrows != P.vrows) {
+        per = vrows / P.ncta;
+        rem = vrows - per * P.ncta;
+    }
+    cur = cta * per + min(cta, rem);
+    end = cur + per + (cta < rem ? 1 : 0);
+}
+
 // Walks the tiles of this CTA's row range [cur, end). Every role runs the same walk.
 // t.seg is the segment (plain modes) or the expert slot (routed modes).
 struct TileWalk {
@@ -146,8 +161,7 @@ struct TileWalk {
         n_act = n_active;
         const int vrows = (P.mode == kMoeGateUp) ? n_active * P.erows : P.vrows;
         const int cta = static_cast<int>(blockIdx.x) - P.cta0;
-        cur = static_cast<int>((long long)vrows * cta / P.ncta);
-        end = static_cast<int>((long long)vrows * (cta + 1) / P.ncta);
+        cta_rows(P, vrows, cta, cur, end);
         if (P.mode == kMoeDown && n_active == 0) end = cur;
         e = 0;
     }
@@ -530,8 +544,8 @@ __device__ __forceinline__ void stream_body(const Params &P, uint8_t *smem)
         if (P.mode == kMoeDown && walk.n_act == 0 && P.residual) {
             // no routed expert lives on this device: the block reduces to the residual
             const int cta = static_cast<int>(blockIdx.x) - P.cta0;
-            const int r0 = static_cast<int>((long long)P.vrows * cta / P.ncta);
-            const int r1 = static_cast<int>((long long)P.vrows * (cta + 1) / P.ncta);
+            int r0, r1;
+            cta_rows(P, P.vrows, cta, r0, r1);
             for (int r = r0 + lane; r < r1; r += 32) P.seg[0].y[r] = __ldcg(P.residual + r);
         }
         Tile t, ahead;
@@ -925,6 +939,8 @@ inline bool prepare(Params &P, const char *where, int grid_cap, int force_ru, La
     P.err = device_error_word();
     P.cta0 = 0;
     P.ncta = grid;
+    P.per_cta = P.vrows / grid;
+    P.rem_cta = P.vrows % grid;
     P.ru = ru;
     L_out = L;
     grid_out = grid;
