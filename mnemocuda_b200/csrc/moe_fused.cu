@@ -11,15 +11,15 @@
 // for the barrier, so the down-projection weights stream in while the last
 // gate/up tiles are consumed and while the CTAs meet.
 //
-// Roles per CTA (448 threads): warps 0-11 consume tiles (int8 dp4a dot
+// Roles per CTA (480 threads): warps 0-11 consume tiles (int8 dp4a dot
 // products, see q4k_policy.cuh / q6k_policy.cuh) and leave per-column-group
-// partial sums in shared memory; the warp that stores the last partial sum of
-// a tile finishes it (SwiGLU and the act store, or the running weighted sum
-// over the expert slots in slot order -- deterministic, no atomics). Warp 12
-// issues the weight copies. Warp 13 (the courier) does every slow device-wide
-// step so that no consumer warp waits on global memory: barrier arrivals, the
-// polls, and the bulk copies that bring finished activation vectors into
-// shared memory.
+// partial sums in shared memory. Warp 12 issues the weight copies. Warp 13 (the
+// courier) does every slow device-wide step so that no consumer warp waits on
+// global memory: barrier arrivals, the polls, and the bulk copies that bring
+// finished activation vectors into shared memory. Warp 14 (the epilogue warp)
+// finishes every tile once all consumers have stored their partial sums (SwiGLU
+// and the act rows, or the running weighted sum over the expert slots in slot
+// order -- deterministic, no atomics).
 //
 // The routed slots are handled in batches of two. Gate/up tiles are dealt to
 // the CTAs in batch order, and each batch has its own device-wide barrier: an
@@ -30,6 +30,12 @@
 // being streamed; only the last batch can make the down phase wait. The launch
 // is cooperative (all CTAs co-resident) and every wait gives up after a bounded
 // number of polls, setting the library's device error word instead of hanging.
+//
+// With the routing inside (mb200_moe_block) every CTA first computes a router
+// row and all of them select the experts themselves; with a communicator
+// (mb200_moe_block_push, the PUSH instantiation) the epilogue warp sends the
+// finished rows to the other ranks and collects theirs: the block's all-reduce
+// without a second kernel.
 #include <cstdio>
 
 #include "comm.cuh"
