@@ -417,6 +417,8 @@ __device__ __forceinline__ void push_collect(const FusedParams &P, unsigned long
 
 // Router logits (reference src/kernels.cu:859-880): expert row b, b + G, ... per CTA, by the twelve
 // consumer warps; then the CTA arrives at the routing barrier.
+// NORM: the RMSNorm of x is folded in (a version of its own: the loop body is half the size without it).
+template <bool NORM>
 __device__ __noinline__ void route_logits(const float *router_w, const float *x, const float *norm_w, float norm_eps,
                                           float *logits, unsigned long long *route_ctr, int H, int n_experts, float *rred)
 {
@@ -429,7 +431,7 @@ __device__ __noinline__ void route_logits(const float *router_w, const float *x,
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n4 = P.H >> 2;
     const float4 *x4 = reinterpret_cast<const float4 *>(P.x);
-    const float4 *n4w = reinterpret_cast<const float4 *>(P.norm_w);  // fused RMSNorm: logit = scale * sum Wr (x w)
+    const float4 *n4w = NORM ? reinterpret_cast<const float4 *>(P.norm_w) : nullptr;  // fused RMSNorm: logit = scale * sum Wr (x w)
     for (int row = blockIdx.x; row < P.n_experts; row += gridDim.x) {
         const float4 *w4 = reinterpret_cast<const float4 *>(P.router_w + (size_t)row * P.H);
         float acc = 0.0f, ss = 0.0f;
@@ -445,7 +447,7 @@ __device__ __noinline__ void route_logits(const float *router_w, const float *x,
                 const int i = i0 + u * kConsumers * 32;
                 if (i < n4) {
                     float4 b = __ldcg(x4 + i);
-                    if (n4w) {
+                    if (NORM) {
                         const float4 g = __ldg(n4w + i);
                         ss = fmaf(b.x, b.x, fmaf(b.y, b.y, fmaf(b.z, b.z, fmaf(b.w, b.w, ss))));
                         b.x *= g.x; b.y *= g.y; b.z *= g.z; b.w *= g.w;
@@ -458,7 +460,7 @@ __device__ __noinline__ void route_logits(const float *router_w, const float *x,
             }
         }
         acc = warp_sum(acc);
-        if (n4w) ss = warp_sum(ss);
+        if (NORM) ss = warp_sum(ss);
         if (lane == 0) {
             rred[warp] = acc;
             rred[kConsumers + warp] = ss;
@@ -467,7 +469,7 @@ __device__ __noinline__ void route_logits(const float *router_w, const float *x,
         if (tid == 0) {
             float v = 0.0f, t = 0.0f;
             for (int w = 0; w < kConsumers; w++) v += rred[w];  // fixed order
-            if (n4w) {
+            if (NORM) {
                 for (int w = 0; w < kConsumers; w++) t += rred[kConsumers + w];
                 v *= 1.0f / sqrtf(t / static_cast<float>(P.H) + P.norm_eps);
             }
@@ -889,8 +891,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) moe_fused_kernel(const __gri
     unsigned long long tgt_route = 0;
     if (P.router_w && tid == 0) tgt_route = barrier_target(P.sync + kFusedMaxBatches, P.inv_grid);  // before this CTA arrives
     if (P.pdl) stream::grid_dep_wait();  // x is produced upstream; act / y may still be in use there
-    if (P.router_w)
-        route_logits(P.router_w, P.x, P.norm_w, P.norm_eps, P.logits, P.sync + kFusedMaxBatches, P.H, P.n_experts, rred);
+    if (P.router_w) {
+        if (P.norm_w)
+            route_logits<true>(P.router_w, P.x, P.norm_w, P.norm_eps, P.logits, P.sync + kFusedMaxBatches, P.H, P.n_experts, rred);
+        else
+            route_logits<false>(P.router_w, P.x, P.norm_w, P.norm_eps, P.logits, P.sync + kFusedMaxBatches, P.H, P.n_experts, rred);
+    }
     const Layout LB = stream::layout<Q4>(P.bprB, 0, 0, 1, 1);
     const Layout LC = stream::layout<FD>(P.bprC, 0, 0, 1, 1);
     {
