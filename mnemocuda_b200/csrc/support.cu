@@ -478,19 +478,55 @@ attn_decode_kernel(const float *__restrict__ q, const __half *__restrict__ kv_k,
     if (!is_last) return;
     __threadfence();
     // ---- last CTA of this KV head: merge the chunks ----
+    // The sixteen threads of a head (half a warp) first fetch the chunks' (max, sum) pairs side by side -- chunk
+    // c by lane c mod 16 -- and reduce them with shuffles; then every thread adds up its eight dims over the chunks,
+    // eight chunks' loads in flight at a time. (A loop that loads and uses one chunk after the other is a chain of S
+    // L2 round trips: with 37 chunks it was most of this kernel's time.)
     if (head < nh) {
+        const int sub = tid & 15;
+        const unsigned half_mask = 0xFFFFu << (tid & 16);
+        float *fsm = osm;  // [S][16] weights of the chunks (the warps' results above have been consumed)
+        constexpr int kMaxPer = 10;  // chunks per lane: S <= 160
+        float mc[kMaxPer], lc[kMaxPer];
+#pragma unroll
+        for (int i = 0; i < kMaxPer; i++) {
+            const int c = sub + 16 * i;
+            const size_t sl = (size_t)blockIdx.x * S + (c < S ? c : 0);
+            mc[i] = c < S ? __ldcg(P.ml + (sl * 2 + 0) * 16 + head) : -INFINITY;
+            lc[i] = c < S ? __ldcg(P.ml + (sl * 2 + 1) * 16 + head) : 0.0f;
+        }
         float Mt = -INFINITY;
-        for (int c = 0; c < S; c++) Mt = fmaxf(Mt, __ldcg(P.ml + (((size_t)blockIdx.x * S + c) * 2 + 0) * 16 + head));
-        float Lt = 0.0f, o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int c = 0; c < S; c++) {
-            const size_t sl = (size_t)blockIdx.x * S + c;
-            const float mc = __ldcg(P.ml + (sl * 2 + 0) * 16 + head);
-            const float f = (mc == -INFINITY) ? 0.0f : exp2f(mc - Mt);
-            Lt = fmaf(__ldcg(P.ml + (sl * 2 + 1) * 16 + head), f, Lt);
-            const float4 a = __ldcg(reinterpret_cast<const float4 *>(P.part + (sl * 16 + head) * kHD + d0));
-            const float4 b = __ldcg(reinterpret_cast<const float4 *>(P.part + (sl * 16 + head) * kHD + d0 + 4));
-            o[0] = fmaf(a.x, f, o[0]); o[1] = fmaf(a.y, f, o[1]); o[2] = fmaf(a.z, f, o[2]); o[3] = fmaf(a.w, f, o[3]);
-            o[4] = fmaf(b.x, f, o[4]); o[5] = fmaf(b.y, f, o[5]); o[6] = fmaf(b.z, f, o[6]); o[7] = fmaf(b.w, f, o[7]);
+#pragma unroll
+        for (int i = 0; i < kMaxPer; i++) Mt = fmaxf(Mt, mc[i]);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) Mt = fmaxf(Mt, __shfl_xor_sync(half_mask, Mt, o));
+        float Lt = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kMaxPer; i++) {
+            const int c = sub + 16 * i;
+            const float f = (mc[i] == -INFINITY) ? 0.0f : exp2f(mc[i] - Mt);
+            Lt = fmaf(lc[i], f, Lt);
+            if (c < S) fsm[c * 16 + head] = f;
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) Lt += __shfl_xor_sync(half_mask, Lt, o);
+        __syncwarp(half_mask);
+        float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int c0 = 0; c0 < S; c0 += 8) {
+            float4 a[8], b[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int c = min(c0 + u, S - 1);
+                const size_t sl = (size_t)blockIdx.x * S + c;
+                a[u] = __ldcg(reinterpret_cast<const float4 *>(P.part + (sl * 16 + head) * kHD + d0));
+                b[u] = __ldcg(reinterpret_cast<const float4 *>(P.part + (sl * 16 + head) * kHD + d0 + 4));
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const float f = (c0 + u < S) ? fsm[(c0 + u) * 16 + head] : 0.0f;  // in chunk order, as before
+                o[0] = fmaf(a[u].x, f, o[0]); o[1] = fmaf(a[u].y, f, o[1]); o[2] = fmaf(a[u].z, f, o[2]); o[3] = fmaf(a[u].w, f, o[3]);
+                o[4] = fmaf(b[u].x, f, o[4]); o[5] = fmaf(b[u].y, f, o[5]); o[6] = fmaf(b[u].z, f, o[6]); o[7] = fmaf(b[u].w, f, o[7]);
+            }
         }
         const float inv = Lt > 0.0f ? 1.0f / Lt : 0.0f;
         float *dst = P.out + (size_t)(h0 + head) * kHD + d0;
