@@ -368,15 +368,32 @@ __global__ void __launch_bounds__(kI8Warps * 32) attn_int8_kernel(const float *q
     __threadfence();
     for (int i = threadIdx.x; i < GQA * 128; i += blockDim.x) {
         const int h = i >> 7;
+        // eight chunks' loads in flight at a time (one chunk after the other would be a chain of L2 round trips)
         float M = -INFINITY;
-        for (int c = 0; c < chunks; c++) M = fmaxf(M, __ldcg(g_i8.ml + ((size_t)(grp * chunks + c) * kI8MaxGqa + h) * 2));
+        for (int c0 = 0; c0 < chunks; c0 += 8) {
+            float mv[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                mv[u] = c0 + u < chunks ? __ldcg(g_i8.ml + ((size_t)(grp * chunks + c0 + u) * kI8MaxGqa + h) * 2) : -INFINITY;
+#pragma unroll
+            for (int u = 0; u < 8; u++) M = fmaxf(M, mv[u]);
+        }
         float o = 0.0f, L = 0.0f;
-        for (int c = 0; c < chunks; c++) {
-            const size_t b = (size_t)(grp * chunks + c) * kI8MaxGqa;
-            const float mc = __ldcg(g_i8.ml + (b + h) * 2);
-            const float f = mc == -INFINITY ? 0.0f : __expf(mc - M);
-            o += __ldcg(g_i8.part + b * 128 + i) * f;
-            L += __ldcg(g_i8.ml + (b + h) * 2 + 1) * f;
+        for (int c0 = 0; c0 < chunks; c0 += 8) {
+            float mv[8], lv[8], pv[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const size_t b = (size_t)(grp * chunks + min(c0 + u, chunks - 1)) * kI8MaxGqa;
+                mv[u] = __ldcg(g_i8.ml + (b + h) * 2);
+                lv[u] = __ldcg(g_i8.ml + (b + h) * 2 + 1);
+                pv[u] = __ldcg(g_i8.part + b * 128 + i);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const float f = (c0 + u >= chunks || mv[u] == -INFINITY) ? 0.0f : __expf(mv[u] - M);
+                o += pv[u] * f;
+                L += lv[u] * f;
+            }
         }
         out[((size_t)grp * GQA) * 128 + i] = L > 0.0f ? o / L : 0.0f;
     }
