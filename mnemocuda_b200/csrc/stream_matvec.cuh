@@ -497,19 +497,29 @@ __device__ __forceinline__ void stream_body(const Params &P, uint8_t *smem)
                 mbar_init(&empty[s], kConsumers);
             }
             mbar_fence_init();
-            if (routed) {
-                // which experts to stream is decided by the upstream kernel (the router): wait for it first
-                if (P.pdl) grid_dep_wait();
-                int n = 0;
-                for (int e = 0; e < P.n_slots; e++) {
-                    const int id = __ldcg(P.ids + e);
-                    const bool here = id >= P.expert_lo && id - P.expert_lo < P.expert_cnt;  // empty slots have id < 0
-                    sid[e] = here ? id - P.expert_lo : -1;
-                    swt[e] = (!here || P.wts == nullptr) ? 0.0f : __ldcg(P.wts + e);  // gate/up has no routing weights
-                    if (here) act_list[n++] = e;
-                }
-                *n_act_p = n;
+        }
+        if (routed) {
+            // which experts to stream is decided by the upstream kernel (the router): wait for it first. Lane e reads
+            // slot e -- one round trip for all slots (one thread reading them in turn was a chain of 2 x n_slots
+            // round trips before the first weight byte could be requested) -- and a ballot compacts the served slots.
+            if (P.pdl) grid_dep_wait();
+            int id = -1;
+            float w = 0.0f;
+            if (lane < P.n_slots) {
+                id = __ldcg(P.ids + lane);
+                if (P.wts != nullptr) w = __ldcg(P.wts + lane);  // gate/up has no routing weights
             }
+            const bool here = lane < P.n_slots && id >= P.expert_lo && id - P.expert_lo < P.expert_cnt;  // empty slots have id < 0
+            const unsigned served = __ballot_sync(0xffffffffu, here);
+            if (lane < P.n_slots) {
+                sid[lane] = here ? id - P.expert_lo : -1;
+                swt[lane] = here ? w : 0.0f;
+            }
+            if (here) act_list[__popc(served & ((1u << lane) - 1u))] = lane;
+            if (lane == 0) *n_act_p = __popc(served);
+            __syncwarp();
+        }
+        if (lane == 0) {
             walk.init(P, act_list, routed ? *n_act_p : 0);
             Tile t;
             for (int s = 0; s < S; s++) {
