@@ -94,19 +94,22 @@ __global__ void __launch_bounds__(kPushThreads) push_collective_kernel(const Pus
     bool ok = true;
     const uint2 *mine = P.self.cells + par_off;
     for (int i = tid; i < P.n && ok; i += nthr) {
-        float acc = 0.0f;
-        for (int q = 0; q < P.world; q++) {  // fixed order: every rank computes the same bits
-            float v;
-            if (!wait_cell(mine + (size_t)q * P.max_floats + i, tag, v, t0)) {
-                ok = false;
-                break;
-            }
-            if (P.reduce)
-                acc = q == 0 ? v : acc + v;
-            else
-                P.out[(size_t)q * P.n + i] = v;
+        float v[kMaxWorld];
+        if (!wait_cells(mine + i, P.max_floats, P.world, tag, v, t0)) {
+            ok = false;
+            break;
         }
-        if (ok && P.reduce) P.out[i] = acc;
+        if (P.reduce) {
+            float acc = v[0];
+#pragma unroll
+            for (int q = 1; q < kMaxWorld; q++)  // fixed order: every rank computes the same bits
+                if (q < P.world) acc += v[q];
+            P.out[i] = acc;
+        } else {
+#pragma unroll
+            for (int q = 0; q < kMaxWorld; q++)
+                if (q < P.world) P.out[(size_t)q * P.n + i] = v[q];
+        }
     }
     if (!ok) atomicExch(P.err, MB200_ERR_TIMEOUT);
     // ---- the last CTA to finish publishes the sequence number for the next launch ----

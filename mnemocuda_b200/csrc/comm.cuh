@@ -50,4 +50,26 @@ __device__ __forceinline__ bool wait_cell(const uint2 *p, uint32_t tag, float &v
     }
 }
 
+// The cells of one element from every source rank (rank q's cell at p + q * stride): all of them are requested at
+// once -- the pieces arrive at about the same time, and polling them one after the other would cost a memory round
+// trip per rank -- and only a cell that does not carry `tag` yet is waited for. v[q] receives rank q's value.
+__device__ __forceinline__ bool wait_cells(const uint2 *p, size_t stride, int world, uint32_t tag, float (&v)[kMaxWorld],
+                                           long long t0)
+{
+    uint2 c[kMaxWorld];
+#pragma unroll
+    for (int q = 0; q < kMaxWorld; q++)
+        if (q < world) c[q] = ld_cell(p + (size_t)q * stride);
+#pragma unroll
+    for (int q = 0; q < kMaxWorld; q++) {
+        if (q >= world) break;
+        if (c[q].y == tag) {
+            v[q] = __uint_as_float(c[q].x);
+        } else if (!wait_cell(p + (size_t)q * stride, tag, v[q], t0)) {
+            return false;
+        }
+    }
+    return true;
+}
+
 }  // namespace mb200

@@ -388,16 +388,16 @@ __device__ __forceinline__ void push_collect(const FusedParams &P, unsigned long
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     bool ok = true;
     for (int row = r0 + lane; row < r1 && ok; row += 32) {
-        float acc = 0.0f;
-        for (int q = 0; q < P.push.world; q++) {  // fixed order: every rank computes the same bits
-            float v;
-            if (!wait_cell(P.push.self_cells + par_off + (size_t)q * P.push.max_floats + row, tag, v, t0)) {
-                ok = false;
-                break;
-            }
-            acc = q == 0 ? v : acc + v;
+        float v[kMaxWorld];
+        if (!wait_cells(P.push.self_cells + par_off + row, P.push.max_floats, P.push.world, tag, v, t0)) {
+            ok = false;
+            break;
         }
-        if (ok) P.y[row] = acc;
+        float acc = v[0];
+#pragma unroll
+        for (int q = 1; q < kMaxWorld; q++)  // fixed order: every rank computes the same bits
+            if (q < P.push.world) acc += v[q];
+        P.y[row] = acc;
     }
     if (!ok) atomicExch(P.err, MB200_ERR_TIMEOUT);
     __syncwarp();
